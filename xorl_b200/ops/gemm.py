@@ -1,0 +1,114 @@
+"""Dense GEMM on tcgen05 (``csrc/gemm.cu``) and the ``linear`` autograd function built on it.
+
+``gemm(a, b, a_mn, b_mn)`` computes ``op(a) @ op(b).T`` where an operand flagged ``*_mn`` is
+stored transposed (reduction dimension outermost).  Forward, dgrad and wgrad of a linear layer
+are the three layout combinations (K,K), (K,MN) and (MN,MN), so no transpose copy is ever made.
+Replaces ``F.linear`` / cuBLAS in the reference (every nn.Linear, e.g.
+src/xorl/models/transformers/qwen3/modeling_qwen3.py:40-81).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+_launches = 0
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+         accumulate: bool = False) -> torch.Tensor:
+    """C[M,N] (+)= op(a)[M,K] @ op(b)[N,K]^T with fp32 accumulation."""
+    assert a.dim() == 2 and b.dim() == 2
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"reduction dims differ: {K} vs {Kb}"
+    if not a.is_cuda:
+        A = a.t() if a_mn else a
+        B = b.t() if b_mn else b
+        res = (A.float() @ B.float().t())
+        dt = out.dtype if out is not None else (out_dtype or a.dtype)
+        if out is not None:
+            if accumulate:
+                out.add_(res.to(dt))
+            else:
+                out.copy_(res.to(dt))
+            return out
+        return res.to(dt)
+    global _launches
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "bf16 operands required"
+    if a.stride(1) != 1 or a.stride(0) % 8 or a.data_ptr() % 16:
+        a = a.contiguous()
+    if b.stride(1) != 1 or b.stride(0) % 8 or b.data_ptr() % 16:
+        b = b.contiguous()
+    if a.stride(0) % 8 or b.stride(0) % 8:
+        # leading dimensions must be multiples of 8 elements for TMA: pad the reduction dim
+        raise ValueError("gemm operands need leading dimensions that are multiples of 8")
+    if out is None:
+        out = torch.empty((M, N), device=a.device, dtype=out_dtype or torch.bfloat16)
+        assert not accumulate
+    assert out.shape == (M, N) and out.stride(1) == 1
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    rc = _lib.cuda_lib().xb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+        out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate),
+        _lib.stream_ptr())
+    _lib.check(rc, "xb_gemm_bf16")
+    _launches += 1
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x @ w.T.  The weight is kept on ctx as a plain attribute (not through
+    save_for_backward) because ZeRO-3 re-fills the same gathered buffer before backward."""
+
+    @staticmethod
+    def forward(ctx, x, w, wgrad_out):
+        ctx.x_shape = x.shape
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(x2)
+        ctx.w = w
+        ctx.wgrad_out = wgrad_out
+        y = gemm(x2, w)
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2,) = ctx.saved_tensors
+        w = ctx.w
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).reshape(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            tgt = ctx.wgrad_out
+            if tgt is not None:
+                # accumulate straight into the flat gradient buffer of the ZeRO unit
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=tgt, accumulate=True)
+                dw = None
+                w._xb_grad_written = True
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        return dx, dw, None
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """Linear layer through the tcgen05 GEMM (CUDA) or torch (CPU)."""
+    if not x.is_cuda:
+        return torch.nn.functional.linear(x, w, bias)
+    y = _Linear.apply(x, w, getattr(w, "_xb_grad_buf", None))
+    if bias is not None:
+        y = y + bias
+    return y
