@@ -14,7 +14,7 @@
 // (src/xorl/models/layers/attention/backend/flash_attention.py:382-531).
 #include "common.cuh"
 
-namespace xb_attn_fwd {
+namespace xb_attn_fwd_ns {
 
 constexpr int D = 128;
 constexpr int BQ = 128;
@@ -347,7 +347,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
 }
 
-}  // namespace xb_attn_fwd
+}  // namespace xb_attn_fwd_ns
 
 // q: [T, Hq, 128] with token stride ldq;  k, v: [T, Hkv, 128] with token strides ldk, ldv;
 // out: [T, Hq, 128] token stride ldo;  lse: [Hq, T] fp32;  cu_seqlens: int32 [num_seqs + 1] on the
@@ -356,7 +356,7 @@ XB_API int xb_attn_fwd(const void* q, const void* k, const void* v, void* out, f
                        const int* cu_seqlens, long long ldq, long long ldk, long long ldv,
                        long long ldo, int num_seqs, int T, int Hq, int Hkv, int D, int causal,
                        float scale, int max_tiles, void* stream) {
-  using namespace xb_attn_fwd;
+  using namespace xb_attn_fwd_ns;
   if (D != 128) return -1;
   if (T <= 0 || num_seqs <= 0) return 0;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8) || Hq % Hkv) return -1;

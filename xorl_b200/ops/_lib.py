@@ -52,7 +52,7 @@ _SIGNATURES = {
     "xb_stochastic_round": [P, P, L, c_uint, P],
     "xb_cast_accum": [P, P, L, F, I, P],
     "xb_attn_fwd": [P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, F, I, P],
-    "xb_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, I, I, I, I, I, I, F, I, P],
+    "xb_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, I, I, I, I, I, I, F, I, P],
 }
 
 

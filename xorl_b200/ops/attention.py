@@ -1,0 +1,233 @@
+"""Variable-length flash attention (``csrc/attn_fwd.cu`` / ``csrc/attn_bwd.cu``) and the fused
+qk-RMSNorm + RoPE + attention block used by the decoder layers.
+
+Layout is the packed one of the reference's varlen path
+(src/xorl/models/layers/attention/backend/flash_attention.py:295-532): tokens of all sequences
+concatenated, ``cu_seqlens`` int32 prefix sums, q ``[T, Hq, D]``, k/v ``[T, Hkv, D]``.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from .grad_sink import deliver_param_grad
+
+_launches = 0
+
+
+def launch_count() -> int:
+    return _launches
+
+
+# --------------------------------------------------------------------------------------------
+# Reference implementations (CPU lane and test oracle)
+# --------------------------------------------------------------------------------------------
+def attention_reference(q, k, v, cu_seqlens, causal=True, scale=None):
+    """Plain fp32 attention over packed sequences. q [T,Hq,D], k/v [T,Hkv,D]."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    out = torch.empty_like(q)
+    cu = cu_seqlens.tolist()
+    g = Hq // Hkv
+    for b in range(len(cu) - 1):
+        s, e = cu[b], cu[b + 1]
+        if e <= s:
+            continue
+        qb = q[s:e].float().transpose(0, 1)                      # [Hq, L, D]
+        kb = k[s:e].float().transpose(0, 1).repeat_interleave(g, 0)
+        vb = v[s:e].float().transpose(0, 1).repeat_interleave(g, 0)
+        sc = torch.matmul(qb, kb.transpose(1, 2)) * scale
+        if causal:
+            L = e - s
+            mask = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+            sc = sc.masked_fill(~mask, float("-inf"))
+        p = torch.softmax(sc, dim=-1)
+        out[s:e] = torch.matmul(p, vb).transpose(0, 1).to(q.dtype)
+    return out
+
+
+def rope_reference(x, cos, sin):
+    """Rotate-half RoPE. x [T, H, D]; cos/sin [T, D/2]."""
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    c, s = cos[:, None, :].float(), sin[:, None, :].float()
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
+def _head_rmsnorm_ref(x, w, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+
+
+def qk_norm_rope_attention_reference(qkv, wq, wk, cos, sin, cu_seqlens, Hq, Hkv, D, eps, causal,
+                                     scale):
+    T = qkv.shape[0]
+    q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    q = q.reshape(T, Hq, D)
+    k = k.reshape(T, Hkv, D)
+    v = v.reshape(T, Hkv, D)
+    if wq is not None:
+        q = _head_rmsnorm_ref(q, wq, eps)
+        k = _head_rmsnorm_ref(k, wk, eps)
+    q = rope_reference(q, cos, sin)
+    k = rope_reference(k, cos, sin)
+    return attention_reference(q, k, v, cu_seqlens, causal, scale).reshape(T, Hq * D)
+
+
+# --------------------------------------------------------------------------------------------
+# CUDA path
+# --------------------------------------------------------------------------------------------
+def _attn_fwd(q, k, v, cu_seqlens, causal, scale):
+    global _launches
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    out = torch.empty((T, Hq, D), device=q.device, dtype=q.dtype)
+    lse = torch.empty((Hq, T), device=q.device, dtype=torch.float32)
+    nseq = cu_seqlens.numel() - 1
+    rc = _lib.cuda_lib().xb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                     lse.data_ptr(), cu_seqlens.data_ptr(), q.stride(0),
+                                     k.stride(0), v.stride(0), out.stride(0), nseq, T, Hq, Hkv, D,
+                                     int(causal), float(scale), 0, _lib.stream_ptr())
+    _lib.check(rc, "xb_attn_fwd")
+    _launches += 1
+    return out, lse
+
+
+def _attn_bwd(q, k, v, out, dout, lse, cu_seqlens, causal, scale, dv_out):
+    """Returns dq fp32 [T,Hq,D], dk fp32 [T,Hkv,D]; writes dv (bf16) into ``dv_out``."""
+    global _launches
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    delta = torch.empty((Hq, T), device=q.device, dtype=torch.float32)
+    dq = torch.empty((T, Hq, D), device=q.device, dtype=torch.float32)
+    dk = torch.empty((T, Hkv, D), device=q.device, dtype=torch.float32)
+    nseq = cu_seqlens.numel() - 1
+    rc = _lib.cuda_lib().xb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                     dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                                     dq.data_ptr(), dk.data_ptr(), dv_out.data_ptr(),
+                                     cu_seqlens.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
+                                     out.stride(0), dout.stride(0), dv_out.stride(0), nseq, T, Hq,
+                                     Hkv, D, int(causal), float(scale), 0, _lib.stream_ptr())
+    _lib.check(rc, "xb_attn_bwd")
+    _launches += 3
+    return dq, dk
+
+
+def _kernel_ok(t: torch.Tensor, D: int) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and D == 128
+
+
+class _FlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, causal, scale):
+        def fix(t):
+            if t.stride(2) != 1 or t.stride(1) != t.shape[2] or t.stride(0) % 8 or t.data_ptr() % 16:
+                return t.contiguous()
+            return t
+        q, k, v = fix(q), fix(k), fix(v)
+        out, lse = _attn_fwd(q, k, v, cu_seqlens, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        dout = dout.contiguous()
+        dv = torch.empty_like(v.contiguous())
+        dq, dk = _attn_bwd(q, k, v, out, dout, lse, cu, ctx.causal, ctx.scale, dv)
+        return dq.to(q.dtype), dk.to(k.dtype), dv, None, None, None
+
+
+def flash_attn_varlen(q, k, v, cu_seqlens, causal=True, scale=None):
+    """Packed varlen attention. q [T,Hq,D], k/v [T,Hkv,D], cu_seqlens int32 [B+1]."""
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if _kernel_ok(q, D):
+        return _FlashAttn.apply(q, k, v, cu_seqlens, causal, scale)
+    return attention_reference(q, k, v, cu_seqlens, causal, scale)
+
+
+class _QKNormRopeAttn(torch.autograd.Function):
+    """qkv [T, (Hq+2Hkv)*D] -> attention output [T, Hq*D]: per-head RMSNorm on q and k (optional),
+    rotate-half RoPE, causal varlen attention.  The v slice is consumed in place through a strided
+    view, and backward writes dq/dk/dv straight into one dqkv buffer."""
+
+    @staticmethod
+    def forward(ctx, qkv, wq, wk, cos, sin, cu_seqlens, Hq, Hkv, D, eps, causal, scale):
+        global _launches
+        T = qkv.shape[0]
+        if not qkv.is_contiguous():
+            qkv = qkv.contiguous()
+        do_norm = wq is not None
+        lib = _lib.cuda_lib()
+        qk = torch.empty((T, (Hq + Hkv) * D), device=qkv.device, dtype=qkv.dtype)
+        rstd = torch.empty((T, Hq + Hkv), device=qkv.device, dtype=torch.float32) if do_norm else None
+        _lib.check(lib.xb_qk_norm_rope_fwd(qkv.data_ptr(), qkv.stride(0), _lib.ptr(wq), _lib.ptr(wk),
+                                           cos.data_ptr(), sin.data_ptr(), qk.data_ptr(),
+                                           qk.stride(0), _lib.ptr(rstd), T, Hq, Hkv, D, float(eps),
+                                           int(do_norm), _lib.stream_ptr()), "xb_qk_norm_rope_fwd")
+        _launches += 1
+        q = qk[:, :Hq * D].view(T, Hq, D)
+        k = qk[:, Hq * D:].view(T, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+        out, lse = _attn_fwd(q, k, v, cu_seqlens, causal, scale)
+        ctx.save_for_backward(qkv, qk, out, lse, cos, sin, cu_seqlens, rstd)
+        ctx.wq, ctx.wk = wq, wk
+        ctx.cfg = (Hq, Hkv, D, eps, causal, scale)
+        return out.view(T, Hq * D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        global _launches
+        qkv, qk, out, lse, cos, sin, cu, rstd = ctx.saved_tensors
+        Hq, Hkv, D, eps, causal, scale = ctx.cfg
+        wq, wk = ctx.wq, ctx.wk
+        do_norm = wq is not None
+        T = qkv.shape[0]
+        dout = dout.reshape(T, Hq, D)
+        if not dout.is_contiguous():
+            dout = dout.contiguous()
+        q = qk[:, :Hq * D].view(T, Hq, D)
+        k = qk[:, Hq * D:].view(T, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+        dqkv = torch.empty_like(qkv)
+        dv = dqkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+        dq, dk = _attn_bwd(q, k, v, out, dout, lse, cu, causal, scale, dv)
+        lib = _lib.cuda_lib()
+        partial = dwq = dwk = None
+        if do_norm:
+            rows = lib.xb_qk_norm_rope_bwd_partial_rows()
+            partial = torch.empty(rows * 2 * D, device=qkv.device, dtype=torch.float32)
+            dwq = torch.zeros(D, device=qkv.device, dtype=torch.bfloat16)
+            dwk = torch.zeros(D, device=qkv.device, dtype=torch.bfloat16)
+        _lib.check(lib.xb_qk_norm_rope_bwd(None, dq.data_ptr(), dk.data_ptr(), 0, qkv.data_ptr(),
+                                           qkv.stride(0), _lib.ptr(wq), _lib.ptr(wk), cos.data_ptr(),
+                                           sin.data_ptr(), _lib.ptr(rstd), dqkv.data_ptr(),
+                                           dqkv.stride(0), _lib.ptr(partial), _lib.ptr(dwq),
+                                           _lib.ptr(dwk), 0, T, Hq, Hkv, D, int(do_norm),
+                                           _lib.stream_ptr()), "xb_qk_norm_rope_bwd")
+        _launches += 4 if do_norm else 1
+        gq = gk = None
+        if do_norm:
+            gq = deliver_param_grad(wq, dwq)
+            gk = deliver_param_grad(wk, dwk)
+        return dqkv, gq, gk, None, None, None, None, None, None, None, None, None
+
+
+def qk_norm_rope_attention(qkv, wq, wk, cos, sin, cu_seqlens, Hq, Hkv, D, eps=1e-6, causal=True,
+                           scale=None):
+    """Fused attention block over a packed qkv activation.
+
+    qkv: [T, (Hq + 2*Hkv) * D]; wq/wk: per-head RMSNorm weights [D] or None (no qk-norm);
+    cos/sin: fp32 [T, D/2] gathered at each token's position.  Returns [T, Hq*D].
+    """
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if _kernel_ok(qkv, D):
+        return _QKNormRopeAttn.apply(qkv, wq, wk, cos, sin, cu_seqlens, Hq, Hkv, D, eps, causal,
+                                     scale)
+    return qk_norm_rope_attention_reference(qkv, wq, wk, cos, sin, cu_seqlens, Hq, Hkv, D, eps,
+                                            causal, scale)

@@ -11,6 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
+from .grad_sink import grad_target, mark_written
 
 _launches = 0
 
@@ -73,12 +74,13 @@ class _Linear(torch.autograd.Function):
     save_for_backward) because ZeRO-3 re-fills the same gathered buffer before backward."""
 
     @staticmethod
-    def forward(ctx, x, w, wgrad_out):
+    def forward(ctx, x, w):
         ctx.x_shape = x.shape
         x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
         ctx.save_for_backward(x2)
         ctx.w = w
-        ctx.wgrad_out = wgrad_out
         y = gemm(x2, w)
         return y.reshape(*x.shape[:-1], w.shape[0])
 
@@ -93,22 +95,23 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).reshape(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            tgt = ctx.wgrad_out
+            tgt, fresh = grad_target(w)
             if tgt is not None:
-                # accumulate straight into the flat gradient buffer of the ZeRO unit
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=tgt, accumulate=True)
-                dw = None
-                w._xb_grad_written = True
+                # write straight into the flat gradient buffer of the ZeRO unit
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=tgt, accumulate=not fresh)
+                mark_written(w)
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
-        return dx, dw, None
+        return dx, dw
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """Linear layer through the tcgen05 GEMM (CUDA) or torch (CPU)."""
     if not x.is_cuda:
         return torch.nn.functional.linear(x, w, bias)
-    y = _Linear.apply(x, w, getattr(w, "_xb_grad_buf", None))
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[-1] % 8:
+        return torch.nn.functional.linear(x, w, bias)
+    y = _Linear.apply(x, w)
     if bias is not None:
         y = y + bias
     return y

@@ -1,0 +1,39 @@
+"""Where custom autograd functions put parameter gradients.
+
+The ZeRO engine points every parameter of the unit that is running backward at its slice of the
+unit's flat gradient buffer (``p._xb_grad_buf``).  Kernels that can accumulate in their epilogue
+(the wgrad GEMM) write there directly; everything else hands its gradient to
+``deliver_param_grad`` which adds it to the slice.  Without an engine (plain autograd use, unit
+tests) the gradient is simply returned to autograd.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def grad_target(p: torch.Tensor):
+    """(buffer view or None, fresh) — ``fresh`` means nothing has been written yet in this
+    backward pass, so the first writer may overwrite instead of accumulate."""
+    buf = getattr(p, "_xb_grad_buf", None)
+    if buf is None:
+        return None, False
+    return buf, getattr(p, "_xb_grad_fresh", False)
+
+
+def mark_written(p: torch.Tensor) -> None:
+    p._xb_grad_fresh = False
+
+
+def deliver_param_grad(p: torch.Tensor, g: torch.Tensor):
+    """Adds ``g`` to the engine's buffer and returns None, or returns ``g`` cast to the parameter
+    dtype when no engine buffer is attached."""
+    buf, fresh = grad_target(p)
+    if buf is None:
+        return g.to(p.dtype).reshape(p.shape)
+    g = g.reshape(buf.shape)
+    if fresh:
+        buf.copy_(g)
+        mark_written(p)
+    else:
+        buf.add_(g.to(buf.dtype))
+    return None

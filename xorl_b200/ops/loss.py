@@ -1,0 +1,134 @@
+"""Cross-entropy and the fused lm-head + cross-entropy (``csrc/loss.cu`` + tcgen05 GEMMs).
+
+``fused_linear_cross_entropy`` never materialises ``[tokens, vocab]`` logits beyond one token
+chunk (bf16) and computes the gradients of hidden states and lm-head weight in the same pass, in
+the spirit of the reference's chunked lm-head loss (src/xorl/ops/loss/causallm_loss.py:445-864).
+Loss reduction is a **sum** over valid tokens (labels != ignore_index); callers divide by the
+global token count (src/xorl/distributed/gradient_accumulate_loss.py:7-64).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .gemm import gemm
+from .grad_sink import deliver_param_grad, grad_target, mark_written
+
+IGNORE_INDEX = -100
+_launches = 0
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def cross_entropy_sum_reference(logits: torch.Tensor, labels: torch.Tensor,
+                                ignore_index: int = IGNORE_INDEX) -> torch.Tensor:
+    return F.cross_entropy(logits.float(), labels, ignore_index=ignore_index, reduction="sum")
+
+
+def ce_chunk_(logits: torch.Tensor, labels: torch.Tensor, grad_scale: float, write_grad: bool,
+              ignore_index: int = IGNORE_INDEX, z_loss: float = 0.0):
+    """Per-row losses and LSE of a bf16 logits chunk; rewrites ``logits`` with d(loss)/d(logits)
+    times ``grad_scale`` when ``write_grad``."""
+    global _launches
+    rows, V = logits.shape
+    loss = torch.empty(rows, device=logits.device, dtype=torch.float32)
+    lse = torch.empty(rows, device=logits.device, dtype=torch.float32)
+    _lib.check(_lib.cuda_lib().xb_cross_entropy(logits.data_ptr(), logits.stride(0),
+                                                labels.data_ptr(), loss.data_ptr(), lse.data_ptr(),
+                                                rows, V, ignore_index, float(grad_scale),
+                                                int(write_grad), float(z_loss), _lib.stream_ptr()),
+               "xb_cross_entropy")
+    _launches += 1
+    return loss, lse
+
+
+class _FusedLinearCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, grad_scale, chunk_tokens, ignore_index, z_loss,
+                want_logprobs):
+        T, H = hidden.shape
+        V = weight.shape[0]
+        need_dh = hidden.requires_grad
+        need_dw = weight.requires_grad
+        dh = torch.empty_like(hidden) if need_dh else None
+        tgt, fresh = grad_target(weight) if need_dw else (None, False)
+        dw_local = None
+        if need_dw and tgt is None:
+            dw_local = torch.zeros((V, H), device=hidden.device, dtype=torch.float32)
+        losses = torch.empty(T, device=hidden.device, dtype=torch.float32)
+        ldv = (V + 7) // 8 * 8
+        buf = torch.empty((min(chunk_tokens, T), ldv), device=hidden.device, dtype=torch.bfloat16)
+        first = True
+        for s in range(0, T, chunk_tokens):
+            e = min(T, s + chunk_tokens)
+            h = hidden[s:e]
+            logits = buf[: e - s, :V]
+            gemm(h, weight, out=logits)
+            l, _ = ce_chunk_(logits, labels[s:e], grad_scale, need_dh or need_dw, ignore_index,
+                             z_loss)
+            losses[s:e] = l
+            if need_dh:
+                gemm(logits, weight, b_mn=True, out=dh[s:e])
+            if need_dw:
+                if tgt is not None:
+                    gemm(logits, h, a_mn=True, b_mn=True, out=tgt, accumulate=not (fresh and first))
+                else:
+                    gemm(logits, h, a_mn=True, b_mn=True, out=dw_local, accumulate=True)
+            first = False
+        if need_dw and tgt is not None:
+            mark_written(weight)
+        ctx.dh = dh
+        ctx.dw_local = dw_local
+        ctx.weight = weight
+        loss_sum = losses.sum()
+        if want_logprobs:
+            ctx.mark_non_differentiable(losses)
+            return loss_sum * grad_scale, losses
+        return loss_sum * grad_scale, None
+
+    @staticmethod
+    def backward(ctx, g, _g2):
+        dh = ctx.dh
+        if dh is not None:
+            dh = dh * g.to(dh.dtype)
+        dw = None
+        if ctx.dw_local is not None:
+            dw = deliver_param_grad(ctx.weight, ctx.dw_local * g)
+        ctx.dh = ctx.dw_local = None
+        return dh, dw, None, None, None, None, None, None
+
+
+def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                               grad_scale: float = 1.0, chunk_tokens: int = 1024,
+                               ignore_index: int = IGNORE_INDEX, z_loss: float = 0.0,
+                               return_token_losses: bool = False):
+    """``grad_scale * sum_t CE(hidden[t] @ weight.T, labels[t])``.
+
+    The lm-head weight gradient is produced during the forward call with the scale folded in, so
+    the returned scalar must be back-propagated with an upstream gradient of 1 (``loss.backward()``
+    directly on it or on a sum it is part of).
+    """
+    if hidden.is_cuda and hidden.dtype == torch.bfloat16 and hidden.shape[-1] % 8 == 0:
+        loss, tl = _FusedLinearCE.apply(hidden.reshape(-1, hidden.shape[-1]), weight,
+                                        labels.reshape(-1), float(grad_scale), int(chunk_tokens),
+                                        int(ignore_index), float(z_loss), bool(return_token_losses))
+        return (loss, tl) if return_token_losses else loss
+    # CPU / fp32 lane: chunked plain torch, same reduction
+    h2 = hidden.reshape(-1, hidden.shape[-1])
+    lab = labels.reshape(-1)
+    total = hidden.new_zeros((), dtype=torch.float32)
+    tls = []
+    for s in range(0, h2.shape[0], chunk_tokens):
+        logits = F.linear(h2[s:s + chunk_tokens], weight).float()
+        tl = F.cross_entropy(logits, lab[s:s + chunk_tokens], ignore_index=ignore_index,
+                             reduction="none")
+        if z_loss:
+            lse = torch.logsumexp(logits, dim=-1)
+            tl = tl + z_loss * lse.pow(2) * (lab[s:s + chunk_tokens] != ignore_index)
+        total = total + tl.sum()
+        tls.append(tl.detach())
+    loss = total * grad_scale
+    return (loss, torch.cat(tls)) if return_token_losses else loss
