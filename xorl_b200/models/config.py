@@ -1,0 +1,185 @@
+"""Model configuration shared by every decoder family.
+
+Reads Hugging Face ``config.json`` files (or a plain dict) and normalises the family-specific
+spellings into one dataclass; the per-family registry entries in ``registry.py`` only set flags.
+Covers the fields the reference's family configs read (src/xorl/models/transformers/*/configuration_*.py).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import asdict, dataclass, field, fields
+from typing import Any, Dict, List, Optional
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "qwen3"
+    architectures: List[str] = field(default_factory=list)
+    vocab_size: int = 151936
+    hidden_size: int = 4096
+    intermediate_size: int = 12288
+    num_hidden_layers: int = 36
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: Optional[int] = None
+    hidden_act: str = "silu"
+    max_position_embeddings: int = 40960
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    rope_scaling: Optional[Dict[str, Any]] = None
+    partial_rotary_factor: float = 1.0
+    tie_word_embeddings: bool = False
+    attention_bias: bool = False
+    attention_dropout: float = 0.0
+    mlp_bias: bool = False
+    use_qk_norm: bool = True
+    qk_norm_full: bool = False          # olmo2: RMSNorm over the whole projection, not per head
+    norm_placement: str = "pre"         # "pre" (llama/qwen) or "post" (olmo2)
+    zero_centered_norm: bool = False
+    sliding_window: Optional[int] = None
+    layer_types: Optional[List[str]] = None
+    initializer_range: float = 0.02
+    torch_dtype: str = "bfloat16"
+    # ---- mixture of experts -----------------------------------------------------------------
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    shared_expert_intermediate_size: int = 0
+    n_shared_experts: int = 0
+    norm_topk_prob: bool = True
+    decoder_sparse_step: int = 1
+    mlp_only_layers: List[int] = field(default_factory=list)
+    first_k_dense_replace: int = 0
+    router_aux_loss_coef: float = 0.001
+    output_router_logits: bool = False
+    scoring_func: str = "softmax"       # softmax | sigmoid
+    routed_scaling_factor: float = 1.0
+    n_group: int = 1
+    topk_group: int = 1
+    router_bias: bool = False
+    expert_bias: bool = False
+    swiglu_limit: Optional[float] = None
+    attention_sinks: bool = False
+    extra: Dict[str, Any] = field(default_factory=dict)
+
+    def __post_init__(self):
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if self.num_key_value_heads is None:
+            self.num_key_value_heads = self.num_attention_heads
+
+    # -- derived ------------------------------------------------------------------------------
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_is_moe(self, idx: int) -> bool:
+        if not self.is_moe or idx in self.mlp_only_layers or idx < self.first_k_dense_replace:
+            return False
+        return (idx + 1) % max(1, self.decoder_sparse_step) == 0
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def num_parameters(self, include_embeddings: bool = True) -> int:
+        H, I, L = self.hidden_size, self.intermediate_size, self.num_hidden_layers
+        attn = H * (self.q_size + 2 * self.kv_size) + self.q_size * H
+        if self.use_qk_norm:
+            attn += 2 * self.head_dim
+        total = 0
+        for i in range(L):
+            total += attn + 2 * H
+            if self.layer_is_moe(i):
+                total += H * self.num_experts + self.num_experts * 3 * H * self.moe_intermediate_size
+                total += 3 * H * self.shared_expert_intermediate_size
+            else:
+                total += 3 * H * I
+        total += H
+        if include_embeddings:
+            total += self.vocab_size * H * (1 if self.tie_word_embeddings else 2)
+        return total
+
+    # -- io -----------------------------------------------------------------------------------
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "ModelConfig":
+        d = dict(d)
+        known = {f.name for f in fields(cls)}
+        # family-specific spellings
+        if "num_local_experts" in d and "num_experts" not in d:
+            d["num_experts"] = d.pop("num_local_experts")
+        if "n_routed_experts" in d and "num_experts" not in d:
+            d["num_experts"] = d.pop("n_routed_experts")
+        if "experts_per_token" in d and "num_experts_per_tok" not in d:
+            d["num_experts_per_tok"] = d.pop("experts_per_token")
+        if "rope_parameters" in d and isinstance(d["rope_parameters"], dict):
+            rp = d.pop("rope_parameters")
+            d.setdefault("rope_theta", rp.get("rope_theta", 1e6))
+            if rp.get("rope_type", "default") != "default":
+                d.setdefault("rope_scaling", rp)
+        mt = d.get("model_type", "qwen3")
+        if "use_qk_norm" not in d:
+            d["use_qk_norm"] = mt in ("qwen3", "qwen3_moe", "olmo2", "qwen3_5", "qwen3_5_moe",
+                                      "glm4_moe") and d.get("use_qk_norm", True)
+        if mt == "olmo2":
+            d.setdefault("norm_placement", "post")
+            d.setdefault("qk_norm_full", True)
+        if mt in ("qwen2",):
+            d.setdefault("attention_bias", True)
+            d["use_qk_norm"] = False
+        if mt in ("llama",):
+            d["use_qk_norm"] = False
+        extra = {k: d.pop(k) for k in list(d) if k not in known}
+        cfg = cls(**d)
+        cfg.extra = extra
+        return cfg
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "ModelConfig":
+        p = path if path.endswith(".json") else os.path.join(path, "config.json")
+        with open(p) as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self) -> Dict[str, Any]:
+        d = asdict(self)
+        extra = d.pop("extra", {})
+        d.update(extra)
+        return d
+
+    def save_pretrained(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, "config.json"), "w") as f:
+            json.dump(self.to_dict(), f, indent=2)
+
+
+# Named presets for the benchmark configurations (architecture only; weights are random-init).
+PRESETS: Dict[str, Dict[str, Any]] = {
+    "tiny-qwen3": dict(model_type="qwen3", vocab_size=1024, hidden_size=256, intermediate_size=768,
+                       num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                       rope_theta=1e6, tie_word_embeddings=True, max_position_embeddings=4096),
+    "qwen3-8b": dict(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+                     num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                     rope_theta=1e6, tie_word_embeddings=False),
+    "qwen3-32b": dict(model_type="qwen3", vocab_size=151936, hidden_size=5120, intermediate_size=25600,
+                      num_hidden_layers=64, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                      rope_theta=1e6, tie_word_embeddings=False),
+    "qwen3-30b-a3b": dict(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048,
+                          intermediate_size=6144, num_hidden_layers=48, num_attention_heads=32,
+                          num_key_value_heads=4, head_dim=128, rope_theta=1e6, num_experts=128,
+                          num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True,
+                          router_aux_loss_coef=1e-3, tie_word_embeddings=False),
+    "llama3-8b": dict(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                      num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
+                      rope_theta=5e5, rms_norm_eps=1e-5, tie_word_embeddings=False, use_qk_norm=False),
+}
+
+
+def preset(name: str, **overrides) -> ModelConfig:
+    d = dict(PRESETS[name])
+    d.update(overrides)
+    return ModelConfig.from_dict(d)

@@ -1,0 +1,182 @@
+"""Generic decoder-only language model used by the dense and MoE families.
+
+The model is organised as *units* — embedding, each decoder layer, head (final norm + lm_head) —
+which is the granularity at which the ZeRO-3 engine gathers parameters, recomputes activations
+and reduce-scatters gradients.  Between units the activation is the pair ``(h, residual)`` whose
+sum is the residual stream, so every RMSNorm runs fused with the preceding residual add
+(src/xorl/models/transformers/qwen3/modeling_qwen3.py:98-156 has the same fused pre-norm).
+Without an engine, ``forward`` runs everything under ordinary autograd.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Optional
+
+import torch
+from torch import nn
+
+from ..ops import embedding as emb_ops
+from ..ops import loss as loss_ops
+from .config import ModelConfig
+from .context import StepContext, cu_seqlens_from_position_ids, packed_metadata_from_padded
+from .layers import MLP, Attention, Linear, RMSNorm
+from .rope import RotaryEmbedding
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.post_norm = cfg.norm_placement == "post"
+        self.self_attn = Attention(cfg, layer_idx, dtype=dtype, device=device)
+        if cfg.layer_is_moe(layer_idx):
+            from .moe import MoEBlock
+            self.mlp = MoEBlock(cfg, layer_idx, dtype=dtype, device=device)
+        else:
+            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.mlp_bias, dtype=dtype,
+                           device=device)
+        zc = cfg.zero_centered_norm
+        if self.post_norm:
+            self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, zc, dtype, device)
+            self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, zc, dtype, device)
+        else:
+            self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, zc, dtype, device)
+            self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, zc, dtype, device)
+
+    def forward(self, h: torch.Tensor, residual: Optional[torch.Tensor], ctx: StepContext):
+        if self.post_norm:
+            x = h if residual is None else h + residual
+            x = x + self.post_attention_layernorm(self.self_attn(x, ctx))
+            x = x + self.post_feedforward_layernorm(self._mlp(x, ctx))
+            return x, None
+        if residual is None:
+            y, x = self.input_layernorm(h), h
+        else:
+            y, x = self.input_layernorm(h, residual=residual)
+        a = self.self_attn(y, ctx)
+        y, x = self.post_attention_layernorm(a, residual=x)
+        return self._mlp(y, ctx), x
+
+    def _mlp(self, y, ctx):
+        if isinstance(self.mlp, MLP):
+            return self.mlp(y)
+        return self.mlp(y, ctx)
+
+
+class DecoderLM(nn.Module):
+    """Causal language model over packed sequences."""
+
+    def __init__(self, cfg: ModelConfig, dtype=None, device=None):
+        super().__init__()
+        self.config = cfg
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+        self.layers = nn.ModuleList(DecoderLayer(cfg, i, dtype, device)
+                                    for i in range(cfg.num_hidden_layers))
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.zero_centered_norm, dtype, device)
+        self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, bias=False, dtype=dtype, device=device)
+        if cfg.tie_word_embeddings:
+            self.lm_head.weight = self.embed_tokens.weight
+        self.rotary = RotaryEmbedding(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling,
+                                      cfg.partial_rotary_factor, cfg.max_position_embeddings)
+        self.loss_chunk_tokens = 1024
+        self.cp_strategy = None
+
+    # ---- initialisation ---------------------------------------------------------------------
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0) -> None:
+        """N(0, initializer_range) for matrices and embeddings, ones (zeros if zero-centred) for
+        norm weights, zeros for biases.  Each parameter draws from its own generator seeded by
+        (seed, position in named_parameters) so the result does not depend on how parameters are
+        later sharded."""
+        std = self.config.initializer_range
+        for idx, (name, p) in enumerate(self.named_parameters()):
+            init_parameter_(name, p, std, seed, idx, self.config.zero_centered_norm)
+
+    # ---- unit-level API used by the engine ------------------------------------------------------
+    def make_context(self, input_ids, position_ids=None, cu_seqlens=None, causal=True,
+                     training=True) -> StepContext:
+        dev = input_ids.device
+        if input_ids.dim() == 2 and position_ids is None and cu_seqlens is None:
+            B, S = input_ids.shape
+            cu_seqlens, position_ids = packed_metadata_from_padded(B, S, dev)
+        if position_ids is None:
+            cu = cu_seqlens.to(torch.int64)
+            T = input_ids.numel()
+            idx = torch.arange(T, device=dev)
+            seg = torch.searchsorted(cu[1:].contiguous(), idx, right=True)
+            position_ids = idx - cu[seg]
+        position_ids = position_ids.reshape(-1)
+        if cu_seqlens is None:
+            cu_seqlens = cu_seqlens_from_position_ids(position_ids)
+        cu_seqlens = cu_seqlens.to(device=dev, dtype=torch.int32)
+        ctx = StepContext(cu_seqlens=cu_seqlens, position_ids=position_ids, causal=causal,
+                          training=training, cp=self.cp_strategy)
+        if ctx.cp is not None:
+            ctx.cp.prepare(self, ctx)
+        else:
+            ctx.cos, ctx.sin = self.rotary(position_ids)
+        return ctx
+
+    def forward_embed(self, input_ids: torch.Tensor, ctx: StepContext):
+        return emb_ops.embedding(input_ids.reshape(-1), self.embed_tokens.weight), None
+
+    def forward_head(self, h, residual, ctx: StepContext) -> torch.Tensor:
+        if residual is None:
+            return self.norm(h)
+        return self.norm(h, residual=residual)[0]
+
+    def head_loss(self, h, residual, labels: torch.Tensor, ctx: StepContext, grad_scale: float = 1.0,
+                  return_token_losses: bool = False):
+        """grad_scale * sum of token cross-entropies (labels == -100 ignored)."""
+        hidden = self.forward_head(h, residual, ctx)
+        return loss_ops.fused_linear_cross_entropy(hidden, self.lm_head.weight, labels.reshape(-1),
+                                                   grad_scale, self.loss_chunk_tokens,
+                                                   return_token_losses=return_token_losses)
+
+    def unit_modules(self):
+        """(name, modules) per ZeRO unit, in execution order.  The root unit (embedding, final
+        norm, lm_head) stays gathered for the whole step."""
+        root = [self.embed_tokens, self.norm, self.lm_head]
+        return [("root", root)] + [(f"layers.{i}", [l]) for i, l in enumerate(self.layers)]
+
+    # ---- plain autograd forward --------------------------------------------------------------
+    def forward(self, input_ids, labels=None, position_ids=None, cu_seqlens=None,
+                grad_scale: float = 1.0, return_hidden: bool = False) -> Dict[str, Any]:
+        ctx = self.make_context(input_ids, position_ids, cu_seqlens, training=self.training)
+        h, res = self.forward_embed(input_ids, ctx)
+        for layer in self.layers:
+            h, res = layer(h, res, ctx)
+        out: Dict[str, Any] = {"aux": ctx.aux}
+        if labels is not None:
+            out["loss"] = self.head_loss(h, res, labels, ctx, grad_scale)
+        if return_hidden or labels is None:
+            out["last_hidden_state"] = self.forward_head(h, res, ctx)
+        return out
+
+    @torch.no_grad()
+    def logits(self, input_ids, position_ids=None, cu_seqlens=None) -> torch.Tensor:
+        hid = self.forward(input_ids, None, position_ids, cu_seqlens)["last_hidden_state"]
+        return torch.nn.functional.linear(hid, self.lm_head.weight)
+
+
+@torch.no_grad()
+def init_parameter_(name: str, p: torch.Tensor, std: float, seed: int, index: int,
+                    zero_centered_norm: bool = False) -> None:
+    if p.is_meta:
+        return
+    leaf = name.rsplit(".", 1)[-1]
+    if p.dim() == 1:
+        if leaf == "bias" or "bias" in leaf:
+            p.zero_()
+        elif zero_centered_norm:
+            p.zero_()
+        else:
+            p.fill_(1.0)
+        return
+    g = torch.Generator(device="cpu").manual_seed((seed * 1000003 + index * 7919 + 17) % (2 ** 63 - 1))
+    if p.numel() <= (1 << 24) or p.device.type == "cpu":
+        vals = torch.empty(p.shape, dtype=torch.float32).normal_(0.0, std, generator=g)
+        p.copy_(vals.to(p.device))
+    else:
+        # large tensors: draw on the device (still deterministic per (seed, index))
+        gd = torch.Generator(device=p.device).manual_seed((seed * 1000003 + index * 7919 + 17) % (2 ** 63 - 1))
+        p.copy_(torch.empty(p.shape, dtype=torch.float32, device=p.device).normal_(0.0, std, generator=gd))

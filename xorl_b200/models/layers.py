@@ -1,0 +1,116 @@
+"""Building blocks of the decoder families: RMSNorm, linear, fused-qkv attention, SwiGLU MLP.
+
+Modules own parameters only; the math is in ``xorl_b200.ops`` (sm_100a kernels on CUDA, PyTorch on
+CPU).  Parameter names follow the reference's fused layout (``self_attn.qkv_proj``,
+``mlp.gate_up_proj``; src/xorl/models/layers/attention/multi_head_attention.py:15-189,
+src/xorl/models/transformers/qwen3/modeling_qwen3.py:40-81) so checkpoints interchange.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ..ops import activation as act_ops
+from ..ops import attention as attn_ops
+from ..ops import gemm as gemm_ops
+from ..ops import norm as norm_ops
+from .config import ModelConfig
+from .context import StepContext
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float = 1e-6, zero_centered: bool = False, dtype=None,
+                 device=None):
+        super().__init__()
+        init = torch.zeros if zero_centered else torch.ones
+        self.weight = nn.Parameter(init(dim, dtype=dtype, device=device))
+        self.eps = eps
+        self.zero_centered = zero_centered
+
+    def forward(self, x, residual=None):
+        return norm_ops.rmsnorm(x, self.weight, self.eps, residual=residual,
+                                zero_centered=self.zero_centered)
+
+
+class Linear(nn.Module):
+    """Weight ``[out, in]`` (+ optional bias); forward through the tcgen05 GEMM."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, dtype=None,
+                 device=None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+
+    def forward(self, x):
+        return gemm_ops.linear(x, self.weight, self.bias)
+
+
+class Attention(nn.Module):
+    """Fused qkv projection -> (per-head qk RMSNorm) -> RoPE -> varlen causal attention -> o_proj.
+    A context-parallel strategy on ``ctx.cp`` takes over the middle part when present."""
+
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        self.Hq, self.Hkv, self.D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        H = cfg.hidden_size
+        self.qkv_proj = Linear(H, (self.Hq + 2 * self.Hkv) * self.D, bias=cfg.attention_bias,
+                               dtype=dtype, device=device)
+        self.o_proj = Linear(self.Hq * self.D, H, bias=False, dtype=dtype, device=device)
+        self.use_qk_norm = cfg.use_qk_norm
+        if cfg.use_qk_norm:
+            nd = self.D if not cfg.qk_norm_full else None
+            self.q_norm = RMSNorm(nd or self.Hq * self.D, cfg.rms_norm_eps, dtype=dtype, device=device)
+            self.k_norm = RMSNorm(nd or self.Hkv * self.D, cfg.rms_norm_eps, dtype=dtype, device=device)
+        self.scale = 1.0 / math.sqrt(self.D)
+        self.window = cfg.sliding_window if (cfg.layer_types is None or
+                                            cfg.layer_types[layer_idx] == "sliding_attention") else None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        qkv = self.qkv_proj(x)
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        if ctx.cp is not None:
+            out = ctx.cp.attention(self, qkv, ctx)
+        elif self.cfg.qk_norm_full or self.cfg.partial_rotary_factor != 1.0:
+            out = self._unfused_attention(qkv, ctx)
+        else:
+            wq = self.q_norm.weight if self.use_qk_norm else None
+            wk = self.k_norm.weight if self.use_qk_norm else None
+            out = attn_ops.qk_norm_rope_attention(qkv, wq, wk, ctx.cos, ctx.sin, ctx.cu_seqlens,
+                                                  Hq, Hkv, D, self.cfg.rms_norm_eps, ctx.causal,
+                                                  self.scale)
+        return self.o_proj(out)
+
+    def _unfused_attention(self, qkv, ctx):
+        """General path (whole-projection qk-norm, partial rotary): separate ops."""
+        T = qkv.shape[0]
+        Hq, Hkv, D = self.Hq, self.Hkv, self.D
+        q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+        if self.use_qk_norm:
+            q, k = self.q_norm(q), self.k_norm(k)
+        q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
+        rot = ctx.cos.shape[-1] * 2
+        if rot == D:
+            q, k = attn_ops.rope_reference(q, ctx.cos, ctx.sin), attn_ops.rope_reference(k, ctx.cos, ctx.sin)
+        else:
+            q = torch.cat([attn_ops.rope_reference(q[..., :rot], ctx.cos, ctx.sin), q[..., rot:]], -1)
+            k = torch.cat([attn_ops.rope_reference(k[..., :rot], ctx.cos, ctx.sin), k[..., rot:]], -1)
+        out = attn_ops.flash_attn_varlen(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale)
+        return out.reshape(T, Hq * D)
+
+
+class MLP(nn.Module):
+    """SwiGLU feed-forward with a fused gate_up projection ``[2I, H]`` (gate rows first)."""
+
+    def __init__(self, hidden: int, intermediate: int, bias: bool = False, dtype=None, device=None):
+        super().__init__()
+        self.gate_up_proj = Linear(hidden, 2 * intermediate, bias=bias, dtype=dtype, device=device)
+        self.down_proj = Linear(intermediate, hidden, bias=bias, dtype=dtype, device=device)
+
+    def forward(self, x):
+        return self.down_proj(act_ops.swiglu(self.gate_up_proj(x)))

@@ -1,0 +1,233 @@
+"""Optimizers that update the ZeRO engine's flat fp32 shards in one kernel per shard.
+
+AdamW (fp32 moments), AnyPrecision AdamW (bf16 moments, optional Kahan compensation), SGD with
+momentum, SignSGD — the optimizer set of src/xorl/optim/optimizer.py:114-242.  The update reads the
+clip coefficient from device memory, so a step needs no host synchronisation, and writes the
+compute-dtype copy of the weights that the next all-gather sends.
+Weight-decay exclusions follow ``no_decay_modules`` (module class names) and ``no_decay_params``
+(substring patterns).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..ops import optim as optim_ops
+from ..parallel.zero import FlatParamGroup, Zero3Engine
+
+
+def _decay_table(engine: Zero3Engine, weight_decay: float, no_decay_modules: Sequence[str],
+                 no_decay_params: Sequence[str]) -> Dict[str, float]:
+    table: Dict[str, float] = {}
+    no_decay_names = set()
+    if no_decay_modules:
+        for mname, mod in engine.model.named_modules():
+            if type(mod).__name__ in no_decay_modules:
+                for pname, _ in mod.named_parameters(recurse=False):
+                    no_decay_names.add(f"{mname}.{pname}" if mname else pname)
+    for g in engine.all_groups():
+        for name, _ in g.named_params:
+            wd = weight_decay
+            if name in no_decay_names or any(pat in name for pat in (no_decay_params or [])):
+                wd = 0.0
+            table[name] = wd
+    return table
+
+
+class ShardedOptimizer:
+    """Base: owns per-group state tensors and iterates (group, segment) pairs."""
+
+    kind = "base"
+
+    def __init__(self, engine: Zero3Engine, lr: float, weight_decay: float = 0.0,
+                 no_decay_modules: Sequence[str] = (), no_decay_params: Sequence[str] = ()):
+        self.engine = engine
+        self.lr = lr
+        self.weight_decay = weight_decay
+        self.step_count = 0
+        self._decay = _decay_table(engine, weight_decay, no_decay_modules, no_decay_params)
+        self.state: Dict[str, Dict[int, torch.Tensor]] = {}
+        self.lr_scale: Dict[int, float] = {}
+
+    def set_lr(self, lr: float) -> None:
+        self.lr = lr
+
+    def _segments(self, g: FlatParamGroup) -> List[Tuple[int, int, float]]:
+        """Maximal runs of the shard with equal weight decay (padding inherits its neighbour's)."""
+        segs = g.param_segments_in_shard()
+        if not segs:
+            return [(0, g.shard_numel, 0.0)]
+        runs: List[List] = []
+        cursor = 0
+        for i, a, b in segs:
+            wd = self._decay[g.named_params[i][0]]
+            if runs and runs[-1][2] == wd:
+                runs[-1][1] = b
+            else:
+                runs.append([cursor, b, wd])
+            cursor = b
+        runs[-1][1] = g.shard_numel
+        # 4-element alignment of run boundaries (vectorised kernel): parameter offsets are multiples
+        # of 64 so this only moves boundaries inside alignment padding
+        out = []
+        for a, b, wd in runs:
+            a = (a + 3) // 4 * 4 if a else 0
+            out.append((a, b, wd))
+        for k in range(len(out) - 1):
+            out[k] = (out[k][0], out[k + 1][0], out[k][2])
+        return [(a, b, wd) for a, b, wd in out if b > a]
+
+    def _new_state(self, name: str, dtype=torch.float32) -> Dict[int, torch.Tensor]:
+        d = {id(g): torch.zeros(g.shard_numel, device=self.engine.device, dtype=dtype)
+             for g in self.engine.all_groups()}
+        self.state[name] = d
+        return d
+
+    def zero_grad(self) -> None:
+        self.engine.zero_grad()
+
+    def step(self, clip_coef: Optional[torch.Tensor] = None, grad_scale: float = 1.0) -> None:
+        raise NotImplementedError
+
+    # ---- checkpoint ---------------------------------------------------------------------------
+    def state_dict(self) -> Dict:
+        return {"kind": self.kind, "step": self.step_count, "lr": self.lr}
+
+    def load_state_dict(self, sd: Dict) -> None:
+        self.step_count = int(sd.get("step", 0))
+        self.lr = float(sd.get("lr", self.lr))
+
+
+class ShardedAdamW(ShardedOptimizer):
+    kind = "adamw"
+
+    def __init__(self, engine, lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, **kw):
+        super().__init__(engine, lr, weight_decay, kw.get("no_decay_modules", ()),
+                         kw.get("no_decay_params", ()))
+        self.betas, self.eps = betas, eps
+        self.exp_avg = self._new_state("exp_avg")
+        self.exp_avg_sq = self._new_state("exp_avg_sq")
+
+    def step(self, clip_coef=None, grad_scale: float = 1.0) -> None:
+        self.step_count += 1
+        b1, b2 = self.betas
+        for g in self.engine.all_groups():
+            if not g.grad_ready:
+                continue
+            m, v = self.exp_avg[id(g)], self.exp_avg_sq[id(g)]
+            lp = None if g.shard_lp is g.master else g.shard_lp
+            for a, b, wd in self._segments(g):
+                optim_ops.adamw_step_(g.master[a:b], m[a:b], v[a:b], g.grad_shard[a:b],
+                                      None if lp is None else lp[a:b], lr=self.lr, beta1=b1, beta2=b2,
+                                      eps=self.eps, weight_decay=wd, step=self.step_count,
+                                      grad_scale=grad_scale, clip_coef=clip_coef)
+
+
+class ShardedAnyPrecisionAdamW(ShardedOptimizer):
+    """AdamW with bf16 moments (``optimizer_dtype: bf16``) and optional Kahan compensation;
+    torch ops on the shard (src/xorl/optim/anyprecision_adamw.py)."""
+    kind = "anyprecision_adamw"
+
+    def __init__(self, engine, lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0,
+                 state_dtype=torch.bfloat16, cautious_weight_decay=False, **kw):
+        super().__init__(engine, lr, weight_decay, kw.get("no_decay_modules", ()),
+                         kw.get("no_decay_params", ()))
+        self.betas, self.eps, self.cautious = betas, eps, cautious_weight_decay
+        self.exp_avg = self._new_state("exp_avg", state_dtype)
+        self.exp_avg_sq = self._new_state("exp_avg_sq", state_dtype)
+
+    @torch.no_grad()
+    def step(self, clip_coef=None, grad_scale: float = 1.0) -> None:
+        self.step_count += 1
+        b1, b2 = self.betas
+        bc1 = 1 - b1 ** self.step_count
+        bc2 = 1 - b2 ** self.step_count
+        for g in self.engine.all_groups():
+            if not g.grad_ready:
+                continue
+            for a, b, wd in self._segments(g):
+                p = g.master[a:b]
+                gr = g.grad_shard[a:b] * grad_scale
+                if clip_coef is not None:
+                    gr = gr * clip_coef
+                m = self.exp_avg[id(g)][a:b].float().mul_(b1).add_(gr, alpha=1 - b1)
+                v = self.exp_avg_sq[id(g)][a:b].float().mul_(b2).addcmul_(gr, gr, value=1 - b2)
+                self.exp_avg[id(g)][a:b].copy_(m)
+                self.exp_avg_sq[id(g)][a:b].copy_(v)
+                update = (m / bc1) / ((v / bc2).sqrt_().add_(self.eps))
+                if wd:
+                    if self.cautious:
+                        mask = (update * p >= 0).to(p.dtype)
+                        p.sub_(p * mask, alpha=self.lr * wd)
+                    else:
+                        p.mul_(1 - self.lr * wd)
+                p.sub_(update, alpha=self.lr)
+            self.engine.refresh_compute_copy(g)
+
+
+class ShardedSGD(ShardedOptimizer):
+    kind = "sgd"
+
+    def __init__(self, engine, lr, momentum=0.0, nesterov=False, weight_decay=0.0, **kw):
+        super().__init__(engine, lr, weight_decay, kw.get("no_decay_modules", ()),
+                         kw.get("no_decay_params", ()))
+        self.momentum, self.nesterov = momentum, nesterov
+        self.buf = self._new_state("momentum_buffer") if momentum else None
+
+    @torch.no_grad()
+    def step(self, clip_coef=None, grad_scale: float = 1.0) -> None:
+        self.step_count += 1
+        for g in self.engine.all_groups():
+            if not g.grad_ready:
+                continue
+            for a, b, wd in self._segments(g):
+                p = g.master[a:b]
+                gr = g.grad_shard[a:b] * grad_scale
+                if clip_coef is not None:
+                    gr = gr * clip_coef
+                if wd:
+                    gr = gr.add(p, alpha=wd)
+                if self.buf is not None:
+                    mb = self.buf[id(g)][a:b]
+                    mb.mul_(self.momentum).add_(gr)
+                    gr = gr.add(mb, alpha=self.momentum) if self.nesterov else mb
+                p.sub_(gr, alpha=self.lr)
+            self.engine.refresh_compute_copy(g)
+
+
+class ShardedSignSGD(ShardedOptimizer):
+    kind = "signsgd"
+
+    def step(self, clip_coef=None, grad_scale: float = 1.0) -> None:
+        self.step_count += 1
+        for g in self.engine.all_groups():
+            if not g.grad_ready:
+                continue
+            lp = None if g.shard_lp is g.master else g.shard_lp
+            for a, b, wd in self._segments(g):
+                optim_ops.signsgd_step_(g.master[a:b], g.grad_shard[a:b],
+                                        None if lp is None else lp[a:b], lr=self.lr, weight_decay=wd)
+
+
+def build_optimizer(engine: Zero3Engine, lr: float = 1e-3, betas=(0.9, 0.95), eps: float = 1e-8,
+                    weight_decay: float = 1e-2, optimizer_type: str = "adamw",
+                    optimizer_dtype: str = "bf16", no_decay_modules=None, no_decay_params=None,
+                    optimizer_kwargs: Optional[dict] = None, cautious_weight_decay: bool = False):
+    kw = dict(no_decay_modules=no_decay_modules or (), no_decay_params=no_decay_params or ())
+    okw = dict(optimizer_kwargs or {})
+    if optimizer_type == "adamw" and not cautious_weight_decay:
+        return ShardedAdamW(engine, lr, betas, eps, weight_decay, **kw)
+    if optimizer_type in ("adamw", "anyprecision_adamw"):
+        dt = torch.float32 if (optimizer_dtype == "fp32" or optimizer_type == "adamw") else torch.bfloat16
+        return ShardedAnyPrecisionAdamW(engine, lr, betas, eps, weight_decay, state_dtype=dt,
+                                        cautious_weight_decay=cautious_weight_decay, **kw)
+    if optimizer_type == "sgd":
+        return ShardedSGD(engine, lr, okw.get("momentum", 0.0), okw.get("nesterov", False),
+                          weight_decay, **kw)
+    if optimizer_type in ("signsgd", "distsignsgd"):
+        return ShardedSignSGD(engine, lr, weight_decay, **kw)
+    if optimizer_type == "muon":
+        from .muon import ShardedMuon
+        return ShardedMuon(engine, lr, betas, eps, weight_decay, **okw, **kw)
+    raise ValueError(f"unknown optimizer {optimizer_type!r}")

@@ -1,0 +1,582 @@
+"""ZeRO-3 engine on flat per-unit shards.
+
+Replaces the reference's use of ``torch.distributed.fsdp.fully_shard``
+(src/xorl/distributed/torch_parallelize.py:333-783) with a runtime that owns the memory layout:
+
+* every *unit* (root = embedding + final norm + lm_head, then one per decoder layer) keeps its
+  parameters in one flat buffer; a rank persistently holds only its 1/N slice of the fp32 master
+  weights, the two Adam moments, the fp32 gradient accumulator and the compute-dtype copy that is
+  all-gathered;
+* forward runs unit by unit without an autograd graph and keeps only the unit inputs; backward
+  re-gathers a unit, recomputes it under autograd, back-propagates, and immediately reduces that
+  unit's gradients into the owners' fp32 accumulators (gradient divide factor 1: losses are
+  normalised by the global token count, src/xorl/distributed/torch_parallelize.py:670-672);
+* gathers are prefetched one unit ahead on a side stream, gradient reductions overlap the next
+  unit's backward.
+
+Transports: ``nccl`` / ``gloo`` collectives (baseline, and the CPU lane) or the fused peer-memory
+kernels of ``parallel/symm.py`` when available.
+"""
+from __future__ import annotations
+
+import math
+from contextlib import nullcontext
+from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..ops import optim as optim_ops
+from .state import ParallelState, get_parallel_state
+
+ALIGN = 64  # elements; keeps every parameter and every shard 128-byte aligned in bf16
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class FlatParamGroup:
+    """Parameters of one unit that share a sharding group (dense vs. expert-parallel)."""
+
+    def __init__(self, name: str, named_params: List[Tuple[str, nn.Parameter]], pg, world: int,
+                 rank: int, device: torch.device, compute_dtype: torch.dtype,
+                 replicate_pg=None, replicate_world: int = 1):
+        self.name = name
+        self.named_params = named_params
+        self.pg, self.world, self.rank = pg, world, rank
+        self.replicate_pg, self.replicate_world = replicate_pg, replicate_world
+        self.device, self.compute_dtype = device, compute_dtype
+        self.offsets: List[int] = []
+        off = 0
+        self.shapes = [tuple(getattr(p, "_xb_shape", p.shape)) for _, p in named_params]
+        for shp in self.shapes:
+            self.offsets.append(off)
+            off += _round_up(math.prod(shp), ALIGN)
+        self.numel = off
+        self.padded = _round_up(max(off, 1), world * ALIGN)
+        self.shard_numel = self.padded // world
+        # persistent sharded state
+        self.master: torch.Tensor = None      # fp32 [shard]
+        self.shard_lp: torch.Tensor = None    # compute dtype [shard] (aliases master when fp32)
+        self.grad_shard: torch.Tensor = None  # fp32 [shard]
+        self.grad_ready = False               # grad_shard holds this step's accumulated gradient
+        # transient
+        self.full: Optional[torch.Tensor] = None
+        self.full_persistent = False
+        self.grad_full: Optional[torch.Tensor] = None
+        self.gather_event = None
+        self.reduce_event = None
+        self.weight_decay_mask: Optional[List[float]] = None
+
+    # ---- layout helpers ---------------------------------------------------------------------
+    def shard_range(self) -> Tuple[int, int]:
+        return self.rank * self.shard_numel, (self.rank + 1) * self.shard_numel
+
+    def param_views(self, flat: torch.Tensor) -> List[torch.Tensor]:
+        return [flat[o:o + math.prod(s)].view(s) for o, s in zip(self.offsets, self.shapes)]
+
+    def attach_params(self) -> None:
+        """Point every parameter at its view of the gathered buffer."""
+        for (_, p), v in zip(self.named_params, self.param_views(self.full)):
+            p.data = v
+
+    def detach_params(self) -> None:
+        empty = torch.empty(0, device=self.device, dtype=self.compute_dtype)
+        for _, p in self.named_params:
+            p.data = empty
+
+    def attach_grad_views(self) -> None:
+        for (_, p), v in zip(self.named_params, self.param_views(self.grad_full)):
+            p._xb_grad_buf = v
+            p._xb_grad_fresh = True
+            p.grad = None
+
+    def collect_grads(self) -> None:
+        """Zero slices nobody wrote, fold in gradients that arrived through ``p.grad``."""
+        for _, p in self.named_params:
+            buf = p._xb_grad_buf
+            if p.grad is not None:
+                if p._xb_grad_fresh:
+                    buf.copy_(p.grad)
+                else:
+                    buf.add_(p.grad.to(buf.dtype))
+                p.grad = None
+            elif p._xb_grad_fresh:
+                buf.zero_()
+            p._xb_grad_buf = None
+            p._xb_grad_fresh = False
+
+    def param_segments_in_shard(self) -> List[Tuple[int, int, int]]:
+        """(param index, start, end) in shard-local coordinates for every overlap."""
+        s0, s1 = self.shard_range()
+        out = []
+        for i, (o, shp) in enumerate(zip(self.offsets, self.shapes)):
+            a, b = max(o, s0), min(o + math.prod(shp), s1)
+            if a < b:
+                out.append((i, a - s0, b - s0))
+        return out
+
+
+class ZeroUnit:
+    def __init__(self, name: str, modules: Sequence[nn.Module]):
+        self.name = name
+        self.modules = list(modules)
+        self.groups: List[FlatParamGroup] = []
+
+
+class Zero3Engine:
+    """Runs forward/backward unit by unit with ZeRO-3 sharding (world >= 1)."""
+
+    def __init__(self, model: nn.Module, pstate: Optional[ParallelState] = None, *,
+                 compute_dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None,
+                 reduce_dtype: torch.dtype = torch.float32, reshard_after_forward: bool = True,
+                 recompute: bool = True, seed: int = 0, comm_backend: str = "nccl",
+                 shard: bool = True):
+        self.model = model
+        self.ps = pstate or get_parallel_state()
+        self.device = device or torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        self.compute_dtype = compute_dtype
+        self.reduce_dtype = reduce_dtype
+        self.recompute = recompute
+        self.comm_backend = comm_backend
+        self.is_cuda = self.device.type == "cuda"
+        ps = self.ps
+        if shard and ps.dp_mode == "fsdp2":
+            self.shard_pg, self.shard_world = ps.group("fsdp"), ps.size("fsdp") if "fsdp" in ps.groups else 1
+            self.shard_rank = ps.rank_in("fsdp")
+            self.rep_pg = ps.group("dp_replicate")
+            self.rep_world = ps.dp_replicate_size
+            self.sp_sync_pg = ps.group("sp_grad_sync")
+        else:
+            # ddp / none: every rank holds everything, gradients are all-reduced over dp x sp
+            self.shard_pg, self.shard_world, self.shard_rank = None, 1, 0
+            self.rep_pg, self.rep_world = ps.group("dp_sp"), ps.size("dp_sp") if "dp_sp" in ps.groups else 1
+            self.sp_sync_pg = None
+        self.ep_shard_pg = ps.group("ep_fsdp")
+        self.ep_shard_world = ps.ep_fsdp_size if ps.ep_size > 1 else self.shard_world
+        self.ep_shard_rank = ps.rank_in("ep_fsdp") if ps.ep_size > 1 else self.shard_rank
+        self.reshard = reshard_after_forward and self.shard_world > 1
+        self.units: List[ZeroUnit] = []
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+        self._full_pool: Dict[Tuple[int, torch.dtype], List[torch.Tensor]] = {}
+        self._build_units(seed)
+        self.symm = None  # fused peer-memory transport (attached by parallel.symm when usable)
+
+    # ---------------------------------------------------------------------------------------
+    # construction
+    # ---------------------------------------------------------------------------------------
+    def _swap_parameters(self) -> None:
+        """Replaces every parameter (meta or real) by a storage-less parameter on the engine's
+        device; the original shape and, for real tensors, the initial values are kept on the new
+        object until the unit is materialised.  Tied parameters stay tied."""
+        mapping: Dict[int, nn.Parameter] = {}
+        for mod in self.model.modules():
+            for k, p in list(mod._parameters.items()):
+                if p is None:
+                    continue
+                if id(p) not in mapping:
+                    newp = nn.Parameter(torch.empty(0, device=self.device, dtype=self.compute_dtype),
+                                        requires_grad=p.requires_grad)
+                    newp._xb_shape = tuple(p.shape)
+                    newp._xb_init = None if p.is_meta else p.detach()
+                    for attr in ("_xb_expert", "_xb_tp", "_xb_no_decay"):
+                        if hasattr(p, attr):
+                            setattr(newp, attr, getattr(p, attr))
+                    mapping[id(p)] = newp
+                mod._parameters[k] = mapping[id(p)]
+
+    def _build_units(self, seed: int) -> None:
+        model = self.model
+        self._swap_parameters()
+        seen: set = set()
+        fqn_of = {id(p): n for n, p in model.named_parameters()}
+        index_of = {n: i for i, (n, _) in enumerate(model.named_parameters())}
+        cfg = getattr(model, "config", None)
+        std = getattr(cfg, "initializer_range", 0.02)
+        zc = getattr(cfg, "zero_centered_norm", False)
+        from ..models.decoder import init_parameter_
+        for uname, mods in model.unit_modules():
+            unit = ZeroUnit(uname, mods)
+            dense: List[Tuple[str, nn.Parameter]] = []
+            expert: List[Tuple[str, nn.Parameter]] = []
+            for m in mods:
+                for p in m.parameters():
+                    if id(p) in seen or not p.requires_grad and False:
+                        continue
+                    seen.add(id(p))
+                    (expert if getattr(p, "_xb_expert", False) else dense).append((fqn_of[id(p)], p))
+            for kind, plist in (("dense", dense), ("expert", expert)):
+                if not plist:
+                    continue
+                if kind == "expert" and self.ps.ep_size > 1:
+                    g = FlatParamGroup(f"{uname}.{kind}", plist, self.ep_shard_pg, self.ep_shard_world,
+                                       self.ep_shard_rank, self.device, self.compute_dtype)
+                else:
+                    g = FlatParamGroup(f"{uname}.{kind}", plist, self.shard_pg, self.shard_world,
+                                       self.shard_rank, self.device, self.compute_dtype,
+                                       self.rep_pg, self.rep_world)
+                g.is_expert = kind == "expert"
+                self._materialize_group(g, std, seed, index_of, zc, init_parameter_)
+                unit.groups.append(g)
+            self.units.append(unit)
+        leftover = [n for n, p in model.named_parameters() if id(p) not in seen]
+        if leftover:
+            raise RuntimeError(f"parameters not covered by any ZeRO unit: {leftover[:5]}")
+        # move buffers (rotary tables etc.)
+        for m in model.modules():
+            for k, b in list(m._buffers.items()):
+                if b is not None and b.device != self.device and not b.is_meta:
+                    m._buffers[k] = b.to(self.device)
+
+    def _materialize_group(self, g: FlatParamGroup, std, seed, index_of, zc, init_fn) -> None:
+        """Builds the unit's full fp32 image once (initialising meta parameters in place), keeps
+        this rank's slice as master weights and drops the rest."""
+        full32 = torch.zeros(g.padded, device=self.device, dtype=torch.float32)
+        for (name, p), view in zip(g.named_params, g.param_views(full32)):
+            init = getattr(p, "_xb_init", None)
+            if init is None:
+                init_fn(name, view, std, seed, index_of[name], zc)
+            else:
+                view.copy_(init.to(device=self.device, dtype=torch.float32))
+                p._xb_init = None
+        s0, s1 = g.shard_range()
+        g.master = full32[s0:s1].clone()
+        g.shard_lp = g.master if self.compute_dtype == torch.float32 else g.master.to(self.compute_dtype)
+        g.grad_shard = torch.zeros(g.shard_numel, device=self.device, dtype=torch.float32)
+        del full32
+        if g.world == 1:
+            g.full = g.shard_lp
+            g.full_persistent = True
+            g.attach_params()
+
+    # ---------------------------------------------------------------------------------------
+    # gather / release
+    # ---------------------------------------------------------------------------------------
+    def _take_full(self, numel: int, dtype: torch.dtype, on_comm_stream: bool = False) -> torch.Tensor:
+        """Buffers cycle between parameter gathers (written on the side stream) and gradient
+        buffers (written on the compute stream).  An entry remembers the side-stream event of its
+        last use there; a compute-side taker waits for it."""
+        pool = self._full_pool.setdefault((numel, dtype), [])
+        if pool:
+            t, ev = pool.pop()
+            if ev is not None and not on_comm_stream:
+                torch.cuda.current_stream().wait_event(ev)
+            return t
+        return torch.empty(numel, device=self.device, dtype=dtype)
+
+    def _give_full(self, t: torch.Tensor, comm_event=None) -> None:
+        self._full_pool.setdefault((t.numel(), t.dtype), []).append((t, comm_event))
+
+    def gather(self, unit: ZeroUnit, async_op: bool = True) -> None:
+        """Start (or no-op if already resident) the all-gather of a unit's parameters."""
+        for g in unit.groups:
+            if g.full is not None:
+                continue
+            g.full = self._take_full(g.padded, self.compute_dtype, on_comm_stream=True)
+            if self.symm is not None and self.symm.can_gather(g):
+                self.symm.all_gather(g, self.comm_stream)
+            elif self.is_cuda:
+                self.comm_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.comm_stream):
+                    dist.all_gather_into_tensor(g.full, g.shard_lp, group=g.pg)
+                    g.gather_event = torch.cuda.Event()
+                    g.gather_event.record(self.comm_stream)
+            else:
+                dist.all_gather_into_tensor(g.full, g.shard_lp, group=g.pg)
+
+    def wait_gather(self, unit: ZeroUnit) -> None:
+        for g in unit.groups:
+            if g.gather_event is not None:
+                torch.cuda.current_stream().wait_event(g.gather_event)
+                g.gather_event = None
+            g.attach_params()
+
+    def release(self, unit: ZeroUnit) -> None:
+        for g in unit.groups:
+            if g.full_persistent or g.full is None:
+                continue
+            g.detach_params()
+            if self.is_cuda:
+                # the buffer may be re-filled by the side stream only after compute is done with it
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream())
+                self.comm_stream.wait_event(ev)
+            self._give_full(g.full)
+            g.full = None
+
+    # ---------------------------------------------------------------------------------------
+    # gradient reduction
+    # ---------------------------------------------------------------------------------------
+    def _prepare_grad_buffers(self, unit: ZeroUnit) -> None:
+        for g in unit.groups:
+            g.grad_full = self._take_full(g.padded, self.compute_dtype)
+            g.attach_grad_views()
+
+    def _reduce_unit_grads(self, unit: ZeroUnit) -> None:
+        for g in unit.groups:
+            g.collect_grads()
+            accumulate = g.grad_ready
+            gf = g.grad_full
+            if g.world == 1:
+                if gf.dtype == torch.float32:
+                    if accumulate:
+                        g.grad_shard.add_(gf)
+                    else:
+                        g.grad_shard.copy_(gf)
+                else:
+                    optim_ops.cast_accum_(gf, g.grad_shard, 1.0, accumulate)
+                self._give_full(gf)
+            elif self.symm is not None and self.symm.can_reduce(g):
+                self.symm.reduce_scatter_accumulate(g, gf, accumulate, self.comm_stream)
+            elif self.is_cuda:
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream())
+                self.comm_stream.wait_event(ev)
+                with torch.cuda.stream(self.comm_stream):
+                    self._rs_collective(g, gf, accumulate)
+                    g.reduce_event = torch.cuda.Event()
+                    g.reduce_event.record(self.comm_stream)
+                self._give_full(gf, g.reduce_event)
+            else:
+                self._rs_collective(g, gf, accumulate)
+                self._give_full(gf)
+            g.grad_full = None
+            g.grad_ready = True
+
+    def _rs_collective(self, g: FlatParamGroup, gf: torch.Tensor, accumulate: bool) -> None:
+        src = gf if gf.dtype == self.reduce_dtype else gf.to(self.reduce_dtype)
+        out = torch.empty(g.shard_numel, device=self.device, dtype=src.dtype)
+        dist.reduce_scatter_tensor(out, src, op=dist.ReduceOp.SUM, group=g.pg)
+        if accumulate:
+            g.grad_shard.add_(out)
+        else:
+            g.grad_shard.copy_(out)
+
+    def finish_grad_sync(self) -> None:
+        """Wait for outstanding reductions; all-reduce over replicas (HSDP / DDP) and over
+        sequence-parallel ranks that are not part of the shard group."""
+        if self.is_cuda:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        for unit in self.units:
+            for g in unit.groups:
+                g.reduce_event = None
+                if g.replicate_pg is not None and g.replicate_world > 1:
+                    dist.all_reduce(g.grad_shard, group=g.replicate_pg)
+                if self.sp_sync_pg is not None and not getattr(g, "is_expert", False):
+                    dist.all_reduce(g.grad_shard, group=self.sp_sync_pg)
+
+    def zero_grad(self) -> None:
+        for unit in self.units:
+            for g in unit.groups:
+                g.grad_ready = False
+
+    # ---------------------------------------------------------------------------------------
+    # forward / backward over one micro-batch
+    # ---------------------------------------------------------------------------------------
+    def _units_by_role(self):
+        root = self.units[0]
+        layers = self.units[1:]
+        return root, layers
+
+    def forward_backward(self, input_ids: torch.Tensor, labels: torch.Tensor, *,
+                         position_ids=None, cu_seqlens=None, grad_scale: float = 1.0,
+                         extra_loss_fn: Optional[Callable] = None) -> torch.Tensor:
+        """One micro-batch.  Returns ``grad_scale * sum(token CE)`` (detached).  Gradients are
+        accumulated into the fp32 shards; call ``finish_grad_sync`` after the last micro-batch."""
+        model = self.model
+        root, layers = self._units_by_role()
+        nl = len(layers)
+        self.gather(root)
+        self.wait_gather(root)
+        ctx = model.make_context(input_ids, position_ids, cu_seqlens, training=True)
+        recompute = self.recompute
+        saved_inputs: List[Tuple] = []
+        saved_graph: List[Tuple] = []
+        with torch.no_grad():
+            acts = model.forward_embed(input_ids, ctx)
+        if nl:
+            self.gather(layers[0])
+        for i, unit in enumerate(layers):
+            self.wait_gather(unit)
+            if i + 1 < nl:
+                self.gather(layers[i + 1])
+            layer = unit.modules[0]
+            if recompute:
+                saved_inputs.append(acts)
+                with torch.no_grad():
+                    acts = layer(*acts, ctx)
+            else:
+                ins = tuple(a.detach().requires_grad_() if a is not None else None for a in acts)
+                with torch.enable_grad():
+                    outs = layer(*ins, ctx)
+                saved_graph.append((ins, outs))
+                acts = tuple(o.detach() if o is not None else None for o in outs)
+            if self.reshard and recompute and i < nl - 1:
+                self.release(unit)
+        # ---- head: forward + backward at once ------------------------------------------------
+        self._prepare_grad_buffers(root)
+        head_in = tuple(a.detach().requires_grad_() if a is not None else None for a in acts)
+        with torch.enable_grad():
+            loss = model.head_loss(*head_in, labels, ctx, grad_scale)
+            total = loss
+            if extra_loss_fn is not None:
+                extra = extra_loss_fn(ctx)
+                if extra is not None:
+                    total = total + extra
+            total.backward()
+        dacts = tuple(a.grad if a is not None else None for a in head_in)
+        loss_value = loss.detach()
+        # ---- layers, last to first ------------------------------------------------------------
+        for i in range(nl - 1, -1, -1):
+            unit = layers[i]
+            self.gather(unit)
+            self.wait_gather(unit)
+            if i > 0:
+                self.gather(layers[i - 1])
+            self._prepare_grad_buffers(unit)
+            layer = unit.modules[0]
+            if recompute:
+                ins = tuple(a.detach().requires_grad_() if a is not None else None
+                            for a in saved_inputs[i])
+                saved_inputs[i] = None
+                with torch.enable_grad():
+                    outs = layer(*ins, ctx)
+            else:
+                ins, outs = saved_graph[i]
+                saved_graph[i] = None
+            pairs = [(o, d) for o, d in zip(outs, dacts) if o is not None and d is not None]
+            aux = ctx.aux.pop(("aux_loss", i), None)
+            tensors = [o for o, _ in pairs]
+            grads = [d for _, d in pairs]
+            if aux is not None:
+                tensors.append(aux)
+                grads.append(torch.ones_like(aux))
+            torch.autograd.backward(tensors, grads)
+            dacts = tuple(a.grad if a is not None else None for a in ins)
+            del ins, outs, pairs, tensors, grads
+            self._reduce_unit_grads(unit)
+            if self.reshard:
+                self.release(unit)
+        # ---- embedding backward ----------------------------------------------------------------
+        with torch.enable_grad():
+            emb = model.forward_embed(input_ids, ctx)
+        pairs = [(o, d) for o, d in zip(emb, dacts) if o is not None and d is not None]
+        if pairs and pairs[0][0].requires_grad:
+            torch.autograd.backward([o for o, _ in pairs], [d for _, d in pairs])
+        self._reduce_unit_grads(root)
+        if self.reshard:
+            self.release(root)
+        return loss_value
+
+    @torch.no_grad()
+    def forward_only(self, input_ids, *, position_ids=None, cu_seqlens=None) -> torch.Tensor:
+        """Final normalised hidden states (no gradients, parameters gathered unit by unit)."""
+        model = self.model
+        root, layers = self._units_by_role()
+        self.gather(root)
+        self.wait_gather(root)
+        ctx = model.make_context(input_ids, position_ids, cu_seqlens, training=False)
+        acts = model.forward_embed(input_ids, ctx)
+        for i, unit in enumerate(layers):
+            self.gather(unit)
+            self.wait_gather(unit)
+            if i + 1 < len(layers):
+                self.gather(layers[i + 1])
+            acts = unit.modules[0](*acts, ctx)
+            if self.reshard:
+                self.release(unit)
+        hidden = model.forward_head(*acts, ctx)
+        return hidden
+
+    # ---------------------------------------------------------------------------------------
+    # gradient norm / clipping
+    # ---------------------------------------------------------------------------------------
+    def all_groups(self) -> Iterable[FlatParamGroup]:
+        for u in self.units:
+            yield from u.groups
+
+    def grad_norm_and_clip_coef(self, max_norm: float) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Global L2 norm of the accumulated gradients and ``min(1, max_norm/(norm+1e-6))``, both as
+        1-element device tensors (no host sync).  Dense shards are summed over the shard group,
+        expert shards over ep_fsdp x ep (src/xorl/distributed/fsdp2/clip_grad_norm.py:60-257)."""
+        dev = self.device
+        dense_sq = torch.zeros(1, device=dev, dtype=torch.float32)
+        expert_sq = torch.zeros(1, device=dev, dtype=torch.float32)
+        first_d = first_e = True
+        for g in self.all_groups():
+            if not g.grad_ready:
+                continue
+            if getattr(g, "is_expert", False) and self.ps.ep_size > 1:
+                optim_ops.sumsq_(g.grad_shard, expert_sq, not first_e)
+                first_e = False
+            else:
+                optim_ops.sumsq_(g.grad_shard, dense_sq, not first_d)
+                first_d = False
+        if self.shard_pg is not None:
+            dist.all_reduce(dense_sq, group=self.shard_pg)
+        if self.ps.ep_size > 1:
+            if self.ep_shard_pg is not None:
+                dist.all_reduce(expert_sq, group=self.ep_shard_pg)
+            if self.ps.group("ep") is not None:
+                dist.all_reduce(expert_sq, group=self.ps.group("ep"))
+        total = dense_sq + expert_sq
+        if self.ps.pp_size > 1 and self.ps.group("pp") is not None:
+            dist.all_reduce(total, group=self.ps.group("pp"))
+        norm = torch.zeros(1, device=dev, dtype=torch.float32)
+        coef = torch.ones(1, device=dev, dtype=torch.float32)
+        optim_ops.clip_coef_(total, max_norm, norm, coef)
+        return norm, coef
+
+    # ---------------------------------------------------------------------------------------
+    # full-tensor access (checkpointing, export, weight sync)
+    # ---------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def iter_full_tensors(self, what: str = "master", extra: Optional[Dict[int, torch.Tensor]] = None):
+        """Yields (fqn, full tensor) unit by unit.  ``what``: "master" (fp32 weights),
+        "grad" (fp32 accumulated gradient) or "extra" with a {id(group): shard tensor} mapping
+        (optimizer moments).  Every rank of the shard group must iterate in lock-step."""
+        for g in self.all_groups():
+            if what == "master":
+                shard = g.master
+            elif what == "grad":
+                shard = g.grad_shard
+            else:
+                shard = extra[id(g)]
+            if g.world > 1:
+                full = torch.empty(g.padded, device=self.device, dtype=shard.dtype)
+                dist.all_gather_into_tensor(full, shard.contiguous(), group=g.pg)
+            else:
+                full = shard
+            for (name, _), view in zip(g.named_params, g.param_views(full)):
+                yield name, view
+
+    @torch.no_grad()
+    def load_full_tensors(self, tensors: Dict[str, torch.Tensor], strict: bool = True,
+                          target: str = "master", extra: Optional[Dict[int, torch.Tensor]] = None) -> List[str]:
+        """Copies full tensors (by FQN) into this rank's shards.  Returns the missing names."""
+        missing = []
+        for g in self.all_groups():
+            dst = g.master if target == "master" else extra[id(g)]
+            s0, _ = g.shard_range()
+            for i, a, b in g.param_segments_in_shard():
+                name = g.named_params[i][0]
+                if name not in tensors:
+                    missing.append(name)
+                    continue
+                src = tensors[name].reshape(-1)
+                o = g.offsets[i]
+                dst[a:b].copy_(src[s0 + a - o: s0 + b - o].to(device=self.device, dtype=dst.dtype))
+            if target == "master":
+                self.refresh_compute_copy(g)
+        if strict and missing:
+            raise KeyError(f"missing tensors: {sorted(set(missing))[:8]}")
+        return sorted(set(missing))
+
+    def refresh_compute_copy(self, g: FlatParamGroup) -> None:
+        if g.shard_lp is not g.master:
+            g.shard_lp.copy_(g.master)
+
+    def num_local_elements(self) -> int:
+        return sum(g.shard_numel for g in self.all_groups())
