@@ -1,0 +1,91 @@
+"""Name / shape transforms between the fused in-memory layout and Hugging Face checkpoints.
+
+In memory: ``self_attn.qkv_proj`` (rows q|k|v), ``mlp.gate_up_proj`` (rows gate|up), MoE experts
+stacked as ``mlp.experts.gate_up_proj [E, H, 2I]`` and ``mlp.experts.down_proj [E, I, H]``.
+On disk (HF): ``q_proj/k_proj/v_proj``, ``gate_proj/up_proj`` and one tensor per expert.
+Counterparts: src/xorl/models/transformers/qwen3/checkpoint_handler.py:23-205 and
+qwen3_moe/checkpoint_handler.py.  All FQNs use the ``model.`` prefix of HF causal-LM classes.
+"""
+from __future__ import annotations
+
+import re
+from typing import Dict, Iterator, List, Tuple
+
+import torch
+
+
+def to_checkpoint_fqn(name: str) -> str:
+    """In-memory parameter name -> checkpoint FQN (``model.`` prefix except for ``lm_head``)."""
+    return name if name.startswith("lm_head") else "model." + name
+
+
+def from_checkpoint_fqn(name: str) -> str:
+    return name[len("model."):] if name.startswith("model.") else name
+
+
+class CheckpointHandler:
+    def __init__(self, cfg):
+        self.cfg = cfg
+        self.q, self.kv = cfg.q_size, cfg.kv_size
+        self.I = cfg.intermediate_size
+        self.moe_I = cfg.moe_intermediate_size
+
+    # ---- export: fused -> HF ------------------------------------------------------------------
+    def to_hf(self, name: str, t: torch.Tensor) -> Iterator[Tuple[str, torch.Tensor]]:
+        fq = to_checkpoint_fqn(name)
+        if ".self_attn.qkv_proj." in fq:
+            q, k, v = t.split([self.q, self.kv, self.kv], dim=0)
+            for n, part in (("q_proj", q), ("k_proj", k), ("v_proj", v)):
+                yield fq.replace("qkv_proj", n), part.contiguous()
+        elif ".mlp.experts.gate_up_proj" in fq:
+            E = t.shape[0]
+            base = fq[: fq.index(".experts.")]
+            for e in range(E):
+                g, u = t[e].split(t.shape[-1] // 2, dim=-1)          # [H, I] each
+                yield f"{base}.experts.{e}.gate_proj.weight", g.t().contiguous()
+                yield f"{base}.experts.{e}.up_proj.weight", u.t().contiguous()
+        elif ".mlp.experts.down_proj" in fq:
+            base = fq[: fq.index(".experts.")]
+            for e in range(t.shape[0]):
+                yield f"{base}.experts.{e}.down_proj.weight", t[e].t().contiguous()   # [H, I]
+        elif ".gate_up_proj." in fq:
+            g, u = t.split(t.shape[0] // 2, dim=0)
+            yield fq.replace("gate_up_proj", "gate_proj"), g.contiguous()
+            yield fq.replace("gate_up_proj", "up_proj"), u.contiguous()
+        else:
+            yield fq, t
+
+    # ---- import: HF -> fused ------------------------------------------------------------------
+    def hf_sources(self, name: str) -> List[str]:
+        """HF tensor names needed to build in-memory parameter ``name``."""
+        fq = to_checkpoint_fqn(name)
+        if ".self_attn.qkv_proj." in fq:
+            return [fq.replace("qkv_proj", n) for n in ("q_proj", "k_proj", "v_proj")]
+        if ".mlp.experts.gate_up_proj" in fq:
+            base = fq[: fq.index(".experts.")]
+            out = []
+            for e in range(self.cfg.num_experts):
+                out += [f"{base}.experts.{e}.gate_proj.weight", f"{base}.experts.{e}.up_proj.weight"]
+            return out
+        if ".mlp.experts.down_proj" in fq:
+            base = fq[: fq.index(".experts.")]
+            return [f"{base}.experts.{e}.down_proj.weight" for e in range(self.cfg.num_experts)]
+        if ".gate_up_proj." in fq:
+            return [fq.replace("gate_up_proj", "gate_proj"), fq.replace("gate_up_proj", "up_proj")]
+        return [fq]
+
+    def from_hf(self, name: str, parts: List[torch.Tensor]) -> torch.Tensor:
+        fq = to_checkpoint_fqn(name)
+        if ".mlp.experts.gate_up_proj" in fq:
+            E = len(parts) // 2
+            return torch.stack([torch.cat([parts[2 * e].t(), parts[2 * e + 1].t()], dim=-1)
+                                for e in range(E)])
+        if ".mlp.experts.down_proj" in fq:
+            return torch.stack([p.t() for p in parts])
+        if len(parts) == 1:
+            return parts[0]
+        return torch.cat(parts, dim=0)
+
+
+def get_checkpoint_handler(cfg) -> CheckpointHandler:
+    return CheckpointHandler(cfg)

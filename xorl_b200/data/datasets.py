@@ -1,0 +1,171 @@
+"""Datasets: synthetic ("dummy"), pre-tokenised JSONL / parquet / arrow, and a tokenising text
+loader.  ``prepare_datasets`` mirrors src/xorl/data/prepare/prepare_datasets.py: every entry of
+``data.datasets`` is ``{path, type, max_seq_len, ...}``; ``path: dummy`` builds identical samples
+``[1, 2, ..., L-1, 0]`` on every rank without I/O (src/xorl/data/prepare/prepare_datasets.py:43-87)."""
+from __future__ import annotations
+
+import glob
+import json
+import os
+from typing import Any, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+from torch.utils.data import Dataset
+
+
+class TokenDataset(Dataset):
+    """In-memory list of samples with ``input_ids`` / ``labels`` (unshifted) as int64 arrays."""
+
+    def __init__(self, samples: List[Dict[str, np.ndarray]]):
+        self.samples = samples
+
+    def __len__(self):
+        return len(self.samples)
+
+    def __getitem__(self, i):
+        return self.samples[i]
+
+    @property
+    def lengths(self) -> np.ndarray:
+        return np.array([len(s["input_ids"]) for s in self.samples], dtype=np.int64)
+
+
+class DummyDataset(Dataset):
+    """``num_samples`` identical samples of length k*16+1 (so that the shifted length is a
+    multiple of 16), tokens 1..L-1 followed by the end-of-document id 0."""
+
+    def __init__(self, seq_len: int, num_samples: int = 4096, vocab_size: int = 151936):
+        L = max(1, ((max(seq_len, 1) - 1) // 16) * 16 + 1)
+        toks = (np.arange(L, dtype=np.int64) + 1) % vocab_size
+        toks[-1] = 0
+        self.sample = {"input_ids": toks, "labels": toks.copy()}
+        self.n = num_samples
+        self.sample_len = L
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        return self.sample
+
+    @property
+    def lengths(self) -> np.ndarray:
+        return np.full(self.n, self.sample_len, dtype=np.int64)
+
+
+class RandomTokenDataset(Dataset):
+    """Documents with lengths uniform in [min_len, max_len] and tokens uniform over the vocabulary
+    (deterministic per index)."""
+
+    def __init__(self, num_samples: int, min_len: int, max_len: int, vocab_size: int, seed: int = 0):
+        self.n, self.min_len, self.max_len, self.vocab, self.seed = num_samples, min_len, max_len, vocab_size, seed
+        rng = np.random.default_rng(seed)
+        self._lengths = rng.integers(min_len, max_len + 1, size=num_samples, dtype=np.int64)
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        rng = np.random.default_rng(self.seed * 1000003 + i + 1)
+        toks = rng.integers(0, self.vocab, size=int(self._lengths[i]), dtype=np.int64)
+        return {"input_ids": toks, "labels": toks.copy()}
+
+    @property
+    def lengths(self) -> np.ndarray:
+        return self._lengths
+
+
+def _read_jsonl(path: str) -> List[Dict[str, Any]]:
+    rows = []
+    with open(path) as f:
+        for line in f:
+            line = line.strip()
+            if line:
+                rows.append(json.loads(line))
+    return rows
+
+
+def _load_rows(path: str) -> List[Dict[str, Any]]:
+    files: List[str] = []
+    if os.path.isdir(path):
+        for ext in ("*.jsonl", "*.json", "*.parquet", "*.arrow"):
+            files += sorted(glob.glob(os.path.join(path, ext)))
+    else:
+        files = [path]
+    rows: List[Dict[str, Any]] = []
+    for f in files:
+        if f.endswith(".jsonl"):
+            rows += _read_jsonl(f)
+        elif f.endswith(".json"):
+            with open(f) as fh:
+                d = json.load(fh)
+            rows += d if isinstance(d, list) else [d]
+        elif f.endswith(".parquet"):
+            import pyarrow.parquet as pq
+            rows += pq.read_table(f).to_pylist()
+        elif f.endswith(".arrow"):
+            import pyarrow as pa
+            with pa.memory_map(f) as src:
+                rows += pa.ipc.open_file(src).read_all().to_pylist()
+        else:
+            raise ValueError(f"unsupported dataset file {f}")
+    return rows
+
+
+def prepare_datasets(specs: Sequence[Dict[str, Any]], tokenizer=None, vocab_size: int = 151936,
+                     select_columns: Optional[Sequence[str]] = None, seed: int = 42) -> Dataset:
+    """Builds (and concatenates) the datasets named by ``data.datasets``."""
+    built: List[Dataset] = []
+    for spec in specs:
+        path = spec.get("path")
+        kind = spec.get("type", "tokenized")
+        max_len = int(spec.get("max_seq_len", 4096))
+        if path == "dummy":
+            built.append(DummyDataset(max_len, int(spec.get("num_samples", 4096)), vocab_size))
+            continue
+        if path == "random":
+            built.append(RandomTokenDataset(int(spec.get("num_samples", 4096)),
+                                            int(spec.get("min_seq_len", 256)), max_len, vocab_size,
+                                            int(spec.get("seed", seed))))
+            continue
+        rows = _load_rows(path)
+        samples = []
+        for r in rows:
+            if kind == "tokenized":
+                ids = np.asarray(r["input_ids"], dtype=np.int64)
+                labels = np.asarray(r.get("labels", r["input_ids"]), dtype=np.int64)
+            else:
+                if tokenizer is None:
+                    raise ValueError(f"dataset type {kind!r} needs a tokenizer")
+                text = r.get(spec.get("text_column", "text"))
+                if text is None and "messages" in r:
+                    text = tokenizer.apply_chat_template(r["messages"], tokenize=False)
+                ids = np.asarray(tokenizer(text)["input_ids"], dtype=np.int64)
+                labels = ids.copy()
+            ids, labels = ids[:max_len], labels[:max_len]
+            if len(ids) >= 2:
+                samples.append({"input_ids": ids, "labels": labels})
+        built.append(TokenDataset(samples))
+    if not built:
+        raise ValueError("data.datasets is empty")
+    if len(built) == 1:
+        return built[0]
+    return ConcatTokenDataset(built)
+
+
+class ConcatTokenDataset(Dataset):
+    def __init__(self, parts: Sequence[Dataset]):
+        self.parts = list(parts)
+        self.cum = np.cumsum([0] + [len(p) for p in self.parts])
+
+    def __len__(self):
+        return int(self.cum[-1])
+
+    def __getitem__(self, i):
+        k = int(np.searchsorted(self.cum, i, side="right") - 1)
+        return self.parts[k][i - int(self.cum[k])]
+
+    @property
+    def lengths(self):
+        return np.concatenate([p.lengths for p in self.parts])

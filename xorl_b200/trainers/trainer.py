@@ -1,0 +1,283 @@
+"""Training loop shared by the CLI and the server runner.
+
+Phases follow the reference trainer (src/xorl/trainers/trainer.py:340-376 start-up, :1369-1499
+loop, :1743-1880 step): bootstrap process groups -> build model on the meta device -> ZeRO engine
+materialises and shards it -> data -> optimizer / LR schedule -> resume -> loop.  A step is:
+count valid tokens (all-reduce over dp x sp) -> forward/backward over the micro-batches with
+losses pre-scaled by 1/global_tokens -> finish gradient reduction -> global-norm clip coefficient
+on the device -> fused optimizer step -> LR step.  Artifacts: ``xorl_cli.yaml``,
+``startup_metrics.json``, ``training_metrics.json``, ``checkpoints/global_step_N``.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..arguments import Arguments, save_args
+from ..data import build_dataloader, prepare_datasets
+from ..models import build_model_config, build_model
+from ..optim import build_lr_scheduler, build_optimizer
+from ..parallel.state import get_parallel_state, init_parallel_state, process_group_timeout
+from ..parallel.zero import Zero3Engine
+from ..utils.helper import CudaTimer, EnvironMeter, create_profiler, set_seed
+from ..utils.logging import get_logger, info_rank0
+
+logger = get_logger(__name__)
+IGNORE_INDEX = -100
+
+
+def resolve_device(pref: str = "auto") -> torch.device:
+    if pref == "cpu" or (pref == "auto" and not torch.cuda.is_available()):
+        return torch.device("cpu")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    return torch.device("cuda", local)
+
+
+class Trainer:
+    def __init__(self, args: Arguments, dataset=None, model_config=None):
+        self.args = args
+        self.startup: Dict[str, float] = {}
+        self.global_step = 0
+        self.loss_history: List[float] = []
+        self.metrics_history: List[Dict[str, float]] = []
+        self._timed("bootstrap", self._bootstrap)
+        self._timed("build_model", lambda: self._build_model(model_config))
+        self._timed("build_data", lambda: self._build_data(dataset))
+        self._timed("build_optimizer", self._build_optimizer)
+        self._timed("observability", self._setup_observability)
+        self._timed("resume", self._resume_checkpoint)
+        if self.ps.rank == 0:
+            os.makedirs(args.train.output_dir, exist_ok=True)
+            with open(os.path.join(args.train.output_dir, "startup_metrics.json"), "w") as f:
+                json.dump(self.startup, f, indent=2)
+
+    def _timed(self, name, fn):
+        t0 = time.perf_counter()
+        fn()
+        self.startup[name + "_s"] = time.perf_counter() - t0
+
+    # ------------------------------------------------------------------------------------------
+    def _bootstrap(self) -> None:
+        t = self.args.train
+        self.device = resolve_device(t.device)
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if world > 1 and not dist.is_initialized():
+            backend = "nccl" if self.device.type == "cuda" else "gloo"
+            kw = {"device_id": self.device} if backend == "nccl" else {}
+            dist.init_process_group(backend, timeout=process_group_timeout(), **kw)
+        set_seed(t.seed, t.enable_full_determinism)
+        self.ps = init_parallel_state(
+            dp_replicate_size=t.data_parallel_replicate_size, dp_shard_size=t.data_parallel_shard_size,
+            tp_size=t.tensor_parallel_size, ep_size=t.expert_parallel_size,
+            pp_size=t.pipeline_parallel_size, ulysses_size=t.ulysses_parallel_size,
+            ringattn_size=t.ringattn_parallel_size, lm_head_tp_size=t.lm_head_tensor_parallel_size,
+            dp_mode=t.data_parallel_mode, cp_fsdp_mode=t.cp_fsdp_mode, device_type=self.device.type,
+            ep_intranode=t.ep_intranode)
+        if self.ps.rank == 0:
+            save_args(self.args, t.output_dir)
+        self.compute_dtype = torch.bfloat16 if (t.enable_mixed_precision and self.device.type == "cuda") \
+            else torch.float32
+
+    def _build_model(self, model_config=None) -> None:
+        a, t = self.args, self.args.train
+        self.model_config = model_config or build_model_config(a.model)
+        self.model = build_model(self.model_config, a, device="meta")
+        if t.ce_num_chunks and t.ce_num_chunks > 0:
+            self.model.loss_chunk_tokens = max(256, -(-int(a.data.sample_packing_sequence_len or 4096)
+                                                      * t.micro_batch_size // t.ce_num_chunks))
+        from ..parallel.cp import attach_cp_strategy
+        attach_cp_strategy(self.model, self.ps)
+        recompute = t.enable_gradient_checkpointing and t.gradient_checkpointing_method != "no_recompute"
+        self.engine = Zero3Engine(
+            self.model, self.ps, compute_dtype=self.compute_dtype, device=self.device,
+            reduce_dtype=torch.float32 if t.fsdp_reduce_dtype == "fp32" else torch.bfloat16,
+            reshard_after_forward=True if t.reshard_after_forward is None else t.reshard_after_forward,
+            recompute=recompute, seed=t.seed, comm_backend=t.comm_backend)
+        if t.comm_backend in ("auto", "fused") and self.device.type == "cuda" and self.ps.world_size > 1:
+            from ..parallel.symm import try_attach_symmetric_transport
+            try_attach_symmetric_transport(self.engine, required=(t.comm_backend == "fused"))
+        weights = a.model.model_path
+        if weights and t.load_weights_mode != "skip" and os.path.isdir(weights) and any(
+                f.endswith(".safetensors") for f in os.listdir(weights)):
+            from ..checkpoint.hf_io import load_hf_weights
+            load_hf_weights(self.engine, weights, self.model_config)
+
+    def _build_data(self, dataset=None) -> None:
+        a = self.args
+        if dataset is None:
+            dataset = prepare_datasets(a.data.datasets, vocab_size=self.model_config.vocab_size,
+                                       select_columns=a.data.select_columns, seed=a.train.seed)
+        shard = None
+        if self.ps.sp_size > 1:
+            from ..data import SequenceShardCollator
+            shard = SequenceShardCollator(self.ps.ringattn_size, self.ps.ulysses_size,
+                                          self.ps.ringattn_rank, self.ps.ulysses_rank)
+        self.dataloader = build_dataloader(dataset, a.data, a.train, self.ps, shard)
+        spe = max(1, len(self.dataloader))
+        self.train_steps = a.train.max_steps or spe * a.train.num_train_epochs
+        self.steps_per_epoch = spe
+
+    def _build_optimizer(self) -> None:
+        t = self.args.train
+        self.optimizer = build_optimizer(
+            self.engine, lr=t.lr, weight_decay=t.weight_decay, optimizer_type=t.optimizer,
+            optimizer_dtype=t.optimizer_dtype, no_decay_modules=t.no_decay_modules,
+            no_decay_params=t.no_decay_params, cautious_weight_decay=t.cautious_weight_decay,
+            optimizer_kwargs={k: getattr(t, k) for k in vars(t) if k.startswith("muon_")}
+            if t.optimizer == "muon" else None)
+        self.lr_scheduler = build_lr_scheduler(self.optimizer, self.train_steps, t.lr, t.lr_min,
+                                               t.lr_start, t.lr_warmup_ratio, t.lr_decay_style,
+                                               t.lr_decay_ratio)
+
+    def _setup_observability(self) -> None:
+        t = self.args.train
+        self.meter = EnvironMeter(self.model_config, self.ps.world_size, self.ps.group("dp"),
+                                  recompute=t.enable_gradient_checkpointing)
+        self.timer = CudaTimer(t.enable_step_phase_timing)
+        self.profiler = None
+        if t.enable_profiling and (not t.profile_rank0_only or self.ps.rank == 0):
+            self.profiler = create_profiler(t.profile_start_step, t.profile_end_step, t.profile_trace_dir,
+                                            t.profile_record_shapes, t.profile_profile_memory,
+                                            t.profile_with_stack, self.ps.rank)
+            self.profiler.start()
+        from ..checkpoint import build_checkpointer
+        self.checkpointer = build_checkpointer(self)
+
+    def _resume_checkpoint(self) -> None:
+        path = self.args.train.load_checkpoint_path
+        if not path:
+            return
+        from ..checkpoint import resolve_checkpoint_path
+        path = resolve_checkpoint_path(path, self.args.train.checkpoint_dir)
+        if path is None:
+            info_rank0("no checkpoint to resume from; starting fresh")
+            return
+        extra = self.checkpointer.load(path, load_optimizer=self.args.train.load_optimizer)
+        self.global_step = int(extra.get("global_step", 0))
+        if "lr_scheduler" in extra:
+            self.lr_scheduler.load_state_dict(extra["lr_scheduler"])
+        if "train_dataloader" in extra:
+            self.dataloader.load_state_dict(extra["train_dataloader"])
+        if "environ_meter" in extra:
+            self.meter.load_state_dict(extra["environ_meter"])
+        if "torch_rng_state" in extra:
+            torch.set_rng_state(extra["torch_rng_state"])
+        info_rank0(f"resumed from {path} at step {self.global_step}")
+
+    # ------------------------------------------------------------------------------------------
+    def count_valid_tokens(self, micro_batches) -> int:
+        """Global number of supervised tokens of this step (labels != -100), summed over the
+        dp x sp ranks (src/xorl/trainers/training_utils.py:229-249)."""
+        local = sum(int(mb["num_valid_tokens"]) if "num_valid_tokens" in mb
+                    else int((mb["labels"] != IGNORE_INDEX).sum()) for mb in micro_batches)
+        pg_name = self.ps.loss_group_name
+        if self.ps.world_size > 1 and pg_name in self.ps.groups and self.ps.groups[pg_name].pg is not None:
+            t = torch.tensor([local], dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, group=self.ps.group(pg_name))
+            return int(t.item())
+        return local
+
+    def _to_device(self, mb: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        return {k: (v.to(self.device, non_blocking=True) if torch.is_tensor(v) else v)
+                for k, v in mb.items()}
+
+    def train_step(self, micro_batches: List[Dict[str, torch.Tensor]]) -> Dict[str, Any]:
+        t = self.args.train
+        global_tokens = max(1, self.count_valid_tokens(micro_batches))
+        self.optimizer.zero_grad()
+        total = None
+        for mb in micro_batches:
+            self.meter.add(mb)
+            d = self._to_device(mb)
+            loss = self.engine.forward_backward(
+                d["input_ids"], d["labels"], position_ids=d.get("position_ids"),
+                cu_seqlens=d.get("cu_seqlens"), grad_scale=1.0 / global_tokens,
+                extra_loss_fn=self._extra_loss_fn())
+            total = loss if total is None else total + loss
+        self.engine.finish_grad_sync()
+        norm, coef = self.engine.grad_norm_and_clip_coef(t.max_grad_norm)
+        self.optimizer.step(clip_coef=coef if t.max_grad_norm > 0 else None)
+        self.lr_scheduler.step()
+        if self.ps.world_size > 1 and self.ps.group(self.ps.loss_group_name) is not None:
+            dist.all_reduce(total, group=self.ps.group(self.ps.loss_group_name))
+        self.global_step += 1
+        return {"loss": total, "grad_norm": norm, "lr": self.optimizer.lr, "tokens": global_tokens}
+
+    def _extra_loss_fn(self):
+        return None
+
+    # ------------------------------------------------------------------------------------------
+    def train(self) -> Dict[str, Any]:
+        t = self.args.train
+        done = False
+        while not done:
+            for micro_batches in self.dataloader:
+                if self.global_step >= self.train_steps:
+                    done = True
+                    break
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize()
+                t0 = time.time()
+                out = self.train_step(micro_batches)
+                loss = float(out["loss"])           # device -> host read of the step result
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize()
+                dt = time.time() - t0
+                metrics = self.meter.step(dt, self.global_step)
+                metrics.update(loss=loss, grad_norm=float(out["grad_norm"]), lr=out["lr"],
+                               step=self.global_step, step_time=dt)
+                self.loss_history.append(loss)
+                self.metrics_history.append(metrics)
+                self._maybe_log(metrics)
+                if self.profiler is not None:
+                    self.profiler.step()
+                self._maybe_save_checkpoint()
+                if t.empty_cache_steps and self.global_step % t.empty_cache_steps == 0 \
+                        and self.device.type == "cuda":
+                    torch.cuda.empty_cache()
+            else:
+                if self.global_step >= self.train_steps:
+                    done = True
+            if len(self.dataloader) == 0:
+                break
+        return self._finalize()
+
+    def _maybe_log(self, m: Dict[str, float]) -> None:
+        if self.ps.rank != 0:
+            return
+        logger.info("step %d/%d loss %.4f grad_norm %.3f lr %.3e tok/s %.1fK mfu %.3f step %.3fs",
+                    m["step"], self.train_steps, m["loss"], m["grad_norm"], m["lr"],
+                    m["tokens_per_second(K)"], m["efficiency/mfu"], m["step_time"])
+
+    def _maybe_save_checkpoint(self, force: bool = False) -> None:
+        t = self.args.train
+        if not force and not (t.save_steps and self.global_step % t.save_steps == 0):
+            return
+        extra = {"global_step": self.global_step, "lr_scheduler": self.lr_scheduler.state_dict(),
+                 "train_dataloader": self.dataloader.state_dict(),
+                 "environ_meter": self.meter.state_dict(), "torch_rng_state": torch.get_rng_state()}
+        self.checkpointer.save(self.global_step, extra)
+
+    def _finalize(self) -> Dict[str, Any]:
+        t = self.args.train
+        if self.profiler is not None:
+            self.profiler.stop()
+        result = {"loss_history": self.loss_history, "global_step": self.global_step,
+                  "metrics": self.metrics_history[-1] if self.metrics_history else {}}
+        if t.save_hf_weights and self.global_step > 0 and t.save_steps >= 0 and \
+                os.environ.get("XORL_SKIP_FINAL_EXPORT", "0") != "1":
+            from ..checkpoint.hf_io import save_hf_weights
+            out_dir = os.path.join(t.output_dir, f"global_step_{self.global_step}", "hf_ckpt")
+            save_hf_weights(self.engine, out_dir, self.model_config)
+        if self.ps.rank == 0:
+            with open(os.path.join(t.output_dir, "training_metrics.json"), "w") as f:
+                json.dump(result, f, indent=2, default=float)
+        if dist.is_initialized():
+            dist.barrier()
+        return result
