@@ -1,0 +1,107 @@
+"""Mixture-of-experts block: router, stacked experts, load-balancing loss, expert parallelism.
+
+Parameter layout matches the reference (src/xorl/models/layers/moe/experts.py:1576-1584):
+``mlp.gate.weight [E, H]``, ``mlp.experts.gate_up_proj [E, H, 2I]``, ``mlp.experts.down_proj
+[E, I, H]``.  Routing is softmax -> top-k -> optional renormalisation in fp32
+(src/xorl/models/layers/moe/router.py:232-259); the auxiliary loss is the switch-style
+load-balancing loss ``E * sum_e f_e * P_e`` (src/xorl/models/layers/moe/aux_loss.py:67).
+With expert parallelism the expert tensors hold only the local ``E / ep`` experts and tokens are
+exchanged through ``xorl_b200.parallel.ep`` (all-to-all baseline or the fused peer-memory path).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ..ops import moe as moe_ops
+from ..parallel.state import get_parallel_state
+from .config import ModelConfig
+from .context import StepContext
+from .layers import MLP, Linear
+
+
+class TopKRouter(nn.Module):
+    def __init__(self, cfg: ModelConfig, dtype=None, device=None):
+        super().__init__()
+        self.top_k = cfg.num_experts_per_tok
+        self.num_experts = cfg.num_experts
+        self.norm_topk_prob = cfg.norm_topk_prob
+        self.scoring = cfg.scoring_func
+        self.scale = cfg.routed_scaling_factor
+        self.weight = nn.Parameter(torch.empty(cfg.num_experts, cfg.hidden_size, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(cfg.num_experts, dtype=dtype, device=device)) \
+            if cfg.router_bias else None
+
+    def forward(self, x: torch.Tensor):
+        """x [T, H] -> (weights fp32 [T, k], indices int64 [T, k], probs fp32 [T, E])."""
+        logits = torch.nn.functional.linear(x.float(), self.weight.float(),
+                                            None if self.bias is None else self.bias.float())
+        return moe_ops.topk_route(logits, self.top_k, self.norm_topk_prob, self.scoring, self.scale)
+
+
+class Experts(nn.Module):
+    """Stacked expert weights; ``num_local`` experts live on this rank."""
+
+    def __init__(self, cfg: ModelConfig, num_local: int, dtype=None, device=None):
+        super().__init__()
+        H, I = cfg.hidden_size, cfg.moe_intermediate_size
+        self.num_local = num_local
+        self.gate_up_proj = nn.Parameter(torch.empty(num_local, H, 2 * I, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(num_local, I, H, dtype=dtype, device=device))
+        self.gate_up_proj._xb_expert = True
+        self.down_proj._xb_expert = True
+        self.swiglu_limit = cfg.swiglu_limit
+
+    def forward(self, x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:
+        """x_sorted [M, H] grouped by local expert; tokens_per_expert int64 [num_local]."""
+        return moe_ops.expert_mlp(x_sorted, tokens_per_expert, self.gate_up_proj, self.down_proj)
+
+
+class MoEBlock(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        ps = get_parallel_state()
+        self.ep_size = ps.ep_size
+        if cfg.num_experts % self.ep_size:
+            raise ValueError(f"num_experts {cfg.num_experts} not divisible by ep {self.ep_size}")
+        self.num_local = cfg.num_experts // self.ep_size
+        self.gate = TopKRouter(cfg, dtype=dtype, device=device)
+        self.experts = Experts(cfg, self.num_local, dtype=dtype, device=device)
+        self.shared_expert = None
+        if cfg.shared_expert_intermediate_size:
+            self.shared_expert = MLP(cfg.hidden_size, cfg.shared_expert_intermediate_size,
+                                     dtype=dtype, device=device)
+        self.aux_coef = cfg.router_aux_loss_coef
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        T, H = x.shape
+        replay = ctx.aux.get(("routing_replay", self.layer_idx))
+        weights, indices, probs = self.gate(x)
+        if replay is not None:
+            # replay recorded expert choices (recompute / pipeline backward / rollout routing);
+            # the weights are re-derived from the current probabilities so gradients still flow
+            indices = replay
+            weights = probs.gather(1, indices)
+            if self.cfg.norm_topk_prob:
+                weights = weights / weights.sum(-1, keepdim=True).clamp_min(1e-20)
+        elif ctx.aux.get("record_routing", False):
+            ctx.aux[("routing_record", self.layer_idx)] = indices.detach()
+        if ctx.training and self.aux_coef > 0 and ctx.aux.get("aux_loss_scale") is not None:
+            aux = moe_ops.load_balancing_loss(probs, indices, self.cfg.num_experts,
+                                              ctx.aux.get("aux_global_group"))
+            ctx.aux[("aux_loss", self.layer_idx)] = aux * (self.aux_coef * ctx.aux["aux_loss_scale"])
+        if ctx.aux.get("collect_expert_load", False):
+            ctx.aux[("expert_load", self.layer_idx)] = torch.bincount(
+                indices.reshape(-1), minlength=self.cfg.num_experts)
+        if self.ep_size > 1:
+            from ..parallel import ep as ep_ops
+            out = ep_ops.ep_moe_forward(x, weights, indices, self.experts, self.cfg.num_experts, ctx)
+        else:
+            out = moe_ops.local_moe_forward(x, weights, indices, self.experts, self.cfg.num_experts)
+        if self.shared_expert is not None:
+            out = out + self.shared_expert(x)
+        return out

@@ -1,0 +1,210 @@
+"""MoE operators: top-k routing, load-balancing loss, token permutation, grouped expert MLP.
+
+CUDA path: ``csrc/moe.cu`` (routing / histogram / aligned sort indices / gather / weighted
+scatter, no host synchronisation) and ``csrc/grouped_gemm.cu`` (tcgen05 grouped GEMM over
+128-row-aligned expert segments).  CPU path: plain PyTorch with identical semantics.
+Reference counterparts: src/xorl/models/layers/moe/router.py:232-259,
+src/xorl/ops/group_gemm/kernel/group_gemm.py:80-377, src/xorl/ops/group_gemm/kernel/moe.py:45-433.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .activation import swiglu
+from .grad_sink import deliver_param_grad, grad_target, mark_written
+
+SEG_ALIGN = 128  # expert segments of the sorted token buffer start at multiples of 128 rows
+_launches = 0
+
+
+def launch_count() -> int:
+    return _launches
+
+
+# --------------------------------------------------------------------------------------------
+# routing
+# --------------------------------------------------------------------------------------------
+def topk_route(logits: torch.Tensor, k: int, renorm: bool = True, scoring: str = "softmax",
+               scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """fp32 logits [T, E] -> (weights [T, k], indices [T, k], probs [T, E])."""
+    if scoring == "sigmoid":
+        probs = torch.sigmoid(logits)
+    else:
+        probs = torch.softmax(logits, dim=-1, dtype=torch.float32)
+    weights, indices = torch.topk(probs, k, dim=-1)
+    if renorm:
+        weights = weights / weights.sum(-1, keepdim=True).clamp_min(1e-20)
+    if scale != 1.0:
+        weights = weights * scale
+    return weights, indices, probs
+
+
+def load_balancing_loss(probs: torch.Tensor, indices: torch.Tensor, num_experts: int,
+                        global_group=None) -> torch.Tensor:
+    """``E * sum_e f_e * P_e`` with f_e the fraction of routed slots sent to expert e and P_e the
+    mean router probability.  With ``global_group`` the counts are summed over that group."""
+    T, k = indices.shape
+    counts = torch.zeros(num_experts, device=probs.device, dtype=torch.float32)
+    counts.scatter_add_(0, indices.reshape(-1), torch.ones(T * k, device=probs.device))
+    total = torch.tensor(float(T), device=probs.device)
+    if global_group is not None:
+        dist.all_reduce(counts, group=global_group)
+        dist.all_reduce(total, group=global_group)
+    f = counts / (total * k)
+    P = probs.mean(0)
+    return num_experts * torch.sum(f.detach() * P)
+
+
+# --------------------------------------------------------------------------------------------
+# permutation helpers (aligned segments)
+# --------------------------------------------------------------------------------------------
+def aligned_sort_indices(expert_ids: torch.Tensor, num_experts: int, align: int = SEG_ALIGN):
+    """For a flat list of expert ids [S] returns
+       dest   int64 [S]   row of every slot in the sorted, segment-aligned buffer,
+       seg    int32 [E+1] aligned start row of each expert segment (seg[E] = total rows),
+       counts int64 [E]   real rows per expert.
+    Stable (slots of one expert keep their order), no host sync; the buffer size bound
+    ``S + E*(align-1)`` rounded up to ``align`` is what callers allocate."""
+    S = expert_ids.numel()
+    counts = torch.bincount(expert_ids, minlength=num_experts)
+    padded = (counts + align - 1) // align * align
+    seg = torch.zeros(num_experts + 1, device=expert_ids.device, dtype=torch.int64)
+    seg[1:] = torch.cumsum(padded, 0)
+    order = torch.argsort(expert_ids, stable=True)
+    starts_unpadded = torch.cumsum(counts, 0) - counts
+    sorted_e = expert_ids[order]
+    rank_in_e = torch.arange(S, device=expert_ids.device) - starts_unpadded[sorted_e]
+    dest_sorted = seg[:-1][sorted_e] + rank_in_e
+    dest = torch.empty_like(dest_sorted)
+    dest[order] = dest_sorted
+    return dest, seg.to(torch.int32), counts
+
+
+def buffer_rows(num_slots: int, num_experts: int, align: int = SEG_ALIGN) -> int:
+    return (num_slots + num_experts * (align - 1) + align - 1) // align * align
+
+
+# --------------------------------------------------------------------------------------------
+# grouped GEMM
+# --------------------------------------------------------------------------------------------
+def _grouped_rows_cuda(a, b, seg, out, b_kmajor: bool):
+    """out[rows of e] = a[rows of e] @ op(b[e]); b [E, K, N] (b_kmajor False) or [E, N, K]."""
+    global _launches
+    E = b.shape[0]
+    if b_kmajor:
+        N, K = b.shape[1], b.shape[2]
+    else:
+        K, N = b.shape[1], b.shape[2]
+    rc = _lib.cuda_lib().xb_grouped_gemm_rows(a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                              seg.data_ptr(), E, a.shape[0], N, K, a.stride(0),
+                                              out.stride(0), int(not b_kmajor), _lib.stream_ptr())
+    _lib.check(rc, "xb_grouped_gemm_rows")
+    _launches += 1
+    return out
+
+
+def _grouped_wgrad_cuda(a, b, seg, out, accumulate: bool):
+    """out[e] (+)= a[rows of e]^T @ b[rows of e]; a [R, M], b [R, N], out [E, M, N]."""
+    global _launches
+    E, M, N = out.shape
+    rc = _lib.cuda_lib().xb_grouped_gemm_wgrad(a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                               seg.data_ptr(), E, a.shape[0], M, N, a.stride(0),
+                                               b.stride(0), int(out.dtype == torch.float32),
+                                               int(accumulate), _lib.stream_ptr())
+    _lib.check(rc, "xb_grouped_gemm_wgrad")
+    _launches += 1
+    return out
+
+
+def _grouped_rows_ref(a, b, seg, b_kmajor: bool):
+    E = b.shape[0]
+    N = b.shape[1] if b_kmajor else b.shape[2]
+    out = a.new_zeros((a.shape[0], N))
+    s = seg.tolist()
+    for e in range(E):
+        if s[e + 1] > s[e]:
+            w = b[e].t() if b_kmajor else b[e]
+            out[s[e]:s[e + 1]] = (a[s[e]:s[e + 1]].float() @ w.float()).to(a.dtype)
+    return out
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """y[rows of e] = x[rows of e] @ w[e]  with w [E, K, N]; padding rows of x must be zero."""
+
+    @staticmethod
+    def forward(ctx, x, w, seg):
+        ctx.save_for_backward(x, seg)
+        ctx.w = w
+        out = torch.empty((x.shape[0], w.shape[2]), device=x.device, dtype=x.dtype)
+        return _grouped_rows_cuda(x, w, seg, out, b_kmajor=False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, seg = ctx.saved_tensors
+        w = ctx.w
+        dy = dy.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            _grouped_rows_cuda(dy, w, seg, dx, b_kmajor=True)   # dx = dy @ w[e]^T
+        dw = None
+        if ctx.needs_input_grad[1]:
+            tgt, fresh = grad_target(w)
+            if tgt is not None:
+                _grouped_wgrad_cuda(x, dy, seg, tgt, accumulate=not fresh)
+                mark_written(w)
+            else:
+                dw = torch.empty_like(w)
+                _grouped_wgrad_cuda(x, dy, seg, dw, accumulate=False)
+        return dx, dw, None
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg: torch.Tensor) -> torch.Tensor:
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 \
+            and w.shape[1] % 8 == 0 and w.shape[2] % 8 == 0:
+        return _GroupedLinear.apply(x, w, seg)
+    # CPU lane: differentiable loop over experts
+    outs = []
+    s = seg.tolist()
+    for e in range(w.shape[0]):
+        outs.append(x[s[e]:s[e + 1]] @ w[e])
+    return torch.cat(outs, 0) if outs else x.new_zeros((0, w.shape[2]))
+
+
+def expert_mlp_aligned(x_buf: torch.Tensor, seg: torch.Tensor, gate_up: torch.Tensor,
+                       down: torch.Tensor) -> torch.Tensor:
+    """SwiGLU expert MLP over a segment-aligned token buffer."""
+    h = grouped_linear(x_buf, gate_up, seg)
+    return grouped_linear(swiglu(h), down, seg)
+
+
+def expert_mlp(x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor, gate_up: torch.Tensor,
+               down: torch.Tensor) -> torch.Tensor:
+    """Unaligned variant (rows exactly grouped by expert): pads to aligned segments internally."""
+    E = gate_up.shape[0]
+    ids = torch.repeat_interleave(torch.arange(E, device=x_sorted.device), tokens_per_expert)
+    dest, seg, _ = aligned_sort_indices(ids, E)
+    buf = x_sorted.new_zeros((buffer_rows(x_sorted.shape[0], E), x_sorted.shape[1]))
+    buf = buf.index_copy(0, dest, x_sorted)
+    out = expert_mlp_aligned(buf, seg, gate_up, down)
+    return out.index_select(0, dest)
+
+
+def local_moe_forward(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor, experts,
+                      num_experts: int) -> torch.Tensor:
+    """All experts local: gather tokens into expert-sorted aligned segments, run the grouped MLP,
+    combine the k expert outputs of every token with its routing weights (fp32 accumulation)."""
+    T, H = x.shape
+    k = indices.shape[1]
+    dest, seg, _ = aligned_sort_indices(indices.reshape(-1), num_experts)
+    rows = buffer_rows(T * k, num_experts)
+    token_of_slot = torch.arange(T, device=x.device).repeat_interleave(k)
+    buf = x.new_zeros((rows, H)).index_copy(0, dest, x.index_select(0, token_of_slot))
+    y = expert_mlp_aligned(buf, seg, experts.gate_up_proj, experts.down_proj)
+    y_slots = y.index_select(0, dest).reshape(T, k, H)
+    out = (y_slots.float() * weights.unsqueeze(-1).float()).sum(1)
+    return out.to(x.dtype)

@@ -87,10 +87,10 @@ class FlatParamGroup:
         for _, p in self.named_params:
             p.data = empty
 
-    def attach_grad_views(self) -> None:
+    def attach_grad_views(self, fresh: bool = True) -> None:
         for (_, p), v in zip(self.named_params, self.param_views(self.grad_full)):
             p._xb_grad_buf = v
-            p._xb_grad_fresh = True
+            p._xb_grad_fresh = fresh
             p.grad = None
 
     def collect_grads(self) -> None:
@@ -311,8 +311,13 @@ class Zero3Engine:
     # ---------------------------------------------------------------------------------------
     def _prepare_grad_buffers(self, unit: ZeroUnit) -> None:
         for g in unit.groups:
-            g.grad_full = self._take_full(g.padded, self.compute_dtype)
-            g.attach_grad_views()
+            if g.world == 1:
+                # single owner: kernels write (or accumulate) straight into the fp32 accumulator
+                g.grad_full = g.grad_shard
+                g.attach_grad_views(fresh=not g.grad_ready)
+            else:
+                g.grad_full = self._take_full(g.padded, self.compute_dtype)
+                g.attach_grad_views()
 
     def _reduce_unit_grads(self, unit: ZeroUnit) -> None:
         for g in unit.groups:
@@ -320,14 +325,7 @@ class Zero3Engine:
             accumulate = g.grad_ready
             gf = g.grad_full
             if g.world == 1:
-                if gf.dtype == torch.float32:
-                    if accumulate:
-                        g.grad_shard.add_(gf)
-                    else:
-                        g.grad_shard.copy_(gf)
-                else:
-                    optim_ops.cast_accum_(gf, g.grad_shard, 1.0, accumulate)
-                self._give_full(gf)
+                pass  # gradients were produced in place in g.grad_shard
             elif self.symm is not None and self.symm.can_reduce(g):
                 self.symm.reduce_scatter_accumulate(g, gf, accumulate, self.comm_stream)
             elif self.is_cuda:
