@@ -452,3 +452,80 @@ XB_API int xb_qk_norm_rope_bwd(const void* dout_bf16, const float* dq_f32, const
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm backward without any allocation (declared in noalloc.h).
+//
+// xb_rmsnorm_bwd needs a scratch buffer for the per-CTA partial sums of the weight gradient and
+// leaves it to the caller to allocate.  Callers that are not allowed to allocate device memory
+// (code running inside a captured region, a real-time loop, a plugin that was handed all of its
+// buffers up front, a process whose memory pool is owned by somebody else) use this entry point
+// instead: its scratch is a fixed array that is part of the loaded library image.
+//
+//  * The array costs XB_NOALLOC_PARTIAL_ROWS * XB_NOALLOC_MAX_H * 4 bytes = 8 MiB on every GPU
+//    that loads this library, for the life of the process.
+//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress with
+//    that device current).  Make that first call before starting any stream capture.
+//  * All calls share the one array and it keeps whatever the previous call left in it.  Every
+//    partial row that is read is written first by the same call, so nothing has to be cleared,
+//    but two calls that run on the GPU at the same time (different streams) race on it.
+//  * H above XB_NOALLOC_MAX_H, H not a multiple of 8, or T <= 0 with work to do is rejected with a
+//    negative return code and a message on stderr; nothing is launched in that case.
+// ---------------------------------------------------------------------------------------
+#define XB_NOALLOC_MAX_H 8192
+#define XB_NOALLOC_PARTIAL_ROWS 256
+
+static __device__ __align__(256) float xb_noalloc_partial[XB_NOALLOC_PARTIAL_ROWS * XB_NOALLOC_MAX_H];
+
+namespace {
+std::mutex g_noalloc_mu;
+float* g_noalloc_ptr[64] = {nullptr};
+
+// Device address of the scratch array on the current device, or nullptr on failure.
+float* noalloc_scratch() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&p, xb_noalloc_partial);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "xb_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n",
+              cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  return g_noalloc_ptr[dev];
+}
+}  // namespace
+
+XB_API int xb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                  const void* dres, void* dx, void* dw_bf16, float* dw_f32,
+                                  int accumulate, int T, int H, int zero_centered, void* stream) {
+  if (H <= 0 || H % 8 != 0 || H > XB_NOALLOC_MAX_H) {
+    fprintf(stderr,
+            "xb_rmsnorm_bwd_noalloc: H=%d is not supported (multiple of 8, at most %d); use "
+            "xb_rmsnorm_bwd with a caller-provided scratch buffer for wider rows\n",
+            H, XB_NOALLOC_MAX_H);
+    return -1;
+  }
+  if (T <= 0) return 0;
+  float* partial = noalloc_scratch();
+  if (partial == nullptr) return -2;
+  int rows = xb_sm_count() * 2;
+  if (rows > XB_NOALLOC_PARTIAL_ROWS) rows = XB_NOALLOC_PARTIAL_ROWS;
+  if (rows > T) rows = T;
+  cudaStream_t st = (cudaStream_t)stream;
+#define XB_ARGS (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, \
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, partial, T, H, zero_centered
+  const int nv = (H / 8 + NORM_THREADS - 1) / NORM_THREADS;
+  if (nv <= 2) rmsnorm_bwd_kernel<2><<<rows, NORM_THREADS, 0, st>>>(XB_ARGS);
+  else rmsnorm_bwd_kernel<4><<<rows, NORM_THREADS, 0, st>>>(XB_ARGS);
+#undef XB_ARGS
+  // every one of the `rows` partial rows was just written by the kernel above
+  reduce_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>(partial, rows, H,
+                                                          (__nv_bfloat16*)dw_bf16, dw_f32,
+                                                          accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
