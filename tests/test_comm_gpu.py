@@ -1,0 +1,109 @@
+"""Peer-memory collectives (csrc/comm.cu).
+
+Single GPU: the bounded flag wait gives up after its limit and reports through the status words
+(nothing sets the flag, the context stays usable).  Two or more GPUs: the ZeRO engine with the fused
+peer-memory transport reproduces the NCCL transport's losses."""
+import ctypes
+import json
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def test_flag_wait_times_out_and_reports():
+    from xorl_b200.ops import _lib
+    lib = _lib.cuda_lib()
+    _lib.read_status(clear=True)
+    flags = torch.zeros(32, device="cuda", dtype=torch.int32)
+    rc = lib.xb_symm_wait(flags.data_ptr(), 4, 0, 1, 50, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    st = _lib.read_status(clear=True)
+    assert st[0] == 2, st          # XB_ERR_FLAG_TIMEOUT
+    # a satisfied wait returns immediately and leaves the status clean
+    flags.fill_(5)
+    lib.xb_symm_wait(flags.data_ptr(), 4, 0, 5, 50, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert _lib.read_status(clear=True)[0] == 0
+    x = torch.ones(8, device="cuda")
+    assert float(x.sum()) == 8.0
+
+
+def test_peer_copy_local():
+    from xorl_b200.ops import _lib
+    lib = _lib.cuda_lib()
+    src = torch.randn(1 << 20, device="cuda")
+    dst = torch.empty_like(src)
+    assert lib.xb_peer_copy(dst.data_ptr(), src.data_ptr(), src.numel() * 4, 0,
+                            torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(src, dst)
+
+
+def _worker():
+    import torch.distributed as dist
+    from xorl_b200.models import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.ops import _lib
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.state import init_parallel_state
+    from xorl_b200.parallel.symm import try_attach_symmetric_transport
+    from xorl_b200.parallel.zero import Zero3Engine
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    ps = init_parallel_state(device_type="cuda", dp_mode="fsdp2")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = preset("qwen3-8b", num_hidden_layers=3, hidden_size=1024, intermediate_size=3072,
+                 num_attention_heads=8, num_key_value_heads=2, vocab_size=32000)
+    curves = {}
+    for mode in ("nccl", "fused"):
+        model = DecoderLM(cfg, device="meta")
+        eng = Zero3Engine(model, ps, compute_dtype=torch.bfloat16, device=dev, seed=0)
+        if mode == "fused":
+            assert try_attach_symmetric_transport(eng, required=True)
+        opt = build_optimizer(eng, lr=1e-3, weight_decay=0.0)
+        T = 1024
+        losses = []
+        for step in range(4):
+            g = torch.Generator().manual_seed(100 * step + rank)
+            ids = torch.randint(0, cfg.vocab_size, (T + 1,), generator=g).to(dev)
+            cu = torch.tensor([0, 384, T], device=dev, dtype=torch.int32)
+            opt.zero_grad()
+            loss = eng.forward_backward(ids[:-1], ids[1:], cu_seqlens=cu, grad_scale=1.0 / (T * world))
+            eng.finish_grad_sync()
+            norm, coef = eng.grad_norm_and_clip_coef(1.0)
+            opt.step(clip_coef=coef)
+            dist.all_reduce(loss)
+            losses.append(float(loss))
+        torch.cuda.synchronize()
+        _lib.raise_on_status()
+        curves[mode] = losses
+        del eng, opt, model
+    if rank == 0:
+        print("CURVES " + json.dumps(curves))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.distributed
+def test_fused_transport_matches_nccl():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from dist_utils import run_distributed
+    n = min(torch.cuda.device_count(), 8)
+    out = run_distributed(__file__, n, env={"NCCL_NVLS_ENABLE": "0"})
+    curves = json.loads([l for l in out.splitlines() if l.startswith("CURVES ")][-1][7:])
+    for a, b in zip(curves["nccl"], curves["fused"]):
+        assert abs(a - b) < 2e-2 * abs(a), curves
+    assert curves["fused"][-1] < curves["fused"][0]
+
+
+if __name__ == "__main__":
+    _worker()

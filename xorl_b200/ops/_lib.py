@@ -51,6 +51,13 @@ _SIGNATURES = {
     "xb_signsgd": [P, P, P, L, F, F, P],
     "xb_stochastic_round": [P, P, L, c_uint, P],
     "xb_cast_accum": [P, P, L, F, I, P],
+    "xb_symm_barrier": [P, I, I, I, I, I, P],
+    "xb_symm_wait": [P, I, I, I, I, P],
+    "xb_symm_allgather": [P, P, L, I, I, I, P],
+    "xb_symm_reduce_scatter": [P, P, ctypes.c_ulonglong, L, L, I, F, P, P, I, I, I, I, I, I, I, I, P],
+    "xb_peer_copy": [P, P, L, I, P],
+    "xb_grouped_gemm_rows": [P, P, P, P, I, L, I, I, L, L, I, P],
+    "xb_grouped_gemm_wgrad": [P, P, P, P, I, L, I, I, L, L, I, I, P],
     "xb_attn_fwd": [P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, F, I, P],
     "xb_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, I, I, I, I, I, I, F, I, P],
 }

@@ -315,6 +315,9 @@ class Zero3Engine:
                 # single owner: kernels write (or accumulate) straight into the fp32 accumulator
                 g.grad_full = g.grad_shard
                 g.attach_grad_views(fresh=not g.grad_ready)
+            elif self.symm is not None and self.symm.can_reduce(g):
+                g.grad_full = self.symm.take_grad_buffer(g)
+                g.attach_grad_views()
             else:
                 g.grad_full = self._take_full(g.padded, self.compute_dtype)
                 g.attach_grad_views()
@@ -366,6 +369,9 @@ class Zero3Engine:
                     dist.all_reduce(g.grad_shard, group=self.sp_sync_pg)
 
     def zero_grad(self) -> None:
+        if self.symm is not None:
+            # parameter shards were rewritten by the optimizer: no peer may read them earlier
+            self.symm.step_barrier(torch.cuda.current_stream())
         for unit in self.units:
             for g in unit.groups:
                 g.grad_ready = False
