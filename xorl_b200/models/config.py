@@ -162,6 +162,11 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     "tiny-qwen3": dict(model_type="qwen3", vocab_size=1024, hidden_size=256, intermediate_size=768,
                        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                        rope_theta=1e6, tie_word_embeddings=True, max_position_embeddings=4096),
+    "tiny-qwen3-moe": dict(model_type="qwen3_moe", vocab_size=1024, hidden_size=128, intermediate_size=256,
+                           num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                           rope_theta=1e6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                           norm_topk_prob=True, router_aux_loss_coef=1e-3, tie_word_embeddings=False,
+                           max_position_embeddings=4096),
     "qwen3-8b": dict(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
                      num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                      rope_theta=1e6, tie_word_embeddings=False),

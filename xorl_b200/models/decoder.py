@@ -79,6 +79,8 @@ class DecoderLM(nn.Module):
                                       cfg.partial_rotary_factor, cfg.max_position_embeddings)
         self.loss_chunk_tokens = 1024
         self.cp_strategy = None
+        self.ctx_defaults = {}          # copied into every StepContext.aux (ep_dispatch, ...)
+        self.aux_loss_enabled = False   # MoE load-balancing loss (set by the trainer)
 
     # ---- initialisation ---------------------------------------------------------------------
     @torch.no_grad()
@@ -110,6 +112,7 @@ class DecoderLM(nn.Module):
         cu_seqlens = cu_seqlens.to(device=dev, dtype=torch.int32)
         ctx = StepContext(cu_seqlens=cu_seqlens, position_ids=position_ids, causal=causal,
                           training=training, cp=self.cp_strategy)
+        ctx.aux.update(self.ctx_defaults)
         if ctx.cp is not None:
             ctx.cp.prepare(self, ctx)
         else:

@@ -139,7 +139,7 @@ class _GroupedLinear(torch.autograd.Function):
     def forward(ctx, x, w, seg):
         ctx.save_for_backward(x, seg)
         ctx.w = w
-        out = torch.empty((x.shape[0], w.shape[2]), device=x.device, dtype=x.dtype)
+        out = torch.zeros((x.shape[0], w.shape[2]), device=x.device, dtype=x.dtype)
         return _grouped_rows_cuda(x, w, seg, out, b_kmajor=False)
 
     @staticmethod
@@ -149,7 +149,7 @@ class _GroupedLinear(torch.autograd.Function):
         dy = dy.contiguous()
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = torch.empty_like(x)
+            dx = torch.zeros_like(x)
             _grouped_rows_cuda(dy, w, seg, dx, b_kmajor=True)   # dx = dy @ w[e]^T
         dw = None
         if ctx.needs_input_grad[1]:

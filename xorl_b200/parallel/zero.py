@@ -395,7 +395,13 @@ class Zero3Engine:
         self.gather(root)
         self.wait_gather(root)
         ctx = model.make_context(input_ids, position_ids, cu_seqlens, training=True)
+        if getattr(model, "aux_loss_enabled", False):
+            # per-layer auxiliary losses are weighted like a token mean over the global batch
+            ctx.aux["aux_loss_scale"] = float(ctx.num_tokens) * grad_scale
         recompute = self.recompute
+        # record expert choices in the first pass and replay them when a layer is recomputed, so
+        # both passes dispatch identically (src/xorl/models/layers/moe/routing_replay.py)
+        ctx.aux["record_routing"] = recompute
         saved_inputs: List[Tuple] = []
         saved_graph: List[Tuple] = []
         with torch.no_grad():
@@ -445,13 +451,18 @@ class Zero3Engine:
                 ins = tuple(a.detach().requires_grad_() if a is not None else None
                             for a in saved_inputs[i])
                 saved_inputs[i] = None
+                ctx.aux["record_routing"] = False
+                rec = ctx.aux.pop(("routing_record", getattr(layer, "layer_idx", i)), None)
+                if rec is not None:
+                    ctx.aux[("routing_replay", getattr(layer, "layer_idx", i))] = rec
                 with torch.enable_grad():
                     outs = layer(*ins, ctx)
             else:
                 ins, outs = saved_graph[i]
                 saved_graph[i] = None
             pairs = [(o, d) for o, d in zip(outs, dacts) if o is not None and d is not None]
-            aux = ctx.aux.pop(("aux_loss", i), None)
+            aux = ctx.aux.pop(("aux_loss", getattr(layer, "layer_idx", i)), None)
+            ctx.aux.pop(("routing_replay", getattr(layer, "layer_idx", i)), None)
             tensors = [o for o, _ in pairs]
             grads = [d for _, d in pairs]
             if aux is not None:

@@ -91,6 +91,17 @@ class Trainer:
         if t.ce_num_chunks and t.ce_num_chunks > 0:
             self.model.loss_chunk_tokens = max(256, -(-int(a.data.sample_packing_sequence_len or 4096)
                                                       * t.micro_batch_size // t.ce_num_chunks))
+        if self.model_config.is_moe:
+            self.model.ctx_defaults["ep_dispatch"] = a.model.ep_dispatch
+            if t.softmax_auxiliary_loss or self.model_config.router_aux_loss_coef > 0:
+                coef = t.auxiliary_loss_multiplier if t.softmax_auxiliary_loss \
+                    else self.model_config.router_aux_loss_coef
+                for m in self.model.modules():
+                    if hasattr(m, "aux_coef"):
+                        m.aux_coef = coef
+                self.model.aux_loss_enabled = coef > 0
+                if t.moe_global_load_balancing:
+                    self.model.ctx_defaults["aux_global_group"] = self.ps.group("dp")
         from ..parallel.cp import attach_cp_strategy
         attach_cp_strategy(self.model, self.ps)
         recompute = t.enable_gradient_checkpointing and t.gradient_checkpointing_method != "no_recompute"
