@@ -65,16 +65,25 @@ class DecoderLayer(nn.Module):
 class DecoderLM(nn.Module):
     """Causal language model over packed sequences."""
 
-    def __init__(self, cfg: ModelConfig, dtype=None, device=None):
+    def __init__(self, cfg: ModelConfig, dtype=None, device=None, layer_indices=None,
+                 has_embed: bool = True, has_head: bool = True):
+        """``layer_indices`` / ``has_embed`` / ``has_head`` build only a pipeline stage's part of
+        the model; layers keep their global index in their name (``layers.{i}``)."""
         super().__init__()
         self.config = cfg
-        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
-        self.layers = nn.ModuleList(DecoderLayer(cfg, i, dtype, device)
-                                    for i in range(cfg.num_hidden_layers))
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.zero_centered_norm, dtype, device)
-        self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, bias=False, dtype=dtype, device=device)
-        if cfg.tie_word_embeddings:
+        self.has_embed, self.has_head = has_embed, has_head
+        idx = list(range(cfg.num_hidden_layers)) if layer_indices is None else list(layer_indices)
+        self.layer_indices = idx
+        if has_embed:
+            self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
+        self.layers = nn.ModuleDict({str(i): DecoderLayer(cfg, i, dtype, device) for i in idx})
+        if has_head:
+            self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.zero_centered_norm, dtype, device)
+            self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, bias=False, dtype=dtype, device=device)
+        if cfg.tie_word_embeddings and has_embed and has_head:
             self.lm_head.weight = self.embed_tokens.weight
+        elif cfg.tie_word_embeddings and (has_embed != has_head):
+            raise ValueError("tied embeddings cannot be split across pipeline stages")
         self.rotary = RotaryEmbedding(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling,
                                       cfg.partial_rotary_factor, cfg.max_position_embeddings)
         self.loss_chunk_tokens = 1024
@@ -138,15 +147,20 @@ class DecoderLM(nn.Module):
     def unit_modules(self):
         """(name, modules) per ZeRO unit, in execution order.  The root unit (embedding, final
         norm, lm_head) stays gathered for the whole step."""
-        root = [self.embed_tokens, self.norm, self.lm_head]
-        return [("root", root)] + [(f"layers.{i}", [l]) for i, l in enumerate(self.layers)]
+        root = []
+        if self.has_embed:
+            root.append(self.embed_tokens)
+        if self.has_head:
+            root += [self.norm, self.lm_head]
+        units = [("root", root)] if root else []
+        return units + [(f"layers.{i}", [l]) for i, l in self.layers.items()]
 
     # ---- plain autograd forward --------------------------------------------------------------
     def forward(self, input_ids, labels=None, position_ids=None, cu_seqlens=None,
                 grad_scale: float = 1.0, return_hidden: bool = False) -> Dict[str, Any]:
         ctx = self.make_context(input_ids, position_ids, cu_seqlens, training=self.training)
         h, res = self.forward_embed(input_ids, ctx)
-        for layer in self.layers:
+        for layer in self.layers.values():
             h, res = layer(h, res, ctx)
         out: Dict[str, Any] = {"aux": ctx.aux}
         if labels is not None:

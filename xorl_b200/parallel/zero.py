@@ -322,9 +322,10 @@ class Zero3Engine:
                 g.grad_full = self._take_full(g.padded, self.compute_dtype)
                 g.attach_grad_views()
 
-    def _reduce_unit_grads(self, unit: ZeroUnit) -> None:
+    def _reduce_unit_grads(self, unit: ZeroUnit, collected: bool = False) -> None:
         for g in unit.groups:
-            g.collect_grads()
+            if not collected:
+                g.collect_grads()
             accumulate = g.grad_ready
             gf = g.grad_full
             if g.world == 1:
@@ -380,32 +381,27 @@ class Zero3Engine:
     # forward / backward over one micro-batch
     # ---------------------------------------------------------------------------------------
     def _units_by_role(self):
-        root = self.units[0]
-        layers = self.units[1:]
+        root = next((u for u in self.units if u.name == "root"), None)
+        layers = [u for u in self.units if u.name != "root"]
         return root, layers
 
-    def forward_backward(self, input_ids: torch.Tensor, labels: torch.Tensor, *,
-                         position_ids=None, cu_seqlens=None, grad_scale: float = 1.0,
-                         extra_loss_fn: Optional[Callable] = None) -> torch.Tensor:
-        """One micro-batch.  Returns ``grad_scale * sum(token CE)`` (detached).  Gradients are
-        accumulated into the fp32 shards; call ``finish_grad_sync`` after the last micro-batch."""
+    # ---- primitives shared by the plain step and the pipeline runner ----------------------------
+    def make_step_context(self, input_ids, position_ids=None, cu_seqlens=None, grad_scale: float = 1.0):
         model = self.model
-        root, layers = self._units_by_role()
-        nl = len(layers)
-        self.gather(root)
-        self.wait_gather(root)
         ctx = model.make_context(input_ids, position_ids, cu_seqlens, training=True)
         if getattr(model, "aux_loss_enabled", False):
             # per-layer auxiliary losses are weighted like a token mean over the global batch
             ctx.aux["aux_loss_scale"] = float(ctx.num_tokens) * grad_scale
-        recompute = self.recompute
         # record expert choices in the first pass and replay them when a layer is recomputed, so
         # both passes dispatch identically (src/xorl/models/layers/moe/routing_replay.py)
-        ctx.aux["record_routing"] = recompute
-        saved_inputs: List[Tuple] = []
-        saved_graph: List[Tuple] = []
-        with torch.no_grad():
-            acts = model.forward_embed(input_ids, ctx)
+        ctx.aux["record_routing"] = self.recompute
+        return ctx
+
+    def chunk_forward(self, layers: List[ZeroUnit], acts, ctx, keep_last_gathered: bool = False):
+        """Forward through consecutive layer units.  Returns (acts_out, saved) where ``saved`` is
+        what ``chunk_backward`` needs (unit inputs when recomputing, autograd graphs otherwise)."""
+        nl = len(layers)
+        saved: List = []
         if nl:
             self.gather(layers[0])
         for i, unit in enumerate(layers):
@@ -413,32 +409,25 @@ class Zero3Engine:
             if i + 1 < nl:
                 self.gather(layers[i + 1])
             layer = unit.modules[0]
-            if recompute:
-                saved_inputs.append(acts)
+            if self.recompute:
+                saved.append(acts)
                 with torch.no_grad():
                     acts = layer(*acts, ctx)
             else:
                 ins = tuple(a.detach().requires_grad_() if a is not None else None for a in acts)
                 with torch.enable_grad():
                     outs = layer(*ins, ctx)
-                saved_graph.append((ins, outs))
+                saved.append((ins, outs))
                 acts = tuple(o.detach() if o is not None else None for o in outs)
-            if self.reshard and recompute and i < nl - 1:
+            if self.reshard and self.recompute and not (keep_last_gathered and i == nl - 1):
                 self.release(unit)
-        # ---- head: forward + backward at once ------------------------------------------------
-        self._prepare_grad_buffers(root)
-        head_in = tuple(a.detach().requires_grad_() if a is not None else None for a in acts)
-        with torch.enable_grad():
-            loss = model.head_loss(*head_in, labels, ctx, grad_scale)
-            total = loss
-            if extra_loss_fn is not None:
-                extra = extra_loss_fn(ctx)
-                if extra is not None:
-                    total = total + extra
-            total.backward()
-        dacts = tuple(a.grad if a is not None else None for a in head_in)
-        loss_value = loss.detach()
-        # ---- layers, last to first ------------------------------------------------------------
+        return acts, saved
+
+    def chunk_backward(self, layers: List[ZeroUnit], saved: List, dacts, ctx, defer_reduce: bool = False):
+        """Backward through the same units, last to first.  Returns (dacts_in, pending) where
+        ``pending`` lists the units whose gradient reduction was deferred (``defer_reduce``)."""
+        nl = len(layers)
+        pending: List = []
         for i in range(nl - 1, -1, -1):
             unit = layers[i]
             self.gather(unit)
@@ -447,22 +436,22 @@ class Zero3Engine:
                 self.gather(layers[i - 1])
             self._prepare_grad_buffers(unit)
             layer = unit.modules[0]
-            if recompute:
-                ins = tuple(a.detach().requires_grad_() if a is not None else None
-                            for a in saved_inputs[i])
-                saved_inputs[i] = None
+            lidx = getattr(layer, "layer_idx", i)
+            if self.recompute:
+                ins = tuple(a.detach().requires_grad_() if a is not None else None for a in saved[i])
+                saved[i] = None
                 ctx.aux["record_routing"] = False
-                rec = ctx.aux.pop(("routing_record", getattr(layer, "layer_idx", i)), None)
+                rec = ctx.aux.pop(("routing_record", lidx), None)
                 if rec is not None:
-                    ctx.aux[("routing_replay", getattr(layer, "layer_idx", i))] = rec
+                    ctx.aux[("routing_replay", lidx)] = rec
                 with torch.enable_grad():
                     outs = layer(*ins, ctx)
             else:
-                ins, outs = saved_graph[i]
-                saved_graph[i] = None
+                ins, outs = saved[i]
+                saved[i] = None
             pairs = [(o, d) for o, d in zip(outs, dacts) if o is not None and d is not None]
-            aux = ctx.aux.pop(("aux_loss", getattr(layer, "layer_idx", i)), None)
-            ctx.aux.pop(("routing_replay", getattr(layer, "layer_idx", i)), None)
+            aux = ctx.aux.pop(("aux_loss", lidx), None)
+            ctx.aux.pop(("routing_replay", lidx), None)
             tensors = [o for o, _ in pairs]
             grads = [d for _, d in pairs]
             if aux is not None:
@@ -471,15 +460,71 @@ class Zero3Engine:
             torch.autograd.backward(tensors, grads)
             dacts = tuple(a.grad if a is not None else None for a in ins)
             del ins, outs, pairs, tensors, grads
-            self._reduce_unit_grads(unit)
+            if defer_reduce:
+                pending.append(self._detach_grad_buffers(unit))
+            else:
+                self._reduce_unit_grads(unit)
             if self.reshard:
                 self.release(unit)
-        # ---- embedding backward ----------------------------------------------------------------
+        return dacts, pending
+
+    def _detach_grad_buffers(self, unit: ZeroUnit):
+        """Fold straggler gradients now, but keep the unit's gradient buffers alive for weight
+        gradients that will be produced later (zero-bubble schedules)."""
+        rec = []
+        for g in unit.groups:
+            g.collect_grads()
+            rec.append((g, g.grad_full))
+            g.grad_full = None
+        return unit, rec
+
+    def reduce_deferred(self, pending: List) -> None:
+        for unit, rec in pending:
+            for g, gf in rec:
+                g.grad_full = gf
+                # collect_grads already ran; _reduce_unit_grads calls it again on cleared attrs
+                for _, p in g.named_params:
+                    p._xb_grad_buf = None
+                    p._xb_grad_fresh = False
+            self._reduce_unit_grads(unit, collected=True)
+
+    def head_forward_backward(self, acts, labels, ctx, grad_scale, extra_loss_fn=None):
+        """Final norm + lm-head loss, forward and backward at once.  Returns (loss, dacts)."""
+        head_in = tuple(a.detach().requires_grad_() if a is not None else None for a in acts)
         with torch.enable_grad():
-            emb = model.forward_embed(input_ids, ctx)
+            loss = self.model.head_loss(*head_in, labels, ctx, grad_scale)
+            total = loss
+            if extra_loss_fn is not None:
+                extra = extra_loss_fn(ctx)
+                if extra is not None:
+                    total = total + extra
+            total.backward()
+        return loss.detach(), tuple(a.grad if a is not None else None for a in head_in)
+
+    def embed_backward(self, input_ids, ctx, dacts) -> None:
+        with torch.enable_grad():
+            emb = self.model.forward_embed(input_ids, ctx)
         pairs = [(o, d) for o, d in zip(emb, dacts) if o is not None and d is not None]
         if pairs and pairs[0][0].requires_grad:
             torch.autograd.backward([o for o, _ in pairs], [d for _, d in pairs])
+
+    def forward_backward(self, input_ids: torch.Tensor, labels: torch.Tensor, *,
+                         position_ids=None, cu_seqlens=None, grad_scale: float = 1.0,
+                         extra_loss_fn: Optional[Callable] = None) -> torch.Tensor:
+        """One micro-batch.  Returns ``grad_scale * sum(token CE)`` (detached).  Gradients are
+        accumulated into the fp32 shards; call ``finish_grad_sync`` after the last micro-batch."""
+        model = self.model
+        root, layers = self._units_by_role()
+        self.gather(root)
+        self.wait_gather(root)
+        ctx = self.make_step_context(input_ids, position_ids, cu_seqlens, grad_scale)
+        with torch.no_grad():
+            acts = model.forward_embed(input_ids, ctx)
+        acts, saved = self.chunk_forward(layers, acts, ctx, keep_last_gathered=True)
+        self._prepare_grad_buffers(root)
+        loss_value, dacts = self.head_forward_backward(acts, labels, ctx, grad_scale, extra_loss_fn)
+        dacts, _ = self.chunk_backward(layers, saved, dacts, ctx)
+        self.embed_backward(input_ids, ctx, dacts)
         self._reduce_unit_grads(root)
         if self.reshard:
             self.release(root)
@@ -503,6 +548,8 @@ class Zero3Engine:
             if self.reshard:
                 self.release(unit)
         hidden = model.forward_head(*acts, ctx)
+        if self.reshard:
+            self.release(root)
         return hidden
 
     # ---------------------------------------------------------------------------------------
