@@ -30,11 +30,11 @@ def build_model_config(model_args) -> ModelConfig:
     return cfg
 
 
-def build_model(cfg: ModelConfig, args: Any = None, device="meta", dtype=None):
+def build_model(cfg: ModelConfig, args: Any = None, device="meta", dtype=None, **stage_kw):
     """Instantiates the family's model class (parameters on ``device``; ``meta`` by default, the
     ZeRO engine materialises them shard by shard)."""
     cls = get_model_class(cfg)
-    model = cls(cfg, dtype=dtype, device=device)
+    model = cls(cfg, dtype=dtype, device=device, **stage_kw)
     if args is not None:
         from ..adapters import apply_adapters
         apply_adapters(model, cfg, args)

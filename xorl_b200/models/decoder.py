@@ -189,6 +189,10 @@ def init_parameter_(name: str, p: torch.Tensor, std: float, seed: int, index: in
         else:
             p.fill_(1.0)
         return
+    import zlib
+    # seeded by the parameter *name*, so a pipeline stage that builds only some layers draws the
+    # same values for them as a process that builds the whole model
+    index = zlib.crc32(name.encode())
     g = torch.Generator(device="cpu").manual_seed((seed * 1000003 + index * 7919 + 17) % (2 ** 63 - 1))
     if p.numel() <= (1 << 24) or p.device.type == "cpu":
         vals = torch.empty(p.shape, dtype=torch.float32).normal_(0.0, std, generator=g)

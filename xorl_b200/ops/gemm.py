@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .grad_sink import grad_target, mark_written
+from .grad_sink import current_wgrad_store, grad_target, mark_written
 
 _launches = 0
 
@@ -96,7 +96,13 @@ class _Linear(torch.autograd.Function):
             dx = gemm(dy2, w, b_mn=True).reshape(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             tgt, fresh = grad_target(w)
-            if tgt is not None:
+            store = current_wgrad_store()
+            if tgt is not None and store is not None:
+                # zero-bubble: the buffer slice is claimed now, the GEMM runs in a later W slot
+                mark_written(w)
+                store.append(lambda a=dy2, b=x2, o=tgt, acc=not fresh:
+                             gemm(a, b, a_mn=True, b_mn=True, out=o, accumulate=acc))
+            elif tgt is not None:
                 # write straight into the flat gradient buffer of the ZeRO unit
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=tgt, accumulate=not fresh)
                 mark_written(w)

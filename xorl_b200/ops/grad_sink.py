@@ -37,3 +37,27 @@ def deliver_param_grad(p: torch.Tensor, g: torch.Tensor):
     else:
         buf.add_(g.to(buf.dtype))
     return None
+
+
+# ---- deferred weight gradients (zero-bubble pipeline schedules) --------------------------------
+_wgrad_store = None
+
+
+class defer_wgrad:
+    """While active, linear layers do not run their weight-gradient GEMM in backward but append a
+    closure that does to the returned list; the pipeline runner calls them in a later ``W`` slot."""
+
+    def __enter__(self):
+        global _wgrad_store
+        self.prev = _wgrad_store
+        _wgrad_store = []
+        return _wgrad_store
+
+    def __exit__(self, *exc):
+        global _wgrad_store
+        _wgrad_store = self.prev
+        return False
+
+
+def current_wgrad_store():
+    return _wgrad_store

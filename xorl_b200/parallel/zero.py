@@ -476,6 +476,9 @@ class Zero3Engine:
             g.collect_grads()
             rec.append((g, g.grad_full))
             g.grad_full = None
+            if g.world == 1:
+                # gradients are produced in place in the accumulator: later micro-batches must add
+                g.grad_ready = True
         return unit, rec
 
     def reduce_deferred(self, pending: List) -> None:

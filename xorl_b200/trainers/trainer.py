@@ -87,7 +87,21 @@ class Trainer:
     def _build_model(self, model_config=None) -> None:
         a, t = self.args, self.args.train
         self.model_config = model_config or build_model_config(a.model)
-        self.model = build_model(self.model_config, a, device="meta")
+        stage_kw = {}
+        self.pp_layout = None
+        if self.ps.pp_size > 1:
+            from ..parallel.pp import local_stage_layout
+            if self.model_config.tie_word_embeddings:
+                raise ValueError("pipeline parallelism does not support tied embeddings")
+            self.pp_layout = local_stage_layout(
+                self.model_config.num_hidden_layers, self.ps, t.pipeline_parallel_schedule,
+                t.pipeline_parallel_virtual_stages, input_weight=t.pipeline_parallel_input_weight,
+                output_weight=t.pipeline_parallel_output_weight,
+                first=t.pipeline_parallel_num_layers_in_first_stage,
+                last=t.pipeline_parallel_num_layers_in_last_stage)
+            stage_kw = dict(layer_indices=self.pp_layout["layers"],
+                            has_embed=self.pp_layout["has_embed"], has_head=self.pp_layout["has_head"])
+        self.model = build_model(self.model_config, a, device="meta", **stage_kw)
         if t.ce_num_chunks and t.ce_num_chunks > 0:
             self.model.loss_chunk_tokens = max(256, -(-int(a.data.sample_packing_sequence_len or 4096)
                                                       * t.micro_batch_size // t.ce_num_chunks))
@@ -113,6 +127,12 @@ class Trainer:
         if t.comm_backend in ("auto", "fused") and self.device.type == "cuda" and self.ps.world_size > 1:
             from ..parallel.symm import try_attach_symmetric_transport
             try_attach_symmetric_transport(self.engine, required=(t.comm_backend == "fused"))
+        self.pp_runner = None
+        if self.pp_layout is not None:
+            from ..parallel.pp import PipelineRunner
+            self.pp_runner = PipelineRunner(self.engine, self.ps, t.pipeline_parallel_schedule,
+                                            t.pipeline_parallel_virtual_stages, self.pp_layout,
+                                            t.gradient_accumulation_steps)
         weights = a.model.model_path
         if weights and t.load_weights_mode != "skip" and os.path.isdir(weights) and any(
                 f.endswith(".safetensors") for f in os.listdir(weights)):
@@ -203,6 +223,12 @@ class Trainer:
         global_tokens = max(1, self.count_valid_tokens(micro_batches))
         self.optimizer.zero_grad()
         total = None
+        if self.pp_runner is not None:
+            for mb in micro_batches:
+                self.meter.add(mb)
+            total = self.pp_runner.run([self._to_device(mb) for mb in micro_batches],
+                                       1.0 / global_tokens)
+            micro_batches = []
         for mb in micro_batches:
             self.meter.add(mb)
             d = self._to_device(mb)
