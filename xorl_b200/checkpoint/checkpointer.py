@@ -153,7 +153,7 @@ class DistributedCheckpointer:
             for (name, _), shape in zip(g.named_params, g.shapes):
                 key = f"model.{to_checkpoint_fqn(name)}"
                 if key in sd:
-                    tensors[name] = full_of(sd[key]).reshape(shape)
+                    tensors[name] = full_of(sd[key])
             if tensors:
                 eng.load_full_tensors(tensors, strict=False)
         if load_optimizer and self.optimizer is not None:
@@ -163,7 +163,7 @@ class DistributedCheckpointer:
                     for (name, _), shape in zip(g.named_params, g.shapes):
                         key = f"optimizer.state.{to_checkpoint_fqn(name)}.{sname}"
                         if key in sd:
-                            tensors[name] = full_of(sd[key]).reshape(shape)
+                            tensors[name] = full_of(sd[key])
                     if tensors:
                         eng.load_full_tensors(tensors, strict=False, target="extra", extra=per_group)
         extra_path = os.path.join(path, "extra_state", f"extra_state_rank_{eng.ps.rank}.pt")

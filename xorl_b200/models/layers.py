@@ -49,6 +49,11 @@ class Linear(nn.Module):
         return gemm_ops.linear(x, self.weight, self.bias)
 
 
+def _tp():
+    from ..parallel.tp import tp_info
+    return tp_info()
+
+
 class Attention(nn.Module):
     """Fused qkv projection -> (per-head qk RMSNorm) -> RoPE -> varlen causal attention -> o_proj.
     A context-parallel strategy on ``ctx.cp`` takes over the middle part when present."""
@@ -59,19 +64,39 @@ class Attention(nn.Module):
         self.layer_idx = layer_idx
         self.Hq, self.Hkv, self.D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         H = cfg.hidden_size
+        self.tp, self.tp_rank, self.tp_group = _tp()
+        if self.tp > 1:
+            if self.Hq % self.tp or self.Hkv % self.tp:
+                raise ValueError(f"heads ({self.Hq}, {self.Hkv}) not divisible by tensor_parallel_size {self.tp}")
+            fq, fkv = self.Hq * self.D, self.Hkv * self.D
+            self.Hq //= self.tp
+            self.Hkv //= self.tp
         self.qkv_proj = Linear(H, (self.Hq + 2 * self.Hkv) * self.D, bias=cfg.attention_bias,
                                dtype=dtype, device=device)
         self.o_proj = Linear(self.Hq * self.D, H, bias=False, dtype=dtype, device=device)
+        if self.tp > 1:
+            from ..parallel.tp import mark_col, mark_row
+            mark_col(self.qkv_proj.weight, (fq + 2 * fkv, H), (fq, fkv, fkv))
+            if self.qkv_proj.bias is not None:
+                mark_col(self.qkv_proj.bias, (fq + 2 * fkv,), (fq, fkv, fkv))
+            mark_row(self.o_proj.weight, (H, fq))
         self.use_qk_norm = cfg.use_qk_norm
         if cfg.use_qk_norm:
             nd = self.D if not cfg.qk_norm_full else None
             self.q_norm = RMSNorm(nd or self.Hq * self.D, cfg.rms_norm_eps, dtype=dtype, device=device)
             self.k_norm = RMSNorm(nd or self.Hkv * self.D, cfg.rms_norm_eps, dtype=dtype, device=device)
+            if self.tp > 1 and not cfg.qk_norm_full:
+                # every TP rank sees only its own heads: gradients are summed over the TP group
+                self.q_norm.weight._xb_tp_reduce = True
+                self.k_norm.weight._xb_tp_reduce = True
         self.scale = 1.0 / math.sqrt(self.D)
         self.window = cfg.sliding_window if (cfg.layer_types is None or
                                             cfg.layer_types[layer_idx] == "sliding_attention") else None
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        if self.tp > 1:
+            from ..parallel.tp import copy_to_tp
+            x = copy_to_tp(x, self.tp_group)
         qkv = self.qkv_proj(x)
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         if ctx.cp is not None:
@@ -84,7 +109,11 @@ class Attention(nn.Module):
             out = attn_ops.qk_norm_rope_attention(qkv, wq, wk, ctx.cos, ctx.sin, ctx.cu_seqlens,
                                                   Hq, Hkv, D, self.cfg.rms_norm_eps, ctx.causal,
                                                   self.scale)
-        return self.o_proj(out)
+        out = self.o_proj(out)
+        if self.tp > 1:
+            from ..parallel.tp import reduce_from_tp
+            out = reduce_from_tp(out, self.tp_group)
+        return out
 
     def _unfused_attention(self, qkv, ctx):
         """General path (whole-projection qk-norm, partial rotary): separate ops."""
@@ -107,10 +136,25 @@ class Attention(nn.Module):
 class MLP(nn.Module):
     """SwiGLU feed-forward with a fused gate_up projection ``[2I, H]`` (gate rows first)."""
 
-    def __init__(self, hidden: int, intermediate: int, bias: bool = False, dtype=None, device=None):
+    def __init__(self, hidden: int, intermediate: int, bias: bool = False, dtype=None, device=None,
+                 tensor_parallel: bool = True):
         super().__init__()
+        self.tp, self.tp_rank, self.tp_group = _tp() if tensor_parallel else (1, 0, None)
+        full_I = intermediate
+        if self.tp > 1:
+            if intermediate % self.tp:
+                raise ValueError(f"intermediate size {intermediate} not divisible by tp {self.tp}")
+            intermediate //= self.tp
         self.gate_up_proj = Linear(hidden, 2 * intermediate, bias=bias, dtype=dtype, device=device)
         self.down_proj = Linear(intermediate, hidden, bias=bias, dtype=dtype, device=device)
+        if self.tp > 1:
+            from ..parallel.tp import mark_col, mark_row
+            mark_col(self.gate_up_proj.weight, (2 * full_I, hidden), (full_I, full_I))
+            mark_row(self.down_proj.weight, (hidden, full_I))
 
     def forward(self, x):
+        if self.tp > 1:
+            from ..parallel.tp import copy_to_tp, reduce_from_tp
+            x = copy_to_tp(x, self.tp_group)
+            return reduce_from_tp(self.down_proj(act_ops.swiglu(self.gate_up_proj(x))), self.tp_group)
         return self.down_proj(act_ops.swiglu(self.gate_up_proj(x)))

@@ -181,7 +181,8 @@ class Zero3Engine:
                                         requires_grad=p.requires_grad)
                     newp._xb_shape = tuple(p.shape)
                     newp._xb_init = None if p.is_meta else p.detach()
-                    for attr in ("_xb_expert", "_xb_tp", "_xb_no_decay"):
+                    for attr in ("_xb_expert", "_xb_tp", "_xb_no_decay", "_xb_full_shape",
+                                 "_xb_tp_slice", "_xb_tp_reduce"):
                         if hasattr(p, attr):
                             setattr(newp, attr, getattr(p, attr))
                     mapping[id(p)] = newp
@@ -236,7 +237,14 @@ class Zero3Engine:
         full32 = torch.zeros(g.padded, device=self.device, dtype=torch.float32)
         for (name, p), view in zip(g.named_params, g.param_views(full32)):
             init = getattr(p, "_xb_init", None)
-            if init is None:
+            tp_slice = getattr(p, "_xb_tp_slice", None)
+            if init is None and tp_slice is not None:
+                # tensor-parallel shard: draw the full tensor, keep this rank's slice
+                full = torch.empty(p._xb_full_shape, device=self.device, dtype=torch.float32)
+                init_fn(name, full, std, seed, index_of[name], zc)
+                view.copy_(tp_slice(full))
+                del full
+            elif init is None:
                 init_fn(name, view, std, seed, index_of[name], zc)
             else:
                 view.copy_(init.to(device=self.device, dtype=torch.float32))
@@ -328,6 +336,10 @@ class Zero3Engine:
                 g.collect_grads()
             accumulate = g.grad_ready
             gf = g.grad_full
+            if self.ps.tp_size > 1 and self.ps.group("tp") is not None:
+                for (_, p), v in zip(g.named_params, g.param_views(gf)):
+                    if getattr(p, "_xb_tp_reduce", False):
+                        dist.all_reduce(v, group=self.ps.group("tp"))
             if g.world == 1:
                 pass  # gradients were produced in place in g.grad_shard
             elif self.symm is not None and self.symm.can_reduce(g):
@@ -579,6 +591,20 @@ class Zero3Engine:
             else:
                 optim_ops.sumsq_(g.grad_shard, dense_sq, not first_d)
                 first_d = False
+        tp_pg = self.ps.group("tp") if self.ps.tp_size > 1 else None
+        if tp_pg is not None:
+            # replicated parameters (norm weights, embeddings) hold identical gradients on every
+            # TP rank: count them once, sum only the tensor-parallel shards over the TP group
+            rep_sq = torch.zeros(1, device=dev, dtype=torch.float32)
+            for g in self.all_groups():
+                if not g.grad_ready:
+                    continue
+                for i, a, b in g.param_segments_in_shard():
+                    if getattr(g.named_params[i][1], "_xb_tp", None) is None:
+                        rep_sq += g.grad_shard[a:b].float().pow(2).sum()
+            sharded = dense_sq - rep_sq
+            dist.all_reduce(sharded, group=tp_pg)
+            dense_sq = sharded + rep_sq
         if self.shard_pg is not None:
             dist.all_reduce(dense_sq, group=self.shard_pg)
         if self.ps.ep_size > 1:
@@ -614,7 +640,13 @@ class Zero3Engine:
                 dist.all_gather_into_tensor(full, shard.contiguous(), group=g.pg)
             else:
                 full = shard
-            for (name, _), view in zip(g.named_params, g.param_views(full)):
+            for (name, p), view in zip(g.named_params, g.param_views(full)):
+                spec = getattr(p, "_xb_tp", None)
+                if spec is not None and self.ps.tp_size > 1:
+                    from .tp import unshard_rows
+                    parts = [torch.empty_like(view) for _ in range(self.ps.tp_size)]
+                    dist.all_gather(parts, view.contiguous(), group=self.ps.group("tp"))
+                    view = unshard_rows(parts, spec[1]) if spec[0] == "col" else torch.cat(parts, 1)
                 yield name, view
 
     @torch.no_grad()
@@ -630,7 +662,11 @@ class Zero3Engine:
                 if name not in tensors:
                     missing.append(name)
                     continue
-                src = tensors[name].reshape(-1)
+                src = tensors[name]
+                tp_slice = getattr(g.named_params[i][1], "_xb_tp_slice", None)
+                if tp_slice is not None and tuple(src.shape) == tuple(g.named_params[i][1]._xb_full_shape):
+                    src = tp_slice(src)
+                src = src.reshape(-1)
                 o = g.offsets[i]
                 dst[a:b].copy_(src[s0 + a - o: s0 + b - o].to(device=self.device, dtype=dst.dtype))
             if target == "master":
