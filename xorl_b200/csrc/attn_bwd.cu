@@ -45,6 +45,7 @@ struct Params {
   __nv_bfloat16* dv;    // [T, Hkv, D] with token stride lddv
   long long lddv;
   const int* cu_seqlens;
+  const int* k_starts;  // optional first K/V row per sequence
   int num_seqs;
   int T, Hq, Hkv;
   int causal;
@@ -82,6 +83,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   }
   if (seq < 0) return;
+  const int k_start = p.k_starts ? p.k_starts[seq] : seq_start;
+  if (k_start < 0) return;  // this query block takes no part in the call
   const int kv_head = blockIdx.y;
   const int G = p.Hq / p.Hkv;
   const int kv0 = kt * BKV;                         // position inside the sequence
@@ -129,7 +132,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------------
     if (lane == 0) {
-      const int tok = seq_start + kv0;
+      const int tok = k_start + kv0;
       mbar_expect_tx(&bars->kv_full, 2 * KV_TILE_BYTES);
       tma_load_3d(smem + SMEM_K, &tmap_k, &bars->kv_full, 0, kv_head, tok);
       tma_load_3d(smem + SMEM_K + KV_CHUNK_BYTES, &tmap_k, &bars->kv_full, 64, kv_head, tok);
@@ -391,7 +394,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int i = 0; i < 32; ++i) {
           const int kv_pos = kv0 + c * 32 + i;
           if (kv_pos < seq_len) {
-            const size_t tok = (size_t)seq_start + kv_pos;
+            const size_t tok = (size_t)k_start + kv_pos;
             p.dv[tok * p.lddv + (size_t)kv_head * D + r] = __float2bfloat16(__uint_as_float(a[i]));
             p.dk[(tok * p.Hkv + kv_head) * D + r] = __uint_as_float(b[i]);
           }
@@ -431,11 +434,32 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long ldo,
 // Inputs as in xb_attn_fwd plus out / dout [T, Hq, 128] and lse [Hq, T].
 // Scratch: delta fp32 [Hq * T]; dq_accum fp32 [T * Hq * 128] (this call zeroes it).
 // Outputs: dq_accum (fp32 dQ), dk fp32 [T, Hkv, 128], dv bf16 [T, Hkv, 128] (token stride lddv).
+XB_API int xb_attn_bwd_ex(const void* q, const void* k, const void* v, const void* out,
+                          const void* dout, const float* lse, float* delta, float* dq_accum,
+                          float* dk, void* dv, const int* cu_seqlens, const int* k_starts,
+                          long long ldq, long long ldk, long long ldv, long long ldo, long long lddo,
+                          long long lddv, int num_seqs, int T, int Tk, int Hq, int Hkv, int D,
+                          int causal, float scale, int flags, int max_tiles, void* stream);
+
 XB_API int xb_attn_bwd(const void* q, const void* k, const void* v, const void* out,
                        const void* dout, const float* lse, float* delta, float* dq_accum, float* dk,
                        void* dv, const int* cu_seqlens, long long ldq, long long ldk, long long ldv,
                        long long ldo, long long lddo, long long lddv, int num_seqs, int T, int Hq,
                        int Hkv, int D, int causal, float scale, int max_tiles, void* stream) {
+  return xb_attn_bwd_ex(q, k, v, out, dout, lse, delta, dq_accum, dk, dv, cu_seqlens, nullptr, ldq,
+                        ldk, ldv, ldo, lddo, lddv, num_seqs, T, T, Hq, Hkv, D, causal, scale, 0,
+                        max_tiles, stream);
+}
+
+// Block-pair form (see xb_attn_fwd_ex).  flags bit 0: dq_accum already holds partial sums, do not
+// clear it; bit 1: delta is already computed, do not recompute it.  dk / dv have Tk rows and
+// are written (not accumulated) for the K/V rows this call covers.
+XB_API int xb_attn_bwd_ex(const void* q, const void* k, const void* v, const void* out,
+                          const void* dout, const float* lse, float* delta, float* dq_accum,
+                          float* dk, void* dv, const int* cu_seqlens, const int* k_starts,
+                          long long ldq, long long ldk, long long ldv, long long ldo, long long lddo,
+                          long long lddv, int num_seqs, int T, int Tk, int Hq, int Hkv, int D,
+                          int causal, float scale, int flags, int max_tiles, void* stream) {
   using namespace xb_attn_bwd_ns;
   if (D != 128) return -1;
   if (T <= 0 || num_seqs <= 0) return 0;
@@ -445,23 +469,27 @@ XB_API int xb_attn_bwd(const void* q, const void* k, const void* v, const void* 
   if (xb_make_tmap_3d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, Hq, D, ldq, D, BQ, 1, 64,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
-  if (xb_make_tmap_3d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, Hkv, D, ldk, D, BKV, 1, 64,
+  if (xb_make_tmap_3d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tk, Hkv, D, ldk, D, BKV, 1, 64,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
-  if (xb_make_tmap_3d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, Hkv, D, ldv, D, BKV, 1, 64,
+  if (xb_make_tmap_3d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tk, Hkv, D, ldv, D, BKV, 1, 64,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -4;
   if (xb_make_tmap_3d(&tdo, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, Hq, D, lddo, D, BQ, 1,
                       64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -5;
-  if (cudaMemsetAsync(dq_accum, 0, (size_t)T * Hq * D * sizeof(float), st) != cudaSuccess)
-    return -6;
-  const long long rows = (long long)T * Hq;
-  attn_delta_kernel<<<(int)((rows + 7) / 8), 256, 0, st>>>(
-      (const __nv_bfloat16*)out, ldo, (const __nv_bfloat16*)dout, lddo, delta, T, Hq);
+  if (!(flags & 1)) {
+    if (cudaMemsetAsync(dq_accum, 0, (size_t)T * Hq * D * sizeof(float), st) != cudaSuccess)
+      return -6;
+  }
+  if (!(flags & 2)) {
+    const long long rows = (long long)T * Hq;
+    attn_delta_kernel<<<(int)((rows + 7) / 8), 256, 0, st>>>(
+        (const __nv_bfloat16*)out, ldo, (const __nv_bfloat16*)dout, lddo, delta, T, Hq);
+  }
   Params p;
   p.lse = lse; p.delta = delta; p.dq_accum = dq_accum; p.dk = dk;
-  p.dv = (__nv_bfloat16*)dv; p.lddv = lddv; p.cu_seqlens = cu_seqlens; p.num_seqs = num_seqs;
+  p.dv = (__nv_bfloat16*)dv; p.lddv = lddv; p.cu_seqlens = cu_seqlens; p.k_starts = k_starts; p.num_seqs = num_seqs;
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = xb_status_ptr();

@@ -36,6 +36,7 @@ struct Params {
   long long ldo;
   float* lse;  // [Hq, T]
   const int* cu_seqlens;
+  const int* k_starts;  // optional: first K/V row of every sequence (defaults to cu_seqlens)
   int num_seqs;
   int T, Hq, Hkv;
   int causal;
@@ -72,6 +73,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   }
   if (seq < 0) return;  // uniform for the whole CTA, nothing allocated yet
+  const int k_start = p.k_starts ? p.k_starts[seq] : seq_start;
+  if (k_start < 0) return;  // this query block takes no part in the call
   const int head = blockIdx.y;
   const int kv_head = head / (p.Hq / p.Hkv);
   const int q_row0 = qt * BQ;  // position inside the sequence
@@ -125,7 +128,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int tok = seq_start + j * BKV;
+        const int tok = k_start + j * BKV;
         if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, p.status, XB_K_ATTN_FWD, 100 + s)) {
           ok = false;
           break;
@@ -352,10 +355,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 // q: [T, Hq, 128] with token stride ldq;  k, v: [T, Hkv, 128] with token strides ldk, ldv;
 // out: [T, Hq, 128] token stride ldo;  lse: [Hq, T] fp32;  cu_seqlens: int32 [num_seqs + 1] on the
 // device.  All strides in elements, multiples of 8; base pointers 16-byte aligned.
+XB_API int xb_attn_fwd_ex(const void* q, const void* k, const void* v, void* out, float* lse,
+                          const int* cu_seqlens, const int* k_starts, long long ldq, long long ldk,
+                          long long ldv, long long ldo, int num_seqs, int T, int Tk, int Hq, int Hkv,
+                          int D, int causal, float scale, int max_tiles, void* stream);
+
 XB_API int xb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
                        const int* cu_seqlens, long long ldq, long long ldk, long long ldv,
                        long long ldo, int num_seqs, int T, int Hq, int Hkv, int D, int causal,
                        float scale, int max_tiles, void* stream) {
+  return xb_attn_fwd_ex(q, k, v, out, lse, cu_seqlens, nullptr, ldq, ldk, ldv, ldo, num_seqs, T, T,
+                        Hq, Hkv, D, causal, scale, max_tiles, stream);
+}
+
+// As xb_attn_fwd, but the K/V rows of sequence b start at k_starts[b] (device int32 array, may be
+// null) in K/V tensors of Tk rows.  Query and key lengths of a sequence are equal.  This is the
+// block-pair form used by ring attention: any query block against any key block.
+XB_API int xb_attn_fwd_ex(const void* q, const void* k, const void* v, void* out, float* lse,
+                          const int* cu_seqlens, const int* k_starts, long long ldq, long long ldk,
+                          long long ldv, long long ldo, int num_seqs, int T, int Tk, int Hq, int Hkv,
+                          int D, int causal, float scale, int max_tiles, void* stream) {
   using namespace xb_attn_fwd_ns;
   if (D != 128) return -1;
   if (T <= 0 || num_seqs <= 0) return 0;
@@ -364,14 +383,14 @@ XB_API int xb_attn_fwd(const void* q, const void* k, const void* v, void* out, f
   if (xb_make_tmap_3d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, Hq, D, ldq, D, BQ, 1, 64,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
-  if (xb_make_tmap_3d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, Hkv, D, ldk, D, BKV, 1, 64,
+  if (xb_make_tmap_3d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tk, Hkv, D, ldk, D, BKV, 1, 64,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
-  if (xb_make_tmap_3d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, Hkv, D, ldv, D, BKV, 1, 64,
+  if (xb_make_tmap_3d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tk, Hkv, D, ldv, D, BKV, 1, 64,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -4;
   Params p;
-  p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.lse = lse; p.cu_seqlens = cu_seqlens;
+  p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.lse = lse; p.cu_seqlens = cu_seqlens; p.k_starts = k_starts;
   p.num_seqs = num_seqs; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = xb_status_ptr();

@@ -104,7 +104,7 @@ class DecoderLM(nn.Module):
 
     # ---- unit-level API used by the engine ------------------------------------------------------
     def make_context(self, input_ids, position_ids=None, cu_seqlens=None, causal=True,
-                     training=True) -> StepContext:
+                     training=True, extra=None) -> StepContext:
         dev = input_ids.device
         if input_ids.dim() == 2 and position_ids is None and cu_seqlens is None:
             B, S = input_ids.shape
@@ -122,6 +122,8 @@ class DecoderLM(nn.Module):
         ctx = StepContext(cu_seqlens=cu_seqlens, position_ids=position_ids, causal=causal,
                           training=training, cp=self.cp_strategy)
         ctx.aux.update(self.ctx_defaults)
+        if extra:
+            ctx.aux.update({k: v for k, v in extra.items() if v is not None})
         if ctx.cp is not None:
             ctx.cp.prepare(self, ctx)
         else:

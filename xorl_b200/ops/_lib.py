@@ -58,6 +58,8 @@ _SIGNATURES = {
     "xb_peer_copy": [P, P, L, I, P],
     "xb_grouped_gemm_rows": [P, P, P, P, I, L, I, I, L, L, I, P],
     "xb_grouped_gemm_wgrad": [P, P, P, P, I, L, I, I, L, L, I, I, P],
+    "xb_attn_fwd_ex": [P, P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, I, F, I, P],
+    "xb_attn_bwd_ex": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, I, I, I, I, I, I, I, F, I, I, P],
     "xb_attn_fwd": [P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, F, I, P],
     "xb_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, I, I, I, I, I, I, F, I, P],
 }

@@ -1,0 +1,335 @@
+"""Context parallelism: Ulysses (head-scatter all-to-all), zigzag ring attention, and the hybrid.
+
+Token layout (see ``data.collators.SequenceShardCollator``): every document is padded to a multiple
+of ``2 * ring * ulysses``; ring rank ``r`` owns chunks ``r`` and ``2R-1-r`` of every document
+(zigzag, balanced causal work) and inside a ring rank the Ulysses ranks own contiguous slices.
+
+* Ulysses: q/k/v ``[T_loc, H, D] -> [T_ring, H/U, D]`` by all-to-all before attention and back
+  after (src/xorl/distributed/sequence_parallel/ulysses.py:49-152, strategy.py:164-247).
+* Ring: every rank attends its queries to the K/V of every ring rank.  For source rank ``j`` the
+  zigzag layout reduces the causal structure to whole-block pairs of equal length — (q_a,k_a) and
+  (q_b,k_b) causal plus (q_b,k_a) full when ``j == r``; (q_a,k_a),(q_b,k_a) full when ``j < r``;
+  (q_b,k_a),(q_b,k_b) full when ``j > r`` — each one call of the block-pair attention kernel, merged
+  by log-sum-exp (src/xorl/distributed/sequence_parallel/ring_attention.py:28-77,202-253,331-843).
+  Backward re-uses the gathered K/V, accumulates dQ locally and reduce-scatters dK/dV to owners.
+* Hybrid: Ulysses inside each ring rank group, ring across groups (strategy.py:428-477).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops import attention as attn_ops
+
+
+# --------------------------------------------------------------------------------------------
+# block-pair attention primitive
+# --------------------------------------------------------------------------------------------
+def _block_ref(q, k, v, cu, k_starts, causal, scale):
+    T, Hq, D = q.shape
+    g = Hq // k.shape[1]
+    out = torch.zeros_like(q, dtype=torch.float32)
+    lse = torch.full((Hq, T), float("-inf"), device=q.device, dtype=torch.float32)
+    cu_l, ks = cu.tolist(), k_starts.tolist()
+    for b in range(len(ks)):
+        if ks[b] < 0:
+            continue
+        s, e = cu_l[b], cu_l[b + 1]
+        L = e - s
+        qb = q[s:e].float().transpose(0, 1)
+        kb = k[ks[b]:ks[b] + L].float().transpose(0, 1).repeat_interleave(g, 0)
+        vb = v[ks[b]:ks[b] + L].float().transpose(0, 1).repeat_interleave(g, 0)
+        sc = torch.matmul(qb, kb.transpose(1, 2)) * scale
+        if causal:
+            sc = sc.masked_fill(~torch.ones(L, L, dtype=torch.bool, device=q.device).tril(), float("-inf"))
+        l = torch.logsumexp(sc, dim=-1)
+        out[s:e] = torch.matmul(torch.softmax(sc, -1), vb).transpose(0, 1)
+        lse[:, s:e] = l
+    return out, lse
+
+
+def block_attention(q, k, v, cu, k_starts, causal: bool, scale: float):
+    """Attention of query blocks (tiling given by ``cu``) against key blocks starting at
+    ``k_starts`` (-1 = skip).  Returns (out fp32 [T,Hq,D] zero where skipped, lse [Hq,T] -inf there)."""
+    T, Hq, D = q.shape
+    if q.is_cuda and q.dtype == torch.bfloat16 and D == 128:
+        out = torch.zeros((T, Hq, D), device=q.device, dtype=q.dtype)
+        lse = torch.full((Hq, T), float("-inf"), device=q.device, dtype=torch.float32)
+        k, v = k.contiguous(), v.contiguous()
+        rc = _lib.cuda_lib().xb_attn_fwd_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                            lse.data_ptr(), cu.data_ptr(), k_starts.data_ptr(),
+                                            q.stride(0), k.stride(0), v.stride(0), out.stride(0),
+                                            k_starts.numel(), T, k.shape[0], Hq, k.shape[1], D,
+                                            int(causal), float(scale), 0, _lib.stream_ptr())
+        _lib.check(rc, "xb_attn_fwd_ex")
+        return out.float(), lse
+    return _block_ref(q, k, v, cu, k_starts, causal, scale)
+
+
+def block_attention_bwd(q, k, v, out, dout, lse, delta, dq_acc, cu, k_starts, causal, scale,
+                        first: bool):
+    """Gradients of one block-pair call given the *final* (merged) out / lse.  dq is accumulated
+    into ``dq_acc`` (fp32); returns (dk fp32, dv fp32) for the K/V tensor (zeros where untouched)."""
+    T, Hq, D = q.shape
+    Tk, Hkv = k.shape[0], k.shape[1]
+    if q.is_cuda and q.dtype == torch.bfloat16 and D == 128:
+        dk = torch.zeros((Tk, Hkv, D), device=q.device, dtype=torch.float32)
+        dv = torch.zeros((Tk, Hkv, D), device=q.device, dtype=torch.bfloat16)
+        flags = (0 if first else 1) | (0 if first else 2)
+        rc = _lib.cuda_lib().xb_attn_bwd_ex(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+            delta.data_ptr(), dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu.data_ptr(),
+            k_starts.data_ptr(), q.stride(0), k.stride(0), v.stride(0), out.stride(0), dout.stride(0),
+            dv.stride(0), k_starts.numel(), T, Tk, Hq, Hkv, D, int(causal), float(scale), flags, 0,
+            _lib.stream_ptr())
+        _lib.check(rc, "xb_attn_bwd_ex")
+        return dk, dv.float()
+    # reference math
+    g = Hq // Hkv
+    dk = torch.zeros((Tk, Hkv, D), device=q.device, dtype=torch.float32)
+    dv = torch.zeros_like(dk)
+    cu_l, ks = cu.tolist(), k_starts.tolist()
+    if first:
+        dq_acc.zero_()
+        delta.copy_((out.float() * dout.float()).sum(-1).transpose(0, 1))
+    for b in range(len(ks)):
+        if ks[b] < 0:
+            continue
+        s, e = cu_l[b], cu_l[b + 1]
+        L = e - s
+        qb = q[s:e].float().transpose(0, 1)
+        kb = k[ks[b]:ks[b] + L].float().transpose(0, 1).repeat_interleave(g, 0)
+        vb = v[ks[b]:ks[b] + L].float().transpose(0, 1).repeat_interleave(g, 0)
+        do = dout[s:e].float().transpose(0, 1)
+        sc = torch.matmul(qb, kb.transpose(1, 2)) * scale
+        if causal:
+            sc = sc.masked_fill(~torch.ones(L, L, dtype=torch.bool, device=q.device).tril(), float("-inf"))
+        p = torch.exp(sc - lse[:, s:e].unsqueeze(-1))
+        dp = torch.matmul(do, vb.transpose(1, 2))
+        ds = p * (dp - delta[:, s:e].unsqueeze(-1)) * scale
+        dq_acc[s:e] += torch.matmul(ds, kb).transpose(0, 1)
+        dkb = torch.matmul(ds.transpose(1, 2), qb)          # [Hq, L, D]
+        dvb = torch.matmul(p.transpose(1, 2), do)
+        dk[ks[b]:ks[b] + L] += dkb.reshape(Hkv, g, L, D).sum(1).transpose(0, 1)
+        dv[ks[b]:ks[b] + L] += dvb.reshape(Hkv, g, L, D).sum(1).transpose(0, 1)
+    return dk, dv
+
+
+def _merge(out_acc, lse_acc, out_p, lse_p):
+    """Log-sum-exp merge of partial attention results; tensors are [T,Hq,D] fp32 and [Hq,T]."""
+    new = torch.logaddexp(lse_acc, lse_p)
+    safe = torch.where(torch.isinf(new), torch.zeros_like(new), new)
+    wa = torch.exp(lse_acc - safe).transpose(0, 1).unsqueeze(-1)
+    wp = torch.exp(lse_p - safe).transpose(0, 1).unsqueeze(-1)
+    return out_acc * wa + out_p * wp, new
+
+
+# --------------------------------------------------------------------------------------------
+# ring attention
+# --------------------------------------------------------------------------------------------
+def _ring_calls(cu_blocks: torch.Tensor, r: int, j: int) -> List[Tuple[torch.Tensor, bool]]:
+    """k_starts (per query block) and causal flag of every kernel call for source rank j.
+    ``cu_blocks`` tiles the local tokens into blocks a0,b0,a1,b1,... (two per document)."""
+    starts = cu_blocks[:-1].clone()
+    nb = starts.numel()
+    is_a = torch.arange(nb, device=starts.device) % 2 == 0
+    a_start = starts.clone()
+    a_start[~is_a] = starts[is_a]                 # start of the document's a-block
+    b_start = starts.clone()
+    b_start[is_a] = starts[~is_a]
+    neg = torch.full_like(starts, -1)
+    i32 = lambda t: t.to(torch.int32)
+    if j == r:
+        return [(i32(starts), True),                               # (q_a,k_a), (q_b,k_b) causal
+                (i32(torch.where(is_a, neg, a_start)), False)]    # (q_b,k_a) full
+    if j < r:
+        # two calls: the backward kernel writes dK/dV per key block, so a key block may appear
+        # only once per call
+        return [(i32(torch.where(is_a, a_start, neg)), False),    # (q_a,k_a) full
+                (i32(torch.where(is_a, neg, a_start)), False)]    # (q_b,k_a) full
+    return [(i32(torch.where(is_a, neg, a_start)), False),        # (q_b,k_a)
+            (i32(torch.where(is_a, neg, b_start)), False)]        # (q_b,k_b)
+
+
+class _RingAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_blocks, group, rank, world, scale):
+        T, Hq, D = q.shape
+        kv = torch.stack([k.contiguous(), v.contiguous()])            # [2, T, Hkv, D]
+        gathered = [torch.empty_like(kv) for _ in range(world)]
+        dist.all_gather(gathered, kv, group=group)
+        out = torch.zeros((T, Hq, D), device=q.device, dtype=torch.float32)
+        lse = torch.full((Hq, T), float("-inf"), device=q.device, dtype=torch.float32)
+        qc = q.contiguous()
+        for s in range(world):
+            j = (rank - s) % world
+            kj, vj = gathered[j][0], gathered[j][1]
+            for k_starts, causal in _ring_calls(cu_blocks, rank, j):
+                o_p, l_p = block_attention(qc, kj, vj, cu_blocks, k_starts, causal, scale)
+                out, lse = _merge(out, lse, o_p, l_p)
+        out_lp = out.to(q.dtype)
+        ctx.save_for_backward(qc, torch.stack(gathered), out_lp, lse, cu_blocks)
+        ctx.cfg = (group, rank, world, scale)
+        return out_lp
+
+    @staticmethod
+    def backward(ctx, dout):
+        qc, gathered, out, lse, cu_blocks = ctx.saved_tensors
+        group, rank, world, scale = ctx.cfg
+        T, Hq, D = qc.shape
+        dout = dout.contiguous()
+        dq = torch.zeros((T, Hq, D), device=qc.device, dtype=torch.float32)
+        delta = torch.empty((Hq, T), device=qc.device, dtype=torch.float32)
+        dkv = torch.zeros((world,) + tuple(gathered.shape[1:]), device=qc.device, dtype=torch.float32)
+        first = True
+        for s in range(world):
+            j = (rank - s) % world
+            kj, vj = gathered[j][0], gathered[j][1]
+            for k_starts, causal in _ring_calls(cu_blocks, rank, j):
+                dk, dv = block_attention_bwd(qc, kj, vj, out, dout, lse, delta, dq, cu_blocks,
+                                             k_starts, causal, scale, first)
+                first = False
+                dkv[j, 0] += dk
+                dkv[j, 1] += dv
+        mine = torch.empty_like(dkv[0])
+        _reduce_scatter(mine, dkv, group)
+        return dq.to(qc.dtype), mine[0].to(qc.dtype), mine[1].to(qc.dtype), None, None, None, None, None
+
+
+def _reduce_scatter(out, stacked, group):
+    """out = sum over ranks of stacked[my_rank] (gloo has no reduce_scatter: all-reduce + slice)."""
+    if dist.get_backend(group) == "gloo":
+        t = stacked.clone()
+        dist.all_reduce(t, group=group)
+        out.copy_(t[dist.get_rank(group)])
+    else:
+        dist.reduce_scatter_tensor(out, stacked.contiguous(), group=group)
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# Ulysses all-to-all
+# --------------------------------------------------------------------------------------------
+class _SeqToHead(torch.autograd.Function):
+    """[T_loc, H, D] (all heads, local tokens) -> [U*T_loc, H/U, D] (local heads, group tokens)."""
+
+    @staticmethod
+    def forward(ctx, x, group, world):
+        ctx.group, ctx.world = group, world
+        T, H, D = x.shape
+        send = x.reshape(T, world, H // world, D).permute(1, 0, 2, 3).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+        return recv.reshape(world * T, H // world, D)
+
+    @staticmethod
+    def backward(ctx, g):
+        world = ctx.world
+        TT, Hl, D = g.shape
+        T = TT // world
+        send = g.reshape(world, T, Hl, D).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=ctx.group)
+        return recv.permute(1, 0, 2, 3).reshape(T, world * Hl, D), None, None
+
+
+class _HeadToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, world):
+        ctx.group, ctx.world = group, world
+        TT, Hl, D = x.shape
+        T = TT // world
+        send = x.reshape(world, T, Hl, D).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+        return recv.permute(1, 0, 2, 3).reshape(T, world * Hl, D)
+
+    @staticmethod
+    def backward(ctx, g):
+        world = ctx.world
+        T, H, D = g.shape
+        send = g.reshape(T, world, H // world, D).permute(1, 0, 2, 3).contiguous()
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=ctx.group)
+        return recv.reshape(world * T, H // world, D), None, None
+
+
+# --------------------------------------------------------------------------------------------
+# strategy object used by the attention layers
+# --------------------------------------------------------------------------------------------
+class ContextParallelStrategy:
+    def __init__(self, ps):
+        self.ps = ps
+        self.U, self.R = ps.ulysses_size, ps.ringattn_size
+        self.u_group, self.r_group = ps.group("ulysses"), ps.group("ringattn")
+        self.u_rank, self.r_rank = ps.ulysses_rank, ps.ringattn_rank
+
+    def prepare(self, model, ctx) -> None:
+        """cos/sin for the local tokens' global positions; block tilings for the attention calls."""
+        ctx.cos, ctx.sin = model.rotary(ctx.position_ids)
+        local_cu = ctx.aux.get("local_cu_seqlens")
+        if local_cu is None:
+            raise ValueError("context parallelism needs batches from SequenceShardCollator "
+                             "(local_cu_seqlens missing)")
+        local_cu = local_cu.cpu()
+        lens = (local_cu[1:] - local_cu[:-1]).to(torch.int64)      # this rank's tokens per document
+        dev = ctx.position_ids.device
+        U = self.U
+        ring_lens = lens * U                                       # tokens per document per ring rank
+        if self.R > 1:
+            half = ring_lens // 2
+            blocks = torch.stack([half, half], 1).reshape(-1)      # a, b per document
+            ctx.aux["cp_blocks"] = torch.cat([blocks.new_zeros(1), blocks.cumsum(0)]).to(torch.int32).to(dev)
+        ctx.aux["cp_ring_cu"] = torch.cat([ring_lens.new_zeros(1), ring_lens.cumsum(0)]).to(torch.int32).to(dev)
+        if U > 1:
+            # after the all-to-all tokens are ordered (ulysses rank, document, offset); attention wants
+            # (document, ulysses rank, offset)
+            T_loc = int(lens.sum())
+            doc_of = torch.repeat_interleave(torch.arange(lens.numel()), lens)
+            off = torch.arange(T_loc) - torch.repeat_interleave(local_cu[:-1].to(torch.int64), lens)
+            ring_start = ctx.aux["cp_ring_cu"][:-1].to("cpu", torch.int64)
+            idx = torch.empty(U * T_loc, dtype=torch.int64)
+            for u in range(U):
+                dst = ring_start[doc_of] + u * lens[doc_of] + off
+                idx[dst] = u * T_loc + torch.arange(T_loc)
+            ctx.aux["cp_gather_idx"] = idx.to(dev)
+            inv = torch.empty_like(idx)
+            inv[idx] = torch.arange(idx.numel())
+            ctx.aux["cp_scatter_idx"] = inv.to(dev)
+
+    def attention(self, attn, qkv, ctx) -> torch.Tensor:
+        """qkv: local tokens, all (tensor-parallel-local) heads.  Returns [T_loc, Hq*D]."""
+        Hq, Hkv, D = attn.Hq, attn.Hkv, attn.D
+        T = qkv.shape[0]
+        q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+        q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
+        if attn.use_qk_norm:
+            q = attn_ops._head_rmsnorm_ref(q, attn.q_norm.weight, attn.cfg.rms_norm_eps)
+            k = attn_ops._head_rmsnorm_ref(k, attn.k_norm.weight, attn.cfg.rms_norm_eps)
+        q = attn_ops.rope_reference(q, ctx.cos, ctx.sin)
+        k = attn_ops.rope_reference(k, ctx.cos, ctx.sin)
+        U = self.U
+        if U > 1:
+            if Hkv % U:
+                rep = U // math.gcd(Hkv, U)
+                k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+            gi = ctx.aux["cp_gather_idx"]
+            q = _SeqToHead.apply(q, self.u_group, U).index_select(0, gi)
+            k = _SeqToHead.apply(k, self.u_group, U).index_select(0, gi)
+            v = _SeqToHead.apply(v, self.u_group, U).index_select(0, gi)
+        if self.R > 1:
+            out = _RingAttention.apply(q, k, v, ctx.aux["cp_blocks"], self.r_group, self.r_rank,
+                                       self.R, attn.scale)
+        else:
+            out = attn_ops.flash_attn_varlen(q, k, v, ctx.aux["cp_ring_cu"], ctx.causal, attn.scale)
+        if U > 1:
+            out = _HeadToSeq.apply(out.index_select(0, ctx.aux["cp_scatter_idx"]), self.u_group, U)
+        return out.reshape(T, Hq * D)
+
+
+def build_cp_strategy(model, ps) -> ContextParallelStrategy:
+    return ContextParallelStrategy(ps)

@@ -398,9 +398,10 @@ class Zero3Engine:
         return root, layers
 
     # ---- primitives shared by the plain step and the pipeline runner ----------------------------
-    def make_step_context(self, input_ids, position_ids=None, cu_seqlens=None, grad_scale: float = 1.0):
+    def make_step_context(self, input_ids, position_ids=None, cu_seqlens=None, grad_scale: float = 1.0,
+                          extra=None):
         model = self.model
-        ctx = model.make_context(input_ids, position_ids, cu_seqlens, training=True)
+        ctx = model.make_context(input_ids, position_ids, cu_seqlens, training=True, extra=extra)
         if getattr(model, "aux_loss_enabled", False):
             # per-layer auxiliary losses are weighted like a token mean over the global batch
             ctx.aux["aux_loss_scale"] = float(ctx.num_tokens) * grad_scale
@@ -525,14 +526,14 @@ class Zero3Engine:
 
     def forward_backward(self, input_ids: torch.Tensor, labels: torch.Tensor, *,
                          position_ids=None, cu_seqlens=None, grad_scale: float = 1.0,
-                         extra_loss_fn: Optional[Callable] = None) -> torch.Tensor:
+                         extra_loss_fn: Optional[Callable] = None, extra=None) -> torch.Tensor:
         """One micro-batch.  Returns ``grad_scale * sum(token CE)`` (detached).  Gradients are
         accumulated into the fp32 shards; call ``finish_grad_sync`` after the last micro-batch."""
         model = self.model
         root, layers = self._units_by_role()
         self.gather(root)
         self.wait_gather(root)
-        ctx = self.make_step_context(input_ids, position_ids, cu_seqlens, grad_scale)
+        ctx = self.make_step_context(input_ids, position_ids, cu_seqlens, grad_scale, extra)
         with torch.no_grad():
             acts = model.forward_embed(input_ids, ctx)
         acts, saved = self.chunk_forward(layers, acts, ctx, keep_last_gathered=True)

@@ -235,7 +235,8 @@ class Trainer:
             loss = self.engine.forward_backward(
                 d["input_ids"], d["labels"], position_ids=d.get("position_ids"),
                 cu_seqlens=d.get("cu_seqlens"), grad_scale=1.0 / global_tokens,
-                extra_loss_fn=self._extra_loss_fn())
+                extra_loss_fn=self._extra_loss_fn(),
+                extra={"local_cu_seqlens": mb.get("local_cu_seqlens")})
             total = loss if total is None else total + loss
         self.engine.finish_grad_sync()
         norm, coef = self.engine.grad_norm_and_clip_coef(t.max_grad_norm)
