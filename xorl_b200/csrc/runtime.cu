@@ -39,6 +39,13 @@ int xb_sm_count() {
 }
 
 xb_encode_tiled_fn xb_get_encode_tiled() {
+  // The driver entry point needs a CUDA context bound to the calling thread.  A fresh thread whose
+  // device is 0 (e.g. an autograd worker) has none until its first runtime call, so make one.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(0);
+    ctx_bound = true;
+  }
   std::lock_guard<std::mutex> lk(g_mu);
   if (g_encode == nullptr) {
     void* fn = nullptr;
@@ -65,6 +72,10 @@ int xb_make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, 
   CUresult r = enc(out, dt, 2, const_cast<void*>(base), gdim, gstr, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "xb_make_tmap_2d failed (%d): base=%p rows=%llu cols=%llu ld=%llu box=%ux%u es=%d\n",
+            (int)r, base, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld,
+            box_rows, box_cols, elem_size);
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 

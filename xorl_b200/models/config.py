@@ -167,6 +167,14 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                            rope_theta=1e6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
                            norm_topk_prob=True, router_aux_loss_coef=1e-3, tie_word_embeddings=False,
                            max_position_embeddings=4096),
+    "small-qwen3": dict(model_type="qwen3", vocab_size=4096, hidden_size=512, intermediate_size=1024,
+                        num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                        rope_theta=1e6, tie_word_embeddings=False, max_position_embeddings=8192),
+    "small-qwen3-moe": dict(model_type="qwen3_moe", vocab_size=4096, hidden_size=512, intermediate_size=1024,
+                            num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                            rope_theta=1e6, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=256,
+                            norm_topk_prob=True, router_aux_loss_coef=1e-3, tie_word_embeddings=False,
+                            max_position_embeddings=8192),
     "qwen3-8b": dict(model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
                      num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                      rope_theta=1e6, tie_word_embeddings=False),

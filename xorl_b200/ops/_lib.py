@@ -55,6 +55,9 @@ _SIGNATURES = {
     "xb_symm_wait": [P, I, I, I, I, P],
     "xb_symm_allgather": [P, P, L, I, I, I, P],
     "xb_symm_reduce_scatter": [P, P, ctypes.c_ulonglong, L, L, I, F, P, P, I, I, I, I, I, I, I, I, P],
+    "xb_ep_exchange_counts": [P, P, P, I, I, I, I, I, I, P],
+    "xb_ep_prepare_recv": [P, P, P, P, I, I, I, P],
+    "xb_ep_push_rows": [P, L, P, P, P, P, I, I, I, P, L, P, P, I, I, I, I, I, P],
     "xb_peer_copy": [P, P, L, I, P],
     "xb_grouped_gemm_rows": [P, P, P, P, I, L, I, I, L, L, I, P],
     "xb_grouped_gemm_wgrad": [P, P, P, P, I, L, I, I, L, L, I, I, P],

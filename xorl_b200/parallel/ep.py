@@ -84,7 +84,8 @@ def _unsort(sorted_rows: torch.Tensor, order: torch.Tensor) -> torch.Tensor:
 def ep_moe_forward(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor, experts,
                    num_experts: int, ctx) -> torch.Tensor:
     mode = ctx.aux.get("ep_dispatch", "alltoall")
-    if mode in ("fused", "deepep") and x.is_cuda:
+    if mode in ("fused", "deepep") and x.is_cuda and x.dtype == torch.bfloat16 \
+            and ctx.aux.get("ep_workspace_reuse_ok", True):
         from .ep_fused import fused_ep_forward, fused_ep_available
         if fused_ep_available():
             return fused_ep_forward(x, weights, indices, experts, num_experts, ctx)

@@ -1,0 +1,217 @@
+"""Fused expert-parallel dispatch / combine over peer memory (``csrc/ep.cu``).
+
+Per MoE layer: exchange per-expert counts through peer stores -> every rank derives, on the
+device, the exact row of each of its token slots in the owners' segment-aligned receive buffers
+-> push rows straight into the owners' buffers -> grouped expert MLP on the receive buffer ->
+push expert outputs straight back into the sources' slot buffers -> weighted sum over the k
+experts of a token.  No NCCL call and no host synchronisation on the path; every wait on a peer
+is bounded.  Backward runs the same two pushes in the opposite roles on a second set of buffers.
+
+The receive buffer holds ``XORL_B200_EP_CAPACITY`` (default 2.0) times the balanced load; a
+routing so skewed that a rank would receive more rows than that is reported through the status
+words (rows beyond the capacity are dropped, never written out of bounds).  Workspace tensors
+are reused by every layer, which is safe because layers are recomputed right before their
+backward; without recomputation the all-to-all path is used instead.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops import moe as moe_ops
+from .state import get_parallel_state
+
+FLAG_BYTES = 4096
+S_COUNTS, S_DISP, S_RET, S_BDISP, S_BRET = 0, 16, 32, 48, 64
+C_DISP, C_RET, C_BDISP, C_BRET = 96, 97, 98, 99
+WAIT_MS = 2000
+_WS: Dict = {}
+
+
+def fused_ep_available() -> bool:
+    ps = get_parallel_state()
+    return ps.ep_size > 1 and torch.cuda.is_available() and ps.group("ep") is not None \
+        and os.environ.get("XORL_B200_EP_FUSED", "1") == "1"
+
+
+class _Workspace:
+    def __init__(self, H: int, slots: int, num_experts: int, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        ps = get_parallel_state()
+        self.N, self.rank = ps.ep_size, ps.ep_rank
+        self.El = num_experts // self.N
+        self.E, self.H, self.slots = num_experts, H, slots
+        factor = float(os.environ.get("XORL_B200_EP_CAPACITY", "2.0"))
+        self.cap = moe_ops.buffer_rows(int(min(self.N, factor) * slots), self.El)
+        a = lambda x: (x + 255) // 256 * 256
+        off = FLAG_BYTES
+        self.o_table = off; off = a(off + self.N * self.E * 4)
+        self.o = {}
+        for name, rows, width in (("recv_f", self.cap, H * 2), ("meta_f", self.cap, 4),
+                                  ("ret_f", slots, H * 2), ("recv_b", self.cap, H * 2),
+                                  ("meta_b", self.cap, 4), ("ret_b", slots, H * 2)):
+            self.o[name] = off
+            off = a(off + rows * width)
+        self.heap = symm_mem.empty(off, dtype=torch.uint8, device=device)
+        self.heap.zero_()
+        self.hdl = symm_mem.rendezvous(self.heap, ps.group("ep"))
+        self.base = [int(p) for p in self.hdl.buffer_ptrs]
+        self.epoch = {k: 0 for k in ("counts", "disp", "ret", "bdisp", "bret")}
+        self.lib = _lib.cuda_lib()
+        torch.cuda.synchronize()
+        dist.barrier(group=ps.group("ep"))
+
+    def ptrs(self, off: int):
+        return (ctypes.c_ulonglong * self.N)(*[b + off for b in self.base])
+
+    def view(self, name: str, rows: int, dtype, width_elems: int):
+        es = torch.empty(0, dtype=dtype).element_size()
+        o = self.o[name]
+        return self.heap[o:o + rows * width_elems * es].view(dtype).view(rows, width_elems) \
+            if width_elems > 1 else self.heap[o:o + rows * es].view(dtype)
+
+    def local_flags(self, slot: int) -> int:
+        return self.base[self.rank] + 4 * slot
+
+    def wait(self, slot: int, epoch: int) -> None:
+        _lib.check(self.lib.xb_symm_wait(ctypes.c_void_p(self.local_flags(slot)), self.N, self.rank,
+                                         epoch, WAIT_MS, _lib.stream_ptr()), "xb_symm_wait")
+
+    def push(self, src, src_row, dest_rank, dest_row, tag, dst_name, meta_name, slot, counter, key):
+        self.epoch[key] += 1
+        n_items = dest_rank.numel()
+        _lib.check(self.lib.xb_ep_push_rows(
+            src.data_ptr(), src.stride(0) * 2, _lib.ptr(src_row), dest_rank.data_ptr(),
+            dest_row.data_ptr(), _lib.ptr(tag), 24, n_items, self.H * 2, self.ptrs(self.o[dst_name]),
+            self.H * 2, None if meta_name is None else self.ptrs(self.o[meta_name]), self.ptrs(0),
+            slot, counter, self.rank, self.N, self.epoch[key], _lib.stream_ptr()), "xb_ep_push_rows")
+        self.wait(slot, self.epoch[key])
+
+
+def _workspace(H, slots, E, device) -> _Workspace:
+    key = (H, slots, E)
+    if key not in _WS:
+        _WS[key] = _Workspace(H, slots, E, device)
+    return _WS[key]
+
+
+class _Plan:
+    """Everything both directions need, computed once per layer call on the device."""
+    pass
+
+
+def _make_plan(ws: _Workspace, indices: torch.Tensor) -> _Plan:
+    dev = indices.device
+    T, k = indices.shape
+    flat = indices.reshape(-1)
+    counts = torch.bincount(flat, minlength=ws.E).to(torch.int32)
+    ws.epoch["counts"] += 1
+    _lib.check(ws.lib.xb_ep_exchange_counts(counts.data_ptr(), ws.ptrs(ws.o_table), ws.ptrs(0), S_COUNTS,
+                                            ws.rank, ws.N, ws.E, ws.epoch["counts"], WAIT_MS,
+                                            _lib.stream_ptr()), "xb_ep_exchange_counts")
+    table = ws.heap[ws.o_table:ws.o_table + ws.N * ws.E * 4].view(torch.int32).view(ws.N, ws.E).long()
+    tot = table.sum(0)                                              # [E] rows per expert (all sources)
+    padded = (tot + moe_ops.SEG_ALIGN - 1) // moe_ops.SEG_ALIGN * moe_ops.SEG_ALIGN
+    pe = padded.view(ws.N, ws.El)
+    seg_start = (pe.cumsum(1) - pe).reshape(-1)                     # start row of expert e on its owner
+    before_me = table[:ws.rank].sum(0) if ws.rank > 0 else torch.zeros_like(tot)
+    base = seg_start + before_me
+    order = torch.argsort(flat, stable=True)
+    c64 = counts.long()
+    starts = c64.cumsum(0) - c64
+    sorted_e = flat[order]
+    rank_in_e = torch.empty_like(flat)
+    rank_in_e[order] = torch.arange(flat.numel(), device=dev) - starts[sorted_e]
+    p = _Plan()
+    p.T, p.k = T, k
+    p.dest_rank = (flat // ws.El).to(torch.int32)
+    p.dest_row = (base[flat] + rank_in_e).to(torch.int32)
+    # rows that would fall outside the receive buffer are dropped (and reported by the kernel's
+    # caller through the overflow flag below)
+    over = p.dest_row >= ws.cap
+    p.dest_rank = torch.where(over, torch.full_like(p.dest_rank, -1), p.dest_rank)
+    p.overflow = over.any()
+    p.src_row = (torch.arange(flat.numel(), device=dev) // k).to(torch.int32)
+    mine = slice(ws.rank * ws.El, (ws.rank + 1) * ws.El)
+    my_pad = padded[mine]
+    p.seg = torch.cat([my_pad.new_zeros(1), my_pad.cumsum(0)]).clamp(max=ws.cap // 128 * 128).to(torch.int32)
+    p.tot = tot[mine].to(torch.int32)
+    return p
+
+
+def _prepare(ws: _Workspace, plan: _Plan, recv_name: str, meta_name: str) -> None:
+    x = ws.view(recv_name, ws.cap, torch.bfloat16, ws.H)
+    meta = ws.view(meta_name, ws.cap, torch.int32, 1)
+    _lib.check(ws.lib.xb_ep_prepare_recv(x.data_ptr(), meta.data_ptr(), plan.seg.data_ptr(),
+                                         plan.tot.data_ptr(), ws.El, ws.cap, ws.H * 2,
+                                         _lib.stream_ptr()), "xb_ep_prepare_recv")
+
+
+def _meta_targets(meta: torch.Tensor):
+    valid = meta >= 0
+    rank = torch.where(valid, meta >> 24, torch.full_like(meta, -1))
+    slot = torch.where(valid, meta & 0xFFFFFF, torch.zeros_like(meta))
+    return rank.to(torch.int32), slot.to(torch.int32)
+
+
+class _Dispatch(torch.autograd.Function):
+    """token rows -> owners' receive buffers; backward: gradient rows -> source slots, summed over k."""
+
+    @staticmethod
+    def forward(ctx, x, ws: _Workspace, plan: _Plan):
+        x = x.contiguous()
+        _prepare(ws, plan, "recv_f", "meta_f")
+        ws.push(x, plan.src_row, plan.dest_rank, plan.dest_row, None, "recv_f", "meta_f", S_DISP, C_DISP, "disp")
+        ctx.ws, ctx.plan = ws, plan
+        return ws.view("recv_f", ws.cap, torch.bfloat16, ws.H)
+
+    @staticmethod
+    def backward(ctx, dbuf):
+        ws, plan = ctx.ws, ctx.plan
+        meta = ws.view("meta_f", ws.cap, torch.int32, 1)
+        r, s = _meta_targets(meta)
+        ws.push(dbuf.contiguous(), None, r, s, None, "ret_b", None, S_BRET, C_BRET, "bret")
+        dslots = ws.view("ret_b", plan.T * plan.k, torch.bfloat16, ws.H)
+        dx = dslots.view(plan.T, plan.k, ws.H).float().sum(1).to(torch.bfloat16)
+        return dx, None, None
+
+
+class _Return(torch.autograd.Function):
+    """expert output rows -> source slot buffers; backward: slot gradients -> owners' rows."""
+
+    @staticmethod
+    def forward(ctx, y, ws: _Workspace, plan: _Plan):
+        meta = ws.view("meta_f", ws.cap, torch.int32, 1)
+        r, s = _meta_targets(meta)
+        ws.push(y.contiguous(), None, r, s, None, "ret_f", None, S_RET, C_RET, "ret")
+        ctx.ws, ctx.plan = ws, plan
+        return ws.view("ret_f", plan.T * plan.k, torch.bfloat16, ws.H)
+
+    @staticmethod
+    def backward(ctx, dslots):
+        ws, plan = ctx.ws, ctx.plan
+        _prepare(ws, plan, "recv_b", "meta_b")
+        src_row = torch.arange(plan.T * plan.k, device=dslots.device, dtype=torch.int32)
+        ws.push(dslots.contiguous(), src_row, plan.dest_rank, plan.dest_row, None, "recv_b", "meta_b",
+                S_BDISP, C_BDISP, "bdisp")
+        return ws.view("recv_b", ws.cap, torch.bfloat16, ws.H), None, None
+
+
+def fused_ep_forward(x, weights, indices, experts, num_experts, ctx):
+    T, H = x.shape
+    k = indices.shape[1]
+    slots = ctx.aux.get("ep_max_slots") or T * k
+    ws = _workspace(H, max(slots, T * k), num_experts, x.device)
+    if T * k > ws.slots:
+        raise RuntimeError(f"{T * k} token slots exceed the EP workspace ({ws.slots})")
+    plan = _make_plan(ws, indices)
+    buf = _Dispatch.apply(x, ws, plan)
+    y = moe_ops.expert_mlp_aligned(buf, plan.seg, experts.gate_up_proj, experts.down_proj)
+    y_slots = _Return.apply(y, ws, plan)
+    out = (y_slots.view(T, k, H).float() * weights.unsqueeze(-1).float()).sum(1)
+    return out.to(x.dtype)

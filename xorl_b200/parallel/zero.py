@@ -408,6 +408,9 @@ class Zero3Engine:
         # record expert choices in the first pass and replay them when a layer is recomputed, so
         # both passes dispatch identically (src/xorl/models/layers/moe/routing_replay.py)
         ctx.aux["record_routing"] = self.recompute
+        # the fused EP path reuses its peer-memory workspaces across layers, which is only safe when
+        # a layer's backward immediately follows its (re)computed forward
+        ctx.aux["ep_workspace_reuse_ok"] = self.recompute
         return ctx
 
     def chunk_forward(self, layers: List[ZeroUnit], acts, ctx, keep_last_gathered: bool = False):

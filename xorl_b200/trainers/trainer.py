@@ -107,6 +107,9 @@ class Trainer:
                                                       * t.micro_batch_size // t.ce_num_chunks))
         if self.model_config.is_moe:
             self.model.ctx_defaults["ep_dispatch"] = a.model.ep_dispatch
+            # every EP rank must size its peer-memory workspace identically
+            self.model.ctx_defaults["ep_max_slots"] = int(a.data.sample_packing_sequence_len or 4096) \
+                * t.micro_batch_size * self.model_config.num_experts_per_tok
             if t.softmax_auxiliary_loss or self.model_config.router_aux_loss_coef > 0:
                 coef = t.auxiliary_loss_multiplier if t.softmax_auxiliary_loss \
                     else self.model_config.router_aux_loss_coef
