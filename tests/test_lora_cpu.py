@@ -1,0 +1,104 @@
+"""LoRA on CPU: only adapters train, the delta on fused projections equals per-slice adapters,
+merge folds the update into the base weight, and the PEFT export has the expected names."""
+import os
+
+import torch
+
+from xorl_b200.arguments import LoRAArguments
+from xorl_b200.models.config import preset
+from xorl_b200.models.decoder import DecoderLM
+from xorl_b200.parallel.state import init_parallel_state, reset_parallel_state
+
+
+def _engine(lora_args, tmp=None):
+    from xorl_b200.adapters.lora import inject_lora
+    from xorl_b200.parallel.zero import Zero3Engine
+    reset_parallel_state()
+    ps = init_parallel_state(device_type="cpu")
+    model = DecoderLM(preset("tiny-qwen3", tie_word_embeddings=False), device="meta")
+    wrapped = inject_lora(model, lora_args)
+    eng = Zero3Engine(model, ps, compute_dtype=torch.float32, device=torch.device("cpu"))
+    return model, eng, wrapped
+
+
+def test_lora_trains_only_adapters(tmp_path):
+    from xorl_b200.adapters.lora import merge_lora, save_lora_checkpoint
+    from xorl_b200.optim import build_optimizer
+    la = LoRAArguments(enable_lora=True, lora_rank=4, lora_alpha=8, lora_b_init_std=0.01,
+                       lora_target_modules=["q_proj", "v_proj", "down_proj"])
+    model, eng, wrapped = _engine(la)
+    assert len(wrapped) == 4  # qkv_proj and down_proj in both layers
+    frozen = [g for g in eng.all_groups() if getattr(g, "frozen", False)]
+    train = [g for g in eng.all_groups() if not getattr(g, "frozen", False)]
+    assert frozen and train
+    assert all(".lora_" in n for g in train for n, _ in g.named_params)
+    base_before = {n: t.clone() for n, t in eng.iter_full_tensors("master") if ".lora_" not in n}
+    opt = build_optimizer(eng, lr=1e-2, weight_decay=0.0)
+    ids = torch.randint(0, 1024, (2, 65))
+    losses = []
+    for _ in range(5):
+        opt.zero_grad()
+        loss = eng.forward_backward(ids[:, :-1], ids[:, 1:], grad_scale=1.0 / 128)
+        eng.finish_grad_sync()
+        _, coef = eng.grad_norm_and_clip_coef(1.0)
+        opt.step(clip_coef=coef)
+        losses.append(float(loss))
+    assert losses[-1] < losses[0]
+    for n, t in eng.iter_full_tensors("master"):
+        if ".lora_" not in n:
+            assert torch.equal(t, base_before[n]), n
+    save_lora_checkpoint(eng, str(tmp_path / "peft"), "tiny")
+    from safetensors.torch import load_file
+    sd = load_file(str(tmp_path / "peft" / "adapter_model.safetensors"))
+    assert "base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight" in sd
+    assert "base_model.model.model.layers.1.mlp.down_proj.lora_B.weight" in sd
+    assert os.path.exists(tmp_path / "peft" / "adapter_config.json")
+    # merging keeps the function
+    x, y = ids[:, :-1], ids[:, 1:]
+    with torch.no_grad():
+        before = float(model(x, labels=y, grad_scale=1.0 / 128)["loss"])
+        assert merge_lora(model) == 4
+        after = float(model(x, labels=y, grad_scale=1.0 / 128)["loss"])
+    assert abs(before - after) < 1e-4
+
+
+def test_qlora_and_fp8_and_qarl_forward_backward():
+    from xorl_b200.adapters.fp8 import FP8Linear
+    from xorl_b200.adapters.qarl import fake_quant
+    from xorl_b200.adapters.qlora import inject_qlora
+    from xorl_b200.models.layers import Linear
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.zero import Zero3Engine
+    reset_parallel_state()
+    ps = init_parallel_state(device_type="cpu")
+    for fmt, group in (("nf4", 64), ("nvfp4", 16), ("block_fp8", 128)):
+        la = LoRAArguments(enable_lora=True, enable_qlora=True, lora_rank=4, quant_format=fmt,
+                           quant_group_size=group, lora_b_init_std=0.01,
+                           lora_target_modules=["q_proj", "down_proj"])
+        model = DecoderLM(preset("tiny-qwen3", tie_word_embeddings=False), device="meta")
+        assert len(inject_qlora(model, la)) == 4
+        eng = Zero3Engine(model, ps, compute_dtype=torch.float32, device=torch.device("cpu"))
+        opt = build_optimizer(eng, lr=1e-2, weight_decay=0.0)
+        ids = torch.randint(0, 1024, (2, 65))
+        losses = []
+        for _ in range(4):
+            opt.zero_grad()
+            losses.append(float(eng.forward_backward(ids[:, :-1], ids[:, 1:], grad_scale=1.0 / 128)))
+            eng.finish_grad_sync()
+            opt.step()
+        assert losses[-1] < losses[0], (fmt, losses)
+    # fp8 linear close to the exact one, gradients flow
+    torch.manual_seed(0)
+    base = Linear(256, 128, dtype=torch.float32)
+    torch.nn.init.normal_(base.weight, 0, 0.05)
+    f8 = FP8Linear(base)
+    x = torch.randn(16, 256, requires_grad=True)
+    y = f8(x)
+    ref = x @ base.weight.t()
+    assert (y - ref).norm() / ref.norm() < 0.06
+    y.sum().backward()
+    assert x.grad is not None and base.weight.grad is not None
+    w = torch.randn(32, 64, requires_grad=True)
+    fq = fake_quant(w, "nvfp4")
+    fq.sum().backward()
+    assert torch.allclose(w.grad, torch.ones_like(w))

@@ -1,0 +1,176 @@
+"""LoRA: low-rank adapters on linear layers, fused-projection aware, with PEFT-format export.
+
+``inject_lora`` wraps every targeted ``Linear`` so that ``y = x W^T + (alpha/r) (x A^T) B^T`` with the
+base weight frozen; only ``lora_A`` / ``lora_B`` are trainable and checkpointed.  Targets are given
+by HF-style names (``q_proj``, ``v_proj``, ``gate_proj`` ...): a name that is part of a fused
+projection (``qkv_proj``, ``gate_up_proj``) becomes a *delta* adapter restricted to that slice of
+the fused output, which is numerically the adapter of the unfused module
+(src/xorl/lora/modules/linear.py:23-273, src/xorl/lora/utils.py:465,1109).  ``merge_lora`` folds the
+update into the base weight (ReLoRA-style merges every ``merge_lora_interval`` steps).
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+from torch import nn
+
+from ..models.layers import Linear
+from ..ops import gemm as gemm_ops
+
+FUSED_PARTS = {"qkv_proj": ("q_proj", "k_proj", "v_proj"), "gate_up_proj": ("gate_proj", "up_proj")}
+DEFAULT_TARGETS = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+
+
+class LoraLinear(nn.Module):
+    """A frozen base ``Linear`` plus one low-rank adapter per output slice."""
+
+    def __init__(self, base: Linear, rank: int, alpha: float, slices: List[Tuple[str, int, int]],
+                 b_init_std: float = 0.0, seed: int = 0):
+        super().__init__()
+        self.in_features, self.out_features = base.in_features, base.out_features
+        self.weight = base.weight
+        self.bias = base.bias
+        self.weight.requires_grad_(False)
+        if self.bias is not None:
+            self.bias.requires_grad_(False)
+        self.rank, self.scaling = rank, alpha / rank
+        self.slices = slices                      # (hf name, start row, end row) of the fused output
+        dt, dev = base.weight.dtype, base.weight.device
+        self.lora_A = nn.ParameterDict()
+        self.lora_B = nn.ParameterDict()
+        for name, s, e in slices:
+            a = torch.empty(rank, self.in_features, dtype=dt, device=dev)
+            b = torch.empty(e - s, rank, dtype=dt, device=dev)
+            self.lora_A[name] = nn.Parameter(a)
+            self.lora_B[name] = nn.Parameter(b)
+            self.lora_A[name]._xb_lora = "A"
+            self.lora_B[name]._xb_lora = "B" if b_init_std == 0.0 else "B_random"
+        self.b_init_std = b_init_std
+
+    def forward(self, x):
+        y = gemm_ops.linear(x, self.weight, self.bias)
+        full = len(self.slices) == 1 and self.slices[0][1] == 0 and self.slices[0][2] == self.out_features
+        deltas = []
+        for name, s, e in self.slices:
+            d = gemm_ops.linear(gemm_ops.linear(x, self.lora_A[name]), self.lora_B[name]) * self.scaling
+            if full:
+                return y + d
+            deltas.append((s, e, d))
+        pieces, cur = [], 0
+        for s, e, d in sorted(deltas, key=lambda t: t[0]):
+            if s > cur:
+                pieces.append(y[..., cur:s])
+            pieces.append(y[..., s:e] + d)
+            cur = e
+        if cur < self.out_features:
+            pieces.append(y[..., cur:])
+        return torch.cat(pieces, dim=-1)
+
+    @torch.no_grad()
+    def merge(self) -> None:
+        for name, s, e in self.slices:
+            delta = (self.lora_B[name].float() @ self.lora_A[name].float()) * self.scaling
+            self.weight[s:e] += delta.to(self.weight.dtype)
+            self.lora_B[name].zero_()
+
+
+def _fused_slices(module_name: str, linear: Linear, parent, targets: Iterable[str]):
+    leaf = module_name.rsplit(".", 1)[-1]
+    if leaf in FUSED_PARTS:
+        parts = FUSED_PARTS[leaf]
+        if leaf == "qkv_proj":
+            sizes = [parent.Hq * parent.D, parent.Hkv * parent.D, parent.Hkv * parent.D]
+        else:
+            sizes = [linear.out_features // 2] * 2
+        out, off = [], 0
+        for p, n in zip(parts, sizes):
+            if p in targets:
+                out.append((p, off, off + n))
+            off += n
+        return out
+    if leaf in targets:
+        return [(leaf, 0, linear.out_features)]
+    return []
+
+
+def inject_lora(model: nn.Module, lora_args) -> List[str]:
+    """Replaces targeted linears by ``LoraLinear`` and freezes everything else.  Returns the names
+    of the wrapped modules."""
+    targets = tuple(lora_args.lora_target_modules or DEFAULT_TARGETS)
+    if "all-linear" in targets:
+        targets = DEFAULT_TARGETS
+    exclude = tuple(lora_args.exclude_modules or ())
+    wrapped = []
+    for pname, parent in list(model.named_modules()):
+        for cname, child in list(parent.named_children()):
+            full = f"{pname}.{cname}" if pname else cname
+            if not isinstance(child, Linear) or any(x in full for x in exclude) or cname == "lm_head":
+                continue
+            slices = _fused_slices(full, child, parent, targets)
+            if not slices:
+                continue
+            setattr(parent, cname, LoraLinear(child, lora_args.lora_rank, lora_args.lora_alpha, slices,
+                                              lora_args.lora_b_init_std, lora_args.lora_b_init_seed))
+            wrapped.append(full)
+    for n, p in model.named_parameters():
+        p.requires_grad_(("lora_A" in n) or ("lora_B" in n))
+    model._xb_lora_config = {"r": lora_args.lora_rank, "lora_alpha": lora_args.lora_alpha,
+                             "target_modules": list(targets)}
+    return wrapped
+
+
+def init_lora_parameter_(name: str, p: torch.Tensor, rank: int, seed: int = 0, b_std: float = 0.0) -> None:
+    """Kaiming-uniform A (as PEFT), zero (or N(0, b_std)) B."""
+    import zlib
+    g = torch.Generator().manual_seed((seed * 1000003 + zlib.crc32(name.encode())) % (2 ** 63 - 1))
+    if ".lora_A." in name:
+        bound = 1.0 / math.sqrt(p.shape[1])
+        p.copy_(((torch.rand(p.shape, generator=g) * 2 - 1) * bound * math.sqrt(3.0)).to(p.device))
+    elif b_std > 0:
+        p.copy_(torch.empty(p.shape).normal_(0, b_std, generator=g).to(p.device))
+    else:
+        p.zero_()
+
+
+def merge_lora(model: nn.Module) -> int:
+    n = 0
+    for m in model.modules():
+        if isinstance(m, LoraLinear):
+            m.merge()
+            n += 1
+    return n
+
+
+def lora_state_dict_peft(named_full_tensors: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """In-memory names (``...qkv_proj.lora_A.q_proj``) -> PEFT names
+    (``base_model.model.model...q_proj.lora_A.weight``)."""
+    out = {}
+    for name, t in named_full_tensors.items():
+        if ".lora_A." not in name and ".lora_B." not in name:
+            continue
+        mod, kind, part = name.rsplit(".", 2)
+        parent = mod.rsplit(".", 1)[0]
+        prefix = "base_model.model." + ("" if parent.startswith("lm_head") else "model.")
+        out[f"{prefix}{parent}.{part}.{kind}.weight"] = t
+    return out
+
+
+def save_lora_checkpoint(engine, out_dir: str, base_model_name: str = "") -> None:
+    """PEFT directory: ``adapter_model.safetensors`` + ``adapter_config.json``."""
+    from safetensors.torch import save_file
+    tensors = {n: t.detach().to(torch.bfloat16).cpu().contiguous()
+               for n, t in engine.iter_full_tensors("master") if ".lora_" in n}
+    if engine.ps.rank != 0:
+        return
+    os.makedirs(out_dir, exist_ok=True)
+    save_file(lora_state_dict_peft(tensors), os.path.join(out_dir, "adapter_model.safetensors"),
+              metadata={"format": "pt"})
+    cfg = dict(getattr(engine.model, "_xb_lora_config", {}))
+    cfg.update({"peft_type": "LORA", "task_type": "CAUSAL_LM", "base_model_name_or_path": base_model_name,
+                "bias": "none", "lora_dropout": 0.0, "inference_mode": True, "fan_in_fan_out": False})
+    with open(os.path.join(out_dir, "adapter_config.json"), "w") as f:
+        json.dump(cfg, f, indent=2)

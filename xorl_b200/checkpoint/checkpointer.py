@@ -85,19 +85,18 @@ class DistributedCheckpointer:
                 srcs.append((f"optimizer.state.{{fqn}}.{sname}", "extra", per_group))
         return srcs
 
-    def build_state_dict(self) -> Dict[str, Any]:
+    def build_state_dict(self, include_frozen: bool = True) -> Dict[str, Any]:
         sd: Dict[str, Any] = {}
         eng = self.engine
+        group_of = {name: g for g in eng.all_groups() for name, _ in g.named_params}
         for key_fmt, what, extra in self._state_sources():
-            groups = list(eng.all_groups())
-            gi = 0
-            it = eng.iter_full_tensors(what, extra)
-            for g in groups:
-                for (name, _), shape in zip(g.named_params, g.shapes):
-                    _, view = next(it)
-                    fqn = to_checkpoint_fqn(name)
-                    key = f"model.{fqn}" if key_fmt == "model" else key_fmt.format(fqn=fqn)
-                    sd[key] = self._wrap(g, shape, view.float() if what != "master" else view)
+            for name, view in eng.iter_full_tensors(what, extra):
+                g = group_of[name]
+                if getattr(g, "frozen", False) and not include_frozen:
+                    continue
+                fqn = to_checkpoint_fqn(name)
+                key = f"model.{fqn}" if key_fmt == "model" else key_fmt.format(fqn=fqn)
+                sd[key] = self._wrap(g, view.shape, view.float() if what != "master" else view)
         return sd
 
     # ---- save -----------------------------------------------------------------------------------

@@ -182,6 +182,10 @@ def init_parameter_(name: str, p: torch.Tensor, std: float, seed: int, index: in
                     zero_centered_norm: bool = False) -> None:
     if p.is_meta:
         return
+    if ".lora_A." in name or ".lora_B." in name:
+        from ..adapters.lora import init_lora_parameter_
+        init_lora_parameter_(name, p, 0, seed)
+        return
     leaf = name.rsplit(".", 1)[-1]
     if p.dim() == 1:
         if leaf == "bias" or "bias" in leaf:

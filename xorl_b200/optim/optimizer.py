@@ -80,7 +80,7 @@ class ShardedOptimizer:
 
     def _new_state(self, name: str, dtype=torch.float32) -> Dict[int, torch.Tensor]:
         d = {id(g): torch.zeros(g.shard_numel, device=self.engine.device, dtype=dtype)
-             for g in self.engine.all_groups()}
+             for g in self.engine.all_groups() if not getattr(g, "frozen", False)}
         self.state[name] = d
         return d
 

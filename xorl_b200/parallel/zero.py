@@ -182,7 +182,7 @@ class Zero3Engine:
                     newp._xb_shape = tuple(p.shape)
                     newp._xb_init = None if p.is_meta else p.detach()
                     for attr in ("_xb_expert", "_xb_tp", "_xb_no_decay", "_xb_full_shape",
-                                 "_xb_tp_slice", "_xb_tp_reduce"):
+                                 "_xb_tp_slice", "_xb_tp_reduce", "_xb_materialize", "_xb_lora"):
                         if hasattr(p, attr):
                             setattr(newp, attr, getattr(p, attr))
                     mapping[id(p)] = newp
@@ -202,13 +202,17 @@ class Zero3Engine:
             unit = ZeroUnit(uname, mods)
             dense: List[Tuple[str, nn.Parameter]] = []
             expert: List[Tuple[str, nn.Parameter]] = []
+            frozen: List[Tuple[str, nn.Parameter]] = []
             for m in mods:
                 for p in m.parameters():
                     if id(p) in seen or not p.requires_grad and False:
                         continue
                     seen.add(id(p))
-                    (expert if getattr(p, "_xb_expert", False) else dense).append((fqn_of[id(p)], p))
-            for kind, plist in (("dense", dense), ("expert", expert)):
+                    if not p.requires_grad:
+                        frozen.append((fqn_of[id(p)], p))
+                    else:
+                        (expert if getattr(p, "_xb_expert", False) else dense).append((fqn_of[id(p)], p))
+            for kind, plist in (("dense", dense), ("expert", expert), ("frozen", frozen)):
                 if not plist:
                     continue
                 if kind == "expert" and self.ps.ep_size > 1:
@@ -219,6 +223,7 @@ class Zero3Engine:
                                        self.shard_rank, self.device, self.compute_dtype,
                                        self.rep_pg, self.rep_world)
                 g.is_expert = kind == "expert"
+                g.frozen = kind == "frozen"
                 self._materialize_group(g, std, seed, index_of, zc, init_parameter_)
                 unit.groups.append(g)
             self.units.append(unit)
@@ -234,6 +239,9 @@ class Zero3Engine:
     def _materialize_group(self, g: FlatParamGroup, std, seed, index_of, zc, init_fn) -> None:
         """Builds the unit's full fp32 image once (initialising meta parameters in place), keeps
         this rank's slice as master weights and drops the rest."""
+        if getattr(g, "frozen", False):
+            self._materialize_frozen(g, std, seed, index_of, zc, init_fn)
+            return
         full32 = torch.zeros(g.padded, device=self.device, dtype=torch.float32)
         for (name, p), view in zip(g.named_params, g.param_views(full32)):
             init = getattr(p, "_xb_init", None)
@@ -254,6 +262,39 @@ class Zero3Engine:
         g.shard_lp = g.master if self.compute_dtype == torch.float32 else g.master.to(self.compute_dtype)
         g.grad_shard = torch.zeros(g.shard_numel, device=self.device, dtype=torch.float32)
         del full32
+        if g.world == 1:
+            g.full = g.shard_lp
+            g.full_persistent = True
+            g.attach_params()
+
+    def _materialize_frozen(self, g: FlatParamGroup, std, seed, index_of, zc, init_fn) -> None:
+        """Frozen parameters (LoRA / QLoRA bases) keep only the compute-dtype shard: no master copy,
+        no gradient accumulator, no optimizer state.  A parameter may bring its own
+        ``_xb_materialize(shape, device)`` producing the exact bits to store (packed quantised data
+        reinterpreted in the compute dtype)."""
+        full = torch.zeros(g.padded, device=self.device, dtype=self.compute_dtype)
+        for (name, p), view in zip(g.named_params, g.param_views(full)):
+            mat = getattr(p, "_xb_materialize", None)
+            init = getattr(p, "_xb_init", None)
+            if mat is not None:
+                view.copy_(mat(view.shape, self.device, name, seed))
+            elif init is not None:
+                view.copy_(init.to(device=self.device, dtype=self.compute_dtype))
+                p._xb_init = None
+            else:
+                tmp = torch.empty(view.shape, device=self.device, dtype=torch.float32)
+                tp_slice = getattr(p, "_xb_tp_slice", None)
+                if tp_slice is not None:
+                    fullp = torch.empty(p._xb_full_shape, device=self.device, dtype=torch.float32)
+                    init_fn(name, fullp, std, seed, index_of[name], zc)
+                    tmp.copy_(tp_slice(fullp))
+                else:
+                    init_fn(name, tmp, std, seed, index_of[name], zc)
+                view.copy_(tmp)
+        s0, s1 = g.shard_range()
+        g.master = None
+        g.shard_lp = full[s0:s1].clone()
+        g.grad_shard = None
         if g.world == 1:
             g.full = g.shard_lp
             g.full_persistent = True
@@ -319,6 +360,8 @@ class Zero3Engine:
     # ---------------------------------------------------------------------------------------
     def _prepare_grad_buffers(self, unit: ZeroUnit) -> None:
         for g in unit.groups:
+            if getattr(g, "frozen", False):
+                continue
             if g.world == 1:
                 # single owner: kernels write (or accumulate) straight into the fp32 accumulator
                 g.grad_full = g.grad_shard
@@ -332,6 +375,8 @@ class Zero3Engine:
 
     def _reduce_unit_grads(self, unit: ZeroUnit, collected: bool = False) -> None:
         for g in unit.groups:
+            if getattr(g, "frozen", False):
+                continue
             if not collected:
                 g.collect_grads()
             accumulate = g.grad_ready
@@ -376,6 +421,8 @@ class Zero3Engine:
         for unit in self.units:
             for g in unit.groups:
                 g.reduce_event = None
+                if g.grad_shard is None:
+                    continue
                 if g.replicate_pg is not None and g.replicate_world > 1:
                     dist.all_reduce(g.grad_shard, group=g.replicate_pg)
                 if self.sp_sync_pg is not None and not getattr(g, "is_expert", False):
@@ -489,6 +536,8 @@ class Zero3Engine:
         gradients that will be produced later (zero-bubble schedules)."""
         rec = []
         for g in unit.groups:
+            if getattr(g, "frozen", False):
+                continue
             g.collect_grads()
             rec.append((g, g.grad_full))
             g.grad_full = None
@@ -634,7 +683,9 @@ class Zero3Engine:
         (optimizer moments).  Every rank of the shard group must iterate in lock-step."""
         for g in self.all_groups():
             if what == "master":
-                shard = g.master
+                shard = g.master if g.master is not None else g.shard_lp
+            elif getattr(g, "frozen", False):
+                continue
             elif what == "grad":
                 shard = g.grad_shard
             else:
@@ -659,7 +710,9 @@ class Zero3Engine:
         """Copies full tensors (by FQN) into this rank's shards.  Returns the missing names."""
         missing = []
         for g in self.all_groups():
-            dst = g.master if target == "master" else extra[id(g)]
+            if target != "master" and getattr(g, "frozen", False):
+                continue
+            dst = (g.master if g.master is not None else g.shard_lp) if target == "master" else extra[id(g)]
             s0, _ = g.shard_range()
             for i, a, b in g.param_segments_in_shard():
                 name = g.named_params[i][0]
@@ -680,7 +733,7 @@ class Zero3Engine:
         return sorted(set(missing))
 
     def refresh_compute_copy(self, g: FlatParamGroup) -> None:
-        if g.shard_lp is not g.master:
+        if g.master is not None and g.shard_lp is not g.master:
             g.shard_lp.copy_(g.master)
 
     def num_local_elements(self) -> int:

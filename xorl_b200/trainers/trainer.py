@@ -248,7 +248,40 @@ class Trainer:
         if self.ps.world_size > 1 and self.ps.group(self.ps.loss_group_name) is not None:
             dist.all_reduce(total, group=self.ps.group(self.ps.loss_group_name))
         self.global_step += 1
+        la = self.args.lora
+        if la.enable_lora and la.merge_lora_interval and self.global_step % la.merge_lora_interval == 0:
+            self.maybe_merge_lora()
         return {"loss": total, "grad_norm": norm, "lr": self.optimizer.lr, "tokens": global_tokens}
+
+    def maybe_merge_lora(self) -> None:
+        """ReLoRA-style merge: fold the adapters into the (gathered) base weights, write the shards
+        back, restart B at zero and optionally reset the optimizer moments
+        (src/xorl/trainers/training_utils.py:346-372)."""
+        from ..adapters.lora import LoraLinear
+        eng = self.engine
+        with torch.no_grad():
+            for unit in eng.units:
+                eng.gather(unit)
+                eng.wait_gather(unit)
+                touched = False
+                for mod in unit.modules:
+                    for m in mod.modules():
+                        if isinstance(m, LoraLinear) and hasattr(m, "weight"):
+                            m.merge()
+                            touched = True
+                if touched:
+                    for g in unit.groups:
+                        s0, s1 = g.shard_range()
+                        if g.full is not g.shard_lp:
+                            g.shard_lp.copy_(g.full[s0:s1])
+                        if g.master is not None:
+                            g.master.copy_(g.shard_lp)
+                if eng.reshard:
+                    eng.release(unit)
+        if self.args.lora.reset_optimizer_on_merge:
+            for st in self.optimizer.state.values():
+                for v in st.values():
+                    v.zero_()
 
     def _extra_loss_fn(self):
         return None
@@ -313,9 +346,13 @@ class Trainer:
                   "metrics": self.metrics_history[-1] if self.metrics_history else {}}
         if t.save_hf_weights and self.global_step > 0 and t.save_steps >= 0 and \
                 os.environ.get("XORL_SKIP_FINAL_EXPORT", "0") != "1":
-            from ..checkpoint.hf_io import save_hf_weights
             out_dir = os.path.join(t.output_dir, f"global_step_{self.global_step}", "hf_ckpt")
-            save_hf_weights(self.engine, out_dir, self.model_config)
+            if self.args.lora.enable_lora:
+                from ..adapters.lora import save_lora_checkpoint
+                save_lora_checkpoint(self.engine, out_dir, self.args.model.model_path or "")
+            else:
+                from ..checkpoint.hf_io import save_hf_weights
+                save_hf_weights(self.engine, out_dir, self.model_config)
         if self.ps.rank == 0:
             with open(os.path.join(t.output_dir, "training_metrics.json"), "w") as f:
                 json.dump(result, f, indent=2, default=float)
