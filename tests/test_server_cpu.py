@@ -1,0 +1,308 @@
+"""Training service on CPU: REST contract with the dummy backend (ordering, failure injection,
+sessions, auth), a real tiny model behind the same routes, weight sync transports, the ZMQ remote
+backend and the sparse-delta codec."""
+import os
+import sys
+import threading
+import time
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from fastapi.testclient import TestClient  # noqa: E402
+
+from xorl_b200.server.api_server import ServerState, create_app  # noqa: E402
+from xorl_b200.server.backend import DummyBackend, LocalBackend  # noqa: E402
+from xorl_b200.server.future_store import FutureStore  # noqa: E402
+from xorl_b200.server.orchestrator import (Orchestrator, OrchestratorRequest, RequestProcessor,  # noqa: E402
+                                           SeqIdAwareFIFOPolicy)
+from xorl_b200.server import packing  # noqa: E402
+
+
+def _datum(n, start=1):
+    toks = list(range(start, start + n))
+    return {"model_input": {"tokens": toks},
+            "loss_fn_inputs": {"target_tokens": {"data": toks[1:] + [-100], "dtype": "int64"}}}
+
+
+def _poll(client, rid, timeout=30.0):
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        r = client.post("/api/v1/retrieve_future", json={"request_id": rid}).json()
+        if r.get("type") != "try_again":
+            return r
+        time.sleep(0.01)
+    raise AssertionError("future never resolved")
+
+
+def test_future_store_ttl_and_abort():
+    fs = FutureStore(ttl_seconds=10)
+    a, b = fs.create("x"), fs.create("y")
+    fs.set_result(a, {"ok": 1})
+    assert fs.get(a)["state"] == "done" and fs.pending() == 1
+    assert fs.abort(b) and not fs.abort(b)
+    fs.set_result(b, 1)                       # late result of an aborted request is dropped
+    assert fs.get(b)["state"] == "failed"
+    assert fs.cleanup(now=time.time() + 100) == 2 and fs.get(a) is None
+
+
+def test_packing_and_dp_balance():
+    lengths = [100, 900, 500, 300, 700, 50]
+    for fn in (packing.pack_sequential, packing.pack_best_fit):
+        bins = fn(lengths, 1000)
+        assert sorted(i for b in bins for i in b) == list(range(6))
+        assert all(sum(lengths[i] for i in b) <= 1000 for b in bins)
+    assert len(packing.pack_best_fit(lengths, 1000)) <= len(packing.pack_sequential(lengths, 1000))
+    plan = packing.balance_across_dp(packing.pack_best_fit(lengths, 1000), lengths, 2)
+    assert len(plan) == 2 and len(plan[0]) == len(plan[1])      # equal micro-batch counts per rank
+    mb = packing.datums_to_micro_batch([{"tokens": [5, 6, 7], "target_tokens": [6, 7, -100]},
+                                        {"tokens": [1, 2], "weights": [1.0, 0.0]}], pad_to=8)
+    assert mb["input_ids"].numel() == 8 and mb["cu_seqlens"].tolist() == [0, 3, 5, 8]
+    assert mb["num_valid_tokens"] == 3 and mb["position_ids"][:5].tolist() == [0, 1, 2, 0, 1]
+
+
+def test_seq_id_policy_reorders():
+    p = SeqIdAwareFIFOPolicy(max_wait=60)
+    for s in (2, 0, 1):
+        p.push(OrchestratorRequest(request_id=str(s), op="x", seq_id=s))
+    assert [p.pop().seq_id for _ in range(3)] == [0, 1, 2]
+    p.push(OrchestratorRequest(request_id="late", op="x", seq_id=5))
+    assert p.pop() is None                                     # seq 3, 4 not seen yet
+    p.push(OrchestratorRequest(request_id="n", op="x"))
+    assert p.pop().request_id == "n"                           # un-numbered requests never wait
+
+
+def test_orchestrator_failure_injection():
+    done = {}
+    be = DummyBackend(failure_rate=1.0)
+    o = Orchestrator(be, on_result=lambda rid, res, err: done.__setitem__(rid, (res, err)))
+    o.start()
+    o.submit(OrchestratorRequest(request_id="a", op="optim_step"))
+    t0 = time.time()
+    while "a" not in done and time.time() - t0 < 5:
+        time.sleep(0.01)
+    o.stop()
+    assert done["a"][0] is None and "injected failure" in done["a"][1]
+
+
+def test_rest_contract_dummy_backend(tmp_path):
+    be = DummyBackend(processing_delay=0.05)
+    st = ServerState(be, str(tmp_path), packing_len=64, api_keys=["k1"], session_timeout=0.5)
+    with TestClient(create_app(st)) as c:
+        assert c.get("/health").json()["status"] == "ok"
+        assert c.post("/api/v1/optim_step", json={}).status_code == 401
+        c.headers["x-api-key"] = "k1"
+        # out-of-order seq ids are executed in order (both queue up behind a busy backend)
+        c.post("/api/v1/abort_gradient_epoch", json={})
+        c.post("/api/v1/save_weights", json={})
+        r2 = c.post("/api/v1/optim_step", json={"seq_id": 1}).json()
+        r1 = c.post("/api/v1/forward_backward", json={"seq_id": 0, "forward_backward_input":
+                                                      {"data": [_datum(10), _datum(7)]}}).json()
+        out1, out2 = _poll(c, r1["request_id"]), _poll(c, r2["request_id"])
+        assert be.calls[-2:] == ["forward_backward", "optim_step"]
+        assert out1["type"] == "forward_backward" and len(out1["loss_fn_outputs"]) == 2
+        assert out1["loss_fn_outputs"][0]["logprobs"]["shape"] == [10]
+        assert out2["type"] == "optim_step" and out2["metrics"]["step"] == 1.0
+        # a datum longer than the packing length fails as a user error
+        bad = c.post("/api/v1/forward_backward", json={"forward_backward_input": {"data": [_datum(100)]}}).json()
+        res = _poll(c, bad["request_id"])
+        assert res["type"] == "request_failed" and res["category"] == "user"
+        assert c.post("/api/v1/forward_backward", json={"forward_backward_input": {"data": []}}).status_code == 422
+        assert c.post("/api/v1/retrieve_future", json={"request_id": "nope"}).status_code == 404
+        assert c.post("/api/v1/optim_step", json={"model_id": "ghost"}).status_code == 404
+        # sessions own models and release them on expiry
+        sid = c.post("/api/v1/create_session", json={"tags": ["t"]}).json()["session_id"]
+        mid = c.post("/api/v1/create_model", json={"session_id": sid, "lora_config": {"rank": 4}}).json()["model_id"]
+        assert c.post("/api/v1/session_heartbeat", json={"session_id": sid}).json()["ok"]
+        assert any(r["training_run_id"] == mid for r in c.get("/api/v1/training_runs").json()["training_runs"])
+        time.sleep(0.6)
+        assert c.get("/api/v1/session_info").json()["sessions"] == []
+        assert c.post("/api/v1/optim_step", json={"model_id": mid}).status_code == 404
+        # inference endpoints and sleep / wake
+        c.post("/add_inference_endpoint", json={"url": "http://e1:30000", "world_size": 2})
+        assert c.get("/list_inference_endpoints").json()["endpoints"][0]["world_size"] == 2
+        assert c.post("/api/v1/create_sampling_session", json={}).json()["endpoint"] == "http://e1:30000"
+        assert c.post("/remove_inference_endpoint", json={"url": "http://e1:30000"}).status_code == 200
+        assert c.post("/api/v1/set_sync_quantization", json={"format": "fp8"}).json()["format"] == "fp8"
+        assert c.post("/sleep").json()["asleep"] and c.get("/health").json()["asleep"]
+        assert not c.post("/wake_up").json()["asleep"]
+
+
+def test_rest_failures_surface_as_request_failed(tmp_path):
+    st = ServerState(DummyBackend(failure_rate=1.0), str(tmp_path))
+    with TestClient(create_app(st)) as c:
+        rid = c.post("/api/v1/optim_step", json={}).json()["request_id"]
+        out = _poll(c, rid)
+        assert out["type"] == "request_failed" and out["category"] == "server"
+        assert c.get("/health").json()["pending"] == 0
+
+
+@pytest.fixture()
+def tiny_runner(tmp_path):
+    from xorl_b200.parallel.state import reset_parallel_state
+    from xorl_b200.server.runner import ModelRunner
+    from xorl_b200.server.server_arguments import ServerArguments
+    from xorl_b200.trainers.trainer import Trainer
+    reset_parallel_state()
+    sa = ServerArguments(model_preset="tiny-qwen3", output_dir=str(tmp_path / "srv"), device="cpu",
+                         sample_packing_sequence_len=256, enable_mixed_precision=False)
+    runner = ModelRunner(Trainer(sa.to_trainer_arguments()))
+    yield runner
+    reset_parallel_state()
+
+
+def test_local_backend_trains_and_restores(tmp_path, tiny_runner):
+    st = ServerState(LocalBackend(tiny_runner), tiny_runner.output_dir, packing_len=256)
+    data = [_datum(40, 3), _datum(25, 50), _datum(60, 7)]
+    with TestClient(create_app(st)) as c:
+        def fb(kind="forward_backward", key="forward_backward_input", loss_fn="cross_entropy", d=data, cfg=None):
+            rid = c.post(f"/api/v1/{kind}", json={key: {"data": d, "loss_fn": loss_fn,
+                                                        "loss_fn_config": cfg or {}}}).json()["request_id"]
+            return _poll(c, rid, 120)
+        losses = []
+        for step in range(4):
+            out = fb()
+            assert out["type"] == "forward_backward", out
+            losses.append(out["metrics"]["loss:sum"])
+            o = _poll(c, c.post("/api/v1/optim_step", json={"adam_params": {"learning_rate": 5e-3},
+                                                            "gradient_clip": 1.0}).json()["request_id"], 120)
+            assert o["metrics"]["step"] == step + 1 and o["metrics"]["grad_norm"] > 0
+        assert losses[-1] < losses[0]
+        lp0 = out["loss_fn_outputs"][0]["logprobs"]["data"]
+        assert len(lp0) == 40 and all(v <= 0 for v in lp0[:-1])
+        # forward-only log-probs agree with what the next forward_backward reports
+        f = fb("forward", "forward_input")
+        saved = _poll(c, c.post("/api/v1/save_weights", json={"path": "ckpt_a"}).json()["request_id"], 120)
+        assert saved["path"] == "xorl://default/weights/ckpt_a"
+        assert [x["name"] for x in c.get("/api/v1/list_checkpoints").json()["checkpoints"]] == ["ckpt_a"]
+        out5 = fb()
+        a = f["loss_fn_outputs"][1]["logprobs"]["data"]
+        b = out5["loss_fn_outputs"][1]["logprobs"]["data"]
+        assert max(abs(x - y) for x, y in zip(a, b)) < 1e-4
+        _poll(c, c.post("/api/v1/optim_step", json={"adam_params": {"learning_rate": 5e-3}}).json()["request_id"], 120)
+        moved = fb("forward", "forward_input")["loss_fn_outputs"][1]["logprobs"]["data"]
+        assert max(abs(x - y) for x, y in zip(a, moved)) > 1e-4
+        # restoring the checkpoint restores the log-probs
+        r = _poll(c, c.post("/api/v1/load_weights", json={"path": "xorl://default/weights/ckpt_a"}).json()["request_id"], 120)
+        assert r["type"] == "load_weights", r
+        back = fb("forward", "forward_input")["loss_fn_outputs"][1]["logprobs"]["data"]
+        assert max(abs(x - y) for x, y in zip(a, back)) < 1e-5
+        # a policy-gradient loss through the same route
+        rl = [dict(d) for d in data]
+        for d in rl:
+            n = len(d["model_input"]["tokens"])
+            d["loss_fn_inputs"] = dict(d["loss_fn_inputs"], logprobs={"data": [-2.0] * n, "dtype": "float32"},
+                                       advantages={"data": [0.5] * n, "dtype": "float32"})
+        o = fb(loss_fn="importance_sampling", d=rl)
+        assert o["type"] == "forward_backward", o
+        # an optim_step with nothing accumulated is refused; bad token ids are a user error
+        _poll(c, c.post("/api/v1/abort_gradient_epoch", json={}).json()["request_id"])
+        e = _poll(c, c.post("/api/v1/optim_step", json={}).json()["request_id"])
+        assert e["type"] == "request_failed"
+        badd = {"model_input": {"tokens": [1, 10 ** 7]}, "loss_fn_inputs": {}}
+        e = fb(d=[badd])
+        assert e["type"] == "request_failed" and e["category"] == "user"
+        assert c.post("/api/v1/delete_checkpoint", json={"name": "ckpt_a"}).json()["deleted"] == "ckpt_a"
+
+
+def test_weight_sync_transports(tmp_path, tiny_runner):
+    from safetensors.torch import load_file
+    from xorl_b200.server import weight_sync as ws
+    h = ws.WeightSyncHandler(tiny_runner)
+    out = h.sync(backend="file", directory=str(tmp_path / "w"), bucket_size_mb=1)
+    assert out["synced"] and out["buckets"] >= 1 and os.path.exists(out["index"])
+    got = {}
+    for f in sorted(os.listdir(tmp_path / "w")):
+        if f.endswith(".safetensors"):
+            got.update(load_file(str(tmp_path / "w" / f)))
+    assert "model.layers.0.self_attn.q_proj.weight" in got and "model.layers.0.mlp.up_proj.weight" in got
+    assert not any("qkv_proj" in k or "gate_up_proj" in k for k in got)
+    # sparse delta: first generation full, the second only carries what one step changed
+    d1 = h.sync(backend="sparse_delta", directory=str(tmp_path / "d"))
+    weights = ws.apply_delta_generation(str(tmp_path / "d" / "gen-000001"), {})
+    tiny_runner.forward_backward("default", [{"tokens": list(range(1, 30))}], None)
+    tiny_runner.optim_step("default", adam_params={"learning_rate": 1e-5})
+    d2 = h.sync(backend="sparse_delta", directory=str(tmp_path / "d"))
+    assert d2["delta_stats"]["bytes"] < d1["delta_stats"]["bytes"]
+    ws.apply_delta_generation(str(tmp_path / "d" / "gen-000002"), weights)
+    ref = dict(ws.iter_sync_tensors(tiny_runner.engine, tiny_runner.model.config))
+    for k, v in ref.items():
+        assert torch.equal(weights[k], v.cpu()), k
+    # bucket flattening round trip and the peer-copy transport on host memory
+    bucket = [("a", torch.randn(3, 5).bfloat16()), ("b", torch.arange(7, dtype=torch.uint8))]
+    flat, man = ws.flatten_bucket(bucket)
+    back = ws.unflatten_bucket(flat, man)
+    assert torch.equal(back["a"], bucket[0][1]) and torch.equal(back["b"], bucket[1][1])
+    dst = torch.zeros(flat.numel(), dtype=torch.uint8)
+    ws.PeerCopyTransport(dst.data_ptr(), dst.numel()).send_bucket(bucket)
+    assert torch.equal(dst, flat)
+    # fp8 sync quantisation emits scale companions for 128-aligned matrices only
+    q = ws._quantise("x.q_proj.weight", torch.randn(128, 256), "fp8")
+    assert [n for n, _ in q] == ["x.q_proj.weight", "x.q_proj.weight_scale_inv"] and q[0][1].dtype == torch.uint8
+
+
+def test_endpoint_manager_and_broadcast_group(tmp_path):
+    from xorl_b200.server import weight_sync as ws
+    calls = []
+    em = ws.EndpointManager(post=lambda url, p: calls.append((url, p)) or {}, get=lambda url: {"ok": True})
+    em.add("http://a:1/", 2)
+    em.add("http://b:1", 1)
+    assert em.total_world() == 3 and em.check_health() == {"http://a:1": True, "http://b:1": True}
+    em.broadcast_post("/init_weights_update_group", lambda e, off: {"rank_offset": off})
+    assert [p["rank_offset"] for _, p in calls] == [1, 3]
+    # a stateless 2-rank gloo group: trainer thread broadcasts a bucket, "engine" thread receives it
+    from dist_utils import free_port
+    port = free_port()
+    bucket = [("w", torch.randn(4, 8).bfloat16())]
+    flat, man = ws.flatten_bucket(bucket)
+    got = {}
+
+    def engine():
+        g = ws.StatelessGroupBroadcaster("127.0.0.1", port, 1, 2, "gloo")
+        got.update(g.recv_bucket(man, "cpu"))
+
+    t = threading.Thread(target=engine)
+    t.start()
+    g0 = ws.StatelessGroupBroadcaster("127.0.0.1", port, 0, 2, "gloo")
+    g0.send_bucket(bucket)
+    t.join(30)
+    assert torch.equal(got["w"], bucket[0][1])
+
+
+def test_remote_backend_over_zmq():
+    from xorl_b200.server.launcher import RemoteBackend, serve_zmq
+    from dist_utils import free_port
+    addr = f"tcp://127.0.0.1:{free_port()}"
+    stop = threading.Event()
+    be = DummyBackend()
+    t = threading.Thread(target=serve_zmq, args=(be, addr, stop), daemon=True)
+    t.start()
+    rb = RemoteBackend(addr, timeout_ms=5000)
+    out = rb.forward_backward("default", [{"tokens": [1, 2, 3]}], [[[0]]], "cross_entropy", {})
+    assert out["num_tokens"] == 3 and rb.optim_step("default")["metrics"]["step"] == 1.0
+    assert rb.health()["status"] == "ok"
+    with pytest.raises(RuntimeError):
+        rb._call("no_such_op", "default", {})
+    stop.set()
+    t.join(5)
+
+
+def test_delta_codec_edge_cases():
+    from xorl_b200.server.weight_sync import delta_apply, delta_encode
+    a = torch.zeros(1000, dtype=torch.bfloat16)
+    assert delta_apply(a.clone(), delta_encode(a, a)) == 0
+    b = torch.ones(1000, dtype=torch.bfloat16)
+    c = a.clone()
+    assert delta_apply(c, delta_encode(a, b)) == 1000 and torch.equal(c, b)
+    with pytest.raises(ValueError):
+        delta_apply(torch.zeros(10, dtype=torch.bfloat16), delta_encode(a, b))
+
+
+@pytest.mark.distributed
+def test_dispatcher_two_ranks_agree_on_errors(tmp_path):
+    from dist_utils import run_distributed
+    out = run_distributed(os.path.join(os.path.dirname(__file__), "server_dispatch_worker.py"), 2, str(tmp_path))
+    assert "DISPATCH_OK" in out

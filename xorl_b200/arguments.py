@@ -481,6 +481,12 @@ def parse_args(rootclass=Arguments, argv: Optional[List[str]] = None):
         sec, name = key.split(".", 1)
         cli.setdefault(sec, {})[name] = val
 
+    return build_args(file_cfg, cli, rootclass)
+
+
+def build_args(file_cfg: Dict[str, Any], cli: Optional[Dict[str, Dict[str, Any]]] = None, rootclass=Arguments):
+    """Arguments from a nested ``{section: {key: value}}`` mapping (plus optional overrides)."""
+    cli = cli or {}
     sections = {f.name: f.default_factory for f in fields(rootclass)}
     unknown = [s for s in list(file_cfg) + list(cli) if s not in sections]
     if unknown:

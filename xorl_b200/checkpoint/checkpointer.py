@@ -100,8 +100,9 @@ class DistributedCheckpointer:
         return sd
 
     # ---- save -----------------------------------------------------------------------------------
-    def save(self, global_step: int, extra_state: Optional[Dict[str, Any]] = None) -> str:
-        path = os.path.join(self.dir, f"global_step_{global_step}")
+    def save(self, global_step: int, extra_state: Optional[Dict[str, Any]] = None,
+             path: Optional[str] = None) -> str:
+        path = path or os.path.join(self.dir, f"global_step_{global_step}")
         rank = self.engine.ps.rank
         os.makedirs(os.path.join(path, "extra_state"), exist_ok=True)
         t0 = time.time()

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(CE_THREADS)
 ce_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
           float* __restrict__ loss, float* __restrict__ lse_out, float* __restrict__ stats, int V,
           long long ignore_index, float grad_scale, int write_grad, int mode,
-          long long vocab_start, float z_loss_coef) {
+          long long vocab_start, float z_loss_coef, const float* __restrict__ row_scale) {
   __shared__ float sm[32], ss[32];
   const long long row = blockIdx.x;
   __nv_bfloat16* lr = logits + row * ld;
@@ -105,7 +105,7 @@ ce_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long* __r
   }
   if (!write_grad) return;
   __syncthreads();  // the target logit has been read
-  const float gs = ignored ? 0.f : grad_scale;
+  const float gs = ignored ? 0.f : grad_scale * (row_scale ? row_scale[row] : 1.f);
   const float zfac = 1.f + 2.f * z_loss_coef * lse;  // d(lse + z*lse^2)/d(lse)
   for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
     const uint4 a = reinterpret_cast<const uint4*>(lr)[v];
@@ -157,7 +157,7 @@ XB_API int xb_cross_entropy(void* logits, long long ld, const long long* targets
   if (ld % 8 || (reinterpret_cast<uintptr_t>(logits) % 16)) return -1;
   ce_kernel<<<rows, CE_THREADS, 0, (cudaStream_t)stream>>>(
       (__nv_bfloat16*)logits, ld, targets, loss, lse, nullptr, V, ignore_index, grad_scale,
-      write_grad, 0, 0, z_loss_coef);
+      write_grad, 0, 0, z_loss_coef, nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -169,7 +169,7 @@ XB_API int xb_cross_entropy_vp_stats(void* logits, long long ld, const long long
   if (ld % 8 || (reinterpret_cast<uintptr_t>(logits) % 16)) return -1;
   ce_kernel<<<rows, CE_THREADS, 0, (cudaStream_t)stream>>>(
       (__nv_bfloat16*)logits, ld, targets, nullptr, nullptr, stats, V_local, ignore_index, 0.f, 0,
-      1, vocab_start, 0.f);
+      1, vocab_start, 0.f, nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -179,5 +179,19 @@ XB_API int xb_cross_entropy_vp_grad(void* logits, long long ld, const long long*
   if (rows <= 0) return 0;
   ce_vp_grad_kernel<<<rows, CE_THREADS, 0, (cudaStream_t)stream>>>(
       (__nv_bfloat16*)logits, ld, targets, lse, V_local, ignore_index, grad_scale, vocab_start);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// As xb_cross_entropy with a per-row gradient weight: the gradient of row r is multiplied by
+// grad_scale * row_scale[r].  Used for losses that are functions of per-token log-probabilities.
+XB_API int xb_cross_entropy_rows(void* logits, long long ld, const long long* targets, float* loss,
+                                 float* lse, const float* row_scale, int rows, int V,
+                                 long long ignore_index, float grad_scale, int write_grad,
+                                 void* stream) {
+  if (rows <= 0) return 0;
+  if (ld % 8 || (reinterpret_cast<uintptr_t>(logits) % 16)) return -1;
+  ce_kernel<<<rows, CE_THREADS, 0, (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)logits, ld, targets, loss, lse, nullptr, V, ignore_index, grad_scale,
+      write_grad, 0, 0, 0.f, row_scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "xb_embedding_bwd": [P, P, P, I, I, I, L, P],
     "xb_add_bf16": [P, P, P, L, P],
     "xb_cross_entropy": [P, L, P, P, P, I, I, L, F, I, F, P],
+    "xb_cross_entropy_rows": [P, L, P, P, P, P, I, I, L, F, I, P],
     "xb_cross_entropy_vp_stats": [P, L, P, P, I, I, L, L, P],
     "xb_cross_entropy_vp_grad": [P, L, P, P, I, I, L, L, F, P],
     "xb_adamw": [P, P, P, P, P, L, F, F, F, F, F, I, F, P, P],

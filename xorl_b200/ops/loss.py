@@ -132,3 +132,94 @@ def fused_linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, label
         tls.append(tl.detach())
     loss = total * grad_scale
     return (loss, torch.cat(tls)) if return_token_losses else loss
+
+
+# --------------------------------------------------------------------------------------------
+# losses that are functions of per-token log-probabilities (RL, distillation)
+# --------------------------------------------------------------------------------------------
+def fused_linear_token_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                            loss_fn, grad_scale: float = 1.0, chunk_tokens: int = 1024,
+                            ignore_index: int = IGNORE_INDEX):
+    """``loss_fn(logprobs [T], mask [T]) -> (scalar, metrics)`` evaluated on the log-probabilities of
+    the label tokens, without materialising the logits: pass 1 computes the log-probs chunk by
+    chunk, the loss function runs on that small vector, pass 2 recomputes each logits chunk and
+    back-propagates d(loss)/d(logprob) through the lm-head.  Returns (grad_scale * loss, logprobs,
+    metrics); the hidden-state and lm-head gradients are produced like in
+    ``fused_linear_cross_entropy`` (back-propagate the returned scalar with gradient 1)."""
+    global _launches
+    h2 = hidden.reshape(-1, hidden.shape[-1])
+    lab = labels.reshape(-1)
+    mask = (lab != ignore_index).float()
+    if not (h2.is_cuda and h2.dtype == torch.bfloat16):
+        lps = []
+        for s in range(0, h2.shape[0], chunk_tokens):
+            logits = F.linear(h2[s:s + chunk_tokens], weight).float()
+            lps.append(-F.cross_entropy(logits, lab[s:s + chunk_tokens], ignore_index=ignore_index,
+                                        reduction="none"))
+        lp = torch.cat(lps)
+        loss, metrics = loss_fn(lp, mask)
+        return loss * grad_scale, lp.detach(), metrics
+    T, H = h2.shape
+    V = weight.shape[0]
+    ldv = (V + 7) // 8 * 8
+    buf = torch.empty((min(chunk_tokens, T), ldv), device=h2.device, dtype=torch.bfloat16)
+    lp = torch.empty(T, device=h2.device, dtype=torch.float32)
+    with torch.no_grad():
+        for s in range(0, T, chunk_tokens):
+            e = min(T, s + chunk_tokens)
+            logits = buf[: e - s, :V]
+            gemm(h2[s:e], weight, out=logits)
+            l, _ = ce_chunk_(logits, lab[s:e], 0.0, False, ignore_index)
+            lp[s:e] = -l
+    lp_leaf = lp.clone().requires_grad_()
+    loss, metrics = loss_fn(lp_leaf, mask)
+    (coef,) = torch.autograd.grad(loss, lp_leaf)
+    return _TokenLossBackward.apply(h2, weight, lab, (-coef).contiguous(), float(grad_scale),
+                                    int(chunk_tokens), int(ignore_index), loss.detach()), lp, metrics
+
+
+class _TokenLossBackward(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, row_scale, grad_scale, chunk_tokens, ignore_index, loss_value):
+        global _launches
+        T, H = hidden.shape
+        V = weight.shape[0]
+        need_dh, need_dw = hidden.requires_grad, weight.requires_grad
+        dh = torch.empty_like(hidden) if need_dh else None
+        tgt, fresh = grad_target(weight) if need_dw else (None, False)
+        dw_local = torch.zeros((V, H), device=hidden.device, dtype=torch.float32) \
+            if (need_dw and tgt is None) else None
+        ldv = (V + 7) // 8 * 8
+        buf = torch.empty((min(chunk_tokens, T), ldv), device=hidden.device, dtype=torch.bfloat16)
+        lib = _lib.cuda_lib()
+        scratch = torch.empty(min(chunk_tokens, T), device=hidden.device, dtype=torch.float32)
+        first = True
+        for s in range(0, T, chunk_tokens):
+            e = min(T, s + chunk_tokens)
+            logits = buf[: e - s, :V]
+            gemm(hidden[s:e], weight, out=logits)
+            _lib.check(lib.xb_cross_entropy_rows(logits.data_ptr(), logits.stride(0),
+                                                 labels[s:e].data_ptr(), scratch.data_ptr(), None,
+                                                 row_scale[s:e].data_ptr(), e - s, V, ignore_index,
+                                                 grad_scale, 1, _lib.stream_ptr()),
+                       "xb_cross_entropy_rows")
+            _launches += 1
+            if need_dh:
+                gemm(logits, weight, b_mn=True, out=dh[s:e])
+            if need_dw:
+                if tgt is not None:
+                    gemm(logits, hidden[s:e], a_mn=True, b_mn=True, out=tgt, accumulate=not (fresh and first))
+                else:
+                    gemm(logits, hidden[s:e], a_mn=True, b_mn=True, out=dw_local, accumulate=True)
+            first = False
+        if need_dw and tgt is not None:
+            mark_written(weight)
+        ctx.dh, ctx.dw_local, ctx.weight = dh, dw_local, weight
+        return loss_value * grad_scale
+
+    @staticmethod
+    def backward(ctx, g):
+        dh = ctx.dh * g.to(ctx.dh.dtype) if ctx.dh is not None else None
+        dw = deliver_param_grad(ctx.weight, ctx.dw_local * g) if ctx.dw_local is not None else None
+        ctx.dh = ctx.dw_local = None
+        return dh, dw, None, None, None, None, None, None

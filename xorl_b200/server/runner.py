@@ -1,0 +1,295 @@
+"""Per-rank worker of the training service.
+
+``ModelRunner`` owns the same ZeRO engine / optimizer as the CLI trainer and exposes the service
+operations: ``forward_backward`` (accumulates un-normalised gradients and the number of valid
+tokens of the current gradient epoch), ``optim_step`` (scales by 1/accumulated tokens, clips, steps
+with the client's Adam parameters), ``forward`` (log-probs only), ``save_weights`` /
+``load_weights``, ``sync_inference_weights``, ``sleep`` / ``wake_up`` and ``abort_gradient_epoch``
+(src/xorl/server/runner/model_runner.py:8084-9113).  ``RunnerDispatcher`` is the rank-0 bridge for
+multi-rank fleets: rank 0 broadcasts every command over a gloo group, all ranks execute it, and
+errors are agreed on with an all-reduce before anybody continues
+(src/xorl/server/runner/runner_dispatcher.py:257-395).
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import rl_losses
+from ..ops.loss import fused_linear_token_loss
+from .packing import datums_to_micro_batch
+
+IGNORE_INDEX = -100
+
+
+def validate_token_ids(datums: List[Dict[str, Any]], vocab_size: int) -> None:
+    """Reject ids outside the vocabulary on the host, before they reach an embedding lookup
+    (src/xorl/server/runner/utils/validation.py)."""
+    for i, d in enumerate(datums):
+        for key in ("tokens", "target_tokens"):
+            for t in d.get(key, []):
+                if t != IGNORE_INDEX and not (0 <= int(t) < vocab_size):
+                    raise ValueError(f"datum {i}: {key} contains id {t} outside [0, {vocab_size})")
+
+
+class ModelRunner:
+    def __init__(self, trainer):
+        self.trainer = trainer
+        self.engine = trainer.engine
+        self.optimizer = trainer.optimizer
+        self.model = trainer.model
+        self.device = trainer.device
+        self.ps = trainer.ps
+        self.accumulated_tokens = 0
+        self.epoch_open = False
+        self.step = 0
+        self.asleep = False
+        self.poisoned: Optional[str] = None
+        self.output_dir = trainer.args.train.output_dir
+
+    # ---- helpers --------------------------------------------------------------------------------
+    def _local_batches(self, datums, plan) -> List[Dict[str, Any]]:
+        bins = plan[self.ps.dp_rank] if plan else [list(range(len(datums)))]
+        out = []
+        for b in bins:
+            ds = []
+            for i in b:
+                d = dict(datums[i])
+                d["datum_index"] = i
+                ds.append(d)
+            out.append(datums_to_micro_batch(ds, pad_to=128))
+        return out
+
+    def _loss_closure(self, loss_fn: str, cfg: Dict[str, Any], mb: Dict[str, Any]):
+        fn = rl_losses.LOSS_REGISTRY.get(loss_fn)
+        if fn is None:
+            raise ValueError(f"unknown loss_fn {loss_fn!r}; choose from {sorted(rl_losses.LOSS_REGISTRY)}")
+        extras = {k: v.to(self.device) for k, v in mb.items()
+                  if torch.is_tensor(v) and v.dtype == torch.float32}
+        if "logprobs" in extras and "old_logprobs" not in extras:
+            extras["old_logprobs"] = extras.pop("logprobs")
+        return lambda lp, mask: fn(lp, mask, **extras, **cfg)
+
+    def _check_usable(self) -> None:
+        if self.poisoned:
+            raise RuntimeError(f"runner is poisoned after a failed mutation: {self.poisoned}")
+        if self.asleep:
+            raise RuntimeError("runner is asleep; call wake_up first")
+
+    def preflight(self, op: str, args: Dict[str, Any]) -> None:
+        """Host-only checks that may fail on one rank and not on another.  They run, and their
+        outcome is agreed on by all ranks, before any rank enters the collectives of ``op``."""
+        if op in ("sleep", "wake_up", "abort_gradient_epoch"):
+            return
+        self._check_usable()
+        if op in ("forward_backward", "forward"):
+            validate_token_ids(args.get("datums", []), self.model.config.vocab_size)
+            if args.get("loss_fn", "cross_entropy") not in rl_losses.LOSS_REGISTRY:
+                raise ValueError(f"unknown loss_fn {args.get('loss_fn')!r}")
+        elif op == "optim_step" and not self.epoch_open:
+            raise RuntimeError("optim_step without a preceding forward_backward")
+        elif op == "load_weights":
+            if not os.path.isdir(self._weights_path(args.get("model_id", "default"), args["path"])):
+                raise ValueError(f"no saved weights at {args['path']}")
+
+    # ---- operations -------------------------------------------------------------------------------
+    def forward_backward(self, model_id, datums, plan, loss_fn="cross_entropy", loss_fn_config=None):
+        self._check_usable()
+        validate_token_ids(datums, self.model.config.vocab_size)
+        cfg = dict(loss_fn_config or {})
+        if not self.epoch_open:
+            self.optimizer.zero_grad()
+            self.epoch_open = True
+            self.accumulated_tokens = 0
+        logprobs: Dict[int, List[float]] = {}
+        total = 0.0
+        eng = self.engine
+        for mb in self._local_batches(datums, plan):
+            d = {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in mb.items()}
+            self.accumulated_tokens += mb["num_valid_tokens"]
+            closure = self._loss_closure(loss_fn, cfg, mb)
+            holder = {}
+
+            def head(h, res, labels, ctx, grad_scale, _c=closure, _h=holder):
+                hidden = self.model.forward_head(h, res, ctx)
+                loss, lp, metrics = fused_linear_token_loss(hidden, self.model.lm_head.weight, labels,
+                                                            _c, grad_scale, self.model.loss_chunk_tokens)
+                _h["lp"], _h["metrics"] = lp, metrics
+                return loss
+
+            orig = self.model.head_loss
+            self.model.head_loss = head
+            try:
+                loss = eng.forward_backward(d["input_ids"], d["labels"], position_ids=d["position_ids"],
+                                            cu_seqlens=d["cu_seqlens"], grad_scale=1.0)
+            finally:
+                self.model.head_loss = orig
+            total += float(loss)
+            lp = holder["lp"].float().cpu()
+            for idx, (s, e) in zip(mb["datum_index"], mb["datum_spans"]):
+                logprobs[idx] = lp[s:e].tolist()
+        if self.ps.world_size > 1 and self.ps.group("dp") is not None:
+            t = torch.tensor([total, float(self.accumulated_tokens)], device=self.device)
+            dist.all_reduce(t, group=self.ps.group("dp"))
+            total = float(t[0])
+        return {"loss": total, "num_tokens": sum(len(d["tokens"]) for d in datums),
+                "logprobs": [logprobs.get(i, []) for i in range(len(datums))],
+                "metrics": {"loss:sum": total}}
+
+    @torch.no_grad()
+    def forward(self, model_id, datums, plan, loss_fn="cross_entropy", loss_fn_config=None):
+        self._check_usable()
+        validate_token_ids(datums, self.model.config.vocab_size)
+        logprobs: Dict[int, List[float]] = {}
+        for mb in self._local_batches(datums, plan):
+            d = {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in mb.items()}
+            hidden = self.engine.forward_only(d["input_ids"], position_ids=d["position_ids"],
+                                              cu_seqlens=d["cu_seqlens"])
+            root, _ = self.engine._units_by_role()
+            self.engine.gather(root)
+            self.engine.wait_gather(root)
+            _, lp, _ = fused_linear_token_loss(hidden, self.model.lm_head.weight, d["labels"],
+                                               lambda lp, mask: (lp.sum() * 0, {}), 1.0)
+            lp = lp.float().cpu()
+            for idx, (s, e) in zip(mb["datum_index"], mb["datum_spans"]):
+                logprobs[idx] = lp[s:e].tolist()
+        return {"logprobs": [logprobs.get(i, []) for i in range(len(datums))], "metrics": {}}
+
+    def optim_step(self, model_id, adam_params=None, gradient_clip=None, **_):
+        self._check_usable()
+        if not self.epoch_open:
+            raise RuntimeError("optim_step without a preceding forward_backward")
+        ap = adam_params or {}
+        tokens = self.accumulated_tokens
+        if self.ps.world_size > 1 and self.ps.group("dp_sp") is not None:
+            t = torch.tensor([float(tokens)], device=self.device)
+            dist.all_reduce(t, group=self.ps.group("dp_sp"))
+            tokens = int(t.item())
+        self.engine.finish_grad_sync()
+        scale = 1.0 / max(1, tokens)
+        opt = self.optimizer
+        opt.set_lr(float(ap.get("learning_rate", opt.lr)))
+        if hasattr(opt, "betas"):
+            opt.betas = (float(ap.get("beta1", opt.betas[0])), float(ap.get("beta2", opt.betas[1])))
+            opt.eps = float(ap.get("eps", opt.eps))
+        norm, coef = self.engine.grad_norm_and_clip_coef(0.0)
+        norm_scaled = norm * scale
+        clip = float(gradient_clip) if gradient_clip else 0.0
+        if clip > 0:
+            coef = torch.clamp(clip / (norm_scaled + 1e-6), max=1.0)
+        opt.step(clip_coef=coef if clip > 0 else None, grad_scale=scale)
+        self.epoch_open = False
+        self.step += 1
+        return {"metrics": {"grad_norm": float(norm_scaled), "step": float(self.step),
+                            "learning_rate": opt.lr, "tokens": float(tokens)}}
+
+    def abort_gradient_epoch(self, model_id="default"):
+        self.optimizer.zero_grad()
+        self.epoch_open = False
+        self.accumulated_tokens = 0
+        return {"aborted": True}
+
+    def _weights_path(self, model_id: str, path: str) -> str:
+        if path.startswith("xorl://"):
+            mid, kind, name = path[len("xorl://"):].split("/", 2)
+            return os.path.join(self.output_dir, kind, mid, name)
+        if os.path.isabs(path) or os.sep in path:
+            return path
+        return os.path.join(self.output_dir, "weights", model_id, path)
+
+    def save_weights(self, model_id, path=None, **_):
+        name = path or f"step_{self.step:06d}"
+        out = self._weights_path(model_id, name)
+        self.trainer.checkpointer.save(self.step, {"global_step": self.step, "runner_step": self.step}, path=out)
+        self.trainer.checkpointer.wait()
+        uri = name if name.startswith("xorl://") or os.sep in name else f"xorl://{model_id}/weights/{name}"
+        return {"path": uri, "directory": out}
+
+    def load_weights(self, model_id, path, load_optimizer=True, **_):
+        p = self._weights_path(model_id, path)
+        if not os.path.isdir(p):
+            raise ValueError(f"no saved weights at {path}")
+        try:
+            extra = self.trainer.checkpointer.load(p, load_optimizer=load_optimizer)
+        except Exception as e:  # noqa: BLE001
+            # shards may be half overwritten: refuse further work instead of training on them
+            self.poisoned = f"load_weights({path}) failed midway: {e}"
+            raise
+        self.step = int((extra or {}).get("runner_step", self.step))
+        self.abort_gradient_epoch(model_id)
+        return {"path": path}
+
+    def sync_inference_weights(self, model_id, **kw):
+        from .weight_sync import WeightSyncHandler
+        handler = getattr(self, "_sync", None) or WeightSyncHandler(self)
+        self._sync = handler
+        return handler.sync(**kw)
+
+    def sleep(self):
+        """Release device memory that can be rebuilt (buffer pools) and refuse work until woken."""
+        self.engine._full_pool.clear()
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+        self.asleep = True
+        return {"asleep": True}
+
+    def wake_up(self):
+        self.asleep = False
+        return {"asleep": False}
+
+
+class RunnerDispatcher:
+    """Rank 0 receives commands and broadcasts them to all ranks over a gloo group; after every
+    command the ranks agree on success (all-reduce MAX of an error flag, then gather of messages)."""
+
+    def __init__(self, runner: ModelRunner, cpu_group=None):
+        self.runner = runner
+        self.cpu_group = cpu_group
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+
+    def execute(self, command: Optional[Dict[str, Any]]) -> Dict[str, Any]:
+        """Called on every rank; only rank 0 passes a command."""
+        box = [command]
+        if self.world > 1:
+            dist.broadcast_object_list(box, src=0, group=self.cpu_group)
+        cmd = box[0]
+        if cmd is None or cmd.get("op") == "shutdown":
+            return {"shutdown": True}
+        op, args = cmd["op"], cmd.get("args", {})
+        err = None
+        try:
+            self.runner.preflight(op, args)
+        except Exception as e:  # noqa: BLE001
+            err = f"rank {self.rank}: {type(e).__name__}: {e}"
+        out = self._sync_error_state(err, None)
+        if "error" in out:
+            return out
+        err, result = None, None
+        try:
+            fn = getattr(self.runner, op)
+            result = fn(**args) if op in ("sleep", "wake_up") else fn(cmd.get("model_id", "default"), **args)
+        except Exception as e:  # noqa: BLE001
+            err = f"rank {self.rank}: {type(e).__name__}: {e}"
+        return self._sync_error_state(err, result)
+
+    def _sync_error_state(self, err: Optional[str], result):
+        if self.world > 1:
+            flag = torch.tensor([1 if err else 0])
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.cpu_group)
+            if int(flag.item()):
+                msgs: List[Optional[str]] = [None] * self.world
+                dist.all_gather_object(msgs, err, group=self.cpu_group)
+                return {"error": "; ".join(m for m in msgs if m)}
+            return {"result": result}
+        return {"error": err} if err else {"result": result}
+
+    def worker_loop(self) -> None:
+        while True:
+            out = self.execute(None)
+            if out.get("shutdown"):
+                return

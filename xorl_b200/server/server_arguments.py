@@ -1,0 +1,99 @@
+"""Flat configuration of the training service and its translation into the trainer's sectioned
+arguments (src/xorl/server/server_arguments.py).  One YAML level: model, parallelism, optimizer
+family, packing and service knobs side by side."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field, fields
+from typing import Any, Dict, List, Optional
+
+import yaml
+
+from ..arguments import Arguments, build_args
+
+
+@dataclass
+class ServerArguments:
+    # model
+    model_path: Optional[str] = None
+    config_path: Optional[str] = None
+    model_preset: Optional[str] = None
+    attn_implementation: str = "native"
+    moe_implementation: str = "native"
+    # parallelism
+    data_parallel_mode: str = "fsdp2"
+    data_parallel_shard_size: int = -1
+    data_parallel_replicate_size: int = 1
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    ulysses_parallel_size: int = 1
+    ringattn_parallel_size: int = 1
+    expert_parallel_size: int = 1
+    # training
+    optimizer: str = "adamw"
+    weight_decay: float = 0.0
+    enable_mixed_precision: bool = True
+    enable_gradient_checkpointing: bool = True
+    seed: int = 42
+    output_dir: str = "outputs/server"
+    device: str = "auto"
+    comm_backend: str = "auto"
+    # adapters
+    enable_lora: bool = False
+    lora_rank: int = 16
+    lora_alpha: int = 32
+    lora_target_modules: Optional[List[str]] = None
+    enable_qlora: bool = False
+    quant_format: str = "nvfp4"
+    max_adapters_per_model: int = 8
+    # service
+    api_host: str = "127.0.0.1"
+    api_port: int = 8000
+    sample_packing_sequence_len: int = 4096
+    sample_packing_method: str = "sequential"
+    future_ttl_seconds: float = 3600.0
+    session_timeout_seconds: float = 600.0
+    idle_sleep_seconds: float = 0.0
+    api_keys: List[str] = field(default_factory=list)
+    worker_bind_address: str = "tcp://127.0.0.1:5555"
+    sync_bucket_size_mb: int = 1024
+
+    @classmethod
+    def from_yaml(cls, path: str, overrides: Optional[Dict[str, Any]] = None) -> "ServerArguments":
+        with open(path) as f:
+            raw = yaml.safe_load(f) or {}
+        raw.update(overrides or {})
+        known = {f.name for f in fields(cls)}
+        unknown = sorted(set(raw) - known)
+        if unknown:
+            raise ValueError(f"unknown server config keys: {unknown}")
+        return cls(**raw)
+
+    def to_trainer_arguments(self) -> Arguments:
+        """Sectioned arguments for the in-process trainer the runner is built on."""
+        d = {
+            "model": {"model_path": self.model_path, "config_path": self.config_path,
+                      "attn_implementation": self.attn_implementation,
+                      "moe_implementation": self.moe_implementation},
+            "data": {"datasets": [{"type": "dummy", "path": "dummy"}],
+                     "sample_packing_sequence_len": self.sample_packing_sequence_len},
+            "train": {"output_dir": self.output_dir, "optimizer": self.optimizer,
+                      "weight_decay": self.weight_decay, "seed": self.seed,
+                      "data_parallel_mode": self.data_parallel_mode,
+                      "data_parallel_shard_size": self.data_parallel_shard_size,
+                      "data_parallel_replicate_size": self.data_parallel_replicate_size,
+                      "tensor_parallel_size": self.tensor_parallel_size,
+                      "pipeline_parallel_size": self.pipeline_parallel_size,
+                      "ulysses_parallel_size": self.ulysses_parallel_size,
+                      "ringattn_parallel_size": self.ringattn_parallel_size,
+                      "expert_parallel_size": self.expert_parallel_size,
+                      "enable_mixed_precision": self.enable_mixed_precision,
+                      "enable_gradient_checkpointing": self.enable_gradient_checkpointing,
+                      "device": self.device, "comm_backend": self.comm_backend,
+                      "max_steps": 1, "lr_warmup_ratio": 0.0, "lr_decay_style": "constant"},
+            "lora": {"enable_lora": self.enable_lora, "lora_rank": self.lora_rank,
+                     "lora_alpha": self.lora_alpha, "lora_target_modules": self.lora_target_modules,
+                     "enable_qlora": self.enable_qlora, "quant_format": self.quant_format},
+        }
+        if self.model_preset and not (self.model_path or self.config_path):
+            d["model"]["config_path"] = self.model_preset
+        return build_args(d)
