@@ -38,7 +38,7 @@ def reference_curve(steps=10):
     return losses
 
 
-def engine_curve(steps=10, world=1, rank=0):
+def engine_curve(steps=10, world=1, rank=0, optimizer="adamw", lr=1e-4, fixed_batch=False):
     import torch.distributed as dist
     from xorl_b200.models.config import preset
     from xorl_b200.models.decoder import DecoderLM
@@ -48,10 +48,11 @@ def engine_curve(steps=10, world=1, rank=0):
     m = DecoderLM(preset("tiny-qwen3"), dtype=torch.float32, device="meta")
     eng = Zero3Engine(m, get_parallel_state(), compute_dtype=torch.float32,
                       device=torch.device("cpu"), seed=0)
-    opt = build_optimizer(eng, lr=1e-4, weight_decay=0.0, optimizer_type="adamw")
+    opt = build_optimizer(eng, lr=lr, weight_decay=0.0, optimizer_type=optimizer,
+                          optimizer_kwargs={"muon_lr": 0.01} if optimizer == "muon" else None)
     losses = []
     for s in range(steps):
-        x, y = _data(s)
+        x, y = _data(0 if fixed_batch else s)
         # each rank takes its slice of the global batch; normalisation is by the global count
         xs, ys = x[rank::world], y[rank::world]
         opt.zero_grad()
@@ -86,12 +87,45 @@ def test_fsdp2_two_gloo_ranks_match_single_process():
         assert abs(a - b) < 1e-5, (ref, got)
 
 
+def test_muon_single_process_descends_and_orthogonalises():
+    from xorl_b200.optim.muon import gram_newton_schulz, newton_schulz
+    from xorl_b200.parallel.state import init_parallel_state, reset_parallel_state
+    torch.manual_seed(0)
+    for shape in ((48, 160), (160, 48)):
+        G = torch.randn(shape)
+        X, Y = newton_schulz(G).float(), gram_newton_schulz(G).float()
+        sv = torch.linalg.svdvals(X)
+        assert sv.min() > 0.5 and sv.max() < 1.3                 # all singular values pushed towards 1
+        assert (X - Y).norm() / X.norm() < 0.06                  # Gram form is the same iteration
+    reset_parallel_state()
+    init_parallel_state(device_type="cpu")
+    got = engine_curve(8, optimizer="muon", lr=1e-3, fixed_batch=True)
+    assert got[-1] < got[0] - 0.05, got
+
+
+@pytest.mark.distributed
+def test_muon_two_gloo_ranks_match_single_process():
+    from dist_utils import run_distributed
+    from xorl_b200.parallel.state import init_parallel_state, reset_parallel_state
+    out = run_distributed(__file__, 2, "muon")
+    got = json.loads([l for l in out.splitlines() if l.startswith("LOSSES ")][-1][7:])
+    reset_parallel_state()
+    init_parallel_state(device_type="cpu")
+    ref = engine_curve(6, optimizer="muon", lr=1e-3, fixed_batch=True)
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 2e-3, (ref, got)                      # bf16 iteration, shard-independent
+
+
 if __name__ == "__main__":
     import torch.distributed as dist
     from xorl_b200.parallel.state import init_parallel_state
     dist.init_process_group("gloo")
     init_parallel_state(device_type="cpu", dp_mode="fsdp2")
-    curve = engine_curve(10, dist.get_world_size(), dist.get_rank())
+    if len(sys.argv) > 1 and sys.argv[1] == "muon":
+        curve = engine_curve(6, dist.get_world_size(), dist.get_rank(), optimizer="muon", lr=1e-3,
+                             fixed_batch=True)
+    else:
+        curve = engine_curve(10, dist.get_world_size(), dist.get_rank())
     if dist.get_rank() == 0:
         print("LOSSES " + json.dumps(curve))
     dist.destroy_process_group()
