@@ -1,0 +1,111 @@
+"""fp8 block-scaled GEMM and quantisation kernels, token-loss head and Muon GEMM path on a B200,
+each against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _need_cuda():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from xorl_b200.ops import _lib
+    _lib.cuda_lib()          # fail loudly if the native library is missing on a GPU box
+    yield
+    assert all(v == 0 for v in _lib.read_status()[:4]), _lib.read_status()
+
+
+@pytest.mark.parametrize("M,K", [(256, 512), (1000, 1024), (3, 128)])
+def test_quant_rows_matches_reference(M, K):
+    from xorl_b200.ops import fp8_gemm, quantize as Q
+    x = (torch.randn(M, K, device="cuda") * 3).bfloat16()
+    q, s = fp8_gemm.quantize_rows(x)
+    q_ref, s_ref = Q.block_fp8_quantize_1x128(x)
+    torch.testing.assert_close(s, s_ref, rtol=1e-6, atol=0)
+    # a value on a rounding boundary may fall either way: compare after dequantisation
+    d, d_ref = q.float() * s.repeat_interleave(128, 1), q_ref.float() * s_ref.repeat_interleave(128, 1)
+    assert (d - d_ref).abs().max() <= 0.07 * x.float().abs().max()
+    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-3
+    assert (d - x.float()).abs().max() <= 0.07 * x.float().abs().max()
+
+
+@pytest.mark.parametrize("N,K", [(256, 384), (300, 200)])
+def test_quant_blocks_roundtrip(N, K):
+    from xorl_b200.ops import fp8_gemm, quantize as Q
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    q, s = fp8_gemm.quantize_blocks(w)
+    q_ref, s_ref = Q.block_fp8_quantize_128x128(w)
+    torch.testing.assert_close(s, s_ref, rtol=1e-6, atol=0)
+    assert (q.view(torch.uint8) != q_ref.view(torch.uint8)).float().mean() < 1e-3
+    back = fp8_gemm.dequantize_blocks(q, s)
+    ref = Q.block_fp8_dequantize_128x128(q, s)
+    torch.testing.assert_close(back.float(), ref.float(), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 1024), (1000, 200, 512), (4096, 4096, 4096)])
+def test_block_fp8_gemm_matches_fp32_reference(M, N, K):
+    from xorl_b200.ops import fp8_gemm, quantize as Q
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    # give K blocks very different magnitudes so a wrong scale index cannot hide
+    a = a * (1 + torch.arange(K // 128, device="cuda").repeat_interleave(128)).bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16() * 0.05
+    aq, as_ = fp8_gemm.quantize_rows(a)
+    bq, bs = fp8_gemm.quantize_blocks(b)
+    out = fp8_gemm.block_fp8_gemm(aq, as_, bq, bs)
+    ref = Q.block_fp8_gemm_reference(aq, as_, bq, bs, out_dtype=torch.float32)
+    err = (out.float() - ref).abs().max() / ref.abs().max()
+    assert err < 1e-2, err                                    # bf16 output rounding only
+    dense = a.float() @ b.float().t()
+    assert (out.float() - dense).norm() / dense.norm() < 0.06  # fp8 quantisation noise
+
+
+def test_fp8_linear_training_step():
+    from xorl_b200.adapters.fp8 import _FP8LinearFn
+    x = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(384, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y = _FP8LinearFn.apply(x, w, True)
+    y.float().square().mean().backward()
+    ref = x.detach().float() @ w.detach().float().t()
+    assert (y.float() - ref).norm() / ref.norm() < 0.06
+    assert x.grad is not None and w.grad is not None and torch.isfinite(w.grad).all()
+
+
+def test_token_loss_head_matches_autograd():
+    from xorl_b200.ops import rl_losses
+    from xorl_b200.ops.loss import fused_linear_token_loss
+    torch.manual_seed(0)
+    T, H, V = 700, 256, 1000
+    h = (torch.randn(T, H, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(V, H, device="cuda") * 0.05).bfloat16().requires_grad_()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::7] = -100
+    old = torch.full((T,), -6.5, device="cuda")
+    adv = torch.randn(T, device="cuda")
+    fn = lambda lp, mask: rl_losses.importance_sampling(lp, mask, old_logprobs=old, advantages=adv)
+    loss, lp, _ = fused_linear_token_loss(h, w, labels, fn, 1.0, chunk_tokens=256)
+    loss.backward()
+    h32 = h.detach().float().requires_grad_()
+    w32 = w.detach().float().requires_grad_()
+    logits = h32 @ w32.t()
+    lp_ref = -torch.nn.functional.cross_entropy(logits, labels, ignore_index=-100, reduction="none")
+    loss_ref, _ = fn(lp_ref, (labels != -100).float())
+    loss_ref.backward()
+    torch.testing.assert_close(lp, lp_ref.detach(), rtol=2e-2, atol=3e-2)
+    assert abs(loss.item() - loss_ref.item()) < 2e-2 * max(1.0, abs(loss_ref.item()))
+    assert (h.grad.float() - h32.grad).norm() / h32.grad.norm() < 3e-2
+    assert (w.grad.float() - w32.grad).norm() / w32.grad.norm() < 3e-2
+
+
+def test_muon_newton_schulz_on_tcgen05_gemm():
+    from xorl_b200.optim.muon import gram_newton_schulz, newton_schulz
+    torch.manual_seed(0)
+    G = torch.randn(256, 1024, device="cuda")
+    X = newton_schulz(G).float()
+    Y = gram_newton_schulz(G).float()
+    Xc = newton_schulz(G.cpu()).float()
+    sv = torch.linalg.svdvals(X)
+    assert sv.min() > 0.5 and sv.max() < 1.3
+    assert (X.cpu() - Xc).norm() / Xc.norm() < 0.05
+    assert (X - Y).norm() / X.norm() < 0.06

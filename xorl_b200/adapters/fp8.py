@@ -27,9 +27,9 @@ class _FP8LinearFn(torch.autograd.Function):
             wp = torch.nn.functional.pad(w, (0, pad))
         else:
             x2p, wp = x2, w
-        aq, as_ = Q.block_fp8_quantize_1x128(x2p)
-        bq, bs = Q.block_fp8_quantize_128x128(wp)
         from ..ops import fp8_gemm
+        aq, as_ = fp8_gemm.quantize_rows(x2p)
+        bq, bs = fp8_gemm.quantize_blocks(wp)
         y = fp8_gemm.block_fp8_gemm(aq, as_, bq, bs, out_dtype=x.dtype)
         ctx.save_for_backward(x2, w)
         ctx.fp8_backward = fp8_backward

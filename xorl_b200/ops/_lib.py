@@ -60,6 +60,11 @@ _SIGNATURES = {
     "xb_ep_prepare_recv": [P, P, P, P, I, I, I, P],
     "xb_ep_push_rows": [P, L, P, P, P, P, I, I, I, P, L, P, P, I, I, I, I, I, P],
     "xb_peer_copy": [P, P, L, I, P],
+    "xb_block_fp8_gemm": [P, P, P, P, P, I, I, I, P],
+    "xb_block_fp8_gemm_ex": [P, P, P, P, P, I, I, I, L, L, L, L, L, P],
+    "xb_quant_fp8_rows": [P, L, P, L, P, L, I, I, P],
+    "xb_quant_fp8_blocks": [P, L, P, L, P, L, I, I, P],
+    "xb_dequant_fp8_blocks": [P, L, P, L, P, L, I, I, P],
     "xb_grouped_gemm_rows": [P, P, P, P, I, L, I, I, L, L, I, P],
     "xb_grouped_gemm_wgrad": [P, P, P, P, I, L, I, I, L, L, I, I, P],
     "xb_attn_fwd_ex": [P, P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, I, F, I, P],

@@ -1,0 +1,168 @@
+"""Micro-benchmarks of the native kernels against their library counterparts.
+
+    python -m xorl_b200.utils.kernel_bench gemm --m 4096 --n 6144 --k 4096
+    python -m xorl_b200.utils.kernel_bench fp8_gemm --m 4096 --n 4096 --k 4096
+    python -m xorl_b200.utils.kernel_bench attn --tokens 4096 --heads 32 --kv-heads 8
+    python -m xorl_b200.utils.kernel_bench adamw --numel 268435456
+    python -m xorl_b200.utils.kernel_bench rmsnorm --tokens 16384 --hidden 4096
+
+Timing: CUDA events on the launching stream around each run, ``--warmup`` untimed runs, the median
+of ``--iters`` runs, and a buffer larger than L2 written between runs.  ``--no-lib`` skips the
+library comparison (useful under a profiler, where only the native kernel is of interest).
+One JSON line per case on stdout.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from typing import Callable, Dict
+
+import torch
+
+
+def _time(fn: Callable[[], None], warmup: int, iters: int, flush: torch.Tensor) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(iters):
+        flush.add_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b))
+    return statistics.median(out)
+
+
+def bench_gemm(a) -> Dict:
+    from ..ops.gemm import gemm
+    A = torch.randn(a.k, a.m, device="cuda").bfloat16() if a.a_mn else torch.randn(a.m, a.k, device="cuda").bfloat16()
+    B = torch.randn(a.k, a.n, device="cuda").bfloat16() if a.b_mn else torch.randn(a.n, a.k, device="cuda").bfloat16()
+    C = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: gemm(A, B, a_mn=a.a_mn, b_mn=a.b_mn, out=C), a.warmup, a.iters, a.flush)
+    flops = 2.0 * a.m * a.n * a.k
+    r = {"kernel": "gemm_bf16", "m": a.m, "n": a.n, "k": a.k, "a_mn": a.a_mn, "b_mn": a.b_mn, "ms": ms,
+         "tflops": flops / ms / 1e9}
+    if not a.no_lib:
+        Am = A.t() if a.a_mn else A
+        Bm = B if a.b_mn else B.t()
+        ms2 = _time(lambda: torch.matmul(Am, Bm, out=C), a.warmup, a.iters, a.flush)
+        r.update(lib_ms=ms2, lib_tflops=flops / ms2 / 1e9, ratio=ms2 / ms)
+    return r
+
+
+def bench_fp8_gemm(a) -> Dict:
+    from ..ops import fp8_gemm
+    A = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    B = torch.randn(a.n, a.k, device="cuda").bfloat16()
+    aq, as_ = fp8_gemm.quantize_rows(A)
+    bq, bs = fp8_gemm.quantize_blocks(B)
+    ms = _time(lambda: fp8_gemm.block_fp8_gemm(aq, as_, bq, bs), a.warmup, a.iters, a.flush)
+    msq = _time(lambda: fp8_gemm.quantize_rows(A), a.warmup, a.iters, a.flush)
+    flops = 2.0 * a.m * a.n * a.k
+    r = {"kernel": "block_fp8_gemm", "m": a.m, "n": a.n, "k": a.k, "ms": ms, "tflops": flops / ms / 1e9,
+         "quant_rows_ms": msq, "quant_rows_gbs": (a.m * a.k * 3 + a.m * a.k / 32) / msq / 1e6}
+    if not a.no_lib:
+        C = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+        ms2 = _time(lambda: torch.matmul(A, B.t(), out=C), a.warmup, a.iters, a.flush)
+        r.update(lib_bf16_ms=ms2, lib_bf16_tflops=flops / ms2 / 1e9)
+    return r
+
+
+def bench_attn(a) -> Dict:
+    from ..ops.attention import flash_attn_varlen
+    T, Hq, Hkv, D = a.tokens, a.heads, a.kv_heads, 128
+    q = torch.randn(T, Hq, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(T, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(T, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    lens = [a.doc_len] * (T // a.doc_len) if a.doc_len else [T]
+    if sum(lens) < T:
+        lens.append(T - sum(lens))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    do = torch.randn(T, Hq, D, device="cuda").bfloat16()
+    fl = sum(2.0 * 2 * L * L * Hq * D / 2 for L in lens)           # causal: half of QK^T and PV
+    holder = {}
+
+    def fwd():
+        holder["o"] = flash_attn_varlen(q, k, v, cu, causal=True)
+
+    ms_f = _time(fwd, a.warmup, a.iters, a.flush)
+
+    def bwd():
+        holder["o"].backward(do, retain_graph=True)
+
+    fwd()
+    ms_b = _time(bwd, a.warmup, a.iters, a.flush)
+    r = {"kernel": "flash_attn", "tokens": T, "heads": Hq, "kv_heads": Hkv, "docs": len(lens), "fwd_ms": ms_f,
+         "fwd_tflops": fl / ms_f / 1e9, "bwd_ms": ms_b, "bwd_tflops": 2.5 * fl / ms_b / 1e9}
+    if not a.no_lib:
+        try:
+            from flash_attn import flash_attn_varlen_func
+            qq, kk, vv = (t.detach().clone().requires_grad_() for t in (q, k, v))
+
+            def lf():
+                holder["lo"] = flash_attn_varlen_func(qq, kk, vv, cu, cu, max(lens), max(lens), causal=True)
+
+            ms_lf = _time(lf, a.warmup, a.iters, a.flush)
+            lf()
+            ms_lb = _time(lambda: holder["lo"].backward(do, retain_graph=True), a.warmup, a.iters, a.flush)
+            r.update(lib="flash_attn2", lib_fwd_ms=ms_lf, lib_bwd_ms=ms_lb)
+        except Exception as e:  # noqa: BLE001
+            r["lib_error"] = str(e)[:100]
+    return r
+
+
+def bench_adamw(a) -> Dict:
+    from ..ops import optim as optim_ops
+    n = a.numel
+    w = torch.randn(n, device="cuda")
+    m, v, g = torch.zeros_like(w), torch.zeros_like(w), torch.randn(n, device="cuda")
+    lp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: optim_ops.adamw_step_(w, m, v, g, lp, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8,
+                                             weight_decay=0.01, step=3, grad_scale=1.0, clip_coef=None),
+               a.warmup, a.iters, a.flush)
+    nbytes = n * (4 * 4 + 3 * 4 + 2)          # read w,m,v,g; write w,m,v and the bf16 copy
+    return {"kernel": "adamw", "numel": n, "ms": ms, "gbs": nbytes / ms / 1e6}
+
+
+def bench_rmsnorm(a) -> Dict:
+    from ..ops.norm import rmsnorm
+    x = torch.randn(a.tokens, a.hidden, device="cuda").bfloat16()
+    w = torch.ones(a.hidden, device="cuda").bfloat16()
+    ms = _time(lambda: rmsnorm(x, w, 1e-6), a.warmup, a.iters, a.flush)
+    return {"kernel": "rmsnorm_fwd", "tokens": a.tokens, "hidden": a.hidden, "ms": ms,
+            "gbs": a.tokens * a.hidden * 4 / ms / 1e6}
+
+
+BENCHES = {"gemm": bench_gemm, "fp8_gemm": bench_fp8_gemm, "attn": bench_attn, "adamw": bench_adamw,
+           "rmsnorm": bench_rmsnorm}
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=sorted(BENCHES))
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--a-mn", action="store_true")
+    ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--doc-len", type=int, default=0)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--numel", type=int, default=1 << 28)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-lib", action="store_true")
+    a = ap.parse_args(argv)
+    a.flush = torch.zeros(256 << 20, device="cuda", dtype=torch.uint8)
+    print(json.dumps(BENCHES[a.kernel](a)))
+
+
+if __name__ == "__main__":
+    main()
