@@ -11,10 +11,20 @@ def _ref(a, b, a_mn, b_mn):
     return A @ B.t()
 
 
+@pytest.fixture(params=["single", "pair", "pair2"])
+def variant(request):
+    from xorl_b200.ops import gemm
+    prev = gemm.set_variant(request.param)
+    yield request.param
+    gemm.set_variant(prev)
+    from xorl_b200.ops import _lib
+    assert all(v == 0 for v in _lib.read_status()[:4])
+
+
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (4096, 6144, 4096), (304, 200, 136),
-                                   (1000, 1256, 520), (72, 88, 40)])
-def test_gemm_layouts(M, N, K, a_mn, b_mn):
+                                   (1000, 1256, 520), (72, 88, 40), (2048, 152064, 512)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn, variant):
     from xorl_b200.ops import gemm
     torch.manual_seed(0)
     dev = "cuda"
@@ -28,7 +38,7 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     assert err <= 1e-2 * scale + 1e-2, (err, scale)
 
 
-def test_gemm_fp32_out_and_accumulate():
+def test_gemm_fp32_out_and_accumulate(variant):
     from xorl_b200.ops import gemm
     torch.manual_seed(1)
     a = torch.randn(512, 384, device="cuda", dtype=torch.bfloat16)

@@ -8,12 +8,25 @@ src/xorl/models/transformers/qwen3/modeling_qwen3.py:40-81).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
 from .grad_sink import current_wgrad_store, grad_target, mark_written
 
 _launches = 0
+# "pair2" / "pair": CTA-pair kernels (tcgen05 cta_group::2, csrc/gemm2.cu) with 512x256 / 256x256 pair
+# tiles; "single": one CTA per 128x256 tile (csrc/gemm.cu)
+_VARIANT = os.environ.get("XORL_B200_GEMM", "single")
+
+
+def set_variant(name: str) -> str:
+    """Selects the dense GEMM kernel ("pair" or "single"); returns the previous choice."""
+    global _VARIANT
+    assert name in ("pair2", "pair", "single")
+    prev, _VARIANT = _VARIANT, name
+    return prev
 
 
 def launch_count() -> int:
@@ -60,10 +73,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         assert not accumulate
     assert out.shape == (M, N) and out.stride(1) == 1
     assert out.dtype in (torch.bfloat16, torch.float32)
-    rc = _lib.cuda_lib().xb_gemm_bf16(
-        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
-        out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate),
-        _lib.stream_ptr())
+    lib = _lib.cuda_lib()
+    args = (a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+            out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate))
+    if _VARIANT != "single" and M > 128:
+        msub = 2 if (_VARIANT == "pair2" and M >= 512) else 1
+        rc = lib.xb_gemm_bf16_pair(*args, msub, _lib.stream_ptr())
+    else:
+        rc = lib.xb_gemm_bf16(*args, _lib.stream_ptr())
     _lib.check(rc, "xb_gemm_bf16")
     _launches += 1
     return out

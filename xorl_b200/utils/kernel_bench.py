@@ -39,13 +39,15 @@ def _time(fn: Callable[[], None], warmup: int, iters: int, flush: torch.Tensor) 
 
 
 def bench_gemm(a) -> Dict:
+    from ..ops import gemm as gemm_mod
     from ..ops.gemm import gemm
+    gemm_mod.set_variant(a.variant)
     A = torch.randn(a.k, a.m, device="cuda").bfloat16() if a.a_mn else torch.randn(a.m, a.k, device="cuda").bfloat16()
     B = torch.randn(a.k, a.n, device="cuda").bfloat16() if a.b_mn else torch.randn(a.n, a.k, device="cuda").bfloat16()
     C = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
     ms = _time(lambda: gemm(A, B, a_mn=a.a_mn, b_mn=a.b_mn, out=C), a.warmup, a.iters, a.flush)
     flops = 2.0 * a.m * a.n * a.k
-    r = {"kernel": "gemm_bf16", "m": a.m, "n": a.n, "k": a.k, "a_mn": a.a_mn, "b_mn": a.b_mn, "ms": ms,
+    r = {"kernel": "gemm_bf16", "variant": a.variant, "m": a.m, "n": a.n, "k": a.k, "a_mn": a.a_mn, "b_mn": a.b_mn, "ms": ms,
          "tflops": flops / ms / 1e9}
     if not a.no_lib:
         Am = A.t() if a.a_mn else A
@@ -148,6 +150,7 @@ def main(argv=None) -> None:
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--variant", choices=["single", "pair", "pair2"], default="single")
     ap.add_argument("--a-mn", action="store_true")
     ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--tokens", type=int, default=4096)
