@@ -1,45 +1,40 @@
 // Dense bf16 GEMM on CTA pairs (tcgen05 cta_group::2): C[M,N] (+)= op(A)[M,K] * op(B)[N,K]^T.
 //
-// Two CTAs of a cluster share one 256x256 output tile.  Each loads its own 128 rows of A and its
-// own 128 columns of B (TMA, 128B swizzle, no multicast), so a CTA moves 32 KB per 64-deep K block
-// instead of 48 KB, the shared-memory ring has 6 stages instead of 4, and every B element is read
-// from L2 once per pair.  The leader CTA's MMA thread issues tcgen05.mma.cta_group::2 (M = 256
-// across the pair, N = 256); each CTA's tensor memory receives the accumulator rows of its half
-// and each CTA's epilogue warps write them out.
+// Two CTAs of a cluster share one 512 x 256 output tile.  Each CTA loads two 128-row sub-tiles of
+// A and its own 128 columns of B per 64-deep K block (TMA, 128B swizzle, no multicast); the leader
+// CTA's MMA thread issues tcgen05.mma.cta_group::2 (M = 256 across the pair, N = 256) once per A
+// sub-tile, so every B stage feeds two MMAs.  Compared with one CTA per 128 x 256 tile this moves
+// half the operand bytes per flop through L2 and shared memory, and a 4-stage ring of 48 KB covers
+// twice the load latency.  Each CTA's tensor memory holds its 2 x (128 x 256) fp32 accumulators
+// (all 512 columns); eight epilogue warps drain them, one set of four per sub-tile, and the MMA
+// thread restarts on a sub-tile as soon as that sub-tile has been drained.
+//
+// Work items: the tiles that fill whole waves of the resident pairs are full 512 x 256 tiles; the
+// tiles of the last, partial wave are cut in two (256 rows) or four (256 rows x 128 columns) when
+// that shortens the tail, and all items are dealt round-robin to the pairs.
 //
 // Barriers: the peer's TMA loads complete on the leader's `full` barrier (one barrier tracks both
 // halves of a stage); `empty` and `tmem_full` exist in both CTAs and the leader commits to each
-// with its own tcgen05.commit; `tmem_empty` lives in the leader and receives arrivals from the
+// with its own tcgen05.commit; `tmem_empty[u]` lives in the leader and receives arrivals from the
 // epilogue threads of both CTAs.  Every wait is bounded; after a timeout all roles of both CTAs
 // drain and the tensor memory is freed.
-//
-// MSUB = 2 doubles the rows per CTA (pair tile 512 x 256): every B stage is used by two MMAs, which
-// cuts the operand bytes per flop by a quarter and doubles the time a stage of the ring covers
-// (4 stages of 48 KB).  Both accumulators of a CTA (all 512 tensor-memory columns) then belong to
-// one tile, so the epilogue does not overlap the next tile's MMAs, only its loads.
 // Same operand layouts and contract as the single-CTA kernel in gemm.cu (a_mn / b_mn).
 #include "common.cuh"
 
 namespace xb_gemm2 {
 
-constexpr int BM = 128;          // rows of A per CTA (256 per pair)
-constexpr int BN = 256;          // columns of the pair's tile
-constexpr int BNH = 128;         // columns of B loaded by one CTA
+constexpr int BM = 128;          // rows of one A sub-tile (per CTA)
+constexpr int BN = 256;          // columns of a full tile
+constexpr int BNH = 128;         // columns of B loaded by one CTA for a full tile
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2;          // one 128-row A sub-tile
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BNH * BK * 2;
-constexpr int NUM_THREADS = 192;
+constexpr int STAGE_BYTES = 2 * A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 320;   // TMA warp, MMA warp, 2 x 4 epilogue warps
 constexpr int TMEM_COLS = 512;
-constexpr int MAX_STAGES = 6;
-template <int MSUB> struct Cfg {
-  static constexpr int STAGES = MSUB == 1 ? 6 : 4;
-  static constexpr int STAGE_BYTES = MSUB * A_BYTES + B_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
-  static constexpr int NUM_ACC = 2 / MSUB;       // accumulator sets in tensor memory
-  static constexpr int ACC_COLS = BN * MSUB;
-  static constexpr int TILE_M = 256 * MSUB;      // rows of the pair's tile
-};
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
 struct Params {
   int M, N, K;
@@ -47,17 +42,26 @@ struct Params {
   long long ldc;
   int out_fp32;
   int accumulate;
-  int num_m_blocks, num_n_blocks, group_m;   // in units of pair tiles
+  int num_m_blocks, num_n_blocks, group_m;   // grid of full 512 x 256 tiles
+  int full_items;                            // tiles [0, full_items) are processed whole
+  int split_m, split_n;                      // the remaining tiles are cut split_m x split_n ways
+  int num_items;
   int* status;
 };
 
 struct __align__(8) Barriers {
-  uint64_t full[MAX_STAGES];
-  uint64_t empty[MAX_STAGES];
-  uint64_t tmem_full[2];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full;
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+};
+
+struct Item {
+  int m0, n0;      // origin of the pair's item
+  int nsub;        // 128-row A sub-tiles per CTA (2: 512 rows per pair, 1: 256 rows)
+  int ncols;       // 256 or 128
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -106,6 +110,33 @@ __device__ __forceinline__ bool mbar_wait_cl(uint64_t* bar, uint32_t parity, vol
     }
   }
 }
+// Warp-collective wait for long waits (epilogue warps sit out a whole main loop): one lane polls,
+// with a sleep between polls, so that the barrier word in shared memory is not hammered by 32
+// threads per warp while the tensor core streams its operands from the same shared memory.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int detail) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    if (!mbar_try_wait_cl(bar, parity)) {
+      const uint64_t t0 = xb_globaltimer();
+      for (uint32_t it = 1;; ++it) {
+        __nanosleep(40);
+        if (mbar_try_wait_cl(bar, parity)) break;
+        if ((it & 15u) == 0u) {
+          if (*abort_flag) { ok = 0; break; }
+          if (xb_globaltimer() - t0 > XB_WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            xb_report(status, XB_ERR_MBAR_TIMEOUT, XB_K_GEMM, detail);
+            ok = 0;
+            break;
+          }
+        }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
 // TMA load whose completion is signalled on a barrier that may live in the peer CTA.
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
                                                  int x, int y) {
@@ -146,6 +177,24 @@ __device__ __forceinline__ void tc_commit2(uint32_t bar_cluster_addr) {
                : "memory");
 }
 
+// All MMAs of one K block, fully unrolled for a compile-time number of A sub-tiles.
+template <bool A_MN, bool B_MN, int NSUB>
+__device__ __forceinline__ void issue_kblock(uint32_t tmem_base, uint32_t sa, uint32_t sb, uint32_t idesc,
+                                             bool first) {
+  constexpr uint64_t a_base = A_MN ? xb_smem_desc_base_sw128(BK * 128, 1024) : xb_smem_desc_base_sw128(16, 1024);
+  constexpr uint64_t b_base = B_MN ? xb_smem_desc_base_sw128(BK * 128, 1024) : xb_smem_desc_base_sw128(16, 1024);
+  constexpr uint32_t a_kstep = A_MN ? (UMMA_K * 128) : (UMMA_K * 2);
+  constexpr uint32_t b_kstep = B_MN ? (UMMA_K * 128) : (UMMA_K * 2);
+#pragma unroll
+  for (int k = 0; k < BK / UMMA_K; ++k) {
+    const uint64_t db = xb_smem_desc(b_base, sb + k * b_kstep);
+#pragma unroll
+    for (int u = 0; u < NSUB; ++u)
+      tc_mma2_f16_ss(tmem_base + u * BN, xb_smem_desc(a_base, sa + u * A_BYTES + k * a_kstep), db, idesc,
+                     (first && k == 0) ? 0u : 1u);
+  }
+}
+
 __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& mb, int& nb) {
   const int per_group = p.group_m * p.num_n_blocks;
   const int g = tile / per_group;
@@ -156,15 +205,34 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& mb, 
   nb = t / gsz;
 }
 
-template <bool A_MN, bool B_MN, int MSUB>
+__device__ __forceinline__ Item decode_item(const Params& p, int w) {
+  Item it;
+  int tile, um = 0, un = 0;
+  if (w < p.full_items) {
+    tile = w;
+    it.nsub = 2;
+    it.ncols = BN;
+  } else {
+    const int parts = p.split_m * p.split_n;
+    const int j = w - p.full_items;
+    tile = p.full_items + j / parts;
+    const int sub = j % parts;
+    um = sub % p.split_m;
+    un = sub / p.split_m;
+    it.nsub = p.split_m == 2 ? 1 : 2;
+    it.ncols = BN / p.split_n;
+  }
+  int mb, nb;
+  tile_coords(p, tile, mb, nb);
+  it.m0 = mb * 512 + um * 256;
+  it.n0 = nb * BN + un * it.ncols;
+  return it;
+}
+
+template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-             const Params p) {
-  constexpr int STAGES = Cfg<MSUB>::STAGES;
-  constexpr int STAGE_BYTES = Cfg<MSUB>::STAGE_BYTES;
-  constexpr int NUM_ACC = Cfg<MSUB>::NUM_ACC;
-  constexpr int ACC_COLS = Cfg<MSUB>::ACC_COLS;
-  constexpr int TILE_M = Cfg<MSUB>::TILE_M;
+             const __grid_constant__ CUtensorMap tmap_b64, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
@@ -176,7 +244,6 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   const uint32_t cta = cluster_ctarank();          // 0 = leader
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -184,14 +251,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&bars->tmem_full[a], 1);
-      mbar_init(&bars->tmem_empty[a], 256);
-    }
+    mbar_init(&bars->tmem_full, 1);
+    mbar_init(&bars->tmem_empty[0], 256);
+    mbar_init(&bars->tmem_empty[1], 256);
     bars->abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_b64);
   }
   __syncthreads();
   if (warp == 1) {
@@ -208,11 +275,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        int mb, nb;
-        tile_coords(p, tile, mb, nb);
-        const int m0 = mb * TILE_M + (int)cta * BM;     // sub-tile j adds 256 * j
-        const int n0 = nb * BN + (int)cta * BNH;
+      for (int w = pair; w < p.num_items && ok; w += num_pairs) {
+        const Item item = decode_item(p, w);
+        const int m0 = item.m0 + (int)cta * BM;              // sub-tile u adds 256 * u
+        const int bcols = item.ncols / 2;                     // B columns loaded by this CTA
+        const int n0 = item.n0 + (int)cta * bcols;
+        const uint32_t stage_tx = 2u * (uint32_t)(item.nsub * A_BYTES + bcols * BK * 2);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -221,12 +289,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             break;
           }
           uint8_t* sa = smem + s * STAGE_BYTES;
-          uint8_t* sb = sa + MSUB * A_BYTES;
+          uint8_t* sb = sa + 2 * A_BYTES;
           const uint32_t full_leader = mapa_u32(xb_smem_u32(&bars->full[s]), 0);
-          if (cta == 0) mbar_expect_tx(&bars->full[s], 2 * STAGE_BYTES);
+          if (cta == 0) mbar_expect_tx(&bars->full[s], stage_tx);
           const int k0 = kb * BK;
 #pragma unroll
-          for (int u = 0; u < MSUB; ++u) {
+          for (int u = 0; u < 2; ++u) {
+            if (u >= item.nsub) break;
             if (!A_MN) {
               tma_load_2d_pair(sa + u * A_BYTES, &tmap_a, full_leader, k0, m0 + 256 * u);
             } else {
@@ -237,10 +306,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             }
           }
           if (!B_MN) {
-            tma_load_2d_pair(sb, &tmap_b, full_leader, k0, n0);
+            tma_load_2d_pair(sb, bcols == BNH ? &tmap_b : &tmap_b64, full_leader, k0, n0);
           } else {
-#pragma unroll
-            for (int j = 0; j < BNH / 64; ++j)
+            for (int j = 0; j < bcols / 64; ++j)
               tma_load_2d_pair(sb + j * (BK * 128), &tmap_b, full_leader, n0 + 64 * j, k0);
           }
         }
@@ -262,26 +330,26 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) ---------------------
     if (cta == 0 && lane == 0) {
-      constexpr uint32_t idesc = xb_idesc(1, 1, 256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       constexpr uint64_t a_base = A_MN ? xb_smem_desc_base_sw128(BK * 128, 1024)
                                        : xb_smem_desc_base_sw128(16, 1024);
       constexpr uint64_t b_base = B_MN ? xb_smem_desc_base_sw128(BK * 128, 1024)
                                        : xb_smem_desc_base_sw128(16, 1024);
       constexpr uint32_t a_kstep = A_MN ? (UMMA_K * 128) : (UMMA_K * 2);
       constexpr uint32_t b_kstep = B_MN ? (UMMA_K * 128) : (UMMA_K * 2);
+      // cluster addresses of a barrier in the two CTAs differ from its local address by constants
+      const uint32_t bars_local = xb_smem_u32(bars);
+      const uint32_t off0 = mapa_u32(bars_local, 0) - bars_local;
+      const uint32_t off1 = mapa_u32(bars_local, 1) - bars_local;
       uint32_t it = 0;
       uint32_t tcount = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
-        const int acc = tcount % NUM_ACC;
-        const uint32_t acc_ph = (tcount / NUM_ACC) & 1;
-        if (!mbar_wait_cl(&bars->tmem_empty[acc], acc_ph ^ 1, abort_flag, p.status, 200 + acc)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int w = pair; w < p.num_items && ok; w += num_pairs, ++tcount) {
+        const Item item = decode_item(p, w);
+        constexpr uint32_t idesc256 = xb_idesc(1, 1, 256, 256, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        constexpr uint32_t idesc128 = xb_idesc(1, 1, 256, 128, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        const uint32_t idesc = item.ncols == 256 ? idesc256 : idesc128;
+        const uint32_t acc_ph = tcount & 1;
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait_cl(&bars->full[s], ph, abort_flag, p.status, 300 + s)) {
@@ -290,54 +358,64 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           }
           tc_fence_after();
           const uint32_t sa = xb_smem_u32(smem + s * STAGE_BYTES);
-          const uint32_t sb = sa + MSUB * A_BYTES;
+          const uint32_t sb = sa + 2 * A_BYTES;
+          if (kb == 0) {
+            // sub-tile by sub-tile, so that the first can start while the second is still drained
+            for (int u = 0; u < 2; ++u) {
+              if (!mbar_wait_cl(&bars->tmem_empty[u], acc_ph ^ 1, abort_flag, p.status, 200 + u)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              if (u < item.nsub) {
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t db = xb_smem_desc(b_base, sb + k * b_kstep);
-#pragma unroll
-            for (int u = 0; u < MSUB; ++u) {
-              const uint64_t da = xb_smem_desc(a_base, sa + u * A_BYTES + k * a_kstep);
-              tc_mma2_f16_ss(d_tmem + u * BN, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                  tc_mma2_f16_ss(tmem_base + u * BN, xb_smem_desc(a_base, sa + u * A_BYTES + k * a_kstep),
+                                 xb_smem_desc(b_base, sb + k * b_kstep), idesc, k > 0 ? 1u : 0u);
+              }
             }
+            if (!ok) break;
+          } else if (item.nsub == 2) {
+            issue_kblock<A_MN, B_MN, 2>(tmem_base, sa, sb, idesc, false);
+          } else {
+            issue_kblock<A_MN, B_MN, 1>(tmem_base, sa, sb, idesc, false);
           }
           const uint32_t e = xb_smem_u32(&bars->empty[s]);
-          tc_commit2(mapa_u32(e, 0));
-          tc_commit2(mapa_u32(e, 1));
+          tc_commit2(e + off0);
+          tc_commit2(e + off1);
         }
         if (ok) {
-          const uint32_t f = xb_smem_u32(&bars->tmem_full[acc]);
-          tc_commit2(mapa_u32(f, 0));
-          tc_commit2(mapa_u32(f, 1));
+          const uint32_t f = xb_smem_u32(&bars->tmem_full);
+          tc_commit2(f + off0);
+          tc_commit2(f + off1);
         }
       }
     }
     __syncwarp();
   } else {
-    // ------------------------------- epilogue (both CTAs, own 128 rows) ----------------
-    const int q = warp & 3;
+    // --------------- epilogue (both CTAs; warps 2-5 sub-tile 0, warps 6-9 sub-tile 1) ----------
+    const int q = warp & 3;                 // tensor-memory lane quarter this warp may read
+    const int u = (warp - 2) >> 2;          // sub-tile drained by this warp
     uint32_t tcount = 0;
     bool ok = true;
     const bool vec_ok = p.out_fp32
                             ? ((p.ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(p.C) % 16) == 0)
                             : ((p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) % 16) == 0);
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tcount) {
-      int mb, nb;
-      tile_coords(p, tile, mb, nb);
-      const int acc = tcount % NUM_ACC;
-      const uint32_t acc_ph = (tcount / NUM_ACC) & 1;
-      if (!mbar_wait_cl(&bars->tmem_full[acc], acc_ph, abort_flag, p.status, 400 + acc)) {
+    for (int w = pair; w < p.num_items && ok; w += num_pairs, ++tcount) {
+      const Item item = decode_item(p, w);
+      if (!mbar_wait_warp(&bars->tmem_full, tcount & 1, abort_flag, p.status, 400 + u)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int row0 = mb * TILE_M + (int)cta * BM + q * 32 + lane;
-      const int n0 = nb * BN;
-      const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      const uint32_t empty_leader = mapa_u32(xb_smem_u32(&bars->tmem_empty[u]), 0);
+      const int row = item.m0 + 256 * u + (int)cta * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + u * BN + ((uint32_t)(q * 32) << 16);
+      const int nchunks = u < item.nsub ? item.ncols / 32 : 0;
 #pragma unroll 1
-      for (int c = 0; c < ACC_COLS / 32; ++c) {
-        const int row = row0 + 256 * (c / (BN / 32));
-        const int col0 = n0 + (c % (BN / 32)) * 32;
-        if (col0 >= p.N) continue;
+      for (int c = 0; c < nchunks; ++c) {
+        const int col0 = item.n0 + c * 32;
+        if (col0 >= p.N) break;
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tc_wait_ld();
@@ -399,7 +477,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         }
       }
       tc_fence_before();
-      mbar_arrive_cluster(mapa_u32(xb_smem_u32(&bars->tmem_empty[acc]), 0));
+      mbar_arrive_cluster(empty_leader);
     }
   }
 
@@ -412,16 +490,20 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   }
 }
 
-template <bool A_MN, bool B_MN, int MSUB>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaStream_t stream) {
-  static int pairs_for_dev[64] = {0};
-  constexpr int SMEM_BYTES = Cfg<MSUB>::SMEM_BYTES;
+static int resident_pairs_cache[64] = {0};
+
+template <bool A_MN, bool B_MN>
+static int resident_pairs() {
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kern = gemm2_kernel<A_MN, B_MN, MSUB>;
-  if (!pairs_for_dev[dev & 63]) {
+  static bool configured[64] = {false};
+  auto kern = gemm2_kernel<A_MN, B_MN>;
+  if (!configured[dev & 63]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-      return -10;
+      return -1;
+    configured[dev & 63] = true;
+  }
+  if (!resident_pairs_cache[dev & 63]) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (xb_sm_count() / 2));
     cfg.blockDim = dim3(NUM_THREADS);
@@ -432,28 +514,59 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p,
       clusters = xb_sm_count() / 2;
     }
     if (clusters > xb_sm_count() / 2) clusters = xb_sm_count() / 2;
-    pairs_for_dev[dev & 63] = clusters;
+    resident_pairs_cache[dev & 63] = clusters;
   }
+  return resident_pairs_cache[dev & 63];
+}
+
+// Cuts the tiles of the last, partial wave when that shortens it: a piece of a tile cut f ways takes
+// about 1/f of a tile's time (a little more, hence the penalties), and T tiles cut f ways need
+// ceil(T f / P) rounds on P pairs.
+static void plan_items(Params& p, int pairs, bool can_split_n) {
   const int tiles = p.num_m_blocks * p.num_n_blocks;
-  const int pairs = tiles < pairs_for_dev[dev & 63] ? tiles : pairs_for_dev[dev & 63];
-  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  const int tail = tiles % pairs;
+  p.full_items = tiles - tail;
+  p.split_m = p.split_n = 1;
+  if (tail) {
+    const float penalty[3] = {1.00f, 1.10f, 1.50f};
+    const int f[3] = {1, 2, 4};
+    float best = 1e30f;
+    for (int i = 0; i < (can_split_n ? 3 : 2); ++i) {
+      const int rounds = (tail * f[i] + pairs - 1) / pairs;
+      const float cost = penalty[i] * (float)rounds / (float)f[i];
+      if (cost < best - 1e-6f) {
+        best = cost;
+        p.split_m = f[i] >= 2 ? 2 : 1;
+        p.split_n = f[i] == 4 ? 2 : 1;
+      }
+    }
+  }
+  p.num_items = p.full_items + tail * p.split_m * p.split_n;
+}
+
+template <bool A_MN, bool B_MN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb64, Params& p,
+                  cudaStream_t stream) {
+  const int pairs_max = resident_pairs<A_MN, B_MN>();
+  if (pairs_max <= 0) return -10;
+  plan_items(p, pairs_max, true);
+  const int pairs = p.num_items < pairs_max ? p.num_items : pairs_max;
+  gemm2_kernel<A_MN, B_MN><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb64, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 }  // namespace xb_gemm2
 
-// Same contract as xb_gemm_bf16.  msub = 1: pair tile 256 x 256 with double-buffered accumulators;
-// msub = 2: pair tile 512 x 256.
+// Same contract as xb_gemm_bf16.
 XB_API int xb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                              long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32,
-                             int accumulate, int msub, void* stream) {
+                             int accumulate, void* stream) {
   using namespace xb_gemm2;
-  if (msub != 1 && msub != 2) return -1;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) ||
       (reinterpret_cast<uintptr_t>(B) % 16))
     return -1;
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tb64;
   int rc;
   if (!a_mn)
     rc = xb_make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK,
@@ -462,30 +575,29 @@ XB_API int xb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N
     rc = xb_make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64,
                          CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return -2;
-  if (!b_mn)
+  if (!b_mn) {
     rc = xb_make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BNH, BK,
                          CU_TENSOR_MAP_SWIZZLE_128B);
-  else
+    if (!rc)
+      rc = xb_make_tmap_2d(&tb64, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, 64, BK,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
     rc = xb_make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64,
                          CU_TENSOR_MAP_SWIZZLE_128B);
+    tb64 = tb;
+  }
   if (rc) return -3;
   Params p;
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc;
   p.out_fp32 = out_fp32; p.accumulate = accumulate;
-  p.num_m_blocks = (M + 256 * msub - 1) / (256 * msub);
+  p.num_m_blocks = (M + 511) / 512;
   p.num_n_blocks = (N + BN - 1) / BN;
-  p.group_m = 8 / msub;
+  p.group_m = 4;
   p.status = xb_status_ptr();
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (msub == 1) {
-    if (!a_mn && !b_mn) return launch<false, false, 1>(ta, tb, p, st);
-    if (!a_mn && b_mn) return launch<false, true, 1>(ta, tb, p, st);
-    if (a_mn && !b_mn) return launch<true, false, 1>(ta, tb, p, st);
-    return launch<true, true, 1>(ta, tb, p, st);
-  }
-  if (!a_mn && !b_mn) return launch<false, false, 2>(ta, tb, p, st);
-  if (!a_mn && b_mn) return launch<false, true, 2>(ta, tb, p, st);
-  if (a_mn && !b_mn) return launch<true, false, 2>(ta, tb, p, st);
-  return launch<true, true, 2>(ta, tb, p, st);
+  if (!a_mn && !b_mn) return launch<false, false>(ta, tb, tb64, p, st);
+  if (!a_mn && b_mn) return launch<false, true>(ta, tb, tb64, p, st);
+  if (a_mn && !b_mn) return launch<true, false>(ta, tb, tb64, p, st);
+  return launch<true, true>(ta, tb, tb64, p, st);
 }

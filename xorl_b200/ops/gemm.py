@@ -16,15 +16,15 @@ from . import _lib
 from .grad_sink import current_wgrad_store, grad_target, mark_written
 
 _launches = 0
-# "pair2" / "pair": CTA-pair kernels (tcgen05 cta_group::2, csrc/gemm2.cu) with 512x256 / 256x256 pair
-# tiles; "single": one CTA per 128x256 tile (csrc/gemm.cu)
-_VARIANT = os.environ.get("XORL_B200_GEMM", "single")
+# "pair": CTA-pair kernel (tcgen05 cta_group::2, 512x256 pair tiles, csrc/gemm2.cu);
+# "single": one CTA per 128x256 tile (csrc/gemm.cu), also used for small M
+_VARIANT = os.environ.get("XORL_B200_GEMM", "pair")
 
 
 def set_variant(name: str) -> str:
     """Selects the dense GEMM kernel ("pair" or "single"); returns the previous choice."""
     global _VARIANT
-    assert name in ("pair2", "pair", "single")
+    assert name in ("pair", "single")
     prev, _VARIANT = _VARIANT, name
     return prev
 
@@ -76,9 +76,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     lib = _lib.cuda_lib()
     args = (a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
             out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate))
-    if _VARIANT != "single" and M > 128:
-        msub = 2 if (_VARIANT == "pair2" and M >= 512) else 1
-        rc = lib.xb_gemm_bf16_pair(*args, msub, _lib.stream_ptr())
+    if _VARIANT == "pair" and M >= 384:
+        rc = lib.xb_gemm_bf16_pair(*args, _lib.stream_ptr())
     else:
         rc = lib.xb_gemm_bf16(*args, _lib.stream_ptr())
     _lib.check(rc, "xb_gemm_bf16")

@@ -150,7 +150,7 @@ def main(argv=None) -> None:
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=4096)
-    ap.add_argument("--variant", choices=["single", "pair", "pair2"], default="single")
+    ap.add_argument("--variant", choices=["single", "pair"], default="pair")
     ap.add_argument("--a-mn", action="store_true")
     ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--tokens", type=int, default=4096)
