@@ -19,6 +19,8 @@ kernels of ``parallel/symm.py`` when available.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from contextlib import nullcontext
 from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple
@@ -126,12 +128,88 @@ class ZeroUnit:
         self.groups: List[FlatParamGroup] = []
 
 
+class _Offloaded:
+    """Host copy of a saved activation tuple (pinned), with the events that order the two copies."""
+    __slots__ = ("host", "done", "device", "back")
+
+    def __init__(self, host, done):
+        self.host, self.done, self.device, self.back = host, done, None, None
+
+
+class ActivationOffloader:
+    """Moves the saved inputs of recomputed layers to pinned host memory on a side stream and brings
+    them back one layer ahead of the backward pass (src/xorl/distributed/offloading.py:60-249).
+    Pinned buffers are pooled by shape, so after the first step no host allocation happens."""
+
+    def __init__(self, engine):
+        self.engine = engine
+        self.stream = torch.cuda.Stream() if engine.device.type == "cuda" else None
+        self.pool: Dict[Tuple, List[torch.Tensor]] = {}
+        self.bytes_offloaded = 0
+
+    def _host_buffer(self, t: torch.Tensor) -> torch.Tensor:
+        key = (tuple(t.shape), t.dtype)
+        free = self.pool.setdefault(key, [])
+        if free:
+            return free.pop()
+        return torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=self.stream is not None)
+
+    def offload(self, acts):
+        if self.stream is None:
+            host = tuple(None if a is None else self._host_buffer(a).copy_(a) for a in acts)
+            self.bytes_offloaded += sum(h.numel() * h.element_size() for h in host if h is not None)
+            return _Offloaded(host, None)
+        self.stream.wait_stream(torch.cuda.current_stream())
+        host = []
+        with torch.cuda.stream(self.stream):
+            for a in acts:
+                if a is None:
+                    host.append(None)
+                    continue
+                h = self._host_buffer(a)
+                h.copy_(a, non_blocking=True)
+                a.record_stream(self.stream)
+                host.append(h)
+                self.bytes_offloaded += h.numel() * h.element_size()
+            done = torch.cuda.Event()
+            done.record(self.stream)
+        return _Offloaded(tuple(host), done)
+
+    def prefetch(self, item) -> None:
+        if not isinstance(item, _Offloaded) or item.device is not None:
+            return
+        dev = self.engine.device
+        if self.stream is None:
+            item.device = tuple(None if h is None else h.to(dev) for h in item.host)
+            return
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(item.done)
+            item.device = tuple(None if h is None else h.to(dev, non_blocking=True) for h in item.host)
+            item.back = torch.cuda.Event()
+            item.back.record(self.stream)
+
+    def fetch(self, item):
+        if not isinstance(item, _Offloaded):
+            return item
+        self.prefetch(item)
+        if item.back is not None:
+            torch.cuda.current_stream().wait_event(item.back)
+            for d in item.device:
+                if d is not None:
+                    d.record_stream(torch.cuda.current_stream())
+        for h in item.host:
+            if h is not None:
+                self.pool.setdefault((tuple(h.shape), h.dtype), []).append(h)
+        return item.device
+
+
 class Zero3Engine:
     """Runs forward/backward unit by unit with ZeRO-3 sharding (world >= 1)."""
 
     def __init__(self, model: nn.Module, pstate: Optional[ParallelState] = None, *,
                  compute_dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None,
                  reduce_dtype: torch.dtype = torch.float32, reshard_after_forward: bool = True,
+                 activation_offload: bool = False,
                  recompute: bool = True, seed: int = 0, comm_backend: str = "nccl",
                  shard: bool = True):
         self.model = model
@@ -139,6 +217,8 @@ class Zero3Engine:
         self.device = device or torch.device("cuda" if torch.cuda.is_available() else "cpu")
         self.compute_dtype = compute_dtype
         self.reduce_dtype = reduce_dtype
+        self.bf16_a2a_reduce = os.environ.get("XORL_B200_BF16_A2A_REDUCE", "1") == "1"
+        self.offloader = ActivationOffloader(self) if activation_offload else None
         self.recompute = recompute
         self.comm_backend = comm_backend
         self.is_cuda = self.device.type == "cuda"
@@ -405,6 +485,11 @@ class Zero3Engine:
             g.grad_ready = True
 
     def _rs_collective(self, g: FlatParamGroup, gf: torch.Tensor, accumulate: bool) -> None:
+        if self.reduce_dtype == torch.bfloat16 and gf.dtype == torch.float32 and self.bf16_a2a_reduce:
+            # bf16 on the wire, stochastic rounding on the way out, fp32 summation on arrival
+            from .dist_utils import stochastic_bf16_all_to_all_reduce_scatter
+            stochastic_bf16_all_to_all_reduce_scatter(gf, g.grad_shard, g.pg, accumulate)
+            return
         src = gf if gf.dtype == self.reduce_dtype else gf.to(self.reduce_dtype)
         out = torch.empty(g.shard_numel, device=self.device, dtype=src.dtype)
         dist.reduce_scatter_tensor(out, src, op=dist.ReduceOp.SUM, group=g.pg)
@@ -473,7 +558,7 @@ class Zero3Engine:
                 self.gather(layers[i + 1])
             layer = unit.modules[0]
             if self.recompute:
-                saved.append(acts)
+                saved.append(self.offloader.offload(acts) if self.offloader is not None else acts)
                 with torch.no_grad():
                     acts = layer(*acts, ctx)
             else:
@@ -501,6 +586,10 @@ class Zero3Engine:
             layer = unit.modules[0]
             lidx = getattr(layer, "layer_idx", i)
             if self.recompute:
+                if self.offloader is not None:
+                    if i > 0:
+                        self.offloader.prefetch(saved[i - 1])
+                    saved[i] = self.offloader.fetch(saved[i])
                 ins = tuple(a.detach().requires_grad_() if a is not None else None for a in saved[i])
                 saved[i] = None
                 ctx.aux["record_routing"] = False

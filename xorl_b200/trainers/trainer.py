@@ -125,6 +125,7 @@ class Trainer:
         self.engine = Zero3Engine(
             self.model, self.ps, compute_dtype=self.compute_dtype, device=self.device,
             reduce_dtype=torch.float32 if t.fsdp_reduce_dtype == "fp32" else torch.bfloat16,
+            activation_offload=t.enable_activation_offload,
             reshard_after_forward=True if t.reshard_after_forward is None else t.reshard_after_forward,
             recompute=recompute, seed=t.seed, comm_backend=t.comm_backend)
         if t.comm_backend in ("auto", "fused") and self.device.type == "cuda" and self.ps.world_size > 1:
