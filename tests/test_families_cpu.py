@@ -1,0 +1,198 @@
+"""Model families on CPU: every registered family builds from its preset, trains a few steps
+through the ZeRO engine, and the family-specific pieces (sinks / sliding window attention,
+group-limited sigmoid routing with a selection bias, clamped SwiGLU with expert biases, MLA)
+match independent PyTorch restatements."""
+import math
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+@pytest.fixture(autouse=True)
+def _state():
+    from xorl_b200.parallel.state import init_parallel_state, reset_parallel_state
+    reset_parallel_state()
+    init_parallel_state(device_type="cpu")
+    yield
+    reset_parallel_state()
+
+
+@pytest.mark.parametrize("name", ["tiny-qwen3", "tiny-qwen2", "tiny-olmo2", "tiny-qwen3-moe", "tiny-gpt-oss",
+                                  "tiny-deepseek-v3", "tiny-glm4-moe"])
+def test_family_trains(name):
+    from xorl_b200.models import build_model
+    from xorl_b200.models.config import preset
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.state import get_parallel_state
+    from xorl_b200.parallel.zero import Zero3Engine
+    cfg = preset(name)
+    from xorl_b200.models.registry import get_model_class
+    m = get_model_class(cfg)(cfg, dtype=torch.float32, device="meta")
+    eng = Zero3Engine(m, get_parallel_state(), compute_dtype=torch.float32, device=torch.device("cpu"), seed=0)
+    opt = build_optimizer(eng, lr=3e-3, weight_decay=0.0)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (1, 49), generator=g)
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    cu = torch.tensor([0, 20, 48], dtype=torch.int32)
+    pos = torch.cat([torch.arange(20), torch.arange(28)]).unsqueeze(0)
+    losses = []
+    for _ in range(5):
+        opt.zero_grad()
+        loss = eng.forward_backward(x, y, position_ids=pos, cu_seqlens=cu, grad_scale=1.0 / y.numel())
+        eng.finish_grad_sync()
+        opt.step()
+        losses.append(float(loss))
+    assert all(math.isfinite(l) for l in losses) and losses[-1] < losses[0], losses
+
+
+def test_unbuilt_families_fail_loudly():
+    from xorl_b200.models.config import ModelConfig
+    from xorl_b200.models.registry import get_model_class
+    with pytest.raises(NotImplementedError):
+        get_model_class(ModelConfig.from_dict({"model_type": "nemotron_h"}))
+
+
+def test_attention_window_and_sinks_reference():
+    from xorl_b200.ops.attention import attention_reference
+    torch.manual_seed(0)
+    T, Hq, Hkv, D = 12, 4, 2, 8
+    q, k, v = torch.randn(T, Hq, D), torch.randn(T, Hkv, D), torch.randn(T, Hkv, D)
+    sinks = torch.randn(Hq)
+    cu = torch.tensor([0, 5, 12], dtype=torch.int32)
+    out = attention_reference(q, k, v, cu, True, 0.3, window=3, sinks=sinks)
+    # token by token
+    for (s, e) in ((0, 5), (5, 12)):
+        for t in range(s, e):
+            lo = max(s, t - 2)
+            for h in range(Hq):
+                kk, vv = k[lo:t + 1, h // 2], v[lo:t + 1, h // 2]
+                logits = torch.cat([(kk @ q[t, h]) * 0.3, sinks[h:h + 1]])
+                p = torch.softmax(logits, 0)[:-1]
+                torch.testing.assert_close(out[t, h], p @ vv, rtol=1e-5, atol=1e-5)
+
+
+def test_group_limited_sigmoid_routing():
+    from xorl_b200.ops.moe import topk_route
+    torch.manual_seed(1)
+    T, E, k = 16, 8, 2
+    logits = torch.randn(T, E)
+    bias = torch.randn(E) * 0.5
+    w, idx, probs = topk_route(logits, k, True, "sigmoid", 2.5, n_group=4, topk_group=2, correction_bias=bias)
+    s = torch.sigmoid(logits)
+    for t in range(T):
+        c = s[t] + bias
+        gs = c.view(4, 2).sum(-1)                              # two experts per group: top-2 sum = sum
+        groups = set(gs.topk(2)[1].tolist())
+        allowed = [e for e in range(E) if e // 2 in groups]
+        best = sorted(allowed, key=lambda e: -c[e].item())[:k]
+        assert set(idx[t].tolist()) == set(best)
+        ww = s[t, idx[t]]
+        torch.testing.assert_close(w[t], ww / ww.sum() * 2.5)
+    # gpt-oss style: softmax over the selected logits only
+    w2, idx2, _ = topk_route(logits, k, False, "softmax_after_topk")
+    torch.testing.assert_close(w2, torch.softmax(logits.topk(k)[0], -1))
+
+
+def test_clamped_swiglu_expert_mlp_with_biases():
+    from xorl_b200.ops import moe as moe_ops
+    torch.manual_seed(2)
+    E, H, I = 3, 16, 8
+    counts = torch.tensor([5, 0, 7])
+    x = torch.randn(12, H)
+    gu, dn = torch.randn(E, H, 2 * I) * 0.3, torch.randn(E, I, H) * 0.3
+    gub, dnb = torch.randn(E, 2 * I), torch.randn(E, H)
+    y = moe_ops.expert_mlp(x, counts, gu, dn, gate_up_bias=gub, down_bias=dnb, swiglu_limit=1.5)
+    s = 0
+    for e in range(E):
+        n = counts[e].item()
+        xe = x[s:s + n]
+        h = xe @ gu[e] + gub[e]
+        gate, up = h[:, :I].clamp(max=1.5), h[:, I:].clamp(-1.5, 1.5)
+        ref = ((up + 1) * gate * torch.sigmoid(1.702 * gate)) @ dn[e] + dnb[e]
+        torch.testing.assert_close(y[s:s + n], ref, rtol=1e-4, atol=1e-4)
+        s += n
+
+
+def test_mla_matches_explicit_formula():
+    from xorl_b200.models.config import preset
+    from xorl_b200.models.context import StepContext
+    from xorl_b200.models.mla import MLAttention
+    from xorl_b200.models.rope import RotaryEmbedding
+    cfg = preset("tiny-deepseek-v3")
+    torch.manual_seed(3)
+    m = MLAttention(cfg, 0, dtype=torch.float32)
+    for p in m.parameters():
+        if p.dim() > 1:
+            torch.nn.init.normal_(p, std=0.2)
+    T = 6
+    x = torch.randn(T, cfg.hidden_size)
+    rot = RotaryEmbedding(cfg.head_dim, cfg.rope_theta, None, 1.0, 512)
+    cos, sin = rot(torch.arange(T))
+    ctx = StepContext(cu_seqlens=torch.tensor([0, T], dtype=torch.int32), position_ids=torch.arange(T),
+                      max_seqlen=T, cos=cos, sin=sin)
+    out = m(x, ctx)
+    # explicit: complex rotation on interleaved pairs, per-head loop
+    H, dn, dr, dv = 4, 16, 8, 16
+    q = m.q_b_proj(m.q_a_layernorm(m.q_a_proj(x))).view(T, H, dn + dr)
+    ckv = m.kv_a_proj_with_mqa(x)
+    c, kr = ckv[:, :24], ckv[:, 24:]
+    kv = m.kv_b_proj(m.kv_a_layernorm(c)).view(T, H, dn + dv)
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, dr, 2).float() / dr))
+    ang = torch.arange(T).float()[:, None] * inv[None]
+    rotc = torch.polar(torch.ones_like(ang), ang)                        # [T, dr/2]
+
+    def rope_interleaved(t):                                              # [T, h, dr]
+        z = torch.view_as_complex(t.reshape(*t.shape[:-1], dr // 2, 2).contiguous())
+        return z * rotc[:, None, :]
+
+    qr = rope_interleaved(q[..., dn:])
+    krr = rope_interleaved(kr.reshape(T, 1, dr))
+    ref = torch.zeros(T, H, dv)
+    for h in range(H):
+        s_nope = q[:, h, :dn] @ kv[:, h, :dn].t()
+        s_rope = torch.einsum("ic,jc->ij", qr[:, h], krr[:, 0].conj()).real
+        sc = (s_nope + s_rope) * (dn + dr) ** -0.5
+        sc = sc.masked_fill(~torch.ones(T, T, dtype=torch.bool).tril(), float("-inf"))
+        ref[:, h] = torch.softmax(sc, -1) @ kv[:, h, dn:]
+    ref = m.o_proj(ref.reshape(T, H * dv))
+    torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["tiny-gpt-oss", "tiny-deepseek-v3", "tiny-qwen3-moe"])
+def test_family_hf_roundtrip(name, tmp_path):
+    """Export to HF-named safetensors and load back into a fresh engine: identical weights."""
+    from xorl_b200.checkpoint.hf_io import load_hf_weights, save_hf_weights
+    from xorl_b200.models.config import preset
+    from xorl_b200.models.registry import get_model_class
+    from xorl_b200.parallel.state import get_parallel_state
+    from xorl_b200.parallel.zero import Zero3Engine
+    cfg = preset(name)
+
+    def engine(seed):
+        m = get_model_class(cfg)(cfg, dtype=torch.float32, device="meta")
+        return Zero3Engine(m, get_parallel_state(), compute_dtype=torch.float32, device=torch.device("cpu"), seed=seed)
+
+    a, b = engine(0), engine(1)
+    save_hf_weights(a, str(tmp_path), cfg, dtype=torch.float32)
+    from safetensors import safe_open
+    names = []
+    for f in os.listdir(tmp_path):
+        if f.endswith(".safetensors"):
+            with safe_open(str(tmp_path / f), "pt") as fh:
+                names += list(fh.keys())
+    if name == "tiny-gpt-oss":
+        assert "model.layers.0.mlp.router.weight" in names and "model.layers.0.mlp.experts.gate_up_proj_bias" in names
+        assert "model.layers.0.self_attn.sinks" in names
+    if name == "tiny-deepseek-v3":
+        assert "model.layers.1.mlp.shared_experts.gate_proj.weight" in names
+        assert "model.layers.1.mlp.experts.3.down_proj.weight" in names
+        assert "model.layers.1.mlp.gate.e_score_correction_bias" in names
+    missing = load_hf_weights(b, str(tmp_path), cfg)
+    assert not missing
+    wa = dict(a.iter_full_tensors("master"))
+    for k, v in b.iter_full_tensors("master"):
+        assert torch.equal(v, wa[k]), k

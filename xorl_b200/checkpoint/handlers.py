@@ -87,5 +87,75 @@ class CheckpointHandler:
         return torch.cat(parts, dim=0)
 
 
+class _RenamingHandler(CheckpointHandler):
+    """Base handler plus a table of (in-memory substring, on-disk substring) renames applied after
+    the fused-layout transforms."""
+    RENAMES: Tuple[Tuple[str, str], ...] = ()
+
+    def _out(self, name: str) -> str:
+        for a, b in self.RENAMES:
+            name = name.replace(a, b)
+        return name
+
+    def _in(self, name: str) -> str:
+        for a, b in self.RENAMES:
+            name = name.replace(b, a)
+        return name
+
+    def to_hf(self, name, t):
+        for n, part in super().to_hf(name, t):
+            yield self._out(n), part
+
+    def hf_sources(self, name):
+        return [self._out(n) for n in super().hf_sources(name)]
+
+
+class DeepseekV3Handler(_RenamingHandler):
+    """DeepSeek-V3 / GLM-4.5 MoE: ``shared_experts`` (plural) on disk, the selection bias stored
+    under the router (src/xorl/models/transformers/deepseek_v3/checkpoint_handler.py)."""
+    RENAMES = ((".mlp.shared_expert.", ".mlp.shared_experts."),)
+
+
+class GptOssHandler(CheckpointHandler):
+    """gpt-oss keeps experts stacked on disk, with gate and up columns interleaved, per-expert
+    biases, the router under ``mlp.router`` and one sink logit per head
+    (src/xorl/models/transformers/gpt_oss/checkpoint_handler.py)."""
+
+    def _disk(self, fq: str) -> str:
+        return (fq.replace(".mlp.gate.", ".mlp.router.")
+                  .replace(".experts.gate_up_bias", ".experts.gate_up_proj_bias")
+                  .replace(".experts.down_bias", ".experts.down_proj_bias"))
+
+    def to_hf(self, name, t):
+        fq = to_checkpoint_fqn(name)
+        if ".mlp.experts.gate_up_proj" in fq or ".mlp.experts.gate_up_bias" in fq:
+            g, u = t.chunk(2, dim=-1)
+            yield self._disk(fq), torch.stack([g, u], dim=-1).flatten(-2).contiguous()   # g0 u0 g1 u1 ...
+        elif ".mlp.experts." in fq or ".mlp.gate." in fq:
+            yield self._disk(fq), t
+        else:
+            yield from super().to_hf(name, t)
+
+    def hf_sources(self, name):
+        fq = to_checkpoint_fqn(name)
+        if ".mlp.experts." in fq or ".mlp.gate." in fq:
+            return [self._disk(fq)]
+        return super().hf_sources(name)
+
+    def from_hf(self, name, parts):
+        fq = to_checkpoint_fqn(name)
+        if ".mlp.experts.gate_up_proj" in fq or ".mlp.experts.gate_up_bias" in fq:
+            t = parts[0]
+            return torch.cat([t[..., 0::2], t[..., 1::2]], dim=-1).contiguous()
+        if ".mlp.experts." in fq or ".mlp.gate." in fq:
+            return parts[0]
+        return super().from_hf(name, parts)
+
+
 def get_checkpoint_handler(cfg) -> CheckpointHandler:
+    mt = getattr(cfg, "model_type", "")
+    if mt == "gpt_oss":
+        return GptOssHandler(cfg)
+    if mt in ("deepseek_v3", "glm4_moe"):
+        return DeepseekV3Handler(cfg)
     return CheckpointHandler(cfg)

@@ -134,6 +134,29 @@ class ModelConfig:
             d["use_qk_norm"] = False
         if mt in ("llama",):
             d["use_qk_norm"] = False
+        if mt == "gpt_oss":
+            d["use_qk_norm"] = False
+            d.setdefault("attention_bias", True)
+            d.setdefault("attention_sinks", True)
+            d.setdefault("expert_bias", True)
+            d.setdefault("router_bias", True)
+            d.setdefault("swiglu_limit", 7.0)
+            d.setdefault("scoring_func", "softmax_after_topk")
+            d.setdefault("norm_topk_prob", False)
+            d.setdefault("moe_intermediate_size", d.get("intermediate_size", 0))
+            if d.get("layer_types") is None and d.get("sliding_window"):
+                n = d.get("num_hidden_layers", 0)
+                d["layer_types"] = ["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(n)]
+        if mt in ("deepseek_v3", "glm4_moe"):
+            d["use_qk_norm"] = bool(d.get("use_qk_norm", False)) if mt == "glm4_moe" else False
+            d.setdefault("scoring_func", "sigmoid")
+            d.setdefault("use_correction_bias", True)
+            if d.get("n_shared_experts") and not d.get("shared_expert_intermediate_size"):
+                d["shared_expert_intermediate_size"] = d["n_shared_experts"] * d.get("moe_intermediate_size", 0)
+            if mt == "deepseek_v3" and d.get("moe_layer_freq"):
+                d.setdefault("decoder_sparse_step", d["moe_layer_freq"])
+            if mt == "deepseek_v3":
+                d["head_dim"] = d.get("qk_rope_head_dim", 64)      # rotary table covers the rope slice
         extra = {k: d.pop(k) for k in list(d) if k not in known}
         cfg = cls(**d)
         cfg.extra = extra
@@ -186,6 +209,29 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                           num_key_value_heads=4, head_dim=128, rope_theta=1e6, num_experts=128,
                           num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True,
                           router_aux_loss_coef=1e-3, tie_word_embeddings=False),
+    "tiny-gpt-oss": dict(model_type="gpt_oss", vocab_size=512, hidden_size=64, intermediate_size=64,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                         num_local_experts=4, num_experts_per_tok=2, sliding_window=8, rope_theta=1e4,
+                         max_position_embeddings=512, tie_word_embeddings=False),
+    "tiny-deepseek-v3": dict(model_type="deepseek_v3", vocab_size=512, hidden_size=64, intermediate_size=128,
+                             num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
+                             q_lora_rank=32, kv_lora_rank=24, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                             v_head_dim=16, n_routed_experts=8, num_experts_per_tok=2, n_group=4, topk_group=2,
+                             n_shared_experts=1, moe_intermediate_size=32, first_k_dense_replace=1,
+                             topk_method="noaux_tc", routed_scaling_factor=2.5, norm_topk_prob=True,
+                             rope_theta=1e4, max_position_embeddings=512, tie_word_embeddings=False),
+    "tiny-glm4-moe": dict(model_type="glm4_moe", vocab_size=512, hidden_size=64, intermediate_size=128,
+                          num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                          partial_rotary_factor=0.5, use_qk_norm=True, n_routed_experts=8, num_experts_per_tok=2,
+                          n_group=1, topk_group=1, n_shared_experts=1, moe_intermediate_size=32,
+                          first_k_dense_replace=1, routed_scaling_factor=1.0, norm_topk_prob=True,
+                          rope_theta=1e4, max_position_embeddings=512, tie_word_embeddings=False),
+    "tiny-olmo2": dict(model_type="olmo2", vocab_size=512, hidden_size=64, intermediate_size=128,
+                       num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, rope_theta=1e4,
+                       max_position_embeddings=512, tie_word_embeddings=False),
+    "tiny-qwen2": dict(model_type="qwen2", vocab_size=512, hidden_size=64, intermediate_size=128,
+                       num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, rope_theta=1e4,
+                       max_position_embeddings=512, tie_word_embeddings=True),
     "llama3-8b": dict(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
                       num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8,
                       rope_theta=5e5, rms_norm_eps=1e-5, tie_word_embeddings=False, use_qk_norm=False),

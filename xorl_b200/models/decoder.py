@@ -27,7 +27,11 @@ class DecoderLayer(nn.Module):
         super().__init__()
         self.layer_idx = layer_idx
         self.post_norm = cfg.norm_placement == "post"
-        self.self_attn = Attention(cfg, layer_idx, dtype=dtype, device=device)
+        if cfg.extra.get("kv_lora_rank"):
+            from .mla import MLAttention
+            self.self_attn = MLAttention(cfg, layer_idx, dtype=dtype, device=device)
+        else:
+            self.self_attn = Attention(cfg, layer_idx, dtype=dtype, device=device)
         if cfg.layer_is_moe(layer_idx):
             from .moe import MoEBlock
             self.mlp = MoEBlock(cfg, layer_idx, dtype=dtype, device=device)

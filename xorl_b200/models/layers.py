@@ -92,6 +92,10 @@ class Attention(nn.Module):
         self.scale = 1.0 / math.sqrt(self.D)
         self.window = cfg.sliding_window if (cfg.layer_types is None or
                                             cfg.layer_types[layer_idx] == "sliding_attention") else None
+        self.sinks = nn.Parameter(torch.zeros(self.Hq, dtype=dtype, device=device)) if cfg.attention_sinks else None
+        if self.sinks is not None and self.tp > 1:
+            from ..parallel.tp import mark_col
+            mark_col(self.sinks, (self.Hq * self.tp,), (self.Hq * self.tp,))
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         if self.tp > 1:
@@ -101,7 +105,8 @@ class Attention(nn.Module):
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         if ctx.cp is not None:
             out = ctx.cp.attention(self, qkv, ctx)
-        elif self.cfg.qk_norm_full or self.cfg.partial_rotary_factor != 1.0:
+        elif (self.cfg.qk_norm_full or self.cfg.partial_rotary_factor != 1.0 or self.window
+              or self.sinks is not None):
             out = self._unfused_attention(qkv, ctx)
         else:
             wq = self.q_norm.weight if self.use_qk_norm else None
@@ -120,16 +125,24 @@ class Attention(nn.Module):
         T = qkv.shape[0]
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
-        if self.use_qk_norm:
+        if self.use_qk_norm and self.cfg.qk_norm_full:
             q, k = self.q_norm(q), self.k_norm(k)
         q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
+        if self.use_qk_norm and not self.cfg.qk_norm_full:
+            q = self.q_norm(q.reshape(T * Hq, D)).reshape(T, Hq, D)
+            k = self.k_norm(k.reshape(T * Hkv, D)).reshape(T, Hkv, D)
         rot = ctx.cos.shape[-1] * 2
         if rot == D:
             q, k = attn_ops.rope_reference(q, ctx.cos, ctx.sin), attn_ops.rope_reference(k, ctx.cos, ctx.sin)
         else:
             q = torch.cat([attn_ops.rope_reference(q[..., :rot], ctx.cos, ctx.sin), q[..., rot:]], -1)
             k = torch.cat([attn_ops.rope_reference(k[..., :rot], ctx.cos, ctx.sin), k[..., rot:]], -1)
-        out = attn_ops.flash_attn_varlen(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale)
+        if self.window or self.sinks is not None:
+            # sliding windows and sink logits are not in the tcgen05 kernel: masked-softmax path
+            out = attn_ops.attention_reference(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale,
+                                               window=self.window, sinks=self.sinks)
+        else:
+            out = attn_ops.flash_attn_varlen(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale)
         return out.reshape(T, Hq * D)
 
 

@@ -33,12 +33,18 @@ class TopKRouter(nn.Module):
         self.weight = nn.Parameter(torch.empty(cfg.num_experts, cfg.hidden_size, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(cfg.num_experts, dtype=dtype, device=device)) \
             if cfg.router_bias else None
+        self.n_group, self.topk_group = cfg.n_group, cfg.topk_group
+        # selection-only bias of auxiliary-loss-free balancing: not trained by gradient descent
+        self.e_score_correction_bias = nn.Parameter(
+            torch.zeros(cfg.num_experts, dtype=torch.float32, device=device), requires_grad=False) \
+            if cfg.extra.get("topk_method") == "noaux_tc" or cfg.extra.get("use_correction_bias") else None
 
     def forward(self, x: torch.Tensor):
         """x [T, H] -> (weights fp32 [T, k], indices int64 [T, k], probs fp32 [T, E])."""
         logits = torch.nn.functional.linear(x.float(), self.weight.float(),
                                             None if self.bias is None else self.bias.float())
-        return moe_ops.topk_route(logits, self.top_k, self.norm_topk_prob, self.scoring, self.scale)
+        return moe_ops.topk_route(logits, self.top_k, self.norm_topk_prob, self.scoring, self.scale,
+                                  self.n_group, self.topk_group, self.e_score_correction_bias)
 
 
 class Experts(nn.Module):
@@ -53,10 +59,22 @@ class Experts(nn.Module):
         self.gate_up_proj._xb_expert = True
         self.down_proj._xb_expert = True
         self.swiglu_limit = cfg.swiglu_limit
+        self.gate_up_bias = self.down_bias = None
+        if cfg.expert_bias:
+            self.gate_up_bias = nn.Parameter(torch.zeros(num_local, 2 * I, dtype=dtype, device=device))
+            self.down_bias = nn.Parameter(torch.zeros(num_local, H, dtype=dtype, device=device))
+            self.gate_up_bias._xb_expert = True
+            self.down_bias._xb_expert = True
+
+    def mlp_kwargs(self):
+        if self.gate_up_bias is None and self.swiglu_limit is None:
+            return {}
+        return dict(gate_up_bias=self.gate_up_bias, down_bias=self.down_bias, swiglu_limit=self.swiglu_limit)
 
     def forward(self, x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:
         """x_sorted [M, H] grouped by local expert; tokens_per_expert int64 [num_local]."""
-        return moe_ops.expert_mlp(x_sorted, tokens_per_expert, self.gate_up_proj, self.down_proj)
+        return moe_ops.expert_mlp(x_sorted, tokens_per_expert, self.gate_up_proj, self.down_proj,
+                                  **self.mlp_kwargs())
 
 
 class MoEBlock(nn.Module):

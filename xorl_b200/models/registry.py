@@ -22,14 +22,25 @@ def _decoder():
 for _n in ("qwen3", "Qwen3ForCausalLM", "qwen2", "Qwen2ForCausalLM", "llama", "LlamaForCausalLM",
            "olmo2", "Olmo2ForCausalLM", "qwen3_moe", "Qwen3MoeForCausalLM", "glm4_moe",
            "Glm4MoeForCausalLM", "gpt_oss", "GptOssForCausalLM", "deepseek_v3",
-           "DeepseekV3ForCausalLM", "minimax_m3", "nemotron_h", "qwen3_5", "qwen3_5_moe", "glm5",
-           "deepseek_v4"):
+           "DeepseekV3ForCausalLM"):
     MODEL_REGISTRY[_n] = _decoder
+
+# Families of the reference whose token mixers are not built here (linear-attention / state-space
+# mixers, sparse-index attention, hyper-connections).  Asking for one fails loudly instead of
+# training a different architecture under the same name.
+UNSUPPORTED = {
+    "qwen3_5": "GatedDeltaNet linear-attention layers", "qwen3_5_moe": "GatedDeltaNet linear-attention layers",
+    "nemotron_h": "Mamba2 state-space layers", "glm5": "MLA with the DSA sparse indexer",
+    "deepseek_v4": "compressed sparse attention and hyper-connections", "minimax_m3": "its attention variant",
+}
 
 
 def get_model_class(cfg):
     for key in [cfg.model_type] + list(cfg.architectures or []):
         if key in MODEL_REGISTRY:
             return MODEL_REGISTRY[key]()
+    if cfg.model_type in UNSUPPORTED:
+        raise NotImplementedError(f"model_type {cfg.model_type!r} needs {UNSUPPORTED[cfg.model_type]}, "
+                                  f"which this framework does not implement")
     raise KeyError(f"no model registered for model_type={cfg.model_type!r} "
                    f"architectures={cfg.architectures}")

@@ -24,27 +24,39 @@ def launch_count() -> int:
 # --------------------------------------------------------------------------------------------
 # Reference implementations (CPU lane and test oracle)
 # --------------------------------------------------------------------------------------------
-def attention_reference(q, k, v, cu_seqlens, causal=True, scale=None):
-    """Plain fp32 attention over packed sequences. q [T,Hq,D], k/v [T,Hkv,D]."""
+def attention_reference(q, k, v, cu_seqlens, causal=True, scale=None, window=None, sinks=None):
+    """Plain fp32 attention over packed sequences. q [T,Hq,D], k [T,Hkv,D], v [T,Hkv,Dv].
+    ``window``: a query sees only the last ``window`` keys (itself included).  ``sinks`` fp32 [Hq]:
+    one extra logit per head that joins the softmax denominator but contributes no value
+    (attention sinks of gpt-oss)."""
     T, Hq, D = q.shape
-    Hkv = k.shape[1]
+    Hkv, Dv = k.shape[1], v.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    out = torch.empty_like(q)
+    out = torch.empty((T, Hq, Dv), dtype=q.dtype, device=q.device)
     cu = cu_seqlens.tolist()
     g = Hq // Hkv
     for b in range(len(cu) - 1):
         s, e = cu[b], cu[b + 1]
         if e <= s:
             continue
+        L = e - s
         qb = q[s:e].float().transpose(0, 1)                      # [Hq, L, D]
         kb = k[s:e].float().transpose(0, 1).repeat_interleave(g, 0)
         vb = v[s:e].float().transpose(0, 1).repeat_interleave(g, 0)
         sc = torch.matmul(qb, kb.transpose(1, 2)) * scale
-        if causal:
-            L = e - s
-            mask = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+        if causal or window:
+            i = torch.arange(L, device=q.device)
+            mask = torch.ones(L, L, dtype=torch.bool, device=q.device)
+            if causal:
+                mask &= i[:, None] >= i[None, :]
+            if window:
+                mask &= (i[:, None] - i[None, :]) < window
             sc = sc.masked_fill(~mask, float("-inf"))
-        p = torch.softmax(sc, dim=-1)
+        if sinks is not None:
+            sink = sinks.float().view(Hq, 1, 1).expand(Hq, L, 1)
+            p = torch.softmax(torch.cat([sc, sink], -1), dim=-1)[..., :L]
+        else:
+            p = torch.softmax(sc, dim=-1)
         out[s:e] = torch.matmul(p, vb).transpose(0, 1).to(q.dtype)
     return out
 

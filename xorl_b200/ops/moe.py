@@ -29,13 +29,33 @@ def launch_count() -> int:
 # routing
 # --------------------------------------------------------------------------------------------
 def topk_route(logits: torch.Tensor, k: int, renorm: bool = True, scoring: str = "softmax",
-               scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """fp32 logits [T, E] -> (weights [T, k], indices [T, k], probs [T, E])."""
+               scale: float = 1.0, n_group: int = 1, topk_group: int = 1,
+               correction_bias: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """fp32 logits [T, E] -> (weights [T, k], indices [T, k], probs [T, E]).
+
+    ``scoring`` "softmax" (Qwen/Mixtral style), "sigmoid" (DeepSeek-V3 / GLM-4.5 style) or
+    "softmax_after_topk" (gpt-oss: softmax over the k selected logits).  With ``correction_bias``
+    the *selection* uses ``probs + bias`` while the weights stay the unbiased scores (auxiliary-loss
+    free balancing); with ``n_group > 1`` experts are chosen only inside the ``topk_group`` groups
+    with the best sum of their two best biased scores (src/xorl/models/layers/moe/router.py)."""
+    if scoring == "softmax_after_topk":
+        top, indices = torch.topk(logits, k, dim=-1)
+        weights = torch.softmax(top, dim=-1, dtype=torch.float32)
+        probs = torch.softmax(logits, dim=-1, dtype=torch.float32)
+        return weights * scale if scale != 1.0 else weights, indices, probs
     if scoring == "sigmoid":
         probs = torch.sigmoid(logits)
     else:
         probs = torch.softmax(logits, dim=-1, dtype=torch.float32)
-    weights, indices = torch.topk(probs, k, dim=-1)
+    choice = probs if correction_bias is None else probs + correction_bias.float().unsqueeze(0)
+    if n_group > 1:
+        T, E = choice.shape
+        grouped = choice.view(T, n_group, E // n_group)
+        gscore = grouped.topk(min(2, E // n_group), dim=-1)[0].sum(-1)          # [T, n_group]
+        keep = torch.zeros_like(gscore, dtype=torch.bool).scatter_(1, gscore.topk(topk_group, dim=-1)[1], True)
+        choice = grouped.masked_fill(~keep.unsqueeze(-1), float("-inf")).view(T, E)
+    _, indices = torch.topk(choice, k, dim=-1)
+    weights = probs.gather(1, indices)
     if renorm:
         weights = weights / weights.sum(-1, keepdim=True).clamp_min(1e-20)
     if scale != 1.0:
@@ -175,22 +195,49 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg: torch.Tensor) -> torch
     return torch.cat(outs, 0) if outs else x.new_zeros((0, w.shape[2]))
 
 
+def _rows_to_expert(seg: torch.Tensor, rows: int) -> torch.Tensor:
+    """Expert index of every row of a segment-aligned buffer (rows past the last segment -> last)."""
+    r = torch.arange(rows, device=seg.device)
+    return (torch.bucketize(r, seg[1:].long(), right=True)).clamp_max(seg.numel() - 2)
+
+
+def clamped_swiglu(h: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.Tensor:
+    """gpt-oss activation on a fused [gate | up] tensor: (up.clamp(+-limit) + 1) * gate' * sigmoid(alpha gate')
+    with gate' = gate.clamp(max=limit)."""
+    gate, up = h.float().chunk(2, dim=-1)
+    gate = gate.clamp(max=limit)
+    up = up.clamp(min=-limit, max=limit)
+    return ((up + 1.0) * gate * torch.sigmoid(alpha * gate)).to(h.dtype)
+
+
 def expert_mlp_aligned(x_buf: torch.Tensor, seg: torch.Tensor, gate_up: torch.Tensor,
-                       down: torch.Tensor) -> torch.Tensor:
-    """SwiGLU expert MLP over a segment-aligned token buffer."""
+                       down: torch.Tensor, gate_up_bias: Optional[torch.Tensor] = None,
+                       down_bias: Optional[torch.Tensor] = None,
+                       swiglu_limit: Optional[float] = None) -> torch.Tensor:
+    """SwiGLU expert MLP over a segment-aligned token buffer (optional per-expert biases and the
+    clamped activation of gpt-oss)."""
     h = grouped_linear(x_buf, gate_up, seg)
-    return grouped_linear(swiglu(h), down, seg)
+    if gate_up_bias is None and swiglu_limit is None:
+        return grouped_linear(swiglu(h), down, seg)
+    eid = _rows_to_expert(seg, h.shape[0])
+    if gate_up_bias is not None:
+        h = h + gate_up_bias.index_select(0, eid).to(h.dtype)
+    a = clamped_swiglu(h, swiglu_limit) if swiglu_limit is not None else swiglu(h)
+    y = grouped_linear(a, down, seg)
+    if down_bias is not None:
+        y = y + down_bias.index_select(0, eid[: y.shape[0]]).to(y.dtype)
+    return y
 
 
 def expert_mlp(x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor, gate_up: torch.Tensor,
-               down: torch.Tensor) -> torch.Tensor:
+               down: torch.Tensor, **kw) -> torch.Tensor:
     """Unaligned variant (rows exactly grouped by expert): pads to aligned segments internally."""
     E = gate_up.shape[0]
     ids = torch.repeat_interleave(torch.arange(E, device=x_sorted.device), tokens_per_expert)
     dest, seg, _ = aligned_sort_indices(ids, E)
     buf = x_sorted.new_zeros((buffer_rows(x_sorted.shape[0], E), x_sorted.shape[1]))
     buf = buf.index_copy(0, dest, x_sorted)
-    out = expert_mlp_aligned(buf, seg, gate_up, down)
+    out = expert_mlp_aligned(buf, seg, gate_up, down, **kw)
     return out.index_select(0, dest)
 
 
@@ -204,7 +251,7 @@ def local_moe_forward(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
     rows = buffer_rows(T * k, num_experts)
     token_of_slot = torch.arange(T, device=x.device).repeat_interleave(k)
     buf = x.new_zeros((rows, H)).index_copy(0, dest, x.index_select(0, token_of_slot))
-    y = expert_mlp_aligned(buf, seg, experts.gate_up_proj, experts.down_proj)
+    y = expert_mlp_aligned(buf, seg, experts.gate_up_proj, experts.down_proj, **experts.mlp_kwargs())
     y_slots = y.index_select(0, dest).reshape(T, k, H)
     out = (y_slots.float() * weights.unsqueeze(-1).float()).sum(1)
     return out.to(x.dtype)

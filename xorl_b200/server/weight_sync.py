@@ -26,7 +26,7 @@ from typing import Any, Callable, Dict, Iterator, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from ..checkpoint.handlers import CheckpointHandler
+from ..checkpoint.handlers import get_checkpoint_handler
 from ..ops import _lib
 from ..ops import quantize as Q
 
@@ -114,7 +114,7 @@ def iter_sync_tensors(engine, cfg, dtype=torch.bfloat16, quantization: Optional[
                       ) -> Iterator[Tuple[str, torch.Tensor]]:
     """(engine-side name, tensor) for every weight, in model order.  All ranks of the shard groups
     must iterate together (the gathers are collectives); only the consumer on rank 0 uses them."""
-    handler = CheckpointHandler(cfg)
+    handler = get_checkpoint_handler(cfg)
     for fqn, full in engine.iter_full_tensors("master"):
         if ".lora_" in fqn:
             continue
