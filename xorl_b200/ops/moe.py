@@ -229,6 +229,12 @@ def expert_mlp_aligned(x_buf: torch.Tensor, seg: torch.Tensor, gate_up: torch.Te
     return y
 
 
+def experts_mlp_kwargs(experts) -> dict:
+    """Bias / activation options of an experts holder (plain holders without them -> {})."""
+    fn = getattr(experts, "mlp_kwargs", None)
+    return fn() if callable(fn) else {}
+
+
 def expert_mlp(x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor, gate_up: torch.Tensor,
                down: torch.Tensor, **kw) -> torch.Tensor:
     """Unaligned variant (rows exactly grouped by expert): pads to aligned segments internally."""
@@ -251,7 +257,7 @@ def local_moe_forward(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
     rows = buffer_rows(T * k, num_experts)
     token_of_slot = torch.arange(T, device=x.device).repeat_interleave(k)
     buf = x.new_zeros((rows, H)).index_copy(0, dest, x.index_select(0, token_of_slot))
-    y = expert_mlp_aligned(buf, seg, experts.gate_up_proj, experts.down_proj, **experts.mlp_kwargs())
+    y = expert_mlp_aligned(buf, seg, experts.gate_up_proj, experts.down_proj, **experts_mlp_kwargs(experts))
     y_slots = y.index_select(0, dest).reshape(T, k, H)
     out = (y_slots.float() * weights.unsqueeze(-1).float()).sum(1)
     return out.to(x.dtype)

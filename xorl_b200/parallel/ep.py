@@ -68,7 +68,7 @@ def _alltoall_forward(x, weights, indices, experts, num_experts, ctx):
     rows = moe_ops.buffer_rows(recv.shape[0], El)
     buf = recv.new_zeros((rows, H)).index_copy(0, dest, recv)
     y = moe_ops.expert_mlp_aligned(buf, seg, experts.gate_up_proj, experts.down_proj,
-                                   **experts.mlp_kwargs())
+                                   **moe_ops.experts_mlp_kwargs(experts))
     back = y.index_select(0, dest)
     ret = _AllToAll.apply(back, in_splits, out_splits, group)                  # sorted-slot order
     y_slots = _unsort(ret, order)

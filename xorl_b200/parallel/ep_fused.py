@@ -212,7 +212,7 @@ def fused_ep_forward(x, weights, indices, experts, num_experts, ctx):
     plan = _make_plan(ws, indices)
     buf = _Dispatch.apply(x, ws, plan)
     y = moe_ops.expert_mlp_aligned(buf, plan.seg, experts.gate_up_proj, experts.down_proj,
-                                   **experts.mlp_kwargs())
+                                   **moe_ops.experts_mlp_kwargs(experts))
     y_slots = _Return.apply(y, ws, plan)
     out = (y_slots.view(T, k, H).float() * weights.unsqueeze(-1).float()).sum(1)
     return out.to(x.dtype)
