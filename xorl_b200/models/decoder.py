@@ -83,7 +83,17 @@ class DecoderLM(nn.Module):
         self.layers = nn.ModuleDict({str(i): DecoderLayer(cfg, i, dtype, device) for i in idx})
         if has_head:
             self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.zero_centered_norm, dtype, device)
-            self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, bias=False, dtype=dtype, device=device)
+            from ..parallel.tp import tp_info
+            tp, tp_rank, tp_group = tp_info()
+            # untied heads are sharded by vocabulary rows over the tensor-parallel group and use
+            # the vocab-parallel loss; tied heads stay replicated with the embedding
+            self.vocab_parallel = tp > 1 and not cfg.tie_word_embeddings and cfg.vocab_size % tp == 0
+            self.head_tp = (tp, tp_rank, tp_group)
+            v_local = cfg.vocab_size // tp if self.vocab_parallel else cfg.vocab_size
+            self.lm_head = Linear(cfg.hidden_size, v_local, bias=False, dtype=dtype, device=device)
+            if self.vocab_parallel:
+                from ..parallel.tp import mark_col
+                mark_col(self.lm_head.weight, (cfg.vocab_size, cfg.hidden_size), (cfg.vocab_size,))
         if cfg.tie_word_embeddings and has_embed and has_head:
             self.lm_head.weight = self.embed_tokens.weight
         elif cfg.tie_word_embeddings and (has_embed != has_head):
@@ -146,6 +156,12 @@ class DecoderLM(nn.Module):
                   return_token_losses: bool = False):
         """grad_scale * sum of token cross-entropies (labels == -100 ignored)."""
         hidden = self.forward_head(h, residual, ctx)
+        if getattr(self, "vocab_parallel", False):
+            tp, tp_rank, tp_group = self.head_tp
+            loss = loss_ops.vocab_parallel_linear_cross_entropy(
+                hidden, self.lm_head.weight, labels.reshape(-1), tp_group,
+                tp_rank * (self.config.vocab_size // tp), grad_scale, self.loss_chunk_tokens)
+            return (loss, None) if return_token_losses else loss
         return loss_ops.fused_linear_cross_entropy(hidden, self.lm_head.weight, labels.reshape(-1),
                                                    grad_scale, self.loss_chunk_tokens,
                                                    return_token_losses=return_token_losses)

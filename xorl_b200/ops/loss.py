@@ -223,3 +223,111 @@ class _TokenLossBackward(torch.autograd.Function):
         dw = deliver_param_grad(ctx.weight, ctx.dw_local * g) if ctx.dw_local is not None else None
         ctx.dh = ctx.dw_local = None
         return dh, dw, None, None, None, None, None, None
+
+
+# --------------------------------------------------------------------------------------------
+# vocab-parallel head (tensor-parallel lm-head)
+# --------------------------------------------------------------------------------------------
+class _VocabParallelLinearCE(torch.autograd.Function):
+    """Every rank of ``group`` holds rows [vocab_start, vocab_start + V_local) of the lm-head and
+    the same hidden states.  Per chunk: local logits -> (max, sum-exp, target logit) -> three small
+    all-reduces give the global log-sum-exp -> local gradient of the logits -> partial hidden
+    gradient (all-reduced over the group at the end) and this rank's rows of the weight gradient.
+    The full [T, V] logits never exist on any rank (src/xorl/ops/loss/vocab_parallel_cross_entropy.py)."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, group, vocab_start, grad_scale, chunk_tokens, ignore_index):
+        import torch.distributed as dist
+        global _launches
+        T, H = hidden.shape
+        Vl = weight.shape[0]
+        cuda = hidden.is_cuda and hidden.dtype == torch.bfloat16
+        need_dh, need_dw = hidden.requires_grad, weight.requires_grad
+        dh = torch.zeros_like(hidden, dtype=torch.float32 if not cuda else hidden.dtype) if need_dh else None
+        tgt, fresh = grad_target(weight) if (need_dw and cuda) else (None, False)
+        dw_local = torch.zeros((Vl, H), device=hidden.device, dtype=torch.float32) if (need_dw and tgt is None) else None
+        total = torch.zeros((), device=hidden.device, dtype=torch.float32)
+        ldv = (Vl + 7) // 8 * 8
+        buf = torch.empty((min(chunk_tokens, T), ldv), device=hidden.device, dtype=torch.bfloat16) if cuda else None
+        first = True
+        for s in range(0, T, chunk_tokens):
+            e = min(T, s + chunk_tokens)
+            h, lab = hidden[s:e], labels[s:e]
+            valid = lab != ignore_index
+            if cuda:
+                logits = buf[: e - s, :Vl]
+                gemm(h, weight, out=logits)
+                stats = torch.empty((e - s, 3), device=h.device, dtype=torch.float32)
+                _lib.check(_lib.cuda_lib().xb_cross_entropy_vp_stats(
+                    logits.data_ptr(), logits.stride(0), lab.data_ptr(), stats.data_ptr(), e - s, Vl,
+                    int(vocab_start), ignore_index, _lib.stream_ptr()), "xb_cross_entropy_vp_stats")
+                _launches += 1
+                m, se, tl = stats[:, 0].contiguous(), stats[:, 1].contiguous(), stats[:, 2].contiguous()
+            else:
+                logits = F.linear(h, weight).float()
+                m = logits.max(-1).values
+                se = torch.exp(logits - m[:, None]).sum(-1)
+                lt = lab - vocab_start
+                mine = valid & (lt >= 0) & (lt < Vl)
+                tl = torch.where(mine, logits.gather(1, lt.clamp(0, Vl - 1)[:, None])[:, 0], torch.zeros_like(m))
+            gm = m.clone()
+            dist.all_reduce(gm, op=dist.ReduceOp.MAX, group=group)
+            se = se * torch.exp(m - gm)
+            packed = torch.stack([se, tl])
+            dist.all_reduce(packed, group=group)
+            lse = gm + torch.log(packed[0])
+            total = total + torch.where(valid, lse - packed[1], torch.zeros_like(lse)).sum()
+            if not (need_dh or need_dw):
+                continue
+            if cuda:
+                _lib.check(_lib.cuda_lib().xb_cross_entropy_vp_grad(
+                    logits.data_ptr(), logits.stride(0), lab.data_ptr(), lse.contiguous().data_ptr(), e - s, Vl,
+                    int(vocab_start), ignore_index, float(grad_scale), _lib.stream_ptr()), "xb_cross_entropy_vp_grad")
+                _launches += 1
+                g = logits
+                if need_dh:
+                    gemm(g, weight, b_mn=True, out=dh[s:e])
+                if need_dw:
+                    if tgt is not None:
+                        gemm(g, h, a_mn=True, b_mn=True, out=tgt, accumulate=not (fresh and first))
+                    else:
+                        gemm(g, h, a_mn=True, b_mn=True, out=dw_local, accumulate=True)
+            else:
+                g = torch.exp(logits - lse[:, None])
+                lt = lab - vocab_start
+                mine = valid & (lt >= 0) & (lt < Vl)
+                rows = torch.nonzero(mine)[:, 0]
+                g[rows, lt[rows]] -= 1.0
+                g = g * (valid[:, None] * grad_scale)
+                if need_dh:
+                    dh[s:e] = g @ weight.float()
+                if need_dw:
+                    dw_local += g.t() @ h.float()
+            first = False
+        if need_dh:
+            dist.all_reduce(dh, group=group)
+        if need_dw and tgt is not None:
+            mark_written(weight)
+        ctx.dh, ctx.dw_local, ctx.weight = dh, dw_local, weight
+        ctx.h_dtype = hidden.dtype
+        return total * grad_scale
+
+    @staticmethod
+    def backward(ctx, g):
+        dh = (ctx.dh * g).to(ctx.h_dtype) if ctx.dh is not None else None
+        dw = None
+        if ctx.dw_local is not None:
+            dw = deliver_param_grad(ctx.weight, ctx.dw_local * g)
+        ctx.dh = ctx.dw_local = None
+        return dh, dw, None, None, None, None, None, None
+
+
+def vocab_parallel_linear_cross_entropy(hidden, weight_shard, labels, group, vocab_start: int,
+                                        grad_scale: float = 1.0, chunk_tokens: int = 1024,
+                                        ignore_index: int = IGNORE_INDEX):
+    """``grad_scale * sum_t CE`` with the lm-head sharded by vocabulary rows over ``group``; the
+    hidden states (and labels) are replicated over the group.  Back-propagate the result with an
+    upstream gradient of 1, as for ``fused_linear_cross_entropy``."""
+    return _VocabParallelLinearCE.apply(hidden.reshape(-1, hidden.shape[-1]), weight_shard, labels.reshape(-1),
+                                        group, int(vocab_start), float(grad_scale), int(chunk_tokens),
+                                        int(ignore_index))
