@@ -1,0 +1,63 @@
+"""Preprocess and export command-line tools on CPU."""
+import json
+import os
+import sys
+
+import torch
+import yaml
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def test_preprocess_cli(tmp_path):
+    from xorl_b200.cli.preprocess import main
+    rows = [{"input_ids": list(range(5, 5 + n))} for n in (30, 90, 60, 120, 10)]
+    with open(tmp_path / "d.jsonl", "w") as f:
+        for r in rows:
+            f.write(json.dumps(r) + "\n")
+    cfg = {"model": {"config_path": "tiny-qwen3"},
+           "data": {"datasets": [{"path": str(tmp_path / "d.jsonl"), "type": "tokenized", "max_seq_len": 100}],
+                    "sample_packing_sequence_len": 128, "dataset_prepared_path": str(tmp_path / "prep")},
+           "train": {"output_dir": str(tmp_path / "o"), "device": "cpu"}}
+    (tmp_path / "c.yaml").write_text(yaml.safe_dump(cfg))
+    out = main([str(tmp_path / "c.yaml")])
+    meta = json.load(open(os.path.join(out, "meta.json")))
+    pk = json.load(open(os.path.join(out, "packing.json")))
+    assert meta["num_samples"] == 5 and meta["total_tokens"] == 30 + 90 + 60 + 100 + 10
+    assert sorted(i for b in pk["bins"] for i in b) == [0, 1, 2, 3, 4] and meta["num_bins"] == 3
+    from xorl_b200.data.datasets import prepare_datasets
+    ds = prepare_datasets([{"path": os.path.join(out, "data.arrow"), "type": "tokenized"}])
+    assert len(ds) == 5 and len(ds[3]["input_ids"]) == 100
+
+
+def test_export_quantized_roundtrip(tmp_path):
+    from safetensors.torch import load_file, save_file
+    from xorl_b200.cli import export_nvfp4, export_quantized
+    from xorl_b200.ops import quantize as Q
+    torch.manual_seed(0)
+    src = tmp_path / "src"
+    os.makedirs(src)
+    w = {"model.layers.0.self_attn.q_proj.weight": torch.randn(256, 128).bfloat16(),
+         "model.layers.0.mlp.down_proj.weight": torch.randn(128, 384).bfloat16(),
+         "model.norm.weight": torch.ones(128).bfloat16(),
+         "lm_head.weight": torch.randn(512, 128).bfloat16()}
+    save_file(w, str(src / "model.safetensors"))
+    (src / "config.json").write_text(json.dumps({"model_type": "qwen3", "hidden_size": 128}))
+    st = export_quantized.main(["--src", str(src), "--dst", str(tmp_path / "fp8"), "--format", "block_fp8"])
+    assert st["quantized"] == 2 and st["kept"] == 2 and st["bytes_out"] < st["bytes_in"]
+    out = load_file(str(tmp_path / "fp8" / "model-00001.safetensors"))
+    q = out["model.layers.0.self_attn.q_proj.weight"]
+    s = out["model.layers.0.self_attn.q_proj.weight_scale_inv"]
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (2, 1)
+    back = Q.block_fp8_dequantize_128x128(q, s, dtype=torch.float32)
+    ref = w["model.layers.0.self_attn.q_proj.weight"].float()
+    assert (back - ref).norm() / ref.norm() < 0.05
+    assert torch.equal(out["lm_head.weight"], w["lm_head.weight"])
+    cfg = json.load(open(tmp_path / "fp8" / "config.json"))
+    assert cfg["quantization_config"]["weight_block_size"] == [128, 128] and cfg["hidden_size"] == 128
+    export_nvfp4.main(["--src", str(src), "--dst", str(tmp_path / "fp4")])
+    out4 = load_file(str(tmp_path / "fp4" / "model-00001.safetensors"))
+    k = "model.layers.0.mlp.down_proj.weight"
+    back4 = Q.nvfp4_dequantize(out4[k], out4[k + "_scale"], out4[k + "_scale_2"][0], (128, 384), dtype=torch.float32)
+    assert (back4 - w[k].float()).norm() / w[k].float().norm() < 0.15
+    assert json.load(open(tmp_path / "fp4" / "config.json"))["quantization_config"]["format"] == "nvfp4"
