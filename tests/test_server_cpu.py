@@ -306,3 +306,92 @@ def test_dispatcher_two_ranks_agree_on_errors(tmp_path):
     from dist_utils import run_distributed
     out = run_distributed(os.path.join(os.path.dirname(__file__), "server_dispatch_worker.py"), 2, str(tmp_path))
     assert "DISPATCH_OK" in out
+
+
+def _lora_runner(tmp_path, preset="tiny-qwen3"):
+    from xorl_b200.parallel.state import reset_parallel_state
+    from xorl_b200.server.runner import ModelRunner
+    from xorl_b200.server.server_arguments import ServerArguments
+    from xorl_b200.trainers.trainer import Trainer
+    reset_parallel_state()
+    sa = ServerArguments(model_preset=preset, output_dir=str(tmp_path / "srv"), device="cpu",
+                         sample_packing_sequence_len=256, enable_mixed_precision=False, enable_lora=True,
+                         lora_rank=4, lora_alpha=8)
+    return ModelRunner(Trainer(sa.to_trainer_arguments()))
+
+
+def test_multi_tenant_adapters_are_isolated(tmp_path):
+    os.environ["XORL_MAX_ADAPTERS_PER_MODEL"] = "2"
+    try:
+        r = _lora_runner(tmp_path)
+        data = [{"tokens": list(range(3, 60))}]
+
+        def lp(mid):
+            return r.forward(mid, data, None)["logprobs"][0]
+
+        def train(mid, steps):
+            for _ in range(steps):
+                r.forward_backward(mid, data, None)
+                r.optim_step(mid, adam_params={"learning_rate": 5e-3})
+
+        base = lp("default")
+        r.create_model("a")
+        r.create_model("b")
+        assert lp("a") == base and lp("b") == base            # fresh adapters start as the base model
+        train("a", 3)
+        la = lp("a")
+        assert max(abs(x - y) for x, y in zip(la, base)) > 1e-3
+        assert lp("b") == base and lp("default") == base      # a's training moved nothing else
+        train("b", 2)
+        assert lp("a") == la                                   # ... and b's training did not move a
+        # an open gradient epoch survives a switch to another adapter and back
+        r.forward_backward("a", data, None)
+        tokens_a = r.accumulated_tokens
+        r.forward_backward("b", data, None)
+        r.abort_gradient_epoch("b")
+        m = r.optim_step("a", adam_params={"learning_rate": 5e-3})["metrics"]
+        assert m["tokens"] == tokens_a and m["step"] == 4.0
+        # three adapters with a cap of two in memory: the least recently used one went to disk and comes back
+        assert os.path.isdir(os.path.join(r.output_dir, "adapter_spill"))
+        assert lp("default") == base
+        r.unload_model("b")
+        with pytest.raises(KeyError):
+            r.forward("b", data, None)
+    finally:
+        del os.environ["XORL_MAX_ADAPTERS_PER_MODEL"]
+        from xorl_b200.parallel.state import reset_parallel_state
+        reset_parallel_state()
+
+
+def test_rollout_routing_replay(tmp_path):
+    from xorl_b200.parallel.state import reset_parallel_state
+    from xorl_b200.server.runner import ModelRunner
+    from xorl_b200.server.server_arguments import ServerArguments
+    from xorl_b200.trainers.trainer import Trainer
+    reset_parallel_state()
+    sa = ServerArguments(model_preset="tiny-qwen3-moe", output_dir=str(tmp_path / "srv"), device="cpu",
+                         sample_packing_sequence_len=128, enable_mixed_precision=False)
+    r = ModelRunner(Trainer(sa.to_trainer_arguments()))
+    toks = list(range(5, 45))
+    free = r.forward_backward("default", [{"tokens": toks}], None)["loss"]
+    r.abort_gradient_epoch()
+    # force every token of both MoE layers to experts (0, 1): a different (worse or equal) loss, and
+    # the load statistics must show only those two experts
+    forced = [[[0, 1], [0, 1]] for _ in toks]
+    r.model.ctx_defaults["collect_expert_load"] = True
+    seen = {}
+    orig = r.engine.make_step_context
+
+    def spy(*a, **k):
+        ctx = orig(*a, **k)
+        seen["ctx"] = ctx
+        return ctx
+
+    r.engine.make_step_context = spy
+    out = r.forward_backward("default", [{"tokens": toks, "routed_experts": forced}], None)
+    loads = [v for k, v in seen["ctx"].aux.items() if isinstance(k, tuple) and k[0] == "expert_load"]
+    pad = 128 - len(toks)                                   # padding rows keep the router's own choice
+    assert loads and all(int(l[0]) >= len(toks) and int(l[1]) >= len(toks) and int(l[2:].sum()) <= 2 * pad
+                         for l in loads)
+    assert abs(out["loss"] - free) > 1e-6
+    reset_parallel_state()

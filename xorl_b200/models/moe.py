@@ -94,11 +94,17 @@ class MoEBlock(nn.Module):
             self.shared_expert = MLP(cfg.hidden_size, cfg.shared_expert_intermediate_size,
                                      dtype=dtype, device=device)
         self.aux_coef = cfg.router_aux_loss_coef
+        self.moe_ordinal = sum(cfg.layer_is_moe(i) for i in range(layer_idx))
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H = x.shape
         replay = ctx.aux.get(("routing_replay", self.layer_idx))
         weights, indices, probs = self.gate(x)
+        allr = ctx.aux.get("routing_replay_all")
+        if replay is None and allr is not None:
+            # rollout routing replay: [T, moe_layers, k]; rows of -1 keep the router's own choice
+            r = allr[:, self.moe_ordinal]
+            replay = torch.where(r >= 0, r, indices)
         if replay is not None:
             # replay recorded expert choices (recompute / pipeline backward / rollout routing);
             # the weights are re-derived from the current probabilities so gradients still flow

@@ -122,6 +122,12 @@ class LocalBackend(Backend):
     def abort_gradient_epoch(self, model_id, **kw):
         return self.runner.abort_gradient_epoch(model_id)
 
+    def create_model(self, model_id, **kw):
+        return self.runner.create_model(model_id, **kw)
+
+    def unload_model(self, model_id, **kw):
+        return self.runner.unload_model(model_id, **kw)
+
     def sleep(self, model_id="default", **kw):
         return self.runner.sleep()
 

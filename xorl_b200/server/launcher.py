@@ -21,7 +21,7 @@ from .runner import ModelRunner, RunnerDispatcher
 from .server_arguments import ServerArguments
 
 _OPS = ("forward_backward", "forward", "optim_step", "save_weights", "load_weights",
-        "sync_inference_weights", "abort_gradient_epoch", "sleep", "wake_up")
+        "sync_inference_weights", "abort_gradient_epoch", "sleep", "wake_up", "create_model", "unload_model")
 
 
 class DispatchBackend(Backend):
@@ -60,6 +60,12 @@ class DispatchBackend(Backend):
 
     def abort_gradient_epoch(self, model_id, **kw):
         return self._call("abort_gradient_epoch", model_id, {})
+
+    def create_model(self, model_id, **kw):
+        return self._call("create_model", model_id, kw)
+
+    def unload_model(self, model_id, **kw):
+        return self._call("unload_model", model_id, kw)
 
     def shutdown(self):
         with self._lock:

@@ -62,6 +62,7 @@ def datums_to_micro_batch(datums: List[Dict[str, Any]], pad_to: int = 128) -> Di
     Extra per-token loss inputs are concatenated the same way.  An empty list yields a dummy batch
     with every label ignored, so idle ranks still take part in the collectives."""
     ids, labels, pos, cu = [], [], [], [0]
+    routed: List[torch.Tensor] = []
     extras: Dict[str, List[float]] = {}
     for d in datums:
         toks = list(d["tokens"])
@@ -75,6 +76,9 @@ def datums_to_micro_batch(datums: List[Dict[str, Any]], pad_to: int = 128) -> Di
         pos += list(range(n))
         cu.append(cu[-1] + n)
         for k, v in d.items():
+            if k == "routed_experts":
+                routed.append(torch.tensor(v, dtype=torch.long))
+                continue
             if k in ("tokens", "target_tokens", "weights", "datum_index"):
                 continue
             extras.setdefault(k, []).extend(list(v) + [0.0] * (n - len(v)))
@@ -95,4 +99,9 @@ def datums_to_micro_batch(datums: List[Dict[str, Any]], pad_to: int = 128) -> Di
           "datum_index": [d.get("datum_index", i) for i, d in enumerate(datums)]}
     for k, v in extras.items():
         mb[k] = torch.tensor(v, dtype=torch.float32)
+    if routed and len(routed) == len(datums):
+        r = torch.cat(routed, 0)
+        if pad:
+            r = torch.cat([r, r.new_full((pad,) + tuple(r.shape[1:]), -1)], 0)
+        mb["routed_experts"] = r
     return mb

@@ -50,6 +50,7 @@ class ModelRunner:
         self.asleep = False
         self.poisoned: Optional[str] = None
         self.output_dir = trainer.args.train.output_dir
+        self.adapters = None                 # AdapterManager, created with the first extra adapter
 
     # ---- helpers --------------------------------------------------------------------------------
     def _local_batches(self, datums, plan) -> List[Dict[str, Any]]:
@@ -74,6 +75,36 @@ class ModelRunner:
             extras["old_logprobs"] = extras.pop("logprobs")
         return lambda lp, mask: fn(lp, mask, **extras, **cfg)
 
+    def _activate(self, model_id: str) -> None:
+        if self.adapters is not None:
+            self.adapters.activate(model_id)
+        elif model_id != "default":
+            raise KeyError(f"unknown model_id {model_id!r}")
+
+    def create_model(self, model_id, base_model=None, lora_config=None, **_):
+        """Registers a new named adapter (needs LoRA; the base weights are shared and frozen)."""
+        if not self.trainer.args.lora.enable_lora:
+            raise ValueError("create_model needs a server started with enable_lora")
+        if self.adapters is None:
+            from .adapters import AdapterManager
+            self.adapters = AdapterManager(self, spill_dir=os.path.join(self.output_dir, "adapter_spill"))
+        self.adapters.create(model_id)
+        return {"model_id": model_id, "adapters": self.adapters.list()}
+
+    def unload_model(self, model_id, **_):
+        if self.adapters is not None:
+            self.adapters.unload(model_id)
+        return {"model_id": model_id}
+
+    def _replay_extra(self, mb) -> Optional[Dict[str, Any]]:
+        """Rollout routing replay: ``routed_experts`` [T, moe_layers, k] recorded by the inference
+        engine forces the same expert choices in training (src/xorl/server/runner/utils/
+        routing_replay_handler.py).  Padding tokens carry -1 and keep the router's own choice."""
+        r = mb.get("routed_experts")
+        if r is None:
+            return None
+        return {"routing_replay_all": r.to(self.device).long()}
+
     def _check_usable(self) -> None:
         if self.poisoned:
             raise RuntimeError(f"runner is poisoned after a failed mutation: {self.poisoned}")
@@ -83,7 +114,11 @@ class ModelRunner:
     def preflight(self, op: str, args: Dict[str, Any]) -> None:
         """Host-only checks that may fail on one rank and not on another.  They run, and their
         outcome is agreed on by all ranks, before any rank enters the collectives of ``op``."""
-        if op in ("sleep", "wake_up", "abort_gradient_epoch"):
+        if op in ("sleep", "wake_up", "abort_gradient_epoch", "unload_model"):
+            return
+        if op == "create_model":
+            if not self.trainer.args.lora.enable_lora:
+                raise ValueError("create_model needs a server started with enable_lora")
             return
         self._check_usable()
         if op in ("forward_backward", "forward"):
@@ -99,6 +134,7 @@ class ModelRunner:
     # ---- operations -------------------------------------------------------------------------------
     def forward_backward(self, model_id, datums, plan, loss_fn="cross_entropy", loss_fn_config=None):
         self._check_usable()
+        self._activate(model_id)
         validate_token_ids(datums, self.model.config.vocab_size)
         cfg = dict(loss_fn_config or {})
         if not self.epoch_open:
@@ -125,7 +161,8 @@ class ModelRunner:
             self.model.head_loss = head
             try:
                 loss = eng.forward_backward(d["input_ids"], d["labels"], position_ids=d["position_ids"],
-                                            cu_seqlens=d["cu_seqlens"], grad_scale=1.0)
+                                            cu_seqlens=d["cu_seqlens"], grad_scale=1.0,
+                                            extra=self._replay_extra(mb))
             finally:
                 self.model.head_loss = orig
             total += float(loss)
@@ -143,6 +180,7 @@ class ModelRunner:
     @torch.no_grad()
     def forward(self, model_id, datums, plan, loss_fn="cross_entropy", loss_fn_config=None):
         self._check_usable()
+        self._activate(model_id)
         validate_token_ids(datums, self.model.config.vocab_size)
         logprobs: Dict[int, List[float]] = {}
         for mb in self._local_batches(datums, plan):
@@ -161,6 +199,7 @@ class ModelRunner:
 
     def optim_step(self, model_id, adam_params=None, gradient_clip=None, **_):
         self._check_usable()
+        self._activate(model_id)
         if not self.epoch_open:
             raise RuntimeError("optim_step without a preceding forward_backward")
         ap = adam_params or {}
@@ -188,6 +227,7 @@ class ModelRunner:
                             "learning_rate": opt.lr, "tokens": float(tokens)}}
 
     def abort_gradient_epoch(self, model_id="default"):
+        self._activate(model_id)
         self.optimizer.zero_grad()
         self.epoch_open = False
         self.accumulated_tokens = 0
@@ -202,6 +242,7 @@ class ModelRunner:
         return os.path.join(self.output_dir, "weights", model_id, path)
 
     def save_weights(self, model_id, path=None, **_):
+        self._activate(model_id)
         name = path or f"step_{self.step:06d}"
         out = self._weights_path(model_id, name)
         self.trainer.checkpointer.save(self.step, {"global_step": self.step, "runner_step": self.step}, path=out)
@@ -210,6 +251,7 @@ class ModelRunner:
         return {"path": uri, "directory": out}
 
     def load_weights(self, model_id, path, load_optimizer=True, **_):
+        self._activate(model_id)
         p = self._weights_path(model_id, path)
         if not os.path.isdir(p):
             raise ValueError(f"no saved weights at {path}")
