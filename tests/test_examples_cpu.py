@@ -15,7 +15,7 @@ def test_local_examples_parse(path, monkeypatch):
     from xorl_b200.arguments import parse_args
     from xorl_b200.models import build_model_config
     args = parse_args(argv=[path])
-    cfg = build_model_config(args)
+    cfg = build_model_config(args.model)
     assert cfg.num_hidden_layers > 0 and args.train.output_dir.startswith("outputs/")
 
 

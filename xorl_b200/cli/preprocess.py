@@ -30,11 +30,9 @@ def preprocess(args, out_dir: Optional[str] = None) -> str:
         except Exception:  # noqa: BLE001
             tok = None
     vocab = 151936
-    try:
+    if args.model.config_path or args.model.model_path:
         from ..models import build_model_config
-        vocab = build_model_config(args).vocab_size
-    except Exception:  # noqa: BLE001
-        pass
+        vocab = build_model_config(args.model).vocab_size
     ds = prepare_datasets(args.data.datasets, tokenizer=tok, vocab_size=vocab,
                           select_columns=args.data.select_columns, seed=args.train.seed)
     out_dir = out_dir or args.data.dataset_prepared_path
