@@ -100,9 +100,10 @@ def test_fused_transport_matches_nccl():
     n = min(torch.cuda.device_count(), 8)
     out = run_distributed(__file__, n, env={"NCCL_NVLS_ENABLE": "0"})
     curves = json.loads([l for l in out.splitlines() if l.startswith("CURVES ")][-1][7:])
+    # every step draws fresh uniform random tokens, so the loss stays near ln(vocab): only agreement
+    # between the two transports is meaningful (bf16 on the wire against NCCL's fp32 sum)
     for a, b in zip(curves["nccl"], curves["fused"]):
-        assert abs(a - b) < 2e-2 * abs(a), curves
-    assert curves["fused"][-1] < curves["fused"][0]
+        assert abs(a - b) < 5e-3 * abs(a), curves
 
 
 if __name__ == "__main__":
