@@ -152,10 +152,19 @@ def _make_cu(lens):
     return torch.tensor(cu, device=DEV, dtype=torch.int32)
 
 
+@pytest.fixture(params=["split", "fused"])
+def bwd_mode(request):
+    from xorl_b200.ops import _lib, attention
+    prev = attention.set_backward_mode(request.param)
+    yield request.param
+    attention.set_backward_mode(prev)
+    assert all(v == 0 for v in _lib.read_status()[:4])
+
+
 @pytest.mark.parametrize("lens,Hq,Hkv,causal", [
     ([128], 2, 1, True), ([256], 4, 2, True), ([200, 56, 384], 4, 1, True), ([1000], 8, 2, True),
-    ([300, 100], 2, 2, False), ([4096], 8, 2, True)])
-def test_flash_attention_fwd_bwd(lens, Hq, Hkv, causal):
+    ([300, 100], 2, 2, False), ([4096], 8, 2, True), ([1, 63, 65, 129, 700], 4, 2, True)])
+def test_flash_attention_fwd_bwd(lens, Hq, Hkv, causal, bwd_mode):
     from xorl_b200.ops.attention import attention_reference, flash_attn_varlen
     torch.manual_seed(0)
     D = 128

@@ -429,7 +429,29 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, long long ldo,
   if (lane == 0) delta[(size_t)h * T + t] = s;
 }
 
+static int g_split = 1;
+
 }  // namespace xb_attn_bwd_ns
+
+// 1 (default): dK / dV from the key-stationary kernel in attn_bwd_dkv.cu and dQ from the
+// query-stationary kernel in attn_bwd_dq.cu (no atomics); 0: the single kernel of this file, which
+// adds dQ partials to global memory with fp32 vector reductions.  Returns the previous setting.
+XB_API int xb_attn_bwd_set_split(int split) {
+  const int prev = xb_attn_bwd_ns::g_split;
+  xb_attn_bwd_ns::g_split = split ? 1 : 0;
+  return prev;
+}
+
+XB_API int xb_attn_bwd_dq(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                          const float* delta, float* dq, const int* cu_seqlens, const int* k_starts,
+                          long long ldq, long long ldk, long long ldv, long long lddo, int num_seqs, int T,
+                          int Tk, int Hq, int Hkv, int causal, float scale, int accumulate, int max_q_tiles,
+                          void* stream);
+XB_API int xb_attn_bwd_dkv(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                           const float* delta, float* dk, void* dv, const int* cu_seqlens, const int* k_starts,
+                           long long ldq, long long ldk, long long ldv, long long lddo, long long lddv,
+                           int num_seqs, int T, int Tk, int Hq, int Hkv, int causal, float scale, int max_tiles,
+                           void* stream);
 
 // Inputs as in xb_attn_fwd plus out / dout [T, Hq, 128] and lse [Hq, T].
 // Scratch: delta fp32 [Hq * T]; dq_accum fp32 [T * Hq * 128] (this call zeroes it).
@@ -486,6 +508,16 @@ XB_API int xb_attn_bwd_ex(const void* q, const void* k, const void* v, const voi
     const long long rows = (long long)T * Hq;
     attn_delta_kernel<<<(int)((rows + 7) / 8), 256, 0, st>>>(
         (const __nv_bfloat16*)out, ldo, (const __nv_bfloat16*)dout, lddo, delta, T, Hq);
+  }
+  if (g_split) {
+    // dq_accum is written with plain stores (added to when flags bit 0 is set); rows outside every
+    // sequence keep the zeros of the memset above
+    int rc = xb_attn_bwd_dkv(q, k, v, dout, lse, delta, dk, dv, cu_seqlens, k_starts, ldq, ldk, ldv, lddo, lddv,
+                             num_seqs, T, Tk, Hq, Hkv, causal, scale, max_tiles, stream);
+    if (rc) return rc;
+    const int q_tiles = max_tiles > 0 ? (max_tiles + 1) / 2 + num_seqs : 0;
+    return xb_attn_bwd_dq(q, k, v, dout, lse, delta, dq_accum, cu_seqlens, k_starts, ldq, ldk, ldv, lddo,
+                          num_seqs, T, Tk, Hq, Hkv, causal, scale, (flags & 1) ? 1 : 0, q_tiles, stream);
   }
   Params p;
   p.lse = lse; p.delta = delta; p.dq_accum = dq_accum; p.dk = dk;

@@ -322,6 +322,12 @@ __host__ __device__ constexpr uint32_t xb_idesc(uint32_t a_format, uint32_t b_fo
 // ---------------------------------------------------------------------------------------
 // small math / packing helpers
 // ---------------------------------------------------------------------------------------
+// 2^x on the special-function unit: one instruction (flushes denormal results to zero)
+__device__ __forceinline__ float xb_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

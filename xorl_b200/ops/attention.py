@@ -128,6 +128,14 @@ def _attn_bwd(q, k, v, out, dout, lse, cu_seqlens, causal, scale, dv_out):
     return dq, dk
 
 
+def set_backward_mode(mode: str) -> str:
+    """"split": dK/dV kernel + query-stationary dQ kernel without atomics (default); "fused": one
+    kernel that reduces dQ partials into global memory.  Returns the previous mode."""
+    assert mode in ("split", "fused")
+    prev = _lib.cuda_lib().xb_attn_bwd_set_split(1 if mode == "split" else 0)
+    return "split" if prev else "fused"
+
+
 def _kernel_ok(t: torch.Tensor, D: int) -> bool:
     return t.is_cuda and t.dtype == torch.bfloat16 and D == 128
 

@@ -76,7 +76,9 @@ def bench_fp8_gemm(a) -> Dict:
 
 
 def bench_attn(a) -> Dict:
+    from ..ops import attention as attn_mod
     from ..ops.attention import flash_attn_varlen
+    attn_mod.set_backward_mode(a.attn_bwd)
     T, Hq, Hkv, D = a.tokens, a.heads, a.kv_heads, 128
     q = torch.randn(T, Hq, D, device="cuda").bfloat16().requires_grad_()
     k = torch.randn(T, Hkv, D, device="cuda").bfloat16().requires_grad_()
@@ -99,7 +101,7 @@ def bench_attn(a) -> Dict:
 
     fwd()
     ms_b = _time(bwd, a.warmup, a.iters, a.flush)
-    r = {"kernel": "flash_attn", "tokens": T, "heads": Hq, "kv_heads": Hkv, "docs": len(lens), "fwd_ms": ms_f,
+    r = {"kernel": "flash_attn", "bwd_mode": a.attn_bwd, "tokens": T, "heads": Hq, "kv_heads": Hkv, "docs": len(lens), "fwd_ms": ms_f,
          "fwd_tflops": fl / ms_f / 1e9, "bwd_ms": ms_b, "bwd_tflops": 2.5 * fl / ms_b / 1e9}
     if not a.no_lib:
         try:
@@ -157,6 +159,7 @@ def main(argv=None) -> None:
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--doc-len", type=int, default=0)
+    ap.add_argument("--attn-bwd", choices=["split", "fused"], default="split")
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--numel", type=int, default=1 << 28)
     ap.add_argument("--warmup", type=int, default=3)
