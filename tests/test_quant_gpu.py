@@ -109,3 +109,27 @@ def test_muon_newton_schulz_on_tcgen05_gemm():
     assert sv.min() > 0.5 and sv.max() < 1.3
     assert (X.cpu() - Xc).norm() / Xc.norm() < 0.05
     assert (X - Y).norm() / X.norm() < 0.06
+
+
+@pytest.mark.parametrize("scoring,renorm,E,k,bias", [("softmax", True, 128, 8, False), ("softmax", False, 8, 2, False),
+                                                     ("sigmoid", True, 256, 8, True), ("softmax_after_topk", False, 32, 4, False),
+                                                     ("softmax", True, 60, 3, False)])
+def test_moe_route_kernel_matches_torch(scoring, renorm, E, k, bias, monkeypatch):
+    from xorl_b200.ops import moe
+    torch.manual_seed(E + k)
+    T = 1000
+    logits = torch.randn(T, E, device="cuda")
+    cb = torch.randn(E, device="cuda") * 0.3 if bias else None
+    a = logits.clone().requires_grad_()
+    w, idx, probs = moe.topk_route(a, k, renorm, scoring, 2.5, correction_bias=cb)           # kernel
+    monkeypatch.setenv("XORL_B200_ROUTE_KERNEL", "0")
+    b = logits.clone().requires_grad_()
+    w2, idx2, probs2 = moe.topk_route(b, k, renorm, scoring, 2.5, correction_bias=cb)        # torch ops
+    assert torch.equal(idx.sort(-1).values, idx2.sort(-1).values)
+    torch.testing.assert_close(probs, probs2, rtol=1e-5, atol=1e-6)
+    o1, o2 = idx.argsort(-1), idx2.argsort(-1)
+    torch.testing.assert_close(w.gather(1, o1), w2.gather(1, o2), rtol=1e-5, atol=1e-6)
+    gw, gp = torch.randn_like(w), torch.randn_like(probs)
+    ((w.gather(1, o1) * gw).sum() + (probs * gp).sum()).backward()
+    ((w2.gather(1, o2) * gw).sum() + (probs2 * gp).sum()).backward()
+    torch.testing.assert_close(a.grad, b.grad, rtol=1e-4, atol=1e-5)

@@ -61,6 +61,7 @@ _SIGNATURES = {
     "xb_ep_prepare_recv": [P, P, P, P, I, I, I, P],
     "xb_ep_push_rows": [P, L, P, P, P, P, I, I, I, P, L, P, P, I, I, I, I, I, P],
     "xb_peer_copy": [P, P, L, I, P],
+    "xb_moe_route": [P, L, P, P, P, P, P, I, I, I, I, I, F, P],
     "xb_attn_bwd_set_split": [I],
     "xb_block_fp8_gemm": [P, P, P, P, P, I, I, I, P],
     "xb_block_fp8_gemm_ex": [P, P, P, P, P, I, I, I, L, L, L, L, L, P],

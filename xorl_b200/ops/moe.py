@@ -8,6 +8,8 @@ src/xorl/ops/group_gemm/kernel/group_gemm.py:80-377, src/xorl/ops/group_gemm/ker
 """
 from __future__ import annotations
 
+import os
+
 from typing import Optional, Tuple
 
 import torch
@@ -28,6 +30,57 @@ def launch_count() -> int:
 # --------------------------------------------------------------------------------------------
 # routing
 # --------------------------------------------------------------------------------------------
+_SCORING_ID = {"softmax": 0, "sigmoid": 1, "softmax_after_topk": 2}
+
+
+class _RouteKernel(torch.autograd.Function):
+    """Forward: one fused kernel (csrc/moe_route.cu).  Backward: closed forms on the saved
+    probabilities / choices (a few [T, E] elementwise ops)."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, k, renorm, scoring, scale):
+        global _launches
+        T, E = logits.shape
+        logits = logits.contiguous()
+        w = torch.empty((T, k), device=logits.device, dtype=torch.float32)
+        idx = torch.empty((T, k), device=logits.device, dtype=torch.int64)
+        probs = torch.empty((T, E), device=logits.device, dtype=torch.float32)
+        _lib.check(_lib.cuda_lib().xb_moe_route(
+            logits.data_ptr(), logits.stride(0), _lib.ptr(bias), w.data_ptr(), idx.data_ptr(), probs.data_ptr(),
+            None, T, E, k, _SCORING_ID[scoring], int(renorm), float(scale), _lib.stream_ptr()), "xb_moe_route")
+        _launches += 1
+        ctx.save_for_backward(probs, idx, w)
+        ctx.cfg = (renorm, scoring, scale)
+        ctx.mark_non_differentiable(idx)
+        return w, idx, probs
+
+    @staticmethod
+    def backward(ctx, dw, _didx, dprobs):
+        probs, idx, w = ctx.saved_tensors
+        renorm, scoring, scale = ctx.cfg
+        dp = dprobs.clone() if dprobs is not None else torch.zeros_like(probs)
+        dlogits = None
+        if dw is not None:
+            if scoring == "softmax_after_topk":
+                s = w / scale
+                dl_sel = scale * s * (dw - (dw * s).sum(-1, keepdim=True))
+                dlogits = torch.zeros_like(probs).scatter_add_(1, idx, dl_sel)
+            else:
+                if renorm:
+                    u = w / scale
+                    S = probs.gather(1, idx).sum(-1, keepdim=True).clamp_min(1e-20)
+                    dp_sel = scale / S * (dw - (dw * u).sum(-1, keepdim=True))
+                else:
+                    dp_sel = scale * dw
+                dp.scatter_add_(1, idx, dp_sel)
+        if scoring == "sigmoid":
+            g = dp * probs * (1 - probs)
+        else:
+            g = probs * (dp - (dp * probs).sum(-1, keepdim=True))
+        dlogits = g if dlogits is None else dlogits + g
+        return dlogits, None, None, None, None, None
+
+
 def topk_route(logits: torch.Tensor, k: int, renorm: bool = True, scoring: str = "softmax",
                scale: float = 1.0, n_group: int = 1, topk_group: int = 1,
                correction_bias: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -38,6 +91,9 @@ def topk_route(logits: torch.Tensor, k: int, renorm: bool = True, scoring: str =
     the *selection* uses ``probs + bias`` while the weights stay the unbiased scores (auxiliary-loss
     free balancing); with ``n_group > 1`` experts are chosen only inside the ``topk_group`` groups
     with the best sum of their two best biased scores (src/xorl/models/layers/moe/router.py)."""
+    if (logits.is_cuda and logits.dtype == torch.float32 and n_group <= 1 and logits.shape[1] <= 512 and k <= 32
+            and _lib.have_cuda_lib() and os.environ.get("XORL_B200_ROUTE_KERNEL", "1") == "1"):
+        return _RouteKernel.apply(logits, correction_bias, k, bool(renorm), scoring, float(scale))
     if scoring == "softmax_after_topk":
         top, indices = torch.topk(logits, k, dim=-1)
         weights = torch.softmax(top, dim=-1, dtype=torch.float32)
