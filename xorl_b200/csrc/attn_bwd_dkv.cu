@@ -11,12 +11,10 @@
 // core and the row threads: S / dP in TMEM and P / dS in shared memory.  The MMA thread issues
 // S, dP of step t+1 before it waits for P, dS of step t, so the tensor core multiplies while the
 // row threads exponentiate, and the dV / dK MMAs of step t overlap the row work of step t+1.
-// Two groups of eight row warps take alternate steps (group g owns buffer g of S / dP and of
-// P / dS), two threads per query row with 32 key columns each: four row warps per scheduler hide
-// the latency of the TMEM loads, the exponentials and the shared-memory hand-off, and a group may
-// spend two step times on its step.  lse / delta of a group's next step are fetched a step ahead.
-//   warp 0 : TMA producer (K,V once; Q,dO two-stage ring)    warp 1 : MMA issuer
-//   warps 2..9 : row group 0 (even steps)                    warps 10..17 : row group 1 (odd steps)
+// Eight row warps (two threads per query row, 32 key columns each) put two warps on every
+// scheduler, and lse / delta of the next step are fetched one step ahead, so neither arithmetic nor
+// global-load latency is exposed.
+//   warp 0 : TMA producer (K,V once; Q,dO two-stage ring)    warp 1 : MMA issuer    warps 2..9 : rows
 #include "common.cuh"
 
 namespace xb_attn_dkv_ns {
@@ -24,7 +22,7 @@ namespace xb_attn_dkv_ns {
 constexpr int D = 128;
 constexpr int BQ = 128;
 constexpr int BKV = 64;
-constexpr int NUM_THREADS = 576;
+constexpr int NUM_THREADS = 320;
 constexpr int ROW_THREADS = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0;        // + 128 * buf
@@ -241,14 +239,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   } else {
     // ------------------------------- row threads --------------------------------------
     const int q4 = warp & 3;                 // tensor-memory lane quarter this warp may read
-    const int grp = (warp - 2) >> 3;         // row group = buffer = step parity
-    const int half = ((warp - 2) >> 2) & 1;  // which 32 of the 64 key columns
+    const int half = (warp - 2) >> 2;        // which 32 of the 64 key columns
     const int r = q4 * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
-    const int s = grp;
     bool ok = true;
-    // lse / delta of this group's next step, fetched one step ahead
+    // lse / delta of the step about to run, fetched one step ahead
     float lse_n = 0.f, delta_n = 0.f;
     auto fetch = [&](int t) {
       lse_n = 0.f; delta_n = 0.f;
@@ -262,51 +258,51 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
       }
     };
-    fetch(grp);
-    for (int t = grp; t < n_steps && ok; t += 2) {
+    fetch(0);
+    for (int t = 0; t < n_steps && ok; ++t) {
+      const int s = t & 1;
       const uint32_t ph = (t >> 1) & 1;
-      const int q_lo = (qt0 + t % per_head) * BQ;
-      const int q_pos = q_lo + r;
+      const int q_pos = (qt0 + t % per_head) * BQ + r;
       const bool row_valid = q_pos < seq_len;
       const float lse = lse_n, delta = delta_n;
-      fetch(t + 2);
+      fetch(t + 1);
       // votes keep the warp together: the tcgen05.ld below is warp-collective
       if (!__all_sync(0xffffffffu, mbar_wait(&bars->sdp_full[s], ph, abort_flag, p.status, XB_K_ATTN_BWD, 900 + s))) {
         ok = false;
         break;
       }
       tc_fence_after();
-      // dS here is P o (dP - delta); the softmax scale is applied once, to dK, at the end.
-      // Tiles entirely below the diagonal and inside the sequence (the common case) need no mask.
-      const bool no_mask = (q_lo + BQ <= seq_len) && (kv0 + BKV <= seq_len) &&
-                           (!p.causal || kv0 + BKV - 1 <= q_lo);                 // CTA-uniform
-      const int lim = p.causal ? min(seq_len - 1, q_pos) : seq_len - 1;          // last visible kv position
-      const int nvis = no_mask ? 64 : (row_valid ? (lim - (kv0 + half * 32) + 1) : 0);
-      uint4 pw[4], dw[4];                          // 32 columns of P and dS, packed bf16
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t a[16], b[16];
-        tmem_ld_32x16(tmem_base + lane_addr + COL_S + 128 * s + half * 32 + h * 16, a);
-        tmem_ld_32x16(tmem_base + lane_addr + COL_DP + 128 * s + half * 32 + h * 16, b);
+      float pv[32], ds[32];
+      {
+        uint32_t a[32], b[32];
+        tmem_ld_32x32(tmem_base + lane_addr + COL_S + 128 * s + half * 32, a);
+        tmem_ld_32x32(tmem_base + lane_addr + COL_DP + 128 * s + half * 32, b);
         tc_wait_ld();
-        float pv[16], ds[16];
+        tc_fence_before();
+        mbar_arrive(&bars->sdp_empty[s]);
+        // dS here is P o (dP - delta); the softmax scale is applied once, to dK, at the end.
+        // Tiles entirely below the diagonal and inside the sequence (the common case) need no mask.
+        const int q_lo = (qt0 + t % per_head) * BQ;
+        const bool no_mask = (q_lo + BQ <= seq_len) && (kv0 + BKV <= seq_len) && (!p.causal || kv0 + BKV - 1 <= q_lo);
+        if (no_mask) {                               // CTA-uniform
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float pe = (h * 16 + i) < nvis ? xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) : 0.f;
-          pv[i] = pe;
-          ds[i] = pe * (__uint_as_float(b[i]) - delta);
-        }
+          for (int i = 0; i < 32; ++i) {
+            const float pe = xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse));
+            pv[i] = pe;
+            ds[i] = pe * (__uint_as_float(b[i]) - delta);
+          }
+        } else {
+          const int lim = p.causal ? min(seq_len - 1, q_pos) : seq_len - 1;  // last visible kv position
+          const int nvis = row_valid ? (lim - (kv0 + half * 32) + 1) : 0;     // visible columns of this thread
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          pw[h * 2 + c] = make_uint4(pack_bf16x2(pv[c * 8 + 0], pv[c * 8 + 1]), pack_bf16x2(pv[c * 8 + 2], pv[c * 8 + 3]),
-                                     pack_bf16x2(pv[c * 8 + 4], pv[c * 8 + 5]), pack_bf16x2(pv[c * 8 + 6], pv[c * 8 + 7]));
-          dw[h * 2 + c] = make_uint4(pack_bf16x2(ds[c * 8 + 0], ds[c * 8 + 1]), pack_bf16x2(ds[c * 8 + 2], ds[c * 8 + 3]),
-                                     pack_bf16x2(ds[c * 8 + 4], ds[c * 8 + 5]), pack_bf16x2(ds[c * 8 + 6], ds[c * 8 + 7]));
+          for (int i = 0; i < 32; ++i) {
+            const float pe = i < nvis ? xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) : 0.f;
+            pv[i] = pe;
+            ds[i] = pe * (__uint_as_float(b[i]) - delta);
+          }
         }
       }
-      tc_fence_before();
-      mbar_arrive(&bars->sdp_empty[s]);
-      // the dV / dK MMAs of this group's previous step read this P / dS buffer: wait until they are done
+      // the dV / dK MMAs of step t-2 read this P / dS buffer: wait until they are done
       if (!__all_sync(0xffffffffu, mbar_wait(&bars->pds_free[s], ph ^ 1, abort_flag, p.status, XB_K_ATTN_BWD, 910 + s))) {
         ok = false;
         break;
@@ -316,15 +312,23 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       uint8_t* sd = smem + SMEM_DS + s * PS_BYTES + r * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+        uint4 v, w;
+        v.x = pack_bf16x2(pv[c * 8 + 0], pv[c * 8 + 1]);
+        v.y = pack_bf16x2(pv[c * 8 + 2], pv[c * 8 + 3]);
+        v.z = pack_bf16x2(pv[c * 8 + 4], pv[c * 8 + 5]);
+        v.w = pack_bf16x2(pv[c * 8 + 6], pv[c * 8 + 7]);
+        w.x = pack_bf16x2(ds[c * 8 + 0], ds[c * 8 + 1]);
+        w.y = pack_bf16x2(ds[c * 8 + 2], ds[c * 8 + 3]);
+        w.z = pack_bf16x2(ds[c * 8 + 4], ds[c * 8 + 5]);
+        w.w = pack_bf16x2(ds[c * 8 + 6], ds[c * 8 + 7]);
         const int slot = (half * 4 + c) ^ (r & 7);
-        *reinterpret_cast<uint4*>(sp + slot * 16) = pw[c];
-        *reinterpret_cast<uint4*>(sd + slot * 16) = dw[c];
+        *reinterpret_cast<uint4*>(sp + slot * 16) = v;
+        *reinterpret_cast<uint4*>(sd + slot * 16) = w;
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars->pds_full[s]);
     }
-    if (grp == 0) {
     if (ok && n_steps > 0) ok = mbar_wait(&bars->all_done, 0, abort_flag, p.status, XB_K_ATTN_BWD, 920);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
@@ -350,7 +354,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
       }
     }
-    }   // grp == 0: the final read-out is done by the first row group
   }
 
   tc_fence_before();

@@ -12,9 +12,8 @@
 // single kernel that added 128 x 128 fp32 dQ partials to global memory with vector reductions at
 // every step; the price is a second evaluation of S and dP.
 //   warp 0 : TMA producer (Q, dO once; K, V three-stage ring)     warp 1 : MMA issuer
-//   warps 2..9 / 10..17 : two row groups taking alternate steps (group g owns buffer g of S / dP and
-//                dS), two threads per query row with 32 key columns each, so that four row warps per
-//                scheduler hide the latency of TMEM loads, exponentials and the shared-memory hand-off
+//   warps 2..9 : two threads per query row (32 of the 64 key columns each), two warps per scheduler
+//                so that dependent-issue latency of the softmax arithmetic is hidden
 #include "common.cuh"
 
 namespace xb_attn_dq_ns {
@@ -23,7 +22,7 @@ constexpr int D = 128;
 constexpr int BQ = 128;
 constexpr int BKV = 64;
 constexpr int NS = 3;                          // K/V ring stages
-constexpr int NUM_THREADS = 576;
+constexpr int NUM_THREADS = 320;
 constexpr int ROW_THREADS = 256;
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0;                       // + 128 * buf
@@ -231,8 +230,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   } else {
     // ------------------------------- row threads --------------------------------------
     const int q4 = warp & 3;                 // tensor-memory lane quarter this warp may read
-    const int grp = (warp - 2) >> 3;         // row group = buffer = step parity
-    const int half = ((warp - 2) >> 2) & 1;  // which 32 of the 64 key columns (and which half of d)
+    const int half = (warp - 2) >> 2;        // which 32 of the 64 key columns (and which half of d)
     const int r = q4 * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
@@ -245,9 +243,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       delta = p.delta[(size_t)head * p.T + tok];
     }
     const int lim = p.causal ? min(seq_len - 1, q_pos) : seq_len - 1;
-    const int b = grp;
     bool ok = true;
-    for (int j = grp; j < n_steps && ok; j += 2) {
+    for (int j = 0; j < n_steps && ok; ++j) {
+      const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       // votes keep the warp together: the tcgen05.ld below is warp-collective
       if (!__all_sync(0xffffffffu, mbar_wait(&bars->sdp_full[b], ph, abort_flag, p.status, XB_K_ATTN_BWD, 700 + b))) {
@@ -255,44 +253,51 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         break;
       }
       tc_fence_after();
-      // dS here is P o (dP - delta); the softmax scale is applied once, to dQ, at the end
-      const bool no_mask = (q0 + BQ <= seq_len) && (j * BKV + BKV <= seq_len) &&
-                           (!p.causal || j * BKV + BKV - 1 <= q0);            // CTA-uniform
-      const int nvis = no_mask ? 64 : (row_valid ? (lim - (j * BKV + half * 32) + 1) : 0);
-      uint4 dw[4];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t a[16], d2[16];
-        tmem_ld_32x16(tmem_base + lane_addr + COL_S + 128 * b + half * 32 + h * 16, a);
-        tmem_ld_32x16(tmem_base + lane_addr + COL_DP + 128 * b + half * 32 + h * 16, d2);
+      float ds[32];
+      const int kv0 = j * BKV + half * 32;
+      {
+        uint32_t a[32], d2[32];
+        tmem_ld_32x32(tmem_base + lane_addr + COL_S + 128 * b + half * 32, a);
+        tmem_ld_32x32(tmem_base + lane_addr + COL_DP + 128 * b + half * 32, d2);
         tc_wait_ld();
-        float ds[16];
+        // dS here is P o (dP - delta); the softmax scale is applied once, to dQ, at the end
+        const bool no_mask = (q0 + BQ <= seq_len) && (j * BKV + BKV <= seq_len) &&
+                             (!p.causal || j * BKV + BKV - 1 <= q0);          // CTA-uniform
+        if (no_mask) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          ds[i] = (h * 16 + i) < nvis ? xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) *
-                                            (__uint_as_float(d2[i]) - delta)
-                                      : 0.f;
+          for (int i = 0; i < 32; ++i)
+            ds[i] = xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) * (__uint_as_float(d2[i]) - delta);
+        } else {
+          const int nvis = row_valid ? (lim - kv0 + 1) : 0;
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
-          dw[h * 2 + c] = make_uint4(pack_bf16x2(ds[c * 8 + 0], ds[c * 8 + 1]), pack_bf16x2(ds[c * 8 + 2], ds[c * 8 + 3]),
-                                     pack_bf16x2(ds[c * 8 + 4], ds[c * 8 + 5]), pack_bf16x2(ds[c * 8 + 6], ds[c * 8 + 7]));
+          for (int i = 0; i < 32; ++i)
+            ds[i] = i < nvis ? xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) *
+                                   (__uint_as_float(d2[i]) - delta)
+                             : 0.f;
+        }
       }
       tc_fence_before();
       mbar_arrive(&bars->sdp_empty[b]);
-      // the dQ MMAs of this group's previous step read this dS buffer: wait until they are done
+      // the dQ MMAs of step j-2 read this dS buffer: wait until they are done
       if (!__all_sync(0xffffffffu, mbar_wait(&bars->ds_free[b], ph ^ 1, abort_flag, p.status, XB_K_ATTN_BWD, 710 + b))) {
         ok = false;
         break;
       }
       uint8_t* sd = smem + SMEM_DS + b * DS_BYTES + r * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        *reinterpret_cast<uint4*>(sd + (((half * 4 + c) ^ (r & 7)) * 16)) = dw[c];
+      for (int c = 0; c < 4; ++c) {
+        const int c16 = half * 4 + c;
+        uint4 w;
+        w.x = pack_bf16x2(ds[c * 8 + 0], ds[c * 8 + 1]);
+        w.y = pack_bf16x2(ds[c * 8 + 2], ds[c * 8 + 3]);
+        w.z = pack_bf16x2(ds[c * 8 + 4], ds[c * 8 + 5]);
+        w.w = pack_bf16x2(ds[c * 8 + 6], ds[c * 8 + 7]);
+        *reinterpret_cast<uint4*>(sd + ((c16 ^ (r & 7)) * 16)) = w;
+      }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&bars->ds_full[b]);
     }
-    if (grp == 0) {
     if (ok && n_steps > 0) ok = mbar_wait(&bars->dq_done, 0, abort_flag, p.status, XB_K_ATTN_BWD, 720);
     // tcgen05.ld is warp-collective (.sync.aligned): every lane of the warp executes it, whether or
     // not its row exists; only the stores are per-row
@@ -325,7 +330,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
       }
     }
-    }   // grp == 0: the final read-out is done by the first row group
   }
 
   tc_fence_before();
