@@ -242,7 +242,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tmem_ld_32x32(tmem_base + lane_addr + S_COL0 + s * BKV + c * 32, t);
         tc_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sc[c * 32 + i] = __uint_as_float(t[i]) * p.scale_log2;
+        for (int i = 0; i < 32; ++i) sc[c * 32 + i] = __uint_as_float(t[i]);     // raw scores
       }
       tc_fence_before();
       mbar_arrive(&bars->s_empty[s]);
@@ -255,15 +255,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         for (int i = 0; i < BKV; ++i)
           if (col0 + i > lim) sc[i] = -INFINITY;
       }
-      float mx = m;
+      float mx_raw = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < BKV; ++i) mx = fmaxf(mx, sc[i]);
+      for (int i = 0; i < BKV; ++i) mx_raw = fmaxf(mx_raw, sc[i]);
+      // m is the reference maximum (log2 units) that l and the O accumulator are relative to.  It
+      // only moves when the running maximum grows by more than 2^8: P then stays below 256, exact
+      // enough in bf16 with fp32 accumulation, and most steps skip the rescaling of O in TMEM.
+      const float mx_t = mx_raw * p.scale_log2;              // -inf stays -inf (scale > 0)
+      const float mx = (m == -INFINITY) ? mx_t : ((mx_t - m > 8.f) ? mx_t : m);
       const float m_use = (mx == -INFINITY) ? 0.f : mx;
-      const float alpha = (m == -INFINITY) ? 1.f : exp2f(m - m_use);
+      const float alpha = (m == -INFINITY || mx == m) ? 1.f : xb_ex2(m - m_use);
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < BKV; ++i) {
-        sc[i] = exp2f(sc[i] - m_use);
+        sc[i] = xb_ex2(fmaf(sc[i], p.scale_log2, -m_use));
         sum += sc[i];
       }
       l = l * alpha + sum;
