@@ -87,11 +87,11 @@ def main(argv=None) -> None:
         if rank == 0:
             elem = g.padded
             ag_bytes = elem * 2 * (world - 1) / world                     # bf16 pulled from peers
-            rs_wire = 2 if mode == "fused" else (4 if eng.reduce_dtype == torch.float32 and g.grad_full is None else 2)
-            rs_bytes = elem * (2 if mode == "fused" else torch.empty(0, dtype=eng.compute_dtype).element_size()) \
-                * (world - 1) / world
+            # bytes per element on the wire: bf16 in the fused transport, the reduce dtype through NCCL
+            rs_wire = 2 if mode == "fused" else (4 if eng.reduce_dtype == torch.float32 else 2)
+            rs_bytes = elem * rs_wire * (world - 1) / world
             print(json.dumps({
-                "transport": mode, "n_gpus": world, "unit_params": int(g.numel),
+                "transport": mode, "n_gpus": world, "unit_params": int(g.numel), "rs_wire_bytes_per_elem": rs_wire,
                 "all_gather_ms": ag_ms, "all_gather_gbs_per_gpu": ag_bytes / ag_ms / 1e6,
                 "all_gather_of_nvlink": ag_bytes / ag_ms / 1e6 / a.nvlink_gbs,
                 "reduce_scatter_ms": rs_ms, "reduce_scatter_gbs_per_gpu": rs_bytes / rs_ms / 1e6,
