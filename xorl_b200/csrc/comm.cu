@@ -78,7 +78,10 @@ symm_wait_kernel(const int* flags, int n, int self, int epoch, int* status, uint
   wait_flags(flags, n, self, epoch, status, XB_K_FLAG_WAIT_TEST, limit_ns);
 }
 
-// dst[r * shard_vec + i] = src_r[i]   (16-byte vectors)
+// dst[r * shard_vec + i] = src_r[i]   (16-byte vectors).  U independent 16-byte peer loads are in
+// flight per thread: bytes in flight = CTAs x 512 x 16 x U, which has to cover the NVLink round trip
+// at link bandwidth (about 2 MB).
+template <int U>
 __global__ void __launch_bounds__(512, 2)
 symm_allgather_kernel(uint4* __restrict__ dst, PeerPtrs src, long long shard_vec, int rank, int n) {
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -87,10 +90,12 @@ symm_allgather_kernel(uint4* __restrict__ dst, PeerPtrs src, long long shard_vec
     const uint4* s = reinterpret_cast<const uint4*>(src.p[r]);
     uint4* d = dst + (long long)r * shard_vec;
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    // 4 independent loads in flight per thread
-    for (; i + 3 * stride < shard_vec; i += 4 * stride) {
-      const uint4 a = s[i], b = s[i + stride], c = s[i + 2 * stride], e = s[i + 3 * stride];
-      d[i] = a; d[i + stride] = b; d[i + 2 * stride] = c; d[i + 3 * stride] = e;
+    for (; i + (U - 1) * stride < shard_vec; i += U * stride) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = s[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < U; ++u) d[i + u * stride] = v[u];
     }
     for (; i < shard_vec; i += stride) d[i] = s[i];
   }
@@ -237,9 +242,16 @@ XB_API int xb_symm_wait(const void* flags, int n, int self, int epoch, int wait_
 XB_API int xb_symm_allgather(void* dst, const unsigned long long* src_ptrs, long long shard_bytes,
                              int rank, int n, int num_ctas, void* stream) {
   if (n > MAX_RANKS || shard_bytes % 16) return -1;
+  // num_ctas: low 16 bits = CTAs, bits 16.. = loads in flight per thread (4 or 8; default 4)
+  const int unroll = (num_ctas >> 16) == 8 ? 8 : 4;
+  num_ctas &= 0xffff;
   if (num_ctas <= 0) num_ctas = 64;
-  symm_allgather_kernel<<<num_ctas, 512, 0, (cudaStream_t)stream>>>(
-      (uint4*)dst, make_ptrs(src_ptrs, n), shard_bytes / 16, rank, n);
+  if (unroll == 8)
+    symm_allgather_kernel<8><<<num_ctas, 512, 0, (cudaStream_t)stream>>>(
+        (uint4*)dst, make_ptrs(src_ptrs, n), shard_bytes / 16, rank, n);
+  else
+    symm_allgather_kernel<4><<<num_ctas, 512, 0, (cudaStream_t)stream>>>(
+        (uint4*)dst, make_ptrs(src_ptrs, n), shard_bytes / 16, rank, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -30,6 +30,11 @@ BARRIER_SLOT = 0          # [0, 16)
 BUF_SLOT0 = 64            # per gradient buffer: ready[16], done[16], counter -> 64 ints each
 NUM_GRAD_BUFS = 3
 WAIT_MS = 2000
+# CTAs of the collective kernels (512 threads, no shared memory: they share SMs with the GEMM CTAs)
+# and 16-byte loads in flight per thread of the all-gather
+AG_CTAS = int(os.environ.get("XORL_B200_AG_CTAS", "128"))
+AG_UNROLL = int(os.environ.get("XORL_B200_AG_UNROLL", "8"))
+RS_CTAS = int(os.environ.get("XORL_B200_RS_CTAS", "128"))
 
 
 def _align(x: int, a: int = 256) -> int:
@@ -120,7 +125,7 @@ class SymmetricTransport:
         comm_stream.wait_stream(torch.cuda.current_stream())
         srcs = self._ptrs(self.layout["shard"][id(g)])
         _lib.check(self.lib.xb_symm_allgather(g.full.data_ptr(), srcs, g.shard_numel * 2, self.rank,
-                                              self.world, 32, comm_stream.cuda_stream),
+                                              self.world, AG_CTAS | (AG_UNROLL << 16), comm_stream.cuda_stream),
                    "xb_symm_allgather")
         g.gather_event = torch.cuda.Event()
         g.gather_event.record(comm_stream)
@@ -170,7 +175,7 @@ class SymmetricTransport:
         _lib.check(self.lib.xb_symm_reduce_scatter(
             g.grad_shard.data_ptr(), grads, ctypes.c_ulonglong(mc), g.rank * g.shard_numel,
             g.shard_numel, int(accumulate), 1.0, None, self._flag_ptrs, slot, slot + 16, slot + 32,
-            self.rank, self.world, epoch, WAIT_MS, 48, comm_stream.cuda_stream),
+            self.rank, self.world, epoch, WAIT_MS, RS_CTAS, comm_stream.cuda_stream),
             "xb_symm_reduce_scatter")
         g.reduce_event = torch.cuda.Event()
         g.reduce_event.record(comm_stream)
