@@ -38,6 +38,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count")
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--ep", type=int, default=0,
+                    help="expert-parallel size for MoE models (0: all ranks for MoE, 1 for dense)")
+    ap.add_argument("--ep-dispatch", default="fused", choices=["fused", "alltoall"])
     return ap.parse_args()
 
 
@@ -131,9 +134,12 @@ def run_ours(a):
     assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
     overrides = {"num_hidden_layers": a.layers} if a.layers else {}
     cfg = preset(a.model, **overrides)
+    ep = (a.ep or (world if cfg.is_moe else 1)) if cfg.is_moe else 1
+    moe_train = dict(expert_parallel_size=ep, softmax_auxiliary_loss=True, auxiliary_loss_multiplier=1e-3) \
+        if cfg.is_moe else {}
     out_dir = os.path.join(ROOT, "gpurun_out", "bench_out")
     args = Arguments(
-        model=ModelArguments(config_path=a.model),
+        model=ModelArguments(config_path=a.model, ep_dispatch=a.ep_dispatch),
         data=DataArguments(datasets=[{"path": "dummy", "max_seq_len": 64, "num_samples": 8}],
                            sample_packing_sequence_len=a.seq_len, dataloader_pin_memory=False),
         train=TrainingArguments(output_dir=out_dir, optimizer="adamw", lr=1e-5, weight_decay=0.01,
@@ -141,7 +147,7 @@ def run_ours(a):
                                 data_parallel_mode="fsdp2", enable_mixed_precision=True,
                                 enable_gradient_checkpointing=True, init_device="meta",
                                 load_weights_mode="skip", save_hf_weights=False, use_wandb=False,
-                                comm_backend=a.comm, max_steps=10 ** 9, ce_num_chunks=4))
+                                comm_backend=a.comm, max_steps=10 ** 9, ce_num_chunks=4, **moe_train))
     trainer = Trainer(args, model_config=cfg)
     dev = trainer.device
     torch.cuda.reset_peak_memory_stats()
@@ -205,7 +211,8 @@ def run_ours(a):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": a.model + (f"[{a.layers} layers: DEBUG, not the named model]" if a.layers else ""),
                        "global_batch": world, "seq_len": a.seq_len,
-                       "parallelism": f"fsdp{world}" + ("-fused" if fused else "-nccl" if world > 1 else ""),
+                       "parallelism": f"fsdp{world}" + ("-fused" if fused else "-nccl" if world > 1 else "")
+                       + (f"-ep{ep}-{a.ep_dispatch}" if ep > 1 else ""),
                        "optimizer": "adamw fp32 master+states", "recompute": "full layer",
                        "l2": "per-step working set (16 GB of bf16 weights + activations) >> 126 MB L2",
                        "packed_docs": "lengths U[256,4096], tokens U[vocab]"},
