@@ -133,3 +133,39 @@ def test_moe_route_kernel_matches_torch(scoring, renorm, E, k, bias, monkeypatch
     ((w.gather(1, o1) * gw).sum() + (probs * gp).sum()).backward()
     ((w2.gather(1, o2) * gw).sum() + (probs2 * gp).sum()).backward()
     torch.testing.assert_close(a.grad, b.grad, rtol=1e-4, atol=1e-5)
+
+
+def test_moe_permute_combine_kernels_match_torch_path(monkeypatch):
+    """The gather kernels (permute, weighted combine and their backward) against the index_select /
+    index_copy formulation, forward and every gradient."""
+    from xorl_b200.models.config import preset
+    from xorl_b200.models.context import StepContext
+    from xorl_b200.models.moe import MoEBlock
+    from xorl_b200.parallel.state import init_parallel_state, reset_parallel_state
+    reset_parallel_state()
+    init_parallel_state(device_type="cuda")
+    cfg = preset("qwen3-30b-a3b", hidden_size=256, num_experts=8, num_experts_per_tok=3,
+                 moe_intermediate_size=128, num_hidden_layers=1)
+    torch.manual_seed(0)
+    blk = MoEBlock(cfg, 0, dtype=torch.bfloat16, device="cuda")
+    for p in blk.parameters():
+        torch.nn.init.normal_(p, 0, 0.05)
+    T = 515
+    x0 = (torch.randn(T, 256, device="cuda") * 0.5).to(torch.bfloat16)
+    go = torch.randn(T, 256, device="cuda").to(torch.bfloat16)
+    ctx = StepContext(cu_seqlens=torch.tensor([0, T], device="cuda", dtype=torch.int32),
+                      position_ids=torch.arange(T, device="cuda"))
+    res = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("XORL_B200_MOE_KERNELS", mode)
+        for p in blk.parameters():
+            p.grad = None
+        x = x0.clone().requires_grad_()
+        out = blk(x, ctx)
+        out.backward(go)
+        res[mode] = (out.detach().float(), x.grad.float(), blk.gate.weight.grad.float(),
+                     blk.experts.gate_up_proj.grad.float(), blk.experts.down_proj.grad.float())
+    for a, b, name in zip(res["1"], res["0"], ("out", "dx", "dgate", "dgate_up", "ddown")):
+        tol = 0.02 * b.abs().max().item() + 1e-4
+        assert (a - b).abs().max().item() <= tol, (name, (a - b).abs().max().item(), tol)
+    reset_parallel_state()

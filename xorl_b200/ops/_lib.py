@@ -62,6 +62,9 @@ _SIGNATURES = {
     "xb_ep_push_rows": [P, L, P, P, P, P, I, I, I, P, L, P, P, I, I, I, I, I, P],
     "xb_peer_copy": [P, P, L, I, P],
     "xb_moe_route": [P, L, P, P, P, P, P, I, I, I, I, I, F, P],
+    "xb_moe_gather_rows": [P, L, P, L, P, P, I, I, P],
+    "xb_moe_gather_sum": [P, L, P, L, P, P, I, I, I, P],
+    "xb_moe_slot_dots": [P, P, L, P, L, P, I, I, I, P],
     "xb_attn_bwd_set_split": [I],
     "xb_block_fp8_gemm": [P, P, P, P, P, I, I, I, P],
     "xb_block_fp8_gemm_ex": [P, P, P, P, P, I, I, I, L, L, L, L, L, P],

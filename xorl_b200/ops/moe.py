@@ -303,6 +303,85 @@ def expert_mlp(x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor, gate_up:
     return out.index_select(0, dest)
 
 
+# --------------------------------------------------------------------------------------------
+# permutation / combine kernels (csrc/moe_permute.cu)
+# --------------------------------------------------------------------------------------------
+def _permute_kernels_ok(x: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and _lib.have_cuda_lib()
+            and os.environ.get("XORL_B200_MOE_KERNELS", "1") == "1")
+
+
+def _gather_rows(inp, src_row, rows, scale=None):
+    global _launches
+    out = torch.empty((rows, inp.shape[1]), device=inp.device, dtype=inp.dtype)
+    inp = inp.contiguous()
+    _lib.check(_lib.cuda_lib().xb_moe_gather_rows(out.data_ptr(), out.stride(0), inp.data_ptr(), inp.stride(0),
+                                                  src_row.data_ptr(), _lib.ptr(scale), rows, inp.shape[1],
+                                                  _lib.stream_ptr()), "xb_moe_gather_rows")
+    _launches += 1
+    return out
+
+
+def _gather_sum(inp, idx, w):
+    global _launches
+    T, k = idx.shape
+    inp = inp.contiguous()
+    out = torch.empty((T, inp.shape[1]), device=inp.device, dtype=inp.dtype)
+    _lib.check(_lib.cuda_lib().xb_moe_gather_sum(out.data_ptr(), out.stride(0), inp.data_ptr(), inp.stride(0),
+                                                 idx.data_ptr(), _lib.ptr(w), T, k, inp.shape[1],
+                                                 _lib.stream_ptr()), "xb_moe_gather_sum")
+    _launches += 1
+    return out
+
+
+class _Permute(torch.autograd.Function):
+    """x [T,H] -> buffer [rows,H]: row dest[t,j] holds x[t]; rows nobody owns are zero."""
+
+    @staticmethod
+    def forward(ctx, x, dest, tok_of_row):
+        ctx.save_for_backward(dest)
+        return _gather_rows(x, tok_of_row, tok_of_row.numel())
+
+    @staticmethod
+    def backward(ctx, dbuf):
+        (dest,) = ctx.saved_tensors
+        return _gather_sum(dbuf, dest, None), None, None
+
+
+class _Combine(torch.autograd.Function):
+    """out[t] = sum_j w[t,j] * y[dest[t,j]] (fp32 accumulation, bf16 result)."""
+
+    @staticmethod
+    def forward(ctx, y, w, dest, tok_of_row):
+        w = w.float().contiguous()
+        ctx.save_for_backward(y, w, dest, tok_of_row)
+        return _gather_sum(y, dest, w)
+
+    @staticmethod
+    def backward(ctx, dout):
+        global _launches
+        y, w, dest, tok_of_row = ctx.saved_tensors
+        dout = dout.contiguous()
+        rows = y.shape[0]
+        T, k = dest.shape
+        scale_row = torch.zeros(rows, device=y.device, dtype=torch.float32)
+        scale_row[dest.reshape(-1)] = w.reshape(-1)
+        dy = _gather_rows(dout, tok_of_row, rows, scale_row)
+        dw = torch.empty((T, k), device=y.device, dtype=torch.float32)
+        _lib.check(_lib.cuda_lib().xb_moe_slot_dots(dw.data_ptr(), dout.data_ptr(), dout.stride(0), y.data_ptr(),
+                                                    y.stride(0), dest.data_ptr(), T, k, y.shape[1],
+                                                    _lib.stream_ptr()), "xb_moe_slot_dots")
+        _launches += 1
+        return dy, dw, None, None
+
+
+def token_of_row(dest: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    """Inverse of ``dest`` [T*k]: token index stored in every buffer row, -1 for padding rows."""
+    tok = torch.full((rows,), -1, device=dest.device, dtype=torch.int32)
+    tok[dest] = (torch.arange(dest.numel(), device=dest.device) // k).to(torch.int32)
+    return tok
+
+
 def local_moe_forward(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor, experts,
                       num_experts: int) -> torch.Tensor:
     """All experts local: gather tokens into expert-sorted aligned segments, run the grouped MLP,
@@ -311,6 +390,12 @@ def local_moe_forward(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
     k = indices.shape[1]
     dest, seg, _ = aligned_sort_indices(indices.reshape(-1), num_experts)
     rows = buffer_rows(T * k, num_experts)
+    if _permute_kernels_ok(x):
+        tok = token_of_row(dest, rows, k)
+        dest2 = dest.view(T, k)
+        buf = _Permute.apply(x, dest2, tok)
+        y = expert_mlp_aligned(buf, seg, experts.gate_up_proj, experts.down_proj, **experts_mlp_kwargs(experts))
+        return _Combine.apply(y, weights, dest2, tok)
     token_of_slot = torch.arange(T, device=x.device).repeat_interleave(k)
     buf = x.new_zeros((rows, H)).index_copy(0, dest, x.index_select(0, token_of_slot))
     y = expert_mlp_aligned(buf, seg, experts.gate_up_proj, experts.down_proj, **experts_mlp_kwargs(experts))

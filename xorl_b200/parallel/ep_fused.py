@@ -214,5 +214,10 @@ def fused_ep_forward(x, weights, indices, experts, num_experts, ctx):
     y = moe_ops.expert_mlp_aligned(buf, plan.seg, experts.gate_up_proj, experts.down_proj,
                                    **moe_ops.experts_mlp_kwargs(experts))
     y_slots = _Return.apply(y, ws, plan)
+    if moe_ops._permute_kernels_ok(x):
+        # weighted sum over the k slots of a token in one gather kernel (slot rows are contiguous)
+        slots = torch.arange(T * k, device=x.device).view(T, k)
+        tok = (torch.arange(T * k, device=x.device) // k).to(torch.int32)
+        return moe_ops._Combine.apply(y_slots, weights, slots, tok)
     out = (y_slots.view(T, k, H).float() * weights.unsqueeze(-1).float()).sum(1)
     return out.to(x.dtype)
