@@ -268,7 +268,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         lse = p.lse[(size_t)head * p.T + tok] * LOG2E;
         delta = p.delta[(size_t)head * p.T + tok];
       }
-      if (!mbar_wait(&bars->sdp_full, t & 1, abort_flag, p.status, XB_K_ATTN_BWD, 300)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->sdp_full, t & 1, abort_flag, p.status, XB_K_ATTN_BWD, 300))) {
         ok = false;
         break;
       }
@@ -298,7 +298,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       // previous step's MMAs (which read P/dS from shared memory) are done once dq_full fired
       if (t > 0) {
-        if (!mbar_wait(&bars->dq_full, (t - 1) & 1, abort_flag, p.status, XB_K_ATTN_BWD, 310)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->dq_full, (t - 1) & 1, abort_flag, p.status, XB_K_ATTN_BWD, 310))) {
           ok = false;
           break;
         }
@@ -350,7 +350,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (ok && n_steps > 0) {
       // last dQ tile
       const int t = n_steps - 1;
-      if (mbar_wait(&bars->dq_full, t & 1, abort_flag, p.status, XB_K_ATTN_BWD, 320)) {
+      if (__all_sync(0xffffffffu, mbar_wait(&bars->dq_full, t & 1, abort_flag, p.status, XB_K_ATTN_BWD, 320))) {
         tc_fence_after();
         const int head_p = kv_head * G + t / per_head;
         const int qpos_p = (qt0 + t % per_head) * BQ + r;
@@ -375,6 +375,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
     }
     if (ok && n_steps > 0) ok = mbar_wait(&bars->all_done, 0, abort_flag, p.status, XB_K_ATTN_BWD, 330);
+    ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
       // dV^T / dK^T: this thread holds feature d = r for the 64 kv rows of the tile.  For a fixed

@@ -229,8 +229,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint8_t* sp = smem + SMEM_P;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int s = j & 1;
-      if (!mbar_wait(&bars->s_full[s], (j >> 1) & 1, abort_flag, p.status, XB_K_ATTN_FWD,
-                     300 + s)) {
+      // votes keep the warp together: tcgen05.ld / tcgen05.st below are warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full[s], (j >> 1) & 1, abort_flag, p.status,
+                                             XB_K_ATTN_FWD, 300 + s))) {
         ok = false;
         break;
       }
@@ -275,7 +276,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       m = mx;
 
       if (j > 0) {
-        if (!mbar_wait(&bars->pv_done, (j - 1) & 1, abort_flag, p.status, XB_K_ATTN_FWD, 310)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1, abort_flag, p.status, XB_K_ATTN_FWD, 310))) {
           ok = false;
           break;
         }
@@ -311,6 +312,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (ok && n_kv > 0) {
       ok = mbar_wait(&bars->pv_done, (n_kv - 1) & 1, abort_flag, p.status, XB_K_ATTN_FWD, 320);
     }
+    ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
       const bool valid = row_pos < seq_len;

@@ -208,7 +208,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tile_coords(p, tile, mb, nb);
       const int acc = tcount & 1;
       const uint32_t acc_ph = (tcount >> 1) & 1;
-      if (!mbar_wait(&bars->tmem_full[acc], acc_ph, abort_flag, p.status, XB_K_GEMM, 400 + acc)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[acc], acc_ph, abort_flag, p.status, XB_K_GEMM, 400 + acc))) {
         ok = false;
         break;
       }

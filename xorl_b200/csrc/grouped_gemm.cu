@@ -188,8 +188,8 @@ ggemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       const bool has_acc = tl.num_kb > 0;
       const int acc = tcount & 1;
       if (has_acc) {
-        if (!mbar_wait(&bars->tmem_full[acc], (tcount >> 1) & 1, abort_flag, p.status,
-                       XB_K_GROUPED_GEMM, 400 + acc)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->tmem_full[acc], (tcount >> 1) & 1, abort_flag, p.status,
+                       XB_K_GROUPED_GEMM, 400 + acc))) { ok = false; break; }
         tc_fence_after();
       } else if (p.accumulate) {
         continue;  // nothing to add for an expert without tokens

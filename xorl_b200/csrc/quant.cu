@@ -185,8 +185,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int buf = it & 1;
         const float scale = __ldg(sa_row + kb) * __ldg(sb_row + kb);
-        if (!mbar_wait(&bars->acc_full[buf], (it >> 1) & 1, abort_flag, p.status, XB_K_FP8_GEMM,
-                       400 + buf)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->acc_full[buf], (it >> 1) & 1, abort_flag, p.status, XB_K_FP8_GEMM,
+                       400 + buf))) {
           ok = false;
           break;
         }
