@@ -22,7 +22,7 @@ def _state():
 
 
 @pytest.mark.parametrize("name", ["tiny-qwen3", "tiny-qwen2", "tiny-olmo2", "tiny-qwen3-moe", "tiny-gpt-oss",
-                                  "tiny-deepseek-v3", "tiny-glm4-moe"])
+                                  "tiny-deepseek-v3", "tiny-glm4-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe"])
 def test_family_trains(name):
     from xorl_b200.models import build_model
     from xorl_b200.models.config import preset
@@ -196,3 +196,29 @@ def test_family_hf_roundtrip(name, tmp_path):
     wa = dict(a.iter_full_tensors("master"))
     for k, v in b.iter_full_tensors("master"):
         assert torch.equal(v, wa[k]), k
+
+
+def test_gated_delta_rule_matches_dense_formula():
+    """The recurrence against an explicit per-head float64 restatement, with a document boundary."""
+    from xorl_b200.models.gated_deltanet import causal_depthwise_conv, gated_delta_rule
+    torch.manual_seed(0)
+    T, H, dk, dv = 11, 3, 4, 5
+    q, k = torch.randn(T, H, dk), torch.nn.functional.normalize(torch.randn(T, H, dk), dim=-1)
+    v, g, beta = torch.randn(T, H, dv), -torch.rand(T, H), torch.rand(T, H)
+    cu = torch.tensor([0, 4, 11], dtype=torch.int32)
+    out = gated_delta_rule(q, k, v, g, beta, cu)
+    for h in range(H):
+        for (s, e) in ((0, 4), (4, 11)):
+            S = torch.zeros(dk, dv, dtype=torch.float64)
+            for t in range(s, e):
+                S = math.exp(g[t, h].item()) * S
+                kt = k[t, h].double()
+                S = S + torch.outer(kt, beta[t, h].double() * (v[t, h].double() - S.t() @ kt))
+                torch.testing.assert_close(out[t, h].double(), S.t() @ q[t, h].double(), rtol=1e-5, atol=1e-5)
+    # the convolution is causal and does not cross documents
+    x = torch.randn(T, 6)
+    w = torch.randn(6, 4)
+    y = causal_depthwise_conv(x, w, cu)
+    t = 5                                                     # second token of the second document
+    ref = w[:, 3] * x[5] + w[:, 2] * x[4]
+    torch.testing.assert_close(y[t], ref)

@@ -134,6 +134,16 @@ class ModelConfig:
             d["use_qk_norm"] = False
         if mt in ("llama",):
             d["use_qk_norm"] = False
+        if mt in ("qwen3_5", "qwen3_5_moe", "qwen3_next"):
+            d["use_qk_norm"] = True
+            d.setdefault("zero_centered_norm", True)
+            d.setdefault("partial_rotary_factor", 0.25)
+            d.setdefault("attn_output_gate", True)
+            if d.get("layer_types") is None:
+                n, every = d.get("num_hidden_layers", 0), d.get("full_attention_interval", 4)
+                d["layer_types"] = ["full_attention" if (i + 1) % every == 0 else "linear_attention" for i in range(n)]
+            if mt == "qwen3_5_moe" or d.get("num_experts"):
+                d.setdefault("shared_expert_gate", bool(d.get("shared_expert_intermediate_size")))
         if mt == "gpt_oss":
             d["use_qk_norm"] = False
             d.setdefault("attention_bias", True)
@@ -226,6 +236,18 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                           n_group=1, topk_group=1, n_shared_experts=1, moe_intermediate_size=32,
                           first_k_dense_replace=1, routed_scaling_factor=1.0, norm_topk_prob=True,
                           rope_theta=1e4, max_position_embeddings=512, tie_word_embeddings=False),
+    "tiny-qwen3-5": dict(model_type="qwen3_5", vocab_size=512, hidden_size=64, intermediate_size=128,
+                         num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                         linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=8,
+                         linear_value_head_dim=8, linear_conv_kernel_dim=4, rope_theta=1e4,
+                         max_position_embeddings=512, tie_word_embeddings=False),
+    "tiny-qwen3-5-moe": dict(model_type="qwen3_5_moe", vocab_size=512, hidden_size=64, intermediate_size=128,
+                             num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                             linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=8,
+                             linear_value_head_dim=8, linear_conv_kernel_dim=4, num_experts=8,
+                             num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
+                             norm_topk_prob=True, rope_theta=1e4, max_position_embeddings=512,
+                             tie_word_embeddings=False),
     "tiny-olmo2": dict(model_type="olmo2", vocab_size=512, hidden_size=64, intermediate_size=128,
                        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, rope_theta=1e4,
                        max_position_embeddings=512, tie_word_embeddings=False),

@@ -27,7 +27,10 @@ class DecoderLayer(nn.Module):
         super().__init__()
         self.layer_idx = layer_idx
         self.post_norm = cfg.norm_placement == "post"
-        if cfg.extra.get("kv_lora_rank"):
+        if cfg.layer_types is not None and cfg.layer_types[layer_idx] == "linear_attention":
+            from .gated_deltanet import GatedDeltaNet
+            self.self_attn = GatedDeltaNet(cfg, layer_idx, dtype=dtype, device=device)
+        elif cfg.extra.get("kv_lora_rank"):
             from .mla import MLAttention
             self.self_attn = MLAttention(cfg, layer_idx, dtype=dtype, device=device)
         else:
@@ -207,6 +210,15 @@ def init_parameter_(name: str, p: torch.Tensor, std: float, seed: int, index: in
         init_lora_parameter_(name, p, 0, seed)
         return
     leaf = name.rsplit(".", 1)[-1]
+    if leaf == "A_log":                      # GatedDeltaNet decay rates spread over (0, 16)
+        p.copy_(torch.linspace(0.5, 16.0, p.numel()).log().to(p.device))
+        return
+    if leaf in ("dt_bias", "o_norm_weight"):  # unit step bias / plain (not zero-centred) gated norm
+        p.fill_(1.0)
+        return
+    if leaf == "sinks":
+        p.zero_()
+        return
     if p.dim() == 1:
         if leaf == "bias" or "bias" in leaf:
             p.zero_()

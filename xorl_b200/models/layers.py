@@ -92,6 +92,12 @@ class Attention(nn.Module):
         self.scale = 1.0 / math.sqrt(self.D)
         self.window = cfg.sliding_window if (cfg.layer_types is None or
                                             cfg.layer_types[layer_idx] == "sliding_attention") else None
+        # Qwen3-Next / Qwen3.5: the attention output is multiplied by sigmoid(gate(x)) before o_proj
+        self.out_gate = Linear(H, self.Hq * self.D, dtype=dtype, device=device) \
+            if cfg.extra.get("attn_output_gate") else None
+        if self.out_gate is not None and self.tp > 1:
+            from ..parallel.tp import mark_col
+            mark_col(self.out_gate.weight, (self.Hq * self.tp * self.D, H), (self.Hq * self.tp * self.D,))
         self.sinks = nn.Parameter(torch.zeros(self.Hq, dtype=dtype, device=device)) if cfg.attention_sinks else None
         if self.sinks is not None and self.tp > 1:
             from ..parallel.tp import mark_col
@@ -114,6 +120,8 @@ class Attention(nn.Module):
             out = attn_ops.qk_norm_rope_attention(qkv, wq, wk, ctx.cos, ctx.sin, ctx.cu_seqlens,
                                                   Hq, Hkv, D, self.cfg.rms_norm_eps, ctx.causal,
                                                   self.scale)
+        if self.out_gate is not None:
+            out = out * torch.sigmoid(self.out_gate(x).float()).to(out.dtype)
         out = self.o_proj(out)
         if self.tp > 1:
             from ..parallel.tp import reduce_from_tp

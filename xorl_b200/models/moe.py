@@ -93,6 +93,9 @@ class MoEBlock(nn.Module):
         if cfg.shared_expert_intermediate_size:
             self.shared_expert = MLP(cfg.hidden_size, cfg.shared_expert_intermediate_size,
                                      dtype=dtype, device=device)
+        # Qwen3-Next / Qwen3.5 MoE: the shared expert is scaled by sigmoid(w_g . x) per token
+        self.shared_expert_gate = Linear(cfg.hidden_size, 1, dtype=dtype, device=device) \
+            if (self.shared_expert is not None and cfg.extra.get("shared_expert_gate")) else None
         self.aux_coef = cfg.router_aux_loss_coef
         self.moe_ordinal = sum(cfg.layer_is_moe(i) for i in range(layer_idx))
 
@@ -127,5 +130,8 @@ class MoEBlock(nn.Module):
         else:
             out = moe_ops.local_moe_forward(x, weights, indices, self.experts, self.cfg.num_experts)
         if self.shared_expert is not None:
-            out = out + self.shared_expert(x)
+            sh = self.shared_expert(x)
+            if self.shared_expert_gate is not None:
+                sh = sh * torch.sigmoid(torch.nn.functional.linear(x.float(), self.shared_expert_gate.weight.float())).to(sh.dtype)
+            out = out + sh
         return out
