@@ -169,3 +169,50 @@ def test_moe_permute_combine_kernels_match_torch_path(monkeypatch):
         tol = 0.02 * b.abs().max().item() + 1e-4
         assert (a - b).abs().max().item() <= tol, (name, (a - b).abs().max().item(), tol)
     reset_parallel_state()
+
+
+@pytest.mark.parametrize("N,rank,E,k,T", [(2, 1, 8, 2, 300), (8, 3, 128, 8, 4096), (4, 0, 16, 4, 1000)])
+def test_ep_plan_kernel_matches_torch_formulation(N, rank, E, k, T):
+    """Destination rank / row of every token slot and the local segment table, against the
+    argsort / cumsum formulation (rows of an expert keep slot order in both)."""
+    import ctypes
+    from xorl_b200.ops import _lib
+    torch.manual_seed(N * 100 + E)
+    El = E // N
+    idx = torch.randint(0, E, (T, k), device="cuda")
+    flat = idx.reshape(-1)
+    S = flat.numel()
+    counts = torch.bincount(flat, minlength=E).to(torch.int32)
+    table = torch.randint(0, 2 * S // E, (N, E), device="cuda", dtype=torch.int32)
+    table[rank] = counts
+    cap = (int(1.5 * S) + El * 127 + 127) // 128 * 128
+    dr = torch.empty(S, device="cuda", dtype=torch.int32)
+    drow = torch.empty(S, device="cuda", dtype=torch.int32)
+    seg = torch.empty(El + 1, device="cuda", dtype=torch.int32)
+    tot = torch.empty(El, device="cuda", dtype=torch.int32)
+    ovf = torch.zeros(1, device="cuda", dtype=torch.int32)
+    _lib.check(_lib.cuda_lib().xb_ep_plan(flat.data_ptr(), S, table.data_ptr(), rank, N, E, El, cap, dr.data_ptr(),
+                                          drow.data_ptr(), seg.data_ptr(), tot.data_ptr(), ovf.data_ptr(),
+                                          _lib.stream_ptr()), "xb_ep_plan")
+    # torch formulation
+    tl = table.long()
+    t_all = tl.sum(0)
+    padded = (t_all + 127) // 128 * 128
+    pe = padded.view(N, El)
+    seg_start = (pe.cumsum(1) - pe).reshape(-1)
+    before = tl[:rank].sum(0) if rank > 0 else torch.zeros_like(t_all)
+    base = seg_start + before
+    order = torch.argsort(flat, stable=True)
+    c64 = counts.long()
+    starts = c64.cumsum(0) - c64
+    rank_in_e = torch.empty_like(flat)
+    rank_in_e[order] = torch.arange(S, device="cuda") - starts[flat[order]]
+    ref_row = base[flat] + rank_in_e
+    ref_rank = flat // El
+    over = ref_row >= cap
+    assert torch.equal(dr.long(), torch.where(over, torch.full_like(ref_rank, -1), ref_rank))
+    assert torch.equal(drow.long()[~over], ref_row[~over])
+    assert bool(ovf.item()) == bool(over.any().item())
+    mine = slice(rank * El, (rank + 1) * El)
+    ref_seg = torch.cat([padded.new_zeros(1), padded[mine].cumsum(0)]).clamp(max=cap // 128 * 128)
+    assert torch.equal(seg.long(), ref_seg) and torch.equal(tot.long(), t_all[mine])

@@ -123,7 +123,99 @@ ep_push_rows_kernel(const uint4* __restrict__ src, long long src_ld_vec, const i
   }
 }
 
+// Destination of every token slot, one block per global expert.  Slots of an expert keep their
+// slot order (a block scans the slots in order and ranks its matches with a ballot prefix), so the
+// layout is the same every run.  table: int32 [n][E], counts of every source rank (already
+// exchanged).  Row of a slot on the owner = aligned start of the expert's segment on its owner
+// + rows that lower ranks send to this expert + rank of the slot among this rank's slots of the
+// expert.  Blocks of this rank's own experts also write seg / tot for the grouped GEMMs.
+__global__ void __launch_bounds__(256)
+ep_plan_kernel(const long long* __restrict__ indices, int S, const int* __restrict__ table, int rank, int n,
+               int E, int El, int cap, int* __restrict__ dest_rank, int* __restrict__ dest_row,
+               int* __restrict__ seg, int* __restrict__ tot, int* __restrict__ overflow) {
+  const int e = blockIdx.x;
+  const int owner = e / El, first = owner * El;
+  __shared__ int s_base, s_total, s_start;
+  __shared__ int s_warp[8];
+  __shared__ int s_running;
+  if (threadIdx.x < 32) {
+    // aligned start of expert e inside its owner's buffer: sum of padded totals of the owner's earlier experts
+    int start = 0;
+    for (int e2 = first + (int)threadIdx.x; e2 < e; e2 += 32) {
+      int t = 0;
+      for (int r = 0; r < n; ++r) t += table[r * E + e2];
+      start += (t + 127) / 128 * 128;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) start += __shfl_xor_sync(0xffffffffu, start, o);
+    int mine = 0, before = 0;
+    for (int r = (int)threadIdx.x; r < n; r += 32) {
+      const int c = table[r * E + e];
+      mine += c;
+      if (r < rank) before += c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mine += __shfl_xor_sync(0xffffffffu, mine, o);
+      before += __shfl_xor_sync(0xffffffffu, before, o);
+    }
+    if (threadIdx.x == 0) {
+      s_start = start;
+      s_base = start + before;
+      s_total = mine;
+      s_running = 0;
+    }
+  }
+  __syncthreads();
+  const int lim = cap / 128 * 128;
+  if (owner == rank && threadIdx.x == 0) {
+    const int le = e - first;
+    seg[le] = min(s_start, lim);
+    tot[le] = s_total;
+    if (le == El - 1) seg[El] = min(s_start + (s_total + 127) / 128 * 128, lim);
+  }
+  const int base = s_base;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c0 = 0; c0 < S; c0 += 256) {
+    const int slot = c0 + (int)threadIdx.x;
+    const bool hit = slot < S && indices[slot] == (long long)e;
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) s_warp[warp] = __popc(m);
+    __syncthreads();
+    int before_w = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const int c = s_warp[w];
+      if (w < warp) before_w += c;
+      total += c;
+    }
+    const int running = s_running;
+    if (hit) {
+      const int row = base + running + before_w + __popc(m & ((1u << lane) - 1u));
+      if (row >= cap) {
+        dest_rank[slot] = -1;
+        dest_row[slot] = 0;
+        *overflow = 1;
+      } else {
+        dest_rank[slot] = owner;
+        dest_row[slot] = row;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_running = running + total;
+    __syncthreads();
+  }
+}
+
 }  // namespace
+
+XB_API int xb_ep_plan(const long long* indices, int S, const int* table, int rank, int n, int E, int El, int cap,
+                      int* dest_rank, int* dest_row, int* seg, int* tot, int* overflow, void* stream) {
+  if (E <= 0 || El <= 0 || E % El || n > MAX_RANKS) return -1;
+  ep_plan_kernel<<<E, 256, 0, (cudaStream_t)stream>>>(indices, S, table, rank, n, E, El, cap, dest_rank,
+                                                      dest_row, seg, tot, overflow);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
 
 XB_API int xb_ep_exchange_counts(const int* counts, const unsigned long long* table_ptrs,
                                  const unsigned long long* flag_ptrs, int slot, int rank, int n, int E,

@@ -31,6 +31,7 @@ S_COUNTS, S_DISP, S_RET, S_BDISP, S_BRET = 0, 16, 32, 48, 64
 C_DISP, C_RET, C_BDISP, C_BRET = 96, 97, 98, 99
 WAIT_MS = 2000
 _WS: Dict = {}
+_SRC_ROW: Dict = {}
 
 
 def fused_ep_available() -> bool:
@@ -114,6 +115,26 @@ def _make_plan(ws: _Workspace, indices: torch.Tensor) -> _Plan:
     _lib.check(ws.lib.xb_ep_exchange_counts(counts.data_ptr(), ws.ptrs(ws.o_table), ws.ptrs(0), S_COUNTS,
                                             ws.rank, ws.N, ws.E, ws.epoch["counts"], WAIT_MS,
                                             _lib.stream_ptr()), "xb_ep_exchange_counts")
+    if os.environ.get("XORL_B200_EP_PLAN_KERNEL", "1") == "1":
+        # one kernel: per-slot destination (rank, row), local segment table, overflow flag
+        S = flat.numel()
+        p = _Plan()
+        p.T, p.k = T, k
+        p.dest_rank = torch.empty(S, device=dev, dtype=torch.int32)
+        p.dest_row = torch.empty(S, device=dev, dtype=torch.int32)
+        p.seg = torch.empty(ws.El + 1, device=dev, dtype=torch.int32)
+        p.tot = torch.empty(ws.El, device=dev, dtype=torch.int32)
+        p.overflow = torch.zeros(1, device=dev, dtype=torch.int32)
+        table_ptr = ws.heap.data_ptr() + ws.o_table
+        _lib.check(ws.lib.xb_ep_plan(flat.contiguous().data_ptr(), S, ctypes.c_void_p(table_ptr), ws.rank, ws.N, ws.E,
+                                     ws.El, ws.cap, p.dest_rank.data_ptr(), p.dest_row.data_ptr(),
+                                     p.seg.data_ptr(), p.tot.data_ptr(), p.overflow.data_ptr(),
+                                     _lib.stream_ptr()), "xb_ep_plan")
+        key = (S, k, dev)
+        if key not in _SRC_ROW:
+            _SRC_ROW[key] = (torch.arange(S, device=dev) // k).to(torch.int32)
+        p.src_row = _SRC_ROW[key]
+        return p
     table = ws.heap[ws.o_table:ws.o_table + ws.N * ws.E * 4].view(torch.int32).view(ws.N, ws.E).long()
     tot = table.sum(0)                                              # [E] rows per expert (all sources)
     padded = (tot + moe_ops.SEG_ALIGN - 1) // moe_ops.SEG_ALIGN * moe_ops.SEG_ALIGN
