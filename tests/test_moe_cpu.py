@@ -42,3 +42,19 @@ def test_moe_block_matches_naive():
     (out.sum() + aux).backward()
     assert x.grad is not None and blk.gate.weight.grad is not None
     assert blk.experts.gate_up_proj.grad.abs().sum() > 0
+
+
+def test_canonical_combine_is_order_independent_and_exact():
+    import torch
+    from xorl_b200.ops.moe import canonical_combine
+    torch.manual_seed(0)
+    T, k, H = 7, 6, 9
+    y = torch.randn(T, k, H).bfloat16()
+    w = torch.rand(T, k)
+    out = canonical_combine(y, w)
+    ref = (y.double() * w.double().unsqueeze(-1))
+    tree = ((ref[:, 0] + ref[:, 1]) + (ref[:, 2] + ref[:, 3])) + (ref[:, 4] + ref[:, 5])
+    assert torch.equal(out, tree.to(torch.bfloat16))
+    # the same bits whatever the memory layout of the slots (transposed storage, non-contiguous)
+    y2 = y.permute(1, 0, 2).contiguous().permute(1, 0, 2)
+    assert torch.equal(canonical_combine(y2, w), out)

@@ -128,7 +128,8 @@ class MoEBlock(nn.Module):
             from ..parallel import ep as ep_ops
             out = ep_ops.ep_moe_forward(x, weights, indices, self.experts, self.cfg.num_experts, ctx)
         else:
-            out = moe_ops.local_moe_forward(x, weights, indices, self.experts, self.cfg.num_experts)
+            out = moe_ops.local_moe_forward(x, weights, indices, self.experts, self.cfg.num_experts,
+                                            canonical=bool(ctx.aux.get("canonical_moe", False)))
         if self.shared_expert is not None:
             sh = self.shared_expert(x)
             if self.shared_expert_gate is not None:

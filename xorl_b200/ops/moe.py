@@ -375,6 +375,23 @@ class _Combine(torch.autograd.Function):
         return dy, dw, None, None
 
 
+def canonical_combine(y_slots: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """Bit-reproducible weighted sum over the k expert outputs of every token: products and sums in
+    fp64, added as a fixed balanced binary tree over the slot axis (slot order = the router's
+    order), one final rounding to the output dtype.  The result does not depend on how slots were
+    permuted, exchanged or which rank computed which expert -- the parity lane between training and
+    serving (src/xorl/distributed/canonical_moe.py, canonical_combine.py:315)."""
+    T, k, H = y_slots.shape
+    terms = y_slots.double() * weights.double().unsqueeze(-1)
+    parts = [terms[:, j] for j in range(k)]
+    while len(parts) > 1:
+        nxt = [parts[i] + parts[i + 1] for i in range(0, len(parts) - 1, 2)]
+        if len(parts) % 2:
+            nxt.append(parts[-1])
+        parts = nxt
+    return parts[0].to(y_slots.dtype)
+
+
 def token_of_row(dest: torch.Tensor, rows: int, k: int) -> torch.Tensor:
     """Inverse of ``dest`` [T*k]: token index stored in every buffer row, -1 for padding rows."""
     tok = torch.full((rows,), -1, device=dest.device, dtype=torch.int32)
@@ -383,14 +400,14 @@ def token_of_row(dest: torch.Tensor, rows: int, k: int) -> torch.Tensor:
 
 
 def local_moe_forward(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor, experts,
-                      num_experts: int) -> torch.Tensor:
+                      num_experts: int, canonical: bool = False) -> torch.Tensor:
     """All experts local: gather tokens into expert-sorted aligned segments, run the grouped MLP,
     combine the k expert outputs of every token with its routing weights (fp32 accumulation)."""
     T, H = x.shape
     k = indices.shape[1]
     dest, seg, _ = aligned_sort_indices(indices.reshape(-1), num_experts)
     rows = buffer_rows(T * k, num_experts)
-    if _permute_kernels_ok(x):
+    if _permute_kernels_ok(x) and not canonical:
         tok = token_of_row(dest, rows, k)
         dest2 = dest.view(T, k)
         buf = _Permute.apply(x, dest2, tok)
@@ -400,5 +417,7 @@ def local_moe_forward(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
     buf = x.new_zeros((rows, H)).index_copy(0, dest, x.index_select(0, token_of_slot))
     y = expert_mlp_aligned(buf, seg, experts.gate_up_proj, experts.down_proj, **experts_mlp_kwargs(experts))
     y_slots = y.index_select(0, dest).reshape(T, k, H)
+    if canonical:
+        return canonical_combine(y_slots, weights)
     out = (y_slots.float() * weights.unsqueeze(-1).float()).sum(1)
     return out.to(x.dtype)
