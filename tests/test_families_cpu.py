@@ -162,7 +162,7 @@ def test_mla_matches_explicit_formula():
     torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("name", ["tiny-gpt-oss", "tiny-deepseek-v3", "tiny-qwen3-moe"])
+@pytest.mark.parametrize("name", ["tiny-gpt-oss", "tiny-deepseek-v3", "tiny-qwen3-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe"])
 def test_family_hf_roundtrip(name, tmp_path):
     """Export to HF-named safetensors and load back into a fresh engine: identical weights."""
     from xorl_b200.checkpoint.hf_io import load_hf_weights, save_hf_weights
@@ -187,6 +187,10 @@ def test_family_hf_roundtrip(name, tmp_path):
     if name == "tiny-gpt-oss":
         assert "model.layers.0.mlp.router.weight" in names and "model.layers.0.mlp.experts.gate_up_proj_bias" in names
         assert "model.layers.0.self_attn.sinks" in names
+    if name.startswith("tiny-qwen3-5"):
+        assert "model.layers.0.linear_attn.in_proj_qkv.weight" in names and "model.layers.0.linear_attn.conv1d.weight" in names
+        assert "model.layers.0.linear_attn.in_proj_z.weight" in names and "model.layers.0.linear_attn.A_log" in names
+        assert "model.layers.3.self_attn.q_proj.weight" in names and not any("out_gate" in n or "qkv_proj" in n for n in names)
     if name == "tiny-deepseek-v3":
         assert "model.layers.1.mlp.shared_experts.gate_proj.weight" in names
         assert "model.layers.1.mlp.experts.3.down_proj.weight" in names

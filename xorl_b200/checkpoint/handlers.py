@@ -152,8 +152,109 @@ class GptOssHandler(CheckpointHandler):
         return super().from_hf(name, parts)
 
 
+class Qwen35Handler(CheckpointHandler):
+    """Qwen3.5 / Qwen3.5-MoE.  On disk the linear-attention mixer is ``linear_attn`` with
+    ``in_proj_qkv`` (= rows of q, k, v), ``in_proj_z / in_proj_a / in_proj_b``, one ``conv1d.weight``
+    [C, 1, K] (= q, k, v taps), ``norm``, ``out_proj``, ``dt_bias``, ``A_log``; gated attention stores
+    query and output gate in one ``q_proj`` whose rows alternate per head [query D | gate D]
+    (src/xorl/models/transformers/qwen3_5_shared.py:185-300, qwen3_5/modeling_qwen3_5.py).  Export
+    buffers the pieces of a fused tensor until the last one has been seen."""
+    _SINGLE = {"g_proj": "in_proj_z", "a_proj": "in_proj_a", "b_proj": "in_proj_b", "o_proj": "out_proj"}
+
+    def __init__(self, cfg):
+        super().__init__(cfg)
+        x = cfg.extra
+        self.lk = x["linear_num_key_heads"] * x["linear_key_head_dim"]
+        self.lv = x["linear_num_value_heads"] * x["linear_value_head_dim"]
+        self.Hq, self.D = cfg.num_attention_heads, cfg.head_dim
+        self._pending: Dict[str, Dict[str, torch.Tensor]] = {}
+
+    def _is_linear(self, fq: str) -> bool:
+        m = re.search(r"layers\.(\d+)\.", fq)
+        return bool(m) and self.cfg.layer_types[int(m.group(1))] == "linear_attention"
+
+    # ---- export ---------------------------------------------------------------------------------
+    def to_hf(self, name, t):
+        fq = to_checkpoint_fqn(name)
+        if ".self_attn." in fq and self._is_linear(fq):
+            base, leaf = fq.split(".self_attn.", 1)
+            la = base + ".linear_attn."
+            part = leaf.split(".")[0]
+            if part in ("q_proj", "k_proj", "v_proj") or part in ("q_conv1d", "k_conv1d", "v_conv1d"):
+                conv = "conv1d" in part
+                key = la + ("conv1d.weight" if conv else "in_proj_qkv.weight")
+                buf = self._pending.setdefault(key, {})
+                buf[part[0]] = t.unsqueeze(1) if conv else t
+                if len(buf) == 3:
+                    del self._pending[key]
+                    yield key, torch.cat([buf["q"], buf["k"], buf["v"]], dim=0).contiguous()
+            elif part in self._SINGLE:
+                yield la + leaf.replace(part, self._SINGLE[part], 1), t
+            elif part == "o_norm_weight":
+                yield la + "norm.weight", t
+            else:                                                   # dt_bias, A_log
+                yield la + leaf, t
+            return
+        if ".self_attn.qkv_proj.weight" in fq or ".self_attn.out_gate.weight" in fq:
+            base = fq.split(".self_attn.", 1)[0] + ".self_attn."
+            buf = self._pending.setdefault(base, {})
+            buf["qkv" if "qkv_proj" in fq else "gate"] = t
+            if len(buf) == 2:
+                del self._pending[base]
+                q, k, v = buf["qkv"].split([self.q, self.kv, self.kv], dim=0)
+                qg = torch.cat([q.view(self.Hq, self.D, -1), buf["gate"].view(self.Hq, self.D, -1)], dim=1)
+                yield base + "q_proj.weight", qg.reshape(2 * self.q, -1).contiguous()
+                yield base + "k_proj.weight", k.contiguous()
+                yield base + "v_proj.weight", v.contiguous()
+            return
+        if ".mlp.shared_expert_gate." in fq:
+            yield fq, t
+            return
+        yield from super().to_hf(name, t)
+
+    # ---- import ---------------------------------------------------------------------------------
+    def hf_sources(self, name):
+        fq = to_checkpoint_fqn(name)
+        if ".self_attn." in fq and self._is_linear(fq):
+            base, leaf = fq.split(".self_attn.", 1)
+            la = base + ".linear_attn."
+            part = leaf.split(".")[0]
+            if part in ("q_proj", "k_proj", "v_proj"):
+                return [la + "in_proj_qkv.weight"]
+            if "conv1d" in part:
+                return [la + "conv1d.weight"]
+            if part in self._SINGLE:
+                return [la + leaf.replace(part, self._SINGLE[part], 1)]
+            if part == "o_norm_weight":
+                return [la + "norm.weight"]
+            return [la + leaf]
+        if ".self_attn.out_gate.weight" in fq:
+            return [fq.replace("out_gate", "q_proj")]
+        return super().hf_sources(name)
+
+    def from_hf(self, name, parts):
+        fq = to_checkpoint_fqn(name)
+        if ".self_attn." in fq and self._is_linear(fq):
+            part = fq.split(".self_attn.", 1)[1].split(".")[0]
+            t = parts[0]
+            if part in ("q_proj", "k_proj", "v_proj") or "conv1d" in part:
+                lo = {"q": 0, "k": self.lk, "v": 2 * self.lk}[part[0]]
+                hi = lo + (self.lv if part[0] == "v" else self.lk)
+                t = t[lo:hi]
+                return (t.squeeze(1) if "conv1d" in part else t).contiguous()
+            return t
+        if ".self_attn.out_gate.weight" in fq:
+            return parts[0].view(self.Hq, 2, self.D, -1)[:, 1].reshape(self.q, -1).contiguous()
+        if ".self_attn.qkv_proj.weight" in fq:
+            q = parts[0].view(self.Hq, 2, self.D, -1)[:, 0].reshape(self.q, -1)
+            return torch.cat([q, parts[1], parts[2]], dim=0).contiguous()
+        return super().from_hf(name, parts)
+
+
 def get_checkpoint_handler(cfg) -> CheckpointHandler:
     mt = getattr(cfg, "model_type", "")
+    if mt in ("qwen3_5", "qwen3_5_moe", "qwen3_next"):
+        return Qwen35Handler(cfg)
     if mt == "gpt_oss":
         return GptOssHandler(cfg)
     if mt in ("deepseek_v3", "glm4_moe"):
