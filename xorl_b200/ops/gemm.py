@@ -85,6 +85,24 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
+    """dW = dy2^T @ x2 for weight ``w``: written straight into the flat gradient buffer of the ZeRO
+    unit (returns None), deferred to a W slot of a zero-bubble schedule, or returned as a tensor."""
+    tgt, fresh = grad_target(w)
+    store = current_wgrad_store()
+    if tgt is not None and store is not None:
+        # zero-bubble: the buffer slice is claimed now, the GEMM runs in a later W slot
+        mark_written(w)
+        store.append(lambda a=dy2, b=x2, o=tgt, acc=not fresh:
+                     gemm(a, b, a_mn=True, b_mn=True, out=o, accumulate=acc))
+        return None
+    if tgt is not None:
+        gemm(dy2, x2, a_mn=True, b_mn=True, out=tgt, accumulate=not fresh)
+        mark_written(w)
+        return None
+    return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+
+
 class _Linear(torch.autograd.Function):
     """y = x @ w.T.  The weight is kept on ctx as a plain attribute (not through
     save_for_backward) because ZeRO-3 re-fills the same gathered buffer before backward."""
@@ -111,19 +129,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w, b_mn=True).reshape(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            tgt, fresh = grad_target(w)
-            store = current_wgrad_store()
-            if tgt is not None and store is not None:
-                # zero-bubble: the buffer slice is claimed now, the GEMM runs in a later W slot
-                mark_written(w)
-                store.append(lambda a=dy2, b=x2, o=tgt, acc=not fresh:
-                             gemm(a, b, a_mn=True, b_mn=True, out=o, accumulate=acc))
-            elif tgt is not None:
-                # write straight into the flat gradient buffer of the ZeRO unit
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=tgt, accumulate=not fresh)
-                mark_written(w)
-            else:
-                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+            dw = weight_grad(dy2, x2, w)
         return dx, dw
 
 
