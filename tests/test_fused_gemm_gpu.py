@@ -60,29 +60,34 @@ def test_ag_gemm_transposed_weight():
     assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
 
 
-@pytest.mark.parametrize("M,N,K,R", [(2048, 1024, 256, 4), (1024, 768, 512, 2), (4096, 4096, 512, 8)])
+@pytest.mark.parametrize("M,N,K,R", [(2048, 1024, 256, 4), (1024, 768, 512, 2), (4096, 4096, 512, 8),
+                                     (1920, 512, 256, 2)])      # 960 rows per rank: blocks straddle tiles
 def test_gemm_rs_one_device(M, N, K, R):
+    """Partial results with the rotated block order and the per-owner completion counters (which
+    must be back at zero after every launch), then the reduction over the ranks' blocks."""
     from xorl_b200.ops import _lib
-    from xorl_b200.ops.fused_gemm import Peers, gemm_rs, rs_reduce
+    from xorl_b200.ops.fused_gemm import Peers, _shape_state, gemm_rs, rs_reduce
     torch.manual_seed(2)
     per = M // R
     As = [_rand(M, K) for _ in range(R)]
     Bs = [_rand(N, K) for _ in range(R)]
-    stages = [torch.full((R, per, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(R)]
-    ptrs = [s.data_ptr() for s in stages]
-    for _ in range(2):           # counters must be back at zero after each launch
+    parts = [torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(R)]
+    ptrs = [s.data_ptr() for s in parts]
+    for _ in range(2):
         for r in range(R):
-            gemm_rs(As[r], Bs[r], ptrs, per, Peers(r, R))
+            gemm_rs(As[r], Bs[r], parts[r], ptrs, per, Peers(r, R))
     resid = _rand(per, N)
-    outs = [rs_reduce(stages[o], o, torch.empty(per, N, device="cuda", dtype=torch.bfloat16),
+    outs = [rs_reduce([parts[r][o * per:(o + 1) * per] for r in range(R)],
+                      torch.empty(per, N, device="cuda", dtype=torch.bfloat16),
                       residual=resid if o == 0 else None) for o in range(R)]
     torch.cuda.synchronize()
     _lib.raise_on_status()
+    counters = _shape_state(torch.device("cuda", torch.cuda.current_device()), ("rs", M, N, K), 1)["counters"]
+    assert int(counters.abs().sum()) == 0
     partial = [a.float() @ b.float().t() for a, b in zip(As, Bs)]
+    for r in range(R):
+        assert (parts[r].float() - partial[r]).abs().max().item() <= 2e-2 * partial[r].abs().max().item() + 1e-2
     for o in range(R):
-        for r in range(R):
-            ref_p = partial[r][o * per:(o + 1) * per]
-            assert (stages[o][r].float() - ref_p).abs().max().item() <= 2e-2 * ref_p.abs().max().item() + 1e-2
         ref = sum(p[o * per:(o + 1) * per].to(torch.bfloat16).float() for p in partial)
         if o == 0:
             ref = ref + resid.float()

@@ -51,6 +51,7 @@ def _check(ref, got, tol=0.03):
 CASES = [
     ("fsdp2", 2, dict()),
     ("tp2", 2, dict(tensor_parallel_size=2)),
+    ("tp2_sp_fused", 2, dict(tensor_parallel_size=2, tensor_parallel_sequence_parallel=True)),
     ("pp2_1f1b", 2, dict(pipeline_parallel_size=2, pipeline_parallel_schedule="1F1B")),
     ("pp2_zbv", 2, dict(pipeline_parallel_size=2, pipeline_parallel_schedule="zbvzerobubble")),
     ("ulysses2", 2, dict(ulysses_parallel_size=2)),
@@ -68,6 +69,11 @@ def test_dense_parallel_modes(tmp_path, name, nproc, train):
     ref = _run(tmp_path, "ref", 1)
     got = _run(tmp_path, name, nproc, **train)
     _check(ref, got)
+    if train.get("tensor_parallel_sequence_parallel"):
+        # every collective GEMM of the run went through the single-kernel path
+        with open(tmp_path / name / "training_metrics.json") as f:
+            calls = json.load(f)["tp_collective_gemms"]
+        assert calls["fused"] > 0 and calls["unfused"] == 0, calls   # token counts are multiples of 128
 
 
 @pytest.mark.parametrize("dispatch", ["alltoall", "fused"])

@@ -196,6 +196,9 @@ class TrainingArguments:
     ep_outside: Optional[bool] = None
     ulysses_parallel_size: int = 1
     tensor_parallel_size: int = 1
+    # sequence-parallel activations between the tensor-parallel regions: all-gather -> GEMM and
+    # GEMM -> reduce-scatter run as single kernels over NVLink peer memory
+    tensor_parallel_sequence_parallel: bool = False
     lm_head_tensor_parallel_size: int = 1
     ringattn_parallel_size: int = 1
     pipeline_parallel_size: int = 1

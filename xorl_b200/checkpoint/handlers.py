@@ -251,8 +251,68 @@ class Qwen35Handler(CheckpointHandler):
         return super().from_hf(name, parts)
 
 
+class NemotronHHandler(CheckpointHandler):
+    """Nemotron-H: the module tree is ``backbone.*`` on disk (``embeddings``, ``norm_f``, one
+    ``mixer`` per layer), attention projections are separate, the depthwise convolution is stored as
+    ``conv1d.weight [C, 1, K]`` / ``conv1d.bias``, and the non-gated experts are one
+    ``up_proj [I, latent]`` / ``down_proj [latent, I]`` pair per expert
+    (src/xorl/models/transformers/nemotron_h/checkpoint_handler.py)."""
+    _LEAF = (("mixer.conv1d_weight", "mixer.conv1d.weight"), ("mixer.conv1d_bias", "mixer.conv1d.bias"),
+             ("mixer.norm_weight", "mixer.norm.weight"), ("mixer.shared_expert.", "mixer.shared_experts."))
+
+    def _disk(self, name: str) -> str:
+        fq = to_checkpoint_fqn(name)
+        if fq.startswith("model."):
+            fq = "backbone." + fq[len("model."):]
+        fq = fq.replace("backbone.embed_tokens.", "backbone.embeddings.")
+        if fq.startswith("backbone.norm."):
+            fq = fq.replace("backbone.norm.", "backbone.norm_f.")
+        for a, b in self._LEAF:
+            fq = fq.replace(a, b)
+        return fq
+
+    def to_hf(self, name, t):
+        fq = self._disk(name)
+        if ".mixer.qkv_proj." in fq:
+            q, k, v = t.split([self.q, self.kv, self.kv], dim=0)
+            for n, part in (("q_proj", q), ("k_proj", k), ("v_proj", v)):
+                yield fq.replace("qkv_proj", n), part.contiguous()
+        elif fq.endswith(".mixer.experts.gate_up_proj"):
+            base = fq[: fq.index(".experts.")]
+            for e in range(t.shape[0]):
+                yield f"{base}.experts.{e}.up_proj.weight", t[e].t().contiguous()
+        elif fq.endswith(".mixer.experts.down_proj"):
+            base = fq[: fq.index(".experts.")]
+            for e in range(t.shape[0]):
+                yield f"{base}.experts.{e}.down_proj.weight", t[e].t().contiguous()
+        elif fq.endswith(".mixer.conv1d.weight"):
+            yield fq, t.unsqueeze(1).contiguous()
+        else:
+            yield fq, t
+
+    def hf_sources(self, name):
+        fq = self._disk(name)
+        if ".mixer.qkv_proj." in fq:
+            return [fq.replace("qkv_proj", n) for n in ("q_proj", "k_proj", "v_proj")]
+        if fq.endswith(".mixer.experts.gate_up_proj") or fq.endswith(".mixer.experts.down_proj"):
+            base = fq[: fq.index(".experts.")]
+            leaf = "up_proj" if fq.endswith("gate_up_proj") else "down_proj"
+            return [f"{base}.experts.{e}.{leaf}.weight" for e in range(self.cfg.num_experts)]
+        return [fq]
+
+    def from_hf(self, name, parts):
+        fq = self._disk(name)
+        if fq.endswith(".mixer.experts.gate_up_proj") or fq.endswith(".mixer.experts.down_proj"):
+            return torch.stack([p.t() for p in parts])
+        if fq.endswith(".mixer.conv1d.weight"):
+            return parts[0].squeeze(1).contiguous()
+        return parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
+
+
 def get_checkpoint_handler(cfg) -> CheckpointHandler:
     mt = getattr(cfg, "model_type", "")
+    if mt == "nemotron_h":
+        return NemotronHHandler(cfg)
     if mt in ("qwen3_5", "qwen3_5_moe", "qwen3_next"):
         return Qwen35Handler(cfg)
     if mt == "gpt_oss":

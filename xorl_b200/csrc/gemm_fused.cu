@@ -1,21 +1,24 @@
 // bf16 GEMM on CTA pairs with the collective of one operand, or of the result, in the same kernel.
 //
 //   gather  (all-gather -> GEMM):  one operand is sharded by rows over the ranks (sequence-parallel
-//           activations of a tensor-parallel column linear, or a row-sharded ZeRO-3 weight).  Two
+//           activations of a tensor-parallel column linear, or a row-sharded ZeRO-3 weight).  Four
 //           extra warps per CTA pull the peers' shards into this rank's full copy with plain 16-byte
-//           loads over NVLink, one chunk of tile rows at a time and all CTAs on the same chunk, and
-//           count each finished chunk in global memory.  The TMA warp waits for the chunk that its
-//           next work item reads and then loads it from local memory, so every remote byte crosses
-//           NVLink once and the tensor cores run on the chunks that have already arrived.  Work
-//           items and chunks are walked in the same order, starting at this rank's own rows.
+//           loads over NVLink (16 in flight per thread), one chunk of tile rows at a time and all
+//           CTAs on the same chunk, and count each finished chunk in global memory.  The TMA warp
+//           waits for the chunk that its next work item reads and then loads it from local memory,
+//           so every remote byte crosses NVLink once and the tensor cores run on the chunks that
+//           have already arrived.  Work items and chunks are walked in the same order, starting at
+//           this rank's own rows.
 //   scatter (GEMM -> reduce-scatter):  the rows of the result are owned by the ranks in equal
-//           blocks.  The epilogue converts every partial tile to bf16 and stores it straight into
-//           the owner's staging buffer (slot [this rank]); a count of finished 32 x 128 units per
-//           512-row block tells when all partial rows for an owner have been written, and the owner
-//           is then signalled with a release store.  Blocks are computed in the order rank+1, rank+2,
-//           ..., own block last, so the peers' contributions for the own block arrive while this
-//           rank is still computing; at the end all CTAs wait (bounded) for the peers' signals and
-//           sum the staged partials of the own rows in fp32, in rank order.
+//           blocks.  Every rank writes its partial result into its own symmetric buffer with the
+//           ordinary epilogue (local, coalesced by the memory system), computing the blocks in the
+//           order rank+1, rank+2, ..., own block last; warps count the finished 32-row x 128-column
+//           units per owner, and the warp that completes an owner's block signals that owner with a
+//           release store.  Meanwhile the communication warps of the owner wait for those signals
+//           in the order in which the peers finish (rank-1 first) and pull each peer's partial block
+//           over NVLink into local staging, so the transfers overlap the remaining tiles.  At the
+//           end all CTAs sum the own partial block and the pulled ones in fp32, in rank order
+//           (+ an optional residual), into the output.
 //
 // This is the kernel behind tensor-parallel linears with sequence-parallel activations: the
 // reference runs them as DTensor collectives followed / preceded by cuBLAS
@@ -23,17 +26,20 @@
 // NCCL all-gather (src/xorl/distributed/torch_parallelize.py:333-783).
 //
 // Handshakes use epoch flags in each rank's symmetric flag area (st.release.sys / ld.acquire.sys),
-// every wait is bounded by %globaltimer, and with null flag pointers the kernel runs the same data
-// path on one device (all "peers" are local buffers), which is how it is tested on a single GPU.
+// every wait is bounded by %globaltimer, and with null flag pointers the gather and the partial-
+// result paths run on one device (all "peers" are local buffers), which is how they are tested on
+// a single GPU.
 #include "gemm2_core.cuh"
 
 namespace xb_gemmf {
 using namespace xb_gemm2;
 
 constexpr int MAX_R = 16;
-constexpr int COMM_THREADS = 64;                    // warps 10 and 11
+constexpr int COMM_THREADS = 128;                   // warps 10 to 13
+constexpr int COPY_UNROLL = 16;                     // 16-byte loads in flight per communication thread
 constexpr int NT = NUM_THREADS + COMM_THREADS;
 constexpr int EPI_THREADS = 256;
+constexpr int MAX_SUB = 16;                         // sub-blocks of an owner's rows, signalled one by one
 
 struct Comm {
   int rank, nranks;
@@ -50,13 +56,15 @@ struct Comm {
   unsigned long long* ready;     // [num_chunks] arrival counters (monotonic)
   unsigned long long ready_target;
   // ---- scatter
-  __nv_bfloat16* stage[MAX_R];   // rank o's staging buffer [nranks][rows_per][N]
-  int rows_per;                  // result rows owned by one rank (multiple of 512)
-  __nv_bfloat16* out;            // this rank's reduced rows [rows_per][ldo]; null: no reduction here
+  const __nv_bfloat16* partial[MAX_R];   // rank r's partial result [M][N] (this rank's one is p.C)
+  __nv_bfloat16* pulled;         // local staging [nranks][rows_per][N] for the peers' partial blocks
+  int rows_per;                  // result rows owned by one rank (multiple of 32)
+  __nv_bfloat16* out;            // this rank's reduced rows [rows_per][ldo]; null: partial result only
   long long ldo;
   const __nv_bfloat16* residual; // optional, added to the reduced rows
-  int* counters;                 // [num_m_blocks] units, then [nranks] blocks, then [1] CTAs; zero on entry/exit
-  int units_per_mblock, mblocks_per_rank;
+  int* counters;                 // [nranks][MAX_SUB] units, [1] epilogue CTAs, [1] copy CTAs; zero on entry/exit
+  int sub_rows, num_sub;         // an owner's rows are signalled in num_sub pieces of sub_rows rows
+  int units_per_sub;
   // ---- flags (null: single-device run without handshakes)
   int* flags[MAX_R];
   int ready_slot, done_slot;
@@ -113,37 +121,99 @@ __device__ __forceinline__ Item decode_rot(const Params& p, const Comm& c, int w
   return it;
 }
 
-// Sum of the staged partials of this rank's rows, fp32 in rank order, optional residual.
-__device__ __forceinline__ void reduce_rows(const Comm& c, int N, long long first, long long stride) {
-  const long long row_vec = N >> 3;
-  const long long nvec = (long long)c.rows_per * row_vec;
-  const long long slot_vec = nvec;
-  const uint4* st = reinterpret_cast<const uint4*>(c.stage[c.rank]);
-  for (long long i = first; i < nvec; i += stride) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int r = 0; r < c.nranks; ++r) {
-      const uint4 v = st[(long long)r * slot_vec + i];
-      const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), d = unpack_bf16x2(v.z),
-                   e = unpack_bf16x2(v.w);
-      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-      acc[4] += d.x; acc[5] += d.y; acc[6] += e.x; acc[7] += e.y;
-    }
-    const long long row = i / row_vec;
-    const long long col = (i - row * row_vec) << 3;
-    if (c.residual != nullptr) {
-      const uint4 v = *reinterpret_cast<const uint4*>(c.residual + row * c.ldo + col);
-      const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), d = unpack_bf16x2(v.z),
-                   e = unpack_bf16x2(v.w);
-      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-      acc[4] += d.x; acc[5] += d.y; acc[6] += e.x; acc[7] += e.y;
-    }
-    uint4 o;
-    o.x = pack_bf16x2(acc[0], acc[1]);
-    o.y = pack_bf16x2(acc[2], acc[3]);
-    o.z = pack_bf16x2(acc[4], acc[5]);
-    o.w = pack_bf16x2(acc[6], acc[7]);
-    *reinterpret_cast<uint4*>(c.out + row * c.ldo + col) = o;
+// dst[lo, hi) = src[lo, hi) in 16-byte vectors, this thread taking every stride-th one from `first`.
+// Up to COPY_UNROLL loads are in flight per thread, also in the last, partial batch (a chunk of tile
+// rows is only a dozen strides of the whole grid long).
+__device__ __forceinline__ void copy_span(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                          long long lo, long long hi, long long first, long long stride) {
+  for (long long i = lo + first; i < hi; i += COPY_UNROLL * stride) {
+    uint4 v[COPY_UNROLL];
+#pragma unroll
+    for (int k = 0; k < COPY_UNROLL; ++k)
+      if (i + k * stride < hi) v[k] = src[i + k * stride];
+#pragma unroll
+    for (int k = 0; k < COPY_UNROLL; ++k)
+      if (i + k * stride < hi) dst[i + k * stride] = v[k];
   }
+}
+
+// out = sum over ranks of src[r] (each a contiguous [rows_per][N] block), fp32 in rank order,
+// optional residual.
+struct BlockSources {
+  const uint4* p[MAX_R];
+};
+__device__ __forceinline__ void acc8(float (&acc)[8], const uint4 v) {
+  const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), d = unpack_bf16x2(v.z), e = unpack_bf16x2(v.w);
+  acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+  acc[4] += d.x; acc[5] += d.y; acc[6] += e.x; acc[7] += e.y;
+}
+__device__ __forceinline__ void reduce_rows(const BlockSources& src, int nranks, int rows_per, int N,
+                                            __nv_bfloat16* out, long long ldo, const __nv_bfloat16* residual,
+                                            long long first, long long stride) {
+  constexpr int U = 4;      // vectors per thread and step: U loads in flight for every rank
+  const long long row_vec = N >> 3;
+  const long long nvec = (long long)rows_per * row_vec;
+  for (long long i0 = first; i0 < nvec; i0 += U * stride) {
+    float acc[U][8];
+#pragma unroll
+    for (int k = 0; k < U; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[k][j] = 0.f;
+    for (int r = 0; r < nranks; ++r) {
+      const uint4* sp = src.p[r];
+      uint4 v[U];
+#pragma unroll
+      for (int k = 0; k < U; ++k)
+        if (i0 + k * stride < nvec) v[k] = sp[i0 + k * stride];
+#pragma unroll
+      for (int k = 0; k < U; ++k)
+        if (i0 + k * stride < nvec) acc8(acc[k], v[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const long long i = i0 + k * stride;
+      if (i >= nvec) break;
+      const long long row = i / row_vec;
+      const long long col = (i - row * row_vec) << 3;
+      if (residual != nullptr) acc8(acc[k], *reinterpret_cast<const uint4*>(residual + row * ldo + col));
+      uint4 o;
+      o.x = pack_bf16x2(acc[k][0], acc[k][1]);
+      o.y = pack_bf16x2(acc[k][2], acc[k][3]);
+      o.z = pack_bf16x2(acc[k][4], acc[k][5]);
+      o.w = pack_bf16x2(acc[k][6], acc[k][7]);
+      *reinterpret_cast<uint4*>(out + row * ldo + col) = o;
+    }
+  }
+}
+
+// Last phase of the scatter path, run by the epilogue and the communication warps of every CTA:
+// wait (bounded) until this rank's own block is complete on all CTAs and all CTAs have pulled the
+// peers' blocks, then sum.  `slot`: this thread's index among all reducing threads of the grid.
+__device__ __forceinline__ void scatter_reduce(const Params& p, const Comm& c, int lane, long long slot) {
+  if (lane == 0) {
+    bool good = true;
+    for (int sb = 0; sb < c.num_sub && good; ++sb)
+      good = wait_flag(c.flags[c.rank] + c.ready_slot + c.rank * MAX_SUB + sb, c.epoch, p.status, 3000, c.limit_ns);
+    if (good && ld_acquire_gpu_u64(c.ready) < c.ready_target) {
+      const uint64_t t0 = xb_globaltimer();
+      for (uint32_t spin = 1;; ++spin) {
+        __nanosleep(100);
+        if (ld_acquire_gpu_u64(c.ready) >= c.ready_target) break;
+        if ((spin & 63u) == 0u && xb_globaltimer() - t0 > c.limit_ns) {
+          xb_report(p.status, XB_ERR_FLAG_TIMEOUT, XB_K_AG_GEMM, 3001);
+          break;
+        }
+      }
+    }
+  }
+  __syncwarp();
+  const long long blk = (long long)c.rows_per * p.N;
+  BlockSources src;
+  for (int r = 0; r < c.nranks; ++r)
+    src.p[r] = reinterpret_cast<const uint4*>(r == c.rank ? c.partial[r] + (long long)c.rank * blk
+                                                           : c.pulled + (long long)r * blk);
+  reduce_rows(src, c.nranks, c.rows_per, p.N, c.out, c.ldo, c.residual, slot,
+              (long long)gridDim.x * (EPI_THREADS + COMM_THREADS));
 }
 
 template <bool B_MN>
@@ -334,7 +404,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             ? ((p.ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(p.C) % 16) == 0)
                             : ((p.ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(p.C) % 16) == 0);
     if (c.scatter) {
-      // the owners must have finished reading what an earlier call staged in the same buffers
+      // the owners must have finished pulling what an earlier call left in this partial buffer
       if (linked && etid < c.nranks && etid != c.rank && c.done_needed > 0)
         wait_flag(c.flags[c.rank] + c.done_slot + etid, c.done_needed, p.status, 2000 + etid, c.limit_ns);
       named_bar(2, EPI_THREADS);
@@ -350,18 +420,11 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int row = item.m0 + 256 * u + (int)cta * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + u * BN + ((uint32_t)(q * 32) << 16);
       const int nchunks = u < item.nsub ? item.ncols / 32 : 0;
-      // destination row: the caller's C, or the owner's staging slot of this rank
       __nv_bfloat16* crow_bf = nullptr;
       float* crow_f = nullptr;
       if (row < p.M) {
-        if (c.scatter) {
-          const int o = row / c.rows_per;
-          crow_bf = c.stage[o] + ((long long)c.rank * c.rows_per + (row - o * c.rows_per)) * p.ldc;
-        } else if (p.out_fp32) {
-          crow_f = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc;
-        } else {
-          crow_bf = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc;
-        }
+        if (p.out_fp32) crow_f = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc;
+        else crow_bf = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc;
       }
 #pragma unroll 1
       for (int ch = 0; ch < nchunks; ++ch) {
@@ -395,7 +458,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
           } else {
             __nv_bfloat16* dst = crow_bf + col0;
-            const bool acc = p.accumulate && !c.scatter;
+            const bool acc = p.accumulate != 0;
             if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
@@ -431,60 +494,52 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       tc_fence_before();
       mbar_arrive_cluster(empty_leader);
       if (c.scatter) {
-        // count the finished 32-row x 128-column units of this 512-row block, warp by warp (no
-        // CTA-wide barrier inside the loop: warps may leave it at different items after an abort);
-        // the warp that completes a block, and with it an owner, signals that owner
+        // count the finished 32-row x 128-column units per owner, warp by warp (no CTA-wide
+        // barrier inside the loop: warps may leave it at different items after an abort); the
+        // warp that completes an owner's block tells that owner that it may pull the block
         __threadfence_system();
         __syncwarp();
-        if (lane == 0 && nchunks > 0) {
-          const int mb = item.m0 / 512;
+        const int row0 = item.m0 + 256 * u + (int)cta * BM + q * 32;
+        if (lane == 0 && nchunks > 0 && row0 < p.M) {
+          const int o = row0 / c.rows_per;
+          const int sb = (row0 - o * c.rows_per) / c.sub_rows;
           const int units = item.ncols / 128;
-          int* mb_units = c.counters;
-          int* owner_blocks = c.counters + p.num_m_blocks;
-          if (atomicAdd(mb_units + mb, units) + units == c.units_per_mblock) {
-            const int o = mb / c.mblocks_per_rank;
-            if (atomicAdd(owner_blocks + o, 1) + 1 == c.mblocks_per_rank) {
-              __threadfence_system();
-              if (linked) st_release_sys(c.flags[o] + c.ready_slot + c.rank, c.epoch);
-            }
+          if (atomicAdd(c.counters + o * MAX_SUB + sb, units) + units == c.units_per_sub) {
+            __threadfence_system();
+            if (linked) st_release_sys(c.flags[o] + c.ready_slot + c.rank * MAX_SUB + sb, c.epoch);
           }
         }
       }
     }
     if (c.scatter && c.out != nullptr) {
-      // ---- all partial rows for this rank: wait for every writer, then reduce
-      if (linked && etid < c.nranks)
-        wait_flag(c.flags[c.rank] + c.ready_slot + etid, c.epoch, p.status, 3000 + etid, c.limit_ns);
-      named_bar(2, EPI_THREADS);
-      reduce_rows(c, p.N, (long long)blockIdx.x * EPI_THREADS + etid, (long long)gridDim.x * EPI_THREADS);
+      scatter_reduce(p, c, lane, blockIdx.x * (EPI_THREADS + COMM_THREADS) + etid);
     }
     if (c.scatter) {
-      // the last CTA to get here clears the counters and releases the staging buffers
+      // the last CTA to get here clears the unit counters for the next call
       __threadfence();
       named_bar(2, EPI_THREADS);
       if (etid == 0) {
-        int* cta_count = c.counters + p.num_m_blocks + c.nranks;
+        int* cta_count = c.counters + c.nranks * MAX_SUB;
         if (atomicAdd(cta_count, 1) == (int)gridDim.x - 1) {
           __threadfence();
-          for (int i = 0; i < p.num_m_blocks + c.nranks + 1; ++i) c.counters[i] = 0;
-          if (linked && c.out != nullptr)
-            for (int r = 0; r < c.nranks; ++r)
-              if (r != c.rank) st_release_sys(c.flags[r] + c.done_slot + c.rank, c.epoch);
+          for (int i = 0; i <= c.nranks * MAX_SUB; ++i) c.counters[i] = 0;
         }
       }
     }
   } else {
-    // ------------------------------- communication warps: all-gather ------------------
-    const int ctid = threadIdx.x - NUM_THREADS;     // 0..63
+    // ------------------------------- communication warps --------------------------------
+    const int ctid = threadIdx.x - NUM_THREADS;     // 0..127
+    const long long stride = (long long)gridDim.x * COMM_THREADS;
+    const long long first = (long long)blockIdx.x * COMM_THREADS + ctid;
+    bool copied = false;
     if (c.gather) {
+      // ---- all-gather of the sharded operand, chunk by chunk
       if (linked && blockIdx.x == 0 && ctid < c.nranks && ctid != c.rank) {
         // everything earlier in this stream (the kernel that produced the shard) is complete
         __threadfence_system();
         st_release_sys(c.flags[ctid] + c.ready_slot + c.rank, c.epoch);
       }
       uint32_t seen = linked ? (1u << c.rank) : 0xffffffffu;
-      const long long stride = (long long)gridDim.x * COMM_THREADS;
-      const long long first = (long long)blockIdx.x * COMM_THREADS + ctid;
       for (int j = 0; j < c.num_chunks; ++j) {
         const int ch = (c.chunk0 + j) % c.num_chunks;
         const long long lo = (long long)ch * c.chunk_vec;
@@ -499,17 +554,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             __syncwarp();
             seen |= 1u << r;
           }
-          const uint4* src = c.shard[r] - (long long)r * c.shard_vec;   // indexed by the global vector
-          uint4* dst = c.full;
-          long long i = s0 + first;
-          for (; i + 7 * stride < s1; i += 8 * stride) {
-            uint4 v[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) v[k] = src[i + k * stride];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) dst[i + k * stride] = v[k];
-          }
-          for (; i < s1; i += stride) dst[i] = src[i];
+          // source indexed by the vector's position in the whole operand
+          copy_span(c.full, c.shard[r] - (long long)r * c.shard_vec, s0, s1, first, stride);
           s0 = s1;
         }
         fence_proxy_async();    // these ordinary stores are read through TMA by other CTAs
@@ -517,17 +563,38 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         named_bar(1, COMM_THREADS);
         if (ctid == 0) red_release_gpu_u64(c.ready + ch, 1ull);
       }
-      if (linked) {
-        // the last CTA to finish copying tells the peers that their shards are no longer read
-        __threadfence();
-        named_bar(1, COMM_THREADS);
-        if (ctid == 0) {
-          int* cta_count = c.counters;
-          if (atomicAdd(cta_count, 1) == (int)gridDim.x - 1) {
-            *cta_count = 0;
-            for (int r = 0; r < c.nranks; ++r)
-              if (r != c.rank) st_release_sys(c.flags[r] + c.done_slot + c.rank, c.epoch);
-          }
+      copied = true;
+    } else if (c.scatter && c.out != nullptr) {
+      // ---- pull the peers' partial blocks of this rank's rows, in the order in which they finish
+      const long long blk_vec = ((long long)c.rows_per * p.N) >> 3;
+      const long long sub_vec = ((long long)c.sub_rows * p.N) >> 3;
+      for (int k = 1; k < c.nranks; ++k) {
+        const int r = (c.rank - k + c.nranks) % c.nranks;
+        for (int sb = 0; sb < c.num_sub; ++sb) {      // the peer finishes them in this order
+          if (lane == 0)
+            wait_flag(c.flags[c.rank] + c.ready_slot + r * MAX_SUB + sb, c.epoch, p.status, 5000 + r, c.limit_ns);
+          __syncwarp();
+          copy_span(reinterpret_cast<uint4*>(c.pulled) + (long long)r * blk_vec,
+                    reinterpret_cast<const uint4*>(c.partial[r]) + (long long)c.rank * blk_vec,
+                    sb * sub_vec, (sb + 1) * sub_vec, first, stride);
+        }
+      }
+      __threadfence();
+      named_bar(1, COMM_THREADS);
+      if (ctid == 0) red_release_gpu_u64(c.ready, 1ull);
+      copied = true;
+      scatter_reduce(p, c, lane, blockIdx.x * (EPI_THREADS + COMM_THREADS) + EPI_THREADS + ctid);
+    }
+    if (copied && linked) {
+      // the last CTA to finish copying tells the peers that their buffers are no longer read
+      __threadfence();
+      named_bar(1, COMM_THREADS);
+      if (ctid == 0) {
+        int* cta_count = c.counters + (c.scatter ? c.nranks * MAX_SUB + 1 : 0);
+        if (atomicAdd(cta_count, 1) == (int)gridDim.x - 1) {
+          *cta_count = 0;
+          for (int r = 0; r < c.nranks; ++r)
+            if (r != c.rank) st_release_sys(c.flags[r] + c.done_slot + c.rank, c.epoch);
         }
       }
     }
@@ -543,8 +610,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 }
 
 __global__ void __launch_bounds__(256)
-rs_reduce_kernel(const Comm c, int N) {
-  reduce_rows(c, N, (long long)blockIdx.x * blockDim.x + threadIdx.x, (long long)gridDim.x * blockDim.x);
+rs_reduce_kernel(const BlockSources src, int nranks, int rows_per, int N, __nv_bfloat16* out, long long ldo,
+                 const __nv_bfloat16* residual) {
+  reduce_rows(src, nranks, rows_per, N, out, ldo, residual, (long long)blockIdx.x * blockDim.x + threadIdx.x,
+              (long long)gridDim.x * blockDim.x);
 }
 
 template <bool B_MN>
@@ -581,9 +650,9 @@ static int resident_pairs() {
 struct XbFusedArgs {
   const void* A;                 // [M, K] row-major (the local full copy when A is gathered)
   const void* B;                 // b_mn = 0: [N, K] row-major; b_mn = 1: [K, N] row-major
-  void* C;                       // plain result, or unused with scatter
+  void* C;                       // result; with scatter: this rank's partial buffer [M][N] (= partial_ptrs[rank])
   int M, N, K;
-  long long lda, ldb, ldc;       // ldc: leading dimension of C, or of the staging slots (scatter)
+  long long lda, ldb, ldc;
   int b_mn, out_fp32, accumulate;
   int rank, nranks;
   int gather;                    // 0 / 1 (A) / 2 (B)
@@ -593,8 +662,9 @@ struct XbFusedArgs {
   unsigned long long ready_counters;   // gather: device u64[num_chunks], monotonic
   unsigned long long ready_target;     // gather: value every chunk counter reaches in this call is
                                        //         ready_base + CTAs; pass ready_base here
-  unsigned long long stage_ptrs[16];   // scatter: every rank's staging buffer [nranks][rows][ldc]
-  void* out;                           // scatter: reduced rows of this rank (null: stage only)
+  unsigned long long partial_ptrs[16]; // scatter: every rank's partial-result buffer [M][N] (symmetric)
+  void* pulled;                        // scatter: local staging [nranks][rows_per_rank][N]
+  void* out;                           // scatter: reduced rows of this rank (null: partial result only)
   long long ldo;
   const void* residual;
   unsigned long long counters;         // device int[...] zeroed once by the caller
@@ -615,9 +685,11 @@ XB_API int xb_gemm_fused(XbFusedArgs* a, void* stream) {
     return -1;
   if (a->gather == 1 && (a->lda != K || (K % 8) || a->rows_per_rank * a->nranks < M)) return -4;   // contiguous chunks
   if (a->gather == 2 && (a->b_mn || a->ldb != K || (K % 8) || a->rows_per_rank * a->nranks < N)) return -4;
-  if (a->scatter && ((a->rows_per_rank % 512) || (N % 8) || a->ldc != N || a->out_fp32 ||
-                     a->rows_per_rank * a->nranks < M))
+  if (a->scatter && ((a->rows_per_rank % 32) || (N % 8) || a->ldc != N || a->out_fp32 || a->accumulate ||
+                     a->rows_per_rank * a->nranks != M))
     return -5;
+  if (a->scatter && a->out != nullptr && (a->flag_ptrs[0] == 0 || a->pulled == nullptr || a->ready_counters == 0))
+    return -7;       // pulling needs real peers; on one device only the partial result is produced
   CUtensorMap ta, tb, tb64;
   int rc = xb_make_tmap_2d(&ta, a->A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, a->lda, BM, BK,
                            CU_TENSOR_MAP_SWIZZLE_128B);
@@ -647,7 +719,7 @@ XB_API int xb_gemm_fused(XbFusedArgs* a, void* stream) {
   c.limit_ns = (unsigned long long)(a->wait_ms > 0 ? a->wait_ms : 2000) * 1000000ull;
   for (int r = 0; r < MAX_R; ++r) {
     c.shard[r] = reinterpret_cast<const uint4*>(a->shard_ptrs[r]);
-    c.stage[r] = reinterpret_cast<__nv_bfloat16*>(a->stage_ptrs[r]);
+    c.partial[r] = reinterpret_cast<const __nv_bfloat16*>(a->partial_ptrs[r]);
     c.flags[r] = reinterpret_cast<int*>(a->flag_ptrs[r]);
   }
   c.ready_slot = a->ready_slot; c.done_slot = a->done_slot;
@@ -684,9 +756,16 @@ XB_API int xb_gemm_fused(XbFusedArgs* a, void* stream) {
     if (!c.counters) return -6;
     p.group_m = 1;
     c.rows_per = (int)a->rows_per_rank;
-    c.mblocks_per_rank = c.rows_per / 512;
-    c.units_per_mblock = 32 * p.num_n_blocks;      // 16 warps x 2 column halves per tile
+    // an owner's rows are announced in up to MAX_SUB pieces of at least 512 rows, so that the owner
+    // starts pulling long before its whole block is complete
+    c.num_sub = 1;
+    for (int n = MAX_SUB; n > 1; n >>= 1)
+      if (c.rows_per % (n * 32) == 0 && c.rows_per / n >= 512) { c.num_sub = n; break; }
+    c.sub_rows = c.rows_per / c.num_sub;
+    c.units_per_sub = (c.sub_rows / 32) * 2 * p.num_n_blocks;     // warps x column halves of every tile
     c.rot_m = (int)(((a->rank + 1) * a->rows_per_rank) / 512) % p.num_m_blocks;
+    c.pulled = reinterpret_cast<__nv_bfloat16*>(a->pulled);
+    c.ready = reinterpret_cast<unsigned long long*>(a->ready_counters);
     c.out = reinterpret_cast<__nv_bfloat16*>(a->out);
     c.ldo = a->ldo;
     c.residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
@@ -706,19 +785,17 @@ XB_API int xb_gemm_fused(XbFusedArgs* a, void* stream) {
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-// Sum of the staged partial rows of `rank` (the last phase of the scatter path as a kernel of its
-// own; used when the partials were produced by separate launches on one device).
-XB_API int xb_rs_reduce(const void* stage, int nranks, int rank, int rows_per, int N, void* out,
+// out = sum over r of block_ptrs[r] (contiguous [rows_per][N] bf16 blocks) in fp32 (+ residual): the
+// reduction phase of the scatter path as a kernel of its own (partials produced by separate
+// launches on one device).
+XB_API int xb_rs_reduce(const unsigned long long* block_ptrs, int nranks, int rows_per, int N, void* out,
                         long long ldo, const void* residual, void* stream) {
   using namespace xb_gemmf;
   if ((N % 8) || (ldo % 8) || nranks < 1 || nranks > MAX_R) return -1;
-  Comm c = {};
-  c.rank = rank; c.nranks = nranks;
-  c.rows_per = rows_per;
-  c.stage[rank] = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(stage));
-  c.out = reinterpret_cast<__nv_bfloat16*>(out);
-  c.ldo = ldo;
-  c.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
-  rs_reduce_kernel<<<2 * xb_sm_count(), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(c, N);
+  BlockSources src = {};
+  for (int r = 0; r < nranks; ++r) src.p[r] = reinterpret_cast<const uint4*>(block_ptrs[r]);
+  rs_reduce_kernel<<<2 * xb_sm_count(), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      src, nranks, rows_per, N, reinterpret_cast<__nv_bfloat16*>(out), ldo,
+      reinterpret_cast<const __nv_bfloat16*>(residual));
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

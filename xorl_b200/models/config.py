@@ -75,6 +75,8 @@ class ModelConfig:
         return self.num_experts > 0
 
     def layer_is_moe(self, idx: int) -> bool:
+        if self.extra.get("layers_block_type"):
+            return self.extra["layers_block_type"][idx] == "moe"
         if not self.is_moe or idx in self.mlp_only_layers or idx < self.first_k_dense_replace:
             return False
         return (idx + 1) % max(1, self.decoder_sparse_step) == 0
@@ -167,6 +169,21 @@ class ModelConfig:
                 d.setdefault("decoder_sparse_step", d["moe_layer_freq"])
             if mt == "deepseek_v3":
                 d["head_dim"] = d.get("qk_rope_head_dim", 64)      # rotary table covers the rope slice
+        if mt == "nemotron_h":
+            # one mixer per layer: Mamba2 / attention without rotary embedding / latent MoE / MLP
+            lbt = d.get("layers_block_type")
+            if lbt is None and d.get("hybrid_override_pattern"):
+                lbt = [{"M": "mamba", "*": "attention", "E": "moe", "-": "mlp"}[ch] for ch in d["hybrid_override_pattern"]]
+            lbt = list(lbt or ["mamba", "moe", "attention", "moe"])
+            d["layers_block_type"] = lbt
+            d["num_hidden_layers"] = len(lbt)
+            d["use_qk_norm"] = False
+            d["no_rope"] = True
+            d.setdefault("rms_norm_eps", d.get("layer_norm_epsilon", 1e-5))
+            d.setdefault("scoring_func", "sigmoid")
+            d.setdefault("use_correction_bias", True)
+            d.setdefault("router_aux_loss_coef", 0.0)
+            d.setdefault("initializer_range", 0.02)
         extra = {k: d.pop(k) for k in list(d) if k not in known}
         cfg = cls(**d)
         cfg.extra = extra
@@ -248,6 +265,14 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                              num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
                              norm_topk_prob=True, rope_theta=1e4, max_position_embeddings=512,
                              tie_word_embeddings=False),
+    "tiny-nemotron-h": dict(model_type="nemotron_h", vocab_size=512, hidden_size=64, intermediate_size=128,
+                            layers_block_type=["mamba", "moe", "attention", "mlp", "mamba", "moe"],
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=16, mamba_num_heads=8,
+                            mamba_head_dim=16, n_groups=2, ssm_state_size=16, conv_kernel=4, chunk_size=32,
+                            n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+                            moe_shared_expert_intermediate_size=48, moe_latent_size=32, n_group=2, topk_group=1,
+                            norm_topk_prob=True, routed_scaling_factor=2.0, layer_norm_epsilon=1e-5,
+                            max_position_embeddings=512, tie_word_embeddings=False),
     "tiny-olmo2": dict(model_type="olmo2", vocab_size=512, hidden_size=64, intermediate_size=128,
                        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, rope_theta=1e4,
                        max_position_embeddings=512, tie_word_embeddings=False),

@@ -22,6 +22,11 @@ from .layers import MLP, Attention, Linear, RMSNorm
 from .rope import RotaryEmbedding
 
 
+def _sequence_parallel() -> bool:
+    from ..parallel.state import get_parallel_state
+    return bool(get_parallel_state().tp_sequence_parallel)
+
+
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, dtype=None, device=None):
         super().__init__()
@@ -48,6 +53,14 @@ class DecoderLayer(nn.Module):
         else:
             self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, zc, dtype, device)
             self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, zc, dtype, device)
+        if _sequence_parallel():
+            # every tensor-parallel rank normalises its own tokens: replicated weights that act on
+            # token shards get partial gradients, summed over the group before the optimizer step
+            if not (isinstance(self.self_attn, Attention) and isinstance(self.mlp, MLP)):
+                raise NotImplementedError("tensor_parallel_sequence_parallel supports dense attention + MLP layers")
+            for n, p in self.named_parameters():
+                if "layernorm" in n or n == "mlp.down_proj.bias":
+                    p._xb_tp_reduce = True
 
     def forward(self, h: torch.Tensor, residual: Optional[torch.Tensor], ctx: StepContext):
         if self.post_norm:
@@ -83,7 +96,11 @@ class DecoderLM(nn.Module):
         self.layer_indices = idx
         if has_embed:
             self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)
-        self.layers = nn.ModuleDict({str(i): DecoderLayer(cfg, i, dtype, device) for i in idx})
+        layer_cls = DecoderLayer
+        if cfg.model_type == "nemotron_h":
+            from .nemotron_h import NemotronHLayer
+            layer_cls = NemotronHLayer
+        self.layers = nn.ModuleDict({str(i): layer_cls(cfg, i, dtype, device) for i in idx})
         if has_head:
             self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.zero_centered_norm, dtype, device)
             from ..parallel.tp import tp_info
@@ -103,6 +120,16 @@ class DecoderLM(nn.Module):
             raise ValueError("tied embeddings cannot be split across pipeline stages")
         self.rotary = RotaryEmbedding(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling,
                                       cfg.partial_rotary_factor, cfg.max_position_embeddings)
+        self.sp = None
+        if _sequence_parallel():
+            from ..parallel.tp_fused import sp_context
+            self.sp = sp_context()
+            if cfg.tie_word_embeddings:
+                raise NotImplementedError("tensor_parallel_sequence_parallel needs untied embeddings")
+            if has_embed:
+                self.embed_tokens.weight._xb_tp_reduce = True     # each rank embeds its own tokens
+            if has_head:
+                self.norm.weight._xb_tp_reduce = True
         self.loss_chunk_tokens = 1024
         self.cp_strategy = None
         self.ctx_defaults = {}          # copied into every StepContext.aux (ep_dispatch, ...)
@@ -148,12 +175,19 @@ class DecoderLM(nn.Module):
         return ctx
 
     def forward_embed(self, input_ids: torch.Tensor, ctx: StepContext):
-        return emb_ops.embedding(input_ids.reshape(-1), self.embed_tokens.weight), None
+        ids = input_ids.reshape(-1)
+        if self.sp is not None:
+            from ..parallel.tp_fused import local_tokens
+            ids = local_tokens(ids, self.sp)        # the residual stream holds T / tp tokens per rank
+        return emb_ops.embedding(ids, self.embed_tokens.weight), None
 
     def forward_head(self, h, residual, ctx: StepContext) -> torch.Tensor:
-        if residual is None:
-            return self.norm(h)
-        return self.norm(h, residual=residual)[0]
+        hidden = self.norm(h) if residual is None else self.norm(h, residual=residual)[0]
+        if self.sp is not None:
+            # the loss sees all tokens on every rank and returns the same gradient everywhere
+            from ..parallel.tp_fused import gather_tokens
+            hidden = gather_tokens(hidden, self.sp)
+        return hidden
 
     def head_loss(self, h, residual, labels: torch.Tensor, ctx: StepContext, grad_scale: float = 1.0,
                   return_token_losses: bool = False):
@@ -210,6 +244,14 @@ def init_parameter_(name: str, p: torch.Tensor, std: float, seed: int, index: in
         init_lora_parameter_(name, p, 0, seed)
         return
     leaf = name.rsplit(".", 1)[-1]
+    if ".mixer." in name and leaf in ("A_log", "D", "dt_bias", "norm_weight", "conv1d_bias"):
+        import zlib
+        from .mamba2 import init_mamba_parameter_
+        g = torch.Generator(device="cpu").manual_seed((seed * 1000003 + zlib.crc32(name.encode()) * 7919 + 17) % (2 ** 63 - 1))
+        tmp = torch.empty(p.shape, dtype=torch.float32)
+        init_mamba_parameter_(name, tmp, g)
+        p.copy_(tmp.to(p.device))
+        return
     if leaf == "A_log":                      # GatedDeltaNet decay rates spread over (0, 16)
         p.copy_(torch.linspace(0.5, 16.0, p.numel()).log().to(p.device))
         return

@@ -54,6 +54,15 @@ def _tp():
     return tp_info()
 
 
+def _sp():
+    """The sequence-parallel tensor-parallel context, or None (plain TP with all-reduces)."""
+    from ..parallel.state import get_parallel_state
+    if not get_parallel_state().tp_sequence_parallel:
+        return None
+    from ..parallel.tp_fused import sp_context
+    return sp_context()
+
+
 class Attention(nn.Module):
     """Fused qkv projection -> (per-head qk RMSNorm) -> RoPE -> varlen causal attention -> o_proj.
     A context-parallel strategy on ``ctx.cp`` takes over the middle part when present."""
@@ -65,6 +74,7 @@ class Attention(nn.Module):
         self.Hq, self.Hkv, self.D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         H = cfg.hidden_size
         self.tp, self.tp_rank, self.tp_group = _tp()
+        self.sp = _sp() if self.tp > 1 else None
         if self.tp > 1:
             if self.Hq % self.tp or self.Hkv % self.tp:
                 raise ValueError(f"heads ({self.Hq}, {self.Hkv}) not divisible by tensor_parallel_size {self.tp}")
@@ -90,6 +100,7 @@ class Attention(nn.Module):
                 self.q_norm.weight._xb_tp_reduce = True
                 self.k_norm.weight._xb_tp_reduce = True
         self.scale = 1.0 / math.sqrt(self.D)
+        self.no_rope = bool(cfg.extra.get("no_rope"))       # Nemotron-H attention has no positional embedding
         self.window = cfg.sliding_window if (cfg.layer_types is None or
                                             cfg.layer_types[layer_idx] == "sliding_attention") else None
         # Qwen3-Next / Qwen3.5: the attention output is multiplied by sigmoid(gate(x)) before o_proj
@@ -104,15 +115,22 @@ class Attention(nn.Module):
             mark_col(self.sinks, (self.Hq * self.tp,), (self.Hq * self.tp,))
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        if self.tp > 1:
-            from ..parallel.tp import copy_to_tp
-            x = copy_to_tp(x, self.tp_group)
-        qkv = self.qkv_proj(x)
+        if self.sp is not None:
+            # x holds this rank's tokens: the all-gather runs inside the projection's GEMM kernel
+            from ..parallel.tp_fused import gather_tokens, sp_column_linear
+            qkv = sp_column_linear(x, self.qkv_proj.weight, self.qkv_proj.bias, self.sp)
+            if self.out_gate is not None:
+                x = gather_tokens(x, self.sp)
+        else:
+            if self.tp > 1:
+                from ..parallel.tp import copy_to_tp
+                x = copy_to_tp(x, self.tp_group)
+            qkv = self.qkv_proj(x)
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         if ctx.cp is not None:
             out = ctx.cp.attention(self, qkv, ctx)
         elif (self.cfg.qk_norm_full or self.cfg.partial_rotary_factor != 1.0 or self.window
-              or self.sinks is not None):
+              or self.sinks is not None or self.no_rope):
             out = self._unfused_attention(qkv, ctx)
         else:
             wq = self.q_norm.weight if self.use_qk_norm else None
@@ -122,6 +140,9 @@ class Attention(nn.Module):
                                                   self.scale)
         if self.out_gate is not None:
             out = out * torch.sigmoid(self.out_gate(x).float()).to(out.dtype)
+        if self.sp is not None:
+            from ..parallel.tp_fused import sp_row_linear
+            return sp_row_linear(out, self.o_proj.weight, None, self.sp)
         out = self.o_proj(out)
         if self.tp > 1:
             from ..parallel.tp import reduce_from_tp
@@ -140,7 +161,9 @@ class Attention(nn.Module):
             q = self.q_norm(q.reshape(T * Hq, D)).reshape(T, Hq, D)
             k = self.k_norm(k.reshape(T * Hkv, D)).reshape(T, Hkv, D)
         rot = ctx.cos.shape[-1] * 2
-        if rot == D:
+        if self.no_rope:
+            pass
+        elif rot == D:
             q, k = attn_ops.rope_reference(q, ctx.cos, ctx.sin), attn_ops.rope_reference(k, ctx.cos, ctx.sin)
         else:
             q = torch.cat([attn_ops.rope_reference(q[..., :rot], ctx.cos, ctx.sin), q[..., rot:]], -1)
@@ -161,6 +184,7 @@ class MLP(nn.Module):
                  tensor_parallel: bool = True):
         super().__init__()
         self.tp, self.tp_rank, self.tp_group = _tp() if tensor_parallel else (1, 0, None)
+        self.sp = _sp() if self.tp > 1 else None
         full_I = intermediate
         if self.tp > 1:
             if intermediate % self.tp:
@@ -174,6 +198,12 @@ class MLP(nn.Module):
             mark_row(self.down_proj.weight, (hidden, full_I))
 
     def forward(self, x):
+        if self.sp is not None:
+            from ..parallel.tp_fused import sp_column_linear, sp_row_linear
+            h = act_ops.swiglu(sp_column_linear(x, self.gate_up_proj.weight, self.gate_up_proj.bias, self.sp))
+            y = sp_row_linear(h, self.down_proj.weight, None, self.sp)
+            # a row-parallel bias is replicated: added once, after the reduction
+            return y if self.down_proj.bias is None else y + self.down_proj.bias
         if self.tp > 1:
             from ..parallel.tp import copy_to_tp, reduce_from_tp
             x = copy_to_tp(x, self.tp_group)

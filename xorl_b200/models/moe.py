@@ -50,11 +50,16 @@ class TopKRouter(nn.Module):
 class Experts(nn.Module):
     """Stacked expert weights; ``num_local`` experts live on this rank."""
 
-    def __init__(self, cfg: ModelConfig, num_local: int, dtype=None, device=None):
+    def __init__(self, cfg: ModelConfig, num_local: int, dtype=None, device=None, hidden: Optional[int] = None,
+                 gated: bool = True, activation: Optional[str] = None):
+        """``hidden``: width the experts work on (a latent width for Nemotron-H); ``gated=False``
+        with ``activation="relu2"``: ``down(relu(up(x))^2)``, the up projection stored in
+        ``gate_up_proj [E, H, I]``."""
         super().__init__()
-        H, I = cfg.hidden_size, cfg.moe_intermediate_size
+        H, I = hidden or cfg.hidden_size, cfg.moe_intermediate_size
         self.num_local = num_local
-        self.gate_up_proj = nn.Parameter(torch.empty(num_local, H, 2 * I, dtype=dtype, device=device))
+        self.activation = activation
+        self.gate_up_proj = nn.Parameter(torch.empty(num_local, H, (2 if gated else 1) * I, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(num_local, I, H, dtype=dtype, device=device))
         self.gate_up_proj._xb_expert = True
         self.down_proj._xb_expert = True
@@ -67,9 +72,12 @@ class Experts(nn.Module):
             self.down_bias._xb_expert = True
 
     def mlp_kwargs(self):
-        if self.gate_up_bias is None and self.swiglu_limit is None:
+        if self.gate_up_bias is None and self.swiglu_limit is None and self.activation is None:
             return {}
-        return dict(gate_up_bias=self.gate_up_bias, down_bias=self.down_bias, swiglu_limit=self.swiglu_limit)
+        kw = dict(gate_up_bias=self.gate_up_bias, down_bias=self.down_bias, swiglu_limit=self.swiglu_limit)
+        if self.activation is not None:
+            kw["activation"] = self.activation
+        return kw
 
     def forward(self, x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:
         """x_sorted [M, H] grouped by local expert; tokens_per_expert int64 [num_local]."""
@@ -88,7 +96,7 @@ class MoEBlock(nn.Module):
             raise ValueError(f"num_experts {cfg.num_experts} not divisible by ep {self.ep_size}")
         self.num_local = cfg.num_experts // self.ep_size
         self.gate = TopKRouter(cfg, dtype=dtype, device=device)
-        self.experts = Experts(cfg, self.num_local, dtype=dtype, device=device)
+        self.experts = self.build_experts(cfg, dtype, device)
         self.shared_expert = None
         if cfg.shared_expert_intermediate_size:
             self.shared_expert = MLP(cfg.hidden_size, cfg.shared_expert_intermediate_size,
@@ -98,6 +106,16 @@ class MoEBlock(nn.Module):
             if (self.shared_expert is not None and cfg.extra.get("shared_expert_gate")) else None
         self.aux_coef = cfg.router_aux_loss_coef
         self.moe_ordinal = sum(cfg.layer_is_moe(i) for i in range(layer_idx))
+
+    def build_experts(self, cfg: ModelConfig, dtype, device) -> "Experts":
+        return Experts(cfg, self.num_local, dtype=dtype, device=device)
+
+    def pre_experts(self, x: torch.Tensor) -> torch.Tensor:
+        """Hook: what the routed experts see (identity; a latent projection for Nemotron-H)."""
+        return x
+
+    def post_experts(self, y: torch.Tensor) -> torch.Tensor:
+        return y
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T, H = x.shape
@@ -124,12 +142,14 @@ class MoEBlock(nn.Module):
         if ctx.aux.get("collect_expert_load", False):
             ctx.aux[("expert_load", self.layer_idx)] = torch.bincount(
                 indices.reshape(-1), minlength=self.cfg.num_experts)
+        xe = self.pre_experts(x)
         if self.ep_size > 1:
             from ..parallel import ep as ep_ops
-            out = ep_ops.ep_moe_forward(x, weights, indices, self.experts, self.cfg.num_experts, ctx)
+            out = ep_ops.ep_moe_forward(xe, weights, indices, self.experts, self.cfg.num_experts, ctx)
         else:
-            out = moe_ops.local_moe_forward(x, weights, indices, self.experts, self.cfg.num_experts,
+            out = moe_ops.local_moe_forward(xe, weights, indices, self.experts, self.cfg.num_experts,
                                             canonical=bool(ctx.aux.get("canonical_moe", False)))
+        out = self.post_experts(out)
         if self.shared_expert is not None:
             sh = self.shared_expert(x)
             if self.shared_expert_gate is not None:

@@ -3,8 +3,9 @@
 ``ag_gemm``   all-gather -> GEMM: one operand is sharded by rows over the ranks; communication warps
               of the GEMM kernel pull the peers' shards over NVLink chunk by chunk while the tensor
               cores work on the chunks that have arrived.
-``gemm_rs``   GEMM -> reduce-scatter: the epilogue stores bf16 partial tiles into the row owner's
-              staging buffer, owners are signalled block by block and sum the partials in fp32.
+``gemm_rs``   GEMM -> reduce-scatter: every rank writes its partial result into its symmetric buffer,
+              owners are signalled block by block, pull the peers' blocks of their rows over NVLink
+              while the remaining tiles are computed, and sum all partials in fp32.
 
 These are the building blocks of tensor-parallel linears with sequence-parallel activations
 (``parallel/tp_fused.py``); the reference runs the same linears as DTensor collectives around cuBLAS
@@ -35,8 +36,8 @@ class _Args(ctypes.Structure):
         ("rows_per_rank", ctypes.c_longlong),
         ("ready_counters", ctypes.c_ulonglong),
         ("ready_target", ctypes.c_ulonglong),
-        ("stage_ptrs", ctypes.c_ulonglong * 16),
-        ("out", ctypes.c_void_p), ("ldo", ctypes.c_longlong), ("residual", ctypes.c_void_p),
+        ("partial_ptrs", ctypes.c_ulonglong * 16),
+        ("pulled", ctypes.c_void_p), ("out", ctypes.c_void_p), ("ldo", ctypes.c_longlong), ("residual", ctypes.c_void_p),
         ("counters", ctypes.c_ulonglong),
         ("flag_ptrs", ctypes.c_ulonglong * 16),
         ("ready_slot", ctypes.c_int), ("done_slot", ctypes.c_int),
@@ -125,36 +126,42 @@ def ag_gemm(full: torch.Tensor, shard_ptrs: Sequence[int], rows_per_rank: int, o
     return out
 
 
-def gemm_rs(a: torch.Tensor, b: torch.Tensor, stage_ptrs: Sequence[int], rows_per_rank: int,
-            peers: Peers, *, b_mn: bool = False, epoch: int = 0, done_needed: int = 0,
-            out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+def gemm_rs(a: torch.Tensor, b: torch.Tensor, partial: torch.Tensor, partial_ptrs: Sequence[int],
+            rows_per_rank: int, peers: Peers, *, b_mn: bool = False, epoch: int = 0, done_needed: int = 0,
+            pulled: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+            residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows [rank * rows_per_rank, ...) of sum_r (A_r @ op(B_r)^T): every rank calls this with its
-    partial operands.  ``stage_ptrs[o]`` is owner o's staging buffer ``[nranks, rows_per_rank, N]``
-    (bf16).  With ``out`` the kernel waits for the peers' partial rows and writes the reduced rows of
-    this rank (plus ``residual``); without it only the staging stores are made."""
+    partial operands.  ``partial`` [M, N] (bf16, symmetric memory) receives this rank's partial
+    result and ``partial_ptrs[r]`` is rank r's buffer of the same shape.  With ``out`` (and
+    ``pulled`` [nranks, rows_per_rank, N] as local staging) the kernel pulls the peers' blocks of
+    this rank's rows and writes their fp32 sum (+ ``residual``); without it only ``partial`` is
+    produced.  Returns ``out`` or ``partial``."""
     global _launches
-    _check_bf16(a, b)
+    _check_bf16(a, b, partial)
     M, K = a.shape
     if b_mn:
         Kb, N = b.shape
     else:
         N, Kb = b.shape
-    assert K == Kb and len(stage_ptrs) == peers.nranks and rows_per_rank % 512 == 0
-    st = _shape_state(a.device, ("rs", M, N, K), 0)
+    assert K == Kb and len(partial_ptrs) == peers.nranks and rows_per_rank % 32 == 0
+    assert partial.shape == (M, N) and partial.is_contiguous() and M == rows_per_rank * peers.nranks
+    st = _shape_state(a.device, ("rs", M, N, K), 1)
     args = _Args()
-    args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), None
+    args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), partial.data_ptr()
     args.M, args.N, args.K = M, N, K
     args.lda, args.ldb, args.ldc = a.stride(0), b.stride(0), N
     args.b_mn, args.out_fp32, args.accumulate = int(b_mn), 0, 0
     args.rank, args.nranks = peers.rank, peers.nranks
     args.gather, args.scatter = 0, 1
-    for r, ptr in enumerate(stage_ptrs):
-        args.stage_ptrs[r] = ptr
+    for r, ptr in enumerate(partial_ptrs):
+        args.partial_ptrs[r] = ptr
     args.rows_per_rank = rows_per_rank
+    args.ready_counters = st["ready"].data_ptr()
+    args.ready_target = st["base"]
     if out is not None:
-        _check_bf16(out)
-        assert out.shape == (rows_per_rank, N)
-        args.out, args.ldo = out.data_ptr(), out.stride(0)
+        _check_bf16(out, pulled)
+        assert out.shape == (rows_per_rank, N) and pulled.numel() >= peers.nranks * rows_per_rank * N
+        args.out, args.ldo, args.pulled = out.data_ptr(), out.stride(0), pulled.data_ptr()
         if residual is not None:
             _check_bf16(residual)
             assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
@@ -166,16 +173,20 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, stage_ptrs: Sequence[int], rows_pe
     args.ready_slot, args.done_slot = peers.ready_slot, peers.done_slot
     args.epoch, args.done_needed, args.wait_ms = epoch, done_needed, peers.wait_ms
     _lib.check(_lib.cuda_lib().xb_gemm_fused(ctypes.byref(args), _lib.stream_ptr()), "xb_gemm_fused(scatter)")
+    if out is not None:
+        st["base"] += args.ctas_out
     _launches += 1
-    return out
+    return out if out is not None else partial
 
 
-def rs_reduce(stage: torch.Tensor, rank: int, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out = sum over the first dim of ``stage [nranks, rows, N]`` in fp32 (+ residual): the reduction
-    phase of ``gemm_rs`` as a kernel of its own."""
-    nranks, rows, N = stage.shape
-    _check_bf16(stage, out)
-    _lib.check(_lib.cuda_lib().xb_rs_reduce(stage.data_ptr(), nranks, rank, rows, N, out.data_ptr(), out.stride(0),
+def rs_reduce(blocks: Sequence[torch.Tensor], out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = sum of ``blocks`` (contiguous [rows, N] bf16 tensors, one per rank) in fp32, in order
+    (+ residual): the reduction phase of ``gemm_rs`` as a kernel of its own."""
+    rows, N = blocks[0].shape
+    _check_bf16(out, *blocks)
+    assert all(b.is_contiguous() and b.shape == (rows, N) for b in blocks)
+    ptrs = (ctypes.c_ulonglong * len(blocks))(*[b.data_ptr() for b in blocks])
+    _lib.check(_lib.cuda_lib().xb_rs_reduce(ptrs, len(blocks), rows, N, out.data_ptr(), out.stride(0),
                                             residual.data_ptr() if residual is not None else None,
                                             _lib.stream_ptr()), "xb_rs_reduce")
     return out

@@ -269,10 +269,12 @@ def clamped_swiglu(h: torch.Tensor, limit: float, alpha: float = 1.702) -> torch
 def expert_mlp_aligned(x_buf: torch.Tensor, seg: torch.Tensor, gate_up: torch.Tensor,
                        down: torch.Tensor, gate_up_bias: Optional[torch.Tensor] = None,
                        down_bias: Optional[torch.Tensor] = None,
-                       swiglu_limit: Optional[float] = None) -> torch.Tensor:
+                       swiglu_limit: Optional[float] = None, activation: Optional[str] = None) -> torch.Tensor:
     """SwiGLU expert MLP over a segment-aligned token buffer (optional per-expert biases and the
-    clamped activation of gpt-oss)."""
+    clamped activation of gpt-oss); ``activation="relu2"``: non-gated ``relu(up(x))^2`` experts."""
     h = grouped_linear(x_buf, gate_up, seg)
+    if activation == "relu2":
+        return grouped_linear(torch.relu(h).square(), down, seg)
     if gate_up_bias is None and swiglu_limit is None:
         return grouped_linear(swiglu(h), down, seg)
     eid = _rows_to_expert(seg, h.shape[0])

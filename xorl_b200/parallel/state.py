@@ -58,6 +58,7 @@ class ParallelState:
     lm_head_tp_size: int = 1
     dp_mode: str = "fsdp2"
     cp_fsdp_mode: str = "all"
+    tp_sequence_parallel: bool = False   # residual stream sharded by tokens between TP regions
 
     # ---- sizes ------------------------------------------------------------------------------
     def size(self, name: str) -> int:
@@ -154,7 +155,7 @@ def init_parallel_state(*, dp_size: int = -1, dp_replicate_size: int = 1, dp_sha
                         tp_size: int = 1, ep_size: int = 1, pp_size: int = 1, ulysses_size: int = 1,
                         ringattn_size: int = 1, lm_head_tp_size: int = 1, dp_mode: str = "fsdp2",
                         cp_fsdp_mode: str = "all", device_type: Optional[str] = None,
-                        ep_intranode: bool = True) -> ParallelState:
+                        ep_intranode: bool = True, tp_sequence_parallel: bool = False) -> ParallelState:
     """Builds every process group.  ``torch.distributed`` must be initialised when world > 1."""
     global _STATE
     world = dist.get_world_size() if dist.is_initialized() else 1
@@ -181,7 +182,8 @@ def init_parallel_state(*, dp_size: int = -1, dp_replicate_size: int = 1, dp_sha
     coords = {n: my[i] for i, n in enumerate(DIM_NAMES)}
     st = ParallelState(world_size=world, rank=rank, device_type=device_type, sizes=sizes,
                        coords=coords, ep_size=ep_size, lm_head_tp_size=lm_head_tp_size,
-                       dp_mode=dp_mode, cp_fsdp_mode=cp_fsdp_mode)
+                       dp_mode=dp_mode, cp_fsdp_mode=cp_fsdp_mode,
+                       tp_sequence_parallel=bool(tp_sequence_parallel and tp_size > 1))
     backend = None  # default backend of the world group
 
     def family(dims: Sequence[str]) -> List[List[int]]:

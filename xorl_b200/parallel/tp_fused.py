@@ -13,9 +13,10 @@ op                     forward                         backward (input gradient)
 
 On CUDA each of the four is ONE kernel (``csrc/gemm_fused.cu`` through ``ops/fused_gemm.py``): the
 shards and the staging buffers live in symmetric memory mapped into every peer of the group, the
-all-gather runs in communication warps of the GEMM kernel and the reduce-scatter in its epilogue.
+all-gather runs in communication warps of the GEMM kernel, and so does the pull of the peers' partial
+result blocks of the reduce-scatter, signalled block by block from the epilogue.
 On CPU (gloo), for fp32, or when a shape does not fit the kernel (rows per rank not a multiple of
-512 for the reduce-scatter) the same functions run the collective through ``torch.distributed``
+32 for the reduce-scatter) the same functions run the collective through ``torch.distributed``
 followed / preceded by a plain GEMM, so the model code is identical everywhere.
 
 The reference runs tensor parallelism through DTensor ``ColwiseParallel`` / ``RowwiseParallel``
@@ -35,9 +36,10 @@ import torch.distributed as dist
 from ..ops import _lib
 from ..ops import gemm as gemm_ops
 
-# flag-area layout (int32 slots)
-_G_READY, _G_DONE, _S_READY, _S_DONE = 0, 16, 32, 48
-_FLAG_INTS = 256
+# flag-area layout (int32 slots): 16 per kind, except the reduce-scatter ready flags, which are
+# [rank][sub-block] (16 x 16)
+_G_READY, _G_DONE, _S_DONE, _S_READY = 0, 16, 32, 256
+_FLAG_INTS = 1024
 _RING = 2
 
 
@@ -48,6 +50,7 @@ class SequenceParallelTP:
         self.group, self.rank, self.world = group, rank, world
         self.fused = os.environ.get("XORL_B200_TP_FUSED", "1") == "1"
         self._heap = None
+        self._pulled = None                       # local staging of the peers' partial blocks
         self._cap: Tuple[int, int] = (0, 0)       # (rows per rank, features) the buffers can hold
         self.g_epoch = 0
         self.s_epoch = 0
@@ -119,16 +122,20 @@ class SequenceParallelTP:
         N = w.shape[1] if b_mn else w.shape[0]
         assert T % self.world == 0, f"{T} tokens not divisible by tensor-parallel size {self.world}"
         rows_per = T // self.world
-        if self._fused_ok(a, w) and rows_per % 512 == 0 and N % 8 == 0 and a.shape[1] % 8 == 0:
+        if self._fused_ok(a, w) and rows_per % 32 == 0 and N % 8 == 0 and a.shape[1] % 8 == 0:
             from ..ops import fused_gemm
             self._ensure(rows_per, N, a.device)
             self.s_epoch += 1
             e = self.s_epoch
             off = self._stage_off[e % _RING]
+            partial = self._heap[off:off + T * N * 2].view(torch.bfloat16).view(T, N)
+            if self._pulled is None or self._pulled.numel() < T * N:
+                self._pulled = torch.empty(T * N, device=a.device, dtype=torch.bfloat16)
             out = torch.empty(rows_per, N, device=a.device, dtype=torch.bfloat16)
-            fused_gemm.gemm_rs(a.contiguous(), w, [b + off for b in self._base], rows_per,
+            fused_gemm.gemm_rs(a.contiguous(), w, partial, [b + off for b in self._base], rows_per,
                                self._peers(_S_READY, _S_DONE), b_mn=b_mn, epoch=e,
-                               done_needed=max(e - _RING, 0), out=out, residual=residual)
+                               done_needed=max(e - _RING, 0), pulled=self._pulled, out=out,
+                               residual=residual)
             self.fused_calls += 1
             return out
         self.fallback_calls += 1

@@ -461,7 +461,9 @@ class Zero3Engine:
                 g.collect_grads()
             accumulate = g.grad_ready
             gf = g.grad_full
-            if self.ps.tp_size > 1 and self.ps.group("tp") is not None:
+            if self.ps.tp_size > 1 and self.ps.group("tp") is not None and g.world > 1:
+                # (with a shard group of one the gradients accumulate in place over micro-batches:
+                # their sum over the tensor-parallel group is taken once, in finish_grad_sync)
                 for (_, p), v in zip(g.named_params, g.param_views(gf)):
                     if getattr(p, "_xb_tp_reduce", False):
                         dist.all_reduce(v, group=self.ps.group("tp"))
@@ -508,6 +510,10 @@ class Zero3Engine:
                 g.reduce_event = None
                 if g.grad_shard is None:
                     continue
+                if g.world == 1 and self.ps.tp_size > 1 and self.ps.group("tp") is not None:
+                    for i, a, b in g.param_segments_in_shard():
+                        if getattr(g.named_params[i][1], "_xb_tp_reduce", False):
+                            dist.all_reduce(g.grad_shard[a:b], group=self.ps.group("tp"))
                 if g.replicate_pg is not None and g.replicate_world > 1:
                     dist.all_reduce(g.grad_shard, group=g.replicate_pg)
                 if self.sp_sync_pg is not None and not getattr(g, "is_expert", False):

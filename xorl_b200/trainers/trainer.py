@@ -78,7 +78,7 @@ class Trainer:
             pp_size=t.pipeline_parallel_size, ulysses_size=t.ulysses_parallel_size,
             ringattn_size=t.ringattn_parallel_size, lm_head_tp_size=t.lm_head_tensor_parallel_size,
             dp_mode=t.data_parallel_mode, cp_fsdp_mode=t.cp_fsdp_mode, device_type=self.device.type,
-            ep_intranode=t.ep_intranode)
+            ep_intranode=t.ep_intranode, tp_sequence_parallel=t.tensor_parallel_sequence_parallel)
         if self.ps.rank == 0:
             save_args(self.args, t.output_dir)
         self.compute_dtype = torch.bfloat16 if (t.enable_mixed_precision and self.device.type == "cuda") \
@@ -345,6 +345,10 @@ class Trainer:
             self.profiler.stop()
         result = {"loss_history": self.loss_history, "global_step": self.global_step,
                   "metrics": self.metrics_history[-1] if self.metrics_history else {}}
+        if self.ps.tp_sequence_parallel:
+            from ..parallel.tp_fused import sp_context
+            sp = sp_context()
+            result["tp_collective_gemms"] = {"fused": sp.fused_calls, "unfused": sp.fallback_calls}
         if t.save_hf_weights and self.global_step > 0 and t.save_steps >= 0 and \
                 os.environ.get("XORL_SKIP_FINAL_EXPORT", "0") != "1":
             out_dir = os.path.join(t.output_dir, f"global_step_{self.global_step}", "hf_ckpt")

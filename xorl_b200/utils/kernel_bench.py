@@ -120,6 +120,30 @@ def bench_attn(a) -> Dict:
     return r
 
 
+def bench_fused_gemm(a) -> Dict:
+    """The collective GEMM kernel on one device (``--ranks`` local buffers stand in for the peers):
+    what the gather warps, the rotated raster and the completion counters cost next to the plain
+    CTA-pair GEMM, without any NVLink traffic."""
+    from ..ops.fused_gemm import Peers, ag_gemm, gemm_rs
+    from ..ops.gemm import gemm
+    R = a.ranks
+    A = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    B = torch.randn(a.n, a.k, device="cuda").bfloat16()
+    C = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    shards = [A[r * (a.m // R):(r + 1) * (a.m // R)].clone() for r in range(R)]
+    full = torch.empty_like(A)
+    ptrs = [s_.data_ptr() for s_ in shards]
+    peers = Peers(R // 2, R)
+    partial = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    ms_plain = _time(lambda: gemm(A, B, out=C), a.warmup, a.iters, a.flush)
+    ms_ag = _time(lambda: ag_gemm(full, ptrs, a.m // R, B, peers, gathered="a", out=C), a.warmup, a.iters, a.flush)
+    ms_rs = _time(lambda: gemm_rs(A, B, partial, [partial.data_ptr()] * R, a.m // R, peers), a.warmup, a.iters, a.flush)
+    flops = 2.0 * a.m * a.n * a.k
+    return {"kernel": "gemm_fused_one_device", "m": a.m, "n": a.n, "k": a.k, "ranks": R, "plain_ms": ms_plain,
+            "gather_ms": ms_ag, "partial_ms": ms_rs, "plain_tflops": flops / ms_plain / 1e9,
+            "gather_tflops": flops / ms_ag / 1e9, "partial_tflops": flops / ms_rs / 1e9}
+
+
 def bench_adamw(a) -> Dict:
     from ..ops import optim as optim_ops
     n = a.numel
@@ -143,7 +167,7 @@ def bench_rmsnorm(a) -> Dict:
 
 
 BENCHES = {"gemm": bench_gemm, "fp8_gemm": bench_fp8_gemm, "attn": bench_attn, "adamw": bench_adamw,
-           "rmsnorm": bench_rmsnorm}
+           "rmsnorm": bench_rmsnorm, "fused_gemm": bench_fused_gemm}
 
 
 def main(argv=None) -> None:
@@ -165,6 +189,7 @@ def main(argv=None) -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-lib", action="store_true")
+    ap.add_argument("--ranks", type=int, default=2)
     a = ap.parse_args(argv)
     a.flush = torch.zeros(256 << 20, device="cuda", dtype=torch.uint8)
     print(json.dumps(BENCHES[a.kernel](a)))
