@@ -22,7 +22,8 @@ def _state():
 
 
 @pytest.mark.parametrize("name", ["tiny-qwen3", "tiny-qwen2", "tiny-olmo2", "tiny-qwen3-moe", "tiny-gpt-oss",
-                                  "tiny-deepseek-v3", "tiny-glm4-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe"])
+                                  "tiny-deepseek-v3", "tiny-glm4-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe",
+                                  "tiny-nemotron-h", "tiny-minimax-m3"])
 def test_family_trains(name):
     from xorl_b200.models import build_model
     from xorl_b200.models.config import preset
@@ -162,7 +163,8 @@ def test_mla_matches_explicit_formula():
     torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-4)
 
 
-@pytest.mark.parametrize("name", ["tiny-gpt-oss", "tiny-deepseek-v3", "tiny-qwen3-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe", "tiny-nemotron-h"])
+@pytest.mark.parametrize("name", ["tiny-gpt-oss", "tiny-deepseek-v3", "tiny-qwen3-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe", "tiny-nemotron-h",
+                                  "tiny-minimax-m3"])
 def test_family_hf_roundtrip(name, tmp_path):
     """Export to HF-named safetensors and load back into a fresh engine: identical weights."""
     from xorl_b200.checkpoint.hf_io import load_hf_weights, save_hf_weights
@@ -191,6 +193,13 @@ def test_family_hf_roundtrip(name, tmp_path):
         assert "model.layers.0.linear_attn.in_proj_qkv.weight" in names and "model.layers.0.linear_attn.conv1d.weight" in names
         assert "model.layers.0.linear_attn.in_proj_z.weight" in names and "model.layers.0.linear_attn.A_log" in names
         assert "model.layers.3.self_attn.q_proj.weight" in names and not any("out_gate" in n or "qkv_proj" in n for n in names)
+    if name == "tiny-minimax-m3":
+        for n in ("model.layers.0.mlp.gate_proj.weight", "model.layers.1.block_sparse_moe.experts.3.w1.weight",
+                  "model.layers.1.block_sparse_moe.experts.3.w2.weight", "model.layers.1.block_sparse_moe.gate.weight",
+                  "model.layers.1.block_sparse_moe.e_score_correction_bias",
+                  "model.layers.1.block_sparse_moe.shared_experts.up_proj.weight",
+                  "model.layers.1.self_attn.index_q_proj.weight", "model.layers.1.self_attn.q_norm.weight"):
+            assert n in names, n
     if name == "tiny-nemotron-h":
         for n in ("backbone.embeddings.weight", "backbone.norm_f.weight", "backbone.layers.0.mixer.conv1d.weight",
                   "backbone.layers.0.mixer.A_log", "backbone.layers.0.mixer.norm.weight",
@@ -207,6 +216,49 @@ def test_family_hf_roundtrip(name, tmp_path):
     wa = dict(a.iter_full_tensors("master"))
     for k, v in b.iter_full_tensors("master"):
         assert torch.equal(v, wa[k]), k
+
+
+def test_minimax_sparse_attention_selects_blocks():
+    """Block-sparse inference attention: with enough blocks kept it equals dense causal attention;
+    with few it attends only inside the kept blocks (forced first block, own block, best-scoring)."""
+    from xorl_b200.models.minimax_m3 import msa_attention
+    from xorl_b200.ops.attention import attention_reference
+    torch.manual_seed(0)
+    T, Hq, Hkv, D, Hi, Di, bs = 70, 4, 2, 8, 2, 8, 8
+    q, k, v = torch.randn(T, Hq, D), torch.randn(T, Hkv, D), torch.randn(T, Hkv, D)
+    iq, ik = torch.randn(T, Hi, Di), torch.randn(T, Hi, Di)
+    cu = torch.tensor([0, 30, 70], dtype=torch.int32)
+    dense = attention_reference(q, k, v, cu, True, D ** -0.5)
+    full = msa_attention(q, k, v, iq, ik, cu, D ** -0.5, block_size=bs, topk_blocks=16)
+    assert (full - dense).abs().max() < 1e-5
+    # one kept block = the query's own block (forced): equals attention restricted to that block
+    own = msa_attention(q, k, v, iq, ik, cu, D ** -0.5, block_size=bs, topk_blocks=1, force_end_blocks=1)
+    t = 29                       # last token of the first document: block 3 = keys 24..29
+    kh = k[24:30].repeat_interleave(2, 1)
+    vh = v[24:30].repeat_interleave(2, 1)
+    att = (torch.einsum("hd,khd->hk", q[t], kh) * D ** -0.5).softmax(-1)
+    assert (own[t] - torch.einsum("hk,khd->hd", att, vh)).abs().max() < 1e-5
+    sparse = msa_attention(q, k, v, iq, ik, cu, D ** -0.5, block_size=bs, topk_blocks=2, force_begin_blocks=1)
+    assert torch.isfinite(sparse).all() and (sparse - dense).abs().max() > 1e-3
+
+
+def test_minimax_model_sparse_inference_path():
+    from xorl_b200.models import preset
+    from xorl_b200.models.decoder import DecoderLM
+    torch.manual_seed(0)
+    cfg = preset("tiny-minimax-m3")
+    m = DecoderLM(cfg)
+    m.init_weights(0)
+    assert m.layers["1"].self_attn.is_sparse_layer and not m.layers["0"].self_attn.is_sparse_layer
+    assert m.layers["1"].self_attn.q_norm.weight.shape == (cfg.num_attention_heads * cfg.head_dim,)
+    ids = torch.randint(0, cfg.vocab_size, (64,))
+    cu = torch.tensor([0, 64], dtype=torch.int32)
+    with torch.no_grad():
+        dense = m.logits(ids, cu_seqlens=cu)
+        m.ctx_defaults["minimax_msa"] = True
+        sparse = m.logits(ids, cu_seqlens=cu)
+    assert torch.isfinite(sparse).all() and (sparse - dense).abs().max() > 1e-6
+    assert (sparse[:16] - dense[:16]).abs().max() < 1e-4      # two blocks of 8 are always kept: same as dense
 
 
 def test_mamba2_chunked_scan_matches_recurrence():

@@ -309,8 +309,62 @@ class NemotronHHandler(CheckpointHandler):
         return parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
 
 
+class MiniMaxM3Handler(CheckpointHandler):
+    """MiniMax-M3 text weights: on disk the MoE block is ``block_sparse_moe`` with per-expert
+    ``w1`` (gate), ``w3`` (up), ``w2`` (down), the selection bias directly under the block, and
+    ``shared_experts`` (plural); dense layers keep ``mlp.gate_proj / up_proj / down_proj``
+    (src/xorl/models/transformers/minimax_m3/checkpoint_handler.py).  Keys of a multimodal checkpoint
+    carry a ``language_model.`` prefix, which ``normalize_key`` strips before lookup."""
+
+    @staticmethod
+    def normalize_key(key: str) -> str:
+        for pre, new in (("model.language_model.model.", "model."), ("language_model.model.", "model."),
+                         ("model.language_model.lm_head.", "lm_head."), ("language_model.lm_head.", "lm_head."),
+                         ("model.language_model.", ""), ("language_model.", "")):
+            if key.startswith(pre):
+                return new + key[len(pre):]
+        return key
+
+    def _is_moe(self, fq: str) -> bool:
+        m = re.search(r"layers\.(\d+)\.", fq)
+        return bool(m) and self.cfg.layer_is_moe(int(m.group(1)))
+
+    def _disk(self, fq: str) -> str:
+        if ".mlp." in fq and self._is_moe(fq):
+            fq = fq.replace(".mlp.", ".block_sparse_moe.")
+            fq = fq.replace(".block_sparse_moe.gate.e_score_correction_bias", ".block_sparse_moe.e_score_correction_bias")
+            fq = fq.replace(".block_sparse_moe.shared_expert.", ".block_sparse_moe.shared_experts.")
+        return fq
+
+    def to_hf(self, name, t):
+        fq = to_checkpoint_fqn(name)
+        if ".mlp.experts.gate_up_proj" in fq:
+            base = self._disk(fq[: fq.index(".experts.")] + ".")[:-1]
+            for e in range(t.shape[0]):
+                g, u = t[e].split(t.shape[-1] // 2, dim=-1)
+                yield f"{base}.experts.{e}.w1.weight", g.t().contiguous()
+                yield f"{base}.experts.{e}.w3.weight", u.t().contiguous()
+        elif ".mlp.experts.down_proj" in fq:
+            base = self._disk(fq[: fq.index(".experts.")] + ".")[:-1]
+            for e in range(t.shape[0]):
+                yield f"{base}.experts.{e}.w2.weight", t[e].t().contiguous()
+        else:
+            for n, part in super().to_hf(name, t):
+                yield self._disk(n), part
+
+    def hf_sources(self, name):
+        fq = to_checkpoint_fqn(name)
+        if ".mlp.experts.gate_up_proj" in fq or ".mlp.experts.down_proj" in fq:
+            base = self._disk(fq[: fq.index(".experts.")] + ".")[:-1]
+            ws = ("w1", "w3") if "gate_up_proj" in fq else ("w2",)
+            return [f"{base}.experts.{e}.{w}.weight" for e in range(self.cfg.num_experts) for w in ws]
+        return [self._disk(n) for n in super().hf_sources(name)]
+
+
 def get_checkpoint_handler(cfg) -> CheckpointHandler:
     mt = getattr(cfg, "model_type", "")
+    if mt == "minimax_m3":
+        return MiniMaxM3Handler(cfg)
     if mt == "nemotron_h":
         return NemotronHHandler(cfg)
     if mt in ("qwen3_5", "qwen3_5_moe", "qwen3_next"):

@@ -126,8 +126,8 @@ class ModelConfig:
                 d.setdefault("rope_scaling", rp)
         mt = d.get("model_type", "qwen3")
         if "use_qk_norm" not in d:
-            d["use_qk_norm"] = mt in ("qwen3", "qwen3_moe", "olmo2", "qwen3_5", "qwen3_5_moe",
-                                      "glm4_moe") and d.get("use_qk_norm", True)
+            d["use_qk_norm"] = mt in ("qwen3", "qwen3_moe", "olmo2", "qwen3_5", "qwen3_5_moe", "glm4_moe",
+                                      "minimax_m3", "minimax_m3_vl", "xorl_minimax_m3") and d.get("use_qk_norm", True)
         if mt == "olmo2":
             d.setdefault("norm_placement", "post")
             d.setdefault("qk_norm_full", True)
@@ -169,6 +169,39 @@ class ModelConfig:
                 d.setdefault("decoder_sparse_step", d["moe_layer_freq"])
             if mt == "deepseek_v3":
                 d["head_dim"] = d.get("qk_rope_head_dim", 64)      # rotary table covers the rope slice
+        if mt in ("minimax_m3", "minimax_m3_vl", "xorl_minimax_m3"):
+            # the published config is a multimodal wrapper with the language model under text_config
+            if isinstance(d.get("text_config"), dict):
+                d = {**{k: v for k, v in d.items() if k not in ("text_config", "vision_config")}, **d["text_config"]}
+            mt = d["model_type"] = "minimax_m3"
+            d.pop("vision_config", None)
+            d.setdefault("zero_centered_norm", bool(d.pop("use_gemma_norm", True)))
+            d["use_qk_norm"] = bool(d.get("use_qk_norm", True))
+            d.setdefault("qk_norm_per_head_weights", d.get("qk_norm_type", "per_head") == "per_head")
+            hd = d.get("head_dim", 128)
+            d.setdefault("partial_rotary_factor", d.get("rotary_dim", 64) / hd)
+            d.setdefault("num_experts", d.get("num_local_experts", 128))
+            d.pop("num_local_experts", None)
+            d.setdefault("moe_intermediate_size", d.get("intermediate_size", 3072))
+            d["intermediate_size"] = d.get("dense_intermediate_size", 12288)
+            d.setdefault("shared_expert_intermediate_size",
+                         d.get("shared_intermediate_size", 3072) * d.get("n_shared_experts", 1))
+            d.setdefault("scoring_func", "sigmoid")
+            d.setdefault("use_correction_bias", bool(d.get("use_routing_bias", True)))
+            d.setdefault("routed_scaling_factor", 2.0)
+            d.setdefault("norm_topk_prob", True)
+            d.setdefault("swiglu_limit", 7.0)
+            d.setdefault("dense_swiglu_limit", d["swiglu_limit"])
+            d.setdefault("router_aux_loss_coef", 0.0)
+            n = d.get("num_hidden_layers", 60)
+            freq = d.get("moe_layer_freq")
+            if freq is not None:
+                d.setdefault("mlp_only_layers", [i for i, f in enumerate(freq) if not f])
+            sa = d.pop("sparse_attention_config", None) or {}
+            d.setdefault("sparse_attention_freq", list(sa.get("sparse_attention_freq") or [0] * n))
+            for key, default in (("sparse_block_size", 128), ("sparse_topk_blocks", 16), ("sparse_num_index_heads", 4),
+                                 ("sparse_index_dim", hd), ("sparse_init_block", 0), ("sparse_local_block", 1)):
+                d.setdefault(key, sa.get(key, default))
         if mt == "nemotron_h":
             # one mixer per layer: Mamba2 / attention without rotary embedding / latent MoE / MLP
             lbt = d.get("layers_block_type")
@@ -265,6 +298,14 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                              num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
                              norm_topk_prob=True, rope_theta=1e4, max_position_embeddings=512,
                              tie_word_embeddings=False),
+    "tiny-minimax-m3": dict(model_type="minimax_m3", vocab_size=512, hidden_size=64, num_hidden_layers=4,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=16, rotary_dim=8,
+                            dense_intermediate_size=128, intermediate_size=32, shared_intermediate_size=32,
+                            num_local_experts=8, num_experts_per_tok=2, n_shared_experts=1, moe_layer_freq=[0, 1, 1, 1],
+                            sparse_attention_config=dict(sparse_attention_freq=[0, 1, 0, 1], sparse_block_size=8,
+                                                         sparse_topk_blocks=2, sparse_num_index_heads=2,
+                                                         sparse_index_dim=16, sparse_init_block=1, sparse_local_block=1),
+                            rope_theta=1e4, max_position_embeddings=512, tie_word_embeddings=False),
     "tiny-nemotron-h": dict(model_type="nemotron_h", vocab_size=512, hidden_size=64, intermediate_size=128,
                             layers_block_type=["mamba", "moe", "attention", "mlp", "mamba", "moe"],
                             num_attention_heads=4, num_key_value_heads=2, head_dim=16, mamba_num_heads=8,

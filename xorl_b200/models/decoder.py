@@ -38,6 +38,9 @@ class DecoderLayer(nn.Module):
         elif cfg.extra.get("kv_lora_rank"):
             from .mla import MLAttention
             self.self_attn = MLAttention(cfg, layer_idx, dtype=dtype, device=device)
+        elif cfg.model_type == "minimax_m3":
+            from .minimax_m3 import MiniMaxAttention
+            self.self_attn = MiniMaxAttention(cfg, layer_idx, dtype=dtype, device=device)
         else:
             self.self_attn = Attention(cfg, layer_idx, dtype=dtype, device=device)
         if cfg.layer_is_moe(layer_idx):
@@ -45,7 +48,7 @@ class DecoderLayer(nn.Module):
             self.mlp = MoEBlock(cfg, layer_idx, dtype=dtype, device=device)
         else:
             self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.mlp_bias, dtype=dtype,
-                           device=device)
+                           device=device, swiglu_limit=cfg.extra.get("dense_swiglu_limit"))
         zc = cfg.zero_centered_norm
         if self.post_norm:
             self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, zc, dtype, device)

@@ -49,6 +49,14 @@ class Linear(nn.Module):
         return gemm_ops.linear(x, self.weight, self.bias)
 
 
+def per_head_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, zero_centered: bool) -> torch.Tensor:
+    """x [T, heads, D], weight [heads * D]: RMS over D, one weight vector per head."""
+    h = x.float()
+    h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
+    w = weight.float().view(x.shape[1], x.shape[2])
+    return (h * (1.0 + w if zero_centered else w)).to(x.dtype)
+
+
 def _tp():
     from ..parallel.tp import tp_info
     return tp_info()
@@ -93,8 +101,13 @@ class Attention(nn.Module):
         self.use_qk_norm = cfg.use_qk_norm
         if cfg.use_qk_norm:
             nd = self.D if not cfg.qk_norm_full else None
-            self.q_norm = RMSNorm(nd or self.Hq * self.D, cfg.rms_norm_eps, dtype=dtype, device=device)
-            self.k_norm = RMSNorm(nd or self.Hkv * self.D, cfg.rms_norm_eps, dtype=dtype, device=device)
+            # MiniMax-M3: every head has its own norm weights (statistics still per head)
+            self.qk_norm_per_head = bool(cfg.extra.get("qk_norm_per_head_weights"))
+            if self.qk_norm_per_head:
+                nd = None
+            zc = cfg.zero_centered_norm and self.qk_norm_per_head
+            self.q_norm = RMSNorm(nd or self.Hq * self.D, cfg.rms_norm_eps, zc, dtype=dtype, device=device)
+            self.k_norm = RMSNorm(nd or self.Hkv * self.D, cfg.rms_norm_eps, zc, dtype=dtype, device=device)
             if self.tp > 1 and not cfg.qk_norm_full:
                 # every TP rank sees only its own heads: gradients are summed over the TP group
                 self.q_norm.weight._xb_tp_reduce = True
@@ -130,7 +143,7 @@ class Attention(nn.Module):
         if ctx.cp is not None:
             out = ctx.cp.attention(self, qkv, ctx)
         elif (self.cfg.qk_norm_full or self.cfg.partial_rotary_factor != 1.0 or self.window
-              or self.sinks is not None or self.no_rope):
+              or self.sinks is not None or self.no_rope or getattr(self, "qk_norm_per_head", False)):
             out = self._unfused_attention(qkv, ctx)
         else:
             wq = self.q_norm.weight if self.use_qk_norm else None
@@ -151,13 +164,28 @@ class Attention(nn.Module):
 
     def _unfused_attention(self, qkv, ctx):
         """General path (whole-projection qk-norm, partial rotary): separate ops."""
+        q, k, v = self._qkv_heads(qkv, ctx)
+        T, Hq, D = q.shape
+        if self.window or self.sinks is not None:
+            # sliding windows and sink logits are not in the tcgen05 kernel: masked-softmax path
+            out = attn_ops.attention_reference(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale,
+                                               window=self.window, sinks=self.sinks)
+        else:
+            out = attn_ops.flash_attn_varlen(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale)
+        return out.reshape(T, Hq * D)
+
+    def _qkv_heads(self, qkv, ctx):
+        """Fused projection output -> normalised, rotated q [T, Hq, D], k, v [T, Hkv, D]."""
         T = qkv.shape[0]
         Hq, Hkv, D = self.Hq, self.Hkv, self.D
         q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
         if self.use_qk_norm and self.cfg.qk_norm_full:
             q, k = self.q_norm(q), self.k_norm(k)
         q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
-        if self.use_qk_norm and not self.cfg.qk_norm_full:
+        if self.use_qk_norm and getattr(self, "qk_norm_per_head", False):
+            q = per_head_rmsnorm(q, self.q_norm.weight, self.q_norm.eps, self.q_norm.zero_centered)
+            k = per_head_rmsnorm(k, self.k_norm.weight, self.k_norm.eps, self.k_norm.zero_centered)
+        elif self.use_qk_norm and not self.cfg.qk_norm_full:
             q = self.q_norm(q.reshape(T * Hq, D)).reshape(T, Hq, D)
             k = self.k_norm(k.reshape(T * Hkv, D)).reshape(T, Hkv, D)
         rot = ctx.cos.shape[-1] * 2
@@ -168,21 +196,18 @@ class Attention(nn.Module):
         else:
             q = torch.cat([attn_ops.rope_reference(q[..., :rot], ctx.cos, ctx.sin), q[..., rot:]], -1)
             k = torch.cat([attn_ops.rope_reference(k[..., :rot], ctx.cos, ctx.sin), k[..., rot:]], -1)
-        if self.window or self.sinks is not None:
-            # sliding windows and sink logits are not in the tcgen05 kernel: masked-softmax path
-            out = attn_ops.attention_reference(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale,
-                                               window=self.window, sinks=self.sinks)
-        else:
-            out = attn_ops.flash_attn_varlen(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale)
-        return out.reshape(T, Hq * D)
+        return q, k, v
 
 
 class MLP(nn.Module):
     """SwiGLU feed-forward with a fused gate_up projection ``[2I, H]`` (gate rows first)."""
 
     def __init__(self, hidden: int, intermediate: int, bias: bool = False, dtype=None, device=None,
-                 tensor_parallel: bool = True):
+                 tensor_parallel: bool = True, swiglu_limit: Optional[float] = None):
+        """``swiglu_limit``: clamped activation ``(up.clamp(+-l) + 1) * g * sigmoid(1.702 g)`` with
+        ``g = gate.clamp(max=l)`` (MiniMax-M3) instead of SwiGLU."""
         super().__init__()
+        self.swiglu_limit = swiglu_limit
         self.tp, self.tp_rank, self.tp_group = _tp() if tensor_parallel else (1, 0, None)
         self.sp = _sp() if self.tp > 1 else None
         full_I = intermediate
@@ -197,15 +222,21 @@ class MLP(nn.Module):
             mark_col(self.gate_up_proj.weight, (2 * full_I, hidden), (full_I, full_I))
             mark_row(self.down_proj.weight, (hidden, full_I))
 
+    def _act(self, h):
+        if self.swiglu_limit is not None:
+            from ..ops.moe import clamped_swiglu
+            return clamped_swiglu(h, self.swiglu_limit)
+        return act_ops.swiglu(h)
+
     def forward(self, x):
         if self.sp is not None:
             from ..parallel.tp_fused import sp_column_linear, sp_row_linear
-            h = act_ops.swiglu(sp_column_linear(x, self.gate_up_proj.weight, self.gate_up_proj.bias, self.sp))
+            h = self._act(sp_column_linear(x, self.gate_up_proj.weight, self.gate_up_proj.bias, self.sp))
             y = sp_row_linear(h, self.down_proj.weight, None, self.sp)
             # a row-parallel bias is replicated: added once, after the reduction
             return y if self.down_proj.bias is None else y + self.down_proj.bias
         if self.tp > 1:
             from ..parallel.tp import copy_to_tp, reduce_from_tp
             x = copy_to_tp(x, self.tp_group)
-            return reduce_from_tp(self.down_proj(act_ops.swiglu(self.gate_up_proj(x))), self.tp_group)
-        return self.down_proj(act_ops.swiglu(self.gate_up_proj(x)))
+            return reduce_from_tp(self.down_proj(self._act(self.gate_up_proj(x))), self.tp_group)
+        return self.down_proj(self._act(self.gate_up_proj(x)))

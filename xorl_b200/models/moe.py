@@ -100,7 +100,7 @@ class MoEBlock(nn.Module):
         self.shared_expert = None
         if cfg.shared_expert_intermediate_size:
             self.shared_expert = MLP(cfg.hidden_size, cfg.shared_expert_intermediate_size,
-                                     dtype=dtype, device=device)
+                                     dtype=dtype, device=device, swiglu_limit=cfg.extra.get("dense_swiglu_limit"))
         # Qwen3-Next / Qwen3.5 MoE: the shared expert is scaled by sigmoid(w_g . x) per token
         self.shared_expert_gate = Linear(cfg.hidden_size, 1, dtype=dtype, device=device) \
             if (self.shared_expert is not None and cfg.extra.get("shared_expert_gate")) else None

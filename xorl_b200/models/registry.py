@@ -23,7 +23,8 @@ for _n in ("qwen3", "Qwen3ForCausalLM", "qwen2", "Qwen2ForCausalLM", "llama", "L
            "olmo2", "Olmo2ForCausalLM", "qwen3_moe", "Qwen3MoeForCausalLM", "glm4_moe",
            "Glm4MoeForCausalLM", "gpt_oss", "GptOssForCausalLM", "deepseek_v3",
            "DeepseekV3ForCausalLM", "qwen3_5", "qwen3_5_moe", "qwen3_next", "Qwen3NextForCausalLM",
-           "Qwen3_5ForCausalLM", "Qwen3_5MoeForCausalLM", "nemotron_h", "NemotronHForCausalLM"):
+           "Qwen3_5ForCausalLM", "Qwen3_5MoeForCausalLM", "nemotron_h", "NemotronHForCausalLM",
+           "minimax_m3", "MiniMaxM3SparseForCausalLM", "MiniMaxM3SparseForConditionalGeneration"):
     MODEL_REGISTRY[_n] = _decoder
 
 # Families of the reference whose token mixers are not built here (linear-attention / state-space
@@ -31,7 +32,7 @@ for _n in ("qwen3", "Qwen3ForCausalLM", "qwen2", "Qwen2ForCausalLM", "llama", "L
 # training a different architecture under the same name.
 UNSUPPORTED = {
     "glm5": "MLA with the DSA sparse indexer",
-    "deepseek_v4": "compressed sparse attention and hyper-connections", "minimax_m3": "its attention variant",
+    "deepseek_v4": "compressed sparse attention and hyper-connections",
 }
 
 
