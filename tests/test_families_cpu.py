@@ -23,7 +23,7 @@ def _state():
 
 @pytest.mark.parametrize("name", ["tiny-qwen3", "tiny-qwen2", "tiny-olmo2", "tiny-qwen3-moe", "tiny-gpt-oss",
                                   "tiny-deepseek-v3", "tiny-glm4-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe",
-                                  "tiny-nemotron-h", "tiny-minimax-m3"])
+                                  "tiny-nemotron-h", "tiny-minimax-m3", "tiny-glm5"])
 def test_family_trains(name):
     from xorl_b200.models import build_model
     from xorl_b200.models.config import preset
@@ -164,7 +164,7 @@ def test_mla_matches_explicit_formula():
 
 
 @pytest.mark.parametrize("name", ["tiny-gpt-oss", "tiny-deepseek-v3", "tiny-qwen3-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe", "tiny-nemotron-h",
-                                  "tiny-minimax-m3"])
+                                  "tiny-minimax-m3", "tiny-glm5"])
 def test_family_hf_roundtrip(name, tmp_path):
     """Export to HF-named safetensors and load back into a fresh engine: identical weights."""
     from xorl_b200.checkpoint.hf_io import load_hf_weights, save_hf_weights
@@ -193,6 +193,12 @@ def test_family_hf_roundtrip(name, tmp_path):
         assert "model.layers.0.linear_attn.in_proj_qkv.weight" in names and "model.layers.0.linear_attn.conv1d.weight" in names
         assert "model.layers.0.linear_attn.in_proj_z.weight" in names and "model.layers.0.linear_attn.A_log" in names
         assert "model.layers.3.self_attn.q_proj.weight" in names and not any("out_gate" in n or "qkv_proj" in n for n in names)
+    if name == "tiny-glm5":
+        for n in ("model.layers.0.self_attn.indexer.k_norm.bias", "model.layers.0.self_attn.indexer.wq_b.weight",
+                  "model.layers.2.self_attn.indexer.weights_proj.weight", "model.layers.1.mlp.shared_experts.up_proj.weight",
+                  "model.layers.1.self_attn.kv_a_proj_with_mqa.weight"):
+            assert n in names, n
+        assert not any(n.startswith("model.layers.1.self_attn.indexer") for n in names)     # shares layer 0's selection
     if name == "tiny-minimax-m3":
         for n in ("model.layers.0.mlp.gate_proj.weight", "model.layers.1.block_sparse_moe.experts.3.w1.weight",
                   "model.layers.1.block_sparse_moe.experts.3.w2.weight", "model.layers.1.block_sparse_moe.gate.weight",
@@ -216,6 +222,48 @@ def test_family_hf_roundtrip(name, tmp_path):
     wa = dict(a.iter_full_tensors("master"))
     for k, v in b.iter_full_tensors("master"):
         assert torch.equal(v, wa[k]), k
+
+
+def test_glm5_indexer_selection_and_sharing():
+    """The lightning indexer keeps the top-k causal keys of every query, by the gated ReLU score;
+    layers without an indexer attend to the selection of the closest earlier layer that has one;
+    with top-k >= document length the model equals dense latent attention."""
+    from xorl_b200.models import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.models.glm5 import indexer_scores, select_topk_keys
+    torch.manual_seed(0)
+    L, Hi, Di = 20, 2, 8
+    iq, ik, g = torch.randn(L, Hi, Di), torch.randn(L, Di), torch.rand(L, Hi)
+    sc = indexer_scores(iq, ik, g)
+    ref = torch.zeros(L, L)
+    for t in range(L):
+        for s_ in range(L):
+            ref[t, s_] = sum(g[t, h] * torch.relu(iq[t, h] @ ik[s_]) for h in range(Hi)) * Di ** -0.5
+    assert (sc - ref).abs().max() < 1e-5
+    keep = select_topk_keys(sc, 4)
+    assert keep.sum(-1).tolist() == [min(t + 1, 4) for t in range(L)] and not keep.triu(1).any()
+    t = 15
+    best = sc[t, : t + 1].topk(4).indices.sort().values
+    assert torch.equal(keep[t].nonzero().flatten(), best)
+    cfg = preset("tiny-glm5")
+    m = DecoderLM(cfg)
+    m.init_weights(0)
+    ids = torch.randint(0, cfg.vocab_size, (48,))
+    cu = torch.tensor([0, 20, 48], dtype=torch.int32)
+    with torch.no_grad():
+        sparse = m.logits(ids, cu_seqlens=cu)
+        for l in m.layers.values():
+            if l.self_attn.indexer is not None:
+                l.self_attn.indexer.topk = 1000
+        dense = m.logits(ids, cu_seqlens=cu)
+        ctx = m.make_context(ids, cu_seqlens=cu)
+        h, r = m.forward_embed(ids, ctx)
+        for l in m.layers.values():
+            h, r = l(h, r, ctx)
+    assert (sparse[:8] - dense[:8]).abs().max() < 1e-4         # the first 8 tokens see at most 8 keys
+    assert (sparse - dense).abs().max() > 1e-4
+    assert ("dsa_keep", 0) in ctx.aux and ("dsa_keep", 2) in ctx.aux and ("dsa_keep", 1) not in ctx.aux
+    assert m.layers["1"].self_attn.indexer is None and m.layers["1"].self_attn.producer == 0
 
 
 def test_minimax_sparse_attention_selects_blocks():

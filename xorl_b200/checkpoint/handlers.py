@@ -116,6 +116,13 @@ class DeepseekV3Handler(_RenamingHandler):
     RENAMES = ((".mlp.shared_expert.", ".mlp.shared_experts."),)
 
 
+class Glm5Handler(DeepseekV3Handler):
+    """GLM-5: DeepSeek-style names plus the sparse indexer, whose key LayerNorm is a module on disk
+    (``self_attn.indexer.k_norm.weight / .bias``; src/xorl/models/transformers/glm5/indexer.py)."""
+    RENAMES = DeepseekV3Handler.RENAMES + ((".indexer.k_norm_weight", ".indexer.k_norm.weight"),
+                                           (".indexer.k_norm_bias", ".indexer.k_norm.bias"))
+
+
 class GptOssHandler(CheckpointHandler):
     """gpt-oss keeps experts stacked on disk, with gate and up columns interleaved, per-expert
     biases, the router under ``mlp.router`` and one sink logit per head
@@ -371,6 +378,8 @@ def get_checkpoint_handler(cfg) -> CheckpointHandler:
         return Qwen35Handler(cfg)
     if mt == "gpt_oss":
         return GptOssHandler(cfg)
+    if mt == "glm5":
+        return Glm5Handler(cfg)
     if mt in ("deepseek_v3", "glm4_moe"):
         return DeepseekV3Handler(cfg)
     return CheckpointHandler(cfg)

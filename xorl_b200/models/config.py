@@ -159,7 +159,12 @@ class ModelConfig:
             if d.get("layer_types") is None and d.get("sliding_window"):
                 n = d.get("num_hidden_layers", 0)
                 d["layer_types"] = ["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(n)]
-        if mt in ("deepseek_v3", "glm4_moe"):
+        if mt in ("glm5", "glm_moe_dsa", "xorl_glm5"):
+            if isinstance(d.get("text_config"), dict):
+                d = {**{k: v for k, v in d.items() if k != "text_config"}, **d["text_config"]}
+            mt = d["model_type"] = "glm5"
+            d.setdefault("topk_method", "noaux_tc")
+        if mt in ("deepseek_v3", "glm4_moe", "glm5"):
             d["use_qk_norm"] = bool(d.get("use_qk_norm", False)) if mt == "glm4_moe" else False
             d.setdefault("scoring_func", "sigmoid")
             d.setdefault("use_correction_bias", True)
@@ -167,7 +172,7 @@ class ModelConfig:
                 d["shared_expert_intermediate_size"] = d["n_shared_experts"] * d.get("moe_intermediate_size", 0)
             if mt == "deepseek_v3" and d.get("moe_layer_freq"):
                 d.setdefault("decoder_sparse_step", d["moe_layer_freq"])
-            if mt == "deepseek_v3":
+            if mt in ("deepseek_v3", "glm5"):
                 d["head_dim"] = d.get("qk_rope_head_dim", 64)      # rotary table covers the rope slice
         if mt in ("minimax_m3", "minimax_m3_vl", "xorl_minimax_m3"):
             # the published config is a multimodal wrapper with the language model under text_config
@@ -298,6 +303,13 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                              num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
                              norm_topk_prob=True, rope_theta=1e4, max_position_embeddings=512,
                              tie_word_embeddings=False),
+    "tiny-glm5": dict(model_type="glm5", vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=4,
+                      num_attention_heads=4, num_key_value_heads=4, q_lora_rank=32, kv_lora_rank=16,
+                      qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, n_routed_experts=8,
+                      num_experts_per_tok=2, moe_intermediate_size=32, n_shared_experts=1, first_k_dense_replace=1,
+                      n_group=2, topk_group=1, routed_scaling_factor=2.0, norm_topk_prob=True,
+                      index_n_heads=2, index_head_dim=16, index_topk=8, index_topk_freq=2,
+                      rope_theta=1e4, max_position_embeddings=512, tie_word_embeddings=False),
     "tiny-minimax-m3": dict(model_type="minimax_m3", vocab_size=512, hidden_size=64, num_hidden_layers=4,
                             num_attention_heads=4, num_key_value_heads=2, head_dim=16, rotary_dim=8,
                             dense_intermediate_size=128, intermediate_size=32, shared_intermediate_size=32,

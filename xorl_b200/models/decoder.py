@@ -35,6 +35,9 @@ class DecoderLayer(nn.Module):
         if cfg.layer_types is not None and cfg.layer_types[layer_idx] == "linear_attention":
             from .gated_deltanet import GatedDeltaNet
             self.self_attn = GatedDeltaNet(cfg, layer_idx, dtype=dtype, device=device)
+        elif cfg.model_type == "glm5":
+            from .glm5 import Glm5Attention
+            self.self_attn = Glm5Attention(cfg, layer_idx, dtype=dtype, device=device)
         elif cfg.extra.get("kv_lora_rank"):
             from .mla import MLAttention
             self.self_attn = MLAttention(cfg, layer_idx, dtype=dtype, device=device)

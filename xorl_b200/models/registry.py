@@ -24,6 +24,7 @@ for _n in ("qwen3", "Qwen3ForCausalLM", "qwen2", "Qwen2ForCausalLM", "llama", "L
            "Glm4MoeForCausalLM", "gpt_oss", "GptOssForCausalLM", "deepseek_v3",
            "DeepseekV3ForCausalLM", "qwen3_5", "qwen3_5_moe", "qwen3_next", "Qwen3NextForCausalLM",
            "Qwen3_5ForCausalLM", "Qwen3_5MoeForCausalLM", "nemotron_h", "NemotronHForCausalLM",
+           "glm5", "Glm5ForCausalLM", "GlmMoeDsaForCausalLM",
            "minimax_m3", "MiniMaxM3SparseForCausalLM", "MiniMaxM3SparseForConditionalGeneration"):
     MODEL_REGISTRY[_n] = _decoder
 
@@ -31,7 +32,7 @@ for _n in ("qwen3", "Qwen3ForCausalLM", "qwen2", "Qwen2ForCausalLM", "llama", "L
 # mixers, sparse-index attention, hyper-connections).  Asking for one fails loudly instead of
 # training a different architecture under the same name.
 UNSUPPORTED = {
-    "glm5": "MLA with the DSA sparse indexer",
+
     "deepseek_v4": "compressed sparse attention and hyper-connections",
 }
 
