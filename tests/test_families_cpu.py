@@ -23,7 +23,7 @@ def _state():
 
 @pytest.mark.parametrize("name", ["tiny-qwen3", "tiny-qwen2", "tiny-olmo2", "tiny-qwen3-moe", "tiny-gpt-oss",
                                   "tiny-deepseek-v3", "tiny-glm4-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe",
-                                  "tiny-nemotron-h", "tiny-minimax-m3", "tiny-glm5"])
+                                  "tiny-nemotron-h", "tiny-minimax-m3", "tiny-glm5", "tiny-deepseek-v4"])
 def test_family_trains(name):
     from xorl_b200.models import build_model
     from xorl_b200.models.config import preset
@@ -50,11 +50,77 @@ def test_family_trains(name):
     assert all(math.isfinite(l) for l in losses) and losses[-1] < losses[0], losses
 
 
-def test_unbuilt_families_fail_loudly():
+def test_unknown_family_fails_loudly():
     from xorl_b200.models.config import ModelConfig
     from xorl_b200.models.registry import get_model_class
-    with pytest.raises(NotImplementedError):
-        get_model_class(ModelConfig.from_dict({"model_type": "deepseek_v4"}))
+    with pytest.raises(KeyError):
+        get_model_class(ModelConfig.from_dict({"model_type": "not_a_model"}))
+
+
+def test_deepseek_v4_pieces():
+    """Hyper-connection mixers (Sinkhorn-normalised mixing matrix, collapse / spread algebra), the
+    pooled key compressor against its definition, the window-only attention layer against dense
+    attention with a window and sink logits on a shared key/value head, and hash routing."""
+    from xorl_b200.models import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.models.deepseek_v4 import HyperConnection, hc_split_sinkhorn, rope_tables, rope_tail
+    from xorl_b200.ops.attention import attention_reference
+    torch.manual_seed(0)
+    hc = 4
+    mixes = torch.randn(7, (2 + hc) * hc)
+    pre, post, comb = hc_split_sinkhorn(mixes, torch.tensor([1.0, 0.5, 2.0]), torch.randn((2 + hc) * hc) * 0.1, hc, 20, 1e-6)
+    assert pre.shape == (7, hc) and (pre > 0).all() and (post > 0).all() and (post < 2).all()
+    assert (comb.sum(-1) - 1).abs().max() < 5e-3 and (comb.sum(-2) - 1).abs().max() < 1e-4   # columns were normalised last
+    x, y = torch.randn(7, hc, 5), torch.randn(7, 5)
+    out = HyperConnection.post(y, x, post, comb)
+    ref = torch.stack([post[:, i:i + 1] * y + sum(comb[:, j, i:i + 1] * x[:, j] for j in range(hc)) for i in range(hc)], 1)
+    assert (out - ref).abs().max() < 1e-5
+    # rotating the tail and rotating back is the identity
+    t = torch.randn(6, 2, 16)
+    cos, sin = rope_tables(torch.arange(6), 8, 1e4)
+    assert (rope_tail(rope_tail(t, cos, sin, 8), cos, sin, 8, inverse=True) - t).abs().max() < 1e-5
+    cfg = preset("tiny-deepseek-v4")
+    m = DecoderLM(cfg)
+    m.init_weights(0)
+    ids = torch.randint(0, cfg.vocab_size, (40,))
+    cu = torch.tensor([0, 40], dtype=torch.int32)
+    ctx = m.make_context(ids, cu_seqlens=cu)
+    # compressor of layer 2 would need 128 tokens; layer 1 (ratio 4, overlapping groups)
+    comp = m.layers["1"].self_attn.compressor
+    xin = torch.randn(40, cfg.hidden_size)
+    got = comp(xin, ctx.position_ids)
+    assert got.shape == (10, cfg.extra["v4_head_dim"])
+    hd = comp.hd
+    kv = torch.nn.functional.linear(xin, comp.wkv.weight).view(10, 4, 2 * hd)
+    sc = torch.nn.functional.linear(xin, comp.wgate.weight).view(10, 4, 2 * hd) + comp.ape
+    g = 3                                                   # group 3 pools its own 4 tokens and group 2's
+    slots_kv = torch.cat([kv[g - 1, :, :hd], kv[g, :, hd:]], 0)
+    slots_sc = torch.cat([sc[g - 1, :, :hd], sc[g, :, hd:]], 0)
+    pooled = comp.norm((slots_kv * slots_sc.softmax(0)).sum(0, keepdim=True))
+    c4, s4 = rope_tables(torch.tensor([g * 4]), comp.rd, comp.theta)
+    assert (rope_tail(pooled.unsqueeze(1), c4, s4, comp.rd)[0, 0] - got[g]).abs().max() < 1e-5
+    # layer 0: sliding window + sinks only
+    att = m.layers["0"].self_attn
+    with torch.no_grad():
+        att.attn_sink.copy_(torch.randn(att.H))
+        h = torch.randn(40, cfg.hidden_size)
+        out = att(h, ctx)
+        cos, sin = rope_tables(ctx.position_ids, att.rd, att.theta)
+        q = att.wq_b(att.q_norm(att.wq_a(h))).view(40, att.H, att.hd)
+        q = rope_tail(q * torch.rsqrt(q.square().mean(-1, keepdim=True) + att.eps), cos, sin, att.rd)
+        kv1 = rope_tail(att.kv_norm(att.wkv(h)).unsqueeze(1), cos, sin, att.rd)
+        o = attention_reference(q, kv1, kv1, cu, True, att.scale, window=att.window, sinks=att.attn_sink)
+        o = rope_tail(o, cos, sin, att.rd, inverse=True).reshape(40, att.G, -1)
+        ref = att.wo_b(torch.einsum("tgd,grd->tgr", o, att.wo_a.weight.view(att.G, att.r_o, -1)).reshape(40, -1))
+    assert (out - ref).abs().max() < 1e-4
+    # hash routing: layer 0 sends every token to the experts listed for its id
+    moe = m.layers["0"].mlp
+    assert moe.is_hash_layer and not m.layers["1"].mlp.is_hash_layer
+    ctx.aux["collect_expert_load"] = True
+    with torch.no_grad():
+        moe(torch.randn(40, cfg.hidden_size), ctx)
+    want = torch.bincount(moe.tid2eid[ids].long().reshape(-1), minlength=cfg.num_experts)
+    assert torch.equal(ctx.aux[("expert_load", 0)], want)
 
 
 def test_attention_window_and_sinks_reference():
@@ -164,7 +230,7 @@ def test_mla_matches_explicit_formula():
 
 
 @pytest.mark.parametrize("name", ["tiny-gpt-oss", "tiny-deepseek-v3", "tiny-qwen3-moe", "tiny-qwen3-5", "tiny-qwen3-5-moe", "tiny-nemotron-h",
-                                  "tiny-minimax-m3", "tiny-glm5"])
+                                  "tiny-minimax-m3", "tiny-glm5", "tiny-deepseek-v4"])
 def test_family_hf_roundtrip(name, tmp_path):
     """Export to HF-named safetensors and load back into a fresh engine: identical weights."""
     from xorl_b200.checkpoint.hf_io import load_hf_weights, save_hf_weights
@@ -193,6 +259,12 @@ def test_family_hf_roundtrip(name, tmp_path):
         assert "model.layers.0.linear_attn.in_proj_qkv.weight" in names and "model.layers.0.linear_attn.conv1d.weight" in names
         assert "model.layers.0.linear_attn.in_proj_z.weight" in names and "model.layers.0.linear_attn.A_log" in names
         assert "model.layers.3.self_attn.q_proj.weight" in names and not any("out_gate" in n or "qkv_proj" in n for n in names)
+    if name == "tiny-deepseek-v4":
+        for n in ("model.layers.0.hc_attn_fn", "model.layers.3.hc_ffn_scale", "model.hc_head_base",
+                  "model.layers.0.mlp.tid2eid", "model.layers.1.mlp.gate.e_score_correction_bias",
+                  "model.layers.1.self_attn.indexer.compressor.ape", "model.layers.2.self_attn.compressor.wgate.weight",
+                  "model.layers.0.self_attn.attn_sink", "model.layers.1.mlp.shared_experts.down_proj.weight"):
+            assert n in names, n
     if name == "tiny-glm5":
         for n in ("model.layers.0.self_attn.indexer.k_norm.bias", "model.layers.0.self_attn.indexer.wq_b.weight",
                   "model.layers.2.self_attn.indexer.weights_proj.weight", "model.layers.1.mlp.shared_experts.up_proj.weight",

@@ -123,6 +123,15 @@ class Glm5Handler(DeepseekV3Handler):
                                            (".indexer.k_norm_bias", ".indexer.k_norm.bias"))
 
 
+class DeepseekV4Handler(_RenamingHandler):
+    """DeepSeek-V4 in the reference's own tensor names: the hyper-connection mixers are flat per-layer
+    tensors ``hc_attn_fn / hc_attn_base / hc_attn_scale`` (and ``hc_ffn_*``, ``hc_head_*``), the shared
+    expert is ``shared_experts`` (src/xorl/models/transformers/deepseek_v4/modeling_deepseek_v4.py).
+    The published checkpoint's packed low-precision expert layout is not parsed here."""
+    RENAMES = ((".mlp.shared_expert.", ".mlp.shared_experts."),) + tuple(
+        (f"{pre}.{leaf}", f"{pre}_{leaf}") for pre in ("hc_attn", "hc_ffn", "hc_head") for leaf in ("fn", "base", "scale"))
+
+
 class GptOssHandler(CheckpointHandler):
     """gpt-oss keeps experts stacked on disk, with gate and up columns interleaved, per-expert
     biases, the router under ``mlp.router`` and one sink logit per head
@@ -380,6 +389,8 @@ def get_checkpoint_handler(cfg) -> CheckpointHandler:
         return GptOssHandler(cfg)
     if mt == "glm5":
         return Glm5Handler(cfg)
+    if mt == "deepseek_v4":
+        return DeepseekV4Handler(cfg)
     if mt in ("deepseek_v3", "glm4_moe"):
         return DeepseekV3Handler(cfg)
     return CheckpointHandler(cfg)

@@ -207,6 +207,24 @@ class ModelConfig:
             for key, default in (("sparse_block_size", 128), ("sparse_topk_blocks", 16), ("sparse_num_index_heads", 4),
                                  ("sparse_index_dim", hd), ("sparse_init_block", 0), ("sparse_local_block", 1)):
                 d.setdefault(key, sa.get(key, default))
+        if mt == "deepseek_v4":
+            d["use_qk_norm"] = False
+            d["v4_head_dim"] = d.get("head_dim", 512)
+            d["head_dim"] = d.get("qk_rope_head_dim", 64)
+            d.setdefault("scoring_func", "sqrtsoftplus")
+            d.setdefault("use_correction_bias", True)
+            d.setdefault("sliding_window", 128)
+            d.setdefault("routed_scaling_factor", 1.5)
+            d.setdefault("router_aux_loss_coef", 0.0)
+            d.setdefault("swiglu_limit", 10.0)
+            d.setdefault("dense_swiglu_limit", d["swiglu_limit"])
+            d.setdefault("intermediate_size", d.get("moe_intermediate_size", 2048))
+            if d.get("n_shared_experts") and not d.get("shared_expert_intermediate_size"):
+                d["shared_expert_intermediate_size"] = d["n_shared_experts"] * d.get("moe_intermediate_size", 0)
+            n = d.get("num_hidden_layers", 43)
+            if d.get("compress_ratios") is None:
+                # sliding-window-only first layer, then compressed layers alternating 4 and 128
+                d["compress_ratios"] = [0] + [4 if i % 2 else 128 for i in range(1, n)]
         if mt == "nemotron_h":
             # one mixer per layer: Mamba2 / attention without rotary embedding / latent MoE / MLP
             lbt = d.get("layers_block_type")
@@ -303,6 +321,13 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                              num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
                              norm_topk_prob=True, rope_theta=1e4, max_position_embeddings=512,
                              tie_word_embeddings=False),
+    "tiny-deepseek-v4": dict(model_type="deepseek_v4", vocab_size=512, hidden_size=64, num_hidden_layers=4,
+                             num_attention_heads=4, num_key_value_heads=1, head_dim=32, qk_rope_head_dim=8,
+                             q_lora_rank=32, o_groups=2, o_lora_rank=16, sliding_window=8, index_n_heads=2,
+                             index_head_dim=16, index_topk=3, moe_intermediate_size=32, n_routed_experts=8,
+                             n_shared_experts=1, num_experts_per_tok=2, num_hash_layers=1, hc_mult=2,
+                             hc_sinkhorn_iters=4, compress_ratios=[0, 4, 128, 4], compress_rope_theta=4e4,
+                             rope_theta=1e4, max_position_embeddings=512, tie_word_embeddings=False),
     "tiny-glm5": dict(model_type="glm5", vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=4,
                       num_attention_heads=4, num_key_value_heads=4, q_lora_rank=32, kv_lora_rank=16,
                       qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, n_routed_experts=8,

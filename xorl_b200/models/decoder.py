@@ -106,6 +106,11 @@ class DecoderLM(nn.Module):
         if cfg.model_type == "nemotron_h":
             from .nemotron_h import NemotronHLayer
             layer_cls = NemotronHLayer
+        elif cfg.model_type == "deepseek_v4":
+            from .deepseek_v4 import HyperConnection, V4Layer
+            layer_cls = V4Layer
+            if has_head:
+                self.hc_head = HyperConnection(cfg, device=device, head=True)
         self.layers = nn.ModuleDict({str(i): layer_cls(cfg, i, dtype, device) for i in idx})
         if has_head:
             self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.zero_centered_norm, dtype, device)
@@ -150,7 +155,7 @@ class DecoderLM(nn.Module):
         later sharded."""
         std = self.config.initializer_range
         for idx, (name, p) in enumerate(self.named_parameters()):
-            init_parameter_(name, p, std, seed, idx, self.config.zero_centered_norm)
+            init_parameter_(name, p, std, seed, idx, self.config.zero_centered_norm, self.config.num_experts)
 
     # ---- unit-level API used by the engine ------------------------------------------------------
     def make_context(self, input_ids, position_ids=None, cu_seqlens=None, causal=True,
@@ -172,6 +177,8 @@ class DecoderLM(nn.Module):
         ctx = StepContext(cu_seqlens=cu_seqlens, position_ids=position_ids, causal=causal,
                           training=training, cp=self.cp_strategy)
         ctx.aux.update(self.ctx_defaults)
+        if self.config.extra.get("num_hash_layers"):
+            ctx.aux["input_ids"] = input_ids.reshape(-1)       # hash-routed MoE layers pick experts by token id
         if extra:
             ctx.aux.update({k: v for k, v in extra.items() if v is not None})
         if ctx.cp is not None:
@@ -182,12 +189,18 @@ class DecoderLM(nn.Module):
 
     def forward_embed(self, input_ids: torch.Tensor, ctx: StepContext):
         ids = input_ids.reshape(-1)
+        if self.config.model_type == "deepseek_v4":
+            # hyper-connections: the residual stream starts as hc_mult copies of the embedding
+            e = emb_ops.embedding(ids, self.embed_tokens.weight)
+            return e.unsqueeze(1).repeat(1, int(self.config.extra.get("hc_mult", 4)), 1), None
         if self.sp is not None:
             from ..parallel.tp_fused import local_tokens
             ids = local_tokens(ids, self.sp)        # the residual stream holds T / tp tokens per rank
         return emb_ops.embedding(ids, self.embed_tokens.weight), None
 
     def forward_head(self, h, residual, ctx: StepContext) -> torch.Tensor:
+        if self.config.model_type == "deepseek_v4":
+            return self.norm(self.hc_head.collapse(h))
         hidden = self.norm(h) if residual is None else self.norm(h, residual=residual)[0]
         if self.sp is not None:
             # the loss sees all tokens on every rank and returns the same gradient everywhere
@@ -217,6 +230,8 @@ class DecoderLM(nn.Module):
             root.append(self.embed_tokens)
         if self.has_head:
             root += [self.norm, self.lm_head]
+            if hasattr(self, "hc_head"):
+                root.append(self.hc_head)
         units = [("root", root)] if root else []
         return units + [(f"layers.{i}", [l]) for i, l in self.layers.items()]
 
@@ -242,7 +257,7 @@ class DecoderLM(nn.Module):
 
 @torch.no_grad()
 def init_parameter_(name: str, p: torch.Tensor, std: float, seed: int, index: int,
-                    zero_centered_norm: bool = False) -> None:
+                    zero_centered_norm: bool = False, num_experts: int = 0) -> None:
     if p.is_meta:
         return
     if ".lora_A." in name or ".lora_B." in name:
@@ -257,6 +272,17 @@ def init_parameter_(name: str, p: torch.Tensor, std: float, seed: int, index: in
         tmp = torch.empty(p.shape, dtype=torch.float32)
         init_mamba_parameter_(name, tmp, g)
         p.copy_(tmp.to(p.device))
+        return
+    if leaf in ("attn_sink", "base") or leaf == "tid2eid":
+        if leaf == "tid2eid":
+            import zlib
+            from .deepseek_v4 import init_hash_table_
+            g = torch.Generator(device="cpu").manual_seed((seed * 1000003 + zlib.crc32(name.encode()) * 7919 + 17) % (2 ** 63 - 1))
+            tmp = torch.empty(p.shape, dtype=torch.float32)
+            init_hash_table_(tmp, num_experts or p.shape[1], g)
+            p.copy_(tmp.to(p.device))
+        else:
+            p.zero_()
         return
     if leaf == "A_log":                      # GatedDeltaNet decay rates spread over (0, 16)
         p.copy_(torch.linspace(0.5, 16.0, p.numel()).log().to(p.device))

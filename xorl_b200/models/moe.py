@@ -133,6 +133,8 @@ class MoEBlock(nn.Module):
             weights = probs.gather(1, indices)
             if self.cfg.norm_topk_prob:
                 weights = weights / weights.sum(-1, keepdim=True).clamp_min(1e-20)
+            if self.gate.scale != 1.0 and self.gate.scoring != "softmax_after_topk":
+                weights = weights * self.gate.scale
         elif ctx.aux.get("record_routing", False):
             ctx.aux[("routing_record", self.layer_idx)] = indices.detach()
         if ctx.training and self.aux_coef > 0 and ctx.aux.get("aux_loss_scale") is not None:

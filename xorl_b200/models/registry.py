@@ -24,17 +24,13 @@ for _n in ("qwen3", "Qwen3ForCausalLM", "qwen2", "Qwen2ForCausalLM", "llama", "L
            "Glm4MoeForCausalLM", "gpt_oss", "GptOssForCausalLM", "deepseek_v3",
            "DeepseekV3ForCausalLM", "qwen3_5", "qwen3_5_moe", "qwen3_next", "Qwen3NextForCausalLM",
            "Qwen3_5ForCausalLM", "Qwen3_5MoeForCausalLM", "nemotron_h", "NemotronHForCausalLM",
-           "glm5", "Glm5ForCausalLM", "GlmMoeDsaForCausalLM",
+           "glm5", "Glm5ForCausalLM", "GlmMoeDsaForCausalLM", "deepseek_v4", "DeepseekV4ForCausalLM",
            "minimax_m3", "MiniMaxM3SparseForCausalLM", "MiniMaxM3SparseForConditionalGeneration"):
     MODEL_REGISTRY[_n] = _decoder
 
-# Families of the reference whose token mixers are not built here (linear-attention / state-space
-# mixers, sparse-index attention, hyper-connections).  Asking for one fails loudly instead of
-# training a different architecture under the same name.
-UNSUPPORTED = {
-
-    "deepseek_v4": "compressed sparse attention and hyper-connections",
-}
+# model_type -> reason, for architectures that are known but not built (none at present): asking for
+# one fails loudly instead of training a different architecture under the same name.
+UNSUPPORTED: Dict[str, str] = {}
 
 
 def get_model_class(cfg):

@@ -86,13 +86,14 @@ def topk_route(logits: torch.Tensor, k: int, renorm: bool = True, scoring: str =
                correction_bias: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """fp32 logits [T, E] -> (weights [T, k], indices [T, k], probs [T, E]).
 
-    ``scoring`` "softmax" (Qwen/Mixtral style), "sigmoid" (DeepSeek-V3 / GLM-4.5 style) or
+    ``scoring`` "softmax" (Qwen/Mixtral style), "sigmoid" (DeepSeek-V3 / GLM-4.5 style),
+    "sqrtsoftplus" (DeepSeek-V4: sqrt(softplus(logit)), otherwise like sigmoid) or
     "softmax_after_topk" (gpt-oss: softmax over the k selected logits).  With ``correction_bias``
     the *selection* uses ``probs + bias`` while the weights stay the unbiased scores (auxiliary-loss
     free balancing); with ``n_group > 1`` experts are chosen only inside the ``topk_group`` groups
     with the best sum of their two best biased scores (src/xorl/models/layers/moe/router.py)."""
     if (logits.is_cuda and logits.dtype == torch.float32 and n_group <= 1 and logits.shape[1] <= 512 and k <= 32
-            and _lib.have_cuda_lib() and os.environ.get("XORL_B200_ROUTE_KERNEL", "1") == "1"):
+            and scoring in ("softmax", "sigmoid", "softmax_after_topk") and _lib.have_cuda_lib() and os.environ.get("XORL_B200_ROUTE_KERNEL", "1") == "1"):
         return _RouteKernel.apply(logits, correction_bias, k, bool(renorm), scoring, float(scale))
     if scoring == "softmax_after_topk":
         top, indices = torch.topk(logits, k, dim=-1)
@@ -101,6 +102,8 @@ def topk_route(logits: torch.Tensor, k: int, renorm: bool = True, scoring: str =
         return weights * scale if scale != 1.0 else weights, indices, probs
     if scoring == "sigmoid":
         probs = torch.sigmoid(logits)
+    elif scoring == "sqrtsoftplus":             # DeepSeek-V4
+        probs = torch.sqrt(torch.nn.functional.softplus(logits.float()))
     else:
         probs = torch.softmax(logits, dim=-1, dtype=torch.float32)
     choice = probs if correction_bias is None else probs + correction_bias.float().unsqueeze(0)
