@@ -116,11 +116,63 @@ def test_muon_two_gloo_ranks_match_single_process():
         assert abs(a - b) < 2e-3, (ref, got)                      # bf16 iteration, shard-independent
 
 
+def _distsign_probe(world, rank):
+    """One majority-vote sign SGD step; returns the update of one weight matrix."""
+    from xorl_b200.models.config import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.state import get_parallel_state
+    from xorl_b200.parallel.zero import Zero3Engine
+    m = DecoderLM(preset("tiny-qwen3"), dtype=torch.float32, device="meta")
+    eng = Zero3Engine(m, get_parallel_state(), compute_dtype=torch.float32, device=torch.device("cpu"), seed=0)
+    opt = build_optimizer(eng, lr=1e-2, weight_decay=0.0, optimizer_type="distsignsgd")
+    name = "layers.0.mlp.down_proj.weight"
+    before = dict(eng.iter_full_tensors("master"))[name].clone()
+    x, y = _data(0)
+    opt.zero_grad()
+    eng.forward_backward(x[rank::world], y[rank::world], grad_scale=1.0 / y.numel())
+    eng.finish_grad_sync()
+    opt.step()
+    after = dict(eng.iter_full_tensors("master"))[name]
+    return (after - before)
+
+
+@pytest.mark.distributed
+def test_distsignsgd_votes_before_the_reduction():
+    """Two ranks: the update is -lr * (sign(g_0) + sign(g_1)) / 2 with g_r the gradient of rank r's
+    own micro-batch, not -lr * sign(g_0 + g_1)."""
+    from dist_utils import run_distributed
+    from xorl_b200.models.config import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.optim.optimizer import MultiOptimizer
+    out = run_distributed(__file__, 2, "distsign")
+    got = torch.tensor(json.loads([l for l in out.splitlines() if l.startswith("UPDATE ")][-1][7:]))
+    m = DecoderLM(preset("tiny-qwen3"), dtype=torch.float32)
+    m.init_weights(0)
+    x, y = _data(0)
+    votes = 0
+    for r in range(2):
+        m.zero_grad()
+        m(x[r::2], labels=y[r::2], grad_scale=1.0 / y.numel())["loss"].backward()
+        votes = votes + torch.sign(m.layers["0"].mlp.down_proj.weight.grad)
+    want = -1e-2 * votes / 2
+    assert (got - want[:4, :16]).abs().max() < 1e-6, (got, want[:4, :16])
+    assert set(torch.unique((got / -1e-2 * 2).round()).tolist()) <= {-2.0, -1.0, 0.0, 1.0, 2.0}
+    with pytest.raises(ValueError):
+        MultiOptimizer({})
+
+
 if __name__ == "__main__":
     import torch.distributed as dist
     from xorl_b200.parallel.state import init_parallel_state
     dist.init_process_group("gloo")
     init_parallel_state(device_type="cpu", dp_mode="fsdp2")
+    if len(sys.argv) > 1 and sys.argv[1] == "distsign":
+        upd = _distsign_probe(dist.get_world_size(), dist.get_rank())
+        if dist.get_rank() == 0:
+            print("UPDATE " + json.dumps(upd[:4, :16].tolist()))
+        dist.destroy_process_group()
+        sys.exit(0)
     if len(sys.argv) > 1 and sys.argv[1] == "muon":
         curve = engine_curve(6, dist.get_world_size(), dist.get_rank(), optimizer="muon", lr=1e-3,
                              fixed_batch=True)

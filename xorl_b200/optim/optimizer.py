@@ -210,6 +210,76 @@ class ShardedSignSGD(ShardedOptimizer):
                                         None if lp is None else lp[a:b], lr=self.lr, weight_decay=wd)
 
 
+class ShardedDistSignSGD(ShardedOptimizer):
+    """Majority-vote sign SGD: every data-parallel rank signs the gradient of every micro-batch
+    *before* the reduce-scatter, the votes are summed over ranks and micro-batches, and the update is
+    ``lr * votes / voters`` -- no second sign (src/xorl/optim/distsignsgd.py: ``DistSignReduceScatter``
+    signs the flat buffer, ``DistSignSGD.step`` applies the pre-signed sum).  The engine signs the
+    per-micro-batch gradient buffers (``engine.sign_before_reduce``); a shard group of one rank
+    accumulates raw gradients in place, so there the single voter signs once at the step."""
+    kind = "distsignsgd"
+
+    def __init__(self, engine, lr, weight_decay=0.0, **kw):
+        super().__init__(engine, lr, weight_decay, **kw)
+        engine.sign_before_reduce = True
+
+    def step(self, clip_coef=None, grad_scale: float = 1.0) -> None:
+        self.step_count += 1
+        eng = self.engine
+        for g in eng.all_groups():
+            if not g.grad_ready:
+                continue
+            if g.world > 1:
+                update = g.grad_shard / float(g.world * max(1, eng.micro_batches))
+            else:
+                update = torch.sign(g.grad_shard)
+            for a, b, wd in self._segments(g):
+                if wd:
+                    g.master[a:b].mul_(1.0 - self.lr * wd)
+                g.master[a:b].add_(update[a:b], alpha=-self.lr)
+            if g.shard_lp is not g.master:
+                g.shard_lp.copy_(g.master)
+
+
+class MultiOptimizer:
+    """Several optimizers driven as one (the reference pairs one optimizer for expert parameters with
+    one for the rest, and one per pipeline model part: src/xorl/optim/multi_optimizer.py).  The
+    sharded optimizers here already cover every parameter group of an engine; this wrapper exists for
+    callers that build optimizers per engine (pipeline stages with virtual chunks) or per parameter
+    family and want a single ``step / zero_grad / state_dict`` surface."""
+
+    def __init__(self, optimizers: Dict[str, ShardedOptimizer]):
+        if not optimizers:
+            raise ValueError("MultiOptimizer needs at least one optimizer")
+        self.optimizers = dict(optimizers)
+
+    @property
+    def lr(self) -> float:
+        return next(iter(self.optimizers.values())).lr
+
+    def set_lr(self, lr: float) -> None:
+        for o in self.optimizers.values():
+            o.set_lr(lr)
+
+    def zero_grad(self) -> None:
+        for o in self.optimizers.values():
+            o.zero_grad()
+
+    def step(self, clip_coef=None, grad_scale: float = 1.0) -> None:
+        for o in self.optimizers.values():
+            o.step(clip_coef=clip_coef, grad_scale=grad_scale)
+
+    def state_dict(self) -> Dict:
+        return {name: o.state_dict() for name, o in self.optimizers.items()}
+
+    def load_state_dict(self, sd: Dict) -> None:
+        missing = set(self.optimizers) - set(sd)
+        if missing:
+            raise KeyError(f"optimizer state lacks entries for {sorted(missing)}")
+        for name, o in self.optimizers.items():
+            o.load_state_dict(sd[name])
+
+
 def build_optimizer(engine: Zero3Engine, lr: float = 1e-3, betas=(0.9, 0.95), eps: float = 1e-8,
                     weight_decay: float = 1e-2, optimizer_type: str = "adamw",
                     optimizer_dtype: str = "bf16", no_decay_modules=None, no_decay_params=None,
@@ -225,8 +295,10 @@ def build_optimizer(engine: Zero3Engine, lr: float = 1e-3, betas=(0.9, 0.95), ep
     if optimizer_type == "sgd":
         return ShardedSGD(engine, lr, okw.get("momentum", 0.0), okw.get("nesterov", False),
                           weight_decay, **kw)
-    if optimizer_type in ("signsgd", "distsignsgd"):
+    if optimizer_type == "signsgd":
         return ShardedSignSGD(engine, lr, weight_decay, **kw)
+    if optimizer_type == "distsignsgd":
+        return ShardedDistSignSGD(engine, lr, weight_decay, **kw)
     if optimizer_type == "muon":
         from .muon import ShardedMuon
         return ShardedMuon(engine, lr, betas, eps, weight_decay, **okw, **kw)

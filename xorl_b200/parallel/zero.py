@@ -238,6 +238,8 @@ class Zero3Engine:
         self.ep_shard_world = ps.ep_fsdp_size if ps.ep_size > 1 else self.shard_world
         self.ep_shard_rank = ps.rank_in("ep_fsdp") if ps.ep_size > 1 else self.shard_rank
         self.reshard = reshard_after_forward and self.shard_world > 1
+        self.sign_before_reduce = False        # set by the majority-vote sign SGD optimizer
+        self.micro_batches = 0                 # forward_backward calls since zero_grad
         self.units: List[ZeroUnit] = []
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
         self._full_pool: Dict[Tuple[int, torch.dtype], List[torch.Tensor]] = {}
@@ -461,6 +463,12 @@ class Zero3Engine:
                 g.collect_grads()
             accumulate = g.grad_ready
             gf = g.grad_full
+            if self.sign_before_reduce and g.world > 1:
+                # majority-vote sign SGD: each rank votes with the sign of its micro-batch gradient
+                # (exact sums over sequence-parallel ranks come first)
+                if self.sp_sync_pg is not None and not getattr(g, "is_expert", False):
+                    dist.all_reduce(gf, group=self.sp_sync_pg)
+                gf.sign_()
             if self.ps.tp_size > 1 and self.ps.group("tp") is not None and g.world > 1:
                 # (with a shard group of one the gradients accumulate in place over micro-batches:
                 # their sum over the tensor-parallel group is taken once, in finish_grad_sync)
@@ -516,10 +524,12 @@ class Zero3Engine:
                             dist.all_reduce(g.grad_shard[a:b], group=self.ps.group("tp"))
                 if g.replicate_pg is not None and g.replicate_world > 1:
                     dist.all_reduce(g.grad_shard, group=g.replicate_pg)
-                if self.sp_sync_pg is not None and not getattr(g, "is_expert", False):
+                if self.sp_sync_pg is not None and not getattr(g, "is_expert", False) and not \
+                        (self.sign_before_reduce and g.world > 1):
                     dist.all_reduce(g.grad_shard, group=self.sp_sync_pg)
 
     def zero_grad(self) -> None:
+        self.micro_batches = 0
         if self.symm is not None:
             # parameter shards were rewritten by the optimizer: no peer may read them earlier
             self.symm.step_barrier(torch.cuda.current_stream())
@@ -677,6 +687,7 @@ class Zero3Engine:
         """One micro-batch.  Returns ``grad_scale * sum(token CE)`` (detached).  Gradients are
         accumulated into the fp32 shards; call ``finish_grad_sync`` after the last micro-batch."""
         model = self.model
+        self.micro_batches += 1
         root, layers = self._units_by_role()
         self.gather(root)
         self.wait_gather(root)
