@@ -122,10 +122,13 @@ def test_rest_contract_dummy_backend(tmp_path):
         assert c.get("/api/v1/session_info").json()["sessions"] == []
         assert c.post("/api/v1/optim_step", json={"model_id": mid}).status_code == 404
         # inference endpoints and sleep / wake
-        c.post("/add_inference_endpoint", json={"url": "http://e1:30000", "world_size": 2})
+        assert c.post("/add_inference_endpoint", json={"url": "http://169.254.169.254:80"}).status_code == 422
+        assert c.post("/add_inference_endpoint", json={"url": "ftp://127.0.0.1:21"}).status_code == 422
+        assert c.post("/api/v1/create_model", json={"model_id": "../escape"}).status_code == 422
+        c.post("/add_inference_endpoint", json={"url": "http://127.0.0.1:30000", "world_size": 2})
         assert c.get("/list_inference_endpoints").json()["endpoints"][0]["world_size"] == 2
-        assert c.post("/api/v1/create_sampling_session", json={}).json()["endpoint"] == "http://e1:30000"
-        assert c.post("/remove_inference_endpoint", json={"url": "http://e1:30000"}).status_code == 200
+        assert c.post("/api/v1/create_sampling_session", json={}).json()["endpoint"] == "http://127.0.0.1:30000"
+        assert c.post("/remove_inference_endpoint", json={"url": "http://127.0.0.1:30000"}).status_code == 200
         assert c.post("/api/v1/set_sync_quantization", json={"format": "fp8"}).json()["format"] == "fp8"
         assert c.post("/sleep").json()["asleep"] and c.get("/health").json()["asleep"]
         assert not c.post("/wake_up").json()["asleep"]

@@ -1,0 +1,95 @@
+"""Server support modules: security boundaries, session specs, side payload store."""
+import os
+
+import pytest
+import torch
+
+
+def test_identifiers_and_confined_paths(tmp_path):
+    from xorl_b200.server.security import artifact_path, confine_path, validate_identifier
+    assert validate_identifier("run-01.step_5") == "run-01.step_5"
+    for bad in ("", "..", "../x", "a/b", ".hidden", "x" * 200, "a b"):
+        with pytest.raises(ValueError):
+            validate_identifier(bad)
+    root = tmp_path / "out"
+    (root / "ckpt").mkdir(parents=True)
+    assert confine_path(root, "ckpt/a.pt") == (root / "ckpt" / "a.pt").resolve()
+    for bad in ("../secret", "/etc/passwd", "ckpt/../../x"):
+        with pytest.raises(ValueError):
+            confine_path(root, bad)
+    os.symlink("/etc", root / "link")
+    with pytest.raises(ValueError):
+        confine_path(root, "link/passwd")
+    with pytest.raises(FileNotFoundError):
+        confine_path(root, "ckpt/missing", must_exist=True)
+    with pytest.raises(ValueError):
+        artifact_path("  ", root=root)
+    assert artifact_path("ckpt", root=root, must_exist=True).name == "ckpt"
+
+
+def test_outbound_endpoints(monkeypatch):
+    from xorl_b200.server.security import ALLOWLIST_ENV, endpoint_url, validate_endpoint
+    monkeypatch.delenv(ALLOWLIST_ENV, raising=False)
+    assert validate_endpoint("127.0.0.1", 30000) == ("127.0.0.1", 30000)
+    assert endpoint_url("127.0.0.1", "8000", "/health", require_allowlist=True) == "http://127.0.0.1:8000/health"
+    assert endpoint_url("::1", 8000, "/health") == "http://[::1]:8000/health"
+    for host, port in (("169.254.169.254", 80), ("0.0.0.0", 80), ("224.0.0.1", 80), ("a/b", 80), ("h@x", 80),
+                       ("10.0.0.1", 0), ("10.0.0.1", 70000), ("bad host", 80)):
+        with pytest.raises(ValueError):
+            validate_endpoint(host, port)
+    with pytest.raises(ValueError):
+        validate_endpoint("10.1.2.3", 8000, require_allowlist=True)          # no allow-list configured
+    monkeypatch.setenv(ALLOWLIST_ENV, "10.1.0.0/16, engine.internal")
+    assert validate_endpoint("10.1.2.3", 8000, require_allowlist=True) == ("10.1.2.3", 8000)
+    with pytest.raises(ValueError):
+        validate_endpoint("10.2.0.1", 8000, require_allowlist=True)
+    with pytest.raises(ValueError):
+        endpoint_url("127.0.0.1", 80, "/x?y=1")
+
+
+def test_session_spec_roundtrip(tmp_path):
+    from xorl_b200.server.session_spec import (normalize_session_spec, optimizer_build_kwargs, read_session_spec,
+                                               write_session_spec)
+    defaults = dict(default_rank=16, default_alpha=32, max_rank=64, server_targets=["qkv_proj", "o_proj"])
+    spec = normalize_session_spec(base_model="Qwen/Qwen3-8B", lora={"r": 8, "lora_alpha": 16, "target_modules": ["o_proj"]},
+                                  optimizer={"type": "AdamW", "lr": 3e-5, "betas": [0.9, 0.99]}, lora_defaults=defaults)
+    assert spec["lora"] == {"rank": 8, "alpha": 16.0, "target_modules": ["o_proj"], "dropout": 0.0}
+    assert spec["optimizer"]["type"] == "adamw" and spec["optimizer"]["eps"] == 1e-12
+    kw = optimizer_build_kwargs(spec["optimizer"])
+    assert kw["lr"] == 3e-5 and kw["betas"] == (0.9, 0.99) and kw["optimizer_type"] == "adamw"
+    for bad in (dict(lora={"r": 128}), dict(lora={"rank": 8, "bogus": 1}), dict(lora={"target_modules": ["lm_head"]}),
+                dict(optimizer={"type": "lion"}), dict(optimizer={"lr": float("nan")}), dict(optimizer={"betas": [1.0, 0.9]}),
+                dict(optimizer={"momentum": 0.9})):
+        with pytest.raises(ValueError):
+            normalize_session_spec(base_model="m", lora=bad.get("lora"), optimizer=bad.get("optimizer"), lora_defaults=defaults)
+    write_session_spec(str(tmp_path / "s"), spec)
+    assert read_session_spec(str(tmp_path / "s")) == spec
+    # an older checkpoint with only the PEFT adapter config
+    old = tmp_path / "old"
+    old.mkdir()
+    (old / "adapter_config.json").write_text('{"r": 4, "lora_alpha": 8, "target_modules": ["qkv_proj"]}')
+    got = read_session_spec(str(old), fallback=spec)
+    assert got["lora"]["rank"] == 4 and got["lora"]["target_modules"] == ["qkv_proj"] and got["optimizer"] == spec["optimizer"]
+    with pytest.raises(FileNotFoundError):
+        read_session_spec(str(tmp_path / "none"))
+
+
+def test_side_payload_store(tmp_path):
+    from xorl_b200.server.side_payloads import FilesystemPayloadStore, PayloadError, is_payload_ref, resolve_refs
+    store = FilesystemPayloadStore(str(tmp_path / "payloads"), ttl_seconds=10.0, max_bytes=1 << 20)
+    routing = torch.randint(0, 128, (300, 4, 8), dtype=torch.int16)
+    ref = store.put(routing)
+    assert is_payload_ref(ref) and ref["nbytes"] > routing.numel() * 2
+    req = {"datum": {"tokens": [1, 2, 3], "routing": ref}, "other": [ref, 5]}
+    out = resolve_refs(req, store)
+    assert torch.equal(out["datum"]["routing"], routing) and torch.equal(out["other"][0], routing) and out["other"][1] == 5
+    with pytest.raises(PayloadError):
+        store.get({**ref, "sha256": "0" * 64})
+    with pytest.raises(PayloadError):
+        store.put(torch.zeros(1 << 20))                                  # over the size limit
+    with pytest.raises(ValueError):
+        store.get({**ref, "key": "../escape"})
+    assert store.sweep(now=os.path.getmtime(tmp_path / "payloads" / (ref["key"] + ".pt")) + 5) == 0
+    assert store.sweep(now=os.path.getmtime(tmp_path / "payloads" / (ref["key"] + ".pt")) + 11) == 1
+    with pytest.raises(PayloadError):
+        store.get(ref)

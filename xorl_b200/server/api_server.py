@@ -22,6 +22,7 @@ from fastapi import Depends, FastAPI, Header, HTTPException
 from . import api_types as T
 from .future_store import FutureStore
 from .orchestrator import Orchestrator, OrchestratorRequest, RequestProcessor, SeqIdAwareFIFOPolicy
+from .security import validate_endpoint, validate_identifier
 from .weight_sync import EndpointManager
 
 
@@ -200,6 +201,10 @@ def create_app(state: ServerState) -> FastAPI:
     @app.post("/api/v1/create_model", dependencies=dep)
     def create_model(req: T.CreateModelRequest):
         mid = req.model_id or f"model-{uuid.uuid4().hex[:8]}"
+        try:
+            validate_identifier(mid, "model_id")          # becomes a directory name under weights/
+        except ValueError as e:
+            raise HTTPException(422, str(e)) from None
         if mid in state.models and mid != "default":
             raise HTTPException(409, f"model {mid} exists")
         state.backend.create_model(mid, base_model=req.base_model, lora_config=req.lora_config)
@@ -265,6 +270,10 @@ def create_app(state: ServerState) -> FastAPI:
     @app.post("/api/v1/save_weights_for_sampler", dependencies=dep)
     def save_for_sampler(req: T.SaveWeightsRequest):
         name = req.path or f"sampler-{int(time.time())}"
+        try:
+            validate_identifier(name, "sampler weights name")
+        except ValueError as e:
+            raise HTTPException(422, str(e)) from None
         d = os.path.join(state.output_dir, "sampler_weights", name)
         return state.enqueue("sync_inference_weights", req.model_id,
                              {"backend": "file", "directory": d, "quantization": state.sync_quantization},
@@ -285,8 +294,11 @@ def create_app(state: ServerState) -> FastAPI:
 
     @app.post("/api/v1/delete_checkpoint", dependencies=dep)
     def delete_checkpoint(req: T.DeleteCheckpointRequest):
-        if "/" in req.name or req.name.startswith("."):
-            raise HTTPException(422, "checkpoint names are plain directory names")
+        try:
+            validate_identifier(req.name, "checkpoint name")
+            validate_identifier(req.model_id, "model_id")
+        except ValueError as e:
+            raise HTTPException(422, str(e)) from None
         p = os.path.join(state.weights_dir(req.model_id), req.name)
         if not os.path.isdir(p):
             raise HTTPException(404, f"no checkpoint {req.name}")
@@ -302,6 +314,18 @@ def create_app(state: ServerState) -> FastAPI:
     # ---- inference engines -------------------------------------------------------------------
     @app.post("/add_inference_endpoint", dependencies=dep)
     def add_endpoint(req: T.InferenceEndpoint):
+        # the trainer will send HTTP requests and weight broadcasts there: refuse malformed,
+        # link-local, multicast and reserved targets (and anything off the allow-list when
+        # XORL_REQUIRE_ENDPOINT_ALLOWLIST=1)
+        from urllib.parse import urlsplit
+        u = urlsplit(req.url if "//" in req.url else "http://" + req.url)
+        try:
+            if u.scheme not in ("http", "https") or not u.hostname:
+                raise ValueError(f"endpoint URL {req.url!r} needs an http(s) host")
+            validate_endpoint(u.hostname, u.port or (443 if u.scheme == "https" else 80),
+                              require_allowlist=os.environ.get("XORL_REQUIRE_ENDPOINT_ALLOWLIST", "0") == "1")
+        except ValueError as e:
+            raise HTTPException(422, str(e)) from None
         return state.endpoints.add(req.url, req.world_size, req.name)
 
     @app.post("/remove_inference_endpoint", dependencies=dep)

@@ -234,12 +234,26 @@ class ModelRunner:
         return {"aborted": True}
 
     def _weights_path(self, model_id: str, path: str) -> str:
+        """``xorl://{model}/{weights|sampler_weights}/{name}``, a bare name, or a path: all resolve
+        below the server's output directory (or ``XORL_SERVER_ARTIFACT_ROOT`` when a path lies
+        elsewhere); symlinked components and ``..`` escapes are refused."""
+        from .security import ARTIFACT_ROOT_ENV, confine_path, validate_identifier
         if path.startswith("xorl://"):
-            mid, kind, name = path[len("xorl://"):].split("/", 2)
+            parts = path[len("xorl://"):].split("/")
+            if len(parts) != 3 or parts[1] not in ("weights", "sampler_weights"):
+                raise ValueError(f"malformed weights URI {path!r}")
+            mid, kind, name = (validate_identifier(x, "weights URI component") for x in parts)
             return os.path.join(self.output_dir, kind, mid, name)
         if os.path.isabs(path) or os.sep in path:
-            return path
-        return os.path.join(self.output_dir, "weights", model_id, path)
+            try:
+                return str(confine_path(self.output_dir, path))
+            except ValueError:
+                root = os.environ.get(ARTIFACT_ROOT_ENV, "").strip()
+                if not root:
+                    raise
+                return str(confine_path(root, path))
+        return os.path.join(self.output_dir, "weights", validate_identifier(model_id, "model_id"),
+                            validate_identifier(path, "checkpoint name"))
 
     def save_weights(self, model_id, path=None, **_):
         self._activate(model_id)
