@@ -453,3 +453,50 @@ def test_gated_delta_rule_matches_dense_formula():
     t = 5                                                     # second token of the second document
     ref = w[:, 3] * x[5] + w[:, 2] * x[4]
     torch.testing.assert_close(y[t], ref)
+
+
+@pytest.mark.parametrize("chunk", [8, 64])
+def test_chunked_gated_delta_rule_matches_recurrence(chunk):
+    """The chunked form against the token recurrence: outputs, every gradient, and the state handed
+    from one half of a document to the other."""
+    from xorl_b200.models.gated_deltanet import gated_delta_rule, gated_delta_rule_chunked
+    torch.manual_seed(1)
+    T, H, dk, dv = 150, 2, 8, 12
+    cu = torch.tensor([0, 37, 38, 130, 141], dtype=torch.int32)      # the last 9 tokens are padding
+    mk = lambda *s: torch.randn(*s, dtype=torch.float64)
+    q = torch.nn.functional.normalize(mk(T, H, dk), dim=-1).requires_grad_()
+    k = torch.nn.functional.normalize(mk(T, H, dk), dim=-1).requires_grad_()
+    v = mk(T, H, dv).requires_grad_()
+    g = (-torch.rand(T, H, dtype=torch.float64)).requires_grad_()
+    beta = torch.rand(T, H, dtype=torch.float64).requires_grad_()
+    ref = gated_delta_rule(q, k, v, g, beta, cu)
+    out = gated_delta_rule_chunked(q, k, v, g, beta, cu, chunk=chunk)
+    torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-5)
+    w = mk(T, H, dv)
+    g_ref = torch.autograd.grad((ref * w).sum(), [q, k, v, g, beta])
+    g_out = torch.autograd.grad((out * w).sum(), [q, k, v, g, beta])
+    for a, b in zip(g_out, g_ref):
+        torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-4)
+    # one document of 92 tokens cut at token 50: the second half started from the first half's state
+    sl = lambda x, a, b: x[a:b].detach()
+    one = torch.tensor([0, 92], dtype=torch.int32)
+    full = gated_delta_rule_chunked(*(sl(x, 38, 130) for x in (q, k, v, g, beta)), one, chunk=chunk)
+    h1, S = gated_delta_rule_chunked(*(sl(x, 38, 88) for x in (q, k, v, g, beta)),
+                                     torch.tensor([0, 50]), chunk=chunk, return_final_state=True)
+    h2 = gated_delta_rule_chunked(*(sl(x, 88, 130) for x in (q, k, v, g, beta)),
+                                  torch.tensor([0, 42]), chunk=chunk, initial_state=S)
+    torch.testing.assert_close(torch.cat([h1, h2]), full, rtol=1e-4, atol=1e-5)
+
+
+def test_causal_conv1d_tensor_form_matches_per_document_convolution():
+    from xorl_b200.models.gated_deltanet import causal_depthwise_conv
+    from xorl_b200.ops.seqmix import causal_conv1d, document_starts
+    torch.manual_seed(2)
+    T, C, K = 40, 16, 4
+    cu = torch.tensor([0, 1, 14, 33], dtype=torch.int32)
+    assert document_starts(cu, T).tolist() == [0] + [1] * 13 + [14] * 19 + list(range(33, 40))
+    x, w, b = torch.randn(T, C), torch.randn(C, K), torch.randn(C)
+    y = causal_conv1d(x, w, b, cu, silu=True)
+    ref = torch.nn.functional.silu(causal_depthwise_conv(x, w, cu) + b)
+    torch.testing.assert_close(y[:33], ref[:33], rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(y[35], torch.nn.functional.silu(w[:, 3] * x[35] + b), rtol=1e-5, atol=1e-5)

@@ -66,6 +66,10 @@ class QLoRALinear(LoraLinear):
             raw = self.qparts[key].view(torch.uint8)
             n = math.prod(pshape) * torch.empty(0, dtype=pdt).element_size()
             parts[key] = raw[:n].view(pdt).reshape(pshape)
+        if self.qparts["packed"].is_cuda and self.fmt in ("nf4", "int4", "nvfp4", "mxfp4") \
+                and self.group % 8 == 0 and math.prod(self.w_shape) % 8 == 0:
+            from ..ops.seqmix import dequant4
+            return dequant4(parts, self.fmt, self.group, self.w_shape)
         dt = torch.bfloat16 if self.qparts["packed"].is_cuda else torch.float32
         return Q.dequantize_weight(parts, self.fmt, self.group, self.w_shape, dt)
 

@@ -1,0 +1,293 @@
+// Small memory-bound kernels of the sequence mixers and of the 4-bit weight codecs.
+//
+// 1. Causal depthwise convolution over a packed batch (GatedDeltaNet q/k/v branches, Mamba2 x/B/C
+//    branch): y[t, c] = act(bias[c] + sum_j w[c, j] * x[t - (K-1) + j, c]), taps that would reach
+//    before the start of token t's document read zero.  Forward, and a backward in three passes
+//    without atomics: dpre = dy * act'(pre) (pre recomputed), dx from dpre with the taps mirrored,
+//    and per-chunk partial sums of dw / dbias that the caller adds up in a fixed order.
+//    Reference behaviour: src/xorl/ops/linear_attention/ops/causal_conv1d_triton.py:24 and
+//    src/xorl/ops/ssm/conv.py (conv followed by SiLU, state reset per document).
+// 2. Dequantisation of 4-bit packed weights (two codes per byte, low nibble first) to bf16:
+//    NF4 and INT4 with fp32 group scales, NVFP4 (e2m1 codes, e4m3 scale per group, fp32 global
+//    scale), MXFP4 (e2m1 codes, e8m0 scale per group).
+//    Reference behaviour: src/xorl/ops/quantize/{nf4,int4,nvfp4,mxfp4}_quantize.py.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_TAPS = 8;
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack_bf16x2(w[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                            pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+}
+
+// pre-activation of 8 channels of token t
+__device__ __forceinline__ void conv_pre(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                         const __nv_bfloat16* __restrict__ w,
+                                         const __nv_bfloat16* __restrict__ bias, int t, int start,
+                                         int c0, int K, float (&acc)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = bias ? __bfloat162float(bias[c0 + i]) : 0.f;
+  for (int j = 0; j < K; ++j) {
+    const int src = t - (K - 1) + j;
+    if (src < start) continue;
+    float xv[8];
+    load8(x + (long long)src * ldx + c0, xv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(w[(c0 + i) * K + j]) * xv[i];
+  }
+}
+
+// mode 0: y = act(pre);  mode 1: y = dy * act'(pre)  (dy read from `aux`)
+template <int MODE>
+__global__ void __launch_bounds__(256)
+conv1d_point_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                    const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
+                    const int* __restrict__ doc_start, const __nv_bfloat16* __restrict__ aux,
+                    long long ldaux, __nv_bfloat16* __restrict__ out, long long ldo, int T, int C,
+                    int K, int silu) {
+  const int vec_per_row = C >> 3;
+  const long long total = (long long)T * vec_per_row;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / vec_per_row);
+    const int c0 = (int)(idx % vec_per_row) * 8;
+    float acc[8];
+    conv_pre(x, ldx, w, bias, t, doc_start[t], c0, K, acc);
+    float o[8];
+    if (MODE == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = silu ? acc[i] * sigmoid_f(acc[i]) : acc[i];
+    } else {
+      float d[8];
+      load8(aux + (long long)t * ldaux + c0, d);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float s = sigmoid_f(acc[i]);
+        o[i] = silu ? d[i] * s * (1.f + acc[i] * (1.f - s)) : d[i];
+      }
+    }
+    store8(out + (long long)t * ldo + c0, o);
+  }
+}
+
+// dx[t, c] = sum_j w[c, j] * dpre[t + (K-1) - j, c] over the tokens of the same document
+__global__ void __launch_bounds__(256)
+conv1d_dx_kernel(const __nv_bfloat16* __restrict__ dpre, long long ldd,
+                 const __nv_bfloat16* __restrict__ w, const int* __restrict__ doc_start,
+                 __nv_bfloat16* __restrict__ dx, long long ldx, int T, int C, int K) {
+  const int vec_per_row = C >> 3;
+  const long long total = (long long)T * vec_per_row;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / vec_per_row);
+    const int c0 = (int)(idx % vec_per_row) * 8;
+    const int start = doc_start[t];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < K; ++j) {
+      const int dst = t + (K - 1) - j;                 // the output token that read x[t] with tap j
+      if (dst >= T || doc_start[dst] != start) continue;
+      float dv[8];
+      load8(dpre + (long long)dst * ldd + c0, dv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += __bfloat162float(w[(c0 + i) * K + j]) * dv[i];
+    }
+    store8(dx + (long long)t * ldx + c0, acc);
+  }
+}
+
+// partial[chunk, c, 0..K-1] = sum_t dpre[t, c] * x[t - (K-1) + j, c];  partial[chunk, c, K] = sum_t dpre[t, c]
+// One thread owns two adjacent channels and walks the tokens of its chunk with a register window of
+// the last K inputs.
+__global__ void __launch_bounds__(128)
+conv1d_dw_kernel(const __nv_bfloat16* __restrict__ dpre, long long ldd,
+                 const __nv_bfloat16* __restrict__ x, long long ldx,
+                 const int* __restrict__ doc_start, float* __restrict__ partial, int T, int C, int K,
+                 int chunk_len) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= C) return;
+  const int t0 = blockIdx.y * chunk_len;
+  const int t1 = min(T, t0 + chunk_len);
+  float win0[MAX_TAPS], win1[MAX_TAPS], a0[MAX_TAPS + 1], a1[MAX_TAPS + 1];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) { win0[j] = win1[j] = 0.f; }
+#pragma unroll
+  for (int j = 0; j <= MAX_TAPS; ++j) { a0[j] = a1[j] = 0.f; }
+  // window slot j holds x[t - (K-1) + j]; preload the K-1 tokens before the chunk
+  for (int j = 1; j < K; ++j) {
+    const int src = t0 - K + j;
+    if (src >= 0) {
+      const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + (long long)src * ldx + c));
+      win0[j] = f.x;
+      win1[j] = f.y;
+    }
+  }
+  for (int t = t0; t < t1; ++t) {
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j) {
+      if (j < K - 1) { win0[j] = win0[j + 1]; win1[j] = win1[j + 1]; }
+    }
+    const float2 xc = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + (long long)t * ldx + c));
+    const float2 d = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dpre + (long long)t * ldd + c));
+    const int start = doc_start[t];
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS; ++j) {
+      if (j == K - 1) { win0[j] = xc.x; win1[j] = xc.y; }
+      if (j < K && t - (K - 1) + j >= start) {
+        a0[j] += d.x * win0[j];
+        a1[j] += d.y * win1[j];
+      }
+    }
+    a0[MAX_TAPS] += d.x;
+    a1[MAX_TAPS] += d.y;
+  }
+  float* p0 = partial + ((long long)blockIdx.y * C + c) * (K + 1);
+  float* p1 = p0 + (K + 1);
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) {
+    if (j < K) { p0[j] = a0[j]; p1[j] = a1[j]; }
+  }
+  p0[K] = a0[MAX_TAPS];
+  p1[K] = a1[MAX_TAPS];
+}
+
+// ---------------------------------------------------------------------------------------------
+__constant__ float NF4_TABLE[16] = {
+    -1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+    -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+    0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+    0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+__constant__ float E2M1_TABLE[16] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f,
+                                     -0.f, -0.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+
+enum { FMT_NF4 = 0, FMT_INT4 = 1, FMT_NVFP4 = 2, FMT_MXFP4 = 3 };
+
+// One thread decodes 8 consecutive elements (4 packed bytes); group sizes are multiples of 8, so the
+// eight share one scale.
+template <int FMT>
+__global__ void __launch_bounds__(256)
+dequant4_kernel(const uint32_t* __restrict__ packed, const void* __restrict__ scale,
+                const float* __restrict__ global_scale, __nv_bfloat16* __restrict__ out,
+                long long n_vec, int group) {
+  const float gs = (FMT == FMT_NVFP4) ? *global_scale : 1.f;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec;
+       v += (long long)gridDim.x * blockDim.x) {
+    const uint32_t bits = packed[v];
+    const long long g = (v * 8) / group;
+    float s;
+    if (FMT == FMT_NF4 || FMT == FMT_INT4) {
+      s = reinterpret_cast<const float*>(scale)[g];
+    } else if (FMT == FMT_NVFP4) {
+      const __nv_fp8_storage_t b = reinterpret_cast<const __nv_fp8_storage_t*>(scale)[g];
+      s = __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));
+    } else {
+      s = exp2f((float)reinterpret_cast<const uint8_t*>(scale)[g] - 127.f);
+    }
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t code = (bits >> (4 * i)) & 0xF;
+      float val;
+      if (FMT == FMT_NF4) val = NF4_TABLE[code];
+      else if (FMT == FMT_INT4) val = (float)code - 8.f;
+      else val = E2M1_TABLE[code];
+      o[i] = (FMT == FMT_NVFP4) ? (val * s) * gs : val * s;
+    }
+    store8(out + v * 8, o);
+  }
+}
+
+inline int grid_for(long long work_items, int threads) {
+  long long g = (work_items + threads - 1) / threads;
+  const long long cap = (long long)xb_sm_count() * 16;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// x [T, C] (row stride ldx), w [C, K], bias [C] or null, doc_start [T] (index of the first token of
+// each token's document) -> y [T, C].  C % 8 == 0, row strides % 8 == 0, K <= 8.
+XB_API int xb_causal_conv1d_fwd(const void* x, long long ldx, const void* w, const void* bias,
+                                const int* doc_start, void* y, long long ldy, int T, int C, int K,
+                                int silu, void* stream) {
+  if (C % 8 || ldx % 8 || ldy % 8 || K < 1 || K > MAX_TAPS || !aligned16(x) || !aligned16(y))
+    return -1;
+  if (T <= 0) return 0;
+  conv1d_point_kernel<0><<<grid_for((long long)T * (C / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, doc_start,
+      nullptr, 0, (__nv_bfloat16*)y, ldy, T, C, K, silu);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Number of token chunks (rows of `partial`) the backward writes for T tokens.
+XB_API int xb_causal_conv1d_bwd_chunks(int T) {
+  const int c = (T + 255) / 256;
+  return c < 1 ? 1 : (c > 64 ? 64 : c);
+}
+
+// dy, x [T, C]; dpre [T, C] bf16 workspace (may alias nothing else); dx [T, C];
+// partial [chunks, C, K + 1] fp32 (taps, then the bias column).
+XB_API int xb_causal_conv1d_bwd(const void* dy, long long lddy, const void* x, long long ldx,
+                                const void* w, const void* bias, const int* doc_start, void* dpre,
+                                void* dx, long long lddx, float* partial, int T, int C, int K,
+                                int silu, void* stream) {
+  if (C % 8 || ldx % 8 || lddy % 8 || lddx % 8 || K < 1 || K > MAX_TAPS || !aligned16(x) ||
+      !aligned16(dy) || !aligned16(dx) || !aligned16(dpre))
+    return -1;
+  if (T <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = grid_for((long long)T * (C / 8), 256);
+  conv1d_point_kernel<1><<<grid, 256, 0, st>>>(
+      (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, doc_start,
+      (const __nv_bfloat16*)dy, lddy, (__nv_bfloat16*)dpre, C, T, C, K, silu);
+  conv1d_dx_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dpre, C, (const __nv_bfloat16*)w,
+                                         doc_start, (__nv_bfloat16*)dx, lddx, T, C, K);
+  const int chunks = xb_causal_conv1d_bwd_chunks(T);
+  const int chunk_len = (T + chunks - 1) / chunks;
+  dim3 g((C / 2 + 127) / 128, chunks);
+  conv1d_dw_kernel<<<g, 128, 0, st>>>((const __nv_bfloat16*)dpre, C, (const __nv_bfloat16*)x, ldx,
+                                      doc_start, partial, T, C, K, chunk_len);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// packed: n / 2 bytes; scale: n / group entries (fp32 for nf4 / int4, one byte for nvfp4 / mxfp4);
+// out: n bf16.  n % 8 == 0, group % 8 == 0.
+XB_API int xb_dequant4(const void* packed, const void* scale, const float* global_scale, void* out,
+                       long long n, int group, int fmt, void* stream) {
+  if (n % 8 || group % 8 || group <= 0 || !aligned16(out) ||
+      (reinterpret_cast<uintptr_t>(packed) & 3))
+    return -1;
+  if (fmt == FMT_NVFP4 && !global_scale) return -1;
+  if (n <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long nv = n / 8;
+  const int grid = grid_for(nv, 256);
+  const uint32_t* p = (const uint32_t*)packed;
+  __nv_bfloat16* o = (__nv_bfloat16*)out;
+  switch (fmt) {
+    case FMT_NF4: dequant4_kernel<FMT_NF4><<<grid, 256, 0, st>>>(p, scale, global_scale, o, nv, group); break;
+    case FMT_INT4: dequant4_kernel<FMT_INT4><<<grid, 256, 0, st>>>(p, scale, global_scale, o, nv, group); break;
+    case FMT_NVFP4: dequant4_kernel<FMT_NVFP4><<<grid, 256, 0, st>>>(p, scale, global_scale, o, nv, group); break;
+    case FMT_MXFP4: dequant4_kernel<FMT_MXFP4><<<grid, 256, 0, st>>>(p, scale, global_scale, o, nv, group); break;
+    default: return -1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

@@ -9,19 +9,28 @@ d_k^-1/2), beta = sigmoid(b x), g = -exp(A_log) * softplus(a x + dt_bias), and t
 RMS-normalised per head and gated by SiLU(z) before the output projection
 (src/xorl/ops/linear_attention/layers/gated_deltanet.py:46-470).
 
-This is a plain PyTorch implementation: the recurrence runs token by token inside every document of
-the packed batch (state reset at document boundaries, convolution not crossing them), vectorised
-over heads.  It is exact and differentiable, and meant for functional coverage and small-scale
-runs; the reference's chunked Triton kernels have no CUDA counterpart here yet."""
+``gated_delta_rule`` is the token-by-token recurrence (the definition, used as the test oracle).
+``gated_delta_rule_chunked`` evaluates the same recurrence in chunks of 64 tokens: inside a chunk
+the deltas u_t = beta_t (v_t - (exp(g_t) S_{t-1})^T k_t) solve a unit lower-triangular system
+(I + diag(beta) A) U = diag(beta) (V - diag(gamma) K S_0), A[i, j] = gamma_i / gamma_j k_i.k_j for
+j < i and gamma the running decay product, so every chunk costs a handful of batched matrix
+products and only one [d_k, d_v] state per head crosses chunk borders (the chunked formulation of
+src/xorl/ops/linear_attention/ops/gated_delta_rule/chunk.py).  Documents of the packed batch are cut
+into chunks separately, so neither the state nor the convolution crosses a document start.  The
+short convolutions run on the CUDA kernel of ``ops/seqmix.py`` when the activations are bf16 on a
+GPU."""
 from __future__ import annotations
 
 import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ..ops.seqmix import causal_conv1d
 from .config import ModelConfig
 from .context import StepContext
 from .layers import Linear
+
+CHUNK = 64
 
 
 def causal_depthwise_conv(x: torch.Tensor, weight: torch.Tensor, cu_seqlens) -> torch.Tensor:
@@ -59,6 +68,76 @@ def gated_delta_rule(q, k, v, g, beta, cu_seqlens):
     return torch.stack(out, 0).to(v.dtype)
 
 
+def _chunk_index(cu, T: int, chunk: int, device):
+    """Rows of token indices, one row per chunk of one document (``-1`` pads), and a flag per row
+    that is 1 where the row opens a document."""
+    rows, first = [], []
+    for b in range(len(cu) - 1):
+        s, e = cu[b], cu[b + 1]
+        for c0 in range(s, e, chunk):
+            c1 = min(e, c0 + chunk)
+            rows.append(list(range(c0, c1)) + [-1] * (chunk - (c1 - c0)))
+            first.append(1.0 if c0 == s else 0.0)
+    if not rows:
+        rows, first = [[-1] * chunk], [1.0]
+    return (torch.tensor(rows, dtype=torch.long, device=device),
+            torch.tensor(first, dtype=torch.float32, device=device))
+
+
+def gated_delta_rule_chunked(q, k, v, g, beta, cu_seqlens, chunk: int = CHUNK, initial_state=None,
+                             return_final_state: bool = False):
+    """Same contract as ``gated_delta_rule``.  ``initial_state`` [H, dk, dv] seeds the first
+    document; with ``return_final_state`` the state after the last document's last token is
+    returned as well (both are what a context-parallel rank exchanges with its neighbours)."""
+    T, H, dk = q.shape
+    dv = v.shape[-1]
+    cu = cu_seqlens.tolist()
+    idx, first = _chunk_index(cu, T, chunk, q.device)
+    N = idx.shape[0]
+    valid = (idx >= 0)
+    gi = idx.clamp_min(0)
+    vm = valid.view(N, chunk, 1, 1).float()
+
+    def take(x):                                           # [T, H, d] -> [N, H, C, d], pads zeroed
+        return (x.float()[gi] * vm).permute(0, 2, 1, 3)
+
+    Q, K, V = take(q), take(k), take(v)
+    gg = (g.float()[gi] * vm[..., 0]).permute(0, 2, 1)                     # [N, H, C]
+    bb = (beta.float()[gi] * vm[..., 0]).permute(0, 2, 1)
+    G = gg.cumsum(-1)                                                       # log gamma
+    tri = torch.ones(chunk, chunk, dtype=torch.bool, device=q.device).tril()
+    diff = (G.unsqueeze(-1) - G.unsqueeze(-2)).masked_fill(~tri, 0.0)
+    decay = torch.exp(diff) * tri                                           # gamma_i / gamma_j, j <= i
+    gamma = torch.exp(G)                                                    # [N, H, C]
+    KK = K @ K.transpose(-1, -2)
+    strict = torch.ones(chunk, chunk, dtype=torch.bool, device=q.device).tril(-1)
+    L = bb.unsqueeze(-1) * (decay * KK) * strict                            # diag(beta) A
+    eye = torch.eye(chunk, device=q.device)
+    rhs = torch.cat([bb.unsqueeze(-1) * V, bb.unsqueeze(-1) * gamma.unsqueeze(-1) * K], dim=-1)
+    sol = torch.linalg.solve_triangular(eye + L, rhs, upper=False, unitriangular=True)
+    TV, W = sol[..., :dv], sol[..., dv:]                                    # [N,H,C,dv], [N,H,C,dk]
+    Aqk = decay * (Q @ K.transpose(-1, -2))                                 # [N,H,C,C]
+    Qg = gamma.unsqueeze(-1) * Q
+    g_end = gamma[..., -1]                                                  # [N, H]
+    Kdec = torch.exp(G[..., -1:] - G).unsqueeze(-1) * K                     # gamma_C / gamma_j k_j
+
+    S = torch.zeros(H, dk, dv, dtype=torch.float32, device=q.device)
+    outs = []
+    for n in range(N):
+        if n == 0 and initial_state is not None:
+            S = initial_state.float()
+        elif first[n] > 0:
+            S = torch.zeros_like(S)
+        U = TV[n] - W[n] @ S
+        outs.append(Qg[n] @ S + Aqk[n] @ U)
+        S = g_end[n].view(H, 1, 1) * S + Kdec[n].transpose(-1, -2) @ U
+    O = torch.stack(outs, 0).permute(0, 2, 1, 3)                            # [N, C, H, dv]
+    out = torch.zeros(T, H, dv, dtype=torch.float32, device=q.device)
+    out = out.index_put((idx[valid],), O[valid])
+    out = out.to(v.dtype)
+    return (out, S) if return_final_state else out
+
+
 class GatedDeltaNet(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, dtype=None, device=None):
         super().__init__()
@@ -88,9 +167,9 @@ class GatedDeltaNet(nn.Module):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T = x.shape[0]
         cu = ctx.cu_seqlens
-        q = F.silu(causal_depthwise_conv(self.q_proj(x), self.q_conv1d, cu))
-        k = F.silu(causal_depthwise_conv(self.k_proj(x), self.k_conv1d, cu))
-        v = F.silu(causal_depthwise_conv(self.v_proj(x), self.v_conv1d, cu))
+        q = causal_conv1d(self.q_proj(x), self.q_conv1d, None, cu, silu=True)
+        k = causal_conv1d(self.k_proj(x), self.k_conv1d, None, cu, silu=True)
+        v = causal_conv1d(self.v_proj(x), self.v_conv1d, None, cu, silu=True)
         beta = torch.sigmoid(self.b_proj(x).float())
         g = -torch.exp(self.A_log.float()) * F.softplus(self.a_proj(x).float() + self.dt_bias.float())
         q = F.normalize(q.view(T, self.Hk, self.dk).float(), dim=-1) * self.dk ** -0.5
@@ -98,7 +177,7 @@ class GatedDeltaNet(nn.Module):
         if self.Hv > self.Hk:
             rep = self.Hv // self.Hk
             q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
-        o = gated_delta_rule(q, k, v.view(T, self.Hv, self.dv), g, beta, cu).float()
+        o = gated_delta_rule_chunked(q, k, v.view(T, self.Hv, self.dv), g, beta, cu).float()
         z = self.g_proj(x).view(T, self.Hv, self.dv).float()
         o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.eps) * self.o_norm_weight.float()
         o = (o * F.silu(z)).to(x.dtype)

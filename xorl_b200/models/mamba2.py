@@ -28,7 +28,7 @@ from torch import nn
 
 from .config import ModelConfig
 from .context import StepContext
-from .gated_deltanet import causal_depthwise_conv
+from ..ops.seqmix import causal_conv1d
 from .layers import Linear
 
 
@@ -151,10 +151,7 @@ class Mamba2Mixer(nn.Module):
         T = h.shape[0]
         proj = self.in_proj(h)
         gate, xbc, dt = proj.split([self.d_inner, self.conv_dim, self.H], dim=-1)
-        xbc = causal_depthwise_conv(xbc.contiguous(), self.conv1d_weight, ctx.cu_seqlens)
-        if self.conv1d_bias is not None:
-            xbc = xbc + self.conv1d_bias
-        xbc = F.silu(xbc)
+        xbc = causal_conv1d(xbc.contiguous(), self.conv1d_weight, self.conv1d_bias, ctx.cu_seqlens, silu=True)
         x, B, C = xbc.split([self.d_inner, self.G * self.N, self.G * self.N], dim=-1)
         dt = torch.clamp(F.softplus(dt.float() + self.dt_bias.float()), self.dt_limit[0], self.dt_limit[1])
         A = -torch.exp(self.A_log.float())

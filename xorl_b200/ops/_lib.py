@@ -80,6 +80,10 @@ _SIGNATURES = {
     "xb_attn_bwd_ex": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, I, I, I, I, I, I, I, F, I, I, P],
     "xb_attn_fwd": [P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, F, I, P],
     "xb_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, I, I, I, I, I, I, F, I, P],
+    "xb_causal_conv1d_fwd": [P, L, P, P, P, P, L, I, I, I, I, P],
+    "xb_causal_conv1d_bwd_chunks": [I],
+    "xb_causal_conv1d_bwd": [P, L, P, L, P, P, P, P, P, L, P, I, I, I, I, P],
+    "xb_dequant4": [P, P, P, P, L, I, I, P],
 }
 
 
