@@ -59,6 +59,10 @@ class FlatParamGroup:
         self.numel = off
         self.padded = _round_up(max(off, 1), world * ALIGN)
         self.shard_numel = self.padded // world
+        # element ranges of the flat layout that belong to no parameter (alignment gaps, tail)
+        ends = [o + math.prod(s) for o, s in zip(self.offsets, self.shapes)]
+        starts = self.offsets[1:] + [self.padded]
+        self.gaps = [(e, n) for e, n in zip(ends, starts) if n > e] if self.offsets else [(0, self.padded)]
         # persistent sharded state
         self.master: torch.Tensor = None      # fp32 [shard]
         self.shard_lp: torch.Tensor = None    # compute dtype [shard] (aliases master when fp32)
@@ -88,6 +92,13 @@ class FlatParamGroup:
         empty = torch.empty(0, device=self.device, dtype=self.compute_dtype)
         for _, p in self.named_params:
             p.data = empty
+
+    def zero_grad_gaps(self) -> None:
+        """A gathered gradient buffer comes from a pool (or a ring shared with other groups) and
+        only the parameter slices are written during backward: what lies between them would be
+        summed into the shard by the reduce-scatter and counted in the gradient norm."""
+        for a, b in self.gaps:
+            self.grad_full[a:b].zero_()
 
     def attach_grad_views(self, fresh: bool = True) -> None:
         for (_, p), v in zip(self.named_params, self.param_views(self.grad_full)):
@@ -450,9 +461,11 @@ class Zero3Engine:
                 g.attach_grad_views(fresh=not g.grad_ready)
             elif self.symm is not None and self.symm.can_reduce(g):
                 g.grad_full = self.symm.take_grad_buffer(g)
+                g.zero_grad_gaps()
                 g.attach_grad_views()
             else:
                 g.grad_full = self._take_full(g.padded, self.compute_dtype)
+                g.zero_grad_gaps()
                 g.attach_grad_views()
 
     def _reduce_unit_grads(self, unit: ZeroUnit, collected: bool = False) -> None:
