@@ -24,6 +24,7 @@ from ..models import build_model_config, build_model
 from ..optim import build_lr_scheduler, build_optimizer
 from ..parallel.state import get_parallel_state, init_parallel_state, process_group_timeout
 from ..parallel.zero import Zero3Engine
+from ..utils.diagnostics import nvtx_range
 from ..utils.helper import CudaTimer, EnvironMeter, create_profiler, set_seed
 from ..utils.logging import get_logger, info_rank0
 
@@ -181,6 +182,18 @@ class Trainer:
                                             t.profile_record_shapes, t.profile_profile_memory,
                                             t.profile_with_stack, self.ps.rank)
             self.profiler.start()
+        from ..utils.diagnostics import MemoryHistory, MetricsSink, RankWatchdog, nonfinite_scan_enabled
+        self.memhist = MemoryHistory(self.ps.rank)
+        self.sink = MetricsSink(t, self.ps.rank)
+        self.scan_nonfinite = nonfinite_scan_enabled()
+        self.watchdog = None
+        if self.ps.world_size > 1 and dist.is_initialized() \
+                and os.environ.get("XORL_RANK_WATCHDOG", "1") not in ("0", "false"):
+            store = dist.distributed_c10d._get_default_store()
+            self.watchdog = RankWatchdog(
+                store, self.ps.rank, self.ps.world_size,
+                interval_s=float(os.environ.get("XORL_RANK_WATCHDOG_INTERVAL_S", "5")),
+                timeout_s=float(os.environ.get("XORL_RANK_WATCHDOG_TIMEOUT_S", "300"))).start()
         from ..checkpoint import build_checkpointer
         self.checkpointer = build_checkpointer(self)
 
@@ -243,6 +256,12 @@ class Trainer:
                 extra={"local_cu_seqlens": mb.get("local_cu_seqlens")})
             total = loss if total is None else total + loss
         self.engine.finish_grad_sync()
+        if self.scan_nonfinite:
+            from ..utils.diagnostics import nonfinite_gradient_report
+            bad = nonfinite_gradient_report(self.engine)
+            if bad:
+                logger.warning("step %d rank %d: non-finite gradients in %s", self.global_step + 1,
+                               self.ps.rank, ", ".join(bad[:20]))
         norm, coef = self.engine.grad_norm_and_clip_coef(t.max_grad_norm)
         self.optimizer.step(clip_coef=coef if t.max_grad_norm > 0 else None)
         self.lr_scheduler.step()
@@ -298,9 +317,19 @@ class Trainer:
                     break
                 if self.device.type == "cuda":
                     torch.cuda.synchronize()
+                if self.watchdog is not None:
+                    self.watchdog.check()           # a dead peer is noticed before the next launch
                 t0 = time.time()
-                out = self.train_step(micro_batches)
-                loss = float(out["loss"])           # device -> host read of the step result
+                try:
+                    with nvtx_range("train_step"):
+                        out = self.train_step(micro_batches)
+                    loss = float(out["loss"])       # device -> host read of the step result
+                except BaseException as e:
+                    if isinstance(e, torch.OutOfMemoryError):
+                        self.memhist.on_oom()
+                    if self.watchdog is not None:
+                        self.watchdog.report_failure(f"{type(e).__name__}: {e}")
+                    raise
                 if self.device.type == "cuda":
                     torch.cuda.synchronize()
                 dt = time.time() - t0
@@ -310,6 +339,8 @@ class Trainer:
                 self.loss_history.append(loss)
                 self.metrics_history.append(metrics)
                 self._maybe_log(metrics)
+                self.sink.log(metrics, self.global_step)
+                self.memhist.after_step(self.global_step)
                 if self.profiler is not None:
                     self.profiler.step()
                 self._maybe_save_checkpoint()
@@ -343,6 +374,10 @@ class Trainer:
         t = self.args.train
         if self.profiler is not None:
             self.profiler.stop()
+        if self.watchdog is not None:
+            self.watchdog.stop()
+        self.sink.close()
+        self.memhist.close()
         result = {"loss_history": self.loss_history, "global_step": self.global_step,
                   "metrics": self.metrics_history[-1] if self.metrics_history else {}}
         if self.ps.tp_sequence_parallel:
