@@ -112,6 +112,140 @@ conv1d_dx_kernel(const __nv_bfloat16* __restrict__ dpre, long long ldd,
   }
 }
 
+// ---- streaming forms for K = 4 (the tap count of both mixers) ---------------------------------
+// One thread owns 8 channels and walks a chunk of tokens: weights and the last three input rows
+// stay in registers (packed bf16, unpacked at use, which keeps the kernel near 64 registers and
+// the SM well occupied), so every row of x is read once, and four rows are requested before the
+// first is used.
+constexpr int STREAM_THREADS = 128;
+constexpr int STREAM_CHUNK = 128;
+
+__device__ __forceinline__ uint32_t lane32(const uint4& v, int j) {
+  return j == 0 ? v.x : (j == 1 ? v.y : (j == 2 ? v.z : v.w));
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(STREAM_THREADS, 5)
+conv1d_stream4_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                      const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
+                      const int* __restrict__ doc_start, const __nv_bfloat16* __restrict__ aux,
+                      long long ldaux, __nv_bfloat16* __restrict__ out, long long ldo, int T, int C,
+                      int silu) {
+  const int c0 = (blockIdx.x * STREAM_THREADS + threadIdx.x) * 8;
+  if (c0 >= C) return;
+  const int t0 = blockIdx.y * STREAM_CHUNK;
+  const int t1 = min(T, t0 + STREAM_CHUNK);
+  uint2 wq[8];                                        // the four taps of channel c0 + i
+#pragma unroll
+  for (int i = 0; i < 8; ++i) wq[i] = *reinterpret_cast<const uint2*>(w + (long long)(c0 + i) * 4);
+  uint4 bq = make_uint4(0u, 0u, 0u, 0u);
+  if (bias) bq = *reinterpret_cast<const uint4*>(bias + c0);
+  uint4 h0 = make_uint4(0u, 0u, 0u, 0u), h1 = h0, h2 = h0;     // x[t-3], x[t-2], x[t-1]
+  if (t0 - 3 >= 0) h0 = *reinterpret_cast<const uint4*>(x + (long long)(t0 - 3) * ldx + c0);
+  if (t0 - 2 >= 0) h1 = *reinterpret_cast<const uint4*>(x + (long long)(t0 - 2) * ldx + c0);
+  if (t0 - 1 >= 0) h2 = *reinterpret_cast<const uint4*>(x + (long long)(t0 - 1) * ldx + c0);
+  for (int tb = t0; tb < t1; tb += 4) {
+    uint4 xr[4], dr[4];
+    int st[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int t = min(tb + u, t1 - 1);
+      xr[u] = *reinterpret_cast<const uint4*>(x + (long long)t * ldx + c0);
+      if (MODE == 1) dr[u] = *reinterpret_cast<const uint4*>(aux + (long long)t * ldaux + c0);
+      st[u] = doc_start[t];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int t = tb + u;
+      if (t < t1) {
+        const bool m1 = t - 1 >= st[u], m2 = t - 2 >= st[u], m3 = t - 3 >= st[u];
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 xc = unpack_bf16x2(lane32(xr[u], j));
+          const float2 a1 = unpack_bf16x2(m1 ? lane32(h2, j) : 0u);
+          const float2 a2 = unpack_bf16x2(m2 ? lane32(h1, j) : 0u);
+          const float2 a3 = unpack_bf16x2(m3 ? lane32(h0, j) : 0u);
+          const float2 b = unpack_bf16x2(lane32(bq, j));
+          const float2 w01a = unpack_bf16x2(wq[2 * j].x), w23a = unpack_bf16x2(wq[2 * j].y);
+          const float2 w01b = unpack_bf16x2(wq[2 * j + 1].x), w23b = unpack_bf16x2(wq[2 * j + 1].y);
+          const float pa = b.x + w23a.y * xc.x + w23a.x * a1.x + w01a.y * a2.x + w01a.x * a3.x;
+          const float pb = b.y + w23b.y * xc.y + w23b.x * a1.y + w01b.y * a2.y + w01b.x * a3.y;
+          float ra, rb;
+          if (MODE == 0) {
+            ra = silu ? pa * sigmoid_f(pa) : pa;
+            rb = silu ? pb * sigmoid_f(pb) : pb;
+          } else {
+            const float2 d = unpack_bf16x2(lane32(dr[u], j));
+            const float sa = sigmoid_f(pa), sb = sigmoid_f(pb);
+            ra = silu ? d.x * sa * (1.f + pa * (1.f - sa)) : d.x;
+            rb = silu ? d.y * sb * (1.f + pb * (1.f - sb)) : d.y;
+          }
+          o[j] = pack_bf16x2(ra, rb);
+        }
+        h0 = h1; h1 = h2; h2 = xr[u];
+        *reinterpret_cast<uint4*>(out + (long long)t * ldo + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
+// dx[t] = sum_m w[., 3 - m] * dpre[t + m] over m = 0..3 with t + m in the same document
+__global__ void __launch_bounds__(STREAM_THREADS, 5)
+conv1d_dx_stream4_kernel(const __nv_bfloat16* __restrict__ dpre, long long ldd,
+                         const __nv_bfloat16* __restrict__ w, const int* __restrict__ doc_start,
+                         __nv_bfloat16* __restrict__ dx, long long ldx, int T, int C) {
+  const int c0 = (blockIdx.x * STREAM_THREADS + threadIdx.x) * 8;
+  if (c0 >= C) return;
+  const int t0 = blockIdx.y * STREAM_CHUNK;
+  const int t1 = min(T, t0 + STREAM_CHUNK);
+  uint2 wq[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) wq[i] = *reinterpret_cast<const uint2*>(w + (long long)(c0 + i) * 4);
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  uint4 d0 = zero, d1 = zero, d2 = zero;              // dpre[t], dpre[t+1], dpre[t+2]
+  int s0 = -1, s1 = -1, s2 = -1;                      // their document starts (-1 past the end)
+  if (t0 < T) { d0 = *reinterpret_cast<const uint4*>(dpre + (long long)t0 * ldd + c0); s0 = doc_start[t0]; }
+  if (t0 + 1 < T) { d1 = *reinterpret_cast<const uint4*>(dpre + (long long)(t0 + 1) * ldd + c0); s1 = doc_start[t0 + 1]; }
+  if (t0 + 2 < T) { d2 = *reinterpret_cast<const uint4*>(dpre + (long long)(t0 + 2) * ldd + c0); s2 = doc_start[t0 + 2]; }
+  for (int tb = t0; tb < t1; tb += 4) {
+    uint4 nr[4];
+    int ns[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int src = tb + u + 3;
+      nr[u] = zero;
+      ns[u] = -1;
+      if (src < T) {
+        nr[u] = *reinterpret_cast<const uint4*>(dpre + (long long)src * ldd + c0);
+        ns[u] = doc_start[src];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int t = tb + u;
+      if (t < t1) {
+        const bool m1 = s1 == s0, m2 = s2 == s0, m3 = ns[u] == s0;
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 c = unpack_bf16x2(lane32(d0, j));
+          const float2 a1 = unpack_bf16x2(m1 ? lane32(d1, j) : 0u);
+          const float2 a2 = unpack_bf16x2(m2 ? lane32(d2, j) : 0u);
+          const float2 a3 = unpack_bf16x2(m3 ? lane32(nr[u], j) : 0u);
+          const float2 w01a = unpack_bf16x2(wq[2 * j].x), w23a = unpack_bf16x2(wq[2 * j].y);
+          const float2 w01b = unpack_bf16x2(wq[2 * j + 1].x), w23b = unpack_bf16x2(wq[2 * j + 1].y);
+          o[j] = pack_bf16x2(w23a.y * c.x + w23a.x * a1.x + w01a.y * a2.x + w01a.x * a3.x,
+                             w23b.y * c.y + w23b.x * a1.y + w01b.y * a2.y + w01b.x * a3.y);
+        }
+        d0 = d1; d1 = d2; d2 = nr[u];
+        s0 = s1; s1 = s2; s2 = ns[u];
+        *reinterpret_cast<uint4*>(dx + (long long)t * ldx + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
 // partial[chunk, c, 0..K-1] = sum_t dpre[t, c] * x[t - (K-1) + j, c];  partial[chunk, c, K] = sum_t dpre[t, c]
 // One thread owns two adjacent channels and walks the tokens of its chunk with a register window of
 // the last K inputs.
@@ -186,6 +320,12 @@ dequant4_kernel(const uint32_t* __restrict__ packed, const void* __restrict__ sc
                 const float* __restrict__ global_scale, __nv_bfloat16* __restrict__ out,
                 long long n_vec, int group) {
   const float gs = (FMT == FMT_NVFP4) ? *global_scale : 1.f;
+  // code -> value table in shared memory: 16 entries in 16 banks, so lanes with different codes
+  // do not serialise (a __constant__ table would, one access per distinct code)
+  __shared__ float tab[16];
+  if (threadIdx.x < 16)
+    tab[threadIdx.x] = (FMT == FMT_NF4) ? NF4_TABLE[threadIdx.x] : E2M1_TABLE[threadIdx.x];
+  __syncthreads();
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec;
        v += (long long)gridDim.x * blockDim.x) {
     const uint32_t bits = packed[v];
@@ -204,9 +344,8 @@ dequant4_kernel(const uint32_t* __restrict__ packed, const void* __restrict__ sc
     for (int i = 0; i < 8; ++i) {
       const uint32_t code = (bits >> (4 * i)) & 0xF;
       float val;
-      if (FMT == FMT_NF4) val = NF4_TABLE[code];
-      else if (FMT == FMT_INT4) val = (float)code - 8.f;
-      else val = E2M1_TABLE[code];
+      if (FMT == FMT_INT4) val = (float)code - 8.f;
+      else val = tab[code];
       o[i] = (FMT == FMT_NVFP4) ? (val * s) * gs : val * s;
     }
     store8(out + v * 8, o);
@@ -217,6 +356,10 @@ inline int grid_for(long long work_items, int threads) {
   long long g = (work_items + threads - 1) / threads;
   const long long cap = (long long)xb_sm_count() * 16;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+inline dim3 stream_grid(int T, int C) {
+  return dim3((C / 8 + STREAM_THREADS - 1) / STREAM_THREADS, (T + STREAM_CHUNK - 1) / STREAM_CHUNK);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -231,6 +374,12 @@ XB_API int xb_causal_conv1d_fwd(const void* x, long long ldx, const void* w, con
   if (C % 8 || ldx % 8 || ldy % 8 || K < 1 || K > MAX_TAPS || !aligned16(x) || !aligned16(y))
     return -1;
   if (T <= 0) return 0;
+  if (K == 4) {
+    conv1d_stream4_kernel<0><<<stream_grid(T, C), STREAM_THREADS, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias,
+        doc_start, nullptr, 0, (__nv_bfloat16*)y, ldy, T, C, silu);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
   conv1d_point_kernel<0><<<grid_for((long long)T * (C / 8), 256), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, doc_start,
       nullptr, 0, (__nv_bfloat16*)y, ldy, T, C, K, silu);
@@ -255,11 +404,20 @@ XB_API int xb_causal_conv1d_bwd(const void* dy, long long lddy, const void* x, l
   if (T <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   const int grid = grid_for((long long)T * (C / 8), 256);
-  conv1d_point_kernel<1><<<grid, 256, 0, st>>>(
-      (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, doc_start,
-      (const __nv_bfloat16*)dy, lddy, (__nv_bfloat16*)dpre, C, T, C, K, silu);
-  conv1d_dx_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dpre, C, (const __nv_bfloat16*)w,
-                                         doc_start, (__nv_bfloat16*)dx, lddx, T, C, K);
+  if (K == 4) {
+    conv1d_stream4_kernel<1><<<stream_grid(T, C), STREAM_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias,
+        doc_start, (const __nv_bfloat16*)dy, lddy, (__nv_bfloat16*)dpre, C, T, C, silu);
+    conv1d_dx_stream4_kernel<<<stream_grid(T, C), STREAM_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)dpre, C, (const __nv_bfloat16*)w, doc_start, (__nv_bfloat16*)dx,
+        lddx, T, C);
+  } else {
+    conv1d_point_kernel<1><<<grid, 256, 0, st>>>(
+        (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias,
+        doc_start, (const __nv_bfloat16*)dy, lddy, (__nv_bfloat16*)dpre, C, T, C, K, silu);
+    conv1d_dx_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)dpre, C, (const __nv_bfloat16*)w,
+                                           doc_start, (__nv_bfloat16*)dx, lddx, T, C, K);
+  }
   const int chunks = xb_causal_conv1d_bwd_chunks(T);
   const int chunk_len = (T + chunks - 1) / chunks;
   dim3 g((C / 2 + 127) / 128, chunks);

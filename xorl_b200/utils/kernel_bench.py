@@ -5,6 +5,8 @@
     python -m xorl_b200.utils.kernel_bench attn --tokens 4096 --heads 32 --kv-heads 8
     python -m xorl_b200.utils.kernel_bench adamw --numel 268435456
     python -m xorl_b200.utils.kernel_bench rmsnorm --tokens 16384 --hidden 4096
+    python -m xorl_b200.utils.kernel_bench conv1d --tokens 32768 --hidden 8192 --doc-len 4096
+    python -m xorl_b200.utils.kernel_bench dequant4 --n 12288 --k 4096
 
 Timing: CUDA events on the launching stream around each run, ``--warmup`` untimed runs, the median
 of ``--iters`` runs, and a buffer larger than L2 written between runs.  ``--no-lib`` skips the
@@ -166,7 +168,52 @@ def bench_rmsnorm(a) -> Dict:
             "gbs": a.tokens * a.hidden * 4 / ms / 1e6}
 
 
-BENCHES = {"gemm": bench_gemm, "fp8_gemm": bench_fp8_gemm, "attn": bench_attn, "adamw": bench_adamw,
+def bench_conv1d(a) -> Dict:
+    """Short causal convolution + SiLU over a packed batch (forward, and forward + backward)."""
+    from ..ops import seqmix
+    T, C, K = a.tokens, a.hidden, 4
+    x = torch.randn(T, C, device="cuda").bfloat16().requires_grad_()
+    w = torch.randn(C, K, device="cuda").bfloat16().requires_grad_()
+    doc = a.doc_len or T
+    cu = torch.arange(0, T + 1, doc, device="cuda", dtype=torch.int32)
+    start = seqmix.document_starts(cu, T)
+    dy = torch.randn(T, C, device="cuda").bfloat16()
+    with torch.no_grad():
+        ms_f = _time(lambda: seqmix.causal_conv1d(x, w, None, cu, True, doc_start=start), a.warmup, a.iters, a.flush)
+
+    def fb():
+        x.grad = w.grad = None
+        seqmix.causal_conv1d(x, w, None, cu, True, doc_start=start).backward(dy)
+    ms_fb = _time(fb, a.warmup, a.iters, a.flush)
+    r = {"kernel": "causal_conv1d_silu", "tokens": T, "channels": C, "taps": K, "fwd_ms": ms_f,
+         "fwd_gbs": T * C * 4 / ms_f / 1e6, "fwd_bwd_ms": ms_fb}
+    if not a.no_lib:
+        import torch.nn.functional as F
+        xt = x.detach().t().unsqueeze(0).contiguous()
+
+        def lib():
+            F.silu(F.conv1d(F.pad(xt, (K - 1, 0)), w.detach().unsqueeze(1), groups=C))
+        ms2 = _time(lib, a.warmup, a.iters, a.flush)
+        r.update(lib_fwd_ms=ms2, ratio=ms2 / ms_f)
+    return r
+
+
+def bench_dequant4(a) -> Dict:
+    from ..ops import quantize as Q, seqmix
+    shape = (a.n, a.k)
+    out = {}
+    for fmt, group in (("nf4", 64), ("nvfp4", 16)):
+        parts = {k: v.cuda() for k, v in Q.quantize_weight(torch.randn(64, a.k) * 0.05, fmt, group).items()}
+        reps = a.n // 64                       # quantise a slab on the host, tile it on the device
+        for key in ("packed", "scale"):
+            parts[key] = parts[key].repeat(reps)
+        ms = _time(lambda: seqmix.dequant4(parts, fmt, group, shape), a.warmup, a.iters, a.flush)
+        out[fmt + "_ms"] = ms
+        out[fmt + "_out_gbs"] = a.n * a.k * 2 / ms / 1e6
+    return {"kernel": "dequant4", "n": a.n, "k": a.k, **out}
+
+
+BENCHES = {"conv1d": bench_conv1d, "dequant4": bench_dequant4, "gemm": bench_gemm, "fp8_gemm": bench_fp8_gemm, "attn": bench_attn, "adamw": bench_adamw,
            "rmsnorm": bench_rmsnorm, "fused_gemm": bench_fused_gemm}
 
 
