@@ -111,12 +111,20 @@ def validate_endpoint(host: str, port, *, require_allowlist: bool = False) -> Tu
         elif not named and not (literal and _in_networks(addrs[0], entries)):
             raise ValueError(f"endpoint {h!r} is not in {ALLOWLIST_ENV}")
     for a in addrs:
-        unsafe = a.is_link_local or a.is_multicast or a.is_unspecified or (a.is_reserved and not a.is_loopback)
+        unsafe = a.is_link_local or _is_group_address(a) or a.is_unspecified or (a.is_reserved and not a.is_loopback)
         if unsafe and not _in_networks(a, entries):
             raise ValueError(f"unsafe endpoint address {a}")
         if require_allowlist and a.is_private and not (a.is_loopback or named or _in_networks(a, entries)):
             raise ValueError(f"private endpoint address {a} needs an entry in {ALLOWLIST_ENV}")
     return str(addrs[0]), p
+
+
+_GROUP_NETWORKS = (ipaddress.ip_network("224.0.0.0/4"), ipaddress.ip_network("ff00::/8"))
+
+
+def _is_group_address(a) -> bool:
+    """One-to-many (group) addresses: 224.0.0.0/4 and ff00::/8."""
+    return any(a.version == n.version and a in n for n in _GROUP_NETWORKS)
 
 
 def endpoint_url(host: str, port, path: str, *, require_allowlist: bool = False) -> str:
