@@ -68,7 +68,167 @@ def _open_index(path: str) -> Dict[str, str]:
     return out
 
 
-def load_hf_weights(engine, path: str, cfg, strict: bool = True) -> List[str]:
+class MultiStreamH2D:
+    """Host -> device copies spread over a few CUDA streams with pinned staging buffers, so that
+    the page-locked copy of tensor i + 1 overlaps the DMA of tensor i
+    (src/xorl/models/module_utils.py:926, ``_MultiStreamDMA``).  On CPU it is a plain copy."""
+
+    def __init__(self, device: torch.device, streams: int = 2, staging_bytes: int = 256 << 20):
+        self.device = device
+        self.cuda = device.type == "cuda"
+        self.n = max(1, streams)
+        self.i = 0
+        self.copies = 0
+        if self.cuda:
+            self.streams = [torch.cuda.Stream(device) for _ in range(self.n)]
+            self.staging = [torch.empty(staging_bytes, dtype=torch.uint8, pin_memory=True) for _ in range(self.n)]
+            self.events = [None] * self.n
+
+    def to_device(self, t: torch.Tensor) -> torch.Tensor:
+        self.copies += 1
+        if not self.cuda:
+            return t.to(self.device)
+        k = self.i
+        self.i = (self.i + 1) % self.n
+        nbytes = t.numel() * t.element_size()
+        if nbytes > self.staging[k].numel():
+            return t.to(self.device)                      # larger than a staging slot: direct copy
+        if self.events[k] is not None:
+            self.events[k].synchronize()                  # the slot's previous DMA has finished
+        pinned = self.staging[k][:nbytes].view(t.dtype).reshape(t.shape)
+        pinned.copy_(t)
+        out = torch.empty(t.shape, dtype=t.dtype, device=self.device)
+        with torch.cuda.stream(self.streams[k]):
+            out.copy_(pinned, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.streams[k])
+        self.events[k] = ev
+        torch.cuda.current_stream().wait_event(ev)
+        return out
+
+
+def _weight_signature(weight_map: Dict[str, str]) -> str:
+    import hashlib
+    h = hashlib.sha256()
+    for k in sorted(weight_map):
+        h.update(k.encode())
+        h.update(b"\0")
+    return h.hexdigest()[:16]
+
+
+def check_weight_signatures(path: str, readers_only_ok: bool, is_reader: bool) -> Dict[str, str]:
+    """Every rank reports whether it can open the checkpoint and a digest of its tensor names; all
+    ranks raise together when one cannot or the digests differ, before any sub-group collective
+    could leave the others waiting (src/xorl/models/module_utils.py:1889-1917)."""
+    err, sig, wm = "", "", {}
+    if is_reader or not readers_only_ok:
+        try:
+            wm = _open_index(path)
+            sig = _weight_signature(wm)
+            if not wm:
+                err = f"no safetensors tensors under {path}"
+        except Exception as e:  # noqa: BLE001
+            err = f"{type(e).__name__}: {e}"
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        reports = [None] * dist.get_world_size()
+        dist.all_gather_object(reports, (err, sig))
+    else:
+        reports = [(err, sig)]
+    errs = [f"rank {r}: {e}" for r, (e, _) in enumerate(reports) if e]
+    sigs = {s_ for _, s_ in reports if s_}
+    if errs:
+        raise RuntimeError("checkpoint not readable on every reader: " + "; ".join(errs))
+    if len(sigs) > 1:
+        raise RuntimeError(f"ranks see different checkpoints under {path}: digests {sorted(sigs)}")
+    return wm
+
+
+def _reader_ranks(mode: str) -> List[int]:
+    """``broadcast``: rank 0 reads.  ``grouped``: the lowest rank of every host reads and serves the
+    ranks of its host (src/xorl/models/module_utils.py:1861)."""
+    world = dist.get_world_size()
+    if mode == "broadcast":
+        return [0] * world
+    import socket
+    hosts = [None] * world
+    dist.all_gather_object(hosts, socket.gethostname())
+    first: Dict[str, int] = {}
+    for r, h in enumerate(hosts):
+        first.setdefault(h, r)
+    return [first[h] for h in hosts]
+
+
+def load_hf_weights(engine, path: str, cfg, strict: bool = True, mode: str = "all_ranks",
+                    h2d_streams: int = 2) -> List[str]:
+    """Fills every rank's shards from a Hugging Face safetensors directory.
+
+    ``all_ranks``: every rank reads the tensors that overlap its shard (the page cache serves
+    repeats).  ``broadcast`` / ``grouped``: one reader (rank 0 / the first rank of each host) reads
+    and transforms every tensor once and broadcasts it to the ranks it serves, which keep their
+    slice; file-system traffic drops from world x checkpoint to one (or hosts) x checkpoint."""
+    multi = dist.is_initialized() and dist.get_world_size() > 1
+    ps = engine.ps
+    # served modes walk the same parameter list on every rank and broadcast whole tensors: with
+    # pipeline stages (different lists) or expert parallelism (different expert slices per rank)
+    # every rank reads for itself
+    same_lists = getattr(ps, "pp_size", 1) == 1 and getattr(ps, "ep_size", 1) == 1
+    if mode in ("broadcast", "grouped") and multi and same_lists:
+        return _load_hf_weights_served(engine, path, cfg, strict, mode, h2d_streams)
+    check_weight_signatures(path, readers_only_ok=False, is_reader=True)
+    return _load_hf_weights_all_ranks(engine, path, cfg, strict)
+
+
+def _load_hf_weights_served(engine, path, cfg, strict, mode, h2d_streams) -> List[str]:
+    from safetensors import safe_open
+    rank = dist.get_rank()
+    readers = _reader_ranks(mode)
+    my_reader = readers[rank]
+    is_reader = my_reader == rank
+    wm = check_weight_signatures(path, readers_only_ok=True, is_reader=is_reader)
+    # one sub-group per reader (created by every rank, in the same order)
+    groups = {}
+    for rd in sorted(set(readers)):
+        members = [r for r, x in enumerate(readers) if x == rd]
+        groups[rd] = dist.new_group(members) if len(set(readers)) > 1 else None
+    pg = groups[my_reader]
+    handler = get_checkpoint_handler(cfg)
+    h2d = MultiStreamH2D(engine.device, h2d_streams)
+    handles: Dict[str, object] = {}
+
+    def read(name: str) -> torch.Tensor:
+        fn = wm[name]
+        if fn not in handles:
+            handles[fn] = safe_open(os.path.join(path, fn), "pt")
+        return handles[fn].get_tensor(name)
+
+    missing: List[str] = []
+    for g in engine.all_groups():
+        # the ranks served by one reader may hold different slices: walk all parameters of the
+        # group in the same order everywhere
+        for pname, p in g.named_params:
+            srcs = handler.hf_sources(pname)
+            if cfg.tie_word_embeddings and pname.startswith("lm_head"):
+                srcs = ["model.embed_tokens.weight"]
+            meta = [None]
+            if is_reader:
+                if all(s_ in wm for s_ in srcs):
+                    t = handler.from_hf(pname, [read(s_) for s_ in srcs]).contiguous()
+                    meta = [(tuple(t.shape), t.dtype)]
+            dist.broadcast_object_list(meta, src=my_reader, group=pg)
+            if meta[0] is None:
+                missing.append(pname)
+                continue
+            shape, dtype = meta[0]
+            buf = h2d.to_device(t) if is_reader else torch.empty(shape, dtype=dtype, device=engine.device)
+            dist.broadcast(buf, src=my_reader, group=pg)
+            engine.load_full_tensors({pname: buf}, strict=False)
+    engine.loaded_weight_stats = {"mode": mode, "reader": my_reader, "h2d_copies": h2d.copies}
+    if strict and missing:
+        raise KeyError(f"weights missing from {path}: {missing[:8]}")
+    return missing
+
+
+def _load_hf_weights_all_ranks(engine, path: str, cfg, strict: bool = True) -> List[str]:
     """Every rank reads the tensors it needs (all ranks read; the page cache serves repeats)."""
     from safetensors import safe_open
     handler = get_checkpoint_handler(cfg)

@@ -142,7 +142,7 @@ class Trainer:
         if weights and t.load_weights_mode != "skip" and os.path.isdir(weights) and any(
                 f.endswith(".safetensors") for f in os.listdir(weights)):
             from ..checkpoint.hf_io import load_hf_weights
-            load_hf_weights(self.engine, weights, self.model_config)
+            load_hf_weights(self.engine, weights, self.model_config, mode=t.load_weights_mode)
 
     def _build_data(self, dataset=None) -> None:
         a = self.args
