@@ -111,6 +111,43 @@ def test_muon_newton_schulz_on_tcgen05_gemm():
     assert (X - Y).norm() / X.norm() < 0.06
 
 
+@pytest.mark.parametrize("M,K,block,dt", [(2048, 512, 512, torch.bfloat16), (1000, 256, 256, torch.float32),
+                                          (2304, 1024, 1024, torch.bfloat16)])
+def test_symmetric_gemm_matches_full_product(M, K, block, dt):
+    """Lower panels through the GEMM kernel + mirror kernel against the full product and fp32."""
+    from xorl_b200.ops import gemm as G
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
+    before = G.launch_count()
+    c = G.gemm_symmetric(x, out_dtype=dt, block=block)
+    panels = -(-M // block)
+    assert G.launch_count() == before + panels + 1
+    full = G.gemm(x, x, out_dtype=dt)
+    low = torch.tril(torch.ones(M, M, device="cuda", dtype=torch.bool))
+    assert (c[low].float() - full[low].float()).abs().max() <= 1e-2 * full.float().abs().max()
+    assert torch.equal(c, c.t())                             # exactly symmetric after the mirror
+    ref = x.float() @ x.float().t()
+    assert (c.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+    # a product of two commuting symmetric factors
+    a = full.to(torch.bfloat16)
+    s2 = G.gemm_symmetric(a, a, block=block).float()
+    ref2 = a.float() @ a.float().t()
+    assert (s2 - ref2).abs().max() <= 3e-2 * ref2.abs().max()
+
+
+def test_muon_on_large_matrix_uses_symmetric_panels():
+    from xorl_b200.ops import gemm as G
+    from xorl_b200.optim.muon import newton_schulz
+    torch.manual_seed(1)
+    Gm = torch.randn(2048, 2560, device="cuda")
+    before = G.launch_count()
+    X = newton_schulz(Gm, steps=5).float()
+    # per step: 2 symmetric products (2 panels + mirror each) + 1 plain GEMM
+    assert G.launch_count() - before == 5 * (2 * 3 + 1)
+    sv = torch.linalg.svdvals(X)
+    assert sv.min() > 0.4 and sv.max() < 1.3
+
+
 @pytest.mark.parametrize("scoring,renorm,E,k,bias", [("softmax", True, 128, 8, False), ("softmax", False, 8, 2, False),
                                                      ("sigmoid", True, 256, 8, True), ("softmax_after_topk", False, 32, 4, False),
                                                      ("softmax", True, 60, 3, False)])

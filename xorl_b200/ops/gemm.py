@@ -85,6 +85,30 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+def gemm_symmetric(a: torch.Tensor, b: torch.Tensor | None = None, *, out_dtype: torch.dtype | None = None,
+                   block: int = 1024) -> torch.Tensor:
+    """C = a @ b^T for a product that is known to be symmetric (``b`` omitted: a @ a^T; or two
+    commuting symmetric factors).  Only the row panels on and below the block diagonal go through
+    the GEMM kernel (panel r covers columns 0 .. end of block r); the blocks above are mirrored by
+    ``xb_mirror_lower``.  With M / block panels the GEMM work is (1 + block / M) / 2 of the full
+    product.  Same role as src/xorl/ops/quack/gemm_symmetric.py."""
+    global _launches
+    b = a if b is None else b
+    M = a.shape[0]
+    assert b.shape[0] == M and a.shape[1] == b.shape[1]
+    if not a.is_cuda or M < 2 * block or a.shape[1] % 8 or M % 8:
+        return gemm(a, b, out_dtype=out_dtype)
+    out = torch.empty((M, M), device=a.device, dtype=out_dtype or torch.bfloat16)
+    for r0 in range(0, M, block):
+        r1 = min(M, r0 + block)
+        gemm(a[r0:r1], b[:r1], out=out[r0:r1, :r1])
+    _lib.check(_lib.cuda_lib().xb_mirror_lower(out.data_ptr(), out.stride(0), M, block,
+                                               int(out.dtype == torch.float32), _lib.stream_ptr()),
+               "xb_mirror_lower")
+    _launches += 1
+    return out
+
+
 def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
     """dW = dy2^T @ x2 for weight ``w``: written straight into the flat gradient buffer of the ZeRO
     unit (returns None), deferred to a W slot of a zero-bubble schedule, or returned as a tensor."""

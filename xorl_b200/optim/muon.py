@@ -23,7 +23,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 import torch.distributed as dist
 
-from ..ops.gemm import gemm
+from ..ops.gemm import gemm, gemm_symmetric
 from .optimizer import ShardedOptimizer
 
 NS_COEFFS = (3.4445, -4.7750, 2.0315)
@@ -34,6 +34,14 @@ def _mm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """a [M,K] @ b[N,K]^T in bf16 with fp32 accumulation."""
     if a.is_cuda and a.shape[1] % 8 == 0:
         return gemm(a, b)
+    return (a.float() @ b.float().t()).to(a.dtype)
+
+
+def _mm_sym(a: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a @ b^T where the product is symmetric (b omitted: a @ a^T): block-lower panels + mirror."""
+    if a.is_cuda and a.shape[1] % 8 == 0:
+        return gemm_symmetric(a, b)
+    b = a if b is None else b
     return (a.float() @ b.float().t()).to(a.dtype)
 
 
@@ -53,8 +61,8 @@ def newton_schulz(G: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.T
         X = X.t().contiguous()
     X = X / (X.float().norm() + eps).to(X.dtype)
     for _ in range(steps):
-        A = _mm_nt(X, X)                       # X X^T  (symmetric)
-        B = (b * A.float() + c * _mm_nt(A, A).float()).to(X.dtype)   # A symmetric: A A^T = A A
+        A = _mm_sym(X)                         # X X^T  (symmetric: lower panels + mirror)
+        B = (b * A.float() + c * _mm_sym(A).float()).to(X.dtype)     # A symmetric: A A^T = A A
         X = (a * X.float() + _mm_nn(B, X).float()).to(X.dtype)
     return X.t().contiguous() if transposed else X
 
@@ -73,15 +81,15 @@ def gram_newton_schulz(G: torch.Tensor, steps: int = 5, restart_iterations: Sequ
     X0 = X0 / (X0.float().norm() + eps).to(X0.dtype)
     m = X0.shape[0]
     eye = torch.eye(m, device=X0.device, dtype=torch.float32)
-    A = _mm_nt(X0, X0).float()
+    A = _mm_sym(X0).float()
     Q: Optional[torch.Tensor] = None
     for it in range(steps):
         if it in restart_iterations and Q is not None:
             X0 = _mm_nn(Q.to(torch.bfloat16), X0)
-            A = _mm_nt(X0, X0).float()
+            A = _mm_sym(X0).float()
             Q = None
         A16 = A.to(torch.bfloat16)
-        A2 = _mm_nt(A16, A16).float()
+        A2 = _mm_sym(A16).float()
         P = a * eye + b * A + c * A2
         P16 = P.to(torch.bfloat16)
         Q = P if Q is None else _mm_nt(P16, Q.t().contiguous().to(torch.bfloat16)).float()
