@@ -31,3 +31,32 @@ def test_stage_maps_roundtrip():
             r, k = stage_owner(g, 4, s)
             assert global_stage(r, k, 4, s) == g
     assert estimate_p2p_bytes_per_step(2, 16, 8192, 5120, 2) == 2 * 3 * 16 * 8192 * 5120 * 2 * 2
+
+
+def test_pp_contract_checks():
+    import pytest
+    import torch
+    from xorl_b200.parallel.pp import assign_layers
+    from xorl_b200.parallel.pp_contract import (PPContractError, assert_wire_dtype, validate_layer_identity,
+                                                validate_microbatch_metadata, validate_stage_plan)
+    validate_stage_plan(assign_layers(13, 2, "interleaved1f1b", 2), 13)
+    with pytest.raises(PPContractError, match="cover layers"):
+        validate_stage_plan([[0, 1], [3]], 4)
+    with pytest.raises(PPContractError, match="cover layers"):
+        validate_stage_plan([[2, 3], [0, 1]], 4)
+
+    class L:
+        def __init__(self, i):
+            self.layer_idx = i
+    validate_layer_identity([(4, L(4)), (5, L(5))], [4, 5])
+    with pytest.raises(PPContractError, match="layer_idx=0"):
+        validate_layer_identity([(4, L(0))], [4])
+    assert_wire_dtype(torch.zeros(2, dtype=torch.bfloat16), torch.bfloat16, "x")
+    with pytest.raises(PPContractError, match="expected torch.bfloat16"):
+        assert_wire_dtype(torch.zeros(2), torch.bfloat16, "activation")
+    ok = {"position_ids": torch.arange(8), "cu_seqlens": torch.tensor([0, 3, 8])}
+    validate_microbatch_metadata(ok, 0)
+    with pytest.raises(PPContractError, match="one document"):
+        validate_microbatch_metadata({"position_ids": torch.arange(8), "cu_seqlens": None}, 1)
+    with pytest.raises(PPContractError, match="do not delimit"):
+        validate_microbatch_metadata({"position_ids": torch.arange(8), "cu_seqlens": torch.tensor([0, 9])}, 2)

@@ -20,6 +20,7 @@ import torch.distributed as dist
 
 from ..ops import grad_sink
 from . import pp_schedules as S
+from .pp_contract import assert_wire_dtype, validate_microbatch_metadata
 from .state import ParallelState, process_group_timeout
 
 
@@ -81,9 +82,13 @@ def local_stage_layout(num_layers: int, ps: ParallelState, schedule: str, virtua
     chunks = S.num_chunks(sched, virtual_stages)
     n_stages = pp * chunks
     local = [S.global_stage(r, c, pp, sched) for c in range(chunks)]
-    return {"chunk_layers": [stages[g] for g in local], "chunk_stage": local, "n_stages": n_stages,
-            "has_embed": 0 in local, "has_head": (n_stages - 1) in local,
-            "layers": sorted(sum((stages[g] for g in local), []))}
+    layout = {"chunk_layers": [stages[g] for g in local], "chunk_stage": local, "n_stages": n_stages,
+              "has_embed": 0 in local, "has_head": (n_stages - 1) in local,
+              "layers": sorted(sum((stages[g] for g in local), []))}
+    from .pp_contract import validate_layout, validate_stage_plan
+    validate_stage_plan(stages, num_layers)
+    validate_layout(layout, num_layers)
+    return layout
 
 
 class _PairGroups:
@@ -155,6 +160,9 @@ class PipelineRunner:
         eng = self.engine
         dev = eng.device
         assert len(micro_batches) == self.n_mb, (len(micro_batches), self.n_mb)
+        for i, mb in enumerate(micro_batches):
+            if mb.get("cu_seqlens") is not None and mb.get("position_ids") is not None:
+                validate_microbatch_metadata(mb, i)
         ctxs = [eng.make_step_context(mb["input_ids"], mb.get("position_ids"), mb.get("cu_seqlens"),
                                       grad_scale) for mb in micro_batches]
         H = eng.model.config.hidden_size
@@ -183,6 +191,7 @@ class PipelineRunner:
             return t
 
         def send(kind, m, g, dst, tensor):
+            assert_wire_dtype(tensor, dtype, f"{kind} of micro-batch {m} from stage {g}")
             grp = self.pairs.groups[(self.rank, dst)]
             w = dist.isend(tensor, dst=self.pairs.my_ranks[dst], group=grp)
             sends.append((w, tensor))
