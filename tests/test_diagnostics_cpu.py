@@ -84,3 +84,16 @@ def test_metrics_sink_writes_json_lines_and_helpers_are_inert_on_cpu(tmp_path):
     if not mh.enabled:
         assert mh.after_step(2) is None and mh.on_oom() is None
     mh.close()
+
+
+def test_kernel_pin_is_written_once_and_detects_a_change(tmp_path):
+    from xorl_b200.models.numerics import KernelPinError, pin_kernel_configs
+    first = pin_kernel_configs(str(tmp_path))
+    assert first["mismatch"] == {} and (tmp_path / "kernel_pin.json").exists()
+    assert pin_kernel_configs(str(tmp_path), strict=True)["mismatch"] == {}
+    pin = json.loads((tmp_path / "kernel_pin.json").read_text())
+    pin["native_library_sha256"] = "0" * 64
+    (tmp_path / "kernel_pin.json").write_text(json.dumps(pin))
+    assert "native_library_sha256" in pin_kernel_configs(str(tmp_path))["mismatch"]
+    with pytest.raises(KernelPinError):
+        pin_kernel_configs(str(tmp_path), strict=True)

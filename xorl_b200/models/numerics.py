@@ -73,3 +73,51 @@ def apply_numerical_program(model, prog: NumericalProgram) -> None:
     for m in model.modules():
         if hasattr(m, "router_fp32"):
             m.router_fp32 = prog.router_fp32
+
+
+# ---- kernel pin ---------------------------------------------------------------------------------
+class KernelPinError(RuntimeError):
+    """The kernels of this process differ from the ones a run was pinned to."""
+
+
+def kernel_fingerprint() -> Dict[str, Any]:
+    """What decides the bits a kernel produces here: the native library itself (its kernels have
+    fixed tile shapes, no autotuning and no run-time cache to pin), the selectable kernel variants,
+    and the PyTorch / CUDA versions behind the remaining tensor ops.  The reference pins its
+    autotune caches for the same purpose (src/xorl/ops/kernel_config_pin.py:67-182)."""
+    import hashlib
+
+    import torch
+
+    from ..ops import _lib, gemm as gemm_mod
+    path = _lib.cuda_lib_path()
+    digest = ""
+    if path.exists():
+        h = hashlib.sha256()
+        with open(path, "rb") as f:
+            for blk in iter(lambda: f.read(1 << 20), b""):
+                h.update(blk)
+        digest = h.hexdigest()
+    return {"native_library_sha256": digest, "gemm_variant": getattr(gemm_mod, "_VARIANT", "pair"),
+            "torch": torch.__version__, "cuda": torch.version.cuda or "",
+            "device": torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu"}
+
+
+def pin_kernel_configs(directory: str, strict: bool = False) -> Dict[str, Any]:
+    """Writes ``kernel_pin.json`` on first use; afterwards compares.  A mismatch raises with
+    ``strict`` (bit-exact lanes) and is returned under ``"mismatch"`` otherwise."""
+    import json
+    import os
+    fp = kernel_fingerprint()
+    path = os.path.join(directory, "kernel_pin.json")
+    if not os.path.exists(path):
+        os.makedirs(directory, exist_ok=True)
+        with open(path, "w") as f:
+            json.dump(fp, f, indent=2)
+        return {"pinned": fp, "mismatch": {}}
+    with open(path) as f:
+        old = json.load(f)
+    diff = {k: (old.get(k), fp.get(k)) for k in set(old) | set(fp) if old.get(k) != fp.get(k)}
+    if diff and strict:
+        raise KernelPinError(f"kernels differ from the pin in {path}: {diff}")
+    return {"pinned": old, "mismatch": diff}

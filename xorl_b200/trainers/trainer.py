@@ -194,6 +194,11 @@ class Trainer:
                 store, self.ps.rank, self.ps.world_size,
                 interval_s=float(os.environ.get("XORL_RANK_WATCHDOG_INTERVAL_S", "5")),
                 timeout_s=float(os.environ.get("XORL_RANK_WATCHDOG_TIMEOUT_S", "300"))).start()
+        if self.ps.rank == 0:
+            from ..models.numerics import pin_kernel_configs
+            pin = pin_kernel_configs(t.output_dir, strict=t.enable_full_determinism)
+            if pin["mismatch"]:
+                logger.warning("kernels differ from %s/kernel_pin.json: %s", t.output_dir, pin["mismatch"])
         from ..checkpoint import build_checkpointer
         self.checkpointer = build_checkpointer(self)
 
