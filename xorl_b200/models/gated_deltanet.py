@@ -167,6 +167,11 @@ class GatedDeltaNet(nn.Module):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T = x.shape[0]
         cu = ctx.cu_seqlens
+        if ctx.cp is not None:
+            # the trainer's sequence-shard collator cuts every document across the ranks, while the
+            # state hand-over of parallel/linear_attn_cp.py works on contiguous token shards
+            raise NotImplementedError("GatedDeltaNet layers do not run under ulysses / ring context "
+                                      "parallelism yet: use tensor, pipeline or data parallelism")
         q = causal_conv1d(self.q_proj(x), self.q_conv1d, None, cu, silu=True)
         k = causal_conv1d(self.k_proj(x), self.k_conv1d, None, cu, silu=True)
         v = causal_conv1d(self.v_proj(x), self.v_conv1d, None, cu, silu=True)

@@ -149,6 +149,9 @@ class Mamba2Mixer(nn.Module):
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T = h.shape[0]
+        if ctx.cp is not None:
+            raise NotImplementedError("Mamba2 layers do not run under ulysses / ring context parallelism: "
+                                      "the scan state is not handed across sequence shards")
         proj = self.in_proj(h)
         gate, xbc, dt = proj.split([self.d_inner, self.conv_dim, self.H], dim=-1)
         xbc = causal_conv1d(xbc.contiguous(), self.conv1d_weight, self.conv1d_bias, ctx.cu_seqlens, silu=True)
