@@ -246,6 +246,69 @@ conv1d_dx_stream4_kernel(const __nv_bfloat16* __restrict__ dpre, long long ldd,
   }
 }
 
+// Streaming form of the weight / bias gradient for K = 4: one thread owns 8 channels of one token
+// chunk (uint4 rows, four rows in flight) and writes its 8 x 5 partial sums once.
+__global__ void __launch_bounds__(STREAM_THREADS, 4)
+conv1d_dw_stream4_kernel(const __nv_bfloat16* __restrict__ dpre, long long ldd,
+                         const __nv_bfloat16* __restrict__ x, long long ldx,
+                         const int* __restrict__ doc_start, float* __restrict__ partial, int T, int C,
+                         int chunk_len) {
+  const int c0 = (blockIdx.x * STREAM_THREADS + threadIdx.x) * 8;
+  if (c0 >= C) return;
+  const int t0 = blockIdx.y * chunk_len;
+  const int t1 = min(T, t0 + chunk_len);
+  float acc[8][5];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+#pragma unroll
+    for (int j = 0; j < 5; ++j) acc[i][j] = 0.f;
+  }
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  uint4 h0 = zero, h1 = zero, h2 = zero;              // x[t-3], x[t-2], x[t-1]
+  if (t0 < t1) {
+    if (t0 - 3 >= 0) h0 = *reinterpret_cast<const uint4*>(x + (long long)(t0 - 3) * ldx + c0);
+    if (t0 - 2 >= 0) h1 = *reinterpret_cast<const uint4*>(x + (long long)(t0 - 2) * ldx + c0);
+    if (t0 - 1 >= 0) h2 = *reinterpret_cast<const uint4*>(x + (long long)(t0 - 1) * ldx + c0);
+  }
+  for (int tb = t0; tb < t1; tb += 4) {
+    uint4 xr[4], dr[4];
+    int st[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int t = min(tb + u, t1 - 1);
+      xr[u] = *reinterpret_cast<const uint4*>(x + (long long)t * ldx + c0);
+      dr[u] = *reinterpret_cast<const uint4*>(dpre + (long long)t * ldd + c0);
+      st[u] = doc_start[t];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int t = tb + u;
+      if (t < t1) {
+        const bool m1 = t - 1 >= st[u], m2 = t - 2 >= st[u], m3 = t - 3 >= st[u];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 xc = unpack_bf16x2(lane32(xr[u], j));
+          const float2 a1 = unpack_bf16x2(m1 ? lane32(h2, j) : 0u);
+          const float2 a2 = unpack_bf16x2(m2 ? lane32(h1, j) : 0u);
+          const float2 a3 = unpack_bf16x2(m3 ? lane32(h0, j) : 0u);
+          const float2 d = unpack_bf16x2(lane32(dr[u], j));
+          acc[2 * j][3] += d.x * xc.x; acc[2 * j][2] += d.x * a1.x;
+          acc[2 * j][1] += d.x * a2.x; acc[2 * j][0] += d.x * a3.x; acc[2 * j][4] += d.x;
+          acc[2 * j + 1][3] += d.y * xc.y; acc[2 * j + 1][2] += d.y * a1.y;
+          acc[2 * j + 1][1] += d.y * a2.y; acc[2 * j + 1][0] += d.y * a3.y; acc[2 * j + 1][4] += d.y;
+        }
+        h0 = h1; h1 = h2; h2 = xr[u];
+      }
+    }
+  }
+  float* p = partial + ((long long)blockIdx.y * C + c0) * 5;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+#pragma unroll
+    for (int j = 0; j < 5; ++j) p[i * 5 + j] = acc[i][j];
+  }
+}
+
 // partial[chunk, c, 0..K-1] = sum_t dpre[t, c] * x[t - (K-1) + j, c];  partial[chunk, c, K] = sum_t dpre[t, c]
 // One thread owns two adjacent channels and walks the tokens of its chunk with a register window of
 // the last K inputs.
@@ -389,7 +452,7 @@ XB_API int xb_causal_conv1d_fwd(const void* x, long long ldx, const void* w, con
 // Number of token chunks (rows of `partial`) the backward writes for T tokens.
 XB_API int xb_causal_conv1d_bwd_chunks(int T) {
   const int c = (T + 255) / 256;
-  return c < 1 ? 1 : (c > 64 ? 64 : c);
+  return c < 1 ? 1 : (c > 128 ? 128 : c);
 }
 
 // dy, x [T, C]; dpre [T, C] bf16 workspace (may alias nothing else); dx [T, C];
@@ -420,9 +483,16 @@ XB_API int xb_causal_conv1d_bwd(const void* dy, long long lddy, const void* x, l
   }
   const int chunks = xb_causal_conv1d_bwd_chunks(T);
   const int chunk_len = (T + chunks - 1) / chunks;
-  dim3 g((C / 2 + 127) / 128, chunks);
-  conv1d_dw_kernel<<<g, 128, 0, st>>>((const __nv_bfloat16*)dpre, C, (const __nv_bfloat16*)x, ldx,
-                                      doc_start, partial, T, C, K, chunk_len);
+  if (K == 4) {
+    dim3 g((C / 8 + STREAM_THREADS - 1) / STREAM_THREADS, chunks);
+    conv1d_dw_stream4_kernel<<<g, STREAM_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)dpre, C, (const __nv_bfloat16*)x, ldx, doc_start, partial, T, C,
+        chunk_len);
+  } else {
+    dim3 g((C / 2 + 127) / 128, chunks);
+    conv1d_dw_kernel<<<g, 128, 0, st>>>((const __nv_bfloat16*)dpre, C, (const __nv_bfloat16*)x, ldx,
+                                        doc_start, partial, T, C, K, chunk_len);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -7,6 +7,7 @@
     python -m xorl_b200.utils.kernel_bench rmsnorm --tokens 16384 --hidden 4096
     python -m xorl_b200.utils.kernel_bench conv1d --tokens 32768 --hidden 8192 --doc-len 4096
     python -m xorl_b200.utils.kernel_bench dequant4 --n 12288 --k 4096
+    python -m xorl_b200.utils.kernel_bench symgemm --m 4096 --k 12288 --block 1024
 
 Timing: CUDA events on the launching stream around each run, ``--warmup`` untimed runs, the median
 of ``--iters`` runs, and a buffer larger than L2 written between runs.  ``--no-lib`` skips the
@@ -213,7 +214,24 @@ def bench_dequant4(a) -> Dict:
     return {"kernel": "dequant4", "n": a.n, "k": a.k, **out}
 
 
-BENCHES = {"conv1d": bench_conv1d, "dequant4": bench_dequant4, "gemm": bench_gemm, "fp8_gemm": bench_fp8_gemm, "attn": bench_attn, "adamw": bench_adamw,
+def bench_symgemm(a) -> Dict:
+    """X X^T (the Gram product of Muon's Newton-Schulz step): full GEMM against lower panels + mirror."""
+    from ..ops.gemm import gemm, gemm_symmetric
+    X = (torch.randn(a.m, a.k, device="cuda") * 0.05).bfloat16()
+    ms_full = _time(lambda: gemm(X, X), a.warmup, a.iters, a.flush)
+    ms_sym = _time(lambda: gemm_symmetric(X, block=a.block), a.warmup, a.iters, a.flush)
+    flops = 2.0 * a.m * a.m * a.k
+    r = {"kernel": "gemm_symmetric", "m": a.m, "k": a.k, "block": a.block, "full_ms": ms_full, "sym_ms": ms_sym,
+         "full_tflops": flops / ms_full / 1e9, "sym_effective_tflops": flops / ms_sym / 1e9,
+         "speedup": ms_full / ms_sym}
+    if not a.no_lib:
+        C = torch.empty(a.m, a.m, device="cuda", dtype=torch.bfloat16)
+        ms2 = _time(lambda: torch.matmul(X, X.t(), out=C), a.warmup, a.iters, a.flush)
+        r.update(lib_ms=ms2, lib_tflops=flops / ms2 / 1e9)
+    return r
+
+
+BENCHES = {"symgemm": bench_symgemm, "conv1d": bench_conv1d, "dequant4": bench_dequant4, "gemm": bench_gemm, "fp8_gemm": bench_fp8_gemm, "attn": bench_attn, "adamw": bench_adamw,
            "rmsnorm": bench_rmsnorm, "fused_gemm": bench_fused_gemm}
 
 
@@ -237,6 +255,7 @@ def main(argv=None) -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-lib", action="store_true")
     ap.add_argument("--ranks", type=int, default=2)
+    ap.add_argument("--block", type=int, default=1024)
     a = ap.parse_args(argv)
     a.flush = torch.zeros(256 << 20, device="cuda", dtype=torch.uint8)
     print(json.dumps(BENCHES[a.kernel](a)))
