@@ -61,3 +61,32 @@ def test_export_quantized_roundtrip(tmp_path):
     back4 = Q.nvfp4_dequantize(out4[k], out4[k + "_scale"], out4[k + "_scale_2"][0], (128, 384), dtype=torch.float32)
     assert (back4 - w[k].float()).norm() / w[k].float().norm() < 0.15
     assert json.load(open(tmp_path / "fp4" / "config.json"))["quantization_config"]["format"] == "nvfp4"
+
+
+def test_convert_hf_to_dcp_roundtrip(tmp_path):
+    """HF safetensors -> DCP directory -> a fresh engine holds the same weights."""
+    import torch
+    from xorl_b200.checkpoint.checkpointer import DistributedCheckpointer
+    from xorl_b200.checkpoint.hf_io import save_hf_weights
+    from xorl_b200.cli.convert_hf_to_dcp import main as convert
+    from xorl_b200.models.config import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.parallel.state import get_parallel_state, reset_parallel_state
+    from xorl_b200.parallel.zero import Zero3Engine
+    reset_parallel_state()
+    cfg = preset("tiny-qwen3")
+
+    def engine(seed):
+        m = DecoderLM(cfg, dtype=torch.float32, device="meta")
+        return Zero3Engine(m, get_parallel_state(), compute_dtype=torch.float32, device=torch.device("cpu"), seed=seed)
+
+    src = engine(0)
+    hf = tmp_path / "hf"
+    save_hf_weights(src, str(hf), cfg, dtype=torch.float32)
+    out = convert(["--model-path", str(hf), "--output-dir", str(tmp_path / "out"), "--step", "7"])
+    assert out.endswith("global_step_7") and os.path.exists(os.path.join(out, ".metadata"))
+    dst = engine(1)
+    DistributedCheckpointer(dst, None, str(tmp_path / "out" / "checkpoints")).load(out, load_optimizer=False)
+    for a, b in zip(src.all_groups(), dst.all_groups()):
+        assert torch.equal(a.master, b.master), a.name
+    reset_parallel_state()
