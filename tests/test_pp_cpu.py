@@ -49,3 +49,18 @@ def test_pp2_matches_single_process(tmp_path, schedule):
     assert len(got) == 3
     for a, b in zip(ref, got):
         assert abs(a - b) < 2e-4, (schedule, ref, got)
+
+
+@pytest.mark.distributed
+def test_pp_bubble_profile_is_reported(tmp_path):
+    """XORL_PP_BUBBLE_PROFILE=1: measured wait share, the unit-cost estimate and the bytes sent."""
+    import json
+    from dist_utils import run_distributed
+    cfg = _cfg(tmp_path, "prof", pipeline_parallel_size=2, pipeline_parallel_schedule="1f1b",
+               data_parallel_mode="none", max_steps=2)
+    run_distributed("-m", 2, "xorl_b200.cli.train", cfg, env={"XORL_PP_BUBBLE_PROFILE": "1"})
+    with open(tmp_path / "prof" / "training_metrics.json") as f:
+        b = json.load(f)["pp_bubble"]
+    assert 0.0 <= b["measured_bubble_fraction"] < 1.0 and b["waits"] > 0
+    assert abs(b["analytic_bubble_fraction"] - 0.2) < 1e-6          # (P - 1) / (M + P - 1) with P = 2, M = 4
+    assert b["p2p_sent_bytes"] > 0

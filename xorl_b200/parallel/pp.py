@@ -13,6 +13,8 @@ Reference: src/xorl/distributed/pipeline_parallel.py:138-789, src/xorl/trainers/
 """
 from __future__ import annotations
 
+import os
+import time
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -116,6 +118,8 @@ class PipelineRunner:
                  n_microbatches: int):
         self.engine, self.ps = engine, ps
         self.schedule = schedule.lower()
+        self.virtual_stages = virtual_stages
+        self.bubble_stats: Dict[str, float] = {}
         self.pp, self.rank = ps.pp_size, ps.pp_rank
         self.layout = layout
         self.n_mb = n_microbatches
@@ -160,6 +164,16 @@ class PipelineRunner:
         eng = self.engine
         dev = eng.device
         assert len(micro_batches) == self.n_mb, (len(micro_batches), self.n_mb)
+        # XORL_PP_BUBBLE_PROFILE=1: time spent waiting for a neighbour's activation or gradient,
+        # against the whole step (the device is synchronised around each wait, so the profile
+        # perturbs the run it measures; src/xorl/distributed/pp_profiling.py has the same switch)
+        profile = os.environ.get("XORL_PP_BUBBLE_PROFILE", "0") == "1"
+        prof = {"wait_s": 0.0, "waits": 0, "sent_bytes": 0}
+        t_step = time.perf_counter()
+
+        def _sync():
+            if dev.type == "cuda":
+                torch.cuda.synchronize()
         for i, mb in enumerate(micro_batches):
             if mb.get("cu_seqlens") is not None and mb.get("position_ids") is not None:
                 validate_microbatch_metadata(mb, i)
@@ -195,6 +209,7 @@ class PipelineRunner:
             grp = self.pairs.groups[(self.rank, dst)]
             w = dist.isend(tensor, dst=self.pairs.my_ranks[dst], group=grp)
             sends.append((w, tensor))
+            prof["sent_bytes"] += tensor.numel() * tensor.element_size()
 
         def recv(kind, m, g, src, T):
             """Blocks until message (kind, m, g) from pipeline rank `src` has arrived; posts the
@@ -213,7 +228,15 @@ class PipelineRunner:
                 nxt += 1
             posted[(src, self.rank)] = nxt
             buf, w = recv_bufs.pop(key)
-            w.wait()
+            if profile:
+                _sync()
+                t0 = time.perf_counter()
+                w.wait()
+                _sync()
+                prof["wait_s"] += time.perf_counter() - t0
+                prof["waits"] += 1
+            else:
+                w.wait()
             return buf
 
         for op, m, c in self.actions[self.rank]:
@@ -282,4 +305,13 @@ class PipelineRunner:
         # the loss lives on the last stage: share it along the pipeline group
         if self.pp > 1 and self.ps.group("pp") is not None:
             dist.all_reduce(loss_total, group=self.ps.group("pp"))
+        if profile:
+            _sync()
+            step_s = time.perf_counter() - t_step
+            self.bubble_stats = {
+                "step_s": step_s, "wait_s": prof["wait_s"], "waits": prof["waits"],
+                "measured_bubble_fraction": prof["wait_s"] / max(step_s, 1e-9),
+                "analytic_bubble_fraction": S.analytic_bubble_fraction(self.schedule, self.pp, self.n_mb,
+                                                                       self.virtual_stages),
+                "p2p_sent_bytes": prof["sent_bytes"]}
         return loss_total

@@ -250,6 +250,11 @@ class Trainer:
                 self.meter.add(mb)
             total = self.pp_runner.run([self._to_device(mb) for mb in micro_batches],
                                        1.0 / global_tokens)
+            if self.pp_runner.bubble_stats:
+                b = self.pp_runner.bubble_stats
+                logger.info("pp rank %d: waited %.3f s of %.3f s (%.1f%%; unit-cost estimate %.1f%%), sent %.1f MB",
+                            self.ps.pp_rank, b["wait_s"], b["step_s"], 100 * b["measured_bubble_fraction"],
+                            100 * b["analytic_bubble_fraction"], b["p2p_sent_bytes"] / 1e6)
             micro_batches = []
         for mb in micro_batches:
             self.meter.add(mb)
@@ -385,6 +390,8 @@ class Trainer:
         self.memhist.close()
         result = {"loss_history": self.loss_history, "global_step": self.global_step,
                   "metrics": self.metrics_history[-1] if self.metrics_history else {}}
+        if self.pp_runner is not None and self.pp_runner.bubble_stats:
+            result["pp_bubble"] = dict(self.pp_runner.bubble_stats, pp_rank=self.ps.pp_rank)
         if self.ps.tp_sequence_parallel:
             from ..parallel.tp_fused import sp_context
             sp = sp_context()
