@@ -74,3 +74,24 @@ def test_validation():
         normalize_sampling_transforms(top_k=torch.tensor([1.0, 2.0]), rows=2, device="cpu")
     with pytest.raises(ValueError):
         normalize_sampling_transforms(min_p=torch.tensor([0.1], dtype=torch.float32), rows=2, device="cpu")
+
+
+def test_filtered_token_logprobs_chunks_and_gradients():
+    from xorl_b200.ops.sampling_transforms import filtered_token_logprobs
+    torch.manual_seed(2)
+    T, H, V = 50, 16, 40
+    h = torch.randn(T, H, requires_grad=True)
+    w = (torch.randn(V, H) * 0.3).requires_grad_()
+    logits = (h @ w.t()) / 0.7
+    labels = logits.argmax(-1)
+    labels[3] = -100
+    ks = torch.randint(2, 9, (T,))
+    lp, ok = filtered_token_logprobs(h, w, labels, temperature=0.7, top_k=ks, top_p=0.95, min_p=0.0, chunk_tokens=16)
+    want, ok2 = selected_logprob(logits, labels.clamp_min(0), ks, 0.95, 0.0)
+    keep = labels != -100
+    torch.testing.assert_close(lp[keep], want[keep], rtol=1e-5, atol=1e-5)
+    assert lp[3] == 0 and ok.all()
+    g1 = torch.autograd.grad(lp.sum(), [h, w])
+    g2 = torch.autograd.grad(want[keep].sum(), [h, w])
+    for a, b in zip(g1, g2):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)

@@ -107,3 +107,45 @@ def selected_logprob(logits: torch.Tensor, targets: torch.Tensor, top_k=TOP_K_AL
 def support_workspace_bytes(vocab_size: int, row_chunk: int = ROW_CHUNK) -> int:
     """Peak temporary bytes of one row chunk (sorted values + indices + probabilities + masks)."""
     return row_chunk * vocab_size * (4 + 8 + 4 + 4 + 2)
+
+
+def filtered_token_logprobs(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, *,
+                            temperature: float = 1.0, top_k=TOP_K_ALL, top_p=1.0, min_p=0.0,
+                            chunk_tokens: int = 1024, ignore_index: int = -100):
+    """Log-probability of every label token under the lm-head distribution restricted to the
+    sampling support, chunk by chunk so only ``chunk_tokens x vocab`` logits exist at a time.
+
+    ``hidden`` [T, H], ``weight`` [V, H], ``labels`` [T]; per-row ``top_k / top_p / min_p`` may be
+    tensors of shape [T].  Returns (logprobs [T] fp32, in_support [T] bool); ignored positions get 0
+    and True.  Differentiable in ``hidden`` and ``weight`` (each chunk's logits are recomputed in
+    backward through activation checkpointing, so they are never all alive)."""
+    from torch.utils.checkpoint import checkpoint
+    T = hidden.shape[0]
+    lab = labels.reshape(-1)
+    valid = lab != ignore_index
+    safe = torch.where(valid, lab, torch.zeros_like(lab))
+
+    def rows(v, s, e):
+        return v[s:e] if isinstance(v, torch.Tensor) else v
+
+    def chunk_fn(h, w, tgt, k, p, m):
+        logits = (h.float() @ w.float().t()) if not h.is_cuda else torch.nn.functional.linear(h, w).float()
+        if temperature != 1.0:
+            logits = logits / temperature
+        lp, ok = selected_logprob(logits, tgt, k, p, m)
+        return lp, ok
+
+    lps, oks = [], []
+    needs_grad = torch.is_grad_enabled() and (hidden.requires_grad or weight.requires_grad)
+    for s in range(0, T, chunk_tokens):
+        e = min(T, s + chunk_tokens)
+        args = (hidden[s:e], weight, safe[s:e], rows(top_k, s, e), rows(top_p, s, e), rows(min_p, s, e))
+        if needs_grad:
+            lp, ok = checkpoint(chunk_fn, *args, use_reentrant=False)
+        else:
+            lp, ok = chunk_fn(*args)
+        lps.append(lp)
+        oks.append(ok)
+    lp, ok = torch.cat(lps), torch.cat(oks)
+    lp = torch.where(valid, lp, torch.zeros_like(lp))
+    return lp, ok | ~valid
