@@ -193,6 +193,16 @@ def test_local_backend_trains_and_restores(tmp_path, tiny_runner):
         assert r["type"] == "load_weights", r
         back = fb("forward", "forward_input")["loss_fn_outputs"][1]["logprobs"]["data"]
         assert max(abs(x - y) for x, y in zip(a, back)) < 1e-5
+        # log-probabilities on the sampler's support: top_k = 1 leaves one token, so a label is either
+        # certain (0) or outside the support (-inf); wider filters only raise a kept label's value
+        top1 = fb("forward", "forward_input", cfg={"top_k": 1})
+        v1 = top1["loss_fn_outputs"][1]["logprobs"]["data"][:-1]
+        assert all(x == 0.0 or x <= -1e29 for x in v1)
+        assert top1["metrics"]["out_of_support_tokens"] == sum(
+            x <= -1e29 for o in top1["loss_fn_outputs"] for x in o["logprobs"]["data"])
+        wide = fb("forward", "forward_input", cfg={"top_p": 0.999, "temperature": 1.0})
+        vw = wide["loss_fn_outputs"][1]["logprobs"]["data"][:-1]
+        assert all(w >= x - 1e-5 for w, x in zip(vw, back[:-1]) if w > -1e29)
         # a policy-gradient loss through the same route
         rl = [dict(d) for d in data]
         for d in rl:

@@ -20,8 +20,11 @@ import torch
 import torch.distributed as dist
 
 from ..ops import rl_losses
+from ..ops.sampling_transforms import filtered_token_logprobs
 from ..ops.loss import fused_linear_token_loss
 from .packing import datums_to_micro_batch
+
+OUT_OF_SUPPORT_LOGPROB = -1.0e30     # reported for a label the sampling filter excludes
 
 IGNORE_INDEX = -100
 
@@ -183,6 +186,10 @@ class ModelRunner:
         self._activate(model_id)
         validate_token_ids(datums, self.model.config.vocab_size)
         logprobs: Dict[int, List[float]] = {}
+        cfg = loss_fn_config or {}
+        filt = {k: cfg[k] for k in ("top_k", "top_p", "min_p") if cfg.get(k) is not None}
+        temperature = float(cfg.get("temperature", 1.0))
+        outside = 0
         for mb in self._local_batches(datums, plan):
             d = {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in mb.items()}
             hidden = self.engine.forward_only(d["input_ids"], position_ids=d["position_ids"],
@@ -190,12 +197,21 @@ class ModelRunner:
             root, _ = self.engine._units_by_role()
             self.engine.gather(root)
             self.engine.wait_gather(root)
-            _, lp, _ = fused_linear_token_loss(hidden, self.model.lm_head.weight, d["labels"],
-                                               lambda lp, mask: (lp.sum() * 0, {}), 1.0)
+            if filt or temperature != 1.0:
+                # the sampler drew from a filtered distribution: report the log-probability on the
+                # same support (ops/sampling_transforms.py)
+                lp, ok = filtered_token_logprobs(hidden, self.model.lm_head.weight, d["labels"],
+                                                 temperature=temperature, **filt)
+                outside += int((~ok).sum())
+                lp = lp.clamp_min(OUT_OF_SUPPORT_LOGPROB)       # JSON has no -inf
+            else:
+                _, lp, _ = fused_linear_token_loss(hidden, self.model.lm_head.weight, d["labels"],
+                                                   lambda lp, mask: (lp.sum() * 0, {}), 1.0)
             lp = lp.float().cpu()
             for idx, (s, e) in zip(mb["datum_index"], mb["datum_spans"]):
                 logprobs[idx] = lp[s:e].tolist()
-        return {"logprobs": [logprobs.get(i, []) for i in range(len(datums))], "metrics": {}}
+        metrics = {"out_of_support_tokens": outside} if (filt or temperature != 1.0) else {}
+        return {"logprobs": [logprobs.get(i, []) for i in range(len(datums))], "metrics": metrics}
 
     def optim_step(self, model_id, adam_params=None, gradient_clip=None, **_):
         self._check_usable()
