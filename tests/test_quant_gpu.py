@@ -119,7 +119,7 @@ def test_symmetric_gemm_matches_full_product(M, K, block, dt):
     torch.manual_seed(0)
     x = (torch.randn(M, K, device="cuda") * 0.1).bfloat16()
     before = G.launch_count()
-    c = G.gemm_symmetric(x, out_dtype=dt, block=block)
+    c = G.gemm_symmetric(x, out_dtype=dt, block=block, min_rows=0)
     panels = -(-M // block)
     assert G.launch_count() == before + panels + 1
     full = G.gemm(x, x, out_dtype=dt)
@@ -130,14 +130,15 @@ def test_symmetric_gemm_matches_full_product(M, K, block, dt):
     assert (c.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
     # a product of two commuting symmetric factors
     a = full.to(torch.bfloat16)
-    s2 = G.gemm_symmetric(a, a, block=block).float()
+    s2 = G.gemm_symmetric(a, a, block=block, min_rows=0).float()
     ref2 = a.float() @ a.float().t()
     assert (s2 - ref2).abs().max() <= 3e-2 * ref2.abs().max()
 
 
-def test_muon_on_large_matrix_uses_symmetric_panels():
+def test_muon_on_large_matrix_uses_symmetric_panels(monkeypatch):
     from xorl_b200.ops import gemm as G
     from xorl_b200.optim.muon import newton_schulz
+    monkeypatch.setattr(G, "SYMMETRIC_MIN_ROWS", 0)          # the default keeps small matrices on the plain GEMM
     torch.manual_seed(1)
     Gm = torch.randn(2048, 2560, device="cuda")
     before = G.launch_count()
