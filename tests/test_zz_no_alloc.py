@@ -1,8 +1,8 @@
 """The allocation-free RMSNorm backward (``xb_rmsnorm_bwd_noalloc``).
 
-Some users of the kernel library cannot allocate GPU memory at the point where they call it (they
-are inside a capture, or all memory was handed out in advance), so they cannot supply the scratch
-buffer ``xb_rmsnorm_bwd`` wants.  This test drives the no-allocation variant through its exported C
+Some users of the kernel library cannot allocate GPU memory at the point where they call it (a
+host program that handed out all device memory in advance, a loop with a latency bound that an
+allocator call would break), so they cannot supply the scratch buffer ``xb_rmsnorm_bwd`` wants.  This test drives the no-allocation variant through its exported C
 symbol, twice in a row (the built-in scratch keeps the first call's contents), and compares with
 the regular entry point.  Output tensors are created before the calls; the calls themselves go
 straight to the C function."""
