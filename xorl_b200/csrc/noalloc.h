@@ -3,9 +3,8 @@
 // This header has no counterpart in the reference framework: the reference is pure Python on top
 // of PyTorch's caching allocator and has no notion of a caller that may not allocate.  It exists
 // for users who embed these kernels where cudaMalloc (or a framework allocator) is off limits —
-// inside a region that is being captured, in a latency-bounded loop, or in a host program that
-// pre-partitions all GPU memory — and who therefore cannot provide the scratch buffer that the
-// regular entry point asks for.
+// in a latency-bounded loop, or in a host program that pre-partitions all GPU memory — and who
+// therefore cannot provide the scratch buffer that the regular entry point asks for.
 #pragma once
 
 #ifdef __cplusplus
