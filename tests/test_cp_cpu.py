@@ -34,3 +34,27 @@ def test_zigzag_indices_cover_document():
     allidx = np.concatenate([zigzag_indices(L, cp, r) for r in range(cp)])
     assert sorted(allidx.tolist()) == list(range(L))
     assert zigzag_indices(L, cp, 0).tolist() == list(range(0, 8)) + list(range(56, 64))
+
+
+@pytest.mark.distributed
+def test_gated_deltanet_family_under_ulysses(tmp_path):
+    """Qwen3.5-style hybrid (GatedDeltaNet + gated attention) with every document cut across two
+    sequence-parallel ranks: same losses as one process."""
+    import yaml
+    from dist_utils import run_distributed
+    from xorl_b200.cli.train import main
+    from xorl_b200.parallel.state import reset_parallel_state
+
+    def cfg(name, **train):
+        path = _cfg(tmp_path, name, **train)
+        c = yaml.safe_load(open(path))
+        c["model"] = {"config_path": "tiny-qwen3-5", "foundation": {"tie_word_embeddings": False}}
+        open(path, "w").write(yaml.safe_dump(c))
+        return path
+    reset_parallel_state()
+    main([cfg("gdn_ref", gradient_accumulation_steps=2)])
+    ref = _losses(tmp_path, "gdn_ref")
+    run_distributed("-m", 2, "xorl_b200.cli.train", cfg("gdn_cp", ulysses_parallel_size=2, gradient_accumulation_steps=2))
+    got = _losses(tmp_path, "gdn_cp")
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 3e-4, (ref, got)

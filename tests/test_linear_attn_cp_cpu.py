@@ -85,5 +85,62 @@ def test_cp_delta_rule_and_conv_match_single_process(world):
     run_distributed(__file__, world)
 
 
+
+
+def _worker_docs():
+    """Per-document sharding (every document cut into `world` pieces), including 2-token pieces."""
+    import datetime
+    import torch.distributed as dist
+    from xorl_b200.models.gated_deltanet import gated_delta_rule
+    from xorl_b200.ops.seqmix import causal_conv1d_reference
+    from xorl_b200.parallel.linear_attn_cp import causal_conv1d_cp_docs, gated_delta_rule_cp_docs
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=120))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(0)
+    pieces = [2, 20, 1, 37]                                           # piece length of each document
+    lens = [p * world for p in pieces]
+    T = sum(lens)
+    gcu = [0]
+    for l in lens:
+        gcu.append(gcu[-1] + l)
+    f = lambda *s: torch.randn(*s, dtype=torch.float64)
+    q = torch.nn.functional.normalize(f(T, H, DK), dim=-1)
+    k = torch.nn.functional.normalize(f(T, H, DK), dim=-1)
+    v, g, beta = f(T, H, DV), -torch.rand(T, H, dtype=torch.float64), torch.rand(T, H, dtype=torch.float64)
+    x, w, wo, wy = f(T, C), f(C, K), f(T, H, DV), f(T, C)
+    sel = torch.cat([torch.arange(gcu[d] + rank * p, gcu[d] + (rank + 1) * p) for d, p in enumerate(pieces)])
+    lcu = [0]
+    for p in pieces:
+        lcu.append(lcu[-1] + p)
+    full = [t.clone().requires_grad_() for t in (q, k, v, g, beta, x, w)]
+    ro = gated_delta_rule(*full[:5], torch.tensor(gcu))
+    ry = causal_conv1d_reference(full[5], full[6], None, torch.tensor(gcu), True)
+    ((ro * wo).sum() + (ry * wy).sum()).backward()
+    loc = [t[sel].clone().requires_grad_() for t in (q, k, v, g, beta, x)]
+    wl = w.clone().requires_grad_()
+    o = gated_delta_rule_cp_docs(*loc[:5], torch.tensor(lcu, dtype=torch.int32), dist.group.WORLD, chunk=16)
+    y = causal_conv1d_cp_docs(loc[5], wl, None, torch.tensor(lcu, dtype=torch.int32), dist.group.WORLD, silu=True)
+    torch.testing.assert_close(o, ro[sel], rtol=2e-3, atol=2e-4)
+    torch.testing.assert_close(y, ry[sel], rtol=2e-3, atol=2e-4)
+    ((o * wo[sel]).sum() + (y * wy[sel]).sum()).backward()
+    for got, want in zip(loc, full[:6]):
+        torch.testing.assert_close(got.grad, want.grad[sel], rtol=2e-3, atol=2e-4)
+    gw = wl.grad.clone()
+    dist.all_reduce(gw)
+    torch.testing.assert_close(gw, full[6].grad, rtol=2e-3, atol=2e-4)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("world", [2, 3])
+def test_cp_per_document_sharding_matches_single_process(world):
+    from dist_utils import run_distributed
+    run_distributed(__file__, world, "docs")
+
+
 if __name__ == "__main__":
-    _worker()
+    if len(sys.argv) > 1 and sys.argv[1] == "docs":
+        _worker_docs()
+    else:
+        _worker()

@@ -71,28 +71,33 @@ def gated_delta_rule(q, k, v, g, beta, cu_seqlens):
 def _chunk_index(cu, T: int, chunk: int, device):
     """Rows of token indices, one row per chunk of one document (``-1`` pads), and a flag per row
     that is 1 where the row opens a document."""
-    rows, first = [], []
+    rows, first, doc = [], [], []
     for b in range(len(cu) - 1):
         s, e = cu[b], cu[b + 1]
         for c0 in range(s, e, chunk):
             c1 = min(e, c0 + chunk)
             rows.append(list(range(c0, c1)) + [-1] * (chunk - (c1 - c0)))
             first.append(1.0 if c0 == s else 0.0)
+            doc.append(b)
     if not rows:
-        rows, first = [[-1] * chunk], [1.0]
+        rows, first, doc = [[-1] * chunk], [1.0], [0]
     return (torch.tensor(rows, dtype=torch.long, device=device),
-            torch.tensor(first, dtype=torch.float32, device=device))
+            torch.tensor(first, dtype=torch.float32, device=device), doc)
 
 
 def gated_delta_rule_chunked(q, k, v, g, beta, cu_seqlens, chunk: int = CHUNK, initial_state=None,
                              return_final_state: bool = False):
     """Same contract as ``gated_delta_rule``.  ``initial_state`` [H, dk, dv] seeds the first
-    document; with ``return_final_state`` the state after the last document's last token is
-    returned as well (both are what a context-parallel rank exchanges with its neighbours)."""
+    document, or [D, H, dk, dv] seeds every document; with ``return_final_state`` the state after
+    the last document's last token is returned as well, with ``return_final_state="all"`` the
+    states after every document [D, H, dk, dv] (zeros for empty documents).  These are what
+    context-parallel ranks exchange with their neighbours."""
     T, H, dk = q.shape
     dv = v.shape[-1]
     cu = cu_seqlens.tolist()
-    idx, first = _chunk_index(cu, T, chunk, q.device)
+    idx, first, doc_of = _chunk_index(cu, T, chunk, q.device)
+    n_docs = len(cu) - 1
+    per_doc = initial_state is not None and initial_state.dim() == 4
     N = idx.shape[0]
     valid = (idx >= 0)
     gi = idx.clamp_min(0)
@@ -122,19 +127,30 @@ def gated_delta_rule_chunked(q, k, v, g, beta, cu_seqlens, chunk: int = CHUNK, i
     Kdec = torch.exp(G[..., -1:] - G).unsqueeze(-1) * K                     # gamma_C / gamma_j k_j
 
     S = torch.zeros(H, dk, dv, dtype=torch.float32, device=q.device)
+    zero_state = S
     outs = []
+    finals = {}
+    first_l = first.tolist()
     for n in range(N):
-        if n == 0 and initial_state is not None:
-            S = initial_state.float()
-        elif first[n] > 0:
-            S = torch.zeros_like(S)
+        if first_l[n] > 0:
+            if per_doc:
+                S = initial_state[doc_of[n]].float()
+            elif n == 0 and initial_state is not None:
+                S = initial_state.float()
+            else:
+                S = zero_state
         U = TV[n] - W[n] @ S
         outs.append(Qg[n] @ S + Aqk[n] @ U)
         S = g_end[n].view(H, 1, 1) * S + Kdec[n].transpose(-1, -2) @ U
+        finals[doc_of[n]] = S
     O = torch.stack(outs, 0).permute(0, 2, 1, 3)                            # [N, C, H, dv]
     out = torch.zeros(T, H, dv, dtype=torch.float32, device=q.device)
     out = out.index_put((idx[valid],), O[valid])
     out = out.to(v.dtype)
+    if return_final_state == "all":
+        # a document without tokens leaves its entering state untouched
+        return out, torch.stack([finals.get(d, initial_state[d].float() if per_doc else zero_state)
+                                 for d in range(max(n_docs, 1))], 0)
     return (out, S) if return_final_state else out
 
 
@@ -167,14 +183,22 @@ class GatedDeltaNet(nn.Module):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T = x.shape[0]
         cu = ctx.cu_seqlens
+        cp_group = None
         if ctx.cp is not None:
-            # the trainer's sequence-shard collator cuts every document across the ranks, while the
-            # state hand-over of parallel/linear_attn_cp.py works on contiguous token shards
-            raise NotImplementedError("GatedDeltaNet layers do not run under ulysses / ring context "
-                                      "parallelism yet: use tensor, pipeline or data parallelism")
-        q = causal_conv1d(self.q_proj(x), self.q_conv1d, None, cu, silu=True)
-        k = causal_conv1d(self.k_proj(x), self.k_conv1d, None, cu, silu=True)
-        v = causal_conv1d(self.v_proj(x), self.v_conv1d, None, cu, silu=True)
+            # Ulysses sharding: every document is cut into contiguous pieces, rank u holds piece u;
+            # states and convolution tails are handed over per document (parallel/linear_attn_cp.py)
+            if getattr(ctx.cp, "R", 1) > 1:
+                raise NotImplementedError("GatedDeltaNet layers do not run under ring (zigzag) context "
+                                          "parallelism: use ulysses_parallel_size instead")
+            from ..parallel.linear_attn_cp import causal_conv1d_cp_docs, gated_delta_rule_cp_docs
+            cp_group = ctx.cp.u_group
+            cu = ctx.aux["local_cu_seqlens"]
+            conv = lambda t, w: causal_conv1d_cp_docs(t, w, None, cu, cp_group, silu=True)
+        else:
+            conv = lambda t, w: causal_conv1d(t, w, None, cu, silu=True)
+        q = conv(self.q_proj(x), self.q_conv1d)
+        k = conv(self.k_proj(x), self.k_conv1d)
+        v = conv(self.v_proj(x), self.v_conv1d)
         beta = torch.sigmoid(self.b_proj(x).float())
         g = -torch.exp(self.A_log.float()) * F.softplus(self.a_proj(x).float() + self.dt_bias.float())
         q = F.normalize(q.view(T, self.Hk, self.dk).float(), dim=-1) * self.dk ** -0.5
@@ -182,7 +206,10 @@ class GatedDeltaNet(nn.Module):
         if self.Hv > self.Hk:
             rep = self.Hv // self.Hk
             q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
-        o = gated_delta_rule_chunked(q, k, v.view(T, self.Hv, self.dv), g, beta, cu).float()
+        if cp_group is not None:
+            o = gated_delta_rule_cp_docs(q, k, v.view(T, self.Hv, self.dv), g, beta, cu, cp_group).float()
+        else:
+            o = gated_delta_rule_chunked(q, k, v.view(T, self.Hv, self.dv), g, beta, cu).float()
         z = self.g_proj(x).view(T, self.Hv, self.dv).float()
         o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.eps) * self.o_norm_weight.float()
         o = (o * F.silu(z)).to(x.dtype)

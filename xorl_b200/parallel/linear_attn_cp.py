@@ -148,3 +148,67 @@ def causal_conv1d_cp(x, weight, bias, global_cu, group, silu: bool = True):
     ext = torch.cat([halo, x], 0)
     y = causal_conv1d(ext, weight, bias, torch.tensor(local_cu, dtype=torch.int32, device=x.device), silu=silu)
     return y[n:]
+
+
+# ---- per-document sharding (the trainer's Ulysses layout) ---------------------------------------
+def gated_delta_rule_cp_docs(q, k, v, g, beta, local_cu, group, chunk: int = 64):
+    """Every document of the packed batch is cut into R contiguous pieces and this rank holds piece
+    ``rank`` of each; ``local_cu`` delimits the local pieces.  One widened pass gives the affine
+    map (M, B) of every local piece, one all-gather exchanges them, each rank folds the maps of the
+    earlier pieces per document and a second pass produces the outputs."""
+    from ..models.gated_deltanet import gated_delta_rule_chunked
+    rank = dist.get_rank(group)
+    T, H, dk = q.shape
+    dv = v.shape[-1]
+    cu = local_cu.cpu() if torch.is_tensor(local_cu) else torch.tensor(local_cu)
+    D = cu.numel() - 1
+    v_wide = torch.cat([v.float(), torch.zeros(T, H, dk, device=q.device)], dim=-1)
+    S0 = torch.cat([torch.zeros(H, dk, dv, device=q.device),
+                    torch.eye(dk, device=q.device).expand(H, dk, dk)], dim=-1).expand(D, H, dk, dk + dv)
+    _, S = gated_delta_rule_chunked(q, k, v_wide, g, beta, cu, chunk, initial_state=S0,
+                                    return_final_state="all")                # [D, H, dk, dv + dk]
+    MB = all_gather_with_grad(S, group)                                       # [R, D, H, dk, dv + dk]
+    B_all, M_all = MB[..., :dv], MB[..., dv:]
+    S_in = torch.zeros(D, H, dk, dv, dtype=torch.float32, device=q.device) + 0.0 * MB.sum()
+    for j in range(rank):
+        S_in = M_all[j] @ S_in + B_all[j]
+    return gated_delta_rule_chunked(q, k, v, g, beta, cu, chunk, initial_state=S_in)
+
+
+def causal_conv1d_cp_docs(x, weight, bias, local_cu, group, silu: bool = True):
+    """Short convolution under the same per-document sharding: in front of every local piece go
+    the last K - 1 tokens of the document's earlier pieces (from as many earlier ranks as needed
+    when pieces are shorter than K - 1)."""
+    from ..ops.seqmix import causal_conv1d
+    rank = dist.get_rank(group)
+    n = weight.shape[1] - 1
+    cu = [int(c) for c in (local_cu.tolist() if torch.is_tensor(local_cu) else local_cu)]
+    D, C = len(cu) - 1, x.shape[1]
+    if n <= 0:
+        return causal_conv1d(x, weight, bias, torch.tensor(cu, dtype=torch.int32, device=x.device), silu=silu)
+    tails = []
+    for s, e in zip(cu[:-1], cu[1:]):
+        take = min(e - s, n)
+        t = x[e - take:e]
+        if take < n:
+            t = torch.cat([x.new_zeros((n - take, C)), t], 0)
+        tails.append(t)
+    gathered = all_gather_with_grad(torch.stack(tails, 0), group)            # [R, D, n, C]
+    parts, ext_cu, keep = [], [0], []
+    for d, (s, e) in enumerate(zip(cu[:-1], cu[1:])):
+        p = e - s
+        rows, need, j = [], n, rank - 1
+        while need > 0 and j >= 0 and p > 0:
+            t = min(p, need)
+            rows.insert(0, gathered[j, d, n - t:n])
+            need -= t
+            j -= 1
+        if need > 0:
+            rows.insert(0, gathered[rank, d, :need] * 0.0)                   # document start: zeros
+        parts += rows + [x[s:e]]
+        base = ext_cu[-1]
+        keep.append(torch.arange(base + n, base + n + p))
+        ext_cu.append(base + n + p)
+    ext = torch.cat(parts, 0)
+    y = causal_conv1d(ext, weight, bias, torch.tensor(ext_cu, dtype=torch.int32, device=x.device), silu=silu)
+    return y[torch.cat(keep).to(x.device)]

@@ -305,13 +305,18 @@ class ContextParallelStrategy:
         """qkv: local tokens, all (tensor-parallel-local) heads.  Returns [T_loc, Hq*D]."""
         Hq, Hkv, D = attn.Hq, attn.Hkv, attn.D
         T = qkv.shape[0]
-        q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
-        q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
-        if attn.use_qk_norm:
-            q = attn_ops._head_rmsnorm_ref(q, attn.q_norm.weight, attn.cfg.rms_norm_eps)
-            k = attn_ops._head_rmsnorm_ref(k, attn.k_norm.weight, attn.cfg.rms_norm_eps)
-        q = attn_ops.rope_reference(q, ctx.cos, ctx.sin)
-        k = attn_ops.rope_reference(k, ctx.cos, ctx.sin)
+        if hasattr(attn, "_qkv_heads"):
+            # the layer's own norm / rotary variants (whole-projection or per-head norms, partial
+            # rotary, no positional embedding) on this rank's tokens at their global positions
+            q, k, v = attn._qkv_heads(qkv, ctx)
+        else:
+            q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+            q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
+            if attn.use_qk_norm:
+                q = attn_ops._head_rmsnorm_ref(q, attn.q_norm.weight, attn.cfg.rms_norm_eps)
+                k = attn_ops._head_rmsnorm_ref(k, attn.k_norm.weight, attn.cfg.rms_norm_eps)
+            q = attn_ops.rope_reference(q, ctx.cos, ctx.sin)
+            k = attn_ops.rope_reference(k, ctx.cos, ctx.sin)
         U = self.U
         if U > 1:
             if Hkv % U:
