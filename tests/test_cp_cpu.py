@@ -37,9 +37,10 @@ def test_zigzag_indices_cover_document():
 
 
 @pytest.mark.distributed
-def test_gated_deltanet_family_under_ulysses(tmp_path):
-    """Qwen3.5-style hybrid (GatedDeltaNet + gated attention) with every document cut across two
-    sequence-parallel ranks: same losses as one process."""
+@pytest.mark.parametrize("preset", ["tiny-qwen3-5", "tiny-nemotron-h"])
+def test_gated_deltanet_family_under_ulysses(tmp_path, preset):
+    """Hybrid families (GatedDeltaNet + gated attention; Mamba2 + rotary-free attention + MoE) with
+    every document cut across two sequence-parallel ranks: same losses as one process."""
     import yaml
     from dist_utils import run_distributed
     from xorl_b200.cli.train import main
@@ -48,7 +49,7 @@ def test_gated_deltanet_family_under_ulysses(tmp_path):
     def cfg(name, **train):
         path = _cfg(tmp_path, name, **train)
         c = yaml.safe_load(open(path))
-        c["model"] = {"config_path": "tiny-qwen3-5", "foundation": {"tie_word_embeddings": False}}
+        c["model"] = {"config_path": preset, "foundation": {"tie_word_embeddings": False}}
         open(path, "w").write(yaml.safe_dump(c))
         return path
     reset_parallel_state()

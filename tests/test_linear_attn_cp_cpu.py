@@ -139,8 +139,56 @@ def test_cp_per_document_sharding_matches_single_process(world):
     run_distributed(__file__, world, "docs")
 
 
+def _worker_ssd():
+    import datetime
+    import torch.distributed as dist
+    from xorl_b200.models.mamba2 import segment_ids, ssd_reference
+    from xorl_b200.parallel.linear_attn_cp import ssd_cp_docs
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=120))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(0)
+    pieces = [2, 20, 1, 37]
+    gcu = [0]
+    for p in pieces:
+        gcu.append(gcu[-1] + p * world)
+    T, Hh, P, G, N = gcu[-1], 4, 6, 2, 5
+    f = lambda *s: torch.randn(*s, dtype=torch.float64)
+    x, dt = f(T, Hh, P), torch.rand(T, Hh, dtype=torch.float64) * 0.5 + 0.01
+    A, Bm, Cm, Dv, wy = -torch.rand(Hh, dtype=torch.float64) - 0.1, f(T, G, N), f(T, G, N), f(Hh), f(T, Hh, P)
+    sel = torch.cat([torch.arange(gcu[d] + rank * p, gcu[d] + (rank + 1) * p) for d, p in enumerate(pieces)])
+    lcu = [0]
+    for p in pieces:
+        lcu.append(lcu[-1] + p)
+    full = [t.clone().requires_grad_() for t in (x, dt, A, Bm, Cm, Dv)]
+    ref = ssd_reference(*full, segment_ids(torch.tensor(gcu), T))
+    (ref * wy).sum().backward()
+    loc = [t[sel].clone().requires_grad_() for t in (x, dt)]
+    Al, Dl = A.clone().requires_grad_(), Dv.clone().requires_grad_()
+    Bl, Cl = Bm[sel].clone().requires_grad_(), Cm[sel].clone().requires_grad_()
+    y = ssd_cp_docs(loc[0], loc[1], Al, Bl, Cl, Dl, torch.tensor(lcu, dtype=torch.int32), dist.group.WORLD, chunk=8)
+    torch.testing.assert_close(y.double(), ref[sel].double(), rtol=2e-3, atol=2e-4)
+    (y * wy[sel]).sum().backward()
+    for got, want in ((loc[0], full[0]), (loc[1], full[1]), (Bl, full[3]), (Cl, full[4])):
+        torch.testing.assert_close(got.grad.double(), want.grad[sel].double(), rtol=2e-3, atol=2e-4)
+    for got, want in ((Al, full[2]), (Dl, full[5])):
+        gsum = got.grad.clone()
+        dist.all_reduce(gsum)
+        torch.testing.assert_close(gsum.double(), want.grad.double(), rtol=2e-3, atol=2e-4)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.distributed
+@pytest.mark.parametrize("world", [2, 3])
+def test_cp_mamba2_scan_matches_single_process(world):
+    from dist_utils import run_distributed
+    run_distributed(__file__, world, "ssd")
+
+
 if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "docs":
         _worker_docs()
+    elif len(sys.argv) > 1 and sys.argv[1] == "ssd":
+        _worker_ssd()
     else:
         _worker()

@@ -149,18 +149,33 @@ class Mamba2Mixer(nn.Module):
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         T = h.shape[0]
+        cp_group = None
         if ctx.cp is not None:
-            raise NotImplementedError("Mamba2 layers do not run under ulysses / ring context parallelism: "
-                                      "the scan state is not handed across sequence shards")
+            # Ulysses sharding (rank u holds piece u of every document): convolution tails and scan
+            # states cross the ranks per document (parallel/linear_attn_cp.py)
+            if getattr(ctx.cp, "R", 1) > 1:
+                raise NotImplementedError("Mamba2 layers do not run under ring (zigzag) context parallelism: "
+                                          "use ulysses_parallel_size instead")
+            cp_group = ctx.cp.u_group
+            local_cu = ctx.aux["local_cu_seqlens"]
         proj = self.in_proj(h)
         gate, xbc, dt = proj.split([self.d_inner, self.conv_dim, self.H], dim=-1)
-        xbc = causal_conv1d(xbc.contiguous(), self.conv1d_weight, self.conv1d_bias, ctx.cu_seqlens, silu=True)
+        if cp_group is not None:
+            from ..parallel.linear_attn_cp import causal_conv1d_cp_docs, ssd_cp_docs
+            xbc = causal_conv1d_cp_docs(xbc.contiguous(), self.conv1d_weight, self.conv1d_bias, local_cu,
+                                        cp_group, silu=True)
+        else:
+            xbc = causal_conv1d(xbc.contiguous(), self.conv1d_weight, self.conv1d_bias, ctx.cu_seqlens, silu=True)
         x, B, C = xbc.split([self.d_inner, self.G * self.N, self.G * self.N], dim=-1)
         dt = torch.clamp(F.softplus(dt.float() + self.dt_bias.float()), self.dt_limit[0], self.dt_limit[1])
         A = -torch.exp(self.A_log.float())
-        seg = segment_ids(ctx.cu_seqlens, T)
-        y = ssd_chunked(x.reshape(T, self.H, self.P), dt, A, B.reshape(T, self.G, self.N),
-                        C.reshape(T, self.G, self.N), self.D, seg, self.chunk)
+        if cp_group is not None:
+            y = ssd_cp_docs(x.reshape(T, self.H, self.P), dt, A, B.reshape(T, self.G, self.N),
+                            C.reshape(T, self.G, self.N), self.D, local_cu, cp_group, self.chunk)
+        else:
+            seg = segment_ids(ctx.cu_seqlens, T)
+            y = ssd_chunked(x.reshape(T, self.H, self.P), dt, A, B.reshape(T, self.G, self.N),
+                            C.reshape(T, self.G, self.N), self.D, seg, self.chunk)
         y = gated_group_rmsnorm(y.reshape(T, self.d_inner).to(h.dtype), gate, self.norm_weight,
                                 self.d_inner // self.G, self.eps)
         return self.out_proj(y.to(h.dtype))

@@ -212,3 +212,43 @@ def causal_conv1d_cp_docs(x, weight, bias, local_cu, group, silu: bool = True):
     ext = torch.cat(parts, 0)
     y = causal_conv1d(ext, weight, bias, torch.tensor(ext_cu, dtype=torch.int32, device=x.device), silu=silu)
     return y[torch.cat(keep).to(x.device)]
+
+
+def ssd_cp_docs(x, dt, A, B, C, D, local_cu, group, chunk: int = 128):
+    """Mamba2 scan under per-document sharding.  The state update S_t = a_t S_{t-1} + dt_t x_t (x) B_t
+    has a scalar decay per head, so a piece's map is (prod a, state reached from zero): the local
+    scan runs from a zero state, the pieces' (log-decay, end state) pairs are all-gathered, every
+    rank folds the earlier pieces of each document into the state entering its piece, and adds the
+    missing term  y_t += (prod_{tau <= t} a_tau) * S_in C_t  to its outputs.
+
+    x [T, H, P], dt [T, H] (after softplus / clamp), A [H], B, C [T, G, N], D [H] -> y [T, H, P] fp32."""
+    from ..models.mamba2 import segment_ids, ssd_chunked
+    rank = dist.get_rank(group)
+    T, H, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    rep = H // G
+    cu = (local_cu.cpu() if torch.is_tensor(local_cu) else torch.tensor(local_cu)).to(torch.int64)
+    n_docs = cu.numel() - 1
+    seg = segment_ids(cu.to(x.device), T)
+    y = ssd_chunked(x, dt, A, B, C, D, seg, chunk)
+    la = dt.float() * A.float()                                             # log a_t  [T, H]
+    cs = torch.cat([la.new_zeros(1, H), la.cumsum(0)], 0)                   # exclusive prefix sums
+    cud = cu.to(x.device)
+    base, end = cs[cud[:-1]], cs[cud[1:]]                                   # [D, H]
+    inc = cs[1:] - base[seg]                                                # log decay from piece start through t
+    total = end - base                                                      # log decay of the whole piece
+    w = torch.exp(total[seg] - inc) * dt.float()                            # weight of token t in the end state
+    xf, Bh, Ch = x.float(), B.float().repeat_interleave(rep, 1), C.float().repeat_interleave(rep, 1)
+    bounds = list(zip(cu[:-1].tolist(), cu[1:].tolist()))
+    ends = [torch.einsum("thp,thn->hpn", w[s:e].unsqueeze(-1) * xf[s:e], Bh[s:e]) for s, e in bounds]
+    S_end = torch.stack(ends, 0) if ends else xf.new_zeros(0, H, P, N)
+    packed = torch.cat([S_end.reshape(n_docs, H, P * N), total.unsqueeze(-1)], dim=-1)
+    allp = all_gather_with_grad(packed, group)                              # [R, D, H, P*N + 1]
+    S_in = torch.zeros(n_docs, H, P, N, dtype=torch.float32, device=x.device) + 0.0 * allp.sum()
+    for j in range(rank):
+        S_in = torch.exp(allp[j][..., -1]).view(n_docs, H, 1, 1) * S_in + allp[j][..., :-1].reshape(n_docs, H, P, N)
+    parts = [torch.exp(inc[s:e]).unsqueeze(-1) * torch.einsum("hpn,thn->thp", S_in[d], Ch[s:e])
+             for d, (s, e) in enumerate(bounds)]
+    if parts:
+        y = y + torch.cat(parts, 0)
+    return y
