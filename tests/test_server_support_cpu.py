@@ -93,3 +93,9 @@ def test_side_payload_store(tmp_path):
     assert store.sweep(now=os.path.getmtime(tmp_path / "payloads" / (ref["key"] + ".pt")) + 11) == 1
     with pytest.raises(PayloadError):
         store.get(ref)
+
+
+def test_r3_staging_benchmark_runs(capsys):
+    from xorl_b200.utils.r3_staging_bench import main
+    out = main(["--datums", "6", "--tokens", "128", "--layers", "3", "--top-k", "2", "--pack-len", "512"])
+    assert out["micro_batches"] >= 2 and out["payload_mb"] > 0 and out["store_put_s"] > 0
