@@ -77,7 +77,7 @@ def datums_to_micro_batch(datums: List[Dict[str, Any]], pad_to: int = 128) -> Di
         cu.append(cu[-1] + n)
         for k, v in d.items():
             if k == "routed_experts":
-                routed.append(torch.tensor(v, dtype=torch.long))
+                routed.append(torch.as_tensor(v).to(torch.long))
                 continue
             if k in ("tokens", "target_tokens", "weights", "datum_index"):
                 continue
