@@ -1,8 +1,9 @@
 """Reference arm of bench.py: runs the UNMODIFIED reference (installed under ``baseline/_ref``)
 through its own public API — ``xorl.arguments.parse_args`` -> ``xorl.trainers.trainer.Trainer`` ->
 ``Trainer.train_step`` — on the same metric and configuration as our arm: Qwen3-8B, bf16, FSDP2,
-seq 4096, micro-batch 1 per GPU, packed documents with lengths U[256, 4096], AdamW, gradient
-checkpointing on, random-init weights.  None of this repository's models, kernels or engine is
+seq 4096, micro-batch 1 per GPU, packed documents with lengths U[256, 4096], AdamW, activations
+kept (``gradient_checkpointing_method: no_recompute``, the faster setting for both arms; ``--recompute
+full`` turns recomputation on in both), random-init weights.  None of this repository's models, kernels or engine is
 imported on this path.
 
 Offline constraints recorded here: the reference's FlashAttention-3/4 wheels are not installed in
@@ -37,6 +38,18 @@ def _unavailable(why: str) -> None:
         print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
 
 
+def _recompute_method(choice: str, world: int) -> str:
+    """The reference's own ``train.gradient_checkpointing_method`` values.  ``auto`` keeps the
+    activations (no recomputation) when the sharded state leaves room for them, as our arm does."""
+    if choice == "full":
+        return "recompute_full_layer"
+    if choice == "none":
+        return "no_recompute"
+    # measured on one B200: the reference holds Qwen3-8B's activations beside the unsharded state
+    # (691 ms/step against 756 ms with recomputation), so fewer parameters per rank fit as well
+    return "no_recompute"
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -65,7 +78,7 @@ def _write_model_dir(path: str, layers: int = 0) -> None:
     fast.save_pretrained(path)
 
 
-def _yaml(model_dir: str, out_dir: str, seq_len: int, world: int) -> str:
+def _yaml(model_dir: str, out_dir: str, seq_len: int, world: int, gcm: str) -> str:
     return f"""
 model:
   config_path: {model_dir}
@@ -95,6 +108,7 @@ train:
   max_grad_norm: 1.0
   enable_mixed_precision: true
   enable_gradient_checkpointing: true
+  gradient_checkpointing_method: {gcm}
   init_device: meta
   num_train_epochs: 1000
   max_steps: 1000000
@@ -122,23 +136,27 @@ def run_reference(a) -> None:
     # the reference must be importable as `xorl`; this repository's own package must not be used
     sys.path = [p for p in sys.path if os.path.abspath(p or ".") != ROOT]
     sys.path.insert(0, REF)
-    work = os.path.join(ROOT, "gpurun_out", "ref_run")
+    scratch = getattr(a, "scratch_dir", "") or os.path.join(__import__("tempfile").gettempdir(), "xorl_b200_bench")
+    work = os.path.join(scratch, "ref_run")
+    gcm = _recompute_method(getattr(a, "recompute", "auto"), world)
     model_dir = os.path.join(work, "qwen3_8b")
+    # named after this launch's rendezvous port, so ranks never pick up an earlier run's file
+    cfg_path = os.path.join(work, f"cfg_{os.environ['MASTER_PORT']}_{gcm}.yaml")
     try:
         if rank == 0:
             _write_model_dir(model_dir, getattr(a, "layers", 0))
-            with open(os.path.join(work, "cfg.yaml"), "w") as f:
-                f.write(_yaml(model_dir, os.path.join(work, "out"), a.seq_len, world))
+            with open(cfg_path, "w") as f:
+                f.write(_yaml(model_dir, os.path.join(work, "out"), a.seq_len, world, gcm))
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
         # wait for rank 0's files without a collective (the reference initialises the process group)
         for _ in range(600):
-            if os.path.exists(os.path.join(work, "cfg.yaml")):
+            if os.path.exists(cfg_path):
                 break
             time.sleep(0.1)
         time.sleep(0.5 if rank else 0.0)
-        sys.argv = ["xorl.cli.train", os.path.join(work, "cfg.yaml")]
+        sys.argv = ["xorl.cli.train", cfg_path]
         from xorl.arguments import Arguments, parse_args
         from xorl.trainers.trainer import Trainer
         args = parse_args(Arguments)
@@ -240,6 +258,7 @@ def _measure(trainer, a, world: int, rank: int) -> None:
             "config": {"model": "qwen3-8b" + (f"[{a.layers} layers: DEBUG]" if getattr(a, "layers", 0) else ""),
                        "global_batch": world, "seq_len": seq_len, "parallelism": f"fsdp{world}",
                        "attn_implementation": str(args.model.attn_implementation),
+                       "recompute": str(args.train.gradient_checkpointing_method),
                        "l2": "per-step working set >> 126 MB L2",
                        "packed_docs": "lengths U[256,4096], tokens U[vocab]"},
             "clocks": clocks,

@@ -41,6 +41,11 @@ def parse():
     ap.add_argument("--ep", type=int, default=0,
                     help="expert-parallel size for MoE models (0: all ranks for MoE, 1 for dense)")
     ap.add_argument("--ep-dispatch", default="fused", choices=["fused", "alltoall"])
+    ap.add_argument("--recompute", default="auto", choices=["auto", "full", "none"],
+                    help="activation recomputation; auto keeps activations when they fit (both arms "
+                         "use their own gradient_checkpointing_method key)")
+    ap.add_argument("--scratch-dir", default=os.environ.get("XORL_BENCH_SCRATCH", ""),
+                    help="where the run may write its output directory (default: a temp dir)")
     return ap.parse_args()
 
 
@@ -115,6 +120,37 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
+def scratch_dir(a) -> str:
+    if a.scratch_dir:
+        os.makedirs(a.scratch_dir, exist_ok=True)
+        return a.scratch_dir
+    import tempfile
+    d = os.path.join(tempfile.gettempdir(), "xorl_b200_bench")
+    os.makedirs(d, exist_ok=True)
+    return d
+
+
+def resolve_recompute(a, cfg, world: int) -> str:
+    """Recomputation costs one extra forward per layer; it is only needed when the activations of
+    all layers do not fit beside the sharded state.  ``auto`` turns it off whenever a rank's
+    parameter/optimizer state (18 bytes per parameter over the shard group) plus the stored
+    activations stay below the device memory with a safety margin."""
+    if a.recompute == "full":
+        return "recompute_full_layer"
+    if a.recompute == "none":
+        return "no_recompute"
+    import torch
+    total = torch.cuda.get_device_properties(0).total_memory if torch.cuda.is_available() else 0
+    if cfg.is_moe:
+        return "recompute_full_layer"      # expert workspaces are reused layer by layer
+    params = cfg.num_parameters() if hasattr(cfg, "num_parameters") else 8.2e9
+    state = 18.0 * params / world + (2.0 * params if world > 1 else 0.0)
+    L, H, I = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size
+    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    acts = a.seq_len * 2.0 * L * (6 * H + 2 * qkv + 3 * I)
+    return "no_recompute" if state + acts + 12e9 < total else "recompute_full_layer"
+
+
 def launch_total():
     from xorl_b200.ops import activation, attention, embedding, gemm, loss, norm, optim
     return sum(m.launch_count() for m in (activation, attention, embedding, gemm, loss, norm, optim))
@@ -137,7 +173,8 @@ def run_ours(a):
     ep = (a.ep or (world if cfg.is_moe else 1)) if cfg.is_moe else 1
     moe_train = dict(expert_parallel_size=ep, softmax_auxiliary_loss=True, auxiliary_loss_multiplier=1e-3) \
         if cfg.is_moe else {}
-    out_dir = os.path.join(ROOT, "gpurun_out", "bench_out")
+    out_dir = os.path.join(scratch_dir(a), "bench_out")
+    recompute = resolve_recompute(a, cfg, world)
     args = Arguments(
         model=ModelArguments(config_path=a.model, ep_dispatch=a.ep_dispatch),
         data=DataArguments(datasets=[{"path": "dummy", "max_seq_len": 64, "num_samples": 8}],
@@ -145,7 +182,8 @@ def run_ours(a):
         train=TrainingArguments(output_dir=out_dir, optimizer="adamw", lr=1e-5, weight_decay=0.01,
                                 max_grad_norm=1.0, micro_batch_size=1, gradient_accumulation_steps=1,
                                 data_parallel_mode="fsdp2", enable_mixed_precision=True,
-                                enable_gradient_checkpointing=True, init_device="meta",
+                                enable_gradient_checkpointing=True,
+                                gradient_checkpointing_method=recompute, init_device="meta",
                                 load_weights_mode="skip", save_hf_weights=False, use_wandb=False,
                                 comm_backend=a.comm, max_steps=10 ** 9, ce_num_chunks=4, **moe_train))
     trainer = Trainer(args, model_config=cfg)
@@ -213,7 +251,7 @@ def run_ours(a):
                        "global_batch": world, "seq_len": a.seq_len,
                        "parallelism": f"fsdp{world}" + ("-fused" if fused else "-nccl" if world > 1 else "")
                        + (f"-ep{ep}-{a.ep_dispatch}" if ep > 1 else ""),
-                       "optimizer": "adamw fp32 master+states", "recompute": "full layer",
+                       "optimizer": "adamw fp32 master+states", "recompute": recompute,
                        "l2": "per-step working set (16 GB of bf16 weights + activations) >> 126 MB L2",
                        "packed_docs": "lengths U[256,4096], tokens U[vocab]"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,

@@ -257,10 +257,41 @@ def test_weight_sync_transports(tmp_path, tiny_runner):
     assert [n for n, _ in q] == ["x.q_proj.weight", "x.q_proj.weight_scale_inv"] and q[0][1].dtype == torch.uint8
 
 
+def test_endpoint_requests_revalidate_the_resolved_address(monkeypatch):
+    """A hostname that resolved to a safe address at registration and to the metadata address
+    later: the later request is refused, and requests go to the validated address literal, never
+    to the hostname."""
+    import socket
+    from xorl_b200.server import weight_sync as ws
+    answers = iter(["10.1.2.3", "10.1.2.3", "169.254.169.254"])
+    seen = []
+
+    def fake_getaddrinfo(host, port, *a, **k):
+        ip = next(answers)
+        seen.append((host, ip))
+        return [(socket.AF_INET, socket.SOCK_STREAM, 6, "", (ip, port))]
+
+    monkeypatch.setattr(socket, "getaddrinfo", fake_getaddrinfo)
+    contacted = []
+    em = ws.EndpointManager(post=lambda url, p: contacted.append(url) or {}, get=lambda url: {})
+    info = em.add("http://engine.cluster.local:30000", 1)
+    assert (info["host"], info["port"]) == ("engine.cluster.local", 30000)
+    em.broadcast_post("/pause_generation", lambda e, off: {})
+    assert contacted == ["http://10.1.2.3:30000/pause_generation"]        # the literal, not the name
+    with pytest.raises(ValueError, match="unsafe endpoint address"):
+        em.broadcast_post("/update_weights_from_distributed", lambda e, off: {})
+    assert len(contacted) == 1 and [ip for _, ip in seen][-1] == "169.254.169.254"
+    with pytest.raises(ValueError):
+        em.add("http://engine.cluster.local:30000/some/path")
+    with pytest.raises(ValueError):
+        em.add("https://engine.cluster.local:30000")
+
+
 def test_endpoint_manager_and_broadcast_group(tmp_path):
     from xorl_b200.server import weight_sync as ws
     calls = []
-    em = ws.EndpointManager(post=lambda url, p: calls.append((url, p)) or {}, get=lambda url: {"ok": True})
+    em = ws.EndpointManager(post=lambda url, p: calls.append((url, p)) or {}, get=lambda url: {"ok": True},
+                            url_of=lambda h, p, path: f"http://{h}:{p}{path}")
     em.add("http://a:1/", 2)
     em.add("http://b:1", 1)
     assert em.total_world() == 3 and em.check_health() == {"http://a:1": True, "http://b:1": True}

@@ -38,7 +38,7 @@ def reference_curve(steps=10):
     return losses
 
 
-def engine_curve(steps=10, world=1, rank=0, optimizer="adamw", lr=1e-4, fixed_batch=False):
+def engine_curve(steps=10, world=1, rank=0, optimizer="adamw", lr=1e-4, fixed_batch=False, recompute=True):
     import torch.distributed as dist
     from xorl_b200.models.config import preset
     from xorl_b200.models.decoder import DecoderLM
@@ -47,7 +47,7 @@ def engine_curve(steps=10, world=1, rank=0, optimizer="adamw", lr=1e-4, fixed_ba
     from xorl_b200.parallel.zero import Zero3Engine
     m = DecoderLM(preset("tiny-qwen3"), dtype=torch.float32, device="meta")
     eng = Zero3Engine(m, get_parallel_state(), compute_dtype=torch.float32,
-                      device=torch.device("cpu"), seed=0)
+                      device=torch.device("cpu"), seed=0, recompute=recompute)
     opt = build_optimizer(eng, lr=lr, weight_decay=0.0, optimizer_type=optimizer,
                           optimizer_kwargs={"muon_lr": 0.01} if optimizer == "muon" else None)
     losses = []
@@ -85,6 +85,21 @@ def test_fsdp2_two_gloo_ranks_match_single_process():
     assert len(got) == 10
     for a, b in zip(ref, got):
         assert abs(a - b) < 1e-5, (ref, got)
+
+
+def test_engine_without_recompute_matches_autograd():
+    """Activations kept from the forward pass (no recomputation): same losses, one process and two
+    gloo ranks (parameters stay gathered between a layer's forward and its backward)."""
+    from dist_utils import run_distributed
+    from xorl_b200.parallel.state import init_parallel_state, reset_parallel_state
+    reset_parallel_state()
+    init_parallel_state(device_type="cpu")
+    ref = reference_curve(6)
+    got = engine_curve(6, recompute=False)
+    out = run_distributed(__file__, 2, "norecompute")
+    got2 = json.loads([l for l in out.splitlines() if l.startswith("LOSSES ")][-1][7:])
+    for a, b, c in zip(ref, got, got2):
+        assert abs(a - b) < 1e-5 and abs(a - c) < 1e-5, (ref, got, got2)
 
 
 def test_muon_single_process_descends_and_orthogonalises():
@@ -176,6 +191,8 @@ if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "muon":
         curve = engine_curve(6, dist.get_world_size(), dist.get_rank(), optimizer="muon", lr=1e-3,
                              fixed_batch=True)
+    elif len(sys.argv) > 1 and sys.argv[1] == "norecompute":
+        curve = engine_curve(6, dist.get_world_size(), dist.get_rank(), recompute=False)
     else:
         curve = engine_curve(10, dist.get_world_size(), dist.get_rank())
     if dist.get_rank() == 0:

@@ -22,7 +22,7 @@ from fastapi import Depends, FastAPI, Header, HTTPException
 from . import api_types as T
 from .future_store import FutureStore
 from .orchestrator import Orchestrator, OrchestratorRequest, RequestProcessor, SeqIdAwareFIFOPolicy
-from .security import validate_endpoint, validate_identifier
+from .security import validate_identifier
 from .weight_sync import EndpointManager
 
 
@@ -316,17 +316,12 @@ def create_app(state: ServerState) -> FastAPI:
     def add_endpoint(req: T.InferenceEndpoint):
         # the trainer will send HTTP requests and weight broadcasts there: refuse malformed,
         # link-local, multicast and reserved targets (and anything off the allow-list when
-        # XORL_REQUIRE_ENDPOINT_ALLOWLIST=1)
-        from urllib.parse import urlsplit
-        u = urlsplit(req.url if "//" in req.url else "http://" + req.url)
+        # XORL_REQUIRE_ENDPOINT_ALLOWLIST=1).  Only (host, port) is stored; the same checks run again
+        # on every later request, on the address that request will actually contact.
         try:
-            if u.scheme not in ("http", "https") or not u.hostname:
-                raise ValueError(f"endpoint URL {req.url!r} needs an http(s) host")
-            validate_endpoint(u.hostname, u.port or (443 if u.scheme == "https" else 80),
-                              require_allowlist=os.environ.get("XORL_REQUIRE_ENDPOINT_ALLOWLIST", "0") == "1")
+            return state.endpoints.add(req.url, req.world_size, req.name)
         except ValueError as e:
             raise HTTPException(422, str(e)) from None
-        return state.endpoints.add(req.url, req.world_size, req.name)
 
     @app.post("/remove_inference_endpoint", dependencies=dep)
     def remove_endpoint(req: T.InferenceEndpoint):

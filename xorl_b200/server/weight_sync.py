@@ -34,35 +34,76 @@ from ..ops import quantize as Q
 # ---------------------------------------------------------------------------------------------
 # endpoints
 # ---------------------------------------------------------------------------------------------
+def split_endpoint(url: str) -> Tuple[str, int]:
+    """``http://host:port`` (scheme optional) -> (host, port).  Inference endpoints are plain HTTP
+    inside the cluster; anything else is refused."""
+    from urllib.parse import urlsplit
+    u = urlsplit(url if "//" in url else "http://" + url)
+    if u.scheme != "http" or not u.hostname:
+        raise ValueError(f"endpoint URL {url!r} needs an http host")
+    if u.path not in ("", "/") or u.query or u.fragment or u.username or u.password:
+        raise ValueError(f"endpoint URL {url!r} must be just http://host:port")
+    try:
+        port = u.port or 80
+    except ValueError:
+        raise ValueError(f"endpoint URL {url!r} has an invalid port") from None
+    return u.hostname, port
+
+
 class EndpointManager:
+    """Registered inference engines.  An endpoint is kept as ``(host, port)``; every outbound request
+    URL is rebuilt at the moment of use by ``url_of`` (default ``security.endpoint_url``), which
+    resolves the host again, re-applies the address checks and returns an address literal, so a
+    hostname whose DNS answer changes after registration cannot move the request to an unsafe
+    address (src/xorl/server/weight_sync/backends/nccl_broadcast.py:536-867 builds its URLs the
+    same way)."""
+
     def __init__(self, post: Optional[Callable[[str, Dict[str, Any]], Dict[str, Any]]] = None,
-                 get: Optional[Callable[[str], Dict[str, Any]]] = None, timeout: float = 300.0):
+                 get: Optional[Callable[[str], Dict[str, Any]]] = None, timeout: float = 300.0,
+                 url_of: Optional[Callable[[str, int, str], str]] = None):
         self.endpoints: Dict[str, Dict[str, Any]] = {}
         self.timeout = timeout
         self._post = post or self._http_post
         self._get = get or self._http_get
+        self._url_of = url_of or self._checked_url
+
+    @staticmethod
+    def _checked_url(host: str, port: int, path: str) -> str:
+        from .security import endpoint_url
+        return endpoint_url(host, port, path,
+                            require_allowlist=os.environ.get("XORL_REQUIRE_ENDPOINT_ALLOWLIST", "0") == "1")
 
     def _http_post(self, url, payload):
         import requests
-        r = requests.post(url, json=payload, timeout=self.timeout)
+        r = requests.post(url, json=payload, timeout=self.timeout, allow_redirects=False)
         r.raise_for_status()
         return r.json() if r.content else {}
 
     def _http_get(self, url):
         import requests
-        r = requests.get(url, timeout=self.timeout)
+        r = requests.get(url, timeout=self.timeout, allow_redirects=False)
         r.raise_for_status()
         return r.json() if r.content else {}
 
+    @staticmethod
+    def _key(url: str) -> str:
+        host, port = split_endpoint(url)
+        return f"http://[{host}]:{port}" if ":" in host else f"http://{host}:{port}"
+
     def add(self, url: str, world_size: int = 1, name: Optional[str] = None) -> Dict[str, Any]:
-        url = url.rstrip("/")
-        info = {"url": url, "world_size": int(world_size), "name": name or url, "added": time.time(),
-                "healthy": None}
-        self.endpoints[url] = info
+        host, port = split_endpoint(url)
+        self._url_of(host, port, "/health")          # refuses unsafe targets at registration too
+        key = self._key(url)
+        info = {"url": key, "host": host, "port": port, "world_size": int(world_size),
+                "name": name or key, "added": time.time(), "healthy": None}
+        self.endpoints[key] = info
         return info
 
     def remove(self, url: str) -> bool:
-        return self.endpoints.pop(url.rstrip("/"), None) is not None
+        try:
+            return self.endpoints.pop(self._key(url), None) is not None
+        except ValueError:
+            return False
 
     def list(self) -> List[Dict[str, Any]]:
         return list(self.endpoints.values())
@@ -70,23 +111,27 @@ class EndpointManager:
     def total_world(self) -> int:
         return sum(e["world_size"] for e in self.endpoints.values())
 
+    def request_url(self, endpoint: Dict[str, Any], path: str) -> str:
+        """The URL to contact for ``path`` right now (validated address literal)."""
+        return self._url_of(endpoint["host"], endpoint["port"], path)
+
     def check_health(self) -> Dict[str, bool]:
         out = {}
-        for url, e in self.endpoints.items():
+        for key, e in self.endpoints.items():
             try:
-                self._get(url + "/health")
+                self._get(self.request_url(e, "/health"))
                 e["healthy"] = True
             except Exception:  # noqa: BLE001
                 e["healthy"] = False
-            out[url] = e["healthy"]
+            out[key] = e["healthy"]
         return out
 
     def broadcast_post(self, route: str, payload_of: Callable[[Dict[str, Any], int], Dict[str, Any]]):
         """POST to every endpoint; ``payload_of(endpoint, rank_offset)`` builds the body, where
         ``rank_offset`` is the first sync-group rank of that endpoint (rank 0 is the trainer)."""
         out, offset = [], 1
-        for url, e in self.endpoints.items():
-            out.append(self._post(url + route, payload_of(e, offset)))
+        for e in self.endpoints.values():
+            out.append(self._post(self.request_url(e, route), payload_of(e, offset)))
             offset += e["world_size"]
         return out
 
