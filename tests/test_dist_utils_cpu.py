@@ -117,3 +117,40 @@ def _worker():
 
 if __name__ == "__main__":
     _worker()
+
+
+def test_lr_schedule_matches_the_reference_lambdas():
+    """(step, lr) pairs of the three decay styles against the closed forms of
+    src/xorl/optim/lr_scheduler.py:117,146,183: warm-up is ``step / max(1, warmup)`` starting at
+    ``lr_start`` on step 0, the full rate arrives at step ``warmup``."""
+    import math
+    from xorl_b200.optim.lr_scheduler import build_lr_scheduler
+
+    class Opt:
+        lr = None
+
+        def set_lr(self, lr):
+            self.lr = lr
+
+    def ref(step, style, total=100, lr=1e-3, lr_min=1e-5, lr_start=1e-4, warm=0.1, decay=0.8):
+        w, d = int(total * warm), int(total * decay)
+        if step < w:
+            return lr_start + (lr - lr_start) * step / max(1, w)
+        if style == "constant":
+            return lr
+        if step >= d:
+            return lr_min
+        prog = (step - w) / max(1, d - w)
+        r = lr_min / lr
+        f = (1 - prog) if style == "linear" else 0.5 * (1 + math.cos(math.pi * prog))
+        return lr * (r + (1 - r) * f)
+
+    for style in ("constant", "linear", "cosine"):
+        o = Opt()
+        sch = build_lr_scheduler(o, 100, 1e-3, 1e-5, 1e-4, 0.1, style, 0.8)
+        for step in range(100):
+            assert abs(o.lr - ref(step, style)) < 1e-12, (style, step, o.lr, ref(step, style))
+            sch.step()
+    o = Opt()
+    build_lr_scheduler(o, 100, 1e-3, lr_start=0.0, lr_warmup_ratio=0.1)
+    assert o.lr == 0.0                      # step 0 trains at lr_start

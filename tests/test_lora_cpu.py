@@ -102,3 +102,38 @@ def test_qlora_and_fp8_and_qarl_forward_backward():
     fq = fake_quant(w, "nvfp4")
     fq.sum().backward()
     assert torch.allclose(w.grad, torch.ones_like(w))
+
+
+def test_relora_merge_keeps_fp32_masters_of_the_adapters():
+    """A ReLoRA merge folds B A into the frozen base weight and restarts B at zero; the fp32 master
+    copy of lora_A must survive it bit for bit (it is not rebuilt from its bf16 compute copy)."""
+    from types import SimpleNamespace
+    from xorl_b200.adapters.lora import inject_lora
+    from xorl_b200.parallel.zero import Zero3Engine
+    from xorl_b200.trainers.trainer import Trainer
+    la = LoRAArguments(enable_lora=True, lora_rank=4, lora_alpha=8, lora_b_init_std=0.02,
+                       lora_target_modules=["q_proj", "down_proj"], reset_optimizer_on_merge=False)
+    reset_parallel_state()
+    ps = init_parallel_state(device_type="cpu")
+    model = DecoderLM(preset("tiny-qwen3", tie_word_embeddings=False), device="meta")
+    inject_lora(model, la)
+    eng = Zero3Engine(model, ps, compute_dtype=torch.bfloat16, device=torch.device("cpu"))
+    # give the masters values that bf16 cannot hold
+    for g in eng.all_groups():
+        if g.master is not None:
+            g.master.add_(1e-5 * torch.arange(g.master.numel(), dtype=torch.float32).remainder(7))
+            eng.refresh_compute_copy(g)
+    before = {n: t.clone() for n, t in eng.iter_full_tensors("master")}
+    stub = SimpleNamespace(engine=eng, args=SimpleNamespace(lora=la), optimizer=SimpleNamespace(state={}))
+    Trainer.maybe_merge_lora(stub)
+    after = dict(eng.iter_full_tensors("master"))
+    changed_base = 0
+    for n, t in after.items():
+        if ".lora_A." in n:
+            assert torch.equal(t, before[n]), n
+            assert not torch.equal(t, t.bfloat16().float())          # still holds sub-bf16 bits
+        elif ".lora_B." in n:
+            assert float(t.abs().max()) == 0.0, n
+        elif not torch.equal(t.float(), before[n].float()):
+            changed_base += 1
+    assert changed_base == 4                                          # qkv_proj + down_proj, two layers

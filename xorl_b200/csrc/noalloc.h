@@ -14,7 +14,8 @@ extern "C" {
 // Backward of RMSNorm (same math and argument meaning as xb_rmsnorm_bwd) using a scratch area
 // that lives inside the library image instead of a caller-provided buffer.
 //
-//   dy, x, w      bf16 inputs: upstream gradient [T, H], normalised input [T, H], weight [H]
+//   dy, x, w      bf16 inputs: upstream gradient [T, H], the layer's input before normalisation
+//                 [T, H] (the kernel applies rstd itself), weight [H]
 //   rstd          fp32 [T] from the forward pass
 //   dres          optional bf16 [T, H] gradient of the residual stream, added into dx (may be null)
 //   dx            bf16 [T, H] output
@@ -23,7 +24,7 @@ extern "C" {
 //   stream        cudaStream_t
 //
 // Limits: H must be a multiple of 8 and at most 8192 (the built-in scratch is 256 x 8192 floats,
-// 8 MiB per GPU).  Returns 0 on success, -1 for an unsupported H (a message is printed), -2 when
+// 8 MiB per GPU).  Returns 0 on success (T <= 0: nothing to do, nothing launched), -1 for an unsupported H (a message is printed), -2 when
 // the scratch address could not be resolved, -11 on a launch error.
 //
 // The first call on each device resolves the scratch address; issue it before any stream capture.

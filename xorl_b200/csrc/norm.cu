@@ -458,8 +458,8 @@ XB_API int xb_qk_norm_rope_bwd(const void* dout_bf16, const float* dq_f32, const
 //
 // xb_rmsnorm_bwd needs a scratch buffer for the per-CTA partial sums of the weight gradient and
 // leaves it to the caller to allocate.  Callers that are not allowed to allocate device memory
-// (code running inside a captured region, a real-time loop, a plugin that was handed all of its
-// buffers up front, a process whose memory pool is owned by somebody else) use this entry point
+// (a real-time loop, a plugin that was handed all of its buffers up front, a process whose
+// memory pool is owned by somebody else) use this entry point
 // instead: its scratch is a fixed array that is part of the loaded library image.
 //
 //  * The array costs XB_NOALLOC_PARTIAL_ROWS * XB_NOALLOC_MAX_H * 4 bytes = 8 MiB on every GPU
@@ -469,8 +469,8 @@ XB_API int xb_qk_norm_rope_bwd(const void* dout_bf16, const float* dq_f32, const
 //  * All calls share the one array and it keeps whatever the previous call left in it.  Every
 //    partial row that is read is written first by the same call, so nothing has to be cleared,
 //    but two calls that run on the GPU at the same time (different streams) race on it.
-//  * H above XB_NOALLOC_MAX_H, H not a multiple of 8, or T <= 0 with work to do is rejected with a
-//    negative return code and a message on stderr; nothing is launched in that case.
+//  * H above XB_NOALLOC_MAX_H or not a multiple of 8 is rejected with a negative return code and
+//    a message on stderr; nothing is launched in that case.  T <= 0 returns 0 without launching.
 // ---------------------------------------------------------------------------------------
 #define XB_NOALLOC_MAX_H 8192
 #define XB_NOALLOC_PARTIAL_ROWS 256

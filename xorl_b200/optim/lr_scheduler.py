@@ -14,7 +14,11 @@ class LRScheduler:
         self.train_steps = max(1, int(train_steps))
         self.lr, self.lr_min, self.lr_start = lr, lr_min, lr_start
         self.warmup_steps = int(self.train_steps * lr_warmup_ratio)
-        self.decay_steps = max(1, int(self.train_steps * lr_decay_ratio))
+        self.decay_steps = int(self.train_steps * lr_decay_ratio)
+        if lr <= 0:
+            raise ValueError(f"lr must be > 0, got {lr}")
+        if not 0.0 <= lr_warmup_ratio <= 1.0:
+            raise ValueError(f"lr_warmup_ratio must be in [0, 1], got {lr_warmup_ratio}")
         self.style = lr_decay_style
         if self.style not in ("constant", "linear", "cosine"):
             raise ValueError(f"unknown lr_decay_style {lr_decay_style!r}")
@@ -22,14 +26,16 @@ class LRScheduler:
         self._apply()
 
     def lr_at(self, step: int) -> float:
-        if self.warmup_steps > 0 and step < self.warmup_steps:
-            return self.lr_start + (self.lr - self.lr_start) * (step + 1) / self.warmup_steps
+        """Learning rate of optimizer step number ``step`` (0-based).  Step 0 trains at ``lr_start``
+        and the full rate is reached at step ``warmup_steps``, exactly as the reference's lambdas
+        (src/xorl/optim/lr_scheduler.py:117,146,183: ``current_step / max(1, warmup)``)."""
+        if step < self.warmup_steps:
+            return self.lr_start + (self.lr - self.lr_start) * step / max(1, self.warmup_steps)
         if self.style == "constant":
             return self.lr
         if step >= self.decay_steps:
             return self.lr_min
         prog = (step - self.warmup_steps) / max(1, self.decay_steps - self.warmup_steps)
-        prog = min(max(prog, 0.0), 1.0)
         if self.style == "linear":
             return self.lr_min + (self.lr - self.lr_min) * (1.0 - prog)
         return self.lr_min + (self.lr - self.lr_min) * 0.5 * (1.0 + math.cos(math.pi * prog))

@@ -1,6 +1,6 @@
 """Optimizers that update the ZeRO engine's flat fp32 shards in one kernel per shard.
 
-AdamW (fp32 moments), AnyPrecision AdamW (bf16 moments, optional Kahan compensation), SGD with
+AdamW (fp32 moments), AnyPrecision AdamW (bf16 moments), SGD with
 momentum, SignSGD — the optimizer set of src/xorl/optim/optimizer.py:114-242.  The update reads the
 clip coefficient from device memory, so a step needs no host synchronisation, and writes the
 compute-dtype copy of the weights that the next all-gather sends.
@@ -125,8 +125,10 @@ class ShardedAdamW(ShardedOptimizer):
 
 
 class ShardedAnyPrecisionAdamW(ShardedOptimizer):
-    """AdamW with bf16 moments (``optimizer_dtype: bf16``) and optional Kahan compensation;
-    torch ops on the shard (src/xorl/optim/anyprecision_adamw.py)."""
+    """AdamW with bf16 moments (``optimizer_dtype: bf16``); torch ops on the shard
+    (src/xorl/optim/anyprecision_adamw.py).  The reference's Kahan compensation exists for weights
+    that are themselves bf16; here the update always lands in the fp32 master shard, so there is no
+    rounding of the weight to compensate and no compensation buffer."""
     kind = "anyprecision_adamw"
 
     def __init__(self, engine, lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0,

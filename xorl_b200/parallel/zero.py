@@ -754,10 +754,14 @@ class Zero3Engine:
         dense_sq = torch.zeros(1, device=dev, dtype=torch.float32)
         expert_sq = torch.zeros(1, device=dev, dtype=torch.float32)
         first_d = first_e = True
+
+        def counts_as_expert(g) -> bool:
+            return getattr(g, "is_expert", False) and self.ps.ep_size > 1
+
         for g in self.all_groups():
             if not g.grad_ready:
                 continue
-            if getattr(g, "is_expert", False) and self.ps.ep_size > 1:
+            if counts_as_expert(g):
                 optim_ops.sumsq_(g.grad_shard, expert_sq, not first_e)
                 first_e = False
             else:
@@ -766,15 +770,17 @@ class Zero3Engine:
         tp_pg = self.ps.group("tp") if self.ps.tp_size > 1 else None
         if tp_pg is not None:
             # replicated parameters (norm weights, embeddings) hold identical gradients on every
-            # TP rank: count them once, sum only the tensor-parallel shards over the TP group
+            # TP rank: count them once, sum only the tensor-parallel shards over the TP group.
+            # Expert groups under expert parallelism are not part of dense_sq (they went into
+            # expert_sq above) and are not sliced over the TP group, so they stay out of this split.
             rep_sq = torch.zeros(1, device=dev, dtype=torch.float32)
             for g in self.all_groups():
-                if not g.grad_ready:
+                if not g.grad_ready or counts_as_expert(g):
                     continue
                 for i, a, b in g.param_segments_in_shard():
                     if getattr(g.named_params[i][1], "_xb_tp", None) is None:
                         rep_sq += g.grad_shard[a:b].float().pow(2).sum()
-            sharded = dense_sq - rep_sq
+            sharded = (dense_sq - rep_sq).clamp_(min=0.0)
             dist.all_reduce(sharded, group=tp_pg)
             dense_sq = sharded + rep_sq
         if self.shard_pg is not None:

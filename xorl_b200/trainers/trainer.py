@@ -302,10 +302,18 @@ class Trainer:
                 if touched:
                     for g in unit.groups:
                         s0, s1 = g.shard_range()
-                        if g.full is not g.shard_lp:
-                            g.shard_lp.copy_(g.full[s0:s1])
-                        if g.master is not None:
-                            g.master.copy_(g.shard_lp)
+                        if g.master is None:
+                            # frozen group: the merged base weights live in the compute-dtype shard
+                            if g.full is not g.shard_lp:
+                                g.shard_lp.copy_(g.full[s0:s1])
+                            continue
+                        # trainable group: only lora_B restarts (at zero); every other trainable
+                        # parameter (lora_A, unfrozen weights) keeps its fp32 master value
+                        for i, a, b in g.param_segments_in_shard():
+                            if ".lora_B." in g.named_params[i][0]:
+                                g.master[a:b].zero_()
+                                if g.shard_lp is not g.master:
+                                    g.shard_lp[a:b].zero_()
                 if eng.reshard:
                     eng.release(unit)
         if self.args.lora.reset_optimizer_on_merge:
