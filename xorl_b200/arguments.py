@@ -323,6 +323,11 @@ class TrainingArguments:
         self.data_parallel_replicate_size, self.data_parallel_shard_size = rep, shard
         ranks_per_stage = ws // self.pipeline_parallel_size
         if self.expert_parallel_size > 1:
+            if self.tensor_parallel_size > 1:
+                # tokens are replicated over a tensor-parallel group, so its ranks would dispatch
+                # every token once each and the experts would see it tp times
+                raise NotImplementedError("expert_parallel_size > 1 with tensor_parallel_size > 1 is not "
+                                          "supported: shard the experts (EP) or the dense layers (TP)")
             if ranks_per_stage % self.expert_parallel_size:
                 raise ValueError(f"ranks per PP stage ({ranks_per_stage}) not divisible by "
                                  f"expert_parallel_size ({self.expert_parallel_size})")

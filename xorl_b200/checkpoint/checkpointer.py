@@ -77,6 +77,43 @@ class DistributedCheckpointer:
         return DTensor.from_local(local, self._mesh_for(g), [Shard(0)], run_check=False,
                                   shape=t.shape, stride=stride)
 
+    def _ep_mesh(self):
+        """(ep, ep_fsdp) device mesh of this rank's expert-parallel grid (1-D over ep when every
+        rank of a stage is its own ep_fsdp group)."""
+        if "ep" in self._meshes:
+            return self._meshes["ep"]
+        from torch.distributed.device_mesh import DeviceMesh
+        ps = self.engine.ps
+        ep_ranks, epf_ranks = ps.group_ranks("ep"), ps.group_ranks("ep_fsdp")
+        dev = self.engine.device.type
+        if len(epf_ranks) == 1:
+            mesh = DeviceMesh.from_group(ps.group("ep"), dev, mesh=ep_ranks, mesh_dim_names=("ep",))
+        else:
+            # the expert grid is a reshape of consecutive ranks, hence affine in both coordinates
+            grid = [[e + f - ps.rank for f in epf_ranks] for e in ep_ranks]
+            assert grid[ps.rank_in("ep")][ps.rank_in("ep_fsdp")] == ps.rank
+            mesh = DeviceMesh.from_group([ps.group("ep"), ps.group("ep_fsdp")], dev,
+                                         mesh=torch.tensor(grid), mesh_dim_names=("ep", "ep_fsdp"))
+        self._meshes["ep"] = mesh
+        return mesh
+
+    def _wrap_expert(self, p, local_view: torch.Tensor):
+        """Expert-parallel parameter: this rank's experts ``[E / ep, d1, ...]`` (already gathered over
+        ep_fsdp) as a DTensor of the full ``[E, d1, ...]`` shape, ``Shard(0)`` over ep and
+        ``Shard(1)`` over ep_fsdp -- the placement the reference restores for expert tensors
+        (src/xorl/checkpoint/checkpointer.py:107-160)."""
+        from torch.distributed.tensor import DTensor, Shard
+        ps = self.engine.ps
+        full_shape = tuple(p._xb_full_shape)
+        stride = torch.empty(full_shape, device="meta").stride()
+        mesh = self._ep_mesh()
+        if mesh.ndim == 1:
+            return DTensor.from_local(local_view.clone(), mesh, [Shard(0)], run_check=False,
+                                      shape=full_shape, stride=stride)
+        a, b = _chunk_bounds(full_shape[1], ps.ep_fsdp_size, ps.rank_in("ep_fsdp"))
+        return DTensor.from_local(local_view[:, a:b].clone(), mesh, [Shard(0), Shard(1)], run_check=False,
+                                  shape=full_shape, stride=stride)
+
     def _state_sources(self):
         srcs = [("model", "master", None)]
         opt = self.optimizer
@@ -89,14 +126,19 @@ class DistributedCheckpointer:
         sd: Dict[str, Any] = {}
         eng = self.engine
         group_of = {name: g for g in eng.all_groups() for name, _ in g.named_params}
+        param_of = {name: p for g in eng.all_groups() for name, p in g.named_params}
         for key_fmt, what, extra in self._state_sources():
-            for name, view in eng.iter_full_tensors(what, extra):
+            for name, view in eng.iter_full_tensors(what, extra, ep_full=False):
                 g = group_of[name]
                 if getattr(g, "frozen", False) and not include_frozen:
                     continue
                 fqn = to_checkpoint_fqn(name)
                 key = f"model.{fqn}" if key_fmt == "model" else key_fmt.format(fqn=fqn)
-                sd[key] = self._wrap(g, view.shape, view.float() if what != "master" else view)
+                val = view.float() if what != "master" else view
+                if getattr(param_of[name], "_xb_ep", None) is not None and eng.ps.ep_size > 1:
+                    sd[key] = self._wrap_expert(param_of[name], val)
+                else:
+                    sd[key] = self._wrap(g, view.shape, val)
         return sd
 
     # ---- save -----------------------------------------------------------------------------------

@@ -70,6 +70,12 @@ class Experts(nn.Module):
             self.down_bias = nn.Parameter(torch.zeros(num_local, H, dtype=dtype, device=device))
             self.gate_up_bias._xb_expert = True
             self.down_bias._xb_expert = True
+        ps = get_parallel_state()
+        if ps.ep_size > 1 and num_local * ps.ep_size == cfg.num_experts:
+            from ..parallel.ep import mark_ep
+            for prm in (self.gate_up_proj, self.down_proj, self.gate_up_bias, self.down_bias):
+                if prm is not None:
+                    mark_ep(prm, ps.rank_in("ep"), ps.ep_size)
 
     def mlp_kwargs(self):
         if self.gate_up_bias is None and self.swiglu_limit is None and self.activation is None:

@@ -24,6 +24,18 @@ from ..ops import moe as moe_ops
 from .state import get_parallel_state
 
 
+def mark_ep(p: torch.nn.Parameter, ep_rank: int, ep_size: int) -> None:
+    """Declares ``p`` (first dimension = local experts) as rows ``[ep_rank * n, (ep_rank + 1) * n)`` of
+    a stacked ``[E, ...]`` tensor.  Initialisation draws the full tensor and keeps this slice, full
+    tensors handed to ``Zero3Engine.load_full_tensors`` are sliced the same way, and checkpoints
+    present the parameter as ``[Shard(0) over ep, Shard(1) over ep_fsdp]`` of the full shape
+    (src/xorl/distributed/parallel_plan.py:331-393, src/xorl/checkpoint/checkpointer.py:107-160)."""
+    n = p.shape[0]
+    p._xb_ep = (int(ep_rank), int(ep_size))
+    p._xb_full_shape = (n * ep_size, *p.shape[1:])
+    p._xb_ep_slice = lambda full, a=ep_rank * n, b=(ep_rank + 1) * n: full[a:b]
+
+
 class _AllToAll(torch.autograd.Function):
     """all_to_all_single with variable splits; backward is the reverse exchange."""
 

@@ -35,6 +35,11 @@ from .state import ParallelState, get_parallel_state
 ALIGN = 64  # elements; keeps every parameter and every shard 128-byte aligned in bf16
 
 
+def _slice_fn(p):
+    """This rank's part of the full tensor for a tensor-parallel or expert-parallel parameter."""
+    return getattr(p, "_xb_tp_slice", None) or getattr(p, "_xb_ep_slice", None)
+
+
 def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
@@ -275,7 +280,8 @@ class Zero3Engine:
                     newp._xb_shape = tuple(p.shape)
                     newp._xb_init = None if p.is_meta else p.detach()
                     for attr in ("_xb_expert", "_xb_tp", "_xb_no_decay", "_xb_full_shape",
-                                 "_xb_tp_slice", "_xb_tp_reduce", "_xb_materialize", "_xb_lora"):
+                                 "_xb_tp_slice", "_xb_tp_reduce", "_xb_materialize", "_xb_lora", "_xb_ep",
+                                 "_xb_ep_slice"):
                         if hasattr(p, attr):
                             setattr(newp, attr, getattr(p, attr))
                     mapping[id(p)] = newp
@@ -338,9 +344,9 @@ class Zero3Engine:
         full32 = torch.zeros(g.padded, device=self.device, dtype=torch.float32)
         for (name, p), view in zip(g.named_params, g.param_views(full32)):
             init = getattr(p, "_xb_init", None)
-            tp_slice = getattr(p, "_xb_tp_slice", None)
+            tp_slice = _slice_fn(p)
             if init is None and tp_slice is not None:
-                # tensor-parallel shard: draw the full tensor, keep this rank's slice
+                # tensor- or expert-parallel shard: draw the full tensor, keep this rank's slice
                 full = torch.empty(p._xb_full_shape, device=self.device, dtype=torch.float32)
                 init_fn(name, full, std, seed, index_of[name], zc)
                 view.copy_(tp_slice(full))
@@ -376,7 +382,7 @@ class Zero3Engine:
                 p._xb_init = None
             else:
                 tmp = torch.empty(view.shape, device=self.device, dtype=torch.float32)
-                tp_slice = getattr(p, "_xb_tp_slice", None)
+                tp_slice = _slice_fn(p)
                 if tp_slice is not None:
                     fullp = torch.empty(p._xb_full_shape, device=self.device, dtype=torch.float32)
                     init_fn(name, fullp, std, seed, index_of[name], zc)
@@ -802,8 +808,11 @@ class Zero3Engine:
     # full-tensor access (checkpointing, export, weight sync)
     # ---------------------------------------------------------------------------------------
     @torch.no_grad()
-    def iter_full_tensors(self, what: str = "master", extra: Optional[Dict[int, torch.Tensor]] = None):
-        """Yields (fqn, full tensor) unit by unit.  ``what``: "master" (fp32 weights),
+    def iter_full_tensors(self, what: str = "master", extra: Optional[Dict[int, torch.Tensor]] = None,
+                          ep_full: bool = True):
+        """Yields (fqn, full tensor) unit by unit.  Expert-parallel parameters come back with all
+        ``E`` experts (gathered over the ep group) unless ``ep_full`` is False, in which case they
+        keep this rank's ``[E / ep, ...]`` rows.  ``what``: "master" (fp32 weights),
         "grad" (fp32 accumulated gradient) or "extra" with a {id(group): shard tensor} mapping
         (optimizer moments).  Every rank of the shard group must iterate in lock-step."""
         for g in self.all_groups():
@@ -827,6 +836,10 @@ class Zero3Engine:
                     parts = [torch.empty_like(view) for _ in range(self.ps.tp_size)]
                     dist.all_gather(parts, view.contiguous(), group=self.ps.group("tp"))
                     view = unshard_rows(parts, spec[1]) if spec[0] == "col" else torch.cat(parts, 1)
+                if ep_full and getattr(p, "_xb_ep", None) is not None and self.ps.ep_size > 1:
+                    parts = [torch.empty_like(view) for _ in range(self.ps.ep_size)]
+                    dist.all_gather(parts, view.contiguous(), group=self.ps.group("ep"))
+                    view = torch.cat(parts, 0)
                 yield name, view
 
     @torch.no_grad()
@@ -845,7 +858,7 @@ class Zero3Engine:
                     missing.append(name)
                     continue
                 src = tensors[name]
-                tp_slice = getattr(g.named_params[i][1], "_xb_tp_slice", None)
+                tp_slice = _slice_fn(g.named_params[i][1])
                 if tp_slice is not None and tuple(src.shape) == tuple(g.named_params[i][1]._xb_full_shape):
                     src = tp_slice(src)
                 src = src.reshape(-1)
