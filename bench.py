@@ -171,8 +171,8 @@ def run_ours(a):
     overrides = {"num_hidden_layers": a.layers} if a.layers else {}
     cfg = preset(a.model, **overrides)
     ep = (a.ep or (world if cfg.is_moe else 1)) if cfg.is_moe else 1
-    moe_train = dict(expert_parallel_size=ep, softmax_auxiliary_loss=True, auxiliary_loss_multiplier=1e-3) \
-        if cfg.is_moe else {}
+    # the load-balancing loss comes from the model config (router_aux_loss_coef = 1e-3)
+    moe_train = dict(expert_parallel_size=ep) if cfg.is_moe else {}
     out_dir = os.path.join(scratch_dir(a), "bench_out")
     recompute = resolve_recompute(a, cfg, world)
     args = Arguments(

@@ -47,8 +47,38 @@ def test_dense_train_save_resume(tmp_path):
 def test_moe_ep2_fsdp_trains(tmp_path):
     from dist_utils import run_distributed
     cfg = _cfg(tmp_path, "tiny-qwen3-moe", expert_parallel_size=2, softmax_auxiliary_loss=True,
-               auxiliary_loss_multiplier=1e-3)
+               auxiliary_loss_multiplier=1e-4)   # z-loss on the logits; the router loss comes from the model config
     run_distributed("-m", 2, "xorl_b200.cli.train", cfg)
     with open(tmp_path / "out" / "training_metrics.json") as f:
         hist = json.load(f)["loss_history"]
     assert len(hist) == 6 and hist[-1] < hist[0]
+
+
+def test_softmax_auxiliary_loss_is_the_z_loss_on_the_logits(tmp_path):
+    """``train.softmax_auxiliary_loss`` adds ``auxiliary_loss_multiplier * logsumexp(logits)^2`` per
+    supervised token to the lm-head loss (src/xorl/trainers/trainer.py:481-487); it is not the
+    routers' load-balancing loss, whose weight is the model's ``router_aux_loss_coef``."""
+    from xorl_b200.arguments import build_args
+    from xorl_b200.models.config import preset
+    from xorl_b200.parallel.state import reset_parallel_state
+    from xorl_b200.trainers.trainer import Trainer
+    reset_parallel_state()
+    args = build_args({"model": {"config_path": "tiny-qwen3"},
+                       "data": {"datasets": [{"path": "dummy", "type": "tokenized", "max_seq_len": 64,
+                                              "num_samples": 8}], "sample_packing_sequence_len": 128},
+                       "train": {"output_dir": str(tmp_path / "o"), "device": "cpu", "use_wandb": False,
+                                 "softmax_auxiliary_loss": True, "auxiliary_loss_multiplier": 0.5,
+                                 "save_hf_weights": False, "max_steps": 1}})
+    tr = Trainer(args, model_config=preset("tiny-qwen3"))
+    assert tr.model.z_loss_coef == 0.5
+    eng = tr.engine
+    ids = torch.randint(0, 1024, (1, 65))
+    x, y = ids[:, :-1], ids[:, 1:]
+    got = float(eng.forward_backward(x, y, grad_scale=1.0 / 64))
+    hidden = eng.forward_only(x)
+    w = dict(eng.iter_full_tensors("master"))["lm_head.weight"] if not tr.model_config.tie_word_embeddings \
+        else dict(eng.iter_full_tensors("master"))["embed_tokens.weight"]
+    logits = hidden.reshape(-1, hidden.shape[-1]).float() @ w.float().t()
+    ce = torch.nn.functional.cross_entropy(logits, y.reshape(-1), reduction="sum")
+    z = 0.5 * torch.logsumexp(logits, -1).pow(2).sum()
+    assert abs(got - float(ce + z) / 64) < 1e-3 * abs(got), (got, float(ce + z) / 64)

@@ -213,6 +213,9 @@ class DecoderLM(nn.Module):
         """grad_scale * sum of token cross-entropies (labels == -100 ignored)."""
         hidden = self.forward_head(h, residual, ctx)
         if getattr(self, "vocab_parallel", False):
+            if getattr(self, "z_loss_coef", 0.0):
+                raise NotImplementedError("softmax_auxiliary_loss (z-loss) is not supported with a "
+                                          "vocabulary-parallel lm-head")
             tp, tp_rank, tp_group = self.head_tp
             loss = loss_ops.vocab_parallel_linear_cross_entropy(
                 hidden, self.lm_head.weight, labels.reshape(-1), tp_group,
@@ -220,6 +223,7 @@ class DecoderLM(nn.Module):
             return (loss, None) if return_token_losses else loss
         return loss_ops.fused_linear_cross_entropy(hidden, self.lm_head.weight, labels.reshape(-1),
                                                    grad_scale, self.loss_chunk_tokens,
+                                                   z_loss=float(getattr(self, "z_loss_coef", 0.0)),
                                                    return_token_losses=return_token_losses)
 
     def unit_modules(self):

@@ -110,18 +110,28 @@ class ShardedAdamW(ShardedOptimizer):
         self.exp_avg_sq = self._new_state("exp_avg_sq")
 
     def step(self, clip_coef=None, grad_scale: float = 1.0) -> None:
+        """One fused kernel per equal-decay run of every shard.  On CUDA the kernels go to the
+        engine's optimizer stream, unit by unit in forward order, and the next forward pass waits
+        per unit (``Zero3Engine.begin_update``): the bandwidth-bound update overlaps the
+        tensor-core-bound start of the next step."""
+        from contextlib import nullcontext
         self.step_count += 1
         b1, b2 = self.betas
-        for g in self.engine.all_groups():
-            if not g.grad_ready:
-                continue
-            m, v = self.exp_avg[id(g)], self.exp_avg_sq[id(g)]
-            lp = None if g.shard_lp is g.master else g.shard_lp
-            for a, b, wd in self._segments(g):
-                optim_ops.adamw_step_(g.master[a:b], m[a:b], v[a:b], g.grad_shard[a:b],
-                                      None if lp is None else lp[a:b], lr=self.lr, beta1=b1, beta2=b2,
-                                      eps=self.eps, weight_decay=wd, step=self.step_count,
-                                      grad_scale=grad_scale, clip_coef=clip_coef)
+        eng = self.engine
+        side = eng.begin_update((clip_coef,)) if eng.is_cuda else None
+        with (torch.cuda.stream(side) if side is not None else nullcontext()):
+            for g in eng.all_groups():
+                if not g.grad_ready:
+                    continue
+                m, v = self.exp_avg[id(g)], self.exp_avg_sq[id(g)]
+                lp = None if g.shard_lp is g.master else g.shard_lp
+                for a, b, wd in self._segments(g):
+                    optim_ops.adamw_step_(g.master[a:b], m[a:b], v[a:b], g.grad_shard[a:b],
+                                          None if lp is None else lp[a:b], lr=self.lr, beta1=b1, beta2=b2,
+                                          eps=self.eps, weight_decay=wd, step=self.step_count,
+                                          grad_scale=grad_scale, clip_coef=clip_coef)
+                if side is not None:
+                    eng.mark_updated(g)
 
 
 class ShardedAnyPrecisionAdamW(ShardedOptimizer):

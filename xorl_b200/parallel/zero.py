@@ -79,6 +79,9 @@ class FlatParamGroup:
         self.grad_full: Optional[torch.Tensor] = None
         self.gather_event = None
         self.reduce_event = None
+        self.update_event = None              # optimizer kernels of the last step (side stream)
+        self.sq: Optional[torch.Tensor] = None  # ||grad shard||^2 of this step, when computed early
+        self.sq_valid = False
         self.weight_decay_mask: Optional[List[float]] = None
 
     # ---- layout helpers ---------------------------------------------------------------------
@@ -258,6 +261,18 @@ class Zero3Engine:
         self.micro_batches = 0                 # forward_backward calls since zero_grad
         self.units: List[ZeroUnit] = []
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+        # The optimizer's kernels are bandwidth-bound and the next forward pass is tensor-core
+        # bound: they run side by side.  The update of step t is issued on ``opt_stream`` unit by
+        # unit in forward order, and step t+1 waits per unit (before it reads the unit's parameters
+        # or overwrites its gradient shard), not for the whole update.
+        self.overlap_optimizer = self.is_cuda and os.environ.get("XORL_B200_OVERLAP_OPTIMIZER", "1") == "1"
+        self.opt_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+        self._opt_pending = False
+        # Squared gradient norms are taken per unit as soon as the unit's gradient is final (last
+        # micro-batch only), on a side stream, instead of in one pass after backward.
+        self.early_grad_norm = os.environ.get("XORL_B200_EARLY_GRAD_NORM", "1") == "1"
+        self.final_micro_batch = True          # callers with gradient accumulation set this per micro-batch
+        self.norm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
         self._full_pool: Dict[Tuple[int, torch.dtype], List[torch.Tensor]] = {}
         self._build_units(seed)
         self.symm = None  # fused peer-memory transport (attached by parallel.symm when usable)
@@ -400,6 +415,42 @@ class Zero3Engine:
             g.attach_params()
 
     # ---------------------------------------------------------------------------------------
+    # optimizer overlap
+    # ---------------------------------------------------------------------------------------
+    def begin_update(self, tensors=()):
+        """Stream on which an optimizer should issue its kernels (None: the current stream).  The
+        side stream first waits for everything issued so far (gradients, clip coefficient)."""
+        if not (self.overlap_optimizer and self.symm is None):
+            return None
+        cur = torch.cuda.current_stream()
+        self.opt_stream.wait_stream(cur)
+        for t in tensors:
+            if t is not None and t.is_cuda:
+                t.record_stream(self.opt_stream)
+        self._opt_pending = True
+        return self.opt_stream
+
+    def mark_updated(self, g: FlatParamGroup) -> None:
+        """Called on the optimizer's stream after the last kernel that touches group ``g``."""
+        if self._opt_pending:
+            g.update_event = torch.cuda.Event()
+            g.update_event.record(self.opt_stream)
+
+    def _wait_update(self, g: FlatParamGroup, stream=None) -> None:
+        ev = g.update_event
+        if ev is not None:
+            (stream or torch.cuda.current_stream()).wait_event(ev)
+
+    def sync_optimizer(self) -> None:
+        """Makes the current stream wait for every pending optimizer kernel (anything that reads or
+        writes shards outside the forward / backward path calls this first)."""
+        if self._opt_pending:
+            torch.cuda.current_stream().wait_stream(self.opt_stream)
+            for g in self.all_groups():
+                g.update_event = None
+            self._opt_pending = False
+
+    # ---------------------------------------------------------------------------------------
     # gather / release
     # ---------------------------------------------------------------------------------------
     def _take_full(self, numel: int, dtype: torch.dtype, on_comm_stream: bool = False) -> torch.Tensor:
@@ -423,6 +474,8 @@ class Zero3Engine:
             if g.full is not None:
                 continue
             g.full = self._take_full(g.padded, self.compute_dtype, on_comm_stream=True)
+            if self.is_cuda:
+                self._wait_update(g, self.comm_stream)
             if self.symm is not None and self.symm.can_gather(g):
                 self.symm.all_gather(g, self.comm_stream)
             elif self.is_cuda:
@@ -436,6 +489,8 @@ class Zero3Engine:
 
     def wait_gather(self, unit: ZeroUnit) -> None:
         for g in unit.groups:
+            if g.full_persistent:
+                self._wait_update(g)          # single owner: the optimizer wrote these weights in place
             if g.gather_event is not None:
                 torch.cuda.current_stream().wait_event(g.gather_event)
                 g.gather_event = None
@@ -461,6 +516,8 @@ class Zero3Engine:
         for g in unit.groups:
             if getattr(g, "frozen", False):
                 continue
+            self._wait_update(g)              # the last optimizer step still reads this gradient shard
+            g.sq_valid = False
             if g.world == 1:
                 # single owner: kernels write (or accumulate) straight into the fp32 accumulator
                 g.grad_full = g.grad_shard
@@ -494,16 +551,28 @@ class Zero3Engine:
                 for (_, p), v in zip(g.named_params, g.param_views(gf)):
                     if getattr(p, "_xb_tp_reduce", False):
                         dist.all_reduce(v, group=self.ps.group("tp"))
+            early = self._early_norm_ok(g)
             if g.world == 1:
-                pass  # gradients were produced in place in g.grad_shard
+                # gradients were produced in place in g.grad_shard
+                if early:
+                    ev = torch.cuda.Event()
+                    ev.record(torch.cuda.current_stream())
+                    self.norm_stream.wait_event(ev)
+                    with torch.cuda.stream(self.norm_stream):
+                        self._group_sumsq(g)
             elif self.symm is not None and self.symm.can_reduce(g):
                 self.symm.reduce_scatter_accumulate(g, gf, accumulate, self.comm_stream)
+                if early:
+                    with torch.cuda.stream(self.comm_stream):
+                        self._group_sumsq(g)
             elif self.is_cuda:
                 ev = torch.cuda.Event()
                 ev.record(torch.cuda.current_stream())
                 self.comm_stream.wait_event(ev)
                 with torch.cuda.stream(self.comm_stream):
                     self._rs_collective(g, gf, accumulate)
+                    if early:
+                        self._group_sumsq(g)
                     g.reduce_event = torch.cuda.Event()
                     g.reduce_event.record(self.comm_stream)
                 self._give_full(gf, g.reduce_event)
@@ -512,6 +581,26 @@ class Zero3Engine:
                 self._give_full(gf)
             g.grad_full = None
             g.grad_ready = True
+
+    def _early_norm_ok(self, g: FlatParamGroup) -> bool:
+        """The shard's squared norm may be taken right after this reduction: it is the step's last
+        micro-batch and nothing later in the step (replica / sequence-parallel / tensor-parallel
+        all-reduces of finish_grad_sync, sign votes) changes the shard again."""
+        if not (self.is_cuda and self.early_grad_norm and self.final_micro_batch):
+            return False
+        if self.sign_before_reduce or self.ps.tp_size > 1:
+            return False
+        if g.replicate_pg is not None and g.replicate_world > 1:
+            return False
+        if self.sp_sync_pg is not None and not getattr(g, "is_expert", False):
+            return False
+        return True
+
+    def _group_sumsq(self, g: FlatParamGroup) -> None:
+        if g.sq is None:
+            g.sq = torch.zeros(1, device=self.device, dtype=torch.float32)
+        optim_ops.sumsq_(g.grad_shard, g.sq, False)
+        g.sq_valid = True
 
     def _rs_collective(self, g: FlatParamGroup, gf: torch.Tensor, accumulate: bool) -> None:
         if self.reduce_dtype == torch.bfloat16 and gf.dtype == torch.float32 and self.bf16_a2a_reduce:
@@ -550,6 +639,7 @@ class Zero3Engine:
     def zero_grad(self) -> None:
         self.micro_batches = 0
         if self.symm is not None:
+            self.sync_optimizer()
             # parameter shards were rewritten by the optimizer: no peer may read them earlier
             self.symm.step_barrier(torch.cuda.current_stream())
         for unit in self.units:
@@ -764,15 +854,28 @@ class Zero3Engine:
         def counts_as_expert(g) -> bool:
             return getattr(g, "is_expert", False) and self.ps.ep_size > 1
 
+        if self.is_cuda:
+            # per-unit partial sums taken early live on the side streams
+            torch.cuda.current_stream().wait_stream(self.norm_stream)
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        early_d, early_e = [], []
         for g in self.all_groups():
             if not g.grad_ready:
                 continue
-            if counts_as_expert(g):
+            if g.sq_valid:
+                (early_e if counts_as_expert(g) else early_d).append(g.sq)
+                g.sq_valid = False
+            elif counts_as_expert(g):
                 optim_ops.sumsq_(g.grad_shard, expert_sq, not first_e)
                 first_e = False
             else:
                 optim_ops.sumsq_(g.grad_shard, dense_sq, not first_d)
                 first_d = False
+        # fixed order (unit order), one reduction: the same bits every run
+        if early_d:
+            dense_sq = dense_sq + torch.cat(early_d).sum()
+        if early_e:
+            expert_sq = expert_sq + torch.cat(early_e).sum()
         tp_pg = self.ps.group("tp") if self.ps.tp_size > 1 else None
         if tp_pg is not None:
             # replicated parameters (norm weights, embeddings) hold identical gradients on every
@@ -815,6 +918,7 @@ class Zero3Engine:
         keep this rank's ``[E / ep, ...]`` rows.  ``what``: "master" (fp32 weights),
         "grad" (fp32 accumulated gradient) or "extra" with a {id(group): shard tensor} mapping
         (optimizer moments).  Every rank of the shard group must iterate in lock-step."""
+        self.sync_optimizer()
         for g in self.all_groups():
             if what == "master":
                 shard = g.master if g.master is not None else g.shard_lp
@@ -847,6 +951,7 @@ class Zero3Engine:
                           target: str = "master", extra: Optional[Dict[int, torch.Tensor]] = None) -> List[str]:
         """Copies full tensors (by FQN) into this rank's shards.  Returns the missing names."""
         missing = []
+        self.sync_optimizer()
         for g in self.all_groups():
             if target != "master" and getattr(g, "frozen", False):
                 continue

@@ -46,6 +46,7 @@ class AdapterManager:
 
     def _snapshot(self) -> AdapterState:
         st = AdapterState()
+        self.engine.sync_optimizer()             # shards are read outside the step path
         for g in self._groups:
             d = {"master": self._host(g.master), "grad": self._host(g.grad_shard)}
             for name, per_group in self.optimizer.state.items():
@@ -61,6 +62,7 @@ class AdapterManager:
         return st
 
     def _restore(self, st: AdapterState) -> None:
+        self.engine.sync_optimizer()
         for g, d in zip(self._groups, st.groups):
             g.master.copy_(d["master"], non_blocking=True)
             g.grad_shard.copy_(d["grad"], non_blocking=True)

@@ -111,15 +111,23 @@ class Trainer:
             # every EP rank must size its peer-memory workspace identically
             self.model.ctx_defaults["ep_max_slots"] = int(a.data.sample_packing_sequence_len or 4096) \
                 * t.micro_batch_size * self.model_config.num_experts_per_tok
-            if t.softmax_auxiliary_loss or self.model_config.router_aux_loss_coef > 0:
-                coef = t.auxiliary_loss_multiplier if t.softmax_auxiliary_loss \
-                    else self.model_config.router_aux_loss_coef
+            # the load-balancing loss of the routers is weighted by the model's own
+            # router_aux_loss_coef (src/xorl/trainers/trainer.py:2081-2091)
+            coef = float(self.model_config.router_aux_loss_coef or 0.0)
+            if coef > 0:
                 for m in self.model.modules():
                     if hasattr(m, "aux_coef"):
                         m.aux_coef = coef
-                self.model.aux_loss_enabled = coef > 0
+                self.model.aux_loss_enabled = True
                 if t.moe_global_load_balancing:
                     self.model.ctx_defaults["aux_global_group"] = self.ps.group("dp")
+        if t.softmax_auxiliary_loss:
+            # z-loss on the lm-head logits: auxiliary_loss_multiplier * logsumexp(logits)^2 per
+            # supervised token (src/xorl/trainers/trainer.py:481-487)
+            if t.pipeline_parallel_size > 1:
+                raise NotImplementedError("softmax_auxiliary_loss (z-loss) is not supported with "
+                                          "pipeline parallelism")
+            self.model.z_loss_coef = float(t.auxiliary_loss_multiplier)
         from ..parallel.cp import attach_cp_strategy
         attach_cp_strategy(self.model, self.ps)
         recompute = t.enable_gradient_checkpointing and t.gradient_checkpointing_method != "no_recompute"
@@ -256,9 +264,11 @@ class Trainer:
                             self.ps.pp_rank, b["wait_s"], b["step_s"], 100 * b["measured_bubble_fraction"],
                             100 * b["analytic_bubble_fraction"], b["p2p_sent_bytes"] / 1e6)
             micro_batches = []
-        for mb in micro_batches:
+        for i, mb in enumerate(micro_batches):
             self.meter.add(mb)
             d = self._to_device(mb)
+            # gradient norms are taken unit by unit during the last micro-batch's backward
+            self.engine.final_micro_batch = i == len(micro_batches) - 1
             loss = self.engine.forward_backward(
                 d["input_ids"], d["labels"], position_ids=d.get("position_ids"),
                 cu_seqlens=d.get("cu_seqlens"), grad_scale=1.0 / global_tokens,
@@ -289,6 +299,8 @@ class Trainer:
         (src/xorl/trainers/training_utils.py:346-372)."""
         from ..adapters.lora import LoraLinear
         eng = self.engine
+        if hasattr(eng, "sync_optimizer"):
+            eng.sync_optimizer()
         with torch.no_grad():
             for unit in eng.units:
                 eng.gather(unit)
