@@ -33,6 +33,22 @@ QWEN3_8B = {
 }
 
 
+QWEN3_30B_A3B = {
+    "architectures": ["Qwen3MoeForCausalLM"], "model_type": "qwen3_moe", "vocab_size": 151936,
+    "hidden_size": 2048, "intermediate_size": 6144, "moe_intermediate_size": 768,
+    "num_hidden_layers": 48, "num_attention_heads": 32, "num_key_value_heads": 4, "head_dim": 128,
+    "num_experts": 128, "num_experts_per_tok": 8, "norm_topk_prob": True, "decoder_sparse_step": 1,
+    "mlp_only_layers": [], "output_router_logits": True, "router_aux_loss_coef": 0.001,
+    "hidden_act": "silu", "max_position_embeddings": 40960, "rms_norm_eps": 1e-6,
+    "rope_theta": 1000000.0, "rope_scaling": None, "tie_word_embeddings": False,
+    "attention_bias": False, "attention_dropout": 0.0, "initializer_range": 0.02,
+    "torch_dtype": "bfloat16", "use_cache": False, "sliding_window": None,
+    "use_sliding_window": False, "max_window_layers": 48, "bos_token_id": 151643,
+    "eos_token_id": 151645,
+}
+MODELS = {"qwen3-8b": QWEN3_8B, "qwen3-30b-a3b": QWEN3_30B_A3B}
+
+
 def _unavailable(why: str) -> None:
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
@@ -56,11 +72,11 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _write_model_dir(path: str, layers: int = 0) -> None:
+def _write_model_dir(path: str, layers: int = 0, model: str = "qwen3-8b") -> None:
     """config.json of the named architecture plus a minimal local tokenizer (the dummy dataset is
     pre-tokenised; the reference only asks the tokenizer for its length and special ids)."""
     os.makedirs(path, exist_ok=True)
-    cfg = dict(QWEN3_8B)
+    cfg = dict(MODELS[model])
     if layers:
         cfg["num_hidden_layers"] = layers
         cfg["max_window_layers"] = layers
@@ -78,13 +94,19 @@ def _write_model_dir(path: str, layers: int = 0) -> None:
     fast.save_pretrained(path)
 
 
-def _yaml(model_dir: str, out_dir: str, seq_len: int, world: int, gcm: str) -> str:
+def _yaml(model_dir: str, out_dir: str, seq_len: int, world: int, gcm: str, moe: bool = False,
+          ep: int = 1) -> str:
+    # MoE: the reference's stock expert backend (Triton grouped GEMM) and dispatch (all-to-all) that
+    # import offline; bf16 experts, since it refuses fp8 training on this architecture
+    # (src/xorl/fp8_training/config_compat.py:293-306)
+    moe_model = "  moe_implementation: triton\n  ep_dispatch: alltoall\n" if moe else ""
+    moe_train = f"  expert_parallel_size: {ep}\n" if moe else ""
     return f"""
 model:
   config_path: {model_dir}
   tokenizer_path: {model_dir}
   attn_implementation: native
-data:
+{moe_model}data:
   datasets:
     - path: dummy
       type: tokenized
@@ -100,7 +122,7 @@ train:
   data_parallel_mode: fsdp2
   data_parallel_replicate_size: 1
   data_parallel_shard_size: {world}
-  micro_batch_size: 1
+{moe_train}  micro_batch_size: 1
   gradient_accumulation_steps: 1
   optimizer: adamw
   lr: 1.0e-5
@@ -139,14 +161,22 @@ def run_reference(a) -> None:
     scratch = getattr(a, "scratch_dir", "") or os.path.join(__import__("tempfile").gettempdir(), "xorl_b200_bench")
     work = os.path.join(scratch, "ref_run")
     gcm = _recompute_method(getattr(a, "recompute", "auto"), world)
-    model_dir = os.path.join(work, "qwen3_8b")
+    model = getattr(a, "model", "qwen3-8b")
+    if model not in MODELS:
+        _unavailable(f"the reference arm has no configuration for model {model!r}")
+        return
+    moe = model == "qwen3-30b-a3b"
+    ep = (getattr(a, "ep", 0) or world) if moe else 1
+    if moe and gcm == "no_recompute" and getattr(a, "recompute", "auto") == "auto":
+        gcm = "recompute_full_layer"          # same setting as our arm for the MoE model
+    model_dir = os.path.join(work, model.replace("-", "_"))
     # named after this launch's rendezvous port, so ranks never pick up an earlier run's file
     cfg_path = os.path.join(work, f"cfg_{os.environ['MASTER_PORT']}_{gcm}.yaml")
     try:
         if rank == 0:
-            _write_model_dir(model_dir, getattr(a, "layers", 0))
+            _write_model_dir(model_dir, getattr(a, "layers", 0), model)
             with open(cfg_path, "w") as f:
-                f.write(_yaml(model_dir, os.path.join(work, "out"), a.seq_len, world, gcm))
+                f.write(_yaml(model_dir, os.path.join(work, "out"), a.seq_len, world, gcm, moe, ep))
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -161,7 +191,7 @@ def run_reference(a) -> None:
         from xorl.trainers.trainer import Trainer
         args = parse_args(Arguments)
         trainer = Trainer(args)
-        _measure(trainer, a, world, rank)
+        _measure(trainer, a, world, rank, model, ep)
     except Exception as e:  # noqa: BLE001
         import traceback
         traceback.print_exc()
@@ -201,7 +231,7 @@ def _synthetic_like(example, seq_len: int, vocab: int, seed: int):
     return {k: (v.pin_memory() if torch.is_tensor(v) and not v.is_cuda else v) for k, v in batch.items()}
 
 
-def _measure(trainer, a, world: int, rank: int) -> None:
+def _measure(trainer, a, world: int, rank: int, model: str = "qwen3-8b", ep: int = 1) -> None:
     import torch
     import torch.distributed as dist
     from xorl.distributed.offloading import build_activation_offloading_context
@@ -255,8 +285,9 @@ def _measure(trainer, a, world: int, rank: int) -> None:
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "impl": "reference",
-            "config": {"model": "qwen3-8b" + (f"[{a.layers} layers: DEBUG]" if getattr(a, "layers", 0) else ""),
-                       "global_batch": world, "seq_len": seq_len, "parallelism": f"fsdp{world}",
+            "config": {"model": model + (f"[{a.layers} layers: DEBUG]" if getattr(a, "layers", 0) else ""),
+                       "global_batch": world, "seq_len": seq_len,
+                       "parallelism": f"fsdp{world}" + (f"-ep{ep}-alltoall" if ep > 1 else ""),
                        "attn_implementation": str(args.model.attn_implementation),
                        "recompute": str(args.train.gradient_checkpointing_method),
                        "l2": "per-step working set >> 126 MB L2",

@@ -254,3 +254,80 @@ def test_ep_plan_kernel_matches_torch_formulation(N, rank, E, k, T):
     mine = slice(rank * El, (rank + 1) * El)
     ref_seg = torch.cat([padded.new_zeros(1), padded[mine].cumsum(0)]).clamp(max=cap // 128 * 128)
     assert torch.equal(seg.long(), ref_seg) and torch.equal(tot.long(), t_all[mine])
+
+
+# ---- block-scaled fp8 grouped GEMM (power-of-two scales on the tensor core) ----------------------
+def _mx_case(E, K, N, counts, seed=0):
+    from xorl_b200.ops import moe as moe_ops
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    ids = torch.cat([torch.full((c,), e, dtype=torch.int64) for e, c in enumerate(counts)])
+    dest, seg, _ = moe_ops.aligned_sort_indices(ids.cuda(), E)
+    rows = moe_ops.buffer_rows(ids.numel(), E)
+    x = torch.zeros(rows, K, dtype=torch.bfloat16)
+    x[dest.cpu()] = (torch.randn(ids.numel(), K, generator=g) * torch.rand(ids.numel(), 1, generator=g) * 3).bfloat16()
+    w = (torch.randn(E, K, N, generator=g) * 0.05 * (1 + torch.arange(E).view(E, 1, 1))).bfloat16()
+    return x.cuda(), w.cuda(), seg
+
+
+def test_mx_quantisers_match_the_restatement():
+    from xorl_b200.ops import fp8_grouped as fg
+    x, w, _ = _mx_case(3, 384, 256, [100, 0, 300])
+    q, sf = fg.quantize_rows(x)
+    qr, er = fg.quantize_rows_ref(x.cpu())
+    assert torch.equal(sf[:, :3].cpu().int() - 127, er)
+    assert torch.equal(q.cpu().view(torch.float8_e4m3fn).float(), qr.float())
+    qe = fg.quantize_experts(w)
+    wq, we = fg.quantize_weight_ref(w.cpu())
+    assert torch.equal(qe.sf_kn[:, :, :2].cpu().int() - 127, we)
+    assert torch.equal(qe.sf_nk[:, :, :3].cpu().int() - 127, we.transpose(1, 2))
+    assert torch.equal(qe.q_kn.cpu().view(torch.float8_e4m3fn).float(), wq.float())
+    assert torch.equal(qe.q_nk.cpu().view(torch.float8_e4m3fn).float(), wq.float().transpose(1, 2))
+
+
+@pytest.mark.parametrize("E,K,N,counts", [
+    (3, 384, 256, [100, 0, 300]),                       # an empty expert, N not a multiple of 192
+    (4, 768, 2048, [129, 640, 1, 255]),                 # down projection of Qwen3-30B-A3B
+    (16, 2048, 1536, [2048 + 37 * (i % 5) - 64 * (i % 3) for i in range(16)]),   # gate_up projection, EP 8 load
+])
+def test_mx_grouped_gemm_matches_dequantised_matmul(E, K, N, counts):
+    from xorl_b200.ops import _lib
+    from xorl_b200.ops import fp8_grouped as fg
+    x, w, seg = _mx_case(E, K, N, counts, seed=E)
+    xq, sfx = fg.quantize_rows(x)
+    qe = fg.quantize_experts(w)
+    y = fg.grouped_rows_mx(xq, sfx, qe.q_nk, qe.sf_nk, seg)
+    torch.cuda.synchronize()
+    _lib.raise_on_status()
+    ref = fg.grouped_rows_ref(x.cpu().float(), w.cpu().float(), seg.cpu())
+    err = (y.cpu().float() - ref).abs().max() / ref.abs().max()
+    assert err < 6e-3, err                               # bf16 rounding of the output only
+    # against the unquantised product: the error of the fp8 scheme itself
+    exact = torch.zeros_like(ref)
+    s = seg.cpu().tolist()
+    for e in range(E):
+        exact[s[e]:s[e + 1]] = x.cpu().float()[s[e]:s[e + 1]] @ w.cpu().float()[e]
+    rel = (y.cpu().float() - exact).norm() / exact.norm()
+    assert rel < 0.05, rel
+
+
+def test_mx_grouped_linear_gradients():
+    """Forward and input gradient in fp8 against the bf16 grouped linear; weight gradient (bf16) equal."""
+    from xorl_b200.ops import fp8_grouped as fg
+    from xorl_b200.ops import moe as moe_ops
+    x, w, seg = _mx_case(4, 256, 384, [200, 31, 0, 500], seed=5)
+    outs = {}
+    for mode in (None, "fp8", "bf16"):
+        xi, wi = x.clone().requires_grad_(), w.clone().requires_grad_()
+        y = moe_ops.grouped_linear(xi, wi, seg, mode)
+        dy = torch.randn(y.shape, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+        valid = torch.zeros(y.shape[0], 1, device="cuda", dtype=torch.bfloat16)
+        s = seg.tolist()
+        valid[: s[-1]] = 1
+        y.backward(dy * valid)
+        outs[mode] = (y.float(), xi.grad.float(), wi.grad.float())
+    for mode in ("fp8", "bf16"):
+        for a, b, name, tol in zip(outs[mode], outs[None], ("y", "dx", "dw"), (0.05, 0.05, 1e-6)):
+            if mode == "bf16" and name == "dx":
+                tol = 1e-6
+            rel = (a - b).norm() / b.norm()
+            assert rel <= tol, (mode, name, float(rel))

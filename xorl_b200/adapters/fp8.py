@@ -76,9 +76,27 @@ def inject_fp8_training(model: nn.Module, train_args) -> List[str]:
     n_layers = getattr(model.config, "num_hidden_layers", 0)
     skip_first, skip_last = train_args.fp8_training_num_first_layers_bf16, train_args.fp8_training_num_last_layers_bf16
     wrapped = []
+    from ..models.moe import Experts
+
+    def layer_skipped(full: str) -> bool:
+        parts = full.split(".")
+        if "layers" in parts:
+            li = int(parts[parts.index("layers") + 1])
+            return li < skip_first or li >= n_layers - skip_last
+        return False
+
     for pname, parent in list(model.named_modules()):
         for cname, child in list(parent.named_children()):
             full = f"{pname}.{cname}" if pname else cname
+            if isinstance(child, Experts):
+                # stacked routed experts: both grouped GEMMs of the expert MLP run in block-scaled fp8
+                # (1 x 128 activation scales, 128 x 128 weight scales; ops/fp8_grouped.py)
+                if any(x in full for x in exclude) or (targets and not any(t in full for t in targets)) \
+                        or layer_skipped(full):
+                    continue
+                child.fp8_mode = "fp8" if train_args.fp8_training_backward == "fp8" else "bf16"
+                wrapped.append(full)
+                continue
             if not isinstance(child, Linear) or any(x in full for x in exclude):
                 continue
             if targets and not any(t in full for t in targets):

@@ -19,6 +19,8 @@
 // epilogue threads of both CTAs.  Every wait is bounded; after a timeout all roles of both CTAs
 // drain and the tensor memory is freed.
 // Same operand layouts and contract as the single-CTA kernel in gemm.cu (a_mn / b_mn).
+#include <stdlib.h>
+
 #include "gemm2_core.cuh"
 
 namespace xb_gemm2 {
@@ -26,11 +28,12 @@ namespace xb_gemm2 {
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-             const __grid_constant__ CUtensorMap tmap_b64, const Params p) {
+             const __grid_constant__ CUtensorMap tmap_b64, const __grid_constant__ CUtensorMap tmap_c,
+             const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + OFF_BARS);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -53,6 +56,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     tma_prefetch_desc(&tmap_b64);
+    if (p.tma_epilogue) tma_prefetch_desc(&tmap_c);
   }
   __syncthreads();
   if (warp == 1) {
@@ -206,6 +210,58 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       const int row = item.m0 + 256 * u + (int)cta * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + u * BN + ((uint32_t)(q * 32) << 16);
       const int nchunks = u < item.nsub ? item.ncols / 32 : 0;
+      if (p.tma_epilogue) {
+        // Slabs of 128 rows x 128 bytes (64 bf16 or 32 fp32 columns) go through 128B-swizzled shared
+        // memory and one TMA store (or TMA add, when accumulating into fp32) each: global memory sees
+        // whole 128-byte row segments and no thread waits on a global store.
+        uint8_t* slab = smem + OFF_SLAB + u * SLAB_BYTES;
+        const int r = q * 32 + lane;
+        uint8_t* srow = slab + r * 128;
+        const bool leader = (warp - 2 - 4 * u) == 0 && lane == 0;
+        const int row0 = item.m0 + 256 * u + (int)cta * BM;
+        const int per_slab = p.out_fp32 ? 1 : 2;             // 32-column chunks per slab
+#pragma unroll 1
+        for (int c = 0; c < nchunks; c += per_slab) {
+          const int col0 = item.n0 + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t v[2][32];
+          tmem_ld_32x32(taddr + c * 32, v[0]);
+          if (per_slab == 2) tmem_ld_32x32(taddr + c * 32 + 32, v[1]);
+          tc_wait_ld();
+          if (leader) tma_store_wait_read<0>();               // the previous slab has left shared memory
+          if (u == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+          else asm volatile("bar.sync 3, 128;" ::: "memory");
+          if (p.out_fp32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(srow + ((j ^ (r & 7)) * 16)) =
+                  make_uint4(v[0][4 * j], v[0][4 * j + 1], v[0][4 * j + 2], v[0][4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(v[h][8 * j]), __uint_as_float(v[h][8 * j + 1]));
+                o.y = pack_bf16x2(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3]));
+                o.z = pack_bf16x2(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5]));
+                o.w = pack_bf16x2(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7]));
+                *reinterpret_cast<uint4*>(srow + (((h * 4 + j) ^ (r & 7)) * 16)) = o;
+              }
+          }
+          fence_proxy_async_smem();
+          if (u == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+          else asm volatile("bar.sync 3, 128;" ::: "memory");
+          if (leader) {
+            if (p.accumulate) tma_reduce_add_2d(&tmap_c, slab, col0, row0);
+            else tma_store_2d(&tmap_c, slab, col0, row0);
+            tma_store_commit();
+          }
+        }
+        tc_fence_before();
+        mbar_arrive_cluster(empty_leader);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < nchunks; ++c) {
         const int col0 = item.n0 + c * 32;
@@ -273,6 +329,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       tc_fence_before();
       mbar_arrive_cluster(empty_leader);
     }
+    if (p.tma_epilogue && (warp - 2 - 4 * u) == 0 && lane == 0) tma_store_wait<0>();
   }
 
   // Both CTAs must be done with tensor memory (and with each other's barriers) before it is freed.
@@ -314,13 +371,13 @@ static int resident_pairs() {
 }
 
 template <bool A_MN, bool B_MN>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb64, Params& p,
-                  cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb64, const CUtensorMap& tc,
+                  Params& p, cudaStream_t stream) {
   const int pairs_max = resident_pairs<A_MN, B_MN>();
   if (pairs_max <= 0) return -10;
   plan_items(p, pairs_max, true);
   const int pairs = p.num_items < pairs_max ? p.num_items : pairs_max;
-  gemm2_kernel<A_MN, B_MN><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb64, p);
+  gemm2_kernel<A_MN, B_MN><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb64, tc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -364,9 +421,23 @@ XB_API int xb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N
   p.num_n_blocks = (N + BN - 1) / BN;
   p.group_m = 4;
   p.status = xb_status_ptr();
+  // Output through shared memory + TMA when C can be described by a tensor map (16-byte aligned base
+  // and row pitch) and the mode has a TMA form: plain store, or fp32 add for accumulation.
+  CUtensorMap tc = ta;
+  const int es = out_fp32 ? 4 : 2;
+  p.tma_epilogue = 0;
+  static const bool tma_epi_enabled = []() {
+    const char* e = getenv("XORL_B200_GEMM_TMA_EPILOGUE");
+    return !(e && e[0] == '0');
+  }();
+  if (tma_epi_enabled && (ldc * es) % 16 == 0 && reinterpret_cast<uintptr_t>(C) % 16 == 0 && (!accumulate || out_fp32)) {
+    if (xb_make_tmap_2d(&tc, C, out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, es, M, N,
+                        ldc, BM, 128 / es, CU_TENSOR_MAP_SWIZZLE_128B) == 0)
+      p.tma_epilogue = 1;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (!a_mn && !b_mn) return launch<false, false>(ta, tb, tb64, p, st);
-  if (!a_mn && b_mn) return launch<false, true>(ta, tb, tb64, p, st);
-  if (a_mn && !b_mn) return launch<true, false>(ta, tb, tb64, p, st);
-  return launch<true, true>(ta, tb, tb64, p, st);
+  if (!a_mn && !b_mn) return launch<false, false>(ta, tb, tb64, tc, p, st);
+  if (!a_mn && b_mn) return launch<false, true>(ta, tb, tb64, tc, p, st);
+  if (a_mn && !b_mn) return launch<true, false>(ta, tb, tb64, tc, p, st);
+  return launch<true, true>(ta, tb, tb64, tc, p, st);
 }

@@ -18,7 +18,11 @@ constexpr int B_BYTES = BNH * BK * 2;
 constexpr int STAGE_BYTES = 2 * A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 320;   // TMA warp, MMA warp, 2 x 4 epilogue warps
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+// Epilogue staging: one 16 KB slab (128 rows x 128 bytes, 128B-swizzled) per epilogue warp group.
+constexpr int SLAB_BYTES = BM * 128;
+constexpr int OFF_SLAB = STAGES * STAGE_BYTES;
+constexpr int OFF_BARS = OFF_SLAB + 2 * SLAB_BYTES;
+constexpr int SMEM_BYTES = OFF_BARS + 1024 + 256;
 
 struct Params {
   int M, N, K;
@@ -30,6 +34,7 @@ struct Params {
   int full_items;                            // tiles [0, full_items) are processed whole
   int split_m, split_n;                      // the remaining tiles are cut split_m x split_n ways
   int num_items;
+  int tma_epilogue;                          // C is written through shared memory and TMA stores
   int* status;
 };
 

@@ -706,7 +706,7 @@ XB_API int xb_gemm_fused(XbFusedArgs* a, void* stream) {
     tb64 = tb;
   }
   if (rc) return -3;
-  Params p;
+  Params p{};
   p.M = M; p.N = N; p.K = K;
   p.C = a->C; p.ldc = a->ldc;
   p.out_fp32 = a->out_fp32; p.accumulate = a->accumulate;

@@ -6,7 +6,8 @@
 //   wgrad mode : C[e] (+)= A[rows of e, :]^T @ B[rows of e, :]     per-expert weight gradient
 //
 // Same warp-specialised persistent structure as csrc/gemm.cu (TMA producer / MMA issuer / four
-// epilogue warps, 4-stage ring, two TMEM accumulators).  Because segments are 128-row aligned a
+// epilogue warps, 4-stage ring, two TMEM accumulators).  In rows mode the epilogue stages 64-column
+// bf16 slabs in swizzled shared memory and writes them with TMA stores.  Because segments are 128-row aligned a
 // 128-row tile never straddles two experts, and a 64-row reduction block never mixes experts.
 // Replaces the Triton group_gemm_same_nk / same_mn kernels of the reference
 // (src/xorl/ops/group_gemm/kernel/group_gemm.py:80-377).
@@ -18,7 +19,11 @@ constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192, TMEM_COLS = 512;
 constexpr int MAX_E = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + (MAX_E + 1) * 4;
+constexpr int SLAB_COLS = 64;                      // rows-mode epilogue staging: 128 rows x 64 columns bf16
+constexpr int SLAB_BYTES = BM * SLAB_COLS * 2;
+constexpr int OFF_SLAB = STAGES * STAGE_BYTES;
+constexpr int OFF_BARS = OFF_SLAB + SLAB_BYTES;
+constexpr int SMEM_BYTES = OFF_BARS + 1024 + 256 + (MAX_E + 1) * 4;
 
 struct Params {
   int mode;  // 0 rows, 1 wgrad
@@ -46,7 +51,16 @@ struct Tile {
 __device__ __forceinline__ Tile get_tile(const Params& p, const int* sseg, int t) {
   Tile r;
   if (p.mode == 0) {
-    const int mb = t % p.num_m_blocks, nb = t / p.num_m_blocks;
+    // groups of GROUP_M row blocks, inside a group row block fastest: the CTAs running at any time
+    // share a few B tiles and one group of A rows (resident in L2) instead of streaming all of A once
+    // per column block
+    constexpr int GROUP_M = 16;
+    const int per_group = GROUP_M * p.num_n_blocks;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = min(GROUP_M, p.num_m_blocks - first_m);
+    const int u = t - g * per_group;
+    const int mb = first_m + u % gsz, nb = u / gsz;
     r.m0 = mb * BM;
     r.n0 = nb * BN;
     r.k0 = 0;
@@ -71,12 +85,12 @@ __device__ __forceinline__ Tile get_tile(const Params& p, const int* sseg, int t
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ggemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-             const Params p) {
+             const __grid_constant__ CUtensorMap tmap_c, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~(uintptr_t)1023);
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
-  int* sseg = reinterpret_cast<int*>(smem + STAGES * STAGE_BYTES + 256);
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + OFF_BARS);
+  int* sseg = reinterpret_cast<int*>(smem + OFF_BARS + 256);
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = p.mode == 0 ? p.num_m_blocks * p.num_n_blocks
@@ -89,6 +103,7 @@ ggemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.mode == 0) tma_prefetch_desc(&tmap_c);
   }
   if (warp == 1) { tmem_alloc(&bars->tmem_base, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
@@ -194,6 +209,46 @@ ggemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       } else if (p.accumulate) {
         continue;  // nothing to add for an expert without tokens
       }
+      if (p.mode == 0) {
+        // rows mode (bf16 out, no accumulation): stage 64-column slabs in 128B-swizzled shared memory
+        // and let TMA write them, so that global memory sees whole 128-byte row segments
+        const int r = q * 32 + lane;
+        const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+        uint8_t* slab = smem + OFF_SLAB;
+        uint8_t* srow = slab + r * 128;
+#pragma unroll 1
+        for (int sl = 0; sl < BN / SLAB_COLS; ++sl) {
+          const int col0 = tl.n0 + sl * SLAB_COLS;
+          if (col0 >= p.N) break;
+          uint32_t v[2][32];
+          tmem_ld_32x32(taddr + sl * SLAB_COLS, v[0]);
+          tmem_ld_32x32(taddr + sl * SLAB_COLS + 32, v[1]);
+          tc_wait_ld();
+          if (warp == 2 && lane == 0) tma_store_wait_read<0>();
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[h][8 * j]), __uint_as_float(v[h][8 * j + 1]));
+              o.y = pack_bf16x2(__uint_as_float(v[h][8 * j + 2]), __uint_as_float(v[h][8 * j + 3]));
+              o.z = pack_bf16x2(__uint_as_float(v[h][8 * j + 4]), __uint_as_float(v[h][8 * j + 5]));
+              o.w = pack_bf16x2(__uint_as_float(v[h][8 * j + 6]), __uint_as_float(v[h][8 * j + 7]));
+              *reinterpret_cast<uint4*>(srow + (((h * 4 + j) ^ (r & 7)) * 16)) = o;
+            }
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          if (warp == 2 && lane == 0) {
+            tma_store_2d(&tmap_c, slab, col0, tl.m0);
+            tma_store_commit();
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&bars->tmem_empty[acc]);
+        ++tcount;
+        continue;
+      }
       const int row = tl.m0 + q * 32 + lane;
       const int row_limit = p.mode == 0 ? p.R : p.M;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
@@ -265,13 +320,15 @@ ggemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         ++tcount;
       }
     }
+    if (p.mode == 0 && warp == 2 && lane == 0) tma_store_wait<0>();
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 }
 
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, cudaStream_t st) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Params& p,
+                  cudaStream_t st) {
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -283,7 +340,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p,
   const int tiles = p.mode == 0 ? p.num_m_blocks * p.num_n_blocks : p.E * p.num_m_blocks * p.num_n_blocks;
   if (tiles <= 0) return 0;
   const int grid = tiles < xb_sm_count() ? tiles : xb_sm_count();
-  ggemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, p);
+  ggemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, tc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -296,10 +353,13 @@ XB_API int xb_grouped_gemm_rows(const void* A, const void* B, void* C, const int
                                 void* stream) {
   using namespace xb_ggemm;
   if (E <= 0 || R <= 0) return 0;
-  if (E > MAX_E || (R % BM) || (lda % 8) || (K % 8) || (N % 8)) return -1;
-  CUtensorMap ta, tb;
+  if (E > MAX_E || (R % BM) || (lda % 8) || (K % 8) || (N % 8) || (ldc % 8) ||
+      (reinterpret_cast<uintptr_t>(C) % 16)) return -1;
+  CUtensorMap ta, tb, tc;
   if (xb_make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, K, lda, BM, BK,
                       CU_TENSOR_MAP_SWIZZLE_128B)) return -2;
+  if (xb_make_tmap_2d(&tc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, R, N, ldc, BM, SLAB_COLS,
+                      CU_TENSOR_MAP_SWIZZLE_128B)) return -4;
   int rc;
   if (b_mn)
     rc = xb_make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, E, K, N, (uint64_t)K * N, N, 1,
@@ -313,7 +373,7 @@ XB_API int xb_grouped_gemm_rows(const void* A, const void* B, void* C, const int
   p.out_fp32 = 0; p.accumulate = 0; p.b_mn = b_mn;
   p.num_m_blocks = (int)(R / BM); p.num_n_blocks = (N + BN - 1) / BN;
   p.status = xb_status_ptr();
-  return launch(ta, tb, p, (cudaStream_t)stream);
+  return launch(ta, tb, tc, p, (cudaStream_t)stream);
 }
 
 // A [R, M] (lda), B [R, N] (ldb), C [E, M, N] contiguous; C[e] (+)= A[seg[e]:seg[e+1]]^T @ B[same].
@@ -333,5 +393,5 @@ XB_API int xb_grouped_gemm_wgrad(const void* A, const void* B, void* C, const in
   p.out_fp32 = out_fp32; p.accumulate = accumulate; p.b_mn = 1;
   p.num_m_blocks = (M + BM - 1) / BM; p.num_n_blocks = (N + BN - 1) / BN;
   p.status = xb_status_ptr();
-  return launch(ta, tb, p, (cudaStream_t)stream);
+  return launch(ta, tb, ta, p, (cudaStream_t)stream);   // no output tensor map in wgrad mode
 }

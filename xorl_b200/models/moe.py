@@ -59,6 +59,9 @@ class Experts(nn.Module):
         H, I = hidden or cfg.hidden_size, cfg.moe_intermediate_size
         self.num_local = num_local
         self.activation = activation
+        # block-scaled fp8 expert GEMMs (train.enable_fp8_training): None, "fp8" or "bf16" = precision
+        # of the input-gradient GEMM (train.fp8_training_backward)
+        self.fp8_mode: Optional[str] = None
         self.gate_up_proj = nn.Parameter(torch.empty(num_local, H, (2 if gated else 1) * I, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(num_local, I, H, dtype=dtype, device=device))
         self.gate_up_proj._xb_expert = True
@@ -78,11 +81,13 @@ class Experts(nn.Module):
                     mark_ep(prm, ps.rank_in("ep"), ps.ep_size)
 
     def mlp_kwargs(self):
-        if self.gate_up_bias is None and self.swiglu_limit is None and self.activation is None:
-            return {}
-        kw = dict(gate_up_bias=self.gate_up_bias, down_bias=self.down_bias, swiglu_limit=self.swiglu_limit)
-        if self.activation is not None:
-            kw["activation"] = self.activation
+        kw = {}
+        if not (self.gate_up_bias is None and self.swiglu_limit is None and self.activation is None):
+            kw = dict(gate_up_bias=self.gate_up_bias, down_bias=self.down_bias, swiglu_limit=self.swiglu_limit)
+            if self.activation is not None:
+                kw["activation"] = self.activation
+        if self.fp8_mode is not None:
+            kw["fp8"] = self.fp8_mode
         return kw
 
     def forward(self, x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:

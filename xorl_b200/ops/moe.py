@@ -242,7 +242,12 @@ class _GroupedLinear(torch.autograd.Function):
         return dx, dw, None
 
 
-def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg: torch.Tensor) -> torch.Tensor:
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg: torch.Tensor, fp8: Optional[str] = None) -> torch.Tensor:
+    """``fp8``: None (bf16 GEMMs), "fp8" (block-scaled fp8 forward and input gradient) or "bf16"
+    (fp8 forward, bf16 input gradient) -- ``train.fp8_training_backward``."""
+    if fp8 is not None:
+        from .fp8_grouped import grouped_linear_fp8
+        return grouped_linear_fp8(x, w, seg, backward=fp8)
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 \
             and w.shape[1] % 8 == 0 and w.shape[2] % 8 == 0:
         return _GroupedLinear.apply(x, w, seg)
@@ -272,19 +277,21 @@ def clamped_swiglu(h: torch.Tensor, limit: float, alpha: float = 1.702) -> torch
 def expert_mlp_aligned(x_buf: torch.Tensor, seg: torch.Tensor, gate_up: torch.Tensor,
                        down: torch.Tensor, gate_up_bias: Optional[torch.Tensor] = None,
                        down_bias: Optional[torch.Tensor] = None,
-                       swiglu_limit: Optional[float] = None, activation: Optional[str] = None) -> torch.Tensor:
+                       swiglu_limit: Optional[float] = None, activation: Optional[str] = None,
+                       fp8: Optional[str] = None) -> torch.Tensor:
     """SwiGLU expert MLP over a segment-aligned token buffer (optional per-expert biases and the
-    clamped activation of gpt-oss); ``activation="relu2"``: non-gated ``relu(up(x))^2`` experts."""
-    h = grouped_linear(x_buf, gate_up, seg)
+    clamped activation of gpt-oss); ``activation="relu2"``: non-gated ``relu(up(x))^2`` experts.
+    ``fp8``: run both grouped GEMMs in block-scaled fp8 (see ``grouped_linear``)."""
+    h = grouped_linear(x_buf, gate_up, seg, fp8)
     if activation == "relu2":
-        return grouped_linear(torch.relu(h).square(), down, seg)
+        return grouped_linear(torch.relu(h).square(), down, seg, fp8)
     if gate_up_bias is None and swiglu_limit is None:
-        return grouped_linear(swiglu(h), down, seg)
+        return grouped_linear(swiglu(h), down, seg, fp8)
     eid = _rows_to_expert(seg, h.shape[0])
     if gate_up_bias is not None:
         h = h + gate_up_bias.index_select(0, eid).to(h.dtype)
     a = clamped_swiglu(h, swiglu_limit) if swiglu_limit is not None else swiglu(h)
-    y = grouped_linear(a, down, seg)
+    y = grouped_linear(a, down, seg, fp8)
     if down_bias is not None:
         y = y + down_bias.index_select(0, eid[: y.shape[0]]).to(y.dtype)
     return y

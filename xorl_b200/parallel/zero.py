@@ -637,6 +637,10 @@ class Zero3Engine:
                     dist.all_reduce(g.grad_shard, group=self.sp_sync_pg)
 
     def zero_grad(self) -> None:
+        # called once per optimizer step, before the first forward that sees the new weights:
+        # quantised copies of the weights (block fp8 experts) made from the old ones are stale
+        from ..ops.fp8_grouped import invalidate_weight_cache
+        invalidate_weight_cache()
         self.micro_batches = 0
         if self.symm is not None:
             self.sync_optimizer()
@@ -952,6 +956,9 @@ class Zero3Engine:
         """Copies full tensors (by FQN) into this rank's shards.  Returns the missing names."""
         missing = []
         self.sync_optimizer()
+        if target == "master":
+            from ..ops.fp8_grouped import invalidate_weight_cache
+            invalidate_weight_cache()
         for g in self.all_groups():
             if target != "master" and getattr(g, "frozen", False):
                 continue

@@ -8,6 +8,7 @@
     python -m xorl_b200.utils.kernel_bench conv1d --tokens 32768 --hidden 8192 --doc-len 4096
     python -m xorl_b200.utils.kernel_bench dequant4 --n 12288 --k 4096
     python -m xorl_b200.utils.kernel_bench symgemm --m 4096 --k 12288 --block 1024
+    python -m xorl_b200.utils.kernel_bench grouped --experts 16 --m 32768 --k 2048 --n 1536
 
 Timing: CUDA events on the launching stream around each run, ``--warmup`` untimed runs, the median
 of ``--iters`` runs, and a buffer larger than L2 written between runs.  ``--no-lib`` skips the
@@ -235,6 +236,46 @@ BENCHES = {"symgemm": bench_symgemm, "conv1d": bench_conv1d, "dequant4": bench_d
            "rmsnorm": bench_rmsnorm, "fused_gemm": bench_fused_gemm}
 
 
+def bench_grouped(a) -> Dict:
+    """Grouped expert GEMM (rows mode): bf16 tcgen05 kernel, block-scaled fp8 kernel (operands
+    quantised beforehand; the row quantiser is timed separately) and ``torch._grouped_mm``.
+    ``--m`` rows are spread over ``--experts`` experts with an uneven load (+-12 %)."""
+    from ..ops import fp8_grouped as fg
+    from ..ops import moe as moe_ops
+    E, K, N = a.experts, a.k, a.n
+    base = a.m // E
+    counts = [base + (base // 8) * ((i % 3) - 1) for i in range(E)]
+    ids = torch.cat([torch.full((c,), e, dtype=torch.int64) for e, c in enumerate(counts)]).cuda()
+    dest, seg, _ = moe_ops.aligned_sort_indices(ids, E)
+    rows = moe_ops.buffer_rows(ids.numel(), E)
+    x = torch.zeros(rows, K, device="cuda", dtype=torch.bfloat16)
+    x[dest] = torch.randn(ids.numel(), K, device="cuda").bfloat16()
+    w = (torch.randn(E, K, N, device="cuda") * 0.05).bfloat16()
+    out = torch.zeros(rows, N, device="cuda", dtype=torch.bfloat16)
+    flops = 2.0 * sum(counts) * K * N
+    ms_bf16 = _time(lambda: moe_ops._grouped_rows_cuda(x, w, seg, out, b_kmajor=False), a.warmup, a.iters, a.flush)
+    xq, sfx = fg.quantize_rows(x)
+    qe = fg.quantize_experts(w)
+    ms_fp8 = _time(lambda: fg.grouped_rows_mx(xq, sfx, qe.q_nk, qe.sf_nk, seg, out), a.warmup, a.iters, a.flush)
+    ms_q = _time(lambda: fg.quantize_rows(x), a.warmup, a.iters, a.flush)
+    ms_wq = _time(lambda: fg.quantize_experts(w), a.warmup, a.iters, a.flush)
+    r = {"kernel": "grouped_gemm_rows", "experts": E, "rows": sum(counts), "k": K, "n": N,
+         "bf16_ms": ms_bf16, "bf16_tflops": flops / ms_bf16 / 1e9, "fp8_ms": ms_fp8, "fp8_tflops": flops / ms_fp8 / 1e9,
+         "fp8_over_bf16": ms_bf16 / ms_fp8, "row_quant_ms": ms_q, "weight_quant_ms": ms_wq}
+    if not a.no_lib and hasattr(torch, "_grouped_mm"):
+        xs = torch.randn(sum(counts), K, device="cuda").bfloat16()
+        offs = torch.tensor(counts, device="cuda").cumsum(0).to(torch.int32)
+        try:
+            ms_lib = _time(lambda: torch._grouped_mm(xs, w, offs=offs), a.warmup, a.iters, a.flush)
+            r.update(lib_ms=ms_lib, lib_tflops=flops / ms_lib / 1e9)
+        except Exception as e:  # noqa: BLE001
+            r["lib_error"] = str(e)[:120]
+    return r
+
+
+BENCHES["grouped"] = bench_grouped
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=sorted(BENCHES))
@@ -256,6 +297,7 @@ def main(argv=None) -> None:
     ap.add_argument("--no-lib", action="store_true")
     ap.add_argument("--ranks", type=int, default=2)
     ap.add_argument("--block", type=int, default=1024)
+    ap.add_argument("--experts", type=int, default=16)
     a = ap.parse_args(argv)
     a.flush = torch.zeros(256 << 20, device="cuda", dtype=torch.uint8)
     print(json.dumps(BENCHES[a.kernel](a)))
