@@ -207,7 +207,49 @@ ep_plan_kernel(const long long* __restrict__ indices, int S, const int* __restri
   }
 }
 
+// counts[e] = number of slots routed to expert e (shared-memory histogram, integer atomics)
+__global__ void __launch_bounds__(256)
+moe_histogram_kernel(const long long* __restrict__ idx, int S, int* __restrict__ counts, int E) {
+  extern __shared__ int sh[];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) sh[e] = 0;
+  __syncthreads();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < S; i += gridDim.x * blockDim.x) {
+    const long long e = idx[i];
+    if (e >= 0 && e < E) atomicAdd(&sh[(int)e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    if (sh[e]) atomicAdd(&counts[e], sh[e]);
+}
+
+// meta (tag | rank << 24, or -1 for rows nobody owns) -> (rank or -1, slot)
+__global__ void __launch_bounds__(256)
+ep_meta_targets_kernel(const int* __restrict__ meta, int n, int* __restrict__ rank, int* __restrict__ slot) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int m = meta[i];
+  rank[i] = m >= 0 ? (m >> 24) : -1;
+  slot[i] = m >= 0 ? (m & 0xFFFFFF) : 0;
+}
+
 }  // namespace
+
+XB_API int xb_moe_histogram(const long long* idx, int S, int* counts, int E, void* stream) {
+  if (E <= 0 || E > 8192) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(counts, 0, (size_t)E * sizeof(int), st) != cudaSuccess) return -2;
+  if (S <= 0) return 0;
+  int blocks = (S + 256 * 8 - 1) / (256 * 8);
+  if (blocks > 64) blocks = 64;
+  moe_histogram_kernel<<<blocks, 256, (size_t)E * sizeof(int), st>>>(idx, S, counts, E);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+XB_API int xb_ep_meta_targets(const int* meta, int n, int* rank, int* slot, void* stream) {
+  if (n <= 0) return 0;
+  ep_meta_targets_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(meta, n, rank, slot);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
 
 XB_API int xb_ep_plan(const long long* indices, int S, const int* table, int rank, int n, int E, int El, int cap,
                       int* dest_rank, int* dest_row, int* seg, int* tot, int* overflow, void* stream) {

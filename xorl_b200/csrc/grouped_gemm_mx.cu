@@ -50,9 +50,9 @@ constexpr int SMEM_BYTES = OFF_SEG + (MAX_E + 1) * 4 + 1024;
 struct Params {
   int E, R, N, K;
   const int* seg;
-  const uint8_t* sfa;      // [R, sf_ld]              sf_ld = K/128 rounded up to 16
-  const uint8_t* sfb;      // [E, ceil(N/128), sf_ld]
-  int sf_ld;
+  const uint8_t* sfa;      // [R, sfa_ld]               row strides: multiples of 16 >= K/128
+  const uint8_t* sfb;      // [E, ceil(N/128), sfb_ld]
+  int sfa_ld, sfb_ld;
   __nv_bfloat16* C;
   long long ldc;
   int num_m_blocks, num_n_blocks;
@@ -277,8 +277,8 @@ ggemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int sub = tl.n0 & 127;           // offset of the tile inside its first 128-column block
       const int nb0 = tl.n0 >> 7;
       const int nb1 = min(nb0 + 1, NB - 1);
-      const uint8_t* b0p = p.sfb + ((long long)tl.e * NB + nb0) * p.sf_ld;
-      const uint8_t* b1p = p.sfb + ((long long)tl.e * NB + nb1) * p.sf_ld;
+      const uint8_t* b0p = p.sfb + ((long long)tl.e * NB + nb0) * p.sfb_ld;
+      const uint8_t* b1p = p.sfb + ((long long)tl.e * NB + nb1) * p.sfb_ld;
       uint4 va[4], vb0, vb1;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((kb & 15) == 0) {
@@ -286,7 +286,7 @@ ggemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int row = min(tl.m0 + j * 32 + lane, p.R - 1);
-            va[j] = __ldg(reinterpret_cast<const uint4*>(p.sfa + (long long)row * p.sf_ld + kb));
+            va[j] = __ldg(reinterpret_cast<const uint4*>(p.sfa + (long long)row * p.sfa_ld + kb));
           }
           vb0 = __ldg(reinterpret_cast<const uint4*>(b0p + kb));
           vb1 = __ldg(reinterpret_cast<const uint4*>(b1p + kb));
@@ -432,16 +432,17 @@ quant_mx_weight_kernel(const __nv_bfloat16* __restrict__ w, uint8_t* __restrict_
 
 }  // namespace xb_ggemm_mx
 
-// A e4m3 [R, K] (row stride lda bytes), sfa UE8M0 [R, sf_ld]; B e4m3 [E, N, K] contiguous, sfb UE8M0
-// [E, ceil(N/128), sf_ld]; sf_ld = K/128 rounded up to a multiple of 16 (both arrays 16-byte aligned);
+// A e4m3 [R, K] (row stride lda bytes), sfa UE8M0 [R, sfa_ld]; B e4m3 [E, N, K] contiguous, sfb UE8M0
+// [E, ceil(N/128), sfb_ld]; the scale row strides are multiples of 16 >= K/128 (arrays 16-byte aligned);
 // C bf16 [R, N] (row stride ldc elements); seg int32 [E+1] with 128-aligned entries and seg[E] <= R.
 // K a multiple of 128, N a multiple of 16.
 XB_API int xb_grouped_gemm_mx_rows(const void* A, const void* sfa, const void* B, const void* sfb, void* C,
                                    const int* seg, int E, long long R, int N, int K, long long lda,
-                                   long long ldc, int sf_ld, void* stream) {
+                                   long long ldc, int sfa_ld, int sfb_ld, void* stream) {
   using namespace xb_ggemm_mx;
   if (E <= 0 || R <= 0) return 0;
-  if (E > MAX_E || (R % BM) || (lda % 16) || (K % BK) || (N % 16) || (sf_ld % 16) || sf_ld < K / BK ||
+  if (E > MAX_E || (R % BM) || (lda % 16) || (K % BK) || (N % 16) || (sfa_ld % 16) || sfa_ld < K / BK ||
+      (sfb_ld % 16) || sfb_ld < K / BK ||
       (reinterpret_cast<uintptr_t>(sfa) % 16) || (reinterpret_cast<uintptr_t>(sfb) % 16))
     return -1;
   if ((ldc % 8) || (reinterpret_cast<uintptr_t>(C) % 16)) return -1;
@@ -455,7 +456,7 @@ XB_API int xb_grouped_gemm_mx_rows(const void* A, const void* sfa, const void* B
     return -3;
   Params p{};
   p.E = E; p.R = (int)R; p.N = N; p.K = K; p.seg = seg;
-  p.sfa = (const uint8_t*)sfa; p.sfb = (const uint8_t*)sfb; p.sf_ld = sf_ld;
+  p.sfa = (const uint8_t*)sfa; p.sfb = (const uint8_t*)sfb; p.sfa_ld = sfa_ld; p.sfb_ld = sfb_ld;
   p.C = (__nv_bfloat16*)C; p.ldc = ldc;
   p.num_m_blocks = (int)(R / BM); p.num_n_blocks = (N + BN - 1) / BN;
   p.status = xb_status_ptr();

@@ -22,6 +22,32 @@ from .context import StepContext
 from .layers import MLP, Linear
 
 
+class _RouterLogits(torch.autograd.Function):
+    """fp32 logits = x @ W^T from bf16 operands (one GEMM launch); the backward GEMMs take the
+    logit gradient rounded to bf16."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from ..ops.gemm import gemm
+        ctx.save_for_backward(x)
+        ctx.w = w
+        return gemm(x, w, out_dtype=torch.float32)
+
+    @staticmethod
+    def backward(ctx, dl):
+        from ..ops.gemm import gemm, weight_grad
+        (x,) = ctx.saved_tensors
+        w = ctx.w
+        d = dl.to(torch.bfloat16)
+        dx = gemm(d, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = weight_grad(d, x, w) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    return _RouterLogits.apply(x, w)
+
+
 class TopKRouter(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype=None, device=None):
         super().__init__()
@@ -41,8 +67,15 @@ class TopKRouter(nn.Module):
 
     def forward(self, x: torch.Tensor):
         """x [T, H] -> (weights fp32 [T, k], indices int64 [T, k], probs fp32 [T, E])."""
-        logits = torch.nn.functional.linear(x.float(), self.weight.float(),
-                                            None if self.bias is None else self.bias.float())
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+            # bf16 operands, fp32 accumulation and fp32 logits out of the tcgen05 GEMM: the same products
+            # as an fp32 matmul of the bf16 values, without materialising fp32 copies of x and W
+            logits = router_logits(x, self.weight)
+            if self.bias is not None:
+                logits = logits + self.bias.float()
+        else:
+            logits = torch.nn.functional.linear(x.float(), self.weight.float(),
+                                                None if self.bias is None else self.bias.float())
         return moe_ops.topk_route(logits, self.top_k, self.norm_topk_prob, self.scoring, self.scale,
                                   self.n_group, self.topk_group, self.e_score_correction_bias)
 
@@ -148,13 +181,16 @@ class MoEBlock(nn.Module):
                 weights = weights * self.gate.scale
         elif ctx.aux.get("record_routing", False):
             ctx.aux[("routing_record", self.layer_idx)] = indices.detach()
+        counts = None
         if ctx.training and self.aux_coef > 0 and ctx.aux.get("aux_loss_scale") is not None:
+            counts = moe_ops.expert_histogram(indices, self.cfg.num_experts)
             aux = moe_ops.load_balancing_loss(probs, indices, self.cfg.num_experts,
-                                              ctx.aux.get("aux_global_group"))
+                                              ctx.aux.get("aux_global_group"), counts=counts)
             ctx.aux[("aux_loss", self.layer_idx)] = aux * (self.aux_coef * ctx.aux["aux_loss_scale"])
         if ctx.aux.get("collect_expert_load", False):
-            ctx.aux[("expert_load", self.layer_idx)] = torch.bincount(
-                indices.reshape(-1), minlength=self.cfg.num_experts)
+            if counts is None:
+                counts = moe_ops.expert_histogram(indices, self.cfg.num_experts)
+            ctx.aux[("expert_load", self.layer_idx)] = counts.long()
         xe = self.pre_experts(x)
         if self.ep_size > 1:
             from ..parallel import ep as ep_ops

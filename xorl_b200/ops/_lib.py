@@ -64,6 +64,8 @@ _SIGNATURES = {
     "xb_gemm_fused": [P, P],
     "xb_rs_reduce": [P, I, I, I, P, L, P, P],
     "xb_moe_route": [P, L, P, P, P, P, P, I, I, I, I, I, F, P],
+    "xb_moe_histogram": [P, I, P, I, P],
+    "xb_ep_meta_targets": [P, I, P, P, P],
     "xb_ep_plan": [P, I, P, I, I, I, I, I, P, P, P, P, P, P],
     "xb_moe_gather_rows": [P, L, P, L, P, P, I, I, P],
     "xb_moe_gather_sum": [P, L, P, L, P, P, I, I, I, P],
@@ -76,7 +78,7 @@ _SIGNATURES = {
     "xb_dequant_fp8_blocks": [P, L, P, L, P, L, I, I, P],
     "xb_grouped_gemm_rows": [P, P, P, P, I, L, I, I, L, L, I, P],
     "xb_grouped_gemm_wgrad": [P, P, P, P, I, L, I, I, L, L, I, I, P],
-    "xb_grouped_gemm_mx_rows": [P, P, P, P, P, P, I, L, I, I, L, L, I, P],
+    "xb_grouped_gemm_mx_rows": [P, P, P, P, P, P, I, L, I, I, L, L, I, I, P],
     "xb_quant_mx_rows": [P, L, P, L, P, I, L, I, P],
     "xb_quant_mx_weight": [P, P, P, I, P, P, I, I, I, I, P],
     "xb_attn_fwd_ex": [P, P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, I, F, I, P],

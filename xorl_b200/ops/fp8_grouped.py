@@ -171,12 +171,12 @@ def grouped_rows_mx(xq: torch.Tensor, sfx: torch.Tensor, wq: torch.Tensor, sfw: 
     global _launches
     R, K = xq.shape
     E, N, K2 = wq.shape
-    assert K == K2 and sfx.stride(0) == sfw.stride(1) == sf_stride(K)
+    assert K == K2
     if out is None:
         out = torch.zeros((R, N), device=xq.device, dtype=torch.bfloat16)
     _lib.check(_lib.cuda_lib().xb_grouped_gemm_mx_rows(
         xq.data_ptr(), sfx.data_ptr(), wq.data_ptr(), sfw.data_ptr(), out.data_ptr(), seg.data_ptr(), E, R, N, K,
-        xq.stride(0), out.stride(0), sfx.stride(0), _lib.stream_ptr()), "xb_grouped_gemm_mx_rows")
+        xq.stride(0), out.stride(0), sfx.stride(0), sfw.stride(1), _lib.stream_ptr()), "xb_grouped_gemm_mx_rows")
     _launches += 1
     return out
 

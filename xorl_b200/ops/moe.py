@@ -122,20 +122,37 @@ def topk_route(logits: torch.Tensor, k: int, renorm: bool = True, scoring: str =
     return weights, indices, probs
 
 
+def expert_histogram(indices: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """int32 [E]: number of (token, slot) pairs routed to every expert (one kernel on CUDA)."""
+    global _launches
+    flat = indices.reshape(-1)
+    if flat.is_cuda and flat.dtype == torch.int64 and _lib.have_cuda_lib():
+        flat = flat.contiguous()
+        counts = torch.empty(num_experts, device=flat.device, dtype=torch.int32)
+        _lib.check(_lib.cuda_lib().xb_moe_histogram(flat.data_ptr(), flat.numel(), counts.data_ptr(), num_experts,
+                                                    _lib.stream_ptr()), "xb_moe_histogram")
+        _launches += 1
+        return counts
+    return torch.bincount(flat, minlength=num_experts).to(torch.int32)
+
+
 def load_balancing_loss(probs: torch.Tensor, indices: torch.Tensor, num_experts: int,
-                        global_group=None) -> torch.Tensor:
+                        global_group=None, counts: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``E * sum_e f_e * P_e`` with f_e the fraction of routed slots sent to expert e and P_e the
-    mean router probability.  With ``global_group`` the counts are summed over that group."""
+    mean router probability.  With ``global_group`` the counts are summed over that group.
+    ``counts``: the per-expert histogram of ``indices`` when the caller already has it."""
     T, k = indices.shape
-    counts = torch.zeros(num_experts, device=probs.device, dtype=torch.float32)
-    counts.scatter_add_(0, indices.reshape(-1), torch.ones(T * k, device=probs.device))
-    total = torch.tensor(float(T), device=probs.device)
+    if counts is None:
+        counts = expert_histogram(indices, num_experts)
+    counts = counts.float()
     if global_group is not None:
+        total = torch.tensor(float(T), device=probs.device)
         dist.all_reduce(counts, group=global_group)
         dist.all_reduce(total, group=global_group)
-    f = counts / (total * k)
-    P = probs.mean(0)
-    return num_experts * torch.sum(f.detach() * P)
+        f = counts / (total * k)
+    else:
+        f = counts * (1.0 / (T * k))
+    return num_experts * torch.dot(f, probs.mean(0))
 
 
 # --------------------------------------------------------------------------------------------

@@ -64,11 +64,15 @@ class _Workspace:
         self.base = [int(p) for p in self.hdl.buffer_ptrs]
         self.epoch = {k: 0 for k in ("counts", "disp", "ret", "bdisp", "bret")}
         self.lib = _lib.cuda_lib()
+        self._ptr_cache: Dict[int, object] = {}
         torch.cuda.synchronize()
         dist.barrier(group=ps.group("ep"))
 
     def ptrs(self, off: int):
-        return (ctypes.c_ulonglong * self.N)(*[b + off for b in self.base])
+        arr = self._ptr_cache.get(off)
+        if arr is None:
+            arr = self._ptr_cache[off] = (ctypes.c_ulonglong * self.N)(*[b + off for b in self.base])
+        return arr
 
     def view(self, name: str, rows: int, dtype, width_elems: int):
         es = torch.empty(0, dtype=dtype).element_size()
@@ -223,6 +227,200 @@ class _Return(torch.autograd.Function):
         return ws.view("recv_b", ws.cap, torch.bfloat16, ws.H), None, None
 
 
+class _Scratch:
+    """Per-workspace local buffers of the single-function path: plan arrays, expert activations,
+    return targets and (in fp8 mode) quantised operands.  Allocated once; every layer reuses them,
+    which is safe because a layer's backward directly follows its (re)computed forward."""
+
+    def __init__(self, ws: _Workspace, I2: int, act_I: int, fp8: bool):
+        dev = ws.heap.device
+        S, cap, H, El, E = ws.slots, ws.cap, ws.H, ws.El, ws.E
+        i32 = dict(device=dev, dtype=torch.int32)
+        bf = dict(device=dev, dtype=torch.bfloat16)
+        self.I2, self.I = I2, act_I
+        self.counts = torch.zeros(E, **i32)
+        self.dest_rank = torch.empty(S, **i32)
+        self.dest_row = torch.empty(S, **i32)
+        self.seg = torch.zeros(El + 1, **i32)
+        self.tot = torch.zeros(El, **i32)
+        self.overflow = torch.zeros(1, **i32)
+        self.ret_rank = torch.empty(cap, **i32)
+        self.ret_slot = torch.empty(cap, **i32)
+        self.h = torch.empty((cap, I2), **bf)
+        self.a = torch.empty((cap, act_I), **bf)
+        self.y = torch.empty((cap, H), **bf)          # forward: expert outputs; backward: dx rows
+        self.da = torch.empty((cap, act_I), **bf)
+        self.dys = torch.empty((S, H), **bf)
+        self.slot_idx: Dict[int, torch.Tensor] = {}
+        self.tok_of_slot: Dict[int, torch.Tensor] = {}
+        self.q = None
+        if fp8:
+            from ..ops.fp8_grouped import sf_stride
+            u8 = dict(device=dev, dtype=torch.uint8)
+            kmax = max(H, act_I, I2)
+            self.q = torch.empty((cap, kmax), **u8)
+            self.sf = torch.full((cap, sf_stride(kmax)), 127, **u8)
+
+    def slot_tables(self, k: int, dev):
+        if k not in self.slot_idx:
+            S = self.dest_rank.numel()
+            self.slot_idx[k] = torch.arange(S, device=dev, dtype=torch.int64)
+            self.tok_of_slot[k] = (torch.arange(S, device=dev) // k).to(torch.int32)
+        return self.slot_idx[k], self.tok_of_slot[k]
+
+
+def _scratch(ws: _Workspace, I2: int, act_I: int, fp8: bool) -> _Scratch:
+    sc = getattr(ws, "_scratch", None)
+    if sc is None or sc.I2 != I2 or sc.I != act_I or (fp8 and sc.q is None):
+        sc = _Scratch(ws, I2, act_I, fp8)
+        ws._scratch = sc
+    return sc
+
+
+def _rows_gemm(ws, sc, a, a_cols, w, out, n_out, b_mn: int, fp8, qe_w, qe_sf, st):
+    """out[rows of e, :n_out] = a[rows of e, :a_cols] @ op(w[e]) over the local expert segments."""
+    lib = ws.lib
+    if fp8:
+        _lib.check(lib.xb_quant_mx_rows(a.data_ptr(), a.stride(0), sc.q.data_ptr(), sc.q.stride(0), sc.sf.data_ptr(),
+                                        sc.sf.stride(0), ws.cap, a_cols, st), "xb_quant_mx_rows")
+        _lib.check(lib.xb_grouped_gemm_mx_rows(sc.q.data_ptr(), sc.sf.data_ptr(), qe_w.data_ptr(), qe_sf.data_ptr(),
+                                               out.data_ptr(), sc.seg.data_ptr(), ws.El, ws.cap, n_out, a_cols,
+                                               sc.q.stride(0), out.stride(0), sc.sf.stride(0), qe_sf.stride(1), st),
+                   "xb_grouped_gemm_mx_rows")
+    else:
+        _lib.check(lib.xb_grouped_gemm_rows(a.data_ptr(), w.data_ptr(), out.data_ptr(), sc.seg.data_ptr(), ws.El,
+                                            ws.cap, n_out, a_cols, a.stride(0), out.stride(0), b_mn, st),
+                   "xb_grouped_gemm_rows")
+
+
+class _FusedEPMoE(torch.autograd.Function):
+    """The whole expert-parallel MoE of one layer as ONE autograd node with a hand-written backward:
+    histogram -> count exchange -> plan -> dispatch push -> grouped gate_up GEMM -> SwiGLU -> grouped
+    down GEMM -> return push -> weighted sum over the k slots; backward runs the same pushes in the
+    opposite roles.  Around twenty kernel launches each way, no PyTorch operator, no allocation
+    besides the outputs, no host synchronisation.  (The composite path above builds the same
+    computation from several autograd functions and is kept for experts with biases or clamped /
+    non-gated activations.)"""
+
+    @staticmethod
+    def forward(ctx, x, weights, indices, gate_up, down, ws: _Workspace, fp8_mode):
+        lib, st = ws.lib, _lib.stream_ptr()
+        T, H = x.shape
+        k = indices.shape[1]
+        S = T * k
+        El, I2 = gate_up.shape[0], gate_up.shape[2]
+        I = down.shape[1]
+        fp8 = fp8_mode is not None
+        sc = _scratch(ws, I2, I, fp8)
+        slot_idx, tok_of_slot = sc.slot_tables(k, x.device)
+        x = x.contiguous()
+        idx = indices.contiguous()
+        w32 = weights.detach().float().contiguous()
+        qg = qd = None
+        if fp8:
+            from ..ops.fp8_grouped import cached_quantized_experts
+            qg, qd = cached_quantized_experts(gate_up), cached_quantized_experts(down)
+        # ---- plan -------------------------------------------------------------------------------
+        _lib.check(lib.xb_moe_histogram(idx.data_ptr(), S, sc.counts.data_ptr(), ws.E, st), "xb_moe_histogram")
+        ws.epoch["counts"] += 1
+        _lib.check(lib.xb_ep_exchange_counts(sc.counts.data_ptr(), ws.ptrs(ws.o_table), ws.ptrs(0), S_COUNTS, ws.rank,
+                                             ws.N, ws.E, ws.epoch["counts"], WAIT_MS, st), "xb_ep_exchange_counts")
+        _lib.check(lib.xb_ep_plan(idx.data_ptr(), S, ctypes.c_void_p(ws.heap.data_ptr() + ws.o_table), ws.rank, ws.N,
+                                  ws.E, ws.El, ws.cap, sc.dest_rank.data_ptr(), sc.dest_row.data_ptr(),
+                                  sc.seg.data_ptr(), sc.tot.data_ptr(), sc.overflow.data_ptr(), st), "xb_ep_plan")
+        # ---- dispatch ---------------------------------------------------------------------------
+        recv = ws.view("recv_f", ws.cap, torch.bfloat16, H)
+        meta = ws.view("meta_f", ws.cap, torch.int32, 1)
+        _lib.check(lib.xb_ep_prepare_recv(recv.data_ptr(), meta.data_ptr(), sc.seg.data_ptr(), sc.tot.data_ptr(), El,
+                                          ws.cap, H * 2, st), "xb_ep_prepare_recv")
+        ws.push(x, tok_of_slot[:S], sc.dest_rank[:S], sc.dest_row[:S], None, "recv_f", "meta_f", S_DISP, C_DISP, "disp")
+        # ---- experts ----------------------------------------------------------------------------
+        _rows_gemm(ws, sc, recv, H, gate_up, sc.h, I2, 1, fp8, None if qg is None else qg.q_nk,
+                   None if qg is None else qg.sf_nk, st)
+        _lib.check(lib.xb_swiglu_fwd(sc.h.data_ptr(), sc.a.data_ptr(), ws.cap, I, 1, st), "xb_swiglu_fwd")
+        _rows_gemm(ws, sc, sc.a, I, down, sc.y, H, 1, fp8, None if qd is None else qd.q_nk,
+                   None if qd is None else qd.sf_nk, st)
+        # ---- return -----------------------------------------------------------------------------
+        _lib.check(lib.xb_ep_meta_targets(meta.data_ptr(), ws.cap, sc.ret_rank.data_ptr(), sc.ret_slot.data_ptr(), st),
+                   "xb_ep_meta_targets")
+        ws.push(sc.y, None, sc.ret_rank, sc.ret_slot, None, "ret_f", None, S_RET, C_RET, "ret")
+        y_slots = ws.view("ret_f", S, torch.bfloat16, H)
+        out = torch.empty((T, H), device=x.device, dtype=torch.bfloat16)
+        _lib.check(lib.xb_moe_gather_sum(out.data_ptr(), out.stride(0), y_slots.data_ptr(), H, slot_idx.data_ptr(),
+                                         w32.data_ptr(), T, k, H, st), "xb_moe_gather_sum")
+        ctx.ws, ctx.sc, ctx.dims, ctx.fp8_mode = ws, sc, (T, H, k, S, El, I2, I), fp8_mode
+        ctx.gate_up, ctx.down = gate_up, down
+        ctx.save_for_backward(w32)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops.grad_sink import grad_target, mark_written
+        ws, sc = ctx.ws, ctx.sc
+        T, H, k, S, El, I2, I = ctx.dims
+        (w32,) = ctx.saved_tensors
+        gate_up, down = ctx.gate_up, ctx.down
+        lib, st = ws.lib, _lib.stream_ptr()
+        fp8 = ctx.fp8_mode == "fp8"
+        slot_idx, tok_of_slot = sc.slot_tables(k, dout.device)
+        dout = dout.contiguous()
+        y_slots = ws.view("ret_f", S, torch.bfloat16, H)
+        qg = qd = None
+        if fp8:
+            from ..ops.fp8_grouped import cached_quantized_experts
+            qg, qd = cached_quantized_experts(gate_up), cached_quantized_experts(down)
+        # slot gradients and routing-weight gradients
+        dys = sc.dys[:S]
+        _lib.check(lib.xb_moe_gather_rows(dys.data_ptr(), H, dout.data_ptr(), dout.stride(0), tok_of_slot.data_ptr(),
+                                          w32.data_ptr(), S, H, st), "xb_moe_gather_rows")
+        dw = torch.empty((T, k), device=dout.device, dtype=torch.float32)
+        _lib.check(lib.xb_moe_slot_dots(dw.data_ptr(), dout.data_ptr(), dout.stride(0), y_slots.data_ptr(), H,
+                                        slot_idx.data_ptr(), T, k, H, st), "xb_moe_slot_dots")
+        # slot gradients -> owners' rows (same plan as the dispatch)
+        recv_b = ws.view("recv_b", ws.cap, torch.bfloat16, H)
+        meta_b = ws.view("meta_b", ws.cap, torch.int32, 1)
+        _lib.check(lib.xb_ep_prepare_recv(recv_b.data_ptr(), meta_b.data_ptr(), sc.seg.data_ptr(), sc.tot.data_ptr(), El,
+                                          ws.cap, H * 2, st), "xb_ep_prepare_recv")
+        ws.push(dys, None, sc.dest_rank[:S], sc.dest_row[:S], None, "recv_b", "meta_b", S_BDISP, C_BDISP, "bdisp")
+        recv_f = ws.view("recv_f", ws.cap, torch.bfloat16, H)
+        # down projection: input gradient, then weight gradient (bf16 operands)
+        _rows_gemm(ws, sc, recv_b, H, down, sc.da, I, 0, fp8, None if qd is None else qd.q_kn,
+                   None if qd is None else qd.sf_kn, st)
+        for w, a_rows, b_rows, M_, N_ in ((down, sc.a, recv_b, I, H),):
+            tgt, fresh = grad_target(w)
+            dwt = tgt if tgt is not None else torch.empty_like(w)
+            _lib.check(lib.xb_grouped_gemm_wgrad(a_rows.data_ptr(), b_rows.data_ptr(), dwt.data_ptr(), sc.seg.data_ptr(),
+                                                 El, ws.cap, M_, N_, a_rows.stride(0), b_rows.stride(0),
+                                                 int(dwt.dtype == torch.float32), int(tgt is not None and not fresh), st),
+                       "xb_grouped_gemm_wgrad")
+            if tgt is not None:
+                mark_written(w)
+            d_down = None if tgt is not None else dwt
+        # SwiGLU backward in place: h becomes dh
+        _lib.check(lib.xb_swiglu_bwd(sc.da.data_ptr(), sc.h.data_ptr(), sc.h.data_ptr(), ws.cap, I, st), "xb_swiglu_bwd")
+        tgt, fresh = grad_target(gate_up)
+        dwt = tgt if tgt is not None else torch.empty_like(gate_up)
+        _lib.check(lib.xb_grouped_gemm_wgrad(recv_f.data_ptr(), sc.h.data_ptr(), dwt.data_ptr(), sc.seg.data_ptr(), El,
+                                             ws.cap, H, I2, recv_f.stride(0), sc.h.stride(0),
+                                             int(dwt.dtype == torch.float32), int(tgt is not None and not fresh), st),
+                   "xb_grouped_gemm_wgrad")
+        if tgt is not None:
+            mark_written(gate_up)
+        d_gate_up = None if tgt is not None else dwt
+        _rows_gemm(ws, sc, sc.h, I2, gate_up, sc.y, H, 0, fp8, None if qg is None else qg.q_kn,
+                   None if qg is None else qg.sf_kn, st)
+        # row gradients -> source slots, summed over the k slots of a token
+        meta_f = ws.view("meta_f", ws.cap, torch.int32, 1)
+        _lib.check(lib.xb_ep_meta_targets(meta_f.data_ptr(), ws.cap, sc.ret_rank.data_ptr(), sc.ret_slot.data_ptr(), st),
+                   "xb_ep_meta_targets")
+        ws.push(sc.y, None, sc.ret_rank, sc.ret_slot, None, "ret_b", None, S_BRET, C_BRET, "bret")
+        dslots = ws.view("ret_b", S, torch.bfloat16, H)
+        dx = torch.empty((T, H), device=dout.device, dtype=torch.bfloat16)
+        _lib.check(lib.xb_moe_gather_sum(dx.data_ptr(), dx.stride(0), dslots.data_ptr(), H, slot_idx.data_ptr(), None,
+                                         T, k, H, st), "xb_moe_gather_sum")
+        return dx, dw, None, d_gate_up, d_down, None, None
+
+
 def fused_ep_forward(x, weights, indices, experts, num_experts, ctx):
     T, H = x.shape
     k = indices.shape[1]
@@ -230,10 +428,14 @@ def fused_ep_forward(x, weights, indices, experts, num_experts, ctx):
     ws = _workspace(H, max(slots, T * k), num_experts, x.device)
     if T * k > ws.slots:
         raise RuntimeError(f"{T * k} token slots exceed the EP workspace ({ws.slots})")
+    kw = moe_ops.experts_mlp_kwargs(experts)
+    fp8_mode = kw.pop("fp8", None)
+    if not kw and os.environ.get("XORL_B200_EP_SINGLE_NODE_FN", "1") == "1":
+        return _FusedEPMoE.apply(x, weights, indices, experts.gate_up_proj, experts.down_proj, ws, fp8_mode)
+    kw = moe_ops.experts_mlp_kwargs(experts)
     plan = _make_plan(ws, indices)
     buf = _Dispatch.apply(x, ws, plan)
-    y = moe_ops.expert_mlp_aligned(buf, plan.seg, experts.gate_up_proj, experts.down_proj,
-                                   **moe_ops.experts_mlp_kwargs(experts))
+    y = moe_ops.expert_mlp_aligned(buf, plan.seg, experts.gate_up_proj, experts.down_proj, **kw)
     y_slots = _Return.apply(y, ws, plan)
     if moe_ops._permute_kernels_ok(x):
         # weighted sum over the k slots of a token in one gather kernel (slot rows are contiguous)

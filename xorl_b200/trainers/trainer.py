@@ -276,6 +276,9 @@ class Trainer:
                 extra={"local_cu_seqlens": mb.get("local_cu_seqlens")})
             total = loss if total is None else total + loss
         self.engine.finish_grad_sync()
+        dump = os.environ.get("XORL_DEBUG_DUMP_GRADS")
+        if dump and self.global_step == 0:
+            self._dump_full_gradients(dump)
         if self.scan_nonfinite:
             from ..utils.diagnostics import nonfinite_gradient_report
             bad = nonfinite_gradient_report(self.engine)
@@ -332,6 +335,18 @@ class Trainer:
             for st in self.optimizer.state.values():
                 for v in st.values():
                     v.zero_()
+
+    def _dump_full_gradients(self, out_dir: str) -> None:
+        """Debug aid (``XORL_DEBUG_DUMP_GRADS=<dir>``): after the first step's backward, the fully
+        reduced fp32 gradient of every parameter, gathered to its unsharded shape, is written by the
+        first rank of every pipeline stage.  Runs under any parallel layout, so two layouts can be
+        compared parameter by parameter."""
+        grads = {n: t.detach().float().cpu().clone() for n, t in self.engine.iter_full_tensors("grad")}
+        ps = self.ps
+        first_of_stage = ps.rank == min(ps.group_ranks("stage")) if "stage" in ps.groups else ps.rank == 0
+        if first_of_stage or ps.world_size == 1:
+            os.makedirs(out_dir, exist_ok=True)
+            torch.save(grads, os.path.join(out_dir, f"grads_pp{ps.pp_rank if ps.pp_size > 1 else 0}.pt"))
 
     def _extra_loss_fn(self):
         return None
