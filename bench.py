@@ -41,6 +41,9 @@ def parse():
     ap.add_argument("--ep", type=int, default=0,
                     help="expert-parallel size for MoE models (0: all ranks for MoE, 1 for dense)")
     ap.add_argument("--ep-dispatch", default="fused", choices=["fused", "alltoall"])
+    ap.add_argument("--experts-dtype", default="fp8", choices=["fp8", "bf16"],
+                    help="MoE models: block-scaled fp8 expert GEMMs (1x128 activation / 128x128 weight scales), "
+                         "the precision the Qwen3-30B-A3B configuration names, or bf16")
     ap.add_argument("--recompute", default="auto", choices=["auto", "full", "none"],
                     help="activation recomputation; auto keeps activations when they fit (both arms "
                          "use their own gradient_checkpointing_method key)")
@@ -152,8 +155,8 @@ def resolve_recompute(a, cfg, world: int) -> str:
 
 
 def launch_total():
-    from xorl_b200.ops import activation, attention, embedding, gemm, loss, norm, optim
-    return sum(m.launch_count() for m in (activation, attention, embedding, gemm, loss, norm, optim))
+    from xorl_b200.ops import activation, attention, embedding, fp8_grouped, gemm, loss, moe, norm, optim
+    return sum(m.launch_count() for m in (activation, attention, embedding, fp8_grouped, gemm, loss, moe, norm, optim))
 
 
 # ------------------------------------------------------------------------------------------------
@@ -173,6 +176,9 @@ def run_ours(a):
     ep = (a.ep or (world if cfg.is_moe else 1)) if cfg.is_moe else 1
     # the load-balancing loss comes from the model config (router_aux_loss_coef = 1e-3)
     moe_train = dict(expert_parallel_size=ep) if cfg.is_moe else {}
+    if cfg.is_moe and a.experts_dtype == "fp8":
+        moe_train.update(enable_fp8_training=True, fp8_training_allow_blackwell=True,
+                         fp8_training_target_modules=["experts"])
     out_dir = os.path.join(scratch_dir(a), "bench_out")
     recompute = resolve_recompute(a, cfg, world)
     args = Arguments(
@@ -184,7 +190,8 @@ def run_ours(a):
                                 data_parallel_mode="fsdp2", enable_mixed_precision=True,
                                 enable_gradient_checkpointing=True,
                                 gradient_checkpointing_method=recompute, init_device="meta",
-                                load_weights_mode="skip", save_hf_weights=False, use_wandb=False,
+                                load_weights_mode="skip", save_hf_weights=False, use_wandb=False, save_steps=0,
+                                save_epochs=0,
                                 comm_backend=a.comm, max_steps=10 ** 9, ce_num_chunks=4, **moe_train))
     trainer = Trainer(args, model_config=cfg)
     dev = trainer.device
@@ -252,12 +259,18 @@ def run_ours(a):
                        "parallelism": f"fsdp{world}" + ("-fused" if fused else "-nccl" if world > 1 else "")
                        + (f"-ep{ep}-{a.ep_dispatch}" if ep > 1 else ""),
                        "optimizer": "adamw fp32 master+states", "recompute": recompute,
+                       **({"experts": "block_fp8 e4m3 (1x128 / 128x128 power-of-two scales), bf16 elsewhere"
+                           if a.experts_dtype == "fp8" else "bf16"} if cfg.is_moe else {}),
                        "l2": "per-step working set (16 GB of bf16 weights + activations) >> 126 MB L2",
                        "packed_docs": "lengths U[256,4096], tokens U[vocab]"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "loss": last_loss, "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
             "status_words": status[:4],
         }
+        if cfg.is_moe:
+            from xorl_b200.parallel.ep_fused import PhaseTimes
+            if PhaseTimes.enabled:
+                line["ep_phase_ms_total"] = PhaseTimes.report()
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

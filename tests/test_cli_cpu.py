@@ -90,3 +90,55 @@ def test_convert_hf_to_dcp_roundtrip(tmp_path):
     for a, b in zip(src.all_groups(), dst.all_groups()):
         assert torch.equal(a.master, b.master), a.name
     reset_parallel_state()
+
+
+def test_every_config_key_is_read_or_accounted_for():
+    """No key of the YAML schema is silently ignored: each one is read by some module, or listed as
+    satisfied by design (with the reason), or raises NotImplementedError naming the key when it is set
+    to a value that asks for something that is not built."""
+    import dataclasses
+    import re
+    import pytest
+    from xorl_b200 import arguments as A
+    from xorl_b200 import config_policy as P
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "xorl_b200")
+    src = ""
+    for d, _, files in os.walk(root):
+        for f in files:
+            if f.endswith(".py") and f not in ("arguments.py", "config_policy.py"):
+                src += open(os.path.join(d, f)).read() + "\n"
+    argsrc = open(os.path.join(root, "arguments.py")).read()
+    sections = {"model": A.ModelArguments, "data": A.DataArguments, "train": A.TrainingArguments,
+                "lora": A.LoRAArguments, "distill": A.DistillationArguments}
+    unaccounted = []
+    for sec, cls in sections.items():
+        for f in dataclasses.fields(cls):
+            if not f.init:
+                continue
+            pat = r"\b" + re.escape(f.name) + r"\b"
+            read = re.search(pat, src) is not None or len(re.findall(pat, argsrc)) > 1 \
+                or (f.name.startswith("muon_") and "startswith(\"muon_\")" in src)
+            if read or f.name in P.SATISFIED_BY_DESIGN.get(sec, {}) or f.name in P.UNSUPPORTED.get(sec, {}):
+                continue
+            unaccounted.append(f"{sec}.{f.name}")
+    assert not unaccounted, unaccounted
+    # every unsupported key raises for a value outside its accepted set, and names itself
+    candidates = (True, 7, 0.37, 2.0, 64, "something-else", "true", "tilelang", "flashmla", "full_matrix",
+                  "anyprecision_adamw", "residual", "deep_gemm", ["x"], {"a": 1})
+    for sec, table in P.UNSUPPORTED.items():
+        for key, (ok, why) in table.items():
+            raised = False
+            for bad in candidates:
+                if ok(bad):
+                    continue
+                try:
+                    A.build_args({sec: {key: bad}})
+                except NotImplementedError as e:
+                    assert key in str(e), (key, str(e))
+                    raised = True
+                    break
+                except (ValueError, TypeError):
+                    continue                     # not a value of the field's declared type: try the next
+            assert raised, f"{sec}.{key} never raised NotImplementedError"
+    # the defaults themselves are all accepted
+    A.build_args({})

@@ -64,3 +64,63 @@ def test_numerical_program():
     assert p.router_fp32 and p.reduce_dtype == "bf16" and p.batch_invariant
     rep = describe(p)
     assert "atomics" in rep["attention_backward"] and "note" in rep
+
+
+def test_trainer_distillation_adds_the_teacher_kl(tmp_path):
+    """``distill.enable_distillation``: the step loss is CE + weight * KL(teacher || student) over the
+    supervised tokens (weight 500 here: freshly initialised models are close to uniform, so the KL is small next to the CE), the teacher being a frozen second model; training lowers the KL."""
+    from xorl_b200.arguments import build_args
+    from xorl_b200.models.config import preset
+    from xorl_b200.parallel.state import reset_parallel_state
+    from xorl_b200.trainers.trainer import Trainer
+    reset_parallel_state()
+    args = build_args({"model": {"config_path": "tiny-qwen3"},
+                       "data": {"datasets": [{"path": "dummy", "type": "tokenized", "max_seq_len": 64,
+                                              "num_samples": 8}], "sample_packing_sequence_len": 128},
+                       "train": {"output_dir": str(tmp_path / "o"), "device": "cpu", "use_wandb": False, "lr": 2e-3,
+                                 "save_hf_weights": False, "save_epochs": 0, "max_steps": 1},
+                       "distill": {"enable_distillation": True, "teacher_model_path": "tiny-qwen3",
+                                   "distillation_loss_type": "forward_kl", "distillation_loss_weight": 500.0}})
+    tr = Trainer(args, model_config=preset("tiny-qwen3"))
+    assert tr.teacher_engine is not None
+    assert all(getattr(g, "frozen", False) for g in tr.teacher_engine.all_groups())
+    ids = torch.randint(0, 1024, (1, 65))
+    mb = {"input_ids": ids[:, :-1], "labels": ids[:, 1:]}
+    # manual value of the first step's loss
+    eng, te = tr.engine, tr.teacher_engine
+    hs = eng.forward_only(mb["input_ids"]).reshape(-1, 256).float()
+    ht = te.forward_only(mb["input_ids"]).reshape(-1, 256).float()
+    ws = dict(eng.iter_full_tensors("master"))
+    wt = dict(te.iter_full_tensors("master"))
+    head_s = ws.get("lm_head.weight", ws["embed_tokens.weight"]).float()
+    head_t = wt.get("lm_head.weight", wt["embed_tokens.weight"]).float()
+    lps, lpt = torch.log_softmax(hs @ head_s.t(), -1), torch.log_softmax(ht @ head_t.t(), -1)
+    ce = torch.nn.functional.nll_loss(lps, mb["labels"].reshape(-1), reduction="sum")
+    kl = (lpt.exp() * (lpt - lps)).sum()
+    want = float(ce + 500.0 * kl) / 64
+    first = float(tr.train_step([mb])["loss"])
+    assert abs(first - want) < 1e-3 * abs(want), (first, want)
+    assert float(kl) > 0.5                                            # different seeds: the models disagree
+    for _ in range(8):
+        last = float(tr.train_step([mb])["loss"])
+    assert last < first - 0.2, (first, last)
+    with torch.no_grad():
+        hs2 = eng.forward_only(mb["input_ids"]).reshape(-1, 256).float()
+        head_s2 = dict(eng.iter_full_tensors("master"))
+        head_s2 = head_s2.get("lm_head.weight", head_s2["embed_tokens.weight"]).float()
+        lps2 = torch.log_softmax(hs2 @ head_s2.t(), -1)
+    assert float((lpt.exp() * (lpt - lps2)).sum()) < float(kl)
+
+
+def test_distillation_needs_a_teacher():
+    import pytest
+    from xorl_b200.arguments import build_args
+    from xorl_b200.models.config import preset
+    from xorl_b200.parallel.state import reset_parallel_state
+    from xorl_b200.trainers.trainer import Trainer
+    reset_parallel_state()
+    args = build_args({"model": {"config_path": "tiny-qwen3"}, "train": {"device": "cpu", "use_wandb": False},
+                       "data": {"datasets": [{"path": "dummy", "type": "tokenized", "max_seq_len": 64, "num_samples": 8}]},
+                       "distill": {"enable_distillation": True}})
+    with pytest.raises(ValueError, match="teacher_model_path"):
+        Trainer(args, model_config=preset("tiny-qwen3"))

@@ -33,7 +33,7 @@ def _cfg(tmp, name, model="small-qwen3", dp=1, **train):
                  "sample_packing_sequence_len": 2048, "pad_to_multiple_of": 128,
                  "shuffle_merged_datasets": False},
         "train": {"output_dir": str(tmp / name), "lr": 1e-3, "max_steps": STEPS, "use_wandb": False,
-                  "save_hf_weights": False, "gradient_accumulation_steps": 4 // dp, "num_train_epochs": 1000,
+                  "save_hf_weights": False, "save_epochs": 0, "gradient_accumulation_steps": 4 // dp, "num_train_epochs": 1000,
                   "weight_decay": 0.0, **train},
     }
     p = tmp / f"{name}.yaml"

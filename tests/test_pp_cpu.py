@@ -19,7 +19,7 @@ def _cfg(tmp, name, **train):
                  "sample_packing_sequence_len": 256, "pad_to_multiple_of": 64,
                  "shuffle_merged_datasets": False},
         "train": {"output_dir": str(tmp / name), "lr": 1e-3, "max_steps": 3, "use_wandb": False,
-                  "device": "cpu", "save_hf_weights": False, "gradient_accumulation_steps": 4,
+                  "device": "cpu", "save_hf_weights": False, "save_epochs": 0, "gradient_accumulation_steps": 4,
                   "enable_mixed_precision": False, **train},
     }
     p = tmp / f"{name}.yaml"

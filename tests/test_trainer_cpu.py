@@ -18,7 +18,7 @@ def _cfg(tmp, model, **train):
         "data": {"datasets": [{"path": "dummy", "type": "tokenized", "max_seq_len": 200, "num_samples": 64}],
                  "sample_packing_sequence_len": 512, "pad_to_multiple_of": 64},
         "train": {"output_dir": str(tmp / "out"), "lr": 1e-3, "max_steps": 6, "use_wandb": False,
-                  "device": "cpu", "save_hf_weights": False, **train},
+                  "device": "cpu", "save_hf_weights": False, "save_epochs": 0, **train},
     }
     p = tmp / "cfg.yaml"
     p.write_text(yaml.safe_dump(cfg))
@@ -68,7 +68,7 @@ def test_softmax_auxiliary_loss_is_the_z_loss_on_the_logits(tmp_path):
                                               "num_samples": 8}], "sample_packing_sequence_len": 128},
                        "train": {"output_dir": str(tmp_path / "o"), "device": "cpu", "use_wandb": False,
                                  "softmax_auxiliary_loss": True, "auxiliary_loss_multiplier": 0.5,
-                                 "save_hf_weights": False, "max_steps": 1}})
+                                 "save_hf_weights": False, "save_epochs": 0, "max_steps": 1}})
     tr = Trainer(args, model_config=preset("tiny-qwen3"))
     assert tr.model.z_loss_coef == 0.5
     eng = tr.engine

@@ -390,6 +390,10 @@ class Arguments:
             raise ValueError("tensor parallelism cannot be combined with LoRA")
         if t.pipeline_parallel_size > 1 and self.data.sample_packing_sequence_len is None:
             raise ValueError("pipeline parallelism requires sample packing")
+        # keys whose value asks for something that is not built raise here instead of being ignored
+        from .config_policy import check_supported
+        for section in ("model", "data", "train", "lora", "distill"):
+            check_supported(section, getattr(self, section))
 
 
 # ------------------------------------------------------------------------------------------------

@@ -48,11 +48,14 @@ def _chunk_bounds(dim0: int, world: int, rank: int):
 
 class DistributedCheckpointer:
     def __init__(self, engine, optimizer=None, checkpoint_dir: str = "checkpoints",
-                 save_async: bool = False):
+                 save_async: bool = False, lora_only: bool = False):
         self.engine = engine
         self.optimizer = optimizer
         self.dir = checkpoint_dir
         self.save_async = save_async
+        # lora.save_lora_only: frozen base weights stay out of the checkpoint (adapters, their
+        # optimizer state and the trainer state only); loading such a checkpoint leaves the base alone
+        self.lora_only = lora_only
         self._pending = None
         self._meshes: Dict[int, Any] = {}
 
@@ -151,7 +154,7 @@ class DistributedCheckpointer:
         if self._pending is not None:
             self._pending.result()
             self._pending = None
-        sd = self.build_state_dict()
+        sd = self.build_state_dict(include_frozen=not self.lora_only)
         extra = dict(extra_state or {})
         if self.optimizer is not None:
             extra["optimizer_meta"] = self.optimizer.state_dict()
@@ -176,6 +179,7 @@ class DistributedCheckpointer:
     def load(self, path: str, load_optimizer: bool = True, allow_partial_load: bool = False) -> Dict[str, Any]:
         eng = self.engine
         sd = self.build_state_dict()
+        allow_partial_load = allow_partial_load or self.lora_only
         if not load_optimizer:
             sd = {k: v for k, v in sd.items() if k.startswith("model.")}
         reader = dcp.FileSystemReader(path)
@@ -224,4 +228,5 @@ class DistributedCheckpointer:
 
 def build_checkpointer(trainer) -> DistributedCheckpointer:
     t = trainer.args.train
-    return DistributedCheckpointer(trainer.engine, trainer.optimizer, t.checkpoint_dir, t.save_async)
+    return DistributedCheckpointer(trainer.engine, trainer.optimizer, t.checkpoint_dir, t.save_async,
+                                   lora_only=bool(trainer.args.lora.enable_lora and trainer.args.lora.save_lora_only))

@@ -16,6 +16,12 @@
 //                              it to the fp32 accumulator, emit sum-of-squares partials, tell the
 //                              peers the buffer may be reused  (ZeRO gradient reduce-scatter +
 //                              cast/scale + accumulate in one pass, with bf16 on the wire)
+//   xb_symm_allgather_dma      the same gather as one cudaMemcpyAsync per peer shard: the copy engines
+//                              move the bytes over NVLink and no SM is taken from the GEMMs that run
+//                              beside the prefetch
+//   xb_symm_gather_slices_dma  copy engines bring this rank's slice of every peer's gradient buffer
+//                              into local staging; xb_symm_reduce_scatter then runs on local pointers
+//                              (fp32 sum in rank order + accumulate + norm partials at HBM speed)
 //   xb_symm_wait               block a stream until peers have released a buffer
 //   xb_peer_copy               bulk copy between two mapped buffers (weight sync)
 // These replace the NCCL all-gather / reduce-scatter issued by FSDP2 in the reference
@@ -253,6 +259,35 @@ XB_API int xb_symm_allgather(void* dst, const unsigned long long* src_ptrs, long
     symm_allgather_kernel<4><<<num_ctas, 512, 0, (cudaStream_t)stream>>>(
         (uint4*)dst, make_ptrs(src_ptrs, n), shard_bytes / 16, rank, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// One asynchronous device-to-device copy per rank, starting with the local shard and then walking
+// the peers in ring order (rank + 1, rank + 2, ...), so that at any time every source serves one reader.
+XB_API int xb_symm_allgather_dma(void* dst, const unsigned long long* src_ptrs, long long shard_bytes, int rank,
+                                 int n, void* stream) {
+  if (n > MAX_RANKS || shard_bytes <= 0) return -1;
+  for (int k = 0; k < n; ++k) {
+    const int r = (rank + k) % n;
+    if (cudaMemcpyAsync(static_cast<char*>(dst) + (long long)r * shard_bytes, reinterpret_cast<const void*>(src_ptrs[r]),
+                        (size_t)shard_bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream) != cudaSuccess)
+      return -12;
+  }
+  return 0;
+}
+
+// staging: [n][slice_bytes] local; slot r receives bytes [slice_off_bytes, + slice_bytes) of rank r's
+// buffer (the local rank's slot is skipped: its slice is read in place).
+XB_API int xb_symm_gather_slices_dma(void* staging, const unsigned long long* buf_ptrs, long long slice_off_bytes,
+                                     long long slice_bytes, int rank, int n, void* stream) {
+  if (n > MAX_RANKS || slice_bytes <= 0) return -1;
+  for (int k = 1; k < n; ++k) {
+    const int r = (rank + k) % n;
+    if (cudaMemcpyAsync(static_cast<char*>(staging) + (long long)r * slice_bytes,
+                        reinterpret_cast<const char*>(buf_ptrs[r]) + slice_off_bytes, (size_t)slice_bytes,
+                        cudaMemcpyDeviceToDevice, (cudaStream_t)stream) != cudaSuccess)
+      return -12;
+  }
+  return 0;
 }
 
 // See symm_reduce_scatter_kernel.  mc_base = 0 selects peer loads, otherwise the multicast

@@ -212,6 +212,21 @@ class DecoderLM(nn.Module):
                   return_token_losses: bool = False):
         """grad_scale * sum of token cross-entropies (labels == -100 ignored)."""
         hidden = self.forward_head(h, residual, ctx)
+        distill = ctx.aux.get("distill")
+        if distill is not None:
+            # teacher-student KL on the same hidden states, added to the cross-entropy with the same
+            # token normalisation (``distill.distillation_loss_weight``)
+            t_hidden, t_weight, kind, weight = distill
+            if getattr(self, "vocab_parallel", False):
+                raise NotImplementedError("distillation is not supported with a vocabulary-parallel lm-head")
+            kl = loss_ops.distillation_kl(hidden, self.lm_head.weight, t_hidden, t_weight, labels, kind,
+                                          self.loss_chunk_tokens)
+            ce = loss_ops.fused_linear_cross_entropy(hidden, self.lm_head.weight, labels.reshape(-1), grad_scale,
+                                                     self.loss_chunk_tokens,
+                                                     z_loss=float(getattr(self, "z_loss_coef", 0.0)))
+            ctx.aux["distill_kl"] = kl.detach() * grad_scale
+            total = ce + kl * (weight * grad_scale)
+            return (total, None) if return_token_losses else total
         if getattr(self, "vocab_parallel", False):
             if getattr(self, "z_loss_coef", 0.0):
                 raise NotImplementedError("softmax_auxiliary_loss (z-loss) is not supported with a "

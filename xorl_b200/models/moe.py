@@ -149,6 +149,9 @@ class MoEBlock(nn.Module):
         self.shared_expert_gate = Linear(cfg.hidden_size, 1, dtype=dtype, device=device) \
             if (self.shared_expert is not None and cfg.extra.get("shared_expert_gate")) else None
         self.aux_coef = cfg.router_aux_loss_coef
+        # gradient of the expert outputs with respect to the routing weights reaches the router only
+        # when this is set (``model.train_router``; src/xorl/arguments.py:491-497)
+        self.train_router = True
         self.moe_ordinal = sum(cfg.layer_is_moe(i) for i in range(layer_idx))
 
     def build_experts(self, cfg: ModelConfig, dtype, device) -> "Experts":
@@ -191,6 +194,8 @@ class MoEBlock(nn.Module):
             if counts is None:
                 counts = moe_ops.expert_histogram(indices, self.cfg.num_experts)
             ctx.aux[("expert_load", self.layer_idx)] = counts.long()
+        if not self.train_router:
+            weights = weights.detach()
         xe = self.pre_experts(x)
         if self.ep_size > 1:
             from ..parallel import ep as ep_ops

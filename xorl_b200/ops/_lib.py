@@ -56,6 +56,8 @@ _SIGNATURES = {
     "xb_symm_barrier": [P, I, I, I, I, I, P],
     "xb_symm_wait": [P, I, I, I, I, P],
     "xb_symm_allgather": [P, P, L, I, I, I, P],
+    "xb_symm_allgather_dma": [P, P, L, I, I, P],
+    "xb_symm_gather_slices_dma": [P, P, L, L, I, I, P],
     "xb_symm_reduce_scatter": [P, P, ctypes.c_ulonglong, L, L, I, F, P, P, I, I, I, I, I, I, I, I, P],
     "xb_ep_exchange_counts": [P, P, P, I, I, I, I, I, I, P],
     "xb_ep_prepare_recv": [P, P, P, P, I, I, I, P],

@@ -331,3 +331,35 @@ def vocab_parallel_linear_cross_entropy(hidden, weight_shard, labels, group, voc
     return _VocabParallelLinearCE.apply(hidden.reshape(-1, hidden.shape[-1]), weight_shard, labels.reshape(-1),
                                         group, int(vocab_start), float(grad_scale), int(chunk_tokens),
                                         int(ignore_index))
+
+
+def distillation_kl(hidden_s: torch.Tensor, w_s: torch.Tensor, hidden_t: torch.Tensor, w_t: torch.Tensor,
+                    labels: torch.Tensor, kind: str = "forward_kl", chunk_tokens: int = 1024,
+                    ignore_index: int = IGNORE_INDEX) -> torch.Tensor:
+    """Sum over supervised tokens of the KL divergence between the teacher's and the student's
+    next-token distributions: ``forward_kl`` = KL(teacher || student), ``reverse_kl`` =
+    KL(student || teacher).  Logits are formed chunk by chunk from the final hidden states and the two
+    lm-head weights (the student's through the differentiable linear, so its gradients reach the
+    hidden states and the lm-head like any other loss term); the teacher's side carries no gradient.
+    Keys: ``distill.distillation_loss_type`` (src/xorl/arguments.py:1846-1849)."""
+    from .gemm import linear
+    if kind not in ("forward_kl", "reverse_kl"):
+        raise ValueError(f"distillation_loss_type must be forward_kl or reverse_kl, got {kind!r}")
+    hs = hidden_s.reshape(-1, hidden_s.shape[-1])
+    ht = hidden_t.reshape(-1, hidden_t.shape[-1])
+    lab = labels.reshape(-1)
+    if w_s.shape[0] != w_t.shape[0]:
+        raise ValueError(f"teacher and student vocabularies differ: {w_t.shape[0]} vs {w_s.shape[0]}")
+    total = hs.new_zeros((), dtype=torch.float32)
+    for s in range(0, hs.shape[0], chunk_tokens):
+        e = min(hs.shape[0], s + chunk_tokens)
+        mask = (lab[s:e] != ignore_index).float()
+        logp_s = torch.log_softmax(linear(hs[s:e], w_s).float(), dim=-1)
+        with torch.no_grad():
+            logp_t = torch.log_softmax(linear(ht[s:e], w_t).float(), dim=-1)
+        if kind == "forward_kl":
+            kl = (logp_t.exp() * (logp_t - logp_s)).sum(-1)
+        else:
+            kl = (logp_s.exp() * (logp_s - logp_t)).sum(-1)
+        total = total + (kl * mask).sum()
+    return total

@@ -227,6 +227,40 @@ class _Return(torch.autograd.Function):
         return ws.view("recv_b", ws.cap, torch.bfloat16, ws.H), None, None
 
 
+class PhaseTimes:
+    """Device time per phase of the fused MoE (``XORL_B200_EP_PHASE_TIMING=1``): CUDA events around the
+    plan, the two pushes, the expert GEMMs and the combine, summed over calls; ``report()``
+    synchronises and returns milliseconds per phase and call counts."""
+    enabled = os.environ.get("XORL_B200_EP_PHASE_TIMING", "0") == "1"
+    pending: list = []
+    totals: Dict[str, float] = {}
+    counts: Dict[str, int] = {}
+
+    @classmethod
+    def mark(cls):
+        if not cls.enabled:
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    @classmethod
+    def add(cls, name: str, start, end=None):
+        if cls.enabled and start is not None:
+            cls.pending.append((name, start, end if end is not None else cls.mark()))
+
+    @classmethod
+    def report(cls) -> Dict[str, float]:
+        if not cls.enabled:
+            return {}
+        torch.cuda.synchronize()
+        for name, a, b in cls.pending:
+            cls.totals[name] = cls.totals.get(name, 0.0) + a.elapsed_time(b)
+            cls.counts[name] = cls.counts.get(name, 0) + 1
+        cls.pending = []
+        return {k: round(v, 3) for k, v in cls.totals.items()} | {f"n_{k}": c for k, c in cls.counts.items()}
+
+
 class _Scratch:
     """Per-workspace local buffers of the single-function path: plan arrays, expert activations,
     return targets and (in fp8 mode) quantised operands.  Allocated once; every layer reuses them,
@@ -321,6 +355,7 @@ class _FusedEPMoE(torch.autograd.Function):
             from ..ops.fp8_grouped import cached_quantized_experts
             qg, qd = cached_quantized_experts(gate_up), cached_quantized_experts(down)
         # ---- plan -------------------------------------------------------------------------------
+        t0 = PhaseTimes.mark()
         _lib.check(lib.xb_moe_histogram(idx.data_ptr(), S, sc.counts.data_ptr(), ws.E, st), "xb_moe_histogram")
         ws.epoch["counts"] += 1
         _lib.check(lib.xb_ep_exchange_counts(sc.counts.data_ptr(), ws.ptrs(ws.o_table), ws.ptrs(0), S_COUNTS, ws.rank,
@@ -329,25 +364,35 @@ class _FusedEPMoE(torch.autograd.Function):
                                   ws.E, ws.El, ws.cap, sc.dest_rank.data_ptr(), sc.dest_row.data_ptr(),
                                   sc.seg.data_ptr(), sc.tot.data_ptr(), sc.overflow.data_ptr(), st), "xb_ep_plan")
         # ---- dispatch ---------------------------------------------------------------------------
+        t1 = PhaseTimes.mark()
+        PhaseTimes.add("fwd_plan", t0, t1)
         recv = ws.view("recv_f", ws.cap, torch.bfloat16, H)
         meta = ws.view("meta_f", ws.cap, torch.int32, 1)
         _lib.check(lib.xb_ep_prepare_recv(recv.data_ptr(), meta.data_ptr(), sc.seg.data_ptr(), sc.tot.data_ptr(), El,
                                           ws.cap, H * 2, st), "xb_ep_prepare_recv")
         ws.push(x, tok_of_slot[:S], sc.dest_rank[:S], sc.dest_row[:S], None, "recv_f", "meta_f", S_DISP, C_DISP, "disp")
         # ---- experts ----------------------------------------------------------------------------
+        t2 = PhaseTimes.mark()
+        PhaseTimes.add("fwd_dispatch", t1, t2)
         _rows_gemm(ws, sc, recv, H, gate_up, sc.h, I2, 1, fp8, None if qg is None else qg.q_nk,
                    None if qg is None else qg.sf_nk, st)
         _lib.check(lib.xb_swiglu_fwd(sc.h.data_ptr(), sc.a.data_ptr(), ws.cap, I, 1, st), "xb_swiglu_fwd")
         _rows_gemm(ws, sc, sc.a, I, down, sc.y, H, 1, fp8, None if qd is None else qd.q_nk,
                    None if qd is None else qd.sf_nk, st)
         # ---- return -----------------------------------------------------------------------------
+        t3 = PhaseTimes.mark()
+        PhaseTimes.add("fwd_experts", t2, t3)
         _lib.check(lib.xb_ep_meta_targets(meta.data_ptr(), ws.cap, sc.ret_rank.data_ptr(), sc.ret_slot.data_ptr(), st),
                    "xb_ep_meta_targets")
         ws.push(sc.y, None, sc.ret_rank, sc.ret_slot, None, "ret_f", None, S_RET, C_RET, "ret")
+        t4 = PhaseTimes.mark()
+        PhaseTimes.add("fwd_return", t3, t4)
         y_slots = ws.view("ret_f", S, torch.bfloat16, H)
         out = torch.empty((T, H), device=x.device, dtype=torch.bfloat16)
         _lib.check(lib.xb_moe_gather_sum(out.data_ptr(), out.stride(0), y_slots.data_ptr(), H, slot_idx.data_ptr(),
                                          w32.data_ptr(), T, k, H, st), "xb_moe_gather_sum")
+        PhaseTimes.add("fwd_combine", t4)
+        moe_ops._launches += 14 + (2 if fp8 else 0)
         ctx.ws, ctx.sc, ctx.dims, ctx.fp8_mode = ws, sc, (T, H, k, S, El, I2, I), fp8_mode
         ctx.gate_up, ctx.down = gate_up, down
         ctx.save_for_backward(w32)
@@ -370,12 +415,15 @@ class _FusedEPMoE(torch.autograd.Function):
             from ..ops.fp8_grouped import cached_quantized_experts
             qg, qd = cached_quantized_experts(gate_up), cached_quantized_experts(down)
         # slot gradients and routing-weight gradients
+        b0 = PhaseTimes.mark()
         dys = sc.dys[:S]
         _lib.check(lib.xb_moe_gather_rows(dys.data_ptr(), H, dout.data_ptr(), dout.stride(0), tok_of_slot.data_ptr(),
                                           w32.data_ptr(), S, H, st), "xb_moe_gather_rows")
-        dw = torch.empty((T, k), device=dout.device, dtype=torch.float32)
-        _lib.check(lib.xb_moe_slot_dots(dw.data_ptr(), dout.data_ptr(), dout.stride(0), y_slots.data_ptr(), H,
-                                        slot_idx.data_ptr(), T, k, H, st), "xb_moe_slot_dots")
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty((T, k), device=dout.device, dtype=torch.float32)
+            _lib.check(lib.xb_moe_slot_dots(dw.data_ptr(), dout.data_ptr(), dout.stride(0), y_slots.data_ptr(), H,
+                                            slot_idx.data_ptr(), T, k, H, st), "xb_moe_slot_dots")
         # slot gradients -> owners' rows (same plan as the dispatch)
         recv_b = ws.view("recv_b", ws.cap, torch.bfloat16, H)
         meta_b = ws.view("meta_b", ws.cap, torch.int32, 1)
@@ -383,6 +431,8 @@ class _FusedEPMoE(torch.autograd.Function):
                                           ws.cap, H * 2, st), "xb_ep_prepare_recv")
         ws.push(dys, None, sc.dest_rank[:S], sc.dest_row[:S], None, "recv_b", "meta_b", S_BDISP, C_BDISP, "bdisp")
         recv_f = ws.view("recv_f", ws.cap, torch.bfloat16, H)
+        b1 = PhaseTimes.mark()
+        PhaseTimes.add("bwd_slots_dispatch", b0, b1)
         # down projection: input gradient, then weight gradient (bf16 operands)
         _rows_gemm(ws, sc, recv_b, H, down, sc.da, I, 0, fp8, None if qd is None else qd.q_kn,
                    None if qd is None else qd.sf_kn, st)
@@ -410,6 +460,8 @@ class _FusedEPMoE(torch.autograd.Function):
         _rows_gemm(ws, sc, sc.h, I2, gate_up, sc.y, H, 0, fp8, None if qg is None else qg.q_kn,
                    None if qg is None else qg.sf_kn, st)
         # row gradients -> source slots, summed over the k slots of a token
+        b2 = PhaseTimes.mark()
+        PhaseTimes.add("bwd_experts", b1, b2)
         meta_f = ws.view("meta_f", ws.cap, torch.int32, 1)
         _lib.check(lib.xb_ep_meta_targets(meta_f.data_ptr(), ws.cap, sc.ret_rank.data_ptr(), sc.ret_slot.data_ptr(), st),
                    "xb_ep_meta_targets")
@@ -418,6 +470,8 @@ class _FusedEPMoE(torch.autograd.Function):
         dx = torch.empty((T, H), device=dout.device, dtype=torch.bfloat16)
         _lib.check(lib.xb_moe_gather_sum(dx.data_ptr(), dx.stride(0), dslots.data_ptr(), H, slot_idx.data_ptr(), None,
                                          T, k, H, st), "xb_moe_gather_sum")
+        PhaseTimes.add("bwd_return_sum", b2)
+        moe_ops._launches += 15 + (2 if fp8 else 0)
         return dx, dw, None, d_gate_up, d_down, None, None
 
 

@@ -35,6 +35,9 @@ WAIT_MS = 2000
 AG_CTAS = int(os.environ.get("XORL_B200_AG_CTAS", "128"))
 AG_UNROLL = int(os.environ.get("XORL_B200_AG_UNROLL", "8"))
 RS_CTAS = int(os.environ.get("XORL_B200_RS_CTAS", "128"))
+# "dma": copy engines move the bytes (no SM taken from the GEMMs next to the collective), kernels only
+# synchronise and reduce locally; "kernel": the pull kernels with peer loads
+MODE = os.environ.get("XORL_B200_ZERO_TRANSPORT", "dma")
 
 
 def _align(x: int, a: int = 256) -> int:
@@ -60,7 +63,9 @@ class SymmetricTransport:
         self.buf_cursor = 0
         self.lib = _lib.cuda_lib()
         self._flag_ptrs = (ctypes.c_ulonglong * self.world)(*self.base_ptrs)
-        self.partial = torch.zeros(64, device=engine.device, dtype=torch.float32)
+        self.partial = torch.zeros(max(RS_CTAS, 64), device=engine.device, dtype=torch.float32)
+        self.mode = MODE if MODE in ("dma", "kernel") else "dma"
+        self.staging: Optional[torch.Tensor] = None      # [world, shard] bf16, DMA reduce-scatter
         self.launches = 0
 
     # ------------------------------------------------------------------------------------------
@@ -99,6 +104,7 @@ class SymmetricTransport:
         info_rank0(f"symmetric heap: {total / 2 ** 30:.2f} GiB per rank, {len(groups)} parameter "
                    f"groups, {NUM_GRAD_BUFS} gradient buffers, multimem={'on' if self.mc_base else 'off'}")
         self._groups = {id(g) for g in groups}
+        self._shard_sizes = [g.shard_numel for g in groups]
         return self
 
     # ------------------------------------------------------------------------------------------
@@ -124,9 +130,13 @@ class SymmetricTransport:
         eng = self.engine
         comm_stream.wait_stream(torch.cuda.current_stream())
         srcs = self._ptrs(self.layout["shard"][id(g)])
-        _lib.check(self.lib.xb_symm_allgather(g.full.data_ptr(), srcs, g.shard_numel * 2, self.rank,
-                                              self.world, AG_CTAS | (AG_UNROLL << 16), comm_stream.cuda_stream),
-                   "xb_symm_allgather")
+        if self.mode == "dma":
+            _lib.check(self.lib.xb_symm_allgather_dma(g.full.data_ptr(), srcs, g.shard_numel * 2, self.rank,
+                                                      self.world, comm_stream.cuda_stream), "xb_symm_allgather_dma")
+        else:
+            _lib.check(self.lib.xb_symm_allgather(g.full.data_ptr(), srcs, g.shard_numel * 2, self.rank,
+                                                  self.world, AG_CTAS | (AG_UNROLL << 16), comm_stream.cuda_stream),
+                       "xb_symm_allgather")
         g.gather_event = torch.cuda.Event()
         g.gather_event.record(comm_stream)
         self.launches += 1
@@ -172,11 +182,45 @@ class SymmetricTransport:
         grads = self._ptrs(o)
         slot = BUF_SLOT0 + 64 * b
         mc = self.mc_base + o if self.mc_base else 0
-        _lib.check(self.lib.xb_symm_reduce_scatter(
-            g.grad_shard.data_ptr(), grads, ctypes.c_ulonglong(mc), g.rank * g.shard_numel,
-            g.shard_numel, int(accumulate), 1.0, None, self._flag_ptrs, slot, slot + 16, slot + 32,
-            self.rank, self.world, epoch, WAIT_MS, RS_CTAS, comm_stream.cuda_stream),
-            "xb_symm_reduce_scatter")
+        # sum-of-squares partials of the updated shard come out of the same pass (one per CTA); they are
+        # only kept when nothing later in the step changes the shard (engine._early_norm_ok)
+        want_sq = self.engine._early_norm_ok(g)
+        partial = self.partial[:RS_CTAS] if want_sq else None
+        if self.mode == "dma" and not mc:
+            # 1. everybody's gradients for this buffer are final
+            _lib.check(self.lib.xb_symm_barrier(self._flag_ptrs, slot, self.rank, self.world, epoch, WAIT_MS,
+                                                comm_stream.cuda_stream), "xb_symm_barrier")
+            # 2. copy engines bring this rank's slice of every peer's buffer into local staging
+            if self.staging is None or self.staging.numel() < self.world * g.shard_numel:
+                self.staging = torch.empty(self.world * max(gg_numel for gg_numel in self._shard_sizes),
+                                           device=self.engine.device, dtype=torch.bfloat16)
+            sbytes = g.shard_numel * 2
+            _lib.check(self.lib.xb_symm_gather_slices_dma(self.staging.data_ptr(), grads, g.rank * sbytes, sbytes,
+                                                          self.rank, self.world, comm_stream.cuda_stream),
+                       "xb_symm_gather_slices_dma")
+            # 3. the reduce kernel on local pointers: staging slot r (own slice: in place), arranged so
+            #    that pointer + slice offset lands on the slice
+            base = self.staging.data_ptr()
+            local = [(base + r * sbytes - g.rank * sbytes) if r != self.rank else self.base_ptrs[r] + o
+                     for r in range(self.world)]
+            lptrs = (ctypes.c_ulonglong * self.world)(*local)
+            _lib.check(self.lib.xb_symm_reduce_scatter(
+                g.grad_shard.data_ptr(), lptrs, ctypes.c_ulonglong(0), g.rank * g.shard_numel, g.shard_numel,
+                int(accumulate), 1.0, _lib.ptr(partial), self._flag_ptrs, slot, slot + 16, slot + 32, self.rank,
+                self.world, epoch, WAIT_MS, RS_CTAS, comm_stream.cuda_stream), "xb_symm_reduce_scatter")
+            self.launches += 1
+        else:
+            _lib.check(self.lib.xb_symm_reduce_scatter(
+                g.grad_shard.data_ptr(), grads, ctypes.c_ulonglong(mc), g.rank * g.shard_numel,
+                g.shard_numel, int(accumulate), 1.0, _lib.ptr(partial), self._flag_ptrs, slot, slot + 16, slot + 32,
+                self.rank, self.world, epoch, WAIT_MS, RS_CTAS, comm_stream.cuda_stream),
+                "xb_symm_reduce_scatter")
+        if want_sq:
+            with torch.cuda.stream(comm_stream):
+                if g.sq is None:
+                    g.sq = torch.zeros(1, device=self.engine.device, dtype=torch.float32)
+                torch.sum(partial, dim=0, keepdim=True, out=g.sq)
+            g.sq_valid = True
         g.reduce_event = torch.cuda.Event()
         g.reduce_event.record(comm_stream)
         self.buf_event[b] = g.reduce_event

@@ -230,13 +230,19 @@ class Zero3Engine:
                  reduce_dtype: torch.dtype = torch.float32, reshard_after_forward: bool = True,
                  activation_offload: bool = False,
                  recompute: bool = True, seed: int = 0, comm_backend: str = "nccl",
-                 shard: bool = True):
+                 shard: bool = True, forward_prefetch: bool = True, backward_prefetch: bool = True,
+                 moe_grad_reduce_mode: Optional[str] = None):
         self.model = model
         self.ps = pstate or get_parallel_state()
         self.device = device or torch.device("cuda" if torch.cuda.is_available() else "cpu")
         self.compute_dtype = compute_dtype
         self.reduce_dtype = reduce_dtype
+        # train.moe_grad_reduce_mode: "bf16_a2a_fp32_sum" sends expert gradients as stochastically rounded
+        # bf16 through an all-to-all and sums the received slices in fp32; "reduce_scatter" is the
+        # plain collective in the reduce dtype (src/xorl/distributed/fsdp2/bf16_a2a_reduce.py:64-114)
+        self.moe_grad_reduce_mode = moe_grad_reduce_mode
         self.bf16_a2a_reduce = os.environ.get("XORL_B200_BF16_A2A_REDUCE", "1") == "1"
+        self.forward_prefetch, self.backward_prefetch = forward_prefetch, backward_prefetch
         self.offloader = ActivationOffloader(self) if activation_offload else None
         self.recompute = recompute
         self.comm_backend = comm_backend
@@ -561,8 +567,9 @@ class Zero3Engine:
                     with torch.cuda.stream(self.norm_stream):
                         self._group_sumsq(g)
             elif self.symm is not None and self.symm.can_reduce(g):
+                g.sq_valid = False
                 self.symm.reduce_scatter_accumulate(g, gf, accumulate, self.comm_stream)
-                if early:
+                if early and not g.sq_valid:
                     with torch.cuda.stream(self.comm_stream):
                         self._group_sumsq(g)
             elif self.is_cuda:
@@ -603,7 +610,10 @@ class Zero3Engine:
         g.sq_valid = True
 
     def _rs_collective(self, g: FlatParamGroup, gf: torch.Tensor, accumulate: bool) -> None:
-        if self.reduce_dtype == torch.bfloat16 and gf.dtype == torch.float32 and self.bf16_a2a_reduce:
+        a2a = self.reduce_dtype == torch.bfloat16 and self.bf16_a2a_reduce
+        if getattr(g, "is_expert", False) and self.moe_grad_reduce_mode is not None:
+            a2a = self.moe_grad_reduce_mode == "bf16_a2a_fp32_sum"
+        if a2a and gf.dtype == torch.float32:
             # bf16 on the wire, stochastic rounding on the way out, fp32 summation on arrival
             from .dist_utils import stochastic_bf16_all_to_all_reduce_scatter
             stochastic_bf16_all_to_all_reduce_scatter(gf, g.grad_shard, g.pg, accumulate)
@@ -682,8 +692,9 @@ class Zero3Engine:
         if nl:
             self.gather(layers[0])
         for i, unit in enumerate(layers):
+            self.gather(unit)
             self.wait_gather(unit)
-            if i + 1 < nl:
+            if i + 1 < nl and self.forward_prefetch:
                 self.gather(layers[i + 1])
             layer = unit.modules[0]
             if self.recompute:
@@ -709,7 +720,7 @@ class Zero3Engine:
             unit = layers[i]
             self.gather(unit)
             self.wait_gather(unit)
-            if i > 0:
+            if i > 0 and self.backward_prefetch:
                 self.gather(layers[i - 1])
             self._prepare_grad_buffers(unit)
             layer = unit.modules[0]

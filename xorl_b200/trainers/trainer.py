@@ -10,6 +10,7 @@ on the device -> fused optimizer step -> LR step.  Artifacts: ``xorl_cli.yaml``,
 """
 from __future__ import annotations
 
+import gc
 import json
 import os
 import time
@@ -107,6 +108,15 @@ class Trainer:
             self.model.loss_chunk_tokens = max(256, -(-int(a.data.sample_packing_sequence_len or 4096)
                                                       * t.micro_batch_size // t.ce_num_chunks))
         if self.model_config.is_moe:
+            # model.train_router: whether the gradient of the expert outputs flows into the routing
+            # weights (off by default: the router then learns from the load-balancing loss only);
+            # model.freeze_router: the router weights do not train at all
+            for m in self.model.modules():
+                if hasattr(m, "train_router"):
+                    m.train_router = bool(a.model.train_router)
+                    if a.model.freeze_router:
+                        for prm in m.gate.parameters():
+                            prm.requires_grad_(False)
             self.model.ctx_defaults["ep_dispatch"] = a.model.ep_dispatch
             # every EP rank must size its peer-memory workspace identically
             self.model.ctx_defaults["ep_max_slots"] = int(a.data.sample_packing_sequence_len or 4096) \
@@ -136,10 +146,16 @@ class Trainer:
             reduce_dtype=torch.float32 if t.fsdp_reduce_dtype == "fp32" else torch.bfloat16,
             activation_offload=t.enable_activation_offload,
             reshard_after_forward=True if t.reshard_after_forward is None else t.reshard_after_forward,
-            recompute=recompute, seed=t.seed, comm_backend=t.comm_backend)
+            recompute=recompute, seed=t.seed, comm_backend=t.comm_backend,
+            forward_prefetch=bool(t.enable_forward_prefetch),
+            backward_prefetch=True if t.enable_backward_prefetch is None else bool(t.enable_backward_prefetch),
+            moe_grad_reduce_mode=t.moe_grad_reduce_mode)
         if t.comm_backend in ("auto", "fused") and self.device.type == "cuda" and self.ps.world_size > 1:
             from ..parallel.symm import try_attach_symmetric_transport
             try_attach_symmetric_transport(self.engine, required=(t.comm_backend == "fused"))
+        self.teacher_engine = None
+        if a.distill.enable_distillation:
+            self._build_teacher()
         self.pp_runner = None
         if self.pp_layout is not None:
             from ..parallel.pp import PipelineRunner
@@ -151,6 +167,43 @@ class Trainer:
                 f.endswith(".safetensors") for f in os.listdir(weights)):
             from ..checkpoint.hf_io import load_hf_weights
             load_hf_weights(self.engine, weights, self.model_config, mode=t.load_weights_mode)
+
+    def _build_teacher(self) -> None:
+        """``distill.enable_distillation``: a frozen teacher of the family named by
+        ``distill.teacher_model_path`` (a directory with config.json and, optionally, safetensors
+        weights, or a preset name) runs a forward pass over every micro-batch; its final hidden states
+        and lm-head give the target distribution of the KL term in the head loss."""
+        a, d = self.args, self.args.distill
+        if not d.teacher_model_path:
+            raise ValueError("distill.enable_distillation needs distill.teacher_model_path")
+        if self.pp_layout is not None or self.ps.tp_size > 1:
+            raise NotImplementedError("distillation is not supported with pipeline or tensor parallelism")
+        from ..models.config import ModelConfig, preset
+        path = d.teacher_model_path
+        tcfg = ModelConfig.from_pretrained(path) if os.path.isdir(path) else preset(path)
+        if tcfg.vocab_size != self.model_config.vocab_size:
+            raise ValueError(f"teacher vocabulary {tcfg.vocab_size} != student vocabulary {self.model_config.vocab_size}")
+        teacher = build_model(tcfg, None, device="meta")
+        for p in teacher.parameters():
+            p.requires_grad_(False)
+        from ..parallel.cp import attach_cp_strategy
+        attach_cp_strategy(teacher, self.ps)
+        self.teacher_engine = Zero3Engine(teacher, self.ps, compute_dtype=self.compute_dtype, device=self.device,
+                                          reshard_after_forward=False, recompute=False, seed=a.train.seed + 1)
+        if os.path.isdir(path) and any(f.endswith(".safetensors") for f in os.listdir(path)):
+            from ..checkpoint.hf_io import load_hf_weights
+            load_hf_weights(self.teacher_engine, path, tcfg, mode=a.train.load_weights_mode
+                            if a.train.load_weights_mode != "skip" else "all_ranks")
+        self.teacher_config = tcfg
+
+    def _teacher_targets(self, d: Dict[str, torch.Tensor]):
+        """(final hidden states, lm-head weight, loss type, loss weight) of the teacher for one micro-batch."""
+        te = self.teacher_engine
+        hidden = te.forward_only(d["input_ids"], position_ids=d.get("position_ids"), cu_seqlens=d.get("cu_seqlens"))
+        tm = te.model
+        w = tm.embed_tokens.weight if self.teacher_config.tie_word_embeddings else tm.lm_head.weight
+        dd = self.args.distill
+        return hidden.detach(), w, dd.distillation_loss_type, float(dd.distillation_loss_weight)
 
     def _build_data(self, dataset=None) -> None:
         a = self.args
@@ -184,6 +237,10 @@ class Trainer:
         self.meter = EnvironMeter(self.model_config, self.ps.world_size, self.ps.group("dp"),
                                   recompute=t.enable_gradient_checkpointing)
         self.timer = CudaTimer(t.enable_step_phase_timing)
+        self.component_timer = None
+        if t.enable_per_component_timing:
+            from ..utils.component_timer import PerComponentTimer
+            self.component_timer = PerComponentTimer(self.model)
         self.profiler = None
         if t.enable_profiling and (not t.profile_rank0_only or self.ps.rank == 0):
             self.profiler = create_profiler(t.profile_start_step, t.profile_end_step, t.profile_trace_dir,
@@ -267,15 +324,21 @@ class Trainer:
         for i, mb in enumerate(micro_batches):
             self.meter.add(mb)
             d = self._to_device(mb)
+            phase = self.timer.scope("forward_backward")
+            phase.__enter__()
             # gradient norms are taken unit by unit during the last micro-batch's backward
             self.engine.final_micro_batch = i == len(micro_batches) - 1
+            extra = {"local_cu_seqlens": mb.get("local_cu_seqlens")}
+            if self.teacher_engine is not None:
+                extra["distill"] = self._teacher_targets(d)
             loss = self.engine.forward_backward(
                 d["input_ids"], d["labels"], position_ids=d.get("position_ids"),
                 cu_seqlens=d.get("cu_seqlens"), grad_scale=1.0 / global_tokens,
-                extra_loss_fn=self._extra_loss_fn(),
-                extra={"local_cu_seqlens": mb.get("local_cu_seqlens")})
+                extra_loss_fn=self._extra_loss_fn(), extra=extra)
             total = loss if total is None else total + loss
-        self.engine.finish_grad_sync()
+            phase.__exit__(None, None, None)
+        with self.timer.scope("grad_sync"):
+            self.engine.finish_grad_sync()
         dump = os.environ.get("XORL_DEBUG_DUMP_GRADS")
         if dump and self.global_step == 0:
             self._dump_full_gradients(dump)
@@ -285,8 +348,10 @@ class Trainer:
             if bad:
                 logger.warning("step %d rank %d: non-finite gradients in %s", self.global_step + 1,
                                self.ps.rank, ", ".join(bad[:20]))
-        norm, coef = self.engine.grad_norm_and_clip_coef(t.max_grad_norm)
-        self.optimizer.step(clip_coef=coef if t.max_grad_norm > 0 else None)
+        with self.timer.scope("grad_norm"):
+            norm, coef = self.engine.grad_norm_and_clip_coef(t.max_grad_norm)
+        with self.timer.scope("optimizer"):
+            self.optimizer.step(clip_coef=coef if t.max_grad_norm > 0 else None)
         self.lr_scheduler.step()
         if self.ps.world_size > 1 and self.ps.group(self.ps.loss_group_name) is not None:
             dist.all_reduce(total, group=self.ps.group(self.ps.loss_group_name))
@@ -355,6 +420,11 @@ class Trainer:
     def train(self) -> Dict[str, Any]:
         t = self.args.train
         done = False
+        # train.gc_steps > 0: the cyclic collector runs only at those steps, so that its pauses are the
+        # same on every rank instead of stalling one rank inside a collective
+        gc_was_enabled = gc.isenabled()
+        if t.gc_steps and t.gc_steps > 0:
+            gc.disable()
         while not done:
             for micro_batches in self.dataloader:
                 if self.global_step >= self.train_steps:
@@ -381,6 +451,19 @@ class Trainer:
                 metrics = self.meter.step(dt, self.global_step)
                 metrics.update(loss=loss, grad_norm=float(out["grad_norm"]), lr=out["lr"],
                                step=self.global_step, step_time=dt)
+                if t.enable_step_phase_timing:
+                    # per-phase device time of this step (CUDA events; reading them synchronises, which
+                    # step_phase_timing_sync_cuda=false defers to every 10th step)
+                    if t.step_phase_timing_sync_cuda or self.global_step % 10 == 0:
+                        for k, v in self.timer.summary().items():
+                            metrics[f"phase/{k}_ms"] = v
+                    if self.component_timer is not None:
+                        for k, v in self.component_timer.flush().items():
+                            metrics[f"component/{k}_ms"] = v
+                        self.component_timer.reset()
+                    if t.enable_step_memory_profiling and self.device.type == "cuda":
+                        metrics["memory/peak_allocated_gb"] = torch.cuda.max_memory_allocated() / 2 ** 30
+                        torch.cuda.reset_peak_memory_stats()
                 self.loss_history.append(loss)
                 self.metrics_history.append(metrics)
                 self._maybe_log(metrics)
@@ -389,6 +472,8 @@ class Trainer:
                 if self.profiler is not None:
                     self.profiler.step()
                 self._maybe_save_checkpoint()
+                if t.gc_steps and self.global_step % t.gc_steps == 0:
+                    gc.collect()                 # automatic collection is off during training (see train())
                 if t.empty_cache_steps and self.global_step % t.empty_cache_steps == 0 \
                         and self.device.type == "cuda":
                     torch.cuda.empty_cache()
@@ -397,6 +482,8 @@ class Trainer:
                     done = True
             if len(self.dataloader) == 0:
                 break
+        if gc_was_enabled:
+            gc.enable()
         return self._finalize()
 
     def _maybe_log(self, m: Dict[str, float]) -> None:
@@ -408,7 +495,12 @@ class Trainer:
 
     def _maybe_save_checkpoint(self, force: bool = False) -> None:
         t = self.args.train
-        if not force and not (t.save_steps and self.global_step % t.save_steps == 0):
+        # train.save_steps: every N steps; train.save_epochs: every (fraction of an) epoch, counted in
+        # steps like the reference does (src/xorl/trainers/trainer.py:679-683,2493-2498)
+        epoch_steps = int(t.save_epochs * self.steps_per_epoch) if t.save_epochs else 0
+        due = (t.save_steps and self.global_step % t.save_steps == 0) or \
+            (epoch_steps and self.global_step % epoch_steps == 0)
+        if not force and not due:
             return
         extra = {"global_step": self.global_step, "lr_scheduler": self.lr_scheduler.state_dict(),
                  "train_dataloader": self.dataloader.state_dict(),

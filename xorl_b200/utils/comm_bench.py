@@ -39,12 +39,15 @@ def main(argv=None) -> None:
     ps = init_parallel_state(device_type="cuda", dp_mode="fsdp2")
     world, rank = dist.get_world_size(), dist.get_rank()
     cfg = preset(a.model, num_hidden_layers=2, vocab_size=8192)
-    for mode in ("nccl", "fused"):
+    from ..parallel import symm_transport
+    for mode in ("nccl", "kernel", "dma"):
+        # kernel: pull kernels with peer loads; dma: copy engines move the bytes, kernels reduce locally
         model = DecoderLM(cfg, device="meta")
         eng = Zero3Engine(model, ps, compute_dtype=torch.bfloat16, device=dev, seed=0)
-        if mode == "fused" and not try_attach_symmetric_transport(eng, required=False):
+        symm_transport.MODE = mode
+        if mode != "nccl" and not try_attach_symmetric_transport(eng, required=False):
             if rank == 0:
-                print(json.dumps({"transport": "fused", "unavailable": "symmetric memory could not be set up"}))
+                print(json.dumps({"transport": mode, "unavailable": "symmetric memory could not be set up"}))
             continue
         _, layers = eng._units_by_role()
         unit = layers[0]
@@ -88,7 +91,7 @@ def main(argv=None) -> None:
             elem = g.padded
             ag_bytes = elem * 2 * (world - 1) / world                     # bf16 pulled from peers
             # bytes per element on the wire: bf16 in the fused transport, the reduce dtype through NCCL
-            rs_wire = 2 if mode == "fused" else (4 if eng.reduce_dtype == torch.float32 else 2)
+            rs_wire = 2 if mode != "nccl" else (4 if eng.reduce_dtype == torch.float32 else 2)
             rs_bytes = elem * rs_wire * (world - 1) / world
             print(json.dumps({
                 "transport": mode, "n_gpus": world, "unit_params": int(g.numel), "rs_wire_bytes_per_elem": rs_wire,
