@@ -137,3 +137,59 @@ def test_relora_merge_keeps_fp32_masters_of_the_adapters():
         elif not torch.equal(t.float(), before[n].float()):
             changed_base += 1
     assert changed_base == 4                                          # qkv_proj + down_proj, two layers
+
+
+def _moe_engine(la, seed=0):
+    from xorl_b200.adapters.lora import inject_lora
+    from xorl_b200.parallel.zero import Zero3Engine
+    reset_parallel_state()
+    ps = init_parallel_state(device_type="cpu")
+    model = DecoderLM(preset("tiny-qwen3-moe", router_aux_loss_coef=0.0), device="meta")
+    wrapped = inject_lora(model, la)
+    eng = Zero3Engine(model, ps, compute_dtype=torch.float32, device=torch.device("cpu"), seed=seed)
+    return model, eng, wrapped
+
+
+def test_moe_expert_lora_trains_adapters_and_merges(tmp_path):
+    """Per-expert adapters on gate / up / down of the stacked experts: only they train, the adapter
+    path equals the merged weights, and the PEFT export has one pair per expert."""
+    from xorl_b200.adapters.lora import ExpertsLoRA, merge_lora, save_lora_checkpoint
+    from xorl_b200.optim import build_optimizer
+    la = LoRAArguments(enable_lora=True, lora_rank=8, lora_alpha=16,
+                       lora_target_modules=["q_proj", "gate_proj", "up_proj", "down_proj"])
+    model, eng, wrapped = _moe_engine(la)
+    assert any(n.endswith("mlp.experts") for n in wrapped), wrapped
+    ex = model.layers["0"].mlp.experts
+    assert isinstance(ex.lora, ExpertsLoRA) and ex.lora.gate_proj_lora_A.shape == (8, 128, 8)
+    assert ex.lora.down_proj_lora_B.shape == (8, 8, 128) and not ex.gate_up_proj.requires_grad
+    names = [n for g in eng.all_groups() if not getattr(g, "frozen", False) for n, _ in g.named_params]
+    assert names and all("lora_" in n for n in names)
+    assert any(n.endswith("experts.lora.up_proj_lora_B") for n in names)
+    base = {n: t.clone() for n, t in eng.iter_full_tensors("master") if "lora_" not in n}
+    opt = build_optimizer(eng, lr=1e-2, weight_decay=0.0)
+    ids = torch.randint(0, 1024, (2, 65))
+    losses = []
+    for _ in range(6):
+        opt.zero_grad()
+        losses.append(float(eng.forward_backward(ids[:, :-1], ids[:, 1:], grad_scale=1.0 / 128)))
+        eng.finish_grad_sync()
+        _, coef = eng.grad_norm_and_clip_coef(1.0)
+        opt.step(clip_coef=coef)
+    assert losses[-1] < losses[0] - 0.02, losses
+    for n, t in eng.iter_full_tensors("master"):
+        if "lora_" not in n:
+            assert torch.equal(t, base[n]), n
+    b_norm = float(ex.lora.gate_proj_lora_B.float().norm())
+    assert b_norm > 0                                       # the expert adapters did move
+    save_lora_checkpoint(eng, str(tmp_path / "peft"), "tiny-moe")
+    from safetensors.torch import load_file
+    sd = load_file(str(tmp_path / "peft" / "adapter_model.safetensors"))
+    k = "base_model.model.model.layers.0.mlp.experts.3.gate_proj.lora_A.weight"
+    assert k in sd and tuple(sd[k].shape) == (8, 128)
+    assert tuple(sd["base_model.model.model.layers.1.mlp.experts.7.down_proj.lora_B.weight"].shape) == (128, 8)
+    x, y = ids[:, :-1], ids[:, 1:]
+    with torch.no_grad():
+        before = float(model(x, labels=y, grad_scale=1.0 / 128)["loss"])
+        assert merge_lora(model) >= 3                        # q_proj of two layers + two expert stacks
+        after = float(model(x, labels=y, grad_scale=1.0 / 128)["loss"])
+    assert abs(before - after) < 1e-4 and float(ex.lora.gate_proj_lora_B.abs().max()) == 0.0

@@ -78,6 +78,64 @@ class LoraLinear(nn.Module):
             self.lora_B[name].zero_()
 
 
+class ExpertsLoRA(nn.Module):
+    """Per-expert low-rank adapters on the stacked expert weights of a MoE block: for every targeted
+    projection ``p`` in gate_proj / up_proj / down_proj two trainable tensors ``p_lora_A [E, in, r]``
+    and ``p_lora_B [E, r, out]`` (names and shapes of src/xorl/models/layers/moe/lora.py:13-15), the
+    base expert weights frozen.  Lives as ``experts.lora``; the expert MLP adds
+    ``(alpha / r) (x A_e) B_e`` with two extra grouped GEMMs per projection.  Under expert
+    parallelism the adapter tensors hold the local experts and are sharded like the expert weights."""
+    PROJ = ("gate_proj", "up_proj", "down_proj")
+
+    def __init__(self, experts, rank: int, alpha: float, targets: Iterable[str], b_init_std: float = 0.0):
+        super().__init__()
+        E, H, I2 = experts.gate_up_proj.shape
+        I = experts.down_proj.shape[1]
+        if I2 != 2 * I:
+            raise NotImplementedError("expert LoRA needs gated experts (gate_up_proj of width 2 I)")
+        dims = {"gate_proj": (H, I), "up_proj": (H, I), "down_proj": (I, H)}
+        self.rank, self.scaling = rank, alpha / rank
+        self.targets = tuple(p for p in self.PROJ if p in targets)
+        dt, dev = experts.gate_up_proj.dtype, experts.gate_up_proj.device
+        ep = getattr(experts.gate_up_proj, "_xb_ep", None)
+        for p in self.targets:
+            fin, fout = dims[p]
+            A = nn.Parameter(torch.empty(E, fin, rank, dtype=dt, device=dev))
+            B = nn.Parameter(torch.empty(E, rank, fout, dtype=dt, device=dev))
+            A._xb_lora, B._xb_lora = "A", ("B" if b_init_std == 0.0 else "B_random")
+            for t in (A, B):
+                t._xb_expert = True
+                if ep is not None:
+                    from ..parallel.ep import mark_ep
+                    mark_ep(t, ep[0], ep[1])
+            setattr(self, f"{p}_lora_A", A)
+            setattr(self, f"{p}_lora_B", B)
+        for w in (experts.gate_up_proj, experts.down_proj, experts.gate_up_bias, experts.down_bias):
+            if w is not None:
+                w.requires_grad_(False)
+
+    def tensors(self) -> dict:
+        out = {"scaling": self.scaling}
+        for p in self.targets:
+            out[p] = (getattr(self, f"{p}_lora_A"), getattr(self, f"{p}_lora_B"))
+        return out
+
+    @torch.no_grad()
+    def merge_into(self, experts) -> None:
+        """W += scaling * A B per expert, then B restarts at zero."""
+        I = experts.down_proj.shape[1]
+        for p in self.targets:
+            A, B = getattr(self, f"{p}_lora_A"), getattr(self, f"{p}_lora_B")
+            delta = torch.bmm(A.float(), B.float()) * self.scaling
+            if p == "gate_proj":
+                experts.gate_up_proj[:, :, :I] += delta.to(experts.gate_up_proj.dtype)
+            elif p == "up_proj":
+                experts.gate_up_proj[:, :, I:] += delta.to(experts.gate_up_proj.dtype)
+            else:
+                experts.down_proj += delta.to(experts.down_proj.dtype)
+            B.zero_()
+
+
 def _fused_slices(module_name: str, linear: Linear, parent, targets: Iterable[str]):
     leaf = module_name.rsplit(".", 1)[-1]
     if leaf in FUSED_PARTS:
@@ -116,6 +174,13 @@ def inject_lora(model: nn.Module, lora_args) -> List[str]:
             setattr(parent, cname, LoraLinear(child, lora_args.lora_rank, lora_args.lora_alpha, slices,
                                               lora_args.lora_b_init_std, lora_args.lora_b_init_seed))
             wrapped.append(full)
+    # stacked routed experts of MoE blocks (src/xorl/lora/utils.py:1618 inject_lora_into_model_with_moe)
+    from ..models.moe import Experts
+    for name, mod in list(model.named_modules()):
+        if isinstance(mod, Experts) and not any(x in name for x in exclude) \
+                and any(p in targets for p in ExpertsLoRA.PROJ) and getattr(mod, "activation", None) is None:
+            mod.lora = ExpertsLoRA(mod, lora_args.lora_rank, lora_args.lora_alpha, targets, lora_args.lora_b_init_std)
+            wrapped.append(name)
     for n, p in model.named_parameters():
         p.requires_grad_(("lora_A" in n) or ("lora_B" in n))
     model._xb_lora_config = {"r": lora_args.lora_rank, "lora_alpha": lora_args.lora_alpha,
@@ -127,7 +192,11 @@ def init_lora_parameter_(name: str, p: torch.Tensor, rank: int, seed: int = 0, b
     """Kaiming-uniform A (as PEFT), zero (or N(0, b_std)) B."""
     import zlib
     g = torch.Generator().manual_seed((seed * 1000003 + zlib.crc32(name.encode())) % (2 ** 63 - 1))
-    if ".lora_A." in name:
+    if name.endswith("_lora_A"):
+        # stacked expert adapters [E, in, r]: the same uniform bound per expert, fan-in = in
+        bound = 1.0 / math.sqrt(p.shape[-2])
+        p.copy_(((torch.rand(p.shape, generator=g) * 2 - 1) * bound * math.sqrt(3.0)).to(p.device))
+    elif ".lora_A." in name:
         bound = 1.0 / math.sqrt(p.shape[1])
         p.copy_(((torch.rand(p.shape, generator=g) * 2 - 1) * bound * math.sqrt(3.0)).to(p.device))
     elif b_std > 0:
@@ -142,6 +211,9 @@ def merge_lora(model: nn.Module) -> int:
         if isinstance(m, LoraLinear):
             m.merge()
             n += 1
+        elif isinstance(getattr(m, "lora", None), ExpertsLoRA):
+            m.lora.merge_into(m)
+            n += 1
     return n
 
 
@@ -150,6 +222,14 @@ def lora_state_dict_peft(named_full_tensors: Dict[str, torch.Tensor]) -> Dict[st
     (``base_model.model.model...q_proj.lora_A.weight``)."""
     out = {}
     for name, t in named_full_tensors.items():
+        if name.endswith("_lora_A") or name.endswith("_lora_B"):
+            # stacked expert adapters -> one PEFT pair per expert: A [r, in], B [out, r]
+            mod, leaf = name.rsplit(".", 1)                      # ...mlp.experts.lora , gate_proj_lora_A
+            proj, kind = leaf.rsplit("_lora_", 1)
+            experts = mod.rsplit(".", 1)[0]
+            for e in range(t.shape[0]):
+                out[f"base_model.model.model.{experts}.{e}.{proj}.lora_{kind}.weight"] = t[e].t().contiguous()
+            continue
         if ".lora_A." not in name and ".lora_B." not in name:
             continue
         mod, kind, part = name.rsplit(".", 2)
@@ -163,7 +243,7 @@ def save_lora_checkpoint(engine, out_dir: str, base_model_name: str = "") -> Non
     """PEFT directory: ``adapter_model.safetensors`` + ``adapter_config.json``."""
     from safetensors.torch import save_file
     tensors = {n: t.detach().to(torch.bfloat16).cpu().contiguous()
-               for n, t in engine.iter_full_tensors("master") if ".lora_" in n}
+               for n, t in engine.iter_full_tensors("master") if ".lora_" in n or "_lora_" in n}
     if engine.ps.rank != 0:
         return
     os.makedirs(out_dir, exist_ok=True)

@@ -279,7 +279,7 @@ def init_parameter_(name: str, p: torch.Tensor, std: float, seed: int, index: in
                     zero_centered_norm: bool = False, num_experts: int = 0) -> None:
     if p.is_meta:
         return
-    if ".lora_A." in name or ".lora_B." in name:
+    if ".lora_A." in name or ".lora_B." in name or name.endswith("_lora_A") or name.endswith("_lora_B"):
         from ..adapters.lora import init_lora_parameter_
         init_lora_parameter_(name, p, 0, seed)
         return

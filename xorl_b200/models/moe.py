@@ -121,6 +121,9 @@ class Experts(nn.Module):
                 kw["activation"] = self.activation
         if self.fp8_mode is not None:
             kw["fp8"] = self.fp8_mode
+        lora = getattr(self, "lora", None)
+        if lora is not None:
+            kw["lora"] = lora.tensors()
         return kw
 
     def forward(self, x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:

@@ -295,10 +295,16 @@ def expert_mlp_aligned(x_buf: torch.Tensor, seg: torch.Tensor, gate_up: torch.Te
                        down: torch.Tensor, gate_up_bias: Optional[torch.Tensor] = None,
                        down_bias: Optional[torch.Tensor] = None,
                        swiglu_limit: Optional[float] = None, activation: Optional[str] = None,
-                       fp8: Optional[str] = None) -> torch.Tensor:
+                       fp8: Optional[str] = None, lora: Optional[dict] = None) -> torch.Tensor:
     """SwiGLU expert MLP over a segment-aligned token buffer (optional per-expert biases and the
     clamped activation of gpt-oss); ``activation="relu2"``: non-gated ``relu(up(x))^2`` experts.
-    ``fp8``: run both grouped GEMMs in block-scaled fp8 (see ``grouped_linear``)."""
+    ``fp8``: run both grouped GEMMs in block-scaled fp8 (see ``grouped_linear``).
+    ``lora``: per-expert low-rank adapters ``{"scaling": s, "gate_proj": (A [E,H,r], B [E,r,I]),
+    "up_proj": ..., "down_proj": (A [E,I,r], B [E,r,H])}``; each projection present adds
+    ``s * (x @ A[e]) @ B[e]`` through two more grouped GEMMs
+    (src/xorl/models/layers/moe/lora.py:13-15)."""
+    if lora is not None:
+        return _expert_mlp_lora(x_buf, seg, gate_up, down, lora, fp8)
     h = grouped_linear(x_buf, gate_up, seg, fp8)
     if activation == "relu2":
         return grouped_linear(torch.relu(h).square(), down, seg, fp8)
@@ -311,6 +317,35 @@ def expert_mlp_aligned(x_buf: torch.Tensor, seg: torch.Tensor, gate_up: torch.Te
     y = grouped_linear(a, down, seg, fp8)
     if down_bias is not None:
         y = y + down_bias.index_select(0, eid[: y.shape[0]]).to(y.dtype)
+    return y
+
+
+def _expert_mlp_lora(x_buf, seg, gate_up, down, lora: dict, fp8) -> torch.Tensor:
+    s = float(lora["scaling"])
+    I = down.shape[1]
+    h = grouped_linear(x_buf, gate_up, seg, fp8)
+    parts = []
+    for name in ("gate_proj", "up_proj"):
+        ab = lora.get(name)
+        if ab is None:
+            parts.append(None)
+            continue
+        A, B = ab
+        parts.append(grouped_linear(grouped_linear(x_buf, A, seg), B, seg) * s)
+    if parts[0] is not None or parts[1] is not None:
+        zero = None
+        cols = []
+        for d in parts:
+            if d is None:
+                zero = h.new_zeros((h.shape[0], I)) if zero is None else zero
+                d = zero
+            cols.append(d)
+        h = h + torch.cat(cols, dim=-1)
+    a = swiglu(h)
+    y = grouped_linear(a, down, seg, fp8)
+    ab = lora.get("down_proj")
+    if ab is not None:
+        y = y + grouped_linear(grouped_linear(a, ab[0], seg), ab[1], seg) * s
     return y
 
 

@@ -365,7 +365,7 @@ class Trainer:
         """ReLoRA-style merge: fold the adapters into the (gathered) base weights, write the shards
         back, restart B at zero and optionally reset the optimizer moments
         (src/xorl/trainers/training_utils.py:346-372)."""
-        from ..adapters.lora import LoraLinear
+        from ..adapters.lora import ExpertsLoRA, LoraLinear
         eng = self.engine
         if hasattr(eng, "sync_optimizer"):
             eng.sync_optimizer()
@@ -379,6 +379,9 @@ class Trainer:
                         if isinstance(m, LoraLinear) and hasattr(m, "weight"):
                             m.merge()
                             touched = True
+                        elif isinstance(getattr(m, "lora", None), ExpertsLoRA):
+                            m.lora.merge_into(m)
+                            touched = True
                 if touched:
                     for g in unit.groups:
                         s0, s1 = g.shard_range()
@@ -390,7 +393,7 @@ class Trainer:
                         # trainable group: only lora_B restarts (at zero); every other trainable
                         # parameter (lora_A, unfrozen weights) keeps its fp32 master value
                         for i, a, b in g.param_segments_in_shard():
-                            if ".lora_B." in g.named_params[i][0]:
+                            if ".lora_B." in g.named_params[i][0] or g.named_params[i][0].endswith("_lora_B"):
                                 g.master[a:b].zero_()
                                 if g.shard_lp is not g.master:
                                     g.shard_lp[a:b].zero_()
