@@ -99,3 +99,55 @@ def test_r3_staging_benchmark_runs(capsys):
     from xorl_b200.utils.r3_staging_bench import main
     out = main(["--datums", "6", "--tokens", "128", "--layers", "3", "--top-k", "2", "--pack-len", "512"])
     assert out["micro_batches"] >= 2 and out["payload_mb"] > 0 and out["store_put_s"] > 0
+
+
+def test_supervisor_tears_the_service_down_when_a_member_dies(tmp_path):
+    """Two children; one exits with code 3: the other (which ignores nothing) is terminated, the
+    whole process group with it, and the supervisor returns 3."""
+    import sys
+    import time
+    from xorl_b200.server.supervisor import ChildSpec, Supervisor
+    marker = tmp_path / "ready"
+    sleeper = [sys.executable, "-c", "import time, subprocess, sys\n"
+               "p = subprocess.Popen([sys.executable, '-c', 'import time; time.sleep(600)'])\n"
+               f"open({str(marker)!r}, 'w').write(str(p.pid))\ntime.sleep(600)"]
+    dier = [sys.executable, "-c", "import time, sys; time.sleep(1.5); sys.exit(3)"]
+    sup = Supervisor([ChildSpec("workers", sleeper, ready=lambda: marker.exists()),
+                      ChildSpec("api", dier)], poll_interval=0.05, grace=3.0, log=lambda m: None)
+    t0 = time.time()
+    assert sup.run(install_signal_handlers=False) == 3
+    assert time.time() - t0 < 15 and sup.first_exit == "api"
+    assert any("workers ready" in e for e in sup.events)
+    for c in sup.children:
+        assert c.proc.poll() is not None
+    grandchild = int(marker.read_text())
+    time.sleep(0.3)
+    try:                                   # the worker's own child (same process group) is gone too
+        os.kill(grandchild, 0)
+        alive = os.path.exists(f"/proc/{grandchild}") and "Z" not in open(f"/proc/{grandchild}/stat").read().split()[2]
+    except ProcessLookupError:
+        alive = False
+    assert not alive
+
+
+def test_supervisor_stops_on_request_and_on_unanswered_probes(tmp_path):
+    import sys
+    import threading
+    import time
+    from xorl_b200.server.supervisor import ChildSpec, Supervisor
+    sleeper = [sys.executable, "-c", "import time; time.sleep(600)"]
+    # a member that never becomes ready
+    sup = Supervisor([ChildSpec("workers", sleeper, ready=lambda: False, ready_timeout=1.0)],
+                     poll_interval=0.05, grace=2.0, log=lambda m: None)
+    assert sup.run(install_signal_handlers=False) == 1 and sup.children[0].proc.poll() is not None
+    # a member whose liveness probe stops answering
+    state = {"ok": True}
+    sup = Supervisor([ChildSpec("api", sleeper, alive=lambda: state["ok"])], poll_interval=0.05, grace=2.0,
+                     liveness_timeout=0.5, log=lambda m: None)
+    threading.Timer(0.7, lambda: state.update(ok=False)).start()
+    assert sup.run(install_signal_handlers=False) == 1
+    assert any("unresponsive" in e for e in sup.events)
+    # an orderly stop request
+    sup = Supervisor([ChildSpec("api", sleeper)], poll_interval=0.05, grace=2.0, log=lambda m: None)
+    threading.Timer(0.5, sup.request_stop).start()
+    assert sup.run(install_signal_handlers=False) == 0 and sup.children[0].proc.poll() is not None

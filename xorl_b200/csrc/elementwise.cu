@@ -14,8 +14,10 @@ __device__ __forceinline__ float round_bf16(float x) {
 // gu: [T, 2I] (gate = [:, :I], up = [:, I:]) -> out [T, I]
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
-                  long long T, int I, int two_round) {
+                  long long T, int I, int two_round, const int* __restrict__ row_limit) {
   const int vec_per_row = I >> 3;
+  // row_limit (optional, device memory): only the first *row_limit rows hold data
+  if (row_limit != nullptr) T = min(T, (long long)*row_limit);
   const long long total = T * vec_per_row;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
@@ -39,8 +41,9 @@ swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restric
 // dgu[:, :I] = dout * up * dsilu(gate);  dgu[:, I:] = dout * silu(gate)
 __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gu,
-                  __nv_bfloat16* __restrict__ dgu, long long T, int I) {
+                  __nv_bfloat16* __restrict__ dgu, long long T, int I, const int* __restrict__ row_limit) {
   const int vec_per_row = I >> 3;
+  if (row_limit != nullptr) T = min(T, (long long)*row_limit);
   const long long total = T * vec_per_row;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
@@ -143,7 +146,27 @@ XB_API int xb_swiglu_fwd(const void* gu, void* out, long long T, int I, int two_
   if (I % 8) return -1;
   if (T <= 0) return 0;
   swiglu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, two_round);
+      (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, two_round, nullptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Variants for buffers sized for the worst case: only the first *row_limit rows (an int in device
+// memory, e.g. the end of the last expert segment) are processed; the grid is sized for T rows.
+XB_API int xb_swiglu_fwd_rows(const void* gu, void* out, long long T, int I, int two_round, const int* row_limit,
+                              void* stream) {
+  if (I % 8) return -1;
+  if (T <= 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I, two_round, row_limit);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+XB_API int xb_swiglu_bwd_rows(const void* dout, const void* gu, void* dgu, long long T, int I, const int* row_limit,
+                              void* stream) {
+  if (I % 8) return -1;
+  if (T <= 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)dout, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, T, I, row_limit);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -152,7 +175,7 @@ XB_API int xb_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long 
   if (I % 8) return -1;
   if (T <= 0) return 0;
   swiglu_bwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)dout, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, T, I);
+      (const __nv_bfloat16*)dout, (const __nv_bfloat16*)gu, (__nv_bfloat16*)dgu, T, I, nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

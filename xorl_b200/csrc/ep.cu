@@ -101,7 +101,13 @@ ep_push_rows_kernel(const uint4* __restrict__ src, long long src_ld_vec, const i
     const int row = dest_row[i];
     const uint4* s = src + (size_t)(src_row ? src_row[i] : i) * src_ld_vec;
     uint4* d = reinterpret_cast<uint4*>(dsts.p[dr]) + (size_t)row * dst_ld_vec;
-    for (int v = lane; v < row_vec; v += 32) d[v] = s[v];
+    // four 16-byte loads in flight per lane before the (posted) peer stores
+    int v = lane;
+    for (; v + 96 < row_vec; v += 128) {
+      const uint4 a = s[v], b = s[v + 32], c = s[v + 64], e = s[v + 96];
+      d[v] = a; d[v + 32] = b; d[v + 64] = c; d[v + 96] = e;
+    }
+    for (; v < row_vec; v += 32) d[v] = s[v];
     if (metas.p[0] != nullptr && lane == 0) {
       const int t = tag ? tag[i] : i;
       reinterpret_cast<int*>(metas.p[dr])[row] = t | (rank << tag_rank_shift);
@@ -292,7 +298,10 @@ XB_API int xb_ep_push_rows(const void* src, long long src_ld_bytes, const int* s
   for (int i = 0; i < MAX_RANKS; ++i) mt.p[i] = nullptr;
   if (meta_ptrs) mt = make_ptrs(meta_ptrs, n);
   int* counter = reinterpret_cast<int*>(fl.p[rank]) + counter_slot;
-  const int grid = 64;
+  // nothing else runs while a layer waits for its rows: use every SM (two CTAs each)
+  int grid = xb_sm_count() * 2;
+  if (grid > (n_items + 7) / 8) grid = (n_items + 7) / 8;
+  if (grid < 1) grid = 1;
   ep_push_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
       (const uint4*)src, src_ld_bytes / 16, src_row, dest_rank, dest_row, tag, tag_rank_shift, n_items,
       row_bytes / 16, make_ptrs(dst_ptrs, n), dst_ld_bytes / 16, mt, fl, slot, counter, rank, n, epoch);

@@ -346,9 +346,10 @@ __device__ __forceinline__ uint8_t pow2_scale(float amax, float& inv) {
 // (one 16-byte load, one 8-byte store), the block maximum is taken over 16 lanes.
 __global__ void __launch_bounds__(256)
 quant_mx_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
-                     uint8_t* __restrict__ sf, int sf_ld, long long M, int KB) {
+                     uint8_t* __restrict__ sf, int sf_ld, long long M, int KB, const int* __restrict__ row_limit) {
   const long long row = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
+  if (row_limit != nullptr) M = min(M, (long long)*row_limit);
   if (row >= M) return;
   const __nv_bfloat16* xr = x + row * ldx;
   uint8_t* qr = q + row * ldq;
@@ -476,8 +477,17 @@ XB_API int xb_grouped_gemm_mx_rows(const void* A, const void* sfa, const void* B
 
 // x bf16 [M, K] (row stride ldx elements) -> q e4m3 [M, K] (row stride ldq bytes) + UE8M0 scales [M, sf_ld]
 // (bytes K/128 .. sf_ld - 1 of a scale row are left as they are).
+XB_API int xb_quant_mx_rows_lim(const void* x, long long ldx, void* q, long long ldq, void* sf, int sf_ld,
+                                long long M, int K, const int* row_limit, void* stream);
+
 XB_API int xb_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq, void* sf, int sf_ld, long long M,
                             int K, void* stream) {
+  return xb_quant_mx_rows_lim(x, ldx, q, ldq, sf, sf_ld, M, K, nullptr, stream);
+}
+
+// row_limit (optional, device memory): only the first *row_limit rows are quantised.
+XB_API int xb_quant_mx_rows_lim(const void* x, long long ldx, void* q, long long ldq, void* sf, int sf_ld,
+                                long long M, int K, const int* row_limit, void* stream) {
   if (M <= 0) return 0;
   if ((K % 128) || (ldx % 8) || (ldq % 8) || sf_ld < K / 128 || (reinterpret_cast<uintptr_t>(x) % 16) ||
       (reinterpret_cast<uintptr_t>(q) % 8))
@@ -485,7 +495,7 @@ XB_API int xb_quant_mx_rows(const void* x, long long ldx, void* q, long long ldq
   const int KB = K / 128;
   const long long blocks = (M + 7) / 8;
   xb_ggemm_mx::quant_mx_rows_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (uint8_t*)sf, sf_ld, M, KB);
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (uint8_t*)sf, sf_ld, M, KB, row_limit);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -39,6 +39,9 @@ _SIGNATURES = {
     "xb_qk_norm_rope_bwd": [P, P, P, L, P, L, P, P, P, P, P, P, L, P, P, P, I, I, I, I, I, I, P],
     "xb_swiglu_fwd": [P, P, L, I, I, P],
     "xb_swiglu_bwd": [P, P, P, L, I, P],
+    "xb_swiglu_fwd_rows": [P, P, L, I, I, P, P],
+    "xb_swiglu_bwd_rows": [P, P, P, L, I, P, P],
+    "xb_quant_mx_rows_lim": [P, L, P, L, P, I, L, I, P, P],
     "xb_embedding_fwd": [P, P, P, I, I, L, P],
     "xb_embedding_bwd": [P, P, P, I, I, I, L, P],
     "xb_add_bf16": [P, P, P, L, P],

@@ -276,6 +276,9 @@ class _Scratch:
         self.dest_rank = torch.empty(S, **i32)
         self.dest_row = torch.empty(S, **i32)
         self.seg = torch.zeros(El + 1, **i32)
+        # seg[El] = end of the last expert segment: elementwise kernels over the worst-case sized
+        # buffers stop there
+        self.row_limit_ptr = self.seg.data_ptr() + 4 * El
         self.tot = torch.zeros(El, **i32)
         self.overflow = torch.zeros(1, **i32)
         self.ret_rank = torch.empty(cap, **i32)
@@ -315,8 +318,9 @@ def _rows_gemm(ws, sc, a, a_cols, w, out, n_out, b_mn: int, fp8, qe_w, qe_sf, st
     """out[rows of e, :n_out] = a[rows of e, :a_cols] @ op(w[e]) over the local expert segments."""
     lib = ws.lib
     if fp8:
-        _lib.check(lib.xb_quant_mx_rows(a.data_ptr(), a.stride(0), sc.q.data_ptr(), sc.q.stride(0), sc.sf.data_ptr(),
-                                        sc.sf.stride(0), ws.cap, a_cols, st), "xb_quant_mx_rows")
+        _lib.check(lib.xb_quant_mx_rows_lim(a.data_ptr(), a.stride(0), sc.q.data_ptr(), sc.q.stride(0),
+                                            sc.sf.data_ptr(), sc.sf.stride(0), ws.cap, a_cols, sc.row_limit_ptr, st),
+                   "xb_quant_mx_rows_lim")
         _lib.check(lib.xb_grouped_gemm_mx_rows(sc.q.data_ptr(), sc.sf.data_ptr(), qe_w.data_ptr(), qe_sf.data_ptr(),
                                                out.data_ptr(), sc.seg.data_ptr(), ws.El, ws.cap, n_out, a_cols,
                                                sc.q.stride(0), out.stride(0), sc.sf.stride(0), qe_sf.stride(1), st),
@@ -376,7 +380,8 @@ class _FusedEPMoE(torch.autograd.Function):
         PhaseTimes.add("fwd_dispatch", t1, t2)
         _rows_gemm(ws, sc, recv, H, gate_up, sc.h, I2, 1, fp8, None if qg is None else qg.q_nk,
                    None if qg is None else qg.sf_nk, st)
-        _lib.check(lib.xb_swiglu_fwd(sc.h.data_ptr(), sc.a.data_ptr(), ws.cap, I, 1, st), "xb_swiglu_fwd")
+        _lib.check(lib.xb_swiglu_fwd_rows(sc.h.data_ptr(), sc.a.data_ptr(), ws.cap, I, 1, sc.row_limit_ptr, st),
+                   "xb_swiglu_fwd_rows")
         _rows_gemm(ws, sc, sc.a, I, down, sc.y, H, 1, fp8, None if qd is None else qd.q_nk,
                    None if qd is None else qd.sf_nk, st)
         # ---- return -----------------------------------------------------------------------------
@@ -447,7 +452,8 @@ class _FusedEPMoE(torch.autograd.Function):
                 mark_written(w)
             d_down = None if tgt is not None else dwt
         # SwiGLU backward in place: h becomes dh
-        _lib.check(lib.xb_swiglu_bwd(sc.da.data_ptr(), sc.h.data_ptr(), sc.h.data_ptr(), ws.cap, I, st), "xb_swiglu_bwd")
+        _lib.check(lib.xb_swiglu_bwd_rows(sc.da.data_ptr(), sc.h.data_ptr(), sc.h.data_ptr(), ws.cap, I,
+                                          sc.row_limit_ptr, st), "xb_swiglu_bwd_rows")
         tgt, fresh = grad_target(gate_up)
         dwt = tgt if tgt is not None else torch.empty_like(gate_up)
         _lib.check(lib.xb_grouped_gemm_wgrad(recv_f.data_ptr(), sc.h.data_ptr(), dwt.data_ptr(), sc.seg.data_ptr(), El,

@@ -1,5 +1,7 @@
 """Starts the training service.
 
+``--mode launch`` starts the worker fleet (torchrun) and the API process as children of a supervisor
+(``server/supervisor.py``) that tears the service down when a member dies.
 ``--mode auto`` builds the worker in this process group: under ``torchrun`` every rank builds the
 trainer; rank 0 additionally runs the REST server with a backend that broadcasts each command to
 the other ranks, which sit in ``RunnerDispatcher.worker_loop``.  ``--mode connect`` starts only the
@@ -174,7 +176,10 @@ def build_local_backend(sargs: ServerArguments):
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description="xorl_b200 training service")
-    ap.add_argument("--mode", choices=["auto", "connect", "worker"], default="auto")
+    ap.add_argument("--mode", choices=["auto", "connect", "worker", "launch"], default="auto")
+    ap.add_argument("--nproc", type=int, default=0,
+                    help="--mode launch: ranks of the worker fleet (default: all visible GPUs, at least 1)")
+    ap.add_argument("--master-port", type=int, default=29400)
     ap.add_argument("--config", required=True)
     ap.add_argument("--api-host", default=None)
     ap.add_argument("--api-port", type=int, default=None)
@@ -188,6 +193,16 @@ def main(argv=None) -> None:
     if ns.worker_address:
         sargs.worker_bind_address = ns.worker_address
 
+    if ns.mode == "launch":
+        # separate processes under a supervisor: torchrun worker fleet + API process; when one of them
+        # exits or stops answering, the other is torn down and the exit code is passed on
+        import sys
+        import torch
+        from .supervisor import Supervisor, service_children
+        nproc = ns.nproc or max(1, torch.cuda.device_count())
+        sup = Supervisor(service_children(ns.config, nproc, sargs.api_host, sargs.api_port,
+                                          sargs.worker_bind_address, ns.master_port))
+        sys.exit(sup.run())
     if ns.mode == "connect":
         backend: Backend = RemoteBackend(sargs.worker_bind_address)
         dp = 1
