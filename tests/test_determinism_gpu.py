@@ -111,3 +111,24 @@ def test_grouped_gemm_is_reproducible():
         y.backward(go)
         return [y.detach(), bb.grad, ww.grad]
     _twice(run)
+
+
+def test_batch_invariant_gemm_rows_do_not_depend_on_the_batch():
+    """In batch-invariant mode a row of x @ W^T has the same bits whether it is computed alone, in a
+    batch of 300 rows or as part of 4096 rows (different tile counts, waves and tail handling)."""
+    from xorl_b200.ops import gemm as G
+    torch.manual_seed(0)
+    x = torch.randn(4096, 1024, device="cuda").bfloat16()
+    w = torch.randn(2560, 1024, device="cuda").bfloat16()
+    prev = G.set_batch_invariant(True)
+    try:
+        full = G.gemm(x, w)
+        for rows in (1, 300, 640, 2048):
+            part = G.gemm(x[:rows].contiguous(), w)
+            assert torch.equal(part, full[:rows]), rows
+        mid = G.gemm(x[1000:1513].contiguous(), w)
+        assert torch.equal(mid, full[1000:1513])
+    finally:
+        G.set_batch_invariant(prev)
+    ref = (x.float() @ w.float().t())
+    assert (full.float() - ref).abs().max() <= 0.02 * ref.abs().max()

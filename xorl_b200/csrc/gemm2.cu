@@ -341,6 +341,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   }
 }
 
+// Batch-invariant mode: every output tile is a full 512 x 256 pair tile issued with the same MMA
+// shapes whatever M and N are (the tiles of a partial last wave are not cut), so the value of an
+// output row does not depend on how many other rows the call carries.
+static int g_batch_invariant = 0;
+
 static int resident_pairs_cache[64] = {0};
 
 template <bool A_MN, bool B_MN>
@@ -376,12 +381,23 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
   const int pairs_max = resident_pairs<A_MN, B_MN>();
   if (pairs_max <= 0) return -10;
   plan_items(p, pairs_max, true);
+  if (g_batch_invariant) {
+    p.full_items = p.num_m_blocks * p.num_n_blocks;
+    p.split_m = p.split_n = 1;
+    p.num_items = p.full_items;
+  }
   const int pairs = p.num_items < pairs_max ? p.num_items : pairs_max;
   gemm2_kernel<A_MN, B_MN><<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, tb64, tc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 }  // namespace xb_gemm2
+
+XB_API int xb_gemm_set_batch_invariant(int on) {
+  const int prev = xb_gemm2::g_batch_invariant;
+  xb_gemm2::g_batch_invariant = on ? 1 : 0;
+  return prev;
+}
 
 // Same contract as xb_gemm_bf16.
 XB_API int xb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda,

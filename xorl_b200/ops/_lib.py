@@ -30,6 +30,7 @@ _SIGNATURES = {
     "xb_status_read": [P, I],
     "xb_device_sm_count": [],
     "xb_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, P],
+    "xb_gemm_set_batch_invariant": [I],
     "xb_gemm_bf16_pair": [P, P, P, I, I, I, L, L, L, I, I, I, I, P],
     "xb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, P],
     "xb_rmsnorm_bwd_partial_rows": [I],

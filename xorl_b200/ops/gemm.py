@@ -33,6 +33,25 @@ def launch_count() -> int:
     return _launches
 
 
+_BATCH_INVARIANT = False
+
+
+def set_batch_invariant(on: bool) -> bool:
+    """Batch-invariant GEMMs: the value of an output row no longer depends on how many rows the
+    call carries (src/xorl/ops/batch_invariant_ops.py:177-300 gives the same guarantee with a
+    persistent kernel of fixed tile order).  Here every element of C is owned by one tile whose K
+    loop runs in a fixed order; the mode removes the two things that vary with the problem size:
+    the choice between the single-CTA and the CTA-pair kernel (always the pair kernel) and the
+    cutting of the tiles of a partial last wave (always whole 512 x 256 tiles).  Returns the
+    previous setting.  Also settable with ``XORL_B200_BATCH_INVARIANT=1``."""
+    global _BATCH_INVARIANT
+    prev = _BATCH_INVARIANT
+    _BATCH_INVARIANT = bool(on)
+    if _lib.have_cuda_lib() and torch.cuda.is_available():
+        _lib.cuda_lib().xb_gemm_set_batch_invariant(int(_BATCH_INVARIANT))
+    return prev
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
          accumulate: bool = False) -> torch.Tensor:
@@ -76,7 +95,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     lib = _lib.cuda_lib()
     args = (a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
             out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate))
-    if _VARIANT == "pair" and M >= 384:
+    if _BATCH_INVARIANT or (_VARIANT == "pair" and M >= 384):
         rc = lib.xb_gemm_bf16_pair(*args, _lib.stream_ptr())
     else:
         rc = lib.xb_gemm_bf16(*args, _lib.stream_ptr())
@@ -199,3 +218,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
     if bias is not None:
         y = y + bias
     return y
+
+
+if os.environ.get("XORL_B200_BATCH_INVARIANT", "0") == "1":
+    set_batch_invariant(True)
