@@ -273,7 +273,85 @@ def bench_grouped(a) -> Dict:
     return r
 
 
+def bench_ce(a) -> Dict:
+    """Cross-entropy over one chunk of logits (fp32 statistics, gradient written in place)."""
+    from ..ops.loss import ce_chunk_
+    V = a.n
+    logits = torch.randn(a.tokens, V, device="cuda").bfloat16()
+    labels = torch.randint(0, V, (a.tokens,), device="cuda")
+    ms = _time(lambda: ce_chunk_(logits, labels, 1.0 / a.tokens, True), a.warmup, a.iters, a.flush)
+    return {"kernel": "cross_entropy", "tokens": a.tokens, "vocab": V, "ms": ms,
+            "gbs": a.tokens * V * 2 * 2 / ms / 1e6}          # logits read once, gradient written once
+
+
+def bench_route(a) -> Dict:
+    """Router: fp32 logits -> softmax, top-k, renormalised weights."""
+    from ..ops.moe import expert_histogram, topk_route
+    logits = torch.randn(a.tokens, a.experts, device="cuda")
+    ms = _time(lambda: topk_route(logits, 8, True), a.warmup, a.iters, a.flush)
+    idx = topk_route(logits, 8, True)[1]
+    ms_h = _time(lambda: expert_histogram(idx, a.experts), a.warmup, a.iters, a.flush)
+    return {"kernel": "moe_route", "tokens": a.tokens, "experts": a.experts, "k": 8, "ms": ms,
+            "gbs": a.tokens * a.experts * 4 * 2 / ms / 1e6, "histogram_ms": ms_h}
+
+
+def bench_qk_norm_rope(a) -> Dict:
+    """Per-head qk RMSNorm + rotary embedding on the fused projection output, forward only."""
+    from ..ops import _lib
+    Hq, Hkv, D = a.heads, a.kv_heads, 128
+    T = a.tokens
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    wq, wk = torch.ones(D, device="cuda").bfloat16(), torch.ones(D, device="cuda").bfloat16()
+    pos = torch.arange(T, device="cuda")
+    inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = pos[:, None].float() * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    qk = torch.empty(T, (Hq + Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.empty(T, Hq + Hkv, device="cuda", dtype=torch.float32)
+    lib = _lib.cuda_lib()
+
+    def run():
+        _lib.check(lib.xb_qk_norm_rope_fwd(qkv.data_ptr(), qkv.stride(0), wq.data_ptr(), wk.data_ptr(), cos.data_ptr(),
+                                           sin.data_ptr(), qk.data_ptr(), qk.stride(0), rstd.data_ptr(), T, Hq, Hkv, D,
+                                           1e-6, 1, _lib.stream_ptr()), "xb_qk_norm_rope_fwd")
+    try:
+        ms = _time(run, a.warmup, a.iters, a.flush)
+    except Exception as e:  # noqa: BLE001
+        return {"kernel": "qk_norm_rope_fwd", "error": str(e)[:200]}
+    return {"kernel": "qk_norm_rope_fwd", "tokens": T, "heads": Hq, "kv_heads": Hkv, "ms": ms,
+            "gbs": T * (Hq + Hkv) * D * 2 * 2 / ms / 1e6}
+
+
+def bench_permute(a) -> Dict:
+    """MoE row gather (token -> expert-sorted buffer) and weighted combine (k rows -> token)."""
+    from ..ops import moe as moe_ops
+    T, k, H, E = a.tokens, 8, a.hidden, a.experts
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(64)]).repeat(T // 64 + 1, 1)[:T]
+    dest, seg, _ = moe_ops.aligned_sort_indices(idx.reshape(-1), E)
+    rows = moe_ops.buffer_rows(T * k, E)
+    tok = moe_ops.token_of_row(dest, rows, k)
+    w = torch.rand(T, k, device="cuda")
+    ms_g = _time(lambda: moe_ops._gather_rows(x, tok, rows), a.warmup, a.iters, a.flush)
+    buf = moe_ops._gather_rows(x, tok, rows)
+    d2 = dest.view(T, k)
+    ms_c = _time(lambda: moe_ops._gather_sum(buf, d2, w), a.warmup, a.iters, a.flush)
+    return {"kernel": "moe_permute", "tokens": T, "k": k, "hidden": H, "gather_ms": ms_g,
+            "gather_gbs": (T * k * H * 2 * 2) / ms_g / 1e6, "combine_ms": ms_c,
+            "combine_gbs": (T * k * H * 2 + T * H * 2) / ms_c / 1e6}
+
+
+def bench_mx_quant(a) -> Dict:
+    """Row quantiser of the block-scaled fp8 path (bf16 -> e4m3 + UE8M0 1 x 128 scales)."""
+    from ..ops import fp8_grouped as fg
+    x = torch.randn(a.m, a.k, device="cuda").bfloat16()
+    ms = _time(lambda: fg.quantize_rows(x), a.warmup, a.iters, a.flush)
+    return {"kernel": "quant_mx_rows", "m": a.m, "k": a.k, "ms": ms, "gbs": a.m * a.k * 3 / ms / 1e6}
+
+
 BENCHES["grouped"] = bench_grouped
+BENCHES.update(ce=bench_ce, route=bench_route, qk_norm_rope=bench_qk_norm_rope, permute=bench_permute,
+               mx_quant=bench_mx_quant)
 
 
 def main(argv=None) -> None:
