@@ -13,7 +13,7 @@ import os
 import torch
 
 from . import _lib
-from .grad_sink import current_wgrad_store, grad_target, mark_written
+from .grad_sink import current_wgrad_store, grad_target, mark_written, note_wgrad_issued, wgrad_stream
 
 _launches = 0
 # "pair": CTA-pair kernel (tcgen05 cta_group::2, 512x256 pair tiles, csrc/gemm2.cu);
@@ -172,7 +172,17 @@ def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, w: torch.Tensor):
                      gemm(a, b, a_mn=True, b_mn=True, out=o, accumulate=acc))
         return None
     if tgt is not None:
-        gemm(dy2, x2, a_mn=True, b_mn=True, out=tgt, accumulate=not fresh)
+        side = wgrad_stream(dy2.device) if dy2.is_cuda else None
+        if side is not None:
+            # overlap with the input-gradient GEMM that follows on the main stream
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=tgt, accumulate=not fresh)
+            dy2.record_stream(side)
+            x2.record_stream(side)
+            note_wgrad_issued()
+        else:
+            gemm(dy2, x2, a_mn=True, b_mn=True, out=tgt, accumulate=not fresh)
         mark_written(w)
         return None
     return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
@@ -201,10 +211,12 @@ class _Linear(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = dw = None
-        if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w, b_mn=True).reshape(ctx.x_shape)
+        # the weight gradient is issued first (on its side stream when it goes to an engine buffer), the
+        # input gradient follows on the main stream: the two persistent kernels fill each other's tails
         if ctx.needs_input_grad[1]:
             dw = weight_grad(dy2, x2, w)
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).reshape(ctx.x_shape)
         return dx, dw
 
 

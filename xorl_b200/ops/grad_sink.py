@@ -61,3 +61,41 @@ class defer_wgrad:
 
 def current_wgrad_store():
     return _wgrad_store
+
+
+# ---- weight gradients on a side stream --------------------------------------------------------
+# A linear layer's two backward GEMMs (input gradient and weight gradient) are independent.  Both are
+# persistent kernels that leave part of the GPU idle during their last, partial wave of tiles; issued
+# on two streams, the CTAs of one start on the SMs the other's tail has freed.  The input gradient
+# stays on the main stream (the next layer's backward waits for it); the weight gradient goes to this
+# stream, and whoever consumes the gradient buffers calls ``join_wgrad_stream`` first.
+import os as _os
+
+_WGRAD_OVERLAP = _os.environ.get("XORL_B200_WGRAD_STREAM", "1") == "1"
+_wgrad_stream = {}
+_wgrad_pending = False
+
+
+def wgrad_stream(device: torch.device):
+    """The side stream for weight-gradient GEMMs on ``device`` (None when the overlap is off)."""
+    if not _WGRAD_OVERLAP or device.type != "cuda":
+        return None
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _wgrad_stream.get(key)
+    if st is None:
+        st = _wgrad_stream[key] = torch.cuda.Stream(device)
+    return st
+
+
+def note_wgrad_issued() -> None:
+    global _wgrad_pending
+    _wgrad_pending = True
+
+
+def join_wgrad_stream() -> None:
+    """Makes the current stream wait for every weight-gradient GEMM issued on the side stream."""
+    global _wgrad_pending
+    if _wgrad_pending:
+        for st in _wgrad_stream.values():
+            torch.cuda.current_stream().wait_stream(st)
+        _wgrad_pending = False

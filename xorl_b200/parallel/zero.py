@@ -750,6 +750,9 @@ class Zero3Engine:
                 tensors.append(aux)
                 grads.append(torch.ones_like(aux))
             torch.autograd.backward(tensors, grads)
+            if self.is_cuda:
+                from ..ops.grad_sink import join_wgrad_stream
+                join_wgrad_stream()          # weight-gradient GEMMs issued on their side stream
             dacts = tuple(a.grad if a is not None else None for a in ins)
             del ins, outs, pairs, tensors, grads
             if defer_reduce:
@@ -796,6 +799,9 @@ class Zero3Engine:
                 if extra is not None:
                     total = total + extra
             total.backward()
+        if self.is_cuda:
+            from ..ops.grad_sink import join_wgrad_stream
+            join_wgrad_stream()
         return loss.detach(), tuple(a.grad if a is not None else None for a in head_in)
 
     def embed_backward(self, input_ids, ctx, dacts) -> None:
@@ -804,6 +810,9 @@ class Zero3Engine:
         pairs = [(o, d) for o, d in zip(emb, dacts) if o is not None and d is not None]
         if pairs and pairs[0][0].requires_grad:
             torch.autograd.backward([o for o, _ in pairs], [d for _, d in pairs])
+        if self.is_cuda:
+            from ..ops.grad_sink import join_wgrad_stream
+            join_wgrad_stream()
 
     def forward_backward(self, input_ids: torch.Tensor, labels: torch.Tensor, *,
                          position_ids=None, cu_seqlens=None, grad_scale: float = 1.0,
