@@ -3,13 +3,17 @@
 * ``token_normalised_loss`` -- a loss that is a sum over local tokens divided by the global token
   count, with the matching backward (src/xorl/distributed/gradient_accumulate_loss.py:7-64).
 * ``synchronize_micro_batch_padding`` -- pad every rank's micro-batch to the widest one of the
-  group by growing the trailing padding document, so collectives inside layers (EP, PP p2p) see
-  equal shapes (src/xorl/distributed/sync_padding.py:38-146; not applied under context parallelism).
+  group by growing the trailing padding document (src/xorl/distributed/sync_padding.py:38-146; not
+  applied under context parallelism).  No collective of this package needs equal shapes (flat
+  parameter shards, capacity-sized expert workspaces, negotiated pipeline messages), so the trainer
+  applies it only on request (``XORL_B200_SYNC_PADDING=1``), to equalise per-rank work.
 * ``stochastic_bf16_all_to_all_reduce_scatter`` -- gradient reduce-scatter with bf16 on the wire:
   each rank rounds its fp32 gradient stochastically to bf16, exchanges slices with all-to-all and
   sums the received slices in fp32 (src/xorl/distributed/fsdp2/bf16_a2a_reduce.py:64-114).
-* ``sync_replicated_grads`` -- all-reduce of gradients of parameters replicated over a group
-  (src/xorl/distributed/ep_gradients.py).
+
+Gradients of parameters that the reference replicates over the expert-parallel group (router, norms,
+attention: src/xorl/distributed/ep_gradients.py) need no extra all-reduce here: every non-expert
+parameter is ZeRO-sharded over all data ranks, so its reduce-scatter already sums over them.
 """
 from __future__ import annotations
 
@@ -106,37 +110,3 @@ def stochastic_bf16_all_to_all_reduce_scatter(grad: torch.Tensor, out_shard: tor
         out_shard.add_(total)
     else:
         out_shard.copy_(total)
-
-
-def sync_replicated_grads(params: Iterable[torch.nn.Parameter], group, average: bool = False,
-                          bucket_bytes: int = 64 << 20) -> int:
-    """All-reduces ``p.grad`` of parameters that are replicated over ``group`` in flat buckets.
-    Returns the number of buckets."""
-    if group is None or not dist.is_initialized() or dist.get_world_size(group) == 1:
-        return 0
-    bucket, size, n = [], 0, 0
-
-    def flush():
-        nonlocal bucket, size, n
-        if not bucket:
-            return
-        flat = torch.cat([g.reshape(-1).float() for g in bucket])
-        dist.all_reduce(flat, group=group)
-        if average:
-            flat.div_(dist.get_world_size(group))
-        off = 0
-        for g in bucket:
-            g.copy_(flat[off:off + g.numel()].view_as(g))
-            off += g.numel()
-        bucket, size = [], 0
-        n += 1
-
-    for p in params:
-        if p.grad is None:
-            continue
-        bucket.append(p.grad)
-        size += p.grad.numel() * 4
-        if size >= bucket_bytes:
-            flush()
-    flush()
-    return n

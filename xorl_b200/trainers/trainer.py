@@ -23,6 +23,7 @@ from ..arguments import Arguments, save_args
 from ..data import build_dataloader, prepare_datasets
 from ..models import build_model_config, build_model
 from ..optim import build_lr_scheduler, build_optimizer
+from ..parallel.dist_utils import synchronize_micro_batch_padding
 from ..parallel.state import get_parallel_state, init_parallel_state, process_group_timeout
 from ..parallel.zero import Zero3Engine
 from ..utils.diagnostics import nvtx_range
@@ -252,6 +253,8 @@ class Trainer:
         self.sink = MetricsSink(t, self.ps.rank)
         self.scan_nonfinite = nonfinite_scan_enabled()
         self.watchdog = None
+        # equal micro-batch lengths over the data-parallel group; no collective needs it, it only balances work
+        self._sync_padding = os.environ.get("XORL_B200_SYNC_PADDING", "0") == "1" and self.ps.ulysses_size * self.ps.ringattn_size == 1
         if self.ps.world_size > 1 and dist.is_initialized() \
                 and os.environ.get("XORL_RANK_WATCHDOG", "1") not in ("0", "false"):
             store = dist.distributed_c10d._get_default_store()
@@ -438,6 +441,9 @@ class Trainer:
                 if self.watchdog is not None:
                     self.watchdog.check()           # a dead peer is noticed before the next launch
                 t0 = time.time()
+                if self._sync_padding:
+                    micro_batches = synchronize_micro_batch_padding(
+                        micro_batches, self.ps.group("dp"), multiple_of=max(1, self.args.data.pad_to_multiple_of or 1))
                 try:
                     with nvtx_range("train_step"):
                         out = self.train_step(micro_batches)
