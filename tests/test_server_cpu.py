@@ -64,6 +64,34 @@ def test_packing_and_dp_balance():
     assert mb["num_valid_tokens"] == 3 and mb["position_ids"][:5].tolist() == [0, 1, 2, 0, 1]
 
 
+def test_balanced_dp_packer_and_oversized_policy():
+    from xorl_b200.server.orchestrator import RequestProcessor
+    lengths = [900, 850, 400, 380, 300, 250, 120, 100]
+    bins = packing.pack_balanced_dp(lengths, 1000, dp=4)
+    assert len(bins) % 4 == 0 and all(bins)                       # k*dp bins, none empty: no dummy batches
+    assert sorted(i for b in bins for i in b) == list(range(8))
+    loads = [sum(lengths[i] for i in b) for b in bins]
+    assert max(loads) <= 1000 and max(loads) - min(loads) <= 300
+    plan = RequestProcessor(4, 1000, "balanced_dp").plan([{"tokens": [0] * n} for n in lengths])
+    assert all(len(r) == 1 and r[0] for r in plan)
+    # fewer samples than ranks: best-fit, the dispatcher pads with dummy batches
+    assert packing.pack_balanced_dp([10, 20], 100, dp=4) == packing.pack_best_fit([10, 20], 100)
+    datums = [{"tokens": [1, 2, 3], "weights": [1.0, 1.0, 0.0]}, {"tokens": list(range(9)), "weights": [1.0] * 9,
+                                                                   "tag": "x"}]
+    with pytest.raises(ValueError, match="datum 1 has 9 tokens"):
+        packing.apply_oversized_policy(datums, 4, "error")
+    kept, origin = packing.apply_oversized_policy(datums, 4, "skip")
+    assert origin == [0] and kept[0] is datums[0]
+    kept, origin = packing.apply_oversized_policy(datums, 4, "truncate")
+    assert origin == [0, 1] and kept[1]["tokens"] == [0, 1, 2, 3] and len(kept[1]["weights"]) == 4 and kept[1]["tag"] == "x"
+    rp = RequestProcessor(1, 4, "sequential", on_oversized="skip")
+    kept, origin = rp.admit(datums)
+    res = rp.restore_order({"loss": 1.0, "logprobs": [[0.1, 0.2, 0.3]]}, origin, 2)
+    assert res["logprobs"] == [[0.1, 0.2, 0.3], []] and res["skipped_datums"] == [1]
+    with pytest.raises(ValueError):
+        RequestProcessor(1, 4, "unknown")
+
+
 def test_seq_id_policy_reorders():
     p = SeqIdAwareFIFOPolicy(max_wait=60)
     for s in (2, 0, 1):

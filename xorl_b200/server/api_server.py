@@ -36,13 +36,15 @@ def _datum_to_dict(d: T.Datum) -> Dict[str, Any]:
 class ServerState:
     def __init__(self, backend, output_dir: str = "outputs", dp_size: int = 1, packing_len: int = 4096,
                  packing: str = "sequential", future_ttl: float = 3600.0, session_timeout: float = 600.0,
-                 api_keys: Optional[List[str]] = None, idle_sleep_seconds: float = 0.0):
+                 api_keys: Optional[List[str]] = None, idle_sleep_seconds: float = 0.0,
+                 on_oversized: str = "error"):
         self.backend = backend
         self.output_dir = output_dir
         self.futures = FutureStore(future_ttl)
         self.endpoints = EndpointManager()
         self.orch = Orchestrator(backend, SeqIdAwareFIFOPolicy(),
-                                 RequestProcessor(dp_size, packing_len, packing), self._on_result)
+                                 RequestProcessor(dp_size, packing_len, packing, on_oversized=on_oversized),
+                                 self._on_result)
         self.sessions: Dict[str, Dict[str, Any]] = {}
         self.models: Dict[str, Dict[str, Any]] = {"default": {"model_id": "default", "created": time.time()}}
         self.training_runs: Dict[str, Dict[str, Any]] = {}

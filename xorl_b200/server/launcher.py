@@ -220,8 +220,9 @@ def main(argv=None) -> None:
             return
     import uvicorn
     state = ServerState(backend, sargs.output_dir, dp, sargs.sample_packing_sequence_len,
-                        sargs.sample_packing_method, sargs.future_ttl_seconds, sargs.session_timeout_seconds,
-                        sargs.api_keys, sargs.idle_sleep_seconds)
+                        sargs.sample_packing_strategy or sargs.sample_packing_method, sargs.future_ttl_seconds,
+                        sargs.session_timeout_seconds, sargs.api_keys, sargs.idle_sleep_seconds,
+                        on_oversized=sargs.sample_packing_on_oversized)
     try:
         uvicorn.run(create_app(state), host=sargs.api_host, port=sargs.api_port, log_level="info")
     finally:

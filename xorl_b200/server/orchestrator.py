@@ -14,7 +14,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Any, Callable, Deque, Dict, List, Optional
 
-from .packing import balance_across_dp, pack_best_fit, pack_sequential
+from .packing import apply_oversized_policy, balance_across_dp, pack_balanced_dp, pack_best_fit, pack_sequential
 
 
 @dataclass
@@ -86,9 +86,37 @@ class SeqIdAwareFIFOPolicy(FIFOPolicy):
 class RequestProcessor:
     """Turns API payloads into backend calls (datum packing for forward/forward_backward)."""
 
+    PACKERS = ("sequential", "best_fit", "balanced_dp")
+
     def __init__(self, dp_size: int = 1, packing_len: int = 4096, packing: str = "sequential",
-                 pad_to: int = 128):
+                 pad_to: int = 128, on_oversized: str = "error"):
+        if packing not in self.PACKERS:
+            raise ValueError(f"unknown packing strategy {packing!r}; expected one of {self.PACKERS}")
         self.dp, self.packing_len, self.packing, self.pad_to = dp_size, packing_len, packing, pad_to
+        self.on_oversized = on_oversized
+
+    def admit(self, datums: List[Dict[str, Any]]):
+        """Applies the oversized policy.  Returns the surviving datums and their positions in the request."""
+        kept, origin = apply_oversized_policy(datums, self.packing_len, self.on_oversized)
+        if not kept:
+            raise ValueError("every datum of the request is longer than the packing length")
+        return kept, origin
+
+    @staticmethod
+    def restore_order(result: Any, origin: List[int], n: int) -> Any:
+        """Per-datum lists of a result (one entry per admitted datum) back to one entry per datum of
+        the request; a skipped datum gets an empty entry."""
+        if not isinstance(result, dict) or len(origin) == n:
+            return result
+        out = dict(result)
+        for k, v in result.items():
+            if isinstance(v, list) and len(v) == len(origin):
+                full: List[Any] = [[] for _ in range(n)]
+                for o, item in zip(origin, v):
+                    full[o] = item
+                out[k] = full
+        out["skipped_datums"] = sorted(set(range(n)) - set(origin))
+        return out
 
     def plan(self, datums: List[Dict[str, Any]]) -> List[List[List[int]]]:
         lengths = [len(d["tokens"]) for d in datums]
@@ -96,8 +124,12 @@ class RequestProcessor:
         if too_long:
             raise ValueError(f"datum {too_long[0]} has {lengths[too_long[0]]} tokens, more than the "
                              f"packing length {self.packing_len}")
-        bins = pack_best_fit(lengths, self.packing_len) if self.packing == "best_fit" \
-            else pack_sequential(lengths, self.packing_len)
+        if self.packing == "balanced_dp":
+            bins = pack_balanced_dp(lengths, self.packing_len, self.dp)
+        elif self.packing == "best_fit":
+            bins = pack_best_fit(lengths, self.packing_len)
+        else:
+            bins = pack_sequential(lengths, self.packing_len)
         return balance_across_dp(bins, lengths, self.dp)
 
 
@@ -152,10 +184,12 @@ class Orchestrator:
     def _execute(self, req: OrchestratorRequest) -> None:
         try:
             if req.op in ("forward_backward", "forward"):
-                datums = req.payload["datums"]
+                requested = req.payload["datums"]
+                datums, origin = self.processor.admit(requested)
                 plan = self.processor.plan(datums)
                 res = getattr(self.backend, req.op)(req.model_id, datums, plan, req.payload.get("loss_fn", "cross_entropy"),
                                                     req.payload.get("loss_fn_config", {}))
+                res = self.processor.restore_order(res, origin, len(requested))
             else:
                 res = getattr(self.backend, req.op)(req.model_id, **req.payload)
             self.processed += 1

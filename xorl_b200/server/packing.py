@@ -2,7 +2,9 @@
 (src/xorl/server/orchestrator/packing.py:545-903)."""
 from __future__ import annotations
 
-from typing import Any, Dict, List, Sequence
+import heapq
+import math
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -39,6 +41,67 @@ def pack_best_fit(lengths: Sequence[int], capacity: int) -> List[List[int]]:
             bins[best].append(i)
             space[best] -= n
     return bins
+
+
+def _lpt(lengths: Sequence[int], n_bins: int, capacity: int) -> Optional[List[List[int]]]:
+    """Longest-first into the currently lightest of ``n_bins`` bins; None when a bin would overflow."""
+    order = sorted(range(len(lengths)), key=lambda i: (-lengths[i], i))
+    heap: List[Tuple[int, int]] = [(0, b) for b in range(n_bins)]
+    bins: List[List[int]] = [[] for _ in range(n_bins)]
+    for i in order:
+        load, b = heapq.heappop(heap)
+        if load + lengths[i] > capacity:
+            return None
+        bins[b].append(i)
+        heapq.heappush(heap, (load + lengths[i], b))
+    return [sorted(b) for b in bins]
+
+
+def pack_balanced_dp(lengths: Sequence[int], capacity: int, dp: int) -> List[List[int]]:
+    """``k * dp`` bins of near-equal token count for the smallest ``k`` that fits, so that every
+    data-parallel rank gets ``k`` real micro-batches and no dummy ones
+    (src/xorl/server/orchestrator/packing.py:857-928).  With fewer samples than ranks, or when no
+    multiple of ``dp`` fits, the result is the best-fit packing."""
+    n = len(lengths)
+    if dp <= 1 or n < dp:
+        return pack_best_fit(lengths, capacity)
+    k_min = max(1, math.ceil(sum(lengths) / (dp * capacity)))
+    for k in range(k_min, n // dp + 1):
+        bins = _lpt(lengths, k * dp, capacity)
+        if bins is not None:
+            return bins
+    return pack_best_fit(lengths, capacity)
+
+
+def apply_oversized_policy(datums: List[Dict[str, Any]], capacity: int, mode: str = "error"
+                           ) -> Tuple[List[Dict[str, Any]], List[int]]:
+    """What happens to a datum longer than the packing length: ``error`` raises, ``skip`` drops it,
+    ``truncate`` clips its tokens and every per-token field (src/xorl/server/orchestrator/packing.py:713-792).
+    Returns the surviving datums and the positions (in the input list) they came from."""
+    if mode not in ("error", "skip", "truncate"):
+        raise ValueError(f"unknown on_oversized mode {mode!r}")
+    kept, origin = [], []
+    for i, d in enumerate(datums):
+        n = len(d["tokens"])
+        if n <= capacity:
+            kept.append(d)
+            origin.append(i)
+            continue
+        if mode == "error":
+            raise ValueError(f"datum {i} has {n} tokens, more than the packing length {capacity}")
+        if mode == "skip":
+            continue
+        c = {}
+        for k, v in d.items():
+            if k == "routed_experts":
+                c[k] = v[:capacity]
+            elif hasattr(v, "__len__") and not isinstance(v, (str, bytes, dict)) and len(v) == n:
+                c[k] = v[:capacity]
+            else:
+                c[k] = v
+        kept.append(c)
+        origin.append(i)
+    return kept, origin
 
 
 def balance_across_dp(bins: List[List[int]], lengths: Sequence[int], dp: int) -> List[List[List[int]]]:

@@ -49,7 +49,9 @@ class ServerArguments:
     api_host: str = "127.0.0.1"
     api_port: int = 8000
     sample_packing_sequence_len: int = 4096
-    sample_packing_method: str = "sequential"
+    sample_packing_method: str = "sequential"           # sequential | best_fit | balanced_dp
+    sample_packing_strategy: Optional[str] = None        # the reference's newer name; wins when set
+    sample_packing_on_oversized: str = "error"           # error | skip | truncate
     future_ttl_seconds: float = 3600.0
     session_timeout_seconds: float = 600.0
     idle_sleep_seconds: float = 0.0
