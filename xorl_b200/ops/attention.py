@@ -238,6 +238,72 @@ class _QKNormRopeAttn(torch.autograd.Function):
         return dqkv, gq, gk, None, None, None, None, None, None, None, None, None
 
 
+class _QKNormRope(torch.autograd.Function):
+    """The first half of ``_QKNormRopeAttn`` on its own: qkv [T, (Hq+2Hkv)*D] -> normalised, rotated
+    q [T,Hq,D], k [T,Hkv,D] and the v view, for callers that run attention themselves (context
+    parallelism moves q/k/v between ranks first)."""
+
+    @staticmethod
+    def forward(ctx, qkv, wq, wk, cos, sin, Hq, Hkv, D, eps):
+        global _launches
+        T = qkv.shape[0]
+        if not qkv.is_contiguous():
+            qkv = qkv.contiguous()
+        do_norm = wq is not None
+        qk = torch.empty((T, (Hq + Hkv) * D), device=qkv.device, dtype=qkv.dtype)
+        rstd = torch.empty((T, Hq + Hkv), device=qkv.device, dtype=torch.float32) if do_norm else None
+        _lib.check(_lib.cuda_lib().xb_qk_norm_rope_fwd(
+            qkv.data_ptr(), qkv.stride(0), _lib.ptr(wq), _lib.ptr(wk), cos.data_ptr(), sin.data_ptr(), qk.data_ptr(),
+            qk.stride(0), _lib.ptr(rstd), T, Hq, Hkv, D, float(eps), int(do_norm), _lib.stream_ptr()),
+            "xb_qk_norm_rope_fwd")
+        _launches += 1
+        ctx.save_for_backward(qkv, cos, sin, rstd)
+        ctx.wq, ctx.wk, ctx.cfg = wq, wk, (Hq, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+        return qk[:, :Hq * D].view(T, Hq, D), qk[:, Hq * D:].view(T, Hkv, D), v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        global _launches
+        qkv, cos, sin, rstd = ctx.saved_tensors
+        Hq, Hkv, D = ctx.cfg
+        wq, wk = ctx.wq, ctx.wk
+        do_norm = wq is not None
+        T = qkv.shape[0]
+        dqk = torch.cat([dq.reshape(T, Hq * D), dk.reshape(T, Hkv * D)], 1).to(qkv.dtype).contiguous()
+        dqkv = torch.empty_like(qkv)
+        dqkv[:, (Hq + Hkv) * D:] = dv.reshape(T, Hkv * D)
+        lib = _lib.cuda_lib()
+        partial = dwq = dwk = None
+        if do_norm:
+            rows = lib.xb_qk_norm_rope_bwd_partial_rows()
+            partial = torch.empty(rows * 2 * D, device=qkv.device, dtype=torch.float32)
+            dwq = torch.zeros(D, device=qkv.device, dtype=torch.bfloat16)
+            dwk = torch.zeros(D, device=qkv.device, dtype=torch.bfloat16)
+        _lib.check(lib.xb_qk_norm_rope_bwd(dqk.data_ptr(), None, None, dqk.stride(0), qkv.data_ptr(), qkv.stride(0),
+                                           _lib.ptr(wq), _lib.ptr(wk), cos.data_ptr(), sin.data_ptr(), _lib.ptr(rstd),
+                                           dqkv.data_ptr(), dqkv.stride(0), _lib.ptr(partial), _lib.ptr(dwq),
+                                           _lib.ptr(dwk), 0, T, Hq, Hkv, D, int(do_norm), _lib.stream_ptr()),
+                   "xb_qk_norm_rope_bwd")
+        _launches += 4 if do_norm else 1
+        gq = deliver_param_grad(wq, dwq) if do_norm else None
+        gk = deliver_param_grad(wk, dwk) if do_norm else None
+        return dqkv, gq, gk, None, None, None, None, None, None
+
+
+def qk_norm_rope(qkv, wq, wk, cos, sin, Hq, Hkv, D, eps=1e-6):
+    """qkv [T, (Hq+2Hkv)*D] -> (q [T,Hq,D], k [T,Hkv,D], v [T,Hkv,D]) with per-head RMSNorm (when
+    ``wq``/``wk`` are given) and rotate-half RoPE applied to q and k."""
+    T = qkv.shape[0]
+    if _kernel_ok(qkv, D):
+        return _QKNormRope.apply(qkv, wq, wk, cos, sin, Hq, Hkv, D, eps)
+    q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
+    if wq is not None:
+        q, k = _head_rmsnorm_ref(q, wq, eps), _head_rmsnorm_ref(k, wk, eps)
+    return rope_reference(q, cos, sin), rope_reference(k, cos, sin), v
+
+
 def qk_norm_rope_attention(qkv, wq, wk, cos, sin, cu_seqlens, Hq, Hkv, D, eps=1e-6, causal=True,
                            scale=None):
     """Fused attention block over a packed qkv activation.

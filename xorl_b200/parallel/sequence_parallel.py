@@ -11,7 +11,8 @@ of ``2 * ring * ulysses``; ring rank ``r`` owns chunks ``r`` and ``2R-1-r`` of e
   (q_b,k_b) causal plus (q_b,k_a) full when ``j == r``; (q_a,k_a),(q_b,k_a) full when ``j < r``;
   (q_b,k_a),(q_b,k_b) full when ``j > r`` — each one call of the block-pair attention kernel, merged
   by log-sum-exp (src/xorl/distributed/sequence_parallel/ring_attention.py:28-77,202-253,331-843).
-  Backward re-uses the gathered K/V, accumulates dQ locally and reduce-scatters dK/dV to owners.
+  K/V blocks rotate peer to peer with the next hop in flight under the current block's kernels; backward
+  rotates them again with the dK/dV accumulator of each block travelling along; dQ accumulates locally.
 * Hybrid: Ulysses inside each ring rank group, ring across groups (strategy.py:428-477).
 """
 from __future__ import annotations
@@ -155,60 +156,84 @@ def _ring_calls(cu_blocks: torch.Tensor, r: int, j: int) -> List[Tuple[torch.Ten
             (i32(torch.where(is_a, neg, b_start)), False)]        # (q_b,k_b)
 
 
+def _ring_exchange(send: torch.Tensor, recv: torch.Tensor, group, rank: int, world: int):
+    """Posts ``send`` to the next ring rank and ``recv`` from the previous one; returns the requests.
+    Nothing waits here: the caller computes on the block it already holds and waits afterwards."""
+    nxt = dist.get_global_rank(group, (rank + 1) % world)
+    prv = dist.get_global_rank(group, (rank - 1) % world)
+    return dist.batch_isend_irecv([dist.P2POp(dist.isend, send, nxt, group),
+                                   dist.P2POp(dist.irecv, recv, prv, group)])
+
+
+def _wait_all(reqs) -> None:
+    for r in reqs:
+        r.wait()
+
+
 class _RingAttention(torch.autograd.Function):
+    """K/V blocks travel round the ring one hop per step (two receive buffers: the hop for step
+    ``s+1`` is in flight while step ``s`` computes), so a rank never holds more than its own block
+    plus two in transit, and only its own block is kept for backward
+    (src/xorl/distributed/sequence_parallel/ring_attention.py:168-191).  In backward the blocks make
+    the same trip again and the fp32 dK/dV accumulator of a block travels with it, picking up one
+    contribution per rank; one last hop brings it home (ring_attention.py:612-843)."""
+
     @staticmethod
     def forward(ctx, q, k, v, cu_blocks, group, rank, world, scale):
         T, Hq, D = q.shape
         kv = torch.stack([k.contiguous(), v.contiguous()])            # [2, T, Hkv, D]
-        gathered = [torch.empty_like(kv) for _ in range(world)]
-        dist.all_gather(gathered, kv, group=group)
+        bufs = [torch.empty_like(kv), torch.empty_like(kv)]
         out = torch.zeros((T, Hq, D), device=q.device, dtype=torch.float32)
         lse = torch.full((Hq, T), float("-inf"), device=q.device, dtype=torch.float32)
         qc = q.contiguous()
+        cur = kv
         for s in range(world):
             j = (rank - s) % world
-            kj, vj = gathered[j][0], gathered[j][1]
+            reqs = _ring_exchange(cur, bufs[s % 2], group, rank, world) if s < world - 1 else ()
             for k_starts, causal in _ring_calls(cu_blocks, rank, j):
-                o_p, l_p = block_attention(qc, kj, vj, cu_blocks, k_starts, causal, scale)
+                o_p, l_p = block_attention(qc, cur[0], cur[1], cu_blocks, k_starts, causal, scale)
                 out, lse = _merge(out, lse, o_p, l_p)
+            if s < world - 1:
+                _wait_all(reqs)
+                cur = bufs[s % 2]
         out_lp = out.to(q.dtype)
-        ctx.save_for_backward(qc, torch.stack(gathered), out_lp, lse, cu_blocks)
+        ctx.save_for_backward(qc, kv, out_lp, lse, cu_blocks)
         ctx.cfg = (group, rank, world, scale)
         return out_lp
 
     @staticmethod
     def backward(ctx, dout):
-        qc, gathered, out, lse, cu_blocks = ctx.saved_tensors
+        qc, kv, out, lse, cu_blocks = ctx.saved_tensors
         group, rank, world, scale = ctx.cfg
         T, Hq, D = qc.shape
         dout = dout.contiguous()
         dq = torch.zeros((T, Hq, D), device=qc.device, dtype=torch.float32)
         delta = torch.empty((Hq, T), device=qc.device, dtype=torch.float32)
-        dkv = torch.zeros((world,) + tuple(gathered.shape[1:]), device=qc.device, dtype=torch.float32)
+        bufs = [torch.empty_like(kv), torch.empty_like(kv)]
+        acc_bufs = [torch.empty(kv.shape, device=kv.device, dtype=torch.float32) for _ in range(2)]
+        cur, acc, acc_reqs = kv, None, ()
         first = True
         for s in range(world):
             j = (rank - s) % world
-            kj, vj = gathered[j][0], gathered[j][1]
+            reqs = _ring_exchange(cur, bufs[s % 2], group, rank, world) if s < world - 1 else ()
+            part = None
             for k_starts, causal in _ring_calls(cu_blocks, rank, j):
-                dk, dv = block_attention_bwd(qc, kj, vj, out, dout, lse, delta, dq, cu_blocks,
+                dk, dv = block_attention_bwd(qc, cur[0], cur[1], out, dout, lse, delta, dq, cu_blocks,
                                              k_starts, causal, scale, first)
                 first = False
-                dkv[j, 0] += dk
-                dkv[j, 1] += dv
-        mine = torch.empty_like(dkv[0])
-        _reduce_scatter(mine, dkv, group)
+                both = torch.stack([dk, dv])
+                part = both if part is None else part + both
+            if s > 0:
+                _wait_all(acc_reqs)                                  # block j's accumulator so far
+                part = part + acc_bufs[(s - 1) % 2]
+            acc = part
+            acc_reqs = _ring_exchange(acc, acc_bufs[s % 2], group, rank, world)
+            if s < world - 1:
+                _wait_all(reqs)
+                cur = bufs[s % 2]
+        _wait_all(acc_reqs)                                          # the hop home: this rank's own block
+        mine = acc_bufs[(world - 1) % 2]
         return dq.to(qc.dtype), mine[0].to(qc.dtype), mine[1].to(qc.dtype), None, None, None, None, None
-
-
-def _reduce_scatter(out, stacked, group):
-    """out = sum over ranks of stacked[my_rank] (gloo has no reduce_scatter: all-reduce + slice)."""
-    if dist.get_backend(group) == "gloo":
-        t = stacked.clone()
-        dist.all_reduce(t, group=group)
-        out.copy_(t[dist.get_rank(group)])
-    else:
-        dist.reduce_scatter_tensor(out, stacked.contiguous(), group=group)
-    return out
 
 
 # --------------------------------------------------------------------------------------------
@@ -310,22 +335,21 @@ class ContextParallelStrategy:
             # rotary, no positional embedding) on this rank's tokens at their global positions
             q, k, v = attn._qkv_heads(qkv, ctx)
         else:
-            q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
-            q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
-            if attn.use_qk_norm:
-                q = attn_ops._head_rmsnorm_ref(q, attn.q_norm.weight, attn.cfg.rms_norm_eps)
-                k = attn_ops._head_rmsnorm_ref(k, attn.k_norm.weight, attn.cfg.rms_norm_eps)
-            q = attn_ops.rope_reference(q, ctx.cos, ctx.sin)
-            k = attn_ops.rope_reference(k, ctx.cos, ctx.sin)
+            wq = attn.q_norm.weight if attn.use_qk_norm else None
+            wk = attn.k_norm.weight if attn.use_qk_norm else None
+            # per-head RMSNorm + rotary at the tokens' global positions: the fused kernel on a GPU
+            q, k, v = attn_ops.qk_norm_rope(qkv, wq, wk, ctx.cos, ctx.sin, Hq, Hkv, D, attn.cfg.rms_norm_eps)
         U = self.U
         if U > 1:
             if Hkv % U:
                 rep = U // math.gcd(Hkv, U)
                 k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
-            gi = ctx.aux["cp_gather_idx"]
-            q = _SeqToHead.apply(q, self.u_group, U).index_select(0, gi)
-            k = _SeqToHead.apply(k, self.u_group, U).index_select(0, gi)
-            v = _SeqToHead.apply(v, self.u_group, U).index_select(0, gi)
+            # one all-to-all for q, k and v: heads are laid out (ulysses rank, [q | k | v] heads of that rank)
+            hq, hk = Hq // U, k.shape[1] // U
+            packed = torch.cat([q.reshape(T, U, hq, D), k.reshape(T, U, hk, D), v.reshape(T, U, hk, D)], 2)
+            packed = _SeqToHead.apply(packed.reshape(T, U * (hq + 2 * hk), D), self.u_group, U)
+            packed = packed.index_select(0, ctx.aux["cp_gather_idx"])
+            q, k, v = packed.split([hq, hk, hk], dim=1)
         if self.R > 1:
             out = _RingAttention.apply(q, k, v, ctx.aux["cp_blocks"], self.r_group, self.r_rank,
                                        self.R, attn.scale)
