@@ -185,6 +185,40 @@ def test_flash_attention_fwd_bwd(lens, Hq, Hkv, causal, bwd_mode):
     _close(q.grad, qr.grad, 3e-2, 0.02 * qr.grad.abs().max().item(), "dq")
 
 
+@pytest.mark.parametrize("lens,Hq,Hkv,D,window,sinks", [
+    ([333, 691], 4, 2, 128, 128, False),      # window = one tile; documents that end inside a tile
+    ([1024], 2, 2, 128, 200, False),          # window that straddles tiles
+    ([700, 100], 4, 1, 128, 8, False),        # window far below the tile size
+    ([515], 2, 1, 128, 4096, False),          # window longer than the document: plain causal
+    ([333, 691], 4, 2, 128, 0, True),         # sink logits only
+    ([300, 212, 512], 8, 2, 64, 128, True),   # gpt-oss layer: 64-wide heads, window and sinks
+])
+def test_flash_attention_window_sinks_head_dim(lens, Hq, Hkv, D, window, sinks):
+    from xorl_b200.ops import attention as A
+    torch.manual_seed(0)
+    T = sum(lens)
+    cu = _make_cu(lens)
+    q = torch.randn(T, Hq, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, Hkv, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, Hkv, D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    sk = (torch.randn(Hq, device=DEV) * 2).to(torch.bfloat16).requires_grad_() if sinks else None
+    go = torch.randn(T, Hq, D, device=DEV, dtype=torch.bfloat16)
+    before = A.launch_count()
+    out = A.flash_attn_varlen(q, k, v, cu, causal=True, window=window or None, sinks=sk)
+    out.backward(go)
+    assert A.launch_count() - before == 4, "the tcgen05 kernels must serve windows, sinks and 64-wide heads"
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    skr = sk.detach().float().requires_grad_() if sinks else None
+    ref = A.attention_reference(qr, kr, vr, cu, causal=True, window=window or None, sinks=skr)
+    ref.backward(go.float())
+    _close(out, ref, 2e-2, 2e-2, "out")
+    _close(v.grad, vr.grad, 3e-2, 0.02 * vr.grad.abs().max().item(), "dv")
+    _close(k.grad, kr.grad, 3e-2, 0.02 * kr.grad.abs().max().item(), "dk")
+    _close(q.grad, qr.grad, 3e-2, 0.02 * qr.grad.abs().max().item(), "dq")
+    if sinks:
+        _close(sk.grad, skr.grad, 3e-2, 0.03 * skr.grad.abs().max().item(), "dsinks")
+
+
 @pytest.mark.parametrize("do_norm", [True, False])
 def test_qk_norm_rope_attention(do_norm):
     from xorl_b200.ops.attention import (qk_norm_rope_attention,

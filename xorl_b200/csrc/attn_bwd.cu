@@ -510,7 +510,7 @@ XB_API int xb_attn_bwd_ex(const void* q, const void* k, const void* v, const voi
     attn_delta_kernel<<<(int)((rows + 7) / 8), 256, 0, st>>>(
         (const __nv_bfloat16*)out, ldo, (const __nv_bfloat16*)dout, lddo, delta, T, Hq);
   }
-  if (g_split) {
+  if (g_split || (causal >> 1)) {     // sliding windows are implemented by the split kernels only
     // dq_accum is written with plain stores (added to when flags bit 0 is set); rows outside every
     // sequence keep the zeros of the memset above
     int rc = xb_attn_bwd_dkv(q, k, v, dout, lse, delta, dk, dv, cu_seqlens, k_starts, ldq, ldk, ldv, lddo, lddv,

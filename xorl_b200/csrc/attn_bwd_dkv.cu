@@ -53,6 +53,7 @@ struct Params {
   int num_seqs;
   int T, Hq, Hkv;
   int causal;
+  int window;
   float scale, scale_log2;
   int* status;
 };
@@ -93,7 +94,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int kv0 = kt * BKV;                         // position inside the sequence
   const int n_q_tiles = (seq_len + BQ - 1) / BQ;
   const int qt0 = p.causal ? kv0 / BQ : 0;           // first query tile that sees this KV tile
-  const int per_head = n_q_tiles - qt0;
+  // last query that sees key k under a window is k + window - 1
+  const int qt_end = p.window > 0 ? min(n_q_tiles, (kv0 + BKV + p.window - 2) / BQ + 1) : n_q_tiles;
+  const int per_head = max(0, qt_end - qt0);
   const int n_steps = per_head * G;
 
   extern __shared__ uint8_t smem_raw[];
@@ -283,7 +286,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // dS here is P o (dP - delta); the softmax scale is applied once, to dK, at the end.
         // Tiles entirely below the diagonal and inside the sequence (the common case) need no mask.
         const int q_lo = (qt0 + t % per_head) * BQ;
-        const bool no_mask = (q_lo + BQ <= seq_len) && (kv0 + BKV <= seq_len) && (!p.causal || kv0 + BKV - 1 <= q_lo);
+        const bool no_mask = (q_lo + BQ <= seq_len) && (kv0 + BKV <= seq_len) && (!p.causal || kv0 + BKV - 1 <= q_lo) &&
+                             (p.window <= 0 || kv0 >= q_lo + BQ - p.window);
         if (no_mask) {                               // CTA-uniform
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -294,9 +298,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         } else {
           const int lim = p.causal ? min(seq_len - 1, q_pos) : seq_len - 1;  // last visible kv position
           const int nvis = row_valid ? (lim - (kv0 + half * 32) + 1) : 0;     // visible columns of this thread
+          const int nlo = p.window > 0 ? (q_pos - p.window + 1) - (kv0 + half * 32) : 0;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float pe = i < nvis ? xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) : 0.f;
+            const float pe = (i < nvis && i >= nlo) ? xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) : 0.f;
             pv[i] = pe;
             ds[i] = pe * (__uint_as_float(b[i]) - delta);
           }
@@ -393,7 +398,7 @@ XB_API int xb_attn_bwd_dkv(const void* q, const void* k, const void* v, const vo
   Params p;
   p.lse = lse; p.delta = delta; p.dk = dk; p.dv = (__nv_bfloat16*)dv; p.lddv = lddv;
   p.cu_seqlens = cu_seqlens; p.k_starts = k_starts; p.num_seqs = num_seqs;
-  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.scale = scale;
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal & 1; p.window = causal >> 1; p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = xb_status_ptr();
   static bool configured[64] = {false};

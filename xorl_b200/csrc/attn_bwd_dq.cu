@@ -49,6 +49,7 @@ struct Params {
   int num_seqs;
   int T, Hq, Hkv;
   int causal;
+  int window;
   int accumulate;       // dq already holds partial sums of earlier key blocks: add to it
   float scale, scale_log2;
   int* status;
@@ -91,7 +92,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const int kv_head = head / (p.Hq / p.Hkv);
   const int q0 = qt * BQ;
   const int n_kv_all = (seq_len + BKV - 1) / BKV;
-  const int n_steps = p.causal ? min(n_kv_all, (min(q0 + BQ, seq_len) - 1) / BKV + 1) : n_kv_all;
+  const int n_hi = p.causal ? min(n_kv_all, (min(q0 + BQ, seq_len) - 1) / BKV + 1) : n_kv_all;
+  const int jt0 = p.window > 0 ? max(0, q0 - p.window + 1) / BKV : 0;   // first key tile inside the window
+  const int n_steps = max(0, n_hi - jt0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -148,7 +151,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           ok = false;
           break;
         }
-        const int tok = k_start + j * BKV;
+        const int tok = k_start + (jt0 + j) * BKV;
         uint8_t* sk = smem + SMEM_KV + s * 2 * KV_TILE_BYTES;
         uint8_t* sv = sk + KV_TILE_BYTES;
         mbar_expect_tx(&bars->kv_full[s], 2 * KV_TILE_BYTES);
@@ -254,24 +257,26 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
       tc_fence_after();
       float ds[32];
-      const int kv0 = j * BKV + half * 32;
+      const int kv0 = (jt0 + j) * BKV + half * 32;
       {
         uint32_t a[32], d2[32];
         tmem_ld_32x32(tmem_base + lane_addr + COL_S + 128 * b + half * 32, a);
         tmem_ld_32x32(tmem_base + lane_addr + COL_DP + 128 * b + half * 32, d2);
         tc_wait_ld();
         // dS here is P o (dP - delta); the softmax scale is applied once, to dQ, at the end
-        const bool no_mask = (q0 + BQ <= seq_len) && (j * BKV + BKV <= seq_len) &&
-                             (!p.causal || j * BKV + BKV - 1 <= q0);          // CTA-uniform
+        const int kt = (jt0 + j) * BKV;
+        const bool no_mask = (q0 + BQ <= seq_len) && (kt + BKV <= seq_len) && (!p.causal || kt + BKV - 1 <= q0) &&
+                             (p.window <= 0 || kt >= q0 + BQ - p.window);     // CTA-uniform
         if (no_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             ds[i] = xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) * (__uint_as_float(d2[i]) - delta);
         } else {
           const int nvis = row_valid ? (lim - kv0 + 1) : 0;
+          const int nlo = p.window > 0 ? (q_pos - p.window + 1) - kv0 : 0;   // columns below it are outside the window
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            ds[i] = i < nvis ? xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) *
+            ds[i] = (i < nvis && i >= nlo) ? xb_ex2(fmaf(__uint_as_float(a[i]), p.scale_log2, -lse)) *
                                    (__uint_as_float(d2[i]) - delta)
                              : 0.f;
         }
@@ -367,7 +372,7 @@ XB_API int xb_attn_bwd_dq(const void* q, const void* k, const void* v, const voi
     return -5;
   Params p;
   p.lse = lse; p.delta = delta; p.dq = dq; p.cu_seqlens = cu_seqlens; p.k_starts = k_starts;
-  p.num_seqs = num_seqs; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal; p.accumulate = accumulate;
+  p.num_seqs = num_seqs; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal & 1; p.window = causal >> 1; p.accumulate = accumulate;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
   p.status = xb_status_ptr();
   static bool configured[64] = {false};

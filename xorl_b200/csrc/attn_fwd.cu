@@ -40,6 +40,8 @@ struct Params {
   int num_seqs;
   int T, Hq, Hkv;
   int causal;
+  int window;          // > 0: a query sees only keys with q_pos - k_pos < window
+  const float* sinks;  // optional fp32 [Hq]: one more logit per head in the softmax denominator
   float scale_log2;
   int* status;
 };
@@ -79,7 +81,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int kv_head = head / (p.Hq / p.Hkv);
   const int q_row0 = qt * BQ;  // position inside the sequence
   const int kv_end = p.causal ? min(seq_len, q_row0 + BQ) : seq_len;
-  const int n_kv = (kv_end + BKV - 1) / BKV;
+  // first key tile any row of this query tile can see under a sliding window
+  const int kt0 = p.window > 0 ? max(0, q_row0 - p.window + 1) / BKV : 0;
+  const int n_kv = max(0, (kv_end + BKV - 1) / BKV - kt0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -128,7 +132,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       for (int j = 0; j < n_kv && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int tok = k_start + j * BKV;
+        const int tok = k_start + (kt0 + j) * BKV;
         if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, p.status, XB_K_ATTN_FWD, 100 + s)) {
           ok = false;
           break;
@@ -248,13 +252,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_before();
       mbar_arrive(&bars->s_empty[s]);
 
-      const int col0 = j * BKV;
-      const bool need_mask = (col0 + BKV > seq_len) || (p.causal && col0 + BKV - 1 > q_row0);
+      const int col0 = (kt0 + j) * BKV;
+      const bool need_mask = (col0 + BKV > seq_len) || (p.causal && col0 + BKV - 1 > q_row0) ||
+                             (p.window > 0 && col0 < q_row0 + BQ - p.window);
       if (need_mask) {
         const int lim = p.causal ? min(seq_len - 1, row_pos) : seq_len - 1;  // last valid column
+        const int lo = p.window > 0 ? row_pos - p.window + 1 : 0;            // first valid column
 #pragma unroll
         for (int i = 0; i < BKV; ++i)
-          if (col0 + i > lim) sc[i] = -INFINITY;
+          if (col0 + i > lim || col0 + i < lo) sc[i] = -INFINITY;
       }
       float mx_raw = -INFINITY;
 #pragma unroll
@@ -316,6 +322,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (ok) {
       tc_fence_after();
       const bool valid = row_pos < seq_len;
+      if (p.sinks != nullptr) {
+        // the sink logit joins the denominator (and the LSE) and contributes no value
+        const float sk = __ldg(p.sinks + head) * 1.4426950408889634f;
+        if (m == -INFINITY) { m = sk; l = 1.f; }
+        else l += xb_ex2(sk - m);
+      }
       const float inv = (l > 0.f) ? 1.f / l : 0.f;
       __nv_bfloat16* orow =
           p.out + (size_t)(seq_start + row_pos) * p.ldo + (size_t)head * D;
@@ -366,6 +378,10 @@ XB_API int xb_attn_fwd_ex(const void* q, const void* k, const void* v, void* out
                           const int* cu_seqlens, const int* k_starts, long long ldq, long long ldk,
                           long long ldv, long long ldo, int num_seqs, int T, int Tk, int Hq, int Hkv,
                           int D, int causal, float scale, int max_tiles, void* stream);
+XB_API int xb_attn_fwd_sink(const void* q, const void* k, const void* v, void* out, float* lse,
+                            const int* cu_seqlens, const int* k_starts, const float* sinks, long long ldq,
+                            long long ldk, long long ldv, long long ldo, int num_seqs, int T, int Tk, int Hq,
+                            int Hkv, int D, int causal, float scale, int max_tiles, void* stream);
 
 XB_API int xb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse,
                        const int* cu_seqlens, long long ldq, long long ldk, long long ldv,
@@ -382,6 +398,17 @@ XB_API int xb_attn_fwd_ex(const void* q, const void* k, const void* v, void* out
                           const int* cu_seqlens, const int* k_starts, long long ldq, long long ldk,
                           long long ldv, long long ldo, int num_seqs, int T, int Tk, int Hq, int Hkv,
                           int D, int causal, float scale, int max_tiles, void* stream) {
+  return xb_attn_fwd_sink(q, k, v, out, lse, cu_seqlens, k_starts, nullptr, ldq, ldk, ldv, ldo, num_seqs, T,
+                          Tk, Hq, Hkv, D, causal, scale, max_tiles, stream);
+}
+
+// As xb_attn_fwd_ex with two more features.  ``causal``: bit 0 is the causal flag, the bits above it
+// hold a sliding-window length (0: none): a query sees the keys with q_pos - k_pos < window.
+// ``sinks``: optional fp32 [Hq] device array of per-head sink logits.
+XB_API int xb_attn_fwd_sink(const void* q, const void* k, const void* v, void* out, float* lse,
+                            const int* cu_seqlens, const int* k_starts, const float* sinks, long long ldq,
+                            long long ldk, long long ldv, long long ldo, int num_seqs, int T, int Tk, int Hq,
+                            int Hkv, int D, int causal, float scale, int max_tiles, void* stream) {
   using namespace xb_attn_fwd_ns;
   if (D != 128) return -1;
   if (T <= 0 || num_seqs <= 0) return 0;
@@ -398,7 +425,8 @@ XB_API int xb_attn_fwd_ex(const void* q, const void* k, const void* v, void* out
     return -4;
   Params p;
   p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.lse = lse; p.cu_seqlens = cu_seqlens; p.k_starts = k_starts;
-  p.num_seqs = num_seqs; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
+  p.num_seqs = num_seqs; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal & 1;
+  p.window = causal >> 1; p.sinks = sinks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = xb_status_ptr();
   static bool configured[64] = {false};

@@ -166,12 +166,9 @@ class Attention(nn.Module):
         """General path (whole-projection qk-norm, partial rotary): separate ops."""
         q, k, v = self._qkv_heads(qkv, ctx)
         T, Hq, D = q.shape
-        if self.window or self.sinks is not None:
-            # sliding windows and sink logits are not in the tcgen05 kernel: masked-softmax path
-            out = attn_ops.attention_reference(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale,
-                                               window=self.window, sinks=self.sinks)
-        else:
-            out = attn_ops.flash_attn_varlen(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale)
+        # sliding windows and sink logits are features of the tcgen05 kernel (masked softmax on CPU)
+        out = attn_ops.flash_attn_varlen(q, k, v, ctx.cu_seqlens, ctx.causal, self.scale,
+                                         window=self.window, sinks=self.sinks)
         return out.reshape(T, Hq * D)
 
     def _qkv_heads(self, qkv, ctx):

@@ -87,6 +87,7 @@ _SIGNATURES = {
     "xb_grouped_gemm_mx_rows": [P, P, P, P, P, P, I, L, I, I, L, L, I, I, P],
     "xb_quant_mx_rows": [P, L, P, L, P, I, L, I, P],
     "xb_quant_mx_weight": [P, P, P, I, P, P, I, I, I, I, P],
+    "xb_attn_fwd_sink": [P, P, P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, I, F, I, P],
     "xb_attn_fwd_ex": [P, P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, I, F, I, P],
     "xb_attn_bwd_ex": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, I, I, I, I, I, I, I, F, I, I, P],
     "xb_attn_fwd": [P, P, P, P, P, P, L, L, L, L, I, I, I, I, I, I, F, I, P],

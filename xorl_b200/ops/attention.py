@@ -10,6 +10,7 @@ from __future__ import annotations
 import math
 
 import torch
+import torch.nn.functional as F
 
 from . import _lib
 from .grad_sink import deliver_param_grad
@@ -92,24 +93,30 @@ def qk_norm_rope_attention_reference(qkv, wq, wk, cos, sin, cu_seqlens, Hq, Hkv,
 # --------------------------------------------------------------------------------------------
 # CUDA path
 # --------------------------------------------------------------------------------------------
-def _attn_fwd(q, k, v, cu_seqlens, causal, scale):
+def _mask_arg(causal: bool, window) -> int:
+    """The kernels' mask word: bit 0 causal, the bits above it a sliding-window length (0: none)."""
+    return int(bool(causal)) | (int(window or 0) << 1)
+
+
+def _attn_fwd(q, k, v, cu_seqlens, causal, scale, window=0, sinks=None):
     global _launches
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     out = torch.empty((T, Hq, D), device=q.device, dtype=q.dtype)
     lse = torch.empty((Hq, T), device=q.device, dtype=torch.float32)
     nseq = cu_seqlens.numel() - 1
-    rc = _lib.cuda_lib().xb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                     lse.data_ptr(), cu_seqlens.data_ptr(), q.stride(0),
-                                     k.stride(0), v.stride(0), out.stride(0), nseq, T, Hq, Hkv, D,
-                                     int(causal), float(scale), 0, _lib.stream_ptr())
-    _lib.check(rc, "xb_attn_fwd")
+    rc = _lib.cuda_lib().xb_attn_fwd_sink(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                          lse.data_ptr(), cu_seqlens.data_ptr(), None, _lib.ptr(sinks), q.stride(0),
+                                          k.stride(0), v.stride(0), out.stride(0), nseq, T, T, Hq, Hkv, D,
+                                          _mask_arg(causal, window), float(scale), 0, _lib.stream_ptr())
+    _lib.check(rc, "xb_attn_fwd_sink")
     _launches += 1
     return out, lse
 
 
-def _attn_bwd(q, k, v, out, dout, lse, cu_seqlens, causal, scale, dv_out):
-    """Returns dq fp32 [T,Hq,D], dk fp32 [T,Hkv,D]; writes dv (bf16) into ``dv_out``."""
+def _attn_bwd(q, k, v, out, dout, lse, cu_seqlens, causal, scale, dv_out, window=0, want_delta=False):
+    """Returns dq fp32 [T,Hq,D], dk fp32 [T,Hkv,D]; writes dv (bf16) into ``dv_out``.  With
+    ``want_delta`` also the per-row sums of dO o O (fp32 [Hq, T])."""
     global _launches
     T, Hq, D = q.shape
     Hkv = k.shape[1]
@@ -122,10 +129,10 @@ def _attn_bwd(q, k, v, out, dout, lse, cu_seqlens, causal, scale, dv_out):
                                      dq.data_ptr(), dk.data_ptr(), dv_out.data_ptr(),
                                      cu_seqlens.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
                                      out.stride(0), dout.stride(0), dv_out.stride(0), nseq, T, Hq,
-                                     Hkv, D, int(causal), float(scale), 0, _lib.stream_ptr())
+                                     Hkv, D, _mask_arg(causal, window), float(scale), 0, _lib.stream_ptr())
     _lib.check(rc, "xb_attn_bwd")
     _launches += 3
-    return dq, dk
+    return (dq, dk, delta) if want_delta else (dq, dk)
 
 
 def set_backward_mode(mode: str) -> str:
@@ -142,33 +149,50 @@ def _kernel_ok(t: torch.Tensor, D: int) -> bool:
 
 class _FlashAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, cu_seqlens, causal, scale):
+    def forward(ctx, q, k, v, cu_seqlens, causal, scale, window, sinks):
         def fix(t):
             if t.stride(2) != 1 or t.stride(1) != t.shape[2] or t.stride(0) % 8 or t.data_ptr() % 16:
                 return t.contiguous()
             return t
         q, k, v = fix(q), fix(k), fix(v)
-        out, lse = _attn_fwd(q, k, v, cu_seqlens, causal, scale)
-        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens)
-        ctx.causal, ctx.scale = causal, scale
+        sinks_f = sinks.detach().float().contiguous() if sinks is not None else None
+        out, lse = _attn_fwd(q, k, v, cu_seqlens, causal, scale, window, sinks_f)
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens, sinks_f)
+        ctx.causal, ctx.scale, ctx.window = causal, scale, window
+        ctx.sinks_dtype = sinks.dtype if sinks is not None else None
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, out, lse, cu = ctx.saved_tensors
+        q, k, v, out, lse, cu, sinks_f = ctx.saved_tensors
         dout = dout.contiguous()
         dv = torch.empty_like(v.contiguous())
-        dq, dk = _attn_bwd(q, k, v, out, dout, lse, cu, ctx.causal, ctx.scale, dv)
-        return dq.to(q.dtype), dk.to(k.dtype), dv, None, None, None
+        dq, dk, delta = _attn_bwd(q, k, v, out, dout, lse, cu, ctx.causal, ctx.scale, dv, ctx.window, True)
+        dsinks = None
+        if sinks_f is not None:
+            # d/d sink = -sum over rows of p_sink * delta, p_sink = exp(sink - lse); rows outside
+            # every sequence have lse = 0 written by nobody, so they are masked by position
+            pos = torch.arange(lse.shape[1], device=lse.device)
+            valid = ((pos >= cu[0]) & (pos < cu[-1])).view(1, -1)
+            contrib = torch.where(valid, torch.exp(sinks_f.view(-1, 1) - lse) * delta, torch.zeros_like(lse))
+            dsinks = (-contrib.sum(1)).to(ctx.sinks_dtype)
+        return dq.to(q.dtype), dk.to(k.dtype), dv, None, None, None, None, dsinks
 
 
-def flash_attn_varlen(q, k, v, cu_seqlens, causal=True, scale=None):
-    """Packed varlen attention. q [T,Hq,D], k/v [T,Hkv,D], cu_seqlens int32 [B+1]."""
+def flash_attn_varlen(q, k, v, cu_seqlens, causal=True, scale=None, window=None, sinks=None):
+    """Packed varlen attention. q [T,Hq,D], k/v [T,Hkv,D], cu_seqlens int32 [B+1].  ``window``: a
+    query sees only the last ``window`` keys (itself included); ``sinks`` [Hq]: per-head sink logits.
+    Head dims below 128 run on the 128-wide kernel with zero-padded heads (the products are unchanged)."""
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if _kernel_ok(q, D):
-        return _FlashAttn.apply(q, k, v, cu_seqlens, causal, scale)
-    return attention_reference(q, k, v, cu_seqlens, causal, scale)
+    window = int(window or 0)
+    if q.is_cuda and q.dtype == torch.bfloat16 and v.shape[-1] == D and D < 128 and D % 8 == 0:
+        pad = (0, 128 - D)
+        out = _FlashAttn.apply(F.pad(q, pad), F.pad(k, pad), F.pad(v, pad), cu_seqlens, causal, scale, window, sinks)
+        return out[..., :D]
+    if _kernel_ok(q, D) and v.shape[-1] == D:
+        return _FlashAttn.apply(q, k, v, cu_seqlens, causal, scale, window, sinks)
+    return attention_reference(q, k, v, cu_seqlens, causal, scale, window=window or None, sinks=sinks)
 
 
 class _QKNormRopeAttn(torch.autograd.Function):
