@@ -220,11 +220,23 @@ class _Linear(torch.autograd.Function):
         return dx, dw
 
 
+_LIBRARY_FALLBACKS: set = set()
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """Linear layer through the tcgen05 GEMM (CUDA) or torch (CPU)."""
     if not x.is_cuda:
         return torch.nn.functional.linear(x, w, bias)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[-1] % 8:
+        # the tcgen05 kernel takes bf16 operands with a reduction dim that is a multiple of 8; anything
+        # else runs in the library, and says so once per case instead of doing it silently
+        key = (x.dtype, w.dtype, x.shape[-1] % 8 != 0)
+        if key not in _LIBRARY_FALLBACKS:
+            _LIBRARY_FALLBACKS.add(key)
+            import logging
+            logging.getLogger("xorl_b200").warning(
+                "ops.gemm.linear: %s x %s with K=%d runs in the library GEMM, not the tcgen05 kernel "
+                "(bf16 operands and K %% 8 == 0 are required)", x.dtype, w.dtype, x.shape[-1])
         return torch.nn.functional.linear(x, w, bias)
     y = _Linear.apply(x, w)
     if bias is not None:
