@@ -200,6 +200,11 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, int P,
 // qkv: [T, (Hq + 2*Hkv) * D];  out: [T, (Hq + Hkv) * D]  (q heads then k heads).
 // cos/sin: [T, D/2] fp32 (already gathered by position).
 // ---------------------------------------------------------------------------------------
+// One warp takes QKR_HPW heads of one token: the token's cos / sin values are read once and the loads
+// of all its heads are issued before the first is used (32-bit loads of bf16 pairs, 2 * QKR_HPW in
+// flight per lane).
+constexpr int QKR_HPW = 4;
+
 template <int D>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_in,
@@ -209,42 +214,87 @@ qk_norm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_in,
                         float* __restrict__ rstd_out, int T, int Hq, int Hkv, float eps,
                         int do_norm) {
   constexpr int HALF = D / 2;
-  constexpr int PER = HALF / 32;  // elements per lane in each half
+  constexpr int PER = HALF / 32;  // elements per lane in each half (2, 1 or 4): even for D >= 128
   const int heads = Hq + Hkv;
+  const int groups = (heads + QKR_HPW - 1) / QKR_HPW;
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (wid >= (long long)T * heads) return;
-  const int t = (int)(wid / heads);
-  const int h = (int)(wid % heads);
+  if (wid >= (long long)T * groups) return;
+  const int t = (int)(wid / groups);
+  const int h0 = (int)(wid % groups) * QKR_HPW;
   const int lane = threadIdx.x & 31;
-  const __nv_bfloat16* src = qkv + (size_t)t * ld_in + (size_t)h * D;
-  const __nv_bfloat16* w = (h < Hq) ? wq : wk;
-  float a[PER], b[PER];
-  float ss = 0.f;
+  float a[QKR_HPW][PER], b[QKR_HPW][PER];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    a[i] = __bfloat162float(src[lane * PER + i]);
-    b[i] = __bfloat162float(src[HALF + lane * PER + i]);
-    ss += a[i] * a[i] + b[i] * b[i];
-  }
-  float rstd = 1.f;
-  if (do_norm) {
-    ss = warp_sum(ss);
-    rstd = rsqrtf(ss / (float)D + eps);
-    if (lane == 0 && rstd_out) rstd_out[(size_t)t * heads + h] = rstd;
-  }
-  __nv_bfloat16* dst = out + (size_t)t * ld_out + (size_t)h * D;
+  for (int g = 0; g < QKR_HPW; ++g) {
+    const int h = h0 + g;
+    if (h < heads) {
+      const __nv_bfloat16* src = qkv + (size_t)t * ld_in + (size_t)h * D;
+      if constexpr (PER % 2 == 0) {
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
-    const int e = lane * PER + i;
-    float x1 = a[i], x2 = b[i];
-    if (do_norm) {
-      // normalised value is rounded to bf16 before the rotation, as separate modules would do
-      x1 = __bfloat162float(__float2bfloat16(x1 * rstd * __bfloat162float(w[e])));
-      x2 = __bfloat162float(__float2bfloat16(x2 * rstd * __bfloat162float(w[HALF + e])));
+        for (int i = 0; i < PER; i += 2) {
+          const float2 va = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + lane * PER + i));
+          const float2 vb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + HALF + lane * PER + i));
+          a[g][i] = va.x; a[g][i + 1] = va.y;
+          b[g][i] = vb.x; b[g][i + 1] = vb.y;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+          a[g][i] = __bfloat162float(src[lane * PER + i]);
+          b[g][i] = __bfloat162float(src[HALF + lane * PER + i]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < PER; ++i) a[g][i] = b[g][i] = 0.f;
     }
-    const float c = cosb[(size_t)t * HALF + e], s = sinb[(size_t)t * HALF + e];
-    dst[e] = __float2bfloat16(x1 * c - x2 * s);
-    dst[HALF + e] = __float2bfloat16(x2 * c + x1 * s);
+  }
+  float c[PER], sn[PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    c[i] = __ldg(cosb + (size_t)t * HALF + lane * PER + i);
+    sn[i] = __ldg(sinb + (size_t)t * HALF + lane * PER + i);
+  }
+#pragma unroll
+  for (int g = 0; g < QKR_HPW; ++g) {
+    const int h = h0 + g;
+    if (h >= heads) break;                       // warp-uniform
+    float rstd = 1.f;
+    if (do_norm) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) ss += a[g][i] * a[g][i] + b[g][i] * b[g][i];
+      ss = warp_sum(ss);
+      rstd = rsqrtf(ss / (float)D + eps);
+      if (lane == 0 && rstd_out) rstd_out[(size_t)t * heads + h] = rstd;
+    }
+    const __nv_bfloat16* w = (h < Hq) ? wq : wk;
+    __nv_bfloat16* dst = out + (size_t)t * ld_out + (size_t)h * D;
+    __nv_bfloat16 o1[PER], o2[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane * PER + i;
+      float x1 = a[g][i], x2 = b[g][i];
+      if (do_norm) {
+        // normalised value is rounded to bf16 before the rotation, as separate modules would do
+        x1 = __bfloat162float(__float2bfloat16(x1 * rstd * __bfloat162float(w[e])));
+        x2 = __bfloat162float(__float2bfloat16(x2 * rstd * __bfloat162float(w[HALF + e])));
+      }
+      o1[i] = __float2bfloat16(x1 * c[i] - x2 * sn[i]);
+      o2[i] = __float2bfloat16(x2 * c[i] + x1 * sn[i]);
+    }
+    if constexpr (PER % 2 == 0) {
+#pragma unroll
+      for (int i = 0; i < PER; i += 2) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + lane * PER + i) = __halves2bfloat162(o1[i], o1[i + 1]);
+        *reinterpret_cast<__nv_bfloat162*>(dst + HALF + lane * PER + i) = __halves2bfloat162(o2[i], o2[i + 1]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        dst[lane * PER + i] = o1[i];
+        dst[HALF + lane * PER + i] = o2[i];
+      }
+    }
   }
 }
 
@@ -402,7 +452,7 @@ XB_API int xb_qk_norm_rope_fwd(const void* qkv, long long ld_in, const void* wq,
                                float* rstd, int T, int Hq, int Hkv, int D, float eps, int do_norm,
                                void* stream) {
   if (T <= 0) return 0;
-  const long long warps = (long long)T * (Hq + Hkv);
+  const long long warps = (long long)T * ((Hq + Hkv + QKR_HPW - 1) / QKR_HPW);
   const int grid = (int)((warps + 7) / 8);
   cudaStream_t st = (cudaStream_t)stream;
 #define XB_LAUNCH(DD)                                                                          \

@@ -217,10 +217,22 @@ class DecoderLM(nn.Module):
             # teacher-student KL on the same hidden states, added to the cross-entropy with the same
             # token normalisation (``distill.distillation_loss_weight``)
             t_hidden, t_weight, kind, weight = distill
+            from ..ops import kl_losses
             if getattr(self, "vocab_parallel", False):
-                raise NotImplementedError("distillation is not supported with a vocabulary-parallel lm-head")
-            kl = loss_ops.distillation_kl(hidden, self.lm_head.weight, t_hidden, t_weight, labels, kind,
-                                          self.loss_chunk_tokens)
+                # both lm-heads are row-sharded over the tensor-parallel group: the divergence is formed
+                # from local logit shards, only per-token statistics cross the group
+                tp, tp_rank, tp_group = self.head_tp
+                kl = kl_losses.vocab_parallel_kl(hidden, self.lm_head.weight, t_hidden, t_weight, labels,
+                                                 tp_group, kind).sum()
+                loss = loss_ops.vocab_parallel_linear_cross_entropy(
+                    hidden, self.lm_head.weight, labels.reshape(-1), tp_group,
+                    tp_rank * (self.config.vocab_size // tp), grad_scale, self.loss_chunk_tokens)
+                ctx.aux["distill_kl"] = kl.detach() * grad_scale
+                total = loss + kl * (weight * grad_scale)
+                return (total, None) if return_token_losses else total
+            # exact full-vocabulary divergence streamed over vocabulary chunks: [tokens, chunk] peak memory
+            kl = kl_losses.streaming_kl(hidden, self.lm_head.weight, t_hidden, t_weight, labels, kind,
+                                        vocab_chunk=int(getattr(self, "distill_vocab_chunk", 16384))).sum()
             ce = loss_ops.fused_linear_cross_entropy(hidden, self.lm_head.weight, labels.reshape(-1), grad_scale,
                                                      self.loss_chunk_tokens,
                                                      z_loss=float(getattr(self, "z_loss_coef", 0.0)))
