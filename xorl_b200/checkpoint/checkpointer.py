@@ -3,10 +3,13 @@
 Directory layout ``{output_dir}/checkpoints/global_step_{N}/`` with ``.metadata``,
 ``__{rank}_0.distcp``, ``extra_state/extra_state_rank_{r}.pt`` and ``checkpoint_metadata.json``;
 state keys ``model.<fqn>`` and ``optimizer.state.<fqn>.{exp_avg,exp_avg_sq}`` — the layout of
-src/xorl/checkpoint/checkpointer.py:795-1072.  The engine's flat shards are re-expressed as
-per-parameter ``Shard(0)`` DTensors over the shard group, so a checkpoint written at one world
-size loads at another (DCP reshards), and one written by a single process is a plain-tensor
-checkpoint that sharded runs can read.
+src/xorl/checkpoint/checkpointer.py:795-1072.  Every rank writes the pieces of each parameter that
+its flat shards hold (``checkpoint/boxes.py``: rectangular views of the shard with their offsets in
+the full tensor), so a save moves no parameter between ranks and a load writes into the shards in
+place; DCP stores a tensor as such a chunk list, so a checkpoint written at one world size or
+parallel layout loads at another, and ``DTensor``-saved checkpoints of the same keys load too.
+Expert tensors appear under their full ``[E, ...]`` shape (the reference restores them as
+``Shard(0)`` over ep x ``Shard(1)`` over ep_fsdp, checkpointer.py:107-160: the same logical tensor).
 """
 from __future__ import annotations
 
@@ -40,12 +43,6 @@ def resolve_checkpoint_path(path: str, checkpoint_dir: str) -> Optional[str]:
     return os.path.join(checkpoint_dir, max(steps)[1]) if steps else None
 
 
-def _chunk_bounds(dim0: int, world: int, rank: int):
-    per = -(-dim0 // world)
-    a = min(dim0, rank * per)
-    return a, min(dim0, a + per)
-
-
 class DistributedCheckpointer:
     def __init__(self, engine, optimizer=None, checkpoint_dir: str = "checkpoints",
                  save_async: bool = False, lora_only: bool = False):
@@ -59,89 +56,55 @@ class DistributedCheckpointer:
         self._pending = None
         self._meshes: Dict[int, Any] = {}
 
-    # ---- DTensor views ------------------------------------------------------------------------
-    def _mesh_for(self, g):
-        from torch.distributed.device_mesh import DeviceMesh
-        key = id(g.pg)
-        if key not in self._meshes:
-            ranks = dist.get_process_group_ranks(g.pg)
-            self._meshes[key] = DeviceMesh.from_group(g.pg, self.engine.device.type, mesh=ranks)
-        return self._meshes[key]
-
-    def _wrap(self, g, shape, full_view: torch.Tensor):
-        """Local Shard(0) chunk of one full parameter as a DTensor (plain tensor when world==1)."""
-        if g.world == 1 or g.pg is None:
-            return full_view  # a view of the shard itself: saved from / loaded into in place
-        from torch.distributed.tensor import DTensor, Shard
-        t = full_view if full_view.dim() > 0 else full_view.reshape(1)
-        a, b = _chunk_bounds(t.shape[0], g.world, g.rank)
-        local = t[a:b].clone()
-        stride = torch.empty(t.shape, device="meta").stride()
-        return DTensor.from_local(local, self._mesh_for(g), [Shard(0)], run_check=False,
-                                  shape=t.shape, stride=stride)
-
-    def _ep_mesh(self):
-        """(ep, ep_fsdp) device mesh of this rank's expert-parallel grid (1-D over ep when every
-        rank of a stage is its own ep_fsdp group)."""
-        if "ep" in self._meshes:
-            return self._meshes["ep"]
-        from torch.distributed.device_mesh import DeviceMesh
+    # ---- pieces of the flat shards ----------------------------------------------------------------
+    def _placement(self, p, lshape):
+        """(full shape, RowMap) of a parameter that is a tensor- or expert-parallel slice, else (None, None)."""
+        from .boxes import RowMap
         ps = self.engine.ps
-        ep_ranks, epf_ranks = ps.group_ranks("ep"), ps.group_ranks("ep_fsdp")
-        dev = self.engine.device.type
-        if len(epf_ranks) == 1:
-            mesh = DeviceMesh.from_group(ps.group("ep"), dev, mesh=ep_ranks, mesh_dim_names=("ep",))
-        else:
-            # the expert grid is a reshape of consecutive ranks, hence affine in both coordinates
-            grid = [[e + f - ps.rank for f in epf_ranks] for e in ep_ranks]
-            assert grid[ps.rank_in("ep")][ps.rank_in("ep_fsdp")] == ps.rank
-            mesh = DeviceMesh.from_group([ps.group("ep"), ps.group("ep_fsdp")], dev,
-                                         mesh=torch.tensor(grid), mesh_dim_names=("ep", "ep_fsdp"))
-        self._meshes["ep"] = mesh
-        return mesh
-
-    def _wrap_expert(self, p, local_view: torch.Tensor):
-        """Expert-parallel parameter: this rank's experts ``[E / ep, d1, ...]`` (already gathered over
-        ep_fsdp) as a DTensor of the full ``[E, d1, ...]`` shape, ``Shard(0)`` over ep and
-        ``Shard(1)`` over ep_fsdp -- the placement the reference restores for expert tensors
-        (src/xorl/checkpoint/checkpointer.py:107-160)."""
-        from torch.distributed.tensor import DTensor, Shard
-        ps = self.engine.ps
-        full_shape = tuple(p._xb_full_shape)
-        stride = torch.empty(full_shape, device="meta").stride()
-        mesh = self._ep_mesh()
-        if mesh.ndim == 1:
-            return DTensor.from_local(local_view.clone(), mesh, [Shard(0)], run_check=False,
-                                      shape=full_shape, stride=stride)
-        a, b = _chunk_bounds(full_shape[1], ps.ep_fsdp_size, ps.rank_in("ep_fsdp"))
-        return DTensor.from_local(local_view[:, a:b].clone(), mesh, [Shard(0), Shard(1)], run_check=False,
-                                  shape=full_shape, stride=stride)
+        spec = getattr(p, "_xb_tp", None)
+        if spec is not None and ps.tp_size > 1:
+            full = tuple(p._xb_full_shape)
+            if spec[0] == "col":
+                return full, RowMap.row_sections(spec[1] or (full[0],), ps.tp_size, ps.rank_in("tp"))
+            return full, RowMap([(0, lshape[0], 0)], col_offset=ps.rank_in("tp") * lshape[1])
+        if getattr(p, "_xb_ep", None) is not None and ps.ep_size > 1:
+            return tuple(p._xb_full_shape), RowMap([(0, lshape[0], ps.rank_in("ep") * lshape[0])])
+        return None, None
 
     def _state_sources(self):
-        srcs = [("model", "master", None)]
+        srcs = [("model.{fqn}", None)]
         opt = self.optimizer
         if opt is not None:
             for sname, per_group in opt.state.items():
-                srcs.append((f"optimizer.state.{{fqn}}.{sname}", "extra", per_group))
+                srcs.append((f"optimizer.state.{{fqn}}.{sname}", per_group))
         return srcs
 
     def build_state_dict(self, include_frozen: bool = True) -> Dict[str, Any]:
+        """{key: BoxedTensor} over views of this rank's shards (weights: the fp32 masters, or the
+        compute-dtype shard of a frozen group; optimizer state: its flat shards)."""
+        from .boxes import BoxedTensor
         sd: Dict[str, Any] = {}
         eng = self.engine
-        group_of = {name: g for g in eng.all_groups() for name, _ in g.named_params}
-        param_of = {name: p for g in eng.all_groups() for name, p in g.named_params}
-        for key_fmt, what, extra in self._state_sources():
-            for name, view in eng.iter_full_tensors(what, extra, ep_full=False):
-                g = group_of[name]
-                if getattr(g, "frozen", False) and not include_frozen:
-                    continue
-                fqn = to_checkpoint_fqn(name)
-                key = f"model.{fqn}" if key_fmt == "model" else key_fmt.format(fqn=fqn)
-                val = view.float() if what != "master" else view
-                if getattr(param_of[name], "_xb_ep", None) is not None and eng.ps.ep_size > 1:
-                    sd[key] = self._wrap_expert(param_of[name], val)
+        eng.sync_optimizer()
+        for g in eng.all_groups():
+            frozen = getattr(g, "frozen", False)
+            if frozen and not include_frozen:
+                continue
+            s0, _ = g.shard_range()
+            segs = g.param_segments_in_shard()
+            for key_fmt, per_group in self._state_sources():
+                if per_group is None:
+                    flat = g.master if g.master is not None else g.shard_lp
                 else:
-                    sd[key] = self._wrap(g, view.shape, val)
+                    if frozen or id(g) not in per_group:
+                        continue
+                    flat = per_group[id(g)]
+                for i, a, b in segs:
+                    name, p = g.named_params[i]
+                    lshape, o = tuple(g.shapes[i]) or (1,), g.offsets[i]
+                    full_shape, row_map = self._placement(p, lshape)
+                    sd[key_fmt.format(fqn=to_checkpoint_fqn(name))] = BoxedTensor.from_flat(
+                        flat, lshape, a + s0 - o, b + s0 - o, o - s0, full_shape, row_map)
         return sd
 
     # ---- save -----------------------------------------------------------------------------------
@@ -159,14 +122,17 @@ class DistributedCheckpointer:
         if self.optimizer is not None:
             extra["optimizer_meta"] = self.optimizer.state_dict()
         torch.save(extra, os.path.join(path, "extra_state", f"extra_state_rank_{rank}.pt"))
+        from .boxes import BoxSavePlanner
         writer = dcp.FileSystemWriter(path, single_file_per_rank=True, thread_count=1)
         if dist.is_initialized():
             if self.save_async:
-                self._pending = dcp.async_save(sd, storage_writer=writer)
+                # the shards keep training: the writer thread gets a host snapshot of the pieces
+                sd = {k: v.to_host() for k, v in sd.items()}
+                self._pending = dcp.async_save(sd, storage_writer=writer, planner=BoxSavePlanner())
             else:
-                dcp.save(sd, storage_writer=writer)
+                dcp.save(sd, storage_writer=writer, planner=BoxSavePlanner())
         else:
-            dcp.save(sd, storage_writer=writer, no_dist=True)
+            dcp.save(sd, storage_writer=writer, planner=BoxSavePlanner(), no_dist=True)
         if rank == 0:
             with open(os.path.join(path, "checkpoint_metadata.json"), "w") as f:
                 json.dump({"global_step": global_step, "world_size": self.engine.ps.world_size,
@@ -186,32 +152,17 @@ class DistributedCheckpointer:
         if allow_partial_load:
             have = set(reader.read_metadata().state_dict_metadata.keys())
             sd = {k: v for k, v in sd.items() if k in have}
+        from .boxes import BoxLoadPlanner
+        planner = BoxLoadPlanner(allow_partial_load=allow_partial_load)
+        # the pieces are views of the shards: DCP reads every chunk that intersects one straight into it
         if dist.is_initialized():
-            dcp.load(sd, storage_reader=reader)
+            dcp.load(sd, storage_reader=reader, planner=planner)
         else:
-            dcp.load(sd, storage_reader=reader, no_dist=True)
-        # scatter the loaded per-parameter chunks back into the flat shards
-        def full_of(v):
-            return v.full_tensor() if hasattr(v, "full_tensor") else v
-        model_full: Dict[str, torch.Tensor] = {}
+            dcp.load(sd, storage_reader=reader, planner=planner, no_dist=True)
+        from ..ops.fp8_grouped import invalidate_weight_cache
+        invalidate_weight_cache()
         for g in eng.all_groups():
-            tensors = {}
-            for (name, _), shape in zip(g.named_params, g.shapes):
-                key = f"model.{to_checkpoint_fqn(name)}"
-                if key in sd:
-                    tensors[name] = full_of(sd[key])
-            if tensors:
-                eng.load_full_tensors(tensors, strict=False)
-        if load_optimizer and self.optimizer is not None:
-            for sname, per_group in self.optimizer.state.items():
-                for g in eng.all_groups():
-                    tensors = {}
-                    for (name, _), shape in zip(g.named_params, g.shapes):
-                        key = f"optimizer.state.{to_checkpoint_fqn(name)}.{sname}"
-                        if key in sd:
-                            tensors[name] = full_of(sd[key])
-                    if tensors:
-                        eng.load_full_tensors(tensors, strict=False, target="extra", extra=per_group)
+            eng.refresh_compute_copy(g)
         extra_path = os.path.join(path, "extra_state", f"extra_state_rank_{eng.ps.rank}.pt")
         if not os.path.exists(extra_path):
             extra_path = os.path.join(path, "extra_state", "extra_state_rank_0.pt")
