@@ -38,7 +38,8 @@ def main(out_dir):
     losses = []
     for _ in range(2):
         out = backend.forward_backward("default", datums, plan, "cross_entropy", {})
-        assert all(len(lp) == len(d["tokens"]) for lp, d in zip(out["logprobs"], datums)) or True
+        # every datum comes back with its log-probabilities, whichever data-parallel rank ran it
+        assert all(len(lp) == len(d["tokens"]) for lp, d in zip(out["logprobs"], datums)), [len(x) for x in out["logprobs"]]
         losses.append(out["loss"])
         m = backend.optim_step("default", adam_params={"learning_rate": 5e-3})["metrics"]
         assert m["tokens"] == sum(len(d["tokens"]) - 1 for d in datums), m

@@ -416,6 +416,9 @@ def test_multi_tenant_adapters_are_isolated(tmp_path):
         assert lp("b") == base and lp("default") == base      # a's training moved nothing else
         train("b", 2)
         assert lp("a") == la                                   # ... and b's training did not move a
+        # reference pass: the frozen base model's log-probabilities, whatever the adapter has learned
+        ref = r.forward("a", data, None, loss_fn_config={"reference": True})["logprobs"][0]
+        assert ref == base and lp("a") == la                   # and the adapter is back in place afterwards
         # an open gradient epoch survives a switch to another adapter and back
         r.forward_backward("a", data, None)
         tokens_a = r.accumulated_tokens

@@ -13,6 +13,7 @@ from __future__ import annotations
 import json
 import math
 import os
+from contextlib import contextmanager
 from typing import Dict, Iterable, List, Optional, Tuple
 
 import torch
@@ -53,6 +54,8 @@ class LoraLinear(nn.Module):
 
     def forward(self, x):
         y = gemm_ops.linear(x, self.weight, self.bias)
+        if not getattr(self, "enabled", True):
+            return y                              # reference pass: the frozen base model alone
         full = len(self.slices) == 1 and self.slices[0][1] == 0 and self.slices[0][2] == self.out_features
         deltas = []
         for name, s, e in self.slices:
@@ -114,7 +117,9 @@ class ExpertsLoRA(nn.Module):
             if w is not None:
                 w.requires_grad_(False)
 
-    def tensors(self) -> dict:
+    def tensors(self) -> Optional[dict]:
+        if not getattr(self, "enabled", True):
+            return None                           # reference pass: the frozen base experts alone
         out = {"scaling": self.scaling}
         for p in self.targets:
             out[p] = (getattr(self, f"{p}_lora_A"), getattr(self, f"{p}_lora_B"))
@@ -254,3 +259,19 @@ def save_lora_checkpoint(engine, out_dir: str, base_model_name: str = "") -> Non
                 "bias": "none", "lora_dropout": 0.0, "inference_mode": True, "fan_in_fan_out": False})
     with open(os.path.join(out_dir, "adapter_config.json"), "w") as f:
         json.dump(cfg, f, indent=2)
+
+
+@contextmanager
+def adapters_disabled(model: nn.Module):
+    """Inside the block every LoRA module computes its frozen base projection only: the forward pass
+    of the reference policy that the adapters started from (reference log-probabilities for KL
+    penalties, src/xorl/server/runner/model_runner.py ``forward`` with the adapter detached)."""
+    mods = [m for m in model.modules() if isinstance(m, (LoraLinear, ExpertsLoRA))]
+    prev = [getattr(m, "enabled", True) for m in mods]
+    for m in mods:
+        m.enabled = False
+    try:
+        yield len(mods)
+    finally:
+        for m, e in zip(mods, prev):
+            m.enabled = e

@@ -122,7 +122,7 @@ class Experts(nn.Module):
         if self.fp8_mode is not None:
             kw["fp8"] = self.fp8_mode
         lora = getattr(self, "lora", None)
-        if lora is not None:
+        if lora is not None and lora.tensors() is not None:
             kw["lora"] = lora.tensors()
         return kw
 

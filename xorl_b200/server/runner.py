@@ -54,6 +54,7 @@ class ModelRunner:
         self.poisoned: Optional[str] = None
         self.output_dir = trainer.args.train.output_dir
         self.adapters = None                 # AdapterManager, created with the first extra adapter
+        self.host_group = None               # gloo group of all ranks (set by the dispatcher); None: default group
 
     # ---- helpers --------------------------------------------------------------------------------
     def _local_batches(self, datums, plan) -> List[Dict[str, Any]]:
@@ -107,6 +108,19 @@ class ModelRunner:
         if r is None:
             return None
         return {"routing_replay_all": r.to(self.device).long()}
+
+    def _gather_per_datum(self, local: Dict[int, Any]) -> Dict[int, Any]:
+        """Per-datum outputs live on the data-parallel rank that ran the datum; the caller (rank 0)
+        needs all of them.  Ranks that hold the same datum (tensor / context / pipeline peers) carry
+        identical values."""
+        if self.ps.world_size == 1 or not dist.is_initialized():
+            return local
+        parts: List[Optional[Dict[int, Any]]] = [None] * dist.get_world_size(self.host_group)
+        dist.all_gather_object(parts, local, group=self.host_group)
+        merged: Dict[int, Any] = {}
+        for part in parts:
+            merged.update(part or {})
+        return merged
 
     def _check_usable(self) -> None:
         if self.poisoned:
@@ -176,6 +190,7 @@ class ModelRunner:
             t = torch.tensor([total, float(self.accumulated_tokens)], device=self.device)
             dist.all_reduce(t, group=self.ps.group("dp"))
             total = float(t[0])
+        logprobs = self._gather_per_datum(logprobs)
         return {"loss": total, "num_tokens": sum(len(d["tokens"]) for d in datums),
                 "logprobs": [logprobs.get(i, []) for i in range(len(datums))],
                 "metrics": {"loss:sum": total}}
@@ -190,6 +205,13 @@ class ModelRunner:
         filt = {k: cfg[k] for k in ("top_k", "top_p", "min_p") if cfg.get(k) is not None}
         temperature = float(cfg.get("temperature", 1.0))
         outside = 0
+        if cfg.get("reference"):
+            # reference-policy pass: log-probabilities of the frozen base model, adapters bypassed
+            from ..adapters.lora import adapters_disabled
+            with adapters_disabled(self.model) as n:
+                if n == 0:
+                    raise ValueError("a reference pass needs LoRA adapters over a frozen base model")
+                return self.forward(model_id, datums, plan, loss_fn, {k: v for k, v in cfg.items() if k != "reference"})
         for mb in self._local_batches(datums, plan):
             d = {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in mb.items()}
             hidden = self.engine.forward_only(d["input_ids"], position_ids=d["position_ids"],
@@ -211,6 +233,7 @@ class ModelRunner:
             for idx, (s, e) in zip(mb["datum_index"], mb["datum_spans"]):
                 logprobs[idx] = lp[s:e].tolist()
         metrics = {"out_of_support_tokens": outside} if (filt or temperature != 1.0) else {}
+        logprobs = self._gather_per_datum(logprobs)
         return {"logprobs": [logprobs.get(i, []) for i in range(len(datums))], "metrics": metrics}
 
     def optim_step(self, model_id, adam_params=None, gradient_clip=None, **_):
@@ -321,6 +344,7 @@ class RunnerDispatcher:
     def __init__(self, runner: ModelRunner, cpu_group=None):
         self.runner = runner
         self.cpu_group = cpu_group
+        runner.host_group = cpu_group
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.world = dist.get_world_size() if dist.is_initialized() else 1
 
