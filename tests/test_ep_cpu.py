@@ -52,6 +52,13 @@ def _worker():
     gsum = E.gate_up_proj.grad.clone()
     dist.all_reduce(gsum)
     ok = ok and torch.allclose(blk.experts.gate_up_proj.grad, gsum[rank * El:(rank + 1) * El], atol=1e-4)
+    # canonical lane: the fp64 fixed-tree combine under expert parallelism gives the single-process
+    # canonical result (the per-row expert outputs agree to fp32 rounding of the host GEMMs)
+    ctx.aux["canonical_moe"] = True
+    with torch.no_grad():
+        can = blk(x.detach(), ctx)
+        can_ref = moe_ops.local_moe_forward(x.detach(), w.detach(), idx, E, 8, canonical=True)
+    ok = ok and torch.allclose(can, can_ref, atol=2e-6, rtol=0)
     flag = torch.tensor([1.0 if ok else 0.0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:

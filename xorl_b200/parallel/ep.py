@@ -84,6 +84,11 @@ def _alltoall_forward(x, weights, indices, experts, num_experts, ctx):
     back = y.index_select(0, dest)
     ret = _AllToAll.apply(back, in_splits, out_splits, group)                  # sorted-slot order
     y_slots = _unsort(ret, order)
+    if ctx.aux.get("canonical_moe", False):
+        # parity lane: every token's k expert outputs are back on its own rank in the router's slot
+        # order, so the fp64 fixed-tree combine gives the bits of the single-process result whatever
+        # rank computed which expert (src/xorl/distributed/canonical_moe.py, deepep_canonical.py)
+        return moe_ops.canonical_combine(y_slots.reshape(T, k, H), weights)
     out = (y_slots.reshape(T, k, H).float() * weights.unsqueeze(-1).float()).sum(1)
     return out.to(x.dtype)
 
@@ -97,6 +102,8 @@ def _unsort(sorted_rows: torch.Tensor, order: torch.Tensor) -> torch.Tensor:
 def ep_moe_forward(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor, experts,
                    num_experts: int, ctx) -> torch.Tensor:
     mode = ctx.aux.get("ep_dispatch", "alltoall")
+    if ctx.aux.get("canonical_moe", False):
+        mode = "alltoall"                 # the canonical combine lives on the all-to-all path
     if mode in ("fused", "deepep") and x.is_cuda and x.dtype == torch.bfloat16 \
             and ctx.aux.get("ep_workspace_reuse_ok", True):
         from .ep_fused import fused_ep_forward, fused_ep_available
