@@ -82,3 +82,42 @@ def test_softmax_auxiliary_loss_is_the_z_loss_on_the_logits(tmp_path):
     ce = torch.nn.functional.cross_entropy(logits, y.reshape(-1), reduction="sum")
     z = 0.5 * torch.logsumexp(logits, -1).pow(2).sum()
     assert abs(got - float(ce + z) / 64) < 1e-3 * abs(got), (got, float(ce + z) / 64)
+
+
+def test_prepared_dataset_cache_is_built_once_and_keyed_by_content(tmp_path):
+    import json
+    import numpy as np
+    from xorl_b200.data import datasets as D
+    src = tmp_path / "d.jsonl"
+    src.write_text("\n".join(json.dumps({"input_ids": list(range(3 + i, 20 + i))}) for i in range(5)))
+    spec = [{"path": str(src), "type": "tokenized", "max_seq_len": 16}]
+    cache = str(tmp_path / "prepared")
+    calls = {"n": 0}
+    real = D._load_rows
+
+    def counting(path):
+        calls["n"] += 1
+        return real(path)
+    D._load_rows = counting
+    try:
+        a = D.prepare_datasets(spec, cache_dir=cache)
+        b = D.prepare_datasets(spec, cache_dir=cache)                 # second build: read from the cache
+        assert calls["n"] == 1 and len(a) == len(b) == 5
+        assert all(np.array_equal(a[i]["input_ids"], b[i]["input_ids"]) and len(b[i]["input_ids"]) == 16 for i in range(5))
+        # an edited source file is a different key
+        src.write_text("\n".join(json.dumps({"input_ids": list(range(50, 60))}) for _ in range(2)))
+        import os
+        os.utime(src, (1, 1))
+        c = D.prepare_datasets(spec, cache_dir=cache)
+        assert calls["n"] == 2 and len(c) == 2
+        # a builder that fails releases the lock
+        spec2 = [{"path": str(tmp_path / "missing.jsonl"), "type": "tokenized"}]
+        for _ in range(2):
+            try:
+                D.prepare_datasets(spec2, cache_dir=cache)
+            except (FileNotFoundError, ValueError, OSError):
+                pass
+            else:
+                raise AssertionError("a missing file must raise")
+    finally:
+        D._load_rows = real

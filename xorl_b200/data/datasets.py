@@ -113,9 +113,79 @@ def _load_rows(path: str) -> List[Dict[str, Any]]:
     return rows
 
 
+def _spec_digest(spec: Dict[str, Any], tokenizer, select_columns) -> str:
+    """Key of a prepared dataset: the spec, the tokenizer's identity, and the size / mtime of every
+    source file, so that an edited file or another tokenizer never hits a stale cache
+    (src/xorl/data/prepare/hash.py)."""
+    import hashlib
+    path = spec.get("path", "")
+    files = []
+    if os.path.isdir(path):
+        for ext in ("*.jsonl", "*.json", "*.parquet", "*.arrow"):
+            files += sorted(glob.glob(os.path.join(path, ext)))
+    elif os.path.exists(path):
+        files = [path]
+    stat = [(f, os.path.getsize(f), int(os.path.getmtime(f))) for f in files]
+    tok = (getattr(tokenizer, "name_or_path", type(tokenizer).__name__), len(tokenizer)) if tokenizer is not None else None
+    blob = json.dumps([sorted((k, str(v)) for k, v in spec.items()), stat, tok, list(select_columns or [])])
+    return hashlib.sha256(blob.encode()).hexdigest()[:24]
+
+
+def _load_prepared(d: str) -> Optional["TokenDataset"]:
+    if not os.path.exists(os.path.join(d, "done")):
+        return None
+    z = np.load(os.path.join(d, "tokens.npz"))
+    off, ids, labels = z["offsets"], z["input_ids"], z["labels"]
+    return TokenDataset([{"input_ids": ids[off[i]:off[i + 1]], "labels": labels[off[i]:off[i + 1]]}
+                         for i in range(len(off) - 1)])
+
+
+def _store_prepared(d: str, samples: List[Dict[str, np.ndarray]]) -> None:
+    off = np.cumsum([0] + [len(s["input_ids"]) for s in samples]).astype(np.int64)
+    cat = lambda k: np.concatenate([s[k] for s in samples]) if samples else np.zeros(0, np.int64)
+    np.savez(os.path.join(d, "tokens.npz"), offsets=off, input_ids=cat("input_ids"), labels=cat("labels"))
+    with open(os.path.join(d, "done"), "w") as f:
+        f.write(str(len(samples)))
+
+
+def _prepared_or_build(cache_dir: Optional[str], digest: str, build, wait_s: float = 3600.0) -> "TokenDataset":
+    """One process tokenises and writes ``<cache_dir>/<digest>/``, every other process of the job (and
+    every later run) reads it: the first to create the ``lock`` file is the builder, the others poll for
+    the ``done`` marker (src/xorl/data/prepare/file_lock_loader.py)."""
+    if not cache_dir:
+        return TokenDataset(build())
+    d = os.path.join(cache_dir, digest)
+    os.makedirs(d, exist_ok=True)
+    ds = _load_prepared(d)
+    if ds is not None:
+        return ds
+    try:
+        fd = os.open(os.path.join(d, "lock"), os.O_CREAT | os.O_EXCL | os.O_WRONLY)
+    except FileExistsError:
+        import time
+        t0 = time.time()
+        while time.time() - t0 < wait_s:
+            ds = _load_prepared(d)
+            if ds is not None:
+                return ds
+            time.sleep(0.2)
+        raise TimeoutError(f"prepared dataset {d} did not appear within {wait_s:.0f}s (stale lock file?)")
+    try:
+        samples = build()
+        _store_prepared(d, samples)
+    except BaseException:
+        os.close(fd)
+        os.unlink(os.path.join(d, "lock"))        # let another process try
+        raise
+    os.close(fd)
+    return TokenDataset(samples)
+
+
 def prepare_datasets(specs: Sequence[Dict[str, Any]], tokenizer=None, vocab_size: int = 151936,
-                     select_columns: Optional[Sequence[str]] = None, seed: int = 42) -> Dataset:
-    """Builds (and concatenates) the datasets named by ``data.datasets``."""
+                     select_columns: Optional[Sequence[str]] = None, seed: int = 42,
+                     cache_dir: Optional[str] = None) -> Dataset:
+    """Builds (and concatenates) the datasets named by ``data.datasets``.  File-backed datasets are
+    tokenised once and kept under ``cache_dir`` (``data.dataset_prepared_path``)."""
     built: List[Dataset] = []
     for spec in specs:
         path = spec.get("path")
@@ -129,29 +199,34 @@ def prepare_datasets(specs: Sequence[Dict[str, Any]], tokenizer=None, vocab_size
                                             int(spec.get("min_seq_len", 256)), max_len, vocab_size,
                                             int(spec.get("seed", seed))))
             continue
-        rows = _load_rows(path)
-        samples = []
-        for r in rows:
-            if kind == "tokenized":
-                ids = np.asarray(r["input_ids"], dtype=np.int64)
-                labels = np.asarray(r.get("labels", r["input_ids"]), dtype=np.int64)
-            else:
-                if tokenizer is None:
-                    raise ValueError(f"dataset type {kind!r} needs a tokenizer")
-                text = r.get(spec.get("text_column", "text"))
-                if text is None and "messages" in r:
-                    text = tokenizer.apply_chat_template(r["messages"], tokenize=False)
-                ids = np.asarray(tokenizer(text)["input_ids"], dtype=np.int64)
-                labels = ids.copy()
-            ids, labels = ids[:max_len], labels[:max_len]
-            if len(ids) >= 2:
-                samples.append({"input_ids": ids, "labels": labels})
-        built.append(TokenDataset(samples))
+        built.append(_prepared_or_build(cache_dir, _spec_digest(spec, tokenizer, select_columns),
+                                        lambda spec=spec, kind=kind, max_len=max_len, path=path:
+                                        _tokenise_rows(_load_rows(path), spec, kind, max_len, tokenizer)))
     if not built:
         raise ValueError("data.datasets is empty")
     if len(built) == 1:
         return built[0]
     return ConcatTokenDataset(built)
+
+
+def _tokenise_rows(rows, spec, kind, max_len, tokenizer) -> List[Dict[str, np.ndarray]]:
+    samples = []
+    for r in rows:
+        if kind == "tokenized":
+            ids = np.asarray(r["input_ids"], dtype=np.int64)
+            labels = np.asarray(r.get("labels", r["input_ids"]), dtype=np.int64)
+        else:
+            if tokenizer is None:
+                raise ValueError(f"dataset type {kind!r} needs a tokenizer")
+            text = r.get(spec.get("text_column", "text"))
+            if text is None and "messages" in r:
+                text = tokenizer.apply_chat_template(r["messages"], tokenize=False)
+            ids = np.asarray(tokenizer(text)["input_ids"], dtype=np.int64)
+            labels = ids.copy()
+        ids, labels = ids[:max_len], labels[:max_len]
+        if len(ids) >= 2:
+            samples.append({"input_ids": ids, "labels": labels})
+    return samples
 
 
 class ConcatTokenDataset(Dataset):

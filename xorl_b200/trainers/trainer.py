@@ -206,11 +206,25 @@ class Trainer:
         dd = self.args.distill
         return hidden.detach(), w, dd.distillation_loss_type, float(dd.distillation_loss_weight)
 
+    def _tokenizer(self):
+        """Tokenizer for text / chat datasets (local files only); None when the model names none."""
+        m = self.args.model
+        src = m.tokenizer_path or m.model_path
+        if not src or not os.path.isdir(src):
+            return None
+        try:
+            from transformers import AutoTokenizer
+            return AutoTokenizer.from_pretrained(src, local_files_only=True)
+        except Exception as e:  # noqa: BLE001
+            logger.warning("no tokenizer could be loaded from %s (%s): only tokenised datasets can be used", src, e)
+            return None
+
     def _build_data(self, dataset=None) -> None:
         a = self.args
         if dataset is None:
             dataset = prepare_datasets(a.data.datasets, vocab_size=self.model_config.vocab_size,
-                                       select_columns=a.data.select_columns, seed=a.train.seed)
+                                       select_columns=a.data.select_columns, seed=a.train.seed,
+                                       tokenizer=self._tokenizer(), cache_dir=a.data.dataset_prepared_path)
         shard = None
         if self.ps.sp_size > 1:
             from ..data import SequenceShardCollator
