@@ -453,18 +453,14 @@ def test_rollout_routing_replay(tmp_path):
     # force every token of both MoE layers to experts (0, 1): a different (worse or equal) loss, and
     # the load statistics must show only those two experts
     forced = [[[0, 1], [0, 1]] for _ in toks]
-    r.model.ctx_defaults["collect_expert_load"] = True
-    seen = {}
-    orig = r.engine.make_step_context
-
-    def spy(*a, **k):
-        ctx = orig(*a, **k)
-        seen["ctx"] = ctx
-        return ctx
-
-    r.engine.make_step_context = spy
+    loads = []
+    orig_add = r.moe_metrics.add
+    r.moe_metrics.add = lambda layer, counts: (loads.append(counts.clone()), orig_add(layer, counts))[1]
     out = r.forward_backward("default", [{"tokens": toks, "routed_experts": forced}], None)
-    loads = [v for k, v in seen["ctx"].aux.items() if isinstance(k, tuple) and k[0] == "expert_load"]
+    assert out["metrics"]["moe/max_imbalance_ratio"] > 1.5          # two experts took (almost) everything
+    import json as _json
+    rec = [_json.loads(l) for l in open(os.path.join(r.output_dir, "moe_metrics.jsonl"))][-1]
+    assert rec["expert_load"]["num_moe_layers"] == len(loads) and rec["expert_load"]["total_tokens"] == 2 * 128 * len(loads)
     pad = 128 - len(toks)                                   # padding rows keep the router's own choice
     assert loads and all(int(l[0]) >= len(toks) and int(l[1]) >= len(toks) and int(l[2:].sum()) <= 2 * pad
                          for l in loads)

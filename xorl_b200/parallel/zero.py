@@ -244,6 +244,7 @@ class Zero3Engine:
         self.bf16_a2a_reduce = os.environ.get("XORL_B200_BF16_A2A_REDUCE", "1") == "1"
         self.forward_prefetch, self.backward_prefetch = forward_prefetch, backward_prefetch
         self.offloader = ActivationOffloader(self) if activation_offload else None
+        self.expert_load_tracker = None      # utils.moe_metrics.ExpertLoadTracker, attached by the trainer / runner
         self.recompute = recompute
         self.comm_backend = comm_backend
         self.is_cuda = self.device.type == "cuda"
@@ -682,7 +683,16 @@ class Zero3Engine:
         # the fused EP path reuses its peer-memory workspaces across layers, which is only safe when
         # a layer's backward immediately follows its (re)computed forward
         ctx.aux["ep_workspace_reuse_ok"] = self.recompute
+        if getattr(self, "expert_load_tracker", None) is not None and self.expert_load_tracker.enabled:
+            ctx.aux["collect_expert_load"] = True
         return ctx
+
+    def _take_expert_load(self, ctx, lidx: int) -> None:
+        """Moves a layer's per-expert token counts (first forward pass only) to the tracker."""
+        load = ctx.aux.pop(("expert_load", lidx), None)
+        tracker = getattr(self, "expert_load_tracker", None)
+        if load is not None and tracker is not None:
+            tracker.add(lidx, load)
 
     def chunk_forward(self, layers: List[ZeroUnit], acts, ctx, keep_last_gathered: bool = False):
         """Forward through consecutive layer units.  Returns (acts_out, saved) where ``saved`` is
@@ -707,6 +717,8 @@ class Zero3Engine:
                     outs = layer(*ins, ctx)
                 saved.append((ins, outs))
                 acts = tuple(o.detach() if o is not None else None for o in outs)
+            if ctx.aux.get("collect_expert_load"):
+                self._take_expert_load(ctx, getattr(layer, "layer_idx", i))
             if self.reshard and self.recompute and not (keep_last_gathered and i == nl - 1):
                 self.release(unit)
         return acts, saved
@@ -733,6 +745,7 @@ class Zero3Engine:
                 ins = tuple(a.detach().requires_grad_() if a is not None else None for a in saved[i])
                 saved[i] = None
                 ctx.aux["record_routing"] = False
+                ctx.aux["collect_expert_load"] = False          # counted in the first pass already
                 rec = ctx.aux.pop(("routing_record", lidx), None)
                 if rec is not None:
                     ctx.aux[("routing_replay", lidx)] = rec

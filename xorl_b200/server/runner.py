@@ -55,6 +55,13 @@ class ModelRunner:
         self.output_dir = trainer.args.train.output_dir
         self.adapters = None                 # AdapterManager, created with the first extra adapter
         self.host_group = None               # gloo group of all ranks (set by the dispatcher); None: default group
+        # expert-load metrics of MoE models: one JSON line per forward_backward in moe_metrics.jsonl
+        self.moe_metrics = None
+        n_exp = int(getattr(self.model.config, "num_experts", 0) or 0)
+        if n_exp > 0 and os.environ.get("XORL_ENABLE_MOE_METRICS", "1") != "0":
+            from ..utils.moe_metrics import ExpertLoadTracker
+            self.moe_metrics = ExpertLoadTracker(n_exp, self.output_dir, self.ps.rank, self.ps.group("dp"))
+            self.engine.expert_load_tracker = self.moe_metrics
 
     # ---- helpers --------------------------------------------------------------------------------
     def _local_batches(self, datums, plan) -> List[Dict[str, Any]]:
@@ -161,6 +168,7 @@ class ModelRunner:
         logprobs: Dict[int, List[float]] = {}
         total = 0.0
         eng = self.engine
+        t_start = time.time()
         for mb in self._local_batches(datums, plan):
             d = {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in mb.items()}
             self.accumulated_tokens += mb["num_valid_tokens"]
@@ -191,9 +199,16 @@ class ModelRunner:
             dist.all_reduce(t, group=self.ps.group("dp"))
             total = float(t[0])
         logprobs = self._gather_per_datum(logprobs)
+        metrics = {"loss:sum": total}
+        if self.moe_metrics is not None:
+            m = self.moe_metrics.collect(self.step, time.time() - t_start)
+            self.moe_metrics.write(m)
+            if "expert_load" in m:
+                metrics["moe/mean_imbalance_ratio"] = m["expert_load"]["mean_imbalance_ratio"]
+                metrics["moe/max_imbalance_ratio"] = m["expert_load"]["max_imbalance_ratio"]
         return {"loss": total, "num_tokens": sum(len(d["tokens"]) for d in datums),
                 "logprobs": [logprobs.get(i, []) for i in range(len(datums))],
-                "metrics": {"loss:sum": total}}
+                "metrics": metrics}
 
     @torch.no_grad()
     def forward(self, model_id, datums, plan, loss_fn="cross_entropy", loss_fn_config=None):
