@@ -23,11 +23,11 @@ ENV = {"NCCL_NVLS_ENABLE": "0"}
 STEPS = 20
 
 
-def _cfg(tmp, name, model="small-qwen3", dp=1, **train):
+def _cfg(tmp, name, model="small-qwen3", dp=1, foundation=None, **train):
     # 16 samples -> four rows of 2048 tokens; one optimizer step consumes all four (4 / dp micro-batches
     # per rank), so every step of every layout sees the same global batch
     cfg = {
-        "model": {"config_path": model},
+        "model": {"config_path": model, **({"foundation": dict(foundation)} if foundation else {})},
         "data": {"datasets": [{"path": "random", "type": "tokenized", "max_seq_len": 700,
                                "min_seq_len": 400, "num_samples": 16}],
                  "sample_packing_sequence_len": 2048, "pad_to_multiple_of": 128,
@@ -53,10 +53,10 @@ def _grads(tmp, name):
     return out
 
 
-def _run(tmp, name, nproc, model="small-qwen3", dp=1, extra_cli=(), **train):
+def _run(tmp, name, nproc, model="small-qwen3", dp=1, extra_cli=(), foundation=None, **train):
     from dist_utils import run_distributed
     env = dict(ENV, XORL_DEBUG_DUMP_GRADS=str(tmp / name / "grads"))
-    run_distributed("-m", nproc, "xorl_b200.cli.train", _cfg(tmp, name, model, dp, **train), *extra_cli, env=env,
+    run_distributed("-m", nproc, "xorl_b200.cli.train", _cfg(tmp, name, model, dp, foundation, **train), *extra_cli, env=env,
                     timeout=900)
     return _losses(tmp, name), _grads(tmp, name)
 
@@ -94,21 +94,26 @@ CASES = [
                           pipeline_parallel_schedule="interleaved1f1b", pipeline_parallel_virtual_stages=2)),
     ("tp4_sp_fused", 4, 1, dict(tensor_parallel_size=4, tensor_parallel_sequence_parallel=True)),
 ]
+# model overrides of a case (and of the single-GPU run it is compared with): four-way tensor parallelism
+# needs at least four key/value heads
+FOUNDATION = {"tp4_sp_fused": {"num_attention_heads": 8, "num_key_value_heads": 4}}
 _REF = {}
 
 
-def _reference(tmp_path_factory, model):
-    if model not in _REF:
-        _REF[model] = _run(tmp_path_factory.mktemp("ref_" + model.replace("-", "_")), "ref", 1, model=model)
-    return _REF[model]
+def _reference(tmp_path_factory, model, foundation=None):
+    key = (model, tuple(sorted((foundation or {}).items())))
+    if key not in _REF:
+        _REF[key] = _run(tmp_path_factory.mktemp("ref_" + model.replace("-", "_")), "ref", 1, model=model,
+                         foundation=foundation)
+    return _REF[key]
 
 
 @pytest.mark.parametrize("name,nproc,dp,train", CASES, ids=[c[0] for c in CASES])
 def test_dense_parallel_modes(tmp_path, tmp_path_factory, name, nproc, dp, train):
     if torch.cuda.device_count() < nproc:
         pytest.skip(f"needs {nproc} GPUs")
-    ref = _reference(tmp_path_factory, "small-qwen3")
-    got = _run(tmp_path, name, nproc, dp=dp, **train)
+    ref = _reference(tmp_path_factory, "small-qwen3", FOUNDATION.get(name))
+    got = _run(tmp_path, name, nproc, dp=dp, foundation=FOUNDATION.get(name), **train)
     _check(ref, got)
     if train.get("tensor_parallel_sequence_parallel"):
         # every collective GEMM of the run went through the single-kernel path
