@@ -84,3 +84,30 @@ def test_qlora_linear_uses_the_dequant_kernel():
     wd = lin.dequantized_weight()
     assert seqmix.launch_count() == before + 1
     assert (wd.float().cpu() - w).abs().max() < 0.04
+
+
+@pytest.mark.parametrize("fmt,group", [("nf4", 64), ("int4", 128), ("nvfp4", 16), ("mxfp4", 32), ("nf4", 32)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_quant4_kernel_matches_the_tensor_op_definitions(fmt, group, dtype):
+    """The quantiser kernel gives the codes and scales of the tensor-op codecs (run here on the same
+    GPU), and its output decodes through the dequantiser kernel to within the format's step."""
+    from xorl_b200.ops import quantize as Q
+    from xorl_b200.ops import seqmix
+    torch.manual_seed(0)
+    w = (torch.randn(384, 512, device="cuda") * 0.05)
+    w[0, :group] = 0                                   # an all-zero group: scale clamps
+    w[1, 0] = 3.0                                      # an outlier
+    w = w.to(dtype)
+    ref_fn = {"nf4": Q.nf4_quantize, "int4": Q.int4_quantize, "nvfp4": Q.nvfp4_quantize, "mxfp4": Q.mxfp4_quantize}[fmt]
+    ref = ref_fn(w, group)
+    assert seqmix.quant4_supported(w, fmt, group)
+    got = Q.quantize_weight(w, fmt, group)             # dispatches to the kernel on a GPU
+    ref_scale = ref[1].view(torch.uint8) if fmt == "nvfp4" else ref[1]
+    assert torch.equal(got["scale"], ref_scale.to(got["scale"].dtype)), fmt
+    if fmt == "nvfp4":
+        assert torch.equal(got["global_scale"], ref[2].float())
+    mism = (got["packed"] != ref[0]).float().mean().item()
+    assert mism == 0.0, (fmt, mism)
+    back = seqmix.dequant4(got, fmt, group, w.shape).float()
+    err = (back - w.float()).abs().max().item()
+    assert err < 0.3 * w.float().abs().max().item()

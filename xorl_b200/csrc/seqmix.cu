@@ -415,6 +415,105 @@ dequant4_kernel(const uint32_t* __restrict__ packed, const void* __restrict__ sc
   }
 }
 
+// Quantiser for the same four formats: one thread encodes 8 consecutive elements, the group/8 lanes
+// that share a group (2, 4, 8 or 16: aligned inside a warp) agree on its absolute maximum by shuffles.
+// The arithmetic follows the tensor-op definitions step by step (fp32, IEEE division, nearest table
+// entry with the lower index on ties), so the codes are the ones those definitions give.
+template <typename T> __device__ __forceinline__ void load8f(const T* p, float* v);
+template <> __device__ __forceinline__ void load8f<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    v[2 * j] = __uint_as_float(w[j] << 16);
+    v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+  }
+}
+template <> __device__ __forceinline__ void load8f<float>(const float* p, float* v) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+template <int N> __device__ __forceinline__ uint32_t nearest_code(float x, const float* tab) {
+  uint32_t best = 0;
+  float bd = fabsf(x - tab[0]);
+#pragma unroll
+  for (int i = 1; i < N; ++i) {
+    const float d = fabsf(x - tab[i]);
+    if (d < bd) { bd = d; best = i; }
+  }
+  return best;
+}
+
+template <int FMT, typename T>
+__global__ void __launch_bounds__(256)
+quant4_kernel(const T* __restrict__ w, const float* __restrict__ gmax, uint32_t* __restrict__ packed,
+              void* __restrict__ scale, float* __restrict__ global_scale_out, long long n_vec, int group) {
+  __shared__ float tab[16];
+  if (threadIdx.x < 16)
+    tab[threadIdx.x] = (FMT == FMT_NF4) ? NF4_TABLE[threadIdx.x] : E2M1_TABLE[threadIdx.x];
+  __syncthreads();
+  float gs = 1.f;
+  if (FMT == FMT_NVFP4) {
+    gs = fmaxf(*gmax, 1e-12f) / (6.0f * 448.0f);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *global_scale_out = gs;
+  }
+  const int lanes = group >> 3;                        // lanes that share a group
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  // the loop bound is warp-uniform (rounded up to a warp) so that the shuffles below are convergent
+  const long long n_round = (n_vec + 31) / 32 * 32;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_round; v += stride) {
+    float x[8];
+    const bool live = v < n_vec;
+    if (live) load8f<T>(w + v * 8, x);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    for (int o = 1; o < lanes; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (!live) continue;
+    const long long g = (v * 8) / group;
+    const bool writer = ((v * 8) % group) == 0;
+    uint32_t bits = 0;
+    if (FMT == FMT_NF4) {
+      const float s = fmaxf(amax, 1e-12f);
+      if (writer) reinterpret_cast<float*>(scale)[g] = s;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) bits |= nearest_code<16>(x[i] / s, tab) << (4 * i);
+    } else if (FMT == FMT_INT4) {
+      const float s = fmaxf(amax, 1e-12f) / 7.0f;
+      if (writer) reinterpret_cast<float*>(scale)[g] = s;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float q = fminf(fmaxf(rintf(x[i] / s), -8.f), 7.f) + 8.f;
+        bits |= (uint32_t)q << (4 * i);
+      }
+    } else {
+      float denom;
+      if (FMT == FMT_NVFP4) {
+        const float bs = fminf(fmaxf(amax / 6.0f / gs, 1e-12f), 448.0f);
+        const __nv_fp8_storage_t b8 = __nv_cvt_float_to_fp8(bs, __NV_SATFINITE, __NV_E4M3);
+        if (writer) reinterpret_cast<__nv_fp8_storage_t*>(scale)[g] = b8;
+        denom = fmaxf(__half2float(__half(__nv_cvt_fp8_to_halfraw(b8, __NV_E4M3))) * gs, 1e-30f);
+      } else {
+        const float a = fmaxf(amax, 1.17549435e-38f);                       // 2^-126
+        const float e = fminf(fmaxf(ceilf(log2f(a / 6.0f)), -127.f), 127.f);
+        if (writer) reinterpret_cast<uint8_t*>(scale)[g] = (uint8_t)(e + 127.f);
+        denom = exp2f(e);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float q = x[i] / denom;
+        bits |= (nearest_code<8>(fabsf(q), tab) | (q < 0.f ? 8u : 0u)) << (4 * i);
+      }
+    }
+    packed[v] = bits;
+  }
+}
+
 inline int grid_for(long long work_items, int threads) {
   long long g = (work_items + threads - 1) / threads;
   const long long cap = (long long)xb_sm_count() * 16;
@@ -517,5 +616,37 @@ XB_API int xb_dequant4(const void* packed, const void* scale, const float* globa
     case FMT_MXFP4: dequant4_kernel<FMT_MXFP4><<<grid, 256, 0, st>>>(p, scale, global_scale, o, nv, group); break;
     default: return -1;
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// w: n elements (bf16 when w_fp32 == 0, else fp32); packed: n / 2 bytes; scale: n / group entries (fp32
+// for nf4 / int4, one byte for nvfp4 / mxfp4).  nvfp4 also takes gmax (device fp32: max |w| over the whole
+// tensor) and writes the fp32 global scale.  n % 8 == 0; group in {16, 32, 64, 128}.
+XB_API int xb_quant4(const void* w, int w_fp32, const float* gmax, void* packed, void* scale,
+                     float* global_scale_out, long long n, int group, int fmt, void* stream) {
+  if (n % 8 || !(group == 16 || group == 32 || group == 64 || group == 128) || n % group || !aligned16(w) ||
+      (reinterpret_cast<uintptr_t>(packed) & 3))
+    return -1;
+  if (fmt == FMT_NVFP4 && (!gmax || !global_scale_out)) return -1;
+  if (n <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long nv = n / 8;
+  const int grid = grid_for(nv, 256);
+  uint32_t* p = (uint32_t*)packed;
+#define XB_Q4(F)                                                                                          \
+  do {                                                                                                    \
+    if (w_fp32) quant4_kernel<F, float><<<grid, 256, 0, st>>>((const float*)w, gmax, p, scale,            \
+                                                              global_scale_out, nv, group);               \
+    else quant4_kernel<F, __nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)w, gmax, p, scale,    \
+                                                               global_scale_out, nv, group);              \
+  } while (0)
+  switch (fmt) {
+    case FMT_NF4: XB_Q4(FMT_NF4); break;
+    case FMT_INT4: XB_Q4(FMT_INT4); break;
+    case FMT_NVFP4: XB_Q4(FMT_NVFP4); break;
+    case FMT_MXFP4: XB_Q4(FMT_MXFP4); break;
+    default: return -1;
+  }
+#undef XB_Q4
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

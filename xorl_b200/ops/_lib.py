@@ -96,6 +96,7 @@ _SIGNATURES = {
     "xb_causal_conv1d_bwd_chunks": [I],
     "xb_causal_conv1d_bwd": [P, L, P, L, P, P, P, P, P, L, P, I, I, I, I, P],
     "xb_dequant4": [P, P, P, P, L, I, I, P],
+    "xb_quant4": [P, I, P, P, P, P, L, I, I, P],
     "xb_mirror_lower": [P, L, I, I, I, P],
 }
 

@@ -154,6 +154,10 @@ def mxfp4_dequantize(packed, exp_biased, shape, group: int = 32, dtype=torch.bfl
 
 # ---- uniform interface used by QLoRA ------------------------------------------------------------------
 def quantize_weight(w: torch.Tensor, fmt: str, group: int) -> Dict[str, torch.Tensor]:
+    if w.is_cuda and fmt in ("nf4", "int4", "nvfp4", "mxfp4"):
+        from . import seqmix
+        if seqmix.quant4_supported(w, fmt, group):
+            return seqmix.quant4(w, fmt, group)          # quantiser kernel (csrc/seqmix.cu)
     if fmt == "nf4":
         p, s = nf4_quantize(w, group)
         return {"packed": p, "scale": s}

@@ -124,6 +124,35 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Te
     return causal_conv1d_reference(x, weight, bias, cu_seqlens.to(x.device), silu)
 
 
+def quant4_supported(w: torch.Tensor, fmt: str, group: int) -> bool:
+    return (w.is_cuda and fmt in _FMT_CODE and w.dtype in (torch.bfloat16, torch.float32)
+            and group in (16, 32, 64, 128) and w.numel() % group == 0 and w.numel() > 0)
+
+
+def quant4(w: torch.Tensor, fmt: str, group: int) -> Dict[str, torch.Tensor]:
+    """4-bit ``parts`` (the dictionary ``ops.quantize.quantize_weight`` returns) of a weight that lives
+    on the GPU, by the quantiser kernel: the same codes and scales as the tensor-op definitions."""
+    global _launches
+    w = w.contiguous()
+    n = w.numel()
+    dev = w.device
+    packed = torch.empty(n // 2, dtype=torch.uint8, device=dev)
+    byte_scale = fmt in ("nvfp4", "mxfp4")
+    scale = torch.empty(n // group, dtype=torch.uint8 if byte_scale else torch.float32, device=dev)
+    gmax = gs = None
+    if fmt == "nvfp4":
+        gmax = w.abs().max().float().reshape(1)
+        gs = torch.empty(1, dtype=torch.float32, device=dev)
+    _lib.check(_lib.cuda_lib().xb_quant4(w.data_ptr(), int(w.dtype == torch.float32), _lib.ptr(gmax), packed.data_ptr(),
+                                         scale.data_ptr(), _lib.ptr(gs), n, group, _FMT_CODE[fmt], _lib.stream_ptr()),
+               "xb_quant4")
+    _launches += 1
+    parts = {"packed": packed, "scale": scale}
+    if fmt == "nvfp4":
+        parts["global_scale"] = gs
+    return parts
+
+
 def dequant4(parts: Dict[str, torch.Tensor], fmt: str, group: int, shape) -> torch.Tensor:
     """bf16 weight of ``shape`` from 4-bit ``parts`` (``packed``, ``scale`` and, for nvfp4,
     ``global_scale``) that live on the GPU."""
