@@ -193,3 +193,51 @@ def test_moe_expert_lora_trains_adapters_and_merges(tmp_path):
         assert merge_lora(model) >= 3                        # q_proj of two layers + two expert stacks
         after = float(model(x, labels=y, grad_scale=1.0 / 128)["loss"])
     assert abs(before - after) < 1e-4 and float(ex.lora.gate_proj_lora_B.abs().max()) == 0.0
+
+
+def test_qlora_on_moe_experts_trains_and_loads_a_full_precision_checkpoint(tmp_path):
+    """QLoRA over a MoE model: expert stacks are stored packed (4-bit) with per-expert adapters on top and
+    the loss falls; a Hugging Face checkpoint of the full-precision model loads into the packed storage
+    (quantised on the way in), adapters untouched."""
+    from xorl_b200.adapters.qlora import PackedWeight, inject_qlora
+    from xorl_b200.checkpoint.hf_io import load_hf_weights, save_hf_weights
+    from xorl_b200.ops import quantize as Q
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.zero import Zero3Engine
+    reset_parallel_state()
+    ps = init_parallel_state(device_type="cpu")
+    cfg = preset("tiny-qwen3-moe", tie_word_embeddings=False)
+    # a full-precision model written as a Hugging Face checkpoint
+    base = Zero3Engine(DecoderLM(cfg, device="meta"), ps, compute_dtype=torch.float32, device=torch.device("cpu"), seed=3)
+    save_hf_weights(base, str(tmp_path / "hf"), cfg, dtype=torch.float32)
+    full = {n: t.clone() for n, t in base.iter_full_tensors()}
+    la = LoRAArguments(enable_lora=True, enable_qlora=True, lora_rank=4, quant_format="nf4", quant_group_size=64,
+                       lora_b_init_std=0.01, lora_target_modules=["q_proj", "gate_proj", "up_proj", "down_proj"])
+    model = DecoderLM(cfg, device="meta")
+    wrapped = inject_qlora(model, la)
+    assert any(n.endswith("experts") for n in wrapped)
+    eng = Zero3Engine(model, ps, compute_dtype=torch.float32, device=torch.device("cpu"))
+    names = [n for g in eng.all_groups() for n, _ in g.named_params]
+    assert any(".experts.gate_up_proj_q.qparts.packed" in n for n in names)
+    assert not any(n.endswith("experts.gate_up_proj") for n in names)          # no full-precision expert stack is kept
+    assert any("experts.lora.gate_proj_lora_A" in n for n in names)
+    missing = load_hf_weights(eng, str(tmp_path / "hf"), cfg)
+    assert missing == []
+    layer = next(m for m in model.modules() if isinstance(m, PackedWeight) and m.w_shape[2] == 2 * cfg.moe_intermediate_size)
+    for u in eng.units:
+        eng.gather(u)
+        eng.wait_gather(u)
+    src = next(t for n, t in full.items() if n.endswith("layers.0.mlp.experts.gate_up_proj"))
+    want = Q.dequantize_weight(Q.quantize_weight(src.float(), "nf4", 64), "nf4", 64, src.shape, torch.float32)
+    first = next(m for n, m in model.named_modules() if n.endswith("layers.0.mlp.experts.gate_up_proj_q"))
+    assert torch.allclose(first.dequantized().float(), want, atol=1e-6)
+    opt = build_optimizer(eng, lr=1e-2, weight_decay=0.0)
+    ids = torch.randint(0, 1024, (2, 65))
+    losses = []
+    for _ in range(4):
+        opt.zero_grad()
+        losses.append(float(eng.forward_backward(ids[:, :-1], ids[:, 1:], grad_scale=1.0 / 128)))
+        eng.finish_grad_sync()
+        opt.step()
+    assert losses[-1] < losses[0], losses
+    reset_parallel_state()

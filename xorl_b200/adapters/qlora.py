@@ -87,12 +87,96 @@ class QLoRALinear(LoraLinear):
             pieces.append(y[..., cur:])
         return torch.cat(pieces, dim=-1) if len(pieces) > 1 else pieces[0]
 
+    def quantize_parts(self, w: torch.Tensor) -> Dict[str, torch.Tensor]:
+        """Packed storage (one raw-byte tensor per part, in the storage dtype) of a full-precision weight."""
+        if tuple(w.shape) != tuple(self.w_shape):
+            raise ValueError(f"expected a weight of shape {self.w_shape}, got {tuple(w.shape)}")
+        return {k: _as_compute(t, self._store_dtype) for k, t in Q.quantize_weight(w.float(), self.fmt, self.group).items()}
+
     @torch.no_grad()
     def load_base_weight(self, w: torch.Tensor) -> None:
         """Quantise a full-precision weight into this module's packed storage."""
-        parts = Q.quantize_weight(w.float().cpu(), self.fmt, self.group)
-        for key, t in parts.items():
-            self.qparts[key].copy_(_as_compute(t, self._store_dtype).to(self.qparts[key].device))
+        for key, t in self.quantize_parts(w.cpu()).items():
+            self.qparts[key].copy_(t.to(self.qparts[key].device))
+
+
+class PackedWeight(nn.Module):
+    """Packed storage of one stacked expert tensor ``[E_local, K, N]``: the parts of the 4-bit / fp8
+    codec as frozen raw-byte parameters (sharded and gathered by the ZeRO engine like any expert
+    weight), dequantised to the compute dtype on use (src/xorl/qlora/modules/moe_experts.py)."""
+
+    def __init__(self, shape, fmt: str, group: int, dtype, device, ep=None, std: float = 0.02):
+        super().__init__()
+        self.w_shape, self.fmt, self.group, self.ep = tuple(shape), fmt, group, ep
+        self._store_dtype = dtype
+        probe = Q.quantize_weight(torch.zeros(self.w_shape), fmt, group)
+        self.part_meta = {k: (v.dtype, tuple(v.shape)) for k, v in probe.items()}
+        self.qparts = nn.ParameterDict()
+        es = torch.empty(0, dtype=dtype).element_size()
+        for key, (pdt, pshape) in self.part_meta.items():
+            nbytes = math.prod(pshape) * torch.empty(0, dtype=pdt).element_size()
+            n = (nbytes + es - 1) // es
+            p = nn.Parameter(torch.empty(n, dtype=dtype, device=device), requires_grad=False)
+            p._xb_expert = True
+            if ep is not None and ep[1] > 1:
+                # every expert-parallel rank holds the bytes of its own experts: a 1-D tensor split evenly
+                from ..parallel.ep import mark_ep
+                mark_ep(p, ep[0], ep[1])
+                p._xb_full_shape = (n * ep[1],)
+
+            def mat(view_shape, dev, name, seed_, key=key):
+                import zlib
+                g = torch.Generator().manual_seed((seed_ * 1000003 + zlib.crc32(name.rsplit(".", 2)[0].encode())
+                                                   + (ep[0] if ep else 0)) % (2 ** 63 - 1))
+                w = torch.empty(self.w_shape).normal_(0.0, std, generator=g)
+                return self.quantize_parts(w)[key].to(dev).reshape(view_shape)
+            p._xb_materialize = mat
+            self.qparts[key] = p
+
+    def quantize_parts(self, w: torch.Tensor) -> Dict[str, torch.Tensor]:
+        if tuple(w.shape) != self.w_shape:
+            raise ValueError(f"expected experts of shape {self.w_shape}, got {tuple(w.shape)}")
+        return {k: _as_compute(t, self._store_dtype) for k, t in Q.quantize_weight(w.float(), self.fmt, self.group).items()}
+
+    def local_slice(self, full: torch.Tensor) -> torch.Tensor:
+        """This rank's experts of a full ``[E, K, N]`` tensor."""
+        if self.ep is None or self.ep[1] == 1 or full.shape[0] == self.w_shape[0]:
+            return full
+        El = self.w_shape[0]
+        return full[self.ep[0] * El:(self.ep[0] + 1) * El]
+
+    def dequantized(self) -> torch.Tensor:
+        parts = {}
+        for key, (pdt, pshape) in self.part_meta.items():
+            raw = self.qparts[key].view(torch.uint8)
+            n = math.prod(pshape) * torch.empty(0, dtype=pdt).element_size()
+            parts[key] = raw[:n].view(pdt).reshape(pshape)
+        cuda = self.qparts["packed"].is_cuda
+        if cuda and self.fmt in ("nf4", "int4", "nvfp4", "mxfp4") and self.group % 8 == 0:
+            from ..ops.seqmix import dequant4
+            return dequant4(parts, self.fmt, self.group, self.w_shape)
+        return Q.dequantize_weight(parts, self.fmt, self.group, self.w_shape, torch.bfloat16 if cuda else torch.float32)
+
+
+_QUANTIZED_EXPERT_CLASSES: Dict[type, type] = {}
+
+
+def quantize_experts_(experts: nn.Module, fmt: str, group: int) -> None:
+    """Replaces the stacked ``gate_up_proj`` / ``down_proj`` parameters of an experts module by packed
+    storage; the attributes keep working (they dequantise on access), so every expert path -- local,
+    all-to-all, fused dispatch, LoRA -- runs unchanged on the frozen quantised base."""
+    cls = type(experts)
+    if cls not in _QUANTIZED_EXPERT_CLASSES:
+        def prop(name):
+            return property(lambda self: getattr(self, name + "_q").dequantized().to(self._q_compute_dtype))
+        _QUANTIZED_EXPERT_CLASSES[cls] = type("Quantized" + cls.__name__, (cls,),
+                                              {"gate_up_proj": prop("gate_up_proj"), "down_proj": prop("down_proj")})
+    for name in ("gate_up_proj", "down_proj"):
+        p = experts._parameters.pop(name)
+        experts._q_compute_dtype = p.dtype
+        experts.add_module(name + "_q", PackedWeight(tuple(getattr(p, "_xb_shape", p.shape)), fmt, group, p.dtype,
+                                                     p.device, ep=getattr(p, "_xb_ep", None)))
+    experts.__class__ = _QUANTIZED_EXPERT_CLASSES[cls]
 
 
 def inject_qlora(model: nn.Module, lora_args) -> List[str]:
@@ -111,6 +195,17 @@ def inject_qlora(model: nn.Module, lora_args) -> List[str]:
                                                lora_args.quant_format, lora_args.quant_group_size,
                                                lora_args.lora_b_init_std, lora_args.lora_b_init_seed))
             wrapped.append(full)
+    if True:
+        # MoE experts: per-expert adapters (when the expert projections are targeted) over a packed base
+        from ..models.moe import Experts
+        from .lora import ExpertsLoRA
+        for name, m in list(model.named_modules()):
+            if isinstance(m, Experts) and not any(x in name for x in exclude) and "gate_up_proj" in m._parameters:
+                proj = [p for p in ExpertsLoRA.PROJ if p in targets]
+                if proj and getattr(m, "lora", None) is None and m.gate_up_proj.shape[2] == 2 * m.down_proj.shape[1]:
+                    m.lora = ExpertsLoRA(m, lora_args.lora_rank, lora_args.lora_alpha, proj, lora_args.lora_b_init_std)
+                quantize_experts_(m, lora_args.quant_format, lora_args.quant_group_size)
+                wrapped.append(name)
     for n, p in model.named_parameters():
         p.requires_grad_(("lora_A" in n) or ("lora_B" in n))
     model._xb_lora_config = {"r": lora_args.lora_rank, "lora_alpha": lora_args.lora_alpha,

@@ -178,6 +178,39 @@ def load_hf_weights(engine, path: str, cfg, strict: bool = True, mode: str = "al
     return _load_hf_weights_all_ranks(engine, path, cfg, strict)
 
 
+def _is_adapter_param(pname: str) -> bool:
+    """LoRA matrices are created by this framework, never read from a base-model checkpoint."""
+    return "lora_A" in pname or "lora_B" in pname
+
+
+class _PackedSource:
+    """QLoRA bases: the parameter ``<module>.qparts.<part>`` is filled by quantising the module's
+    full-precision weight from the checkpoint (src/xorl/qlora/utils.py:346 ``maybe_quantize_qlora``).
+    ``base_name`` maps the packed parameter to the name its weight would have without QLoRA."""
+
+    def __init__(self, model):
+        self.model = model
+        self._last = (None, None)
+
+    @staticmethod
+    def split(pname: str):
+        if ".qparts." not in pname:
+            return None
+        mod, key = pname.split(".qparts.")
+        return mod, key
+
+    @staticmethod
+    def base_name(mod: str) -> str:
+        return mod[:-2] if mod.endswith("_q") else mod + ".weight"      # experts.gate_up_proj_q / linear
+
+    def part(self, mod: str, key: str, full_weight: torch.Tensor) -> torch.Tensor:
+        if self._last[0] != mod:
+            m = self.model.get_submodule(mod)
+            w = m.local_slice(full_weight) if hasattr(m, "local_slice") else full_weight
+            self._last = (mod, m.quantize_parts(w))
+        return self._last[1][key]
+
+
 def _load_hf_weights_served(engine, path, cfg, strict, mode, h2d_streams) -> List[str]:
     from safetensors import safe_open
     rank = dist.get_rank()
@@ -194,6 +227,7 @@ def _load_hf_weights_served(engine, path, cfg, strict, mode, h2d_streams) -> Lis
     handler = get_checkpoint_handler(cfg)
     h2d = MultiStreamH2D(engine.device, h2d_streams)
     handles: Dict[str, object] = {}
+    packed = _PackedSource(engine.model)
 
     def read(name: str) -> torch.Tensor:
         fn = wm[name]
@@ -206,13 +240,19 @@ def _load_hf_weights_served(engine, path, cfg, strict, mode, h2d_streams) -> Lis
         # the ranks served by one reader may hold different slices: walk all parameters of the
         # group in the same order everywhere
         for pname, p in g.named_params:
-            srcs = handler.hf_sources(pname)
+            if _is_adapter_param(pname):
+                continue
+            packed_of = _PackedSource.split(pname)
+            src_name = _PackedSource.base_name(packed_of[0]) if packed_of else pname
+            srcs = handler.hf_sources(src_name)
             if cfg.tie_word_embeddings and pname.startswith("lm_head"):
                 srcs = ["model.embed_tokens.weight"]
             meta = [None]
             if is_reader:
                 if all(s_ in wm for s_ in srcs):
-                    t = handler.from_hf(pname, [read(s_) for s_ in srcs]).contiguous()
+                    t = handler.from_hf(src_name, [read(s_) for s_ in srcs]).contiguous()
+                    if packed_of:
+                        t = packed.part(packed_of[0], packed_of[1], t).contiguous()
                     meta = [(tuple(t.shape), t.dtype)]
             dist.broadcast_object_list(meta, src=my_reader, group=pg)
             if meta[0] is None:
@@ -242,17 +282,23 @@ def _load_hf_weights_all_ranks(engine, path: str, cfg, strict: bool = True) -> L
         return handles[fn].get_tensor(name)
 
     missing: List[str] = []
+    packed = _PackedSource(engine.model)
     for g in engine.all_groups():
         tensors = {}
         for i, _, _ in g.param_segments_in_shard():
             pname = g.named_params[i][0]
-            srcs = handler.hf_sources(pname)
+            if _is_adapter_param(pname):
+                continue
+            packed_of = _PackedSource.split(pname)
+            src_name = _PackedSource.base_name(packed_of[0]) if packed_of else pname
+            srcs = handler.hf_sources(src_name)
             if cfg.tie_word_embeddings and pname.startswith("lm_head"):
                 srcs = ["model.embed_tokens.weight"]
             if not all(s in weight_map for s in srcs):
                 missing.append(pname)
                 continue
-            tensors[pname] = handler.from_hf(pname, [read(s) for s in srcs])
+            t = handler.from_hf(src_name, [read(s) for s in srcs])
+            tensors[pname] = packed.part(packed_of[0], packed_of[1], t) if packed_of else t
         engine.load_full_tensors(tensors, strict=False) if tensors else None
     if strict and missing:
         raise KeyError(f"weights missing from {path}: {missing[:8]}")
