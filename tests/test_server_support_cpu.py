@@ -151,3 +151,14 @@ def test_supervisor_stops_on_request_and_on_unanswered_probes(tmp_path):
     sup = Supervisor([ChildSpec("api", sleeper)], poll_interval=0.05, grace=2.0, log=lambda m: None)
     threading.Timer(0.5, sup.request_stop).start()
     assert sup.run(install_signal_handlers=False) == 0 and sup.children[0].proc.poll() is not None
+
+
+@pytest.mark.distributed
+def test_weight_sync_stream_covers_all_pipeline_stages(tmp_path):
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_utils import run_distributed
+    out = run_distributed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "weight_sync_pp_worker.py"), 2,
+                          str(tmp_path / "o"))
+    assert "PP_SYNC_OK" in out

@@ -160,15 +160,56 @@ def iter_sync_tensors(engine, cfg, dtype=torch.bfloat16, quantization: Optional[
     """(engine-side name, tensor) for every weight, in model order.  All ranks of the shard groups
     must iterate together (the gathers are collectives); only the consumer on rank 0 uses them."""
     handler = get_checkpoint_handler(cfg)
-    for fqn, full in engine.iter_full_tensors("master"):
-        if ".lora_" in fqn:
-            continue
-        t = full
-        if merged_lora is not None:
-            t = merged_lora(fqn, t)
-        t = t.to(dtype)
-        for name, part in handler.to_hf(fqn, t):
-            yield from _quantise(name, part, quantization)
+
+    def local():
+        for fqn, full in engine.iter_full_tensors("master"):
+            if ".lora_" in fqn:
+                continue
+            t = full
+            if merged_lora is not None:
+                t = merged_lora(fqn, t)
+            t = t.to(dtype)
+            for name, part in handler.to_hf(fqn, t):
+                yield from _quantise(name, part, quantization)
+
+    ps = engine.ps
+    if getattr(ps, "pp_size", 1) <= 1 or not dist.is_initialized():
+        yield from local()
+        return
+    yield from _relay_pipeline_stages(local(), ps, engine.device)
+
+
+def _relay_pipeline_stages(stream, ps, device) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Under pipeline parallelism every stage holds its own layers.  The ranks that share global rank
+    0's data / tensor coordinates (one per stage: rank 0's pipeline group) forward their stage's tensors
+    to rank 0 one by one, in stage order, so the driver sees the whole model in model order
+    (src/xorl/server/weight_sync/handler.py ``_extract_params_for_sync`` with the PP transfer path).
+    Every rank drains its own stage's stream (the gathers inside are collective over the stage)."""
+    mine = ps.group_ranks("pp")
+    leader = 0 in mine
+    rank = ps.rank
+    if not leader:
+        for _ in stream:
+            pass
+        return
+    if rank == 0:
+        yield from stream
+        for src in mine[1:]:
+            while True:
+                box = [None]
+                dist.recv_object_list(box, src=src)
+                if box[0] is None:
+                    break
+                name, shape, dt = box[0]
+                t = torch.empty(shape, dtype=getattr(torch, dt), device=device)
+                dist.recv(t, src=src)
+                yield name, t
+        return
+    # a later stage's leader: wait for its turn implicitly (rank 0 receives in stage order; sends block)
+    for name, t in stream:
+        dist.send_object_list([(name, tuple(t.shape), str(t.dtype).replace("torch.", ""))], dst=0)
+        dist.send(t.contiguous(), dst=0)
+    dist.send_object_list([None], dst=0)
 
 
 def bucketize(stream: Iterator[Tuple[str, torch.Tensor]], bucket_bytes: int
