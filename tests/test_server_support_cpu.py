@@ -162,3 +162,22 @@ def test_weight_sync_stream_covers_all_pipeline_stages(tmp_path):
     out = run_distributed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "weight_sync_pp_worker.py"), 2,
                           str(tmp_path / "o"))
     assert "PP_SYNC_OK" in out
+
+
+@pytest.mark.distributed
+def test_service_runner_under_pipeline_parallelism(tmp_path):
+    import json
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_utils import run_distributed
+    from server_pp_worker import build_runner, drive
+    from xorl_b200.parallel.state import reset_parallel_state
+    reset_parallel_state()
+    ref = drive(build_runner(str(tmp_path / "ref"), pp=1))
+    reset_parallel_state()
+    ref_path = tmp_path / "ref.json"
+    ref_path.write_text(json.dumps(ref))
+    out = run_distributed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "server_pp_worker.py"), 2,
+                          str(tmp_path / "pp"), str(ref_path))
+    assert "PP_RUNNER_OK" in out

@@ -169,6 +169,8 @@ class ModelRunner:
         total = 0.0
         eng = self.engine
         t_start = time.time()
+        if self.trainer.pp_runner is not None:
+            return self._forward_backward_pp(datums, plan, loss_fn, cfg, t_start)
         for mb in self._local_batches(datums, plan):
             d = {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in mb.items()}
             self.accumulated_tokens += mb["num_valid_tokens"]
@@ -210,6 +212,72 @@ class ModelRunner:
                 "logprobs": [logprobs.get(i, []) for i in range(len(datums))],
                 "metrics": metrics}
 
+    # ---- pipeline parallelism -------------------------------------------------------------------
+    def _pp_runner_for(self, n_mb: int):
+        """The trainer's pipeline runner re-planned for ``n_mb`` micro-batches (a request brings as many
+        as its datums pack into); process groups and stage layout are shared."""
+        base = self.trainer.pp_runner
+        if n_mb == base.n_mb:
+            return base
+        cache = self.__dict__.setdefault("_pp_runners", {})
+        if n_mb not in cache:
+            import copy
+            from ..parallel import pp_schedules as S
+            r = copy.copy(base)
+            r.n_mb = n_mb
+            r.actions = S.build_schedule(r.schedule, r.pp, n_mb, r.virtual_stages)
+            S.simulate(r.actions, r.schedule, r.pp, n_mb, r.virtual_stages)
+            r._send_order = r._message_orders()
+            r.bubble_stats = {}
+            cache[n_mb] = r
+        return cache[n_mb]
+
+    def _forward_backward_pp(self, datums, plan, loss_fn, cfg, t_start, zero_loss: bool = False):
+        """One pipelined pass over this rank's micro-batches (src/xorl/server/runner/model_runner.py
+        ``_forward_backward_pp``): the last stage evaluates the token loss of every micro-batch as its
+        activations arrive and keeps the per-token log-probabilities; loss and log-probabilities reach
+        the caller through the reductions below.  The micro-batch count is padded with label-free
+        batches to a multiple of the pipeline size, which every schedule accepts."""
+        pp = self.ps.pp_size
+        batches = self._local_batches(datums, plan)
+        while len(batches) % pp or not batches:
+            batches.append(datums_to_micro_batch([], pad_to=128))
+        dev = [{k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in mb.items()} for mb in batches]
+        slot = {id(d["labels"]): i for i, d in enumerate(dev)}
+        closures = [self._loss_closure(loss_fn, cfg, mb) for mb in batches]
+        lps: Dict[int, torch.Tensor] = {}
+
+        def head(h, res, labels, ctx, grad_scale):
+            i = slot[id(labels)]
+            hidden = self.model.forward_head(h, res, ctx)
+            fn = (lambda lp, mask: (lp.sum() * 0, {})) if zero_loss else closures[i]
+            loss, lp, _ = fused_linear_token_loss(hidden, self.model.lm_head.weight, labels, fn, grad_scale,
+                                                  self.model.loss_chunk_tokens)
+            lps[i] = lp
+            return loss
+
+        orig = self.model.head_loss
+        self.model.head_loss = head
+        try:
+            total_t = self._pp_runner_for(len(dev)).run(dev, 1.0)
+        finally:
+            self.model.head_loss = orig
+        logprobs: Dict[int, List[float]] = {}
+        for i, lp in lps.items():
+            lp = lp.float().cpu()
+            for idx, (s, e) in zip(batches[i]["datum_index"], batches[i]["datum_spans"]):
+                logprobs[idx] = lp[s:e].tolist()
+        if not zero_loss:
+            self.accumulated_tokens += sum(mb["num_valid_tokens"] for mb in batches)
+        t = torch.tensor([float(total_t)], device=self.device)
+        if self.ps.group("dp") is not None:    # the pipeline runner already shares the loss over the stages
+            dist.all_reduce(t, group=self.ps.group("dp"))
+        total = float(t[0])
+        logprobs = self._gather_per_datum(logprobs)
+        return {"loss": total, "num_tokens": sum(len(d["tokens"]) for d in datums),
+                "logprobs": [logprobs.get(i, []) for i in range(len(datums))],
+                "metrics": {"loss:sum": total}}
+
     @torch.no_grad()
     def forward(self, model_id, datums, plan, loss_fn="cross_entropy", loss_fn_config=None):
         self._check_usable()
@@ -220,6 +288,14 @@ class ModelRunner:
         filt = {k: cfg[k] for k in ("top_k", "top_p", "min_p") if cfg.get(k) is not None}
         temperature = float(cfg.get("temperature", 1.0))
         outside = 0
+        if self.trainer.pp_runner is not None:
+            if filt or temperature != 1.0:
+                raise NotImplementedError("filtered / tempered log-probabilities are not available under pipeline parallelism")
+            # the pipelined pass with a zero loss: log-probabilities come out of the last stage, the
+            # backward half of the schedule adds exact zeros to the gradient accumulators
+            with torch.enable_grad():
+                out = self._forward_backward_pp(datums, plan, loss_fn, dict(cfg), time.time(), zero_loss=True)
+            return {"logprobs": out["logprobs"], "metrics": {}}
         if cfg.get("reference"):
             # reference-policy pass: log-probabilities of the frozen base model, adapters bypassed
             from ..adapters.lora import adapters_disabled
