@@ -144,3 +144,22 @@ def test_moe_expert_parallel_block_fp8(tmp_path, tmp_path_factory):
     _check(ref, got)
     bf16 = _reference(tmp_path_factory, "small-qwen3-moe")[0]
     assert abs(ref[0][0] - bf16[0]) < 0.02 * bf16[0] and abs(ref[0][-1] - bf16[-1]) < 0.15 * bf16[-1] + 0.3
+
+
+def test_checkpoint_resume_on_gpu(tmp_path):
+    """Pieces of the flat shards written from device memory, read back into them: a run resumed from
+    step 2 repeats steps 3 and 4 of the uninterrupted run (the kernels are deterministic)."""
+    from dist_utils import run_distributed
+    n = min(2, torch.cuda.device_count())
+    common = dict(max_steps=4)
+    run_distributed("-m", n, "xorl_b200.cli.train", _cfg(tmp_path, "full", dp=n, save_steps=2, **common), env=ENV,
+                    timeout=600)
+    full = _losses(tmp_path, "full")
+    ckpt = tmp_path / "full" / "checkpoints" / "global_step_2"
+    assert (ckpt / ".metadata").exists()
+    run_distributed("-m", n, "xorl_b200.cli.train",
+                    _cfg(tmp_path, "resumed", dp=n, load_checkpoint_path=str(ckpt), **common), env=ENV, timeout=600)
+    got = _losses(tmp_path, "resumed")
+    assert len(got) >= 2
+    for a, b in zip(full[2:], got[-2:]):
+        assert abs(a - b) <= 2e-3 * abs(a), (full, got)
