@@ -181,3 +181,16 @@ def test_service_runner_under_pipeline_parallelism(tmp_path):
     out = run_distributed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "server_pp_worker.py"), 2,
                           str(tmp_path / "pp"), str(ref_path))
     assert "PP_RUNNER_OK" in out
+
+
+def test_server_arguments_reject_inconsistent_settings():
+    from xorl_b200.server.server_arguments import ServerArguments
+    ServerArguments(sample_packing_strategy="balanced_dp", sample_packing_on_oversized="truncate")
+    for kw, msg in ((dict(sample_packing_strategy="tetris"), "sample_packing_strategy"),
+                    (dict(sample_packing_on_oversized="drop"), "on_oversized"),
+                    (dict(pipeline_parallel_size=0), "pipeline_parallel_size"),
+                    (dict(api_port=70000), "api_port"),
+                    (dict(enable_qlora=True), "enable_qlora"),
+                    (dict(worker_bind_address="127.0.0.1:5555"), "worker_bind_address")):
+        with pytest.raises(ValueError, match=msg):
+            ServerArguments(**kw)

@@ -58,7 +58,8 @@ class ModelRunner:
         # expert-load metrics of MoE models: one JSON line per forward_backward in moe_metrics.jsonl
         self.moe_metrics = None
         n_exp = int(getattr(self.model.config, "num_experts", 0) or 0)
-        if n_exp > 0 and os.environ.get("XORL_ENABLE_MOE_METRICS", "1") != "0":
+        if n_exp > 0 and os.environ.get("XORL_ENABLE_MOE_METRICS", "1") != "0" \
+                and getattr(trainer, "enable_moe_metrics", True):
             from ..utils.moe_metrics import ExpertLoadTracker
             self.moe_metrics = ExpertLoadTracker(n_exp, self.output_dir, self.ps.rank, self.ps.group("dp"))
             self.engine.expert_load_tracker = self.moe_metrics

@@ -58,6 +58,33 @@ class ServerArguments:
     api_keys: List[str] = field(default_factory=list)
     worker_bind_address: str = "tcp://127.0.0.1:5555"
     sync_bucket_size_mb: int = 1024
+    enable_moe_metrics: bool = True                      # moe_metrics.jsonl for MoE models
+
+    def __post_init__(self) -> None:
+        """Cross-field checks that would otherwise surface deep inside the worker fleet
+        (src/xorl/server/server_arguments.py:1230-1260)."""
+        strategy = self.sample_packing_strategy or self.sample_packing_method
+        if strategy not in ("sequential", "best_fit", "balanced_dp"):
+            raise ValueError(f"sample_packing_strategy must be sequential, best_fit or balanced_dp, got {strategy!r}")
+        if self.sample_packing_on_oversized not in ("error", "skip", "truncate"):
+            raise ValueError("sample_packing_on_oversized must be error, skip or truncate, "
+                             f"got {self.sample_packing_on_oversized!r}")
+        if self.sample_packing_sequence_len < 1:
+            raise ValueError("sample_packing_sequence_len must be positive")
+        for name in ("tensor_parallel_size", "pipeline_parallel_size", "ulysses_parallel_size",
+                     "ringattn_parallel_size", "expert_parallel_size", "data_parallel_replicate_size"):
+            if getattr(self, name) < 1:
+                raise ValueError(f"{name} must be at least 1")
+        if not (0 < int(self.api_port) < 65536):
+            raise ValueError(f"api_port {self.api_port} is not a TCP port")
+        if self.enable_qlora and not self.enable_lora:
+            raise ValueError("enable_qlora needs enable_lora (the quantised base is frozen; only adapters train)")
+        if self.max_adapters_per_model < 1:
+            raise ValueError("max_adapters_per_model must be at least 1")
+        if self.future_ttl_seconds <= 0 or self.session_timeout_seconds <= 0:
+            raise ValueError("future_ttl_seconds and session_timeout_seconds must be positive")
+        if not self.worker_bind_address.startswith(("tcp://", "ipc://")):
+            raise ValueError(f"worker_bind_address must be a tcp:// or ipc:// ZMQ address, got {self.worker_bind_address!r}")
 
     @classmethod
     def from_yaml(cls, path: str, overrides: Optional[Dict[str, Any]] = None) -> "ServerArguments":
