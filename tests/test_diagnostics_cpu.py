@@ -97,3 +97,29 @@ def test_kernel_pin_is_written_once_and_detects_a_change(tmp_path):
     assert "native_library_sha256" in pin_kernel_configs(str(tmp_path))["mismatch"]
     with pytest.raises(KernelPinError):
         pin_kernel_configs(str(tmp_path), strict=True)
+
+
+def test_canaries_catch_a_write_past_a_guarded_buffer():
+    import torch
+    from xorl_b200.utils import canary
+    buf = canary.guarded_empty((10, 7), torch.bfloat16, "cpu", "scratch.test", force=True)
+    assert buf.shape == (10, 7) and buf.dtype == torch.bfloat16 and buf.data_ptr() % 64 == 0
+    buf.fill_(1.0)                                            # writing the whole body is fine
+    assert canary.check_all() >= 1
+    raw = buf._xb_canary_raw
+    raw[canary.GUARD_BYTES + buf.numel() * 2 + 3] = 0         # one byte past the end
+    with pytest.raises(RuntimeError, match=r"scratch.test \(past its end\)"):
+        canary.check_all()
+    raw[canary.GUARD_BYTES + buf.numel() * 2 + 3] = canary.PATTERN
+    raw[5] = 1                                                # and one before the start
+    with pytest.raises(RuntimeError, match=r"scratch.test \(before its start\)"):
+        canary.check_all()
+    raw[5] = canary.PATTERN
+    del buf, raw
+    import gc
+    gc.collect()
+    canary.check_all()                                        # freed buffers leave the registry
+    assert not any(n == "scratch.test" for n, _, _ in canary._registry)
+    # off by default: a plain allocation
+    plain = canary.guarded_empty((4,), torch.float32, "cpu", "x")
+    assert not hasattr(plain, "_xb_canary_raw")

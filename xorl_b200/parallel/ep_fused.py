@@ -283,11 +283,13 @@ class _Scratch:
         self.overflow = torch.zeros(1, **i32)
         self.ret_rank = torch.empty(cap, **i32)
         self.ret_slot = torch.empty(cap, **i32)
-        self.h = torch.empty((cap, I2), **bf)
-        self.a = torch.empty((cap, act_I), **bf)
-        self.y = torch.empty((cap, H), **bf)          # forward: expert outputs; backward: dx rows
-        self.da = torch.empty((cap, act_I), **bf)
-        self.dys = torch.empty((S, H), **bf)
+        from ..utils.canary import guarded_empty
+        # capacity-sized activations indexed by computed rows: guarded when XORL_B200_CANARIES=1
+        self.h = guarded_empty((cap, I2), torch.bfloat16, dev, "ep_scratch.h")
+        self.a = guarded_empty((cap, act_I), torch.bfloat16, dev, "ep_scratch.a")
+        self.y = guarded_empty((cap, H), torch.bfloat16, dev, "ep_scratch.y")   # forward: expert outputs; backward: dx rows
+        self.da = guarded_empty((cap, act_I), torch.bfloat16, dev, "ep_scratch.da")
+        self.dys = guarded_empty((S, H), torch.bfloat16, dev, "ep_scratch.dys")
         self.slot_idx: Dict[int, torch.Tensor] = {}
         self.tok_of_slot: Dict[int, torch.Tensor] = {}
         self.q = None

@@ -192,8 +192,9 @@ class SymmetricTransport:
                                                 comm_stream.cuda_stream), "xb_symm_barrier")
             # 2. copy engines bring this rank's slice of every peer's buffer into local staging
             if self.staging is None or self.staging.numel() < self.world * g.shard_numel:
-                self.staging = torch.empty(self.world * max(gg_numel for gg_numel in self._shard_sizes),
-                                           device=self.engine.device, dtype=torch.bfloat16)
+                from ..utils.canary import guarded_empty
+                self.staging = guarded_empty(self.world * max(gg_numel for gg_numel in self._shard_sizes),
+                                             torch.bfloat16, self.engine.device, "zero_transport.staging")
             sbytes = g.shard_numel * 2
             _lib.check(self.lib.xb_symm_gather_slices_dma(self.staging.data_ptr(), grads, g.rank * sbytes, sbytes,
                                                           self.rank, self.world, comm_stream.cuda_stream),

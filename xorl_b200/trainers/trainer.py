@@ -267,6 +267,7 @@ class Trainer:
         self.sink = MetricsSink(t, self.ps.rank)
         self.scan_nonfinite = nonfinite_scan_enabled()
         self.watchdog = None
+        self._canaries = os.environ.get("XORL_B200_CANARIES", "0") == "1"
         # equal micro-batch lengths over the data-parallel group; no collective needs it, it only balances work
         self._sync_padding = os.environ.get("XORL_B200_SYNC_PADDING", "0") == "1" and self.ps.ulysses_size * self.ps.ringattn_size == 1
         if self.ps.world_size > 1 and dist.is_initialized() \
@@ -370,6 +371,9 @@ class Trainer:
         with self.timer.scope("optimizer"):
             self.optimizer.step(clip_coef=coef if t.max_grad_norm > 0 else None)
         self.lr_scheduler.step()
+        if self._canaries:
+            from ..utils import canary
+            canary.check_all()                      # XORL_B200_CANARIES=1: guard words around workspaces intact?
         if self.ps.world_size > 1 and self.ps.group(self.ps.loss_group_name) is not None:
             dist.all_reduce(total, group=self.ps.group(self.ps.loss_group_name))
         self.global_step += 1
