@@ -121,6 +121,28 @@ def bench_attn(a) -> Dict:
             r.update(lib="flash_attn2", lib_fwd_ms=ms_lf, lib_bwd_ms=ms_lb)
         except Exception as e:  # noqa: BLE001
             r["lib_error"] = str(e)[:100]
+        # torch SDPA on the cuDNN backend (the library's Blackwell attention); equal-length documents only:
+        # they become the batch dimension
+        if len(set(lens)) == 1:
+            try:
+                from torch.nn.attention import SDPBackend, sdpa_kernel
+                B, L = len(lens), lens[0]
+                q4, k4, v4 = (t.detach().view(B, L, -1, D).transpose(1, 2).contiguous().requires_grad_()
+                              for t in (q, k, v))
+                do4 = do.view(B, L, Hq, D).transpose(1, 2).contiguous()
+
+                def cf():
+                    with sdpa_kernel(SDPBackend.CUDNN_ATTENTION):
+                        holder["co"] = torch.nn.functional.scaled_dot_product_attention(
+                            q4, k4, v4, is_causal=True, enable_gqa=Hq != Hkv)
+
+                ms_cf = _time(cf, a.warmup, a.iters, a.flush)
+                cf()
+                ms_cb = _time(lambda: holder["co"].backward(do4, retain_graph=True), a.warmup, a.iters, a.flush)
+                r.update(cudnn_fwd_ms=ms_cf, cudnn_fwd_tflops=fl / ms_cf / 1e9, cudnn_bwd_ms=ms_cb,
+                         cudnn_bwd_tflops=2.5 * fl / ms_cb / 1e9)
+            except Exception as e:  # noqa: BLE001
+                r["cudnn_error"] = str(e)[:160]
     return r
 
 
