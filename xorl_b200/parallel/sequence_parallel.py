@@ -18,6 +18,7 @@ of ``2 * ring * ulysses``; ring rank ``r`` owns chunks ``r`` and ``2R-1-r`` of e
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -170,6 +171,70 @@ def _wait_all(reqs) -> None:
         r.wait()
 
 
+class _RingPeerKV:
+    """K/V of every ring rank readable in place by the attention kernels of all the others.
+
+    One symmetric heap per (ring group, size): a flag area for the bounded barrier of ``csrc/comm.cu`` and
+    two K/V slots.  A call writes this rank's K/V into slot ``n % 2``, runs the barrier (all ranks have
+    written; since a rank reaches the barrier of call ``n`` only after its kernels of call ``n - 1`` are
+    queued on the same stream, passing the barrier of call ``n - 1`` also means that nobody still reads the
+    slot of call ``n - 2``, which is why two slots and one barrier per call are enough) and returns tensors
+    that alias the peers' slots.  The block-pair attention kernels build their TMA descriptors over those
+    tensors, so remote K/V tiles cross NVLink inside the kernel's own load pipeline, tile by tile, under
+    the MMAs of the previous tile -- there is no exchange step to wait for and no receive buffer
+    (src/xorl/distributed/sequence_parallel/ring_attention.py:168-191 does this hop with batched
+    isend / irecv).  Plain TMA loads only: no cluster multicast."""
+    FLAG_BYTES = 16 * 1024
+    WAIT_MS = 2000
+    _cache: dict = {}
+
+    @classmethod
+    def get(cls, group, world: int, rank: int, numel: int, dtype, device) -> "Optional[_RingPeerKV]":
+        if os.environ.get("XORL_B200_RING_PEER_KV", "1") == "0" or device.type != "cuda" or dtype != torch.bfloat16:
+            return None
+        key = (id(group), device.index)
+        ws = cls._cache.get(key)
+        if ws is None or ws.capacity < numel:
+            try:
+                ws = cls(group, world, rank, numel, dtype, device)
+            except Exception as e:  # noqa: BLE001  (no symmetric memory on this system: rotate through NCCL)
+                from ..utils.logging import info_rank0
+                info_rank0(f"ring attention: peer-memory K/V unavailable ({type(e).__name__}: {e}); using send/recv")
+                os.environ["XORL_B200_RING_PEER_KV"] = "0"
+                return None
+            cls._cache[key] = ws
+        return ws
+
+    def __init__(self, group, world, rank, numel, dtype, device):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        self.world, self.rank, self.dtype = world, rank, dtype
+        self.capacity = numel
+        es = torch.empty(0, dtype=dtype).element_size()
+        self.slot_bytes = (numel * es + 255) // 256 * 256
+        self.heap = symm_mem.empty(self.FLAG_BYTES + 2 * self.slot_bytes, dtype=torch.uint8, device=device)
+        self.heap[:self.FLAG_BYTES].zero_()
+        self.hdl = symm_mem.rendezvous(self.heap, group)
+        self.flag_ptrs = (ctypes.c_ulonglong * world)(*[int(p) for p in self.hdl.buffer_ptrs])
+        self.epoch = 0
+        self.calls = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def publish(self, kv: torch.Tensor):
+        """Writes ``kv`` into the next slot, runs the barrier, returns a function rank -> that rank's K/V."""
+        es = kv.element_size()
+        slot = self.calls % 2
+        self.calls += 1
+        off = self.FLAG_BYTES + slot * self.slot_bytes
+        self.heap[off:off + kv.numel() * es].view(kv.dtype).view(kv.shape).copy_(kv)
+        self.epoch += 1
+        _lib.check(_lib.cuda_lib().xb_symm_barrier(self.flag_ptrs, 0, self.rank, self.world, self.epoch, self.WAIT_MS,
+                                                   _lib.stream_ptr()), "xb_symm_barrier")
+        shape = tuple(kv.shape)
+        return lambda j: self.hdl.get_buffer(j, shape, kv.dtype, off // es)
+
+
 class _RingAttention(torch.autograd.Function):
     """K/V blocks travel round the ring one hop per step (two receive buffers: the hop for step
     ``s+1`` is in flight while step ``s`` computes), so a rank never holds more than its own block
@@ -182,10 +247,24 @@ class _RingAttention(torch.autograd.Function):
     def forward(ctx, q, k, v, cu_blocks, group, rank, world, scale):
         T, Hq, D = q.shape
         kv = torch.stack([k.contiguous(), v.contiguous()])            # [2, T, Hkv, D]
-        bufs = [torch.empty_like(kv), torch.empty_like(kv)]
         out = torch.zeros((T, Hq, D), device=q.device, dtype=torch.float32)
         lse = torch.full((Hq, T), float("-inf"), device=q.device, dtype=torch.float32)
         qc = q.contiguous()
+        peers = _RingPeerKV.get(group, world, rank, kv.numel(), kv.dtype, kv.device)
+        if peers is not None:
+            # the kernels read every rank's K/V where it lies (TMA over NVLink): no hop, no receive buffer
+            kv_of = peers.publish(kv)
+            for s in range(world):
+                j = (rank - s) % world
+                cur = kv if j == rank else kv_of(j)
+                for k_starts, causal in _ring_calls(cu_blocks, rank, j):
+                    o_p, l_p = block_attention(qc, cur[0], cur[1], cu_blocks, k_starts, causal, scale)
+                    out, lse = _merge(out, lse, o_p, l_p)
+            out_lp = out.to(q.dtype)
+            ctx.save_for_backward(qc, kv, out_lp, lse, cu_blocks)
+            ctx.cfg = (group, rank, world, scale)
+            return out_lp
+        bufs = [torch.empty_like(kv), torch.empty_like(kv)]
         cur = kv
         for s in range(world):
             j = (rank - s) % world
@@ -209,13 +288,17 @@ class _RingAttention(torch.autograd.Function):
         dout = dout.contiguous()
         dq = torch.zeros((T, Hq, D), device=qc.device, dtype=torch.float32)
         delta = torch.empty((Hq, T), device=qc.device, dtype=torch.float32)
-        bufs = [torch.empty_like(kv), torch.empty_like(kv)]
+        peers = _RingPeerKV.get(group, world, rank, kv.numel(), kv.dtype, kv.device)
+        kv_of = peers.publish(kv) if peers is not None else None      # K/V read in place from the peers again
+        bufs = [torch.empty_like(kv), torch.empty_like(kv)] if peers is None else None
         acc_bufs = [torch.empty(kv.shape, device=kv.device, dtype=torch.float32) for _ in range(2)]
         cur, acc, acc_reqs = kv, None, ()
         first = True
         for s in range(world):
             j = (rank - s) % world
-            reqs = _ring_exchange(cur, bufs[s % 2], group, rank, world) if s < world - 1 else ()
+            if peers is not None:
+                cur = kv if j == rank else kv_of(j)
+            reqs = _ring_exchange(cur, bufs[s % 2], group, rank, world) if (peers is None and s < world - 1) else ()
             part = None
             for k_starts, causal in _ring_calls(cu_blocks, rank, j):
                 dk, dv = block_attention_bwd(qc, cur[0], cur[1], out, dout, lse, delta, dq, cu_blocks,
@@ -228,7 +311,7 @@ class _RingAttention(torch.autograd.Function):
                 part = part + acc_bufs[(s - 1) % 2]
             acc = part
             acc_reqs = _ring_exchange(acc, acc_bufs[s % 2], group, rank, world)
-            if s < world - 1:
+            if peers is None and s < world - 1:
                 _wait_all(reqs)
                 cur = bufs[s % 2]
         _wait_all(acc_reqs)                                          # the hop home: this rank's own block
