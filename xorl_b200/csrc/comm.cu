@@ -24,6 +24,7 @@
 //                              (fp32 sum in rank order + accumulate + norm partials at HBM speed)
 //   xb_symm_wait               block a stream until peers have released a buffer
 //   xb_peer_copy               bulk copy between two mapped buffers (weight sync)
+//   xb_peer_copy_2d            strided block copy by the copy engines (Ulysses head / sequence exchange)
 // These replace the NCCL all-gather / reduce-scatter issued by FSDP2 in the reference
 // (src/xorl/distributed/torch_parallelize.py:333-783) and its custom bf16 all-to-all reduce
 // (src/xorl/distributed/fsdp2/bf16_a2a_reduce.py:64-114).
@@ -321,4 +322,18 @@ XB_API int xb_peer_copy(void* dst, const void* src, long long bytes, int num_cta
   peer_copy_kernel<<<num_ctas, 512, 0, (cudaStream_t)stream>>>((uint4*)dst, (const uint4*)src,
                                                                bytes / 16);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Strided block copy by the copy engines (no SM): `height` rows of `width` bytes from src (row pitch
+// spitch) to dst (row pitch dpitch); either side may be a peer's mapped memory.  The Ulysses head /
+// sequence exchange is U such copies per rank: every rank writes its slice for rank u straight into
+// u's receive buffer.
+XB_API int xb_peer_copy_2d(void* dst, long long dpitch, const void* src, long long spitch, long long width,
+                           long long height, void* stream) {
+  if (width <= 0 || height <= 0) return 0;
+  if (dpitch < width || spitch < width) return -1;
+  return cudaMemcpy2DAsync(dst, (size_t)dpitch, src, (size_t)spitch, (size_t)width, (size_t)height,
+                           cudaMemcpyDeviceToDevice, (cudaStream_t)stream) == cudaSuccess
+             ? 0
+             : -11;
 }

@@ -67,6 +67,7 @@ _SIGNATURES = {
     "xb_ep_prepare_recv": [P, P, P, P, I, I, I, P],
     "xb_ep_push_rows": [P, L, P, P, P, P, I, I, I, P, L, P, P, I, I, I, I, I, P],
     "xb_peer_copy": [P, P, L, I, P],
+    "xb_peer_copy_2d": [P, L, P, L, L, L, P],
     "xb_gemm_fused": [P, P],
     "xb_rs_reduce": [P, I, I, I, P, L, P, P],
     "xb_moe_route": [P, L, P, P, P, P, P, I, I, I, I, I, F, P],

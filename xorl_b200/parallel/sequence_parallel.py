@@ -366,6 +366,115 @@ class _HeadToSeq(torch.autograd.Function):
         return recv.reshape(world * T, H // world, D), None, None
 
 
+class _PeerExchange:
+    """Head / sequence exchange of Ulysses without a collective library: every rank writes its slice for
+    rank ``u`` straight into ``u``'s receive slot (symmetric memory, one strided copy-engine transfer per
+    destination, no SM and no pack / unpack pass), then the bounded barrier of ``csrc/comm.cu`` tells
+    everybody that its slot is complete.  Two slots alternate, for the reason given in ``_RingPeerKV``
+    (src/xorl/distributed/sequence_parallel/ulysses.py:49-152 does this with all_to_all_single on packed
+    copies)."""
+    FLAG_BYTES = 16 * 1024
+    WAIT_MS = 2000
+    _cache: dict = {}
+
+    @classmethod
+    def get(cls, group, world, rank, nbytes, device) -> "Optional[_PeerExchange]":
+        if os.environ.get("XORL_B200_ULYSSES_PEER", "1") == "0" or device.type != "cuda":
+            return None
+        key = (id(group), device.index)
+        ws = cls._cache.get(key)
+        if ws is None or ws.slot_bytes < nbytes:
+            try:
+                ws = cls(group, world, rank, nbytes, device)
+            except Exception as e:  # noqa: BLE001
+                from ..utils.logging import info_rank0
+                info_rank0(f"ulysses: peer-memory exchange unavailable ({type(e).__name__}: {e}); using all_to_all")
+                os.environ["XORL_B200_ULYSSES_PEER"] = "0"
+                return None
+            cls._cache[key] = ws
+        return ws
+
+    def __init__(self, group, world, rank, nbytes, device):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        self.world, self.rank = world, rank
+        self.slot_bytes = (nbytes + 255) // 256 * 256
+        self.heap = symm_mem.empty(self.FLAG_BYTES + 2 * self.slot_bytes, dtype=torch.uint8, device=device)
+        self.heap[:self.FLAG_BYTES].zero_()
+        self.hdl = symm_mem.rendezvous(self.heap, group)
+        self.base = [int(p) for p in self.hdl.buffer_ptrs]
+        self.flag_ptrs = (ctypes.c_ulonglong * world)(*self.base)
+        self.epoch = 0
+        self.calls = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def _exchange(self, pieces, out_shape, dtype) -> torch.Tensor:
+        """``pieces``: per destination rank (dst byte offset inside the slot, dst pitch, src pointer, src pitch,
+        width, height).  Returns this rank's slot viewed as ``out_shape`` (valid until two calls later)."""
+        lib = _lib.cuda_lib()
+        slot = self.calls % 2
+        self.calls += 1
+        off = self.FLAG_BYTES + slot * self.slot_bytes
+        st = _lib.stream_ptr()
+        for u, (doff, dpitch, sptr, spitch, width, height) in enumerate(pieces):
+            _lib.check(lib.xb_peer_copy_2d(self.base[u] + off + doff, dpitch, sptr, spitch, width, height, st),
+                       "xb_peer_copy_2d")
+        self.epoch += 1
+        _lib.check(lib.xb_symm_barrier(self.flag_ptrs, 0, self.rank, self.world, self.epoch, self.WAIT_MS, st),
+                   "xb_symm_barrier")
+        n = 1
+        for d in out_shape:
+            n *= d
+        es = torch.empty(0, dtype=dtype).element_size()
+        return self.heap[off:off + n * es].view(dtype).view(out_shape)
+
+    def seq_to_head(self, x: torch.Tensor) -> torch.Tensor:
+        """[T, U*h, D] (all heads, local tokens) -> [U*T, h, D] (local heads, the group's tokens)."""
+        T, H, D = x.shape
+        U, es = self.world, x.element_size()
+        row = (H // U) * D * es
+        pieces = [(self.rank * T * row, row, x.data_ptr() + u * row, H * D * es, row, T) for u in range(U)]
+        return self._exchange(pieces, (U * T, H // U, D), x.dtype)
+
+    def head_to_seq(self, x: torch.Tensor) -> torch.Tensor:
+        """[U*T, h, D] -> [T, U*h, D]."""
+        TT, h, D = x.shape
+        U, es = self.world, x.element_size()
+        T = TT // U
+        row = h * D * es
+        pieces = [(self.rank * row, U * row, x.data_ptr() + u * T * row, row, row, T) for u in range(U)]
+        return self._exchange(pieces, (T, U * h, D), x.dtype)
+
+
+def _peer_exchange_for(x: torch.Tensor, group, world):
+    if not x.is_cuda:
+        return None
+    return _PeerExchange.get(group, world, dist.get_rank(group), x.numel() * x.element_size(), x.device)
+
+
+class _SeqToHeadPeer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, world, ex):
+        ctx.group, ctx.world, ctx.ex = group, world, ex
+        return ex.seq_to_head(x.contiguous())          # a view of the receive slot: consume before two more exchanges
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.ex.head_to_seq(g.contiguous()).clone(), None, None, None
+
+
+class _HeadToSeqPeer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, world, ex):
+        ctx.group, ctx.world, ctx.ex = group, world, ex
+        return ex.head_to_seq(x.contiguous()).clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.ex.seq_to_head(g.contiguous()).clone(), None, None, None
+
+
 # --------------------------------------------------------------------------------------------
 # strategy object used by the attention layers
 # --------------------------------------------------------------------------------------------
@@ -430,7 +539,13 @@ class ContextParallelStrategy:
             # one all-to-all for q, k and v: heads are laid out (ulysses rank, [q | k | v] heads of that rank)
             hq, hk = Hq // U, k.shape[1] // U
             packed = torch.cat([q.reshape(T, U, hq, D), k.reshape(T, U, hk, D), v.reshape(T, U, hk, D)], 2)
-            packed = _SeqToHead.apply(packed.reshape(T, U * (hq + 2 * hk), D), self.u_group, U)
+            packed = packed.reshape(T, U * (hq + 2 * hk), D)
+            ex = _peer_exchange_for(packed, self.u_group, U)
+            if ex is not None:
+                # the receive slot is read once, by the gather that puts tokens into document order
+                packed = _SeqToHeadPeer.apply(packed, self.u_group, U, ex)
+            else:
+                packed = _SeqToHead.apply(packed, self.u_group, U)
             packed = packed.index_select(0, ctx.aux["cp_gather_idx"])
             q, k, v = packed.split([hq, hk, hk], dim=1)
         if self.R > 1:
@@ -439,7 +554,10 @@ class ContextParallelStrategy:
         else:
             out = attn_ops.flash_attn_varlen(q, k, v, ctx.aux["cp_ring_cu"], ctx.causal, attn.scale)
         if U > 1:
-            out = _HeadToSeq.apply(out.index_select(0, ctx.aux["cp_scatter_idx"]), self.u_group, U)
+            out = out.index_select(0, ctx.aux["cp_scatter_idx"])
+            ex = _peer_exchange_for(out, self.u_group, U)
+            out = _HeadToSeqPeer.apply(out, self.u_group, U, ex) if ex is not None \
+                else _HeadToSeq.apply(out, self.u_group, U)
         return out.reshape(T, Hq * D)
 
 
