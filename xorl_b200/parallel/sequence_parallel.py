@@ -183,7 +183,7 @@ class _RingPeerKV:
     tensors, so remote K/V tiles cross NVLink inside the kernel's own load pipeline, tile by tile, under
     the MMAs of the previous tile -- there is no exchange step to wait for and no receive buffer
     (src/xorl/distributed/sequence_parallel/ring_attention.py:168-191 does this hop with batched
-    isend / irecv).  Plain TMA loads only: no cluster multicast."""
+    isend / irecv).  The loads are the kernels' ordinary per-CTA TMA tile loads."""
     FLAG_BYTES = 16 * 1024
     WAIT_MS = 2000
     _cache: dict = {}
