@@ -59,3 +59,37 @@ def test_gated_deltanet_family_under_ulysses(tmp_path, preset):
     got = _losses(tmp_path, "gdn_cp")
     for a, b in zip(ref, got):
         assert abs(a - b) < 3e-4, (ref, got)
+
+
+def test_peer_exchange_copy_plans_equal_the_all_to_all_layouts():
+    """The strided copies of the copy-engine Ulysses exchange, replayed on host byte buffers for every
+    rank, give exactly what the all-to-all formulation gives."""
+    import numpy as np
+    import torch
+    from xorl_b200.parallel.sequence_parallel import _PeerExchange
+    U, T, h, D, es = 4, 6, 3, 8, 2
+    H = U * h
+    xs = [torch.randn(T, H, D).to(torch.bfloat16) for _ in range(U)]                    # per-rank inputs
+
+    def replay(pieces_of, srcs, nbytes):
+        slots = [np.zeros(nbytes, dtype=np.uint8) for _ in range(U)]
+        for r in range(U):
+            src = srcs[r].contiguous().view(torch.uint8).reshape(-1).numpy()
+            for u, (doff, dpitch, soff, spitch, width, rows) in enumerate(pieces_of(r)):
+                for i in range(rows):
+                    slots[u][doff + i * dpitch: doff + i * dpitch + width] = src[soff + i * spitch: soff + i * spitch + width]
+        return slots
+
+    nbytes = T * H * D * es
+    got = replay(lambda r: _PeerExchange.seq_to_head_pieces(r, T, H, D, U, es), xs, nbytes)
+    for u in range(U):
+        want = torch.cat([xs[r].reshape(T, U, h, D)[:, u] for r in range(U)], 0)          # [U*T, h, D]
+        out = torch.from_numpy(got[u]).view(torch.bfloat16).reshape(U * T, h, D)
+        assert torch.equal(out, want)
+    # and back: [U*T, h, D] on every rank -> [T, U*h, D]
+    ys = [torch.randn(U * T, h, D).to(torch.bfloat16) for _ in range(U)]
+    got = replay(lambda r: _PeerExchange.head_to_seq_pieces(r, T, h, D, U, es), ys, nbytes)
+    for u in range(U):
+        want = torch.stack([ys[r].reshape(U, T, h, D)[u] for r in range(U)], 1).reshape(T, U * h, D)
+        out = torch.from_numpy(got[u]).view(torch.bfloat16).reshape(T, U * h, D)
+        assert torch.equal(out, want)

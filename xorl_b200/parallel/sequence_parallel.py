@@ -429,22 +429,32 @@ class _PeerExchange:
         es = torch.empty(0, dtype=dtype).element_size()
         return self.heap[off:off + n * es].view(dtype).view(out_shape)
 
+    @staticmethod
+    def seq_to_head_pieces(rank: int, T: int, H: int, D: int, U: int, es: int):
+        """Per destination rank: (dst byte offset in its slot, dst pitch, src byte offset, src pitch, width, rows)."""
+        row = (H // U) * D * es
+        return [(rank * T * row, row, u * row, H * D * es, row, T) for u in range(U)]
+
+    @staticmethod
+    def head_to_seq_pieces(rank: int, T: int, h: int, D: int, U: int, es: int):
+        row = h * D * es
+        return [(rank * row, U * row, u * T * row, row, row, T) for u in range(U)]
+
+    def _with_base(self, pieces, base_ptr: int):
+        return [(doff, dp, base_ptr + soff, sp, w, n) for doff, dp, soff, sp, w, n in pieces]
+
     def seq_to_head(self, x: torch.Tensor) -> torch.Tensor:
         """[T, U*h, D] (all heads, local tokens) -> [U*T, h, D] (local heads, the group's tokens)."""
         T, H, D = x.shape
-        U, es = self.world, x.element_size()
-        row = (H // U) * D * es
-        pieces = [(self.rank * T * row, row, x.data_ptr() + u * row, H * D * es, row, T) for u in range(U)]
-        return self._exchange(pieces, (U * T, H // U, D), x.dtype)
+        pieces = self.seq_to_head_pieces(self.rank, T, H, D, self.world, x.element_size())
+        return self._exchange(self._with_base(pieces, x.data_ptr()), (self.world * T, H // self.world, D), x.dtype)
 
     def head_to_seq(self, x: torch.Tensor) -> torch.Tensor:
         """[U*T, h, D] -> [T, U*h, D]."""
         TT, h, D = x.shape
-        U, es = self.world, x.element_size()
-        T = TT // U
-        row = h * D * es
-        pieces = [(self.rank * row, U * row, x.data_ptr() + u * T * row, row, row, T) for u in range(U)]
-        return self._exchange(pieces, (T, U * h, D), x.dtype)
+        T = TT // self.world
+        pieces = self.head_to_seq_pieces(self.rank, T, h, D, self.world, x.element_size())
+        return self._exchange(self._with_base(pieces, x.data_ptr()), (T, self.world * h, D), x.dtype)
 
 
 def _peer_exchange_for(x: torch.Tensor, group, world):
