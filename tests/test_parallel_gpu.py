@@ -115,6 +115,14 @@ def test_dense_parallel_modes(tmp_path, tmp_path_factory, name, nproc, dp, train
     ref = _reference(tmp_path_factory, "small-qwen3", FOUNDATION.get(name))
     got = _run(tmp_path, name, nproc, dp=dp, foundation=FOUNDATION.get(name), **train)
     _check(ref, got)
+    if train.get("ringattn_parallel_size", 1) > 1 or train.get("ulysses_parallel_size", 1) > 1:
+        # the context-parallel exchanges went through peer memory, not through a collective library
+        with open(tmp_path / name / "training_metrics.json") as f:
+            calls = json.load(f)["cp_peer_paths"]
+        if train.get("ringattn_parallel_size", 1) > 1:
+            assert calls["ring_kv_published"] > 0, calls
+        if train.get("ulysses_parallel_size", 1) > 1:
+            assert calls["ulysses_exchanges"] > 0, calls
     if train.get("tensor_parallel_sequence_parallel"):
         # every collective GEMM of the run went through the single-kernel path
         with open(tmp_path / name / "training_metrics.json") as f:

@@ -171,6 +171,10 @@ def _wait_all(reqs) -> None:
         r.wait()
 
 
+# how often the peer-memory forms ran in this process (the trainer writes them to training_metrics.json)
+PEER_PATH_CALLS = {"ring_kv_published": 0, "ulysses_exchanges": 0}
+
+
 class _RingPeerKV:
     """K/V of every ring rank readable in place by the attention kernels of all the others.
 
@@ -226,6 +230,7 @@ class _RingPeerKV:
         es = kv.element_size()
         slot = self.calls % 2
         self.calls += 1
+        PEER_PATH_CALLS["ring_kv_published"] += 1
         off = self.FLAG_BYTES + slot * self.slot_bytes
         self.heap[off:off + kv.numel() * es].view(kv.dtype).view(kv.shape).copy_(kv)
         self.epoch += 1
@@ -415,6 +420,7 @@ class _PeerExchange:
         lib = _lib.cuda_lib()
         slot = self.calls % 2
         self.calls += 1
+        PEER_PATH_CALLS["ulysses_exchanges"] += 1
         off = self.FLAG_BYTES + slot * self.slot_bytes
         st = _lib.stream_ptr()
         for u, (doff, dpitch, sptr, spitch, width, height) in enumerate(pieces):

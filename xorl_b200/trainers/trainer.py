@@ -546,6 +546,9 @@ class Trainer:
                   "metrics": self.metrics_history[-1] if self.metrics_history else {}}
         if self.pp_runner is not None and self.pp_runner.bubble_stats:
             result["pp_bubble"] = dict(self.pp_runner.bubble_stats, pp_rank=self.ps.pp_rank)
+        if self.ps.sp_size > 1:
+            from ..parallel.sequence_parallel import PEER_PATH_CALLS
+            result["cp_peer_paths"] = dict(PEER_PATH_CALLS)
         if self.ps.tp_sequence_parallel:
             from ..parallel.tp_fused import sp_context
             sp = sp_context()
