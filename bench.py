@@ -38,6 +38,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count")
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--ulysses", type=int, default=1, help="Ulysses sequence-parallel size (long-context runs)")
+    ap.add_argument("--ring", type=int, default=1, help="ring-attention size (long-context runs)")
+    ap.add_argument("--single-doc", action="store_true", help="one document of --seq-len tokens per step")
     ap.add_argument("--ep", type=int, default=0,
                     help="expert-parallel size for MoE models (0: all ranks for MoE, 1 for dense)")
     ap.add_argument("--ep-dispatch", default="fused", choices=["fused", "alltoall"])
@@ -53,7 +56,7 @@ def parse():
 
 
 # ------------------------------------------------------------------------------------------------
-def make_packed_batch(seq_len: int, vocab: int, seed: int):
+def make_packed_batch(seq_len: int, vocab: int, seed: int, single_doc: bool = False):
     """One packed row: documents with lengths uniform in [256, seq_len], tokens uniform over the
     vocabulary; the last document is cut so the row holds exactly seq_len tokens.  Returned in
     pinned host memory (next-token labels, last target of every document ignored)."""
@@ -63,7 +66,7 @@ def make_packed_batch(seq_len: int, vocab: int, seed: int):
     ids = rng.integers(0, vocab, size=seq_len + 1, dtype=np.int64)
     cu = [0]
     while cu[-1] < seq_len:
-        cu.append(min(seq_len, cu[-1] + int(rng.integers(256, seq_len + 1))))
+        cu.append(seq_len if single_doc else min(seq_len, cu[-1] + int(rng.integers(256, seq_len + 1))))
     labels = ids[1:].copy()
     pos = np.zeros(seq_len, dtype=np.int64)
     for a, b in zip(cu[:-1], cu[1:]):
@@ -147,10 +150,10 @@ def resolve_recompute(a, cfg, world: int) -> str:
     if cfg.is_moe:
         return "recompute_full_layer"      # expert workspaces are reused layer by layer
     params = cfg.num_parameters() if hasattr(cfg, "num_parameters") else 8.2e9
-    state = 18.0 * params / world + (2.0 * params if world > 1 else 0.0)
+    state = 18.0 * params / world + (2.0 * params if world > 1 else 0.0)      # ZeRO shards over dp x cp
     L, H, I = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size
     qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
-    acts = a.seq_len * 2.0 * L * (6 * H + 2 * qkv + 3 * I)
+    acts = a.seq_len / max(1, a.ulysses * a.ring) * 2.0 * L * (6 * H + 2 * qkv + 3 * I)
     return "no_recompute" if state + acts + 12e9 < total else "recompute_full_layer"
 
 
@@ -192,13 +195,26 @@ def run_ours(a):
                                 gradient_checkpointing_method=recompute, init_device="meta",
                                 load_weights_mode="skip", save_hf_weights=False, use_wandb=False, save_steps=0,
                                 save_epochs=0,
-                                comm_backend=a.comm, max_steps=10 ** 9, ce_num_chunks=4, **moe_train))
+                                comm_backend=a.comm, max_steps=10 ** 9, ce_num_chunks=4,
+                                ulysses_parallel_size=a.ulysses, ringattn_parallel_size=a.ring, **moe_train))
     trainer = Trainer(args, model_config=cfg)
     dev = trainer.device
     torch.cuda.reset_peak_memory_stats()
     n_total = a.warmup + a.steps
-    host_batches = [make_packed_batch(a.seq_len, cfg.vocab_size, 1000 * rank + s)
-                    for s in range(n_total)]
+    cp = a.ulysses * a.ring
+    if cp > 1:
+        # every rank of a context-parallel group works on the same row and keeps its shard of it
+        from xorl_b200.data import SequenceShardCollator
+        ps = trainer.ps
+        shard = SequenceShardCollator(a.ring, a.ulysses, ps.ringattn_rank, ps.ulysses_rank)
+        host_batches = []
+        for s in range(n_total):
+            row = make_packed_batch(a.seq_len, cfg.vocab_size, 1000 * ps.dp_rank + s, a.single_doc)
+            row.pop("num_valid_tokens")
+            host_batches.append({k: (v.pin_memory() if torch.is_tensor(v) else v) for k, v in shard(row).items()})
+    else:
+        host_batches = [make_packed_batch(a.seq_len, cfg.vocab_size, 1000 * rank + s, a.single_doc)
+                        for s in range(n_total)]
 
     def barrier():
         if world > 1:
@@ -226,7 +242,7 @@ def run_ours(a):
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_per_step = ms.item() / a.steps
-    tokens_per_step = a.seq_len * world
+    tokens_per_step = a.seq_len * world // cp
     value = tokens_per_step / (ms_per_step / 1e3)
     last_loss = float(out["loss"])
 
@@ -255,14 +271,15 @@ def run_ours(a):
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": a.model + (f"[{a.layers} layers: DEBUG, not the named model]" if a.layers else ""),
-                       "global_batch": world, "seq_len": a.seq_len,
+                       "global_batch": world // cp, "seq_len": a.seq_len,
                        "parallelism": f"fsdp{world}" + ("-fused" if fused else "-nccl" if world > 1 else "")
-                       + (f"-ep{ep}-{a.ep_dispatch}" if ep > 1 else ""),
+                       + (f"-ep{ep}-{a.ep_dispatch}" if ep > 1 else "")
+                       + (f"-ring{a.ring}-ulysses{a.ulysses}" if cp > 1 else ""),
                        "optimizer": "adamw fp32 master+states", "recompute": recompute,
                        **({"experts": "block_fp8 e4m3 (1x128 / 128x128 power-of-two scales), bf16 elsewhere"
                            if a.experts_dtype == "fp8" else "bf16"} if cfg.is_moe else {}),
                        "l2": "per-step working set (16 GB of bf16 weights + activations) >> 126 MB L2",
-                       "packed_docs": "lengths U[256,4096], tokens U[vocab]"},
+                       "packed_docs": ("one document per row" if a.single_doc else "lengths U[256,seq_len]") + ", tokens U[vocab]"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "loss": last_loss, "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
             "status_words": status[:4],
