@@ -4,15 +4,19 @@ Token layout (see ``data.collators.SequenceShardCollator``): every document is p
 of ``2 * ring * ulysses``; ring rank ``r`` owns chunks ``r`` and ``2R-1-r`` of every document
 (zigzag, balanced causal work) and inside a ring rank the Ulysses ranks own contiguous slices.
 
-* Ulysses: q/k/v ``[T_loc, H, D] -> [T_ring, H/U, D]`` by all-to-all before attention and back
-  after (src/xorl/distributed/sequence_parallel/ulysses.py:49-152, strategy.py:164-247).
+* Ulysses: q/k/v ``[T_loc, H, D] -> [T_ring, H/U, D]`` in one exchange before attention and back
+  after (src/xorl/distributed/sequence_parallel/ulysses.py:49-152, strategy.py:164-247).  On GPUs the
+  exchange is ``_PeerExchange``: strided copy-engine writes into the peers' symmetric receive slots;
+  elsewhere all_to_all_single.
 * Ring: every rank attends its queries to the K/V of every ring rank.  For source rank ``j`` the
   zigzag layout reduces the causal structure to whole-block pairs of equal length — (q_a,k_a) and
   (q_b,k_b) causal plus (q_b,k_a) full when ``j == r``; (q_a,k_a),(q_b,k_a) full when ``j < r``;
   (q_b,k_a),(q_b,k_b) full when ``j > r`` — each one call of the block-pair attention kernel, merged
   by log-sum-exp (src/xorl/distributed/sequence_parallel/ring_attention.py:28-77,202-253,331-843).
-  K/V blocks rotate peer to peer with the next hop in flight under the current block's kernels; backward
-  rotates them again with the dK/dV accumulator of each block travelling along; dQ accumulates locally.
+  On GPUs every rank publishes its K/V in a symmetric slot and the attention kernels load the peers'
+  tiles in place (``_RingPeerKV``); elsewhere K/V blocks rotate peer to peer with the next hop in flight
+  under the current block's kernels.  Backward reads K/V the same way; the dK/dV accumulator of each
+  block travels rank to rank; dQ accumulates locally.
 * Hybrid: Ulysses inside each ring rank group, ring across groups (strategy.py:428-477).
 """
 from __future__ import annotations
