@@ -180,18 +180,20 @@ PEER_PATH_CALLS = {"ring_kv_published": 0, "ulysses_exchanges": 0}
 
 
 class _RingPeerKV:
-    """K/V of every ring rank readable in place by the attention kernels of all the others.
+    """K/V of every ring rank published in symmetric memory and pulled by the copy engines.
 
     One symmetric heap per (ring group, size): a flag area for the bounded barrier of ``csrc/comm.cu`` and
-    two K/V slots.  A call writes this rank's K/V into slot ``n % 2``, runs the barrier (all ranks have
-    written; since a rank reaches the barrier of call ``n`` only after its kernels of call ``n - 1`` are
-    queued on the same stream, passing the barrier of call ``n - 1`` also means that nobody still reads the
-    slot of call ``n - 2``, which is why two slots and one barrier per call are enough) and returns tensors
-    that alias the peers' slots.  The block-pair attention kernels build their TMA descriptors over those
-    tensors, so remote K/V tiles cross NVLink inside the kernel's own load pipeline, tile by tile, under
-    the MMAs of the previous tile -- there is no exchange step to wait for and no receive buffer
-    (src/xorl/distributed/sequence_parallel/ring_attention.py:168-191 does this hop with batched
-    isend / irecv).  The loads are the kernels' ordinary per-CTA TMA tile loads."""
+    two K/V slots.  A call writes this rank's K/V into slot ``n % 2`` and runs the barrier (all ranks have
+    written; since a rank reaches the barrier of call ``n`` only after its work of call ``n - 1`` is queued
+    on the same stream, passing the barrier of call ``n - 1`` also means that nobody still reads the slot of
+    call ``n - 2``: two slots and one barrier per call are enough).  The block of the rank whose turn comes
+    next is then copied from its owner's slot into one of two local buffers by a copy engine on a side
+    stream, under the attention kernels of the current block, and the kernels read local memory: every
+    remote block crosses NVLink exactly once, straight from its owner (no hop-by-hop rotation), without a
+    collective library and without an SM.  (Letting the attention kernels load the peers' tiles in place
+    was measured first: every query tile re-reads the remote K/V over NVLink, which does not pass through
+    the local L2, and a 65 536-token step took twice as long.)
+    (src/xorl/distributed/sequence_parallel/ring_attention.py:168-191 does the hop with batched isend / irecv.)"""
     FLAG_BYTES = 16 * 1024
     WAIT_MS = 2000
     _cache: dict = {}
@@ -223,14 +225,16 @@ class _RingPeerKV:
         self.heap = symm_mem.empty(self.FLAG_BYTES + 2 * self.slot_bytes, dtype=torch.uint8, device=device)
         self.heap[:self.FLAG_BYTES].zero_()
         self.hdl = symm_mem.rendezvous(self.heap, group)
-        self.flag_ptrs = (ctypes.c_ulonglong * world)(*[int(p) for p in self.hdl.buffer_ptrs])
+        self.base = [int(p) for p in self.hdl.buffer_ptrs]
+        self.flag_ptrs = (ctypes.c_ulonglong * world)(*self.base)
         self.epoch = 0
         self.calls = 0
+        self._bufs = None
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
-    def publish(self, kv: torch.Tensor):
-        """Writes ``kv`` into the next slot, runs the barrier, returns a function rank -> that rank's K/V."""
+    def publish(self, kv: torch.Tensor) -> "_RingFetch":
+        """Writes ``kv`` into the next slot, runs the barrier, returns the fetcher of the peers' blocks."""
         es = kv.element_size()
         slot = self.calls % 2
         self.calls += 1
@@ -240,8 +244,65 @@ class _RingPeerKV:
         self.epoch += 1
         _lib.check(_lib.cuda_lib().xb_symm_barrier(self.flag_ptrs, 0, self.rank, self.world, self.epoch, self.WAIT_MS,
                                                    _lib.stream_ptr()), "xb_symm_barrier")
-        shape = tuple(kv.shape)
-        return lambda j: self.hdl.get_buffer(j, shape, kv.dtype, off // es)
+        return _RingFetch(self, kv, off)
+
+
+class _RingFetch:
+    """Double-buffered copy-engine pulls of the peers' K/V blocks for one ring pass.  ``prefetch(j)`` starts
+    the copy of rank ``j``'s block on the side stream (after the compute stream has released the buffer it
+    lands in); ``take(j)`` makes the compute stream wait for it and returns the local tensor."""
+
+    def __init__(self, ws: _RingPeerKV, kv: torch.Tensor, off: int):
+        self.ws, self.kv, self.off = ws, kv, off
+        self.nbytes = kv.numel() * kv.element_size()
+        if getattr(ws, "_bufs", None) is None or ws._bufs[0].numel() < kv.numel() or ws._bufs[0].dtype != kv.dtype:
+            ws._bufs = [torch.empty(kv.numel(), dtype=kv.dtype, device=kv.device) for _ in range(2)]
+            ws._copy_stream = torch.cuda.Stream(device=kv.device)
+            ws._free = [None, None]                 # event: the compute stream is done with the buffer
+        self.n = 0
+        self.pending = {}
+
+    def prefetch(self, j: int) -> None:
+        ws = self.ws
+        b = self.n % 2
+        self.n += 1
+        cs = ws._copy_stream
+        cs.wait_stream(torch.cuda.current_stream())          # the barrier (peers have written) precedes the copy
+        if ws._free[b] is not None:
+            cs.wait_event(ws._free[b])
+        _lib.check(_lib.cuda_lib().xb_peer_copy_2d(ws._bufs[b].data_ptr(), self.nbytes, ws.base[j] + self.off,
+                                                   self.nbytes, self.nbytes, 1, cs.cuda_stream), "xb_peer_copy_2d")
+        ev = torch.cuda.Event()
+        ev.record(cs)
+        self.pending[j] = (b, ev)
+
+    def take(self, j: int) -> torch.Tensor:
+        b, ev = self.pending.pop(j)
+        torch.cuda.current_stream().wait_event(ev)
+        self._held = b
+        return self.ws._bufs[b][:self.kv.numel()].view(self.kv.shape)
+
+    def release(self) -> None:
+        """The kernels that read the buffer returned by the last ``take`` have been queued."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        self.ws._free[self._held] = ev
+
+
+def _ring_blocks(fetch: Optional["_RingFetch"], kv: torch.Tensor, rank: int, world: int):
+    """Yields (source rank, its K/V) in ring order with the next block's copy in flight."""
+    order = [(rank - s) % world for s in range(world)]
+    if world > 1:
+        fetch.prefetch(order[1])
+    for s, j in enumerate(order):
+        if j == rank:
+            yield j, kv
+            continue
+        cur = fetch.take(j)
+        if s + 1 < world:
+            fetch.prefetch(order[s + 1])
+        yield j, cur
+        fetch.release()
 
 
 class _RingAttention(torch.autograd.Function):
@@ -261,11 +322,8 @@ class _RingAttention(torch.autograd.Function):
         qc = q.contiguous()
         peers = _RingPeerKV.get(group, world, rank, kv.numel(), kv.dtype, kv.device)
         if peers is not None:
-            # the kernels read every rank's K/V where it lies (TMA over NVLink): no hop, no receive buffer
-            kv_of = peers.publish(kv)
-            for s in range(world):
-                j = (rank - s) % world
-                cur = kv if j == rank else kv_of(j)
+            # every peer's block is pulled from its owner's slot by a copy engine, one block ahead
+            for j, cur in _ring_blocks(peers.publish(kv), kv, rank, world):
                 for k_starts, causal in _ring_calls(cu_blocks, rank, j):
                     o_p, l_p = block_attention(qc, cur[0], cur[1], cu_blocks, k_starts, causal, scale)
                     out, lse = _merge(out, lse, o_p, l_p)
@@ -298,15 +356,23 @@ class _RingAttention(torch.autograd.Function):
         dq = torch.zeros((T, Hq, D), device=qc.device, dtype=torch.float32)
         delta = torch.empty((Hq, T), device=qc.device, dtype=torch.float32)
         peers = _RingPeerKV.get(group, world, rank, kv.numel(), kv.dtype, kv.device)
-        kv_of = peers.publish(kv) if peers is not None else None      # K/V read in place from the peers again
+        fetch = peers.publish(kv) if peers is not None else None      # the peers' blocks are pulled again, one ahead
+        order = [(rank - s) % world for s in range(world)]
+        if fetch is not None and world > 1:
+            fetch.prefetch(order[1])
         bufs = [torch.empty_like(kv), torch.empty_like(kv)] if peers is None else None
         acc_bufs = [torch.empty(kv.shape, device=kv.device, dtype=torch.float32) for _ in range(2)]
         cur, acc, acc_reqs = kv, None, ()
         first = True
         for s in range(world):
-            j = (rank - s) % world
-            if peers is not None:
-                cur = kv if j == rank else kv_of(j)
+            j = order[s]
+            if fetch is not None:
+                if j == rank:
+                    cur = kv
+                else:
+                    cur = fetch.take(j)
+                    if s + 1 < world:
+                        fetch.prefetch(order[s + 1])
             reqs = _ring_exchange(cur, bufs[s % 2], group, rank, world) if (peers is None and s < world - 1) else ()
             part = None
             for k_starts, causal in _ring_calls(cu_blocks, rank, j):
@@ -315,6 +381,8 @@ class _RingAttention(torch.autograd.Function):
                 first = False
                 both = torch.stack([dk, dv])
                 part = both if part is None else part + both
+            if fetch is not None and j != rank:
+                fetch.release()
             if s > 0:
                 _wait_all(acc_reqs)                                  # block j's accumulator so far
                 part = part + acc_bufs[(s - 1) % 2]
