@@ -87,13 +87,18 @@ class _Workspace:
         _lib.check(self.lib.xb_symm_wait(ctypes.c_void_p(self.local_flags(slot)), self.N, self.rank,
                                          epoch, WAIT_MS, _lib.stream_ptr()), "xb_symm_wait")
 
-    def push(self, src, src_row, dest_rank, dest_row, tag, dst_name, meta_name, slot, counter, key):
+    def push(self, src, src_row, dest_rank, dest_row, tag, dst_name, meta_name, slot, counter, key,
+             row_bytes: int = 0):
+        """``row_bytes`` (default: one bf16 row of width H) is the payload of a row and the row pitch of both
+        the source and the destination when given (quantised rows: e4m3 values followed by their scales)."""
         self.epoch[key] += 1
         n_items = dest_rank.numel()
+        rb = row_bytes or self.H * 2
+        src_ld = row_bytes or src.stride(0) * src.element_size()
         _lib.check(self.lib.xb_ep_push_rows(
-            src.data_ptr(), src.stride(0) * 2, _lib.ptr(src_row), dest_rank.data_ptr(),
-            dest_row.data_ptr(), _lib.ptr(tag), 24, n_items, self.H * 2, self.ptrs(self.o[dst_name]),
-            self.H * 2, None if meta_name is None else self.ptrs(self.o[meta_name]), self.ptrs(0),
+            src.data_ptr(), src_ld, _lib.ptr(src_row), dest_rank.data_ptr(),
+            dest_row.data_ptr(), _lib.ptr(tag), 24, n_items, rb, self.ptrs(self.o[dst_name]),
+            rb, None if meta_name is None else self.ptrs(self.o[meta_name]), self.ptrs(0),
             slot, counter, self.rank, self.N, self.epoch[key], _lib.stream_ptr()), "xb_ep_push_rows")
         self.wait(slot, self.epoch[key])
 
@@ -300,6 +305,13 @@ class _Scratch:
             self.q = torch.empty((cap, kmax), **u8)
             self.sf = torch.full((cap, sf_stride(kmax)), 127, **u8)
 
+    def quantised_tokens(self, T: int, row_bytes: int) -> torch.Tensor:
+        """[T, row_bytes] bytes: e4m3 values of a token followed by its 1 x 128 scales (16-byte padded)."""
+        buf = getattr(self, "_xrow", None)
+        if buf is None or buf.numel() < T * row_bytes:
+            buf = self._xrow = torch.zeros(T * row_bytes, device=self.h.device, dtype=torch.uint8)
+        return buf[:T * row_bytes].view(T, row_bytes)
+
     def slot_tables(self, k: int, dev):
         if k not in self.slot_idx:
             S = self.dest_rank.numel()
@@ -374,14 +386,37 @@ class _FusedEPMoE(torch.autograd.Function):
         PhaseTimes.add("fwd_plan", t0, t1)
         recv = ws.view("recv_f", ws.cap, torch.bfloat16, H)
         meta = ws.view("meta_f", ws.cap, torch.int32, 1)
-        _lib.check(lib.xb_ep_prepare_recv(recv.data_ptr(), meta.data_ptr(), sc.seg.data_ptr(), sc.tot.data_ptr(), El,
-                                          ws.cap, H * 2, st), "xb_ep_prepare_recv")
-        ws.push(x, tok_of_slot[:S], sc.dest_rank[:S], sc.dest_row[:S], None, "recv_f", "meta_f", S_DISP, C_DISP, "disp")
+        # A pass that no backward follows (the first forward under recomputation, evaluation) keeps nothing
+        # of the received rows, so with fp8 experts the tokens are quantised once at the source (T rows
+        # instead of the T * k received ones) and travel as e4m3 values + scales: half the bytes on NVLink
+        # and no quantiser pass at the experts.  The values are those the experts would compute themselves
+        # (the 1 x 128 quantiser is per row), so both passes of a recomputed layer agree bit for bit.
+        pre_q = fp8 and not any(ctx.needs_input_grad) and os.environ.get("XORL_B200_EP_FP8_PUSH", "1") != "0"
+        if pre_q:
+            from ..ops.fp8_grouped import sf_stride
+            rb = H + sf_stride(H)
+            xrow = sc.quantised_tokens(T, rb)
+            _lib.check(lib.xb_quant_mx_rows(x.data_ptr(), x.stride(0), xrow.data_ptr(), rb, xrow.data_ptr() + H, rb,
+                                            T, H, st), "xb_quant_mx_rows")
+            _lib.check(lib.xb_ep_prepare_recv(recv.data_ptr(), meta.data_ptr(), sc.seg.data_ptr(), sc.tot.data_ptr(), El,
+                                              ws.cap, rb, st), "xb_ep_prepare_recv")
+            ws.push(xrow, tok_of_slot[:S], sc.dest_rank[:S], sc.dest_row[:S], None, "recv_f", "meta_f", S_DISP, C_DISP,
+                    "disp", row_bytes=rb)
+        else:
+            _lib.check(lib.xb_ep_prepare_recv(recv.data_ptr(), meta.data_ptr(), sc.seg.data_ptr(), sc.tot.data_ptr(), El,
+                                              ws.cap, H * 2, st), "xb_ep_prepare_recv")
+            ws.push(x, tok_of_slot[:S], sc.dest_rank[:S], sc.dest_row[:S], None, "recv_f", "meta_f", S_DISP, C_DISP, "disp")
         # ---- experts ----------------------------------------------------------------------------
         t2 = PhaseTimes.mark()
         PhaseTimes.add("fwd_dispatch", t1, t2)
-        _rows_gemm(ws, sc, recv, H, gate_up, sc.h, I2, 1, fp8, None if qg is None else qg.q_nk,
-                   None if qg is None else qg.sf_nk, st)
+        if pre_q:
+            _lib.check(lib.xb_grouped_gemm_mx_rows(recv.data_ptr(), recv.data_ptr() + H, qg.q_nk.data_ptr(),
+                                                   qg.sf_nk.data_ptr(), sc.h.data_ptr(), sc.seg.data_ptr(), ws.El, ws.cap,
+                                                   I2, H, rb, sc.h.stride(0), rb, qg.sf_nk.stride(1), st),
+                       "xb_grouped_gemm_mx_rows")
+        else:
+            _rows_gemm(ws, sc, recv, H, gate_up, sc.h, I2, 1, fp8, None if qg is None else qg.q_nk,
+                       None if qg is None else qg.sf_nk, st)
         _lib.check(lib.xb_swiglu_fwd_rows(sc.h.data_ptr(), sc.a.data_ptr(), ws.cap, I, 1, sc.row_limit_ptr, st),
                    "xb_swiglu_fwd_rows")
         _rows_gemm(ws, sc, sc.a, I, down, sc.y, H, 1, fp8, None if qd is None else qd.q_nk,
