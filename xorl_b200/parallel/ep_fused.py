@@ -355,7 +355,7 @@ class _FusedEPMoE(torch.autograd.Function):
     non-gated activations.)"""
 
     @staticmethod
-    def forward(ctx, x, weights, indices, gate_up, down, ws: _Workspace, fp8_mode):
+    def forward(ctx, x, weights, indices, gate_up, down, ws: _Workspace, fp8_mode, no_backward: bool = False):
         lib, st = ws.lib, _lib.stream_ptr()
         T, H = x.shape
         k = indices.shape[1]
@@ -391,7 +391,9 @@ class _FusedEPMoE(torch.autograd.Function):
         # instead of the T * k received ones) and travel as e4m3 values + scales: half the bytes on NVLink
         # and no quantiser pass at the experts.  The values are those the experts would compute themselves
         # (the 1 x 128 quantiser is per row), so both passes of a recomputed layer agree bit for bit.
-        pre_q = fp8 and not any(ctx.needs_input_grad) and os.environ.get("XORL_B200_EP_FP8_PUSH", "1") != "0"
+        # (``no_backward`` is the caller's ``not torch.is_grad_enabled()``: inside ``forward`` gradient mode is
+        # always off and ``needs_input_grad`` ignores it)
+        pre_q = fp8 and no_backward and os.environ.get("XORL_B200_EP_FP8_PUSH", "1") != "0"
         if pre_q:
             from ..ops.fp8_grouped import sf_stride
             rb = H + sf_stride(H)
@@ -515,7 +517,7 @@ class _FusedEPMoE(torch.autograd.Function):
                                          T, k, H, st), "xb_moe_gather_sum")
         PhaseTimes.add("bwd_return_sum", b2)
         moe_ops._launches += 15 + (2 if fp8 else 0)
-        return dx, dw, None, d_gate_up, d_down, None, None
+        return dx, dw, None, d_gate_up, d_down, None, None, None
 
 
 def fused_ep_forward(x, weights, indices, experts, num_experts, ctx):
@@ -528,7 +530,8 @@ def fused_ep_forward(x, weights, indices, experts, num_experts, ctx):
     kw = moe_ops.experts_mlp_kwargs(experts)
     fp8_mode = kw.pop("fp8", None)
     if not kw and os.environ.get("XORL_B200_EP_SINGLE_NODE_FN", "1") == "1":
-        return _FusedEPMoE.apply(x, weights, indices, experts.gate_up_proj, experts.down_proj, ws, fp8_mode)
+        return _FusedEPMoE.apply(x, weights, indices, experts.gate_up_proj, experts.down_proj, ws, fp8_mode,
+                                 not torch.is_grad_enabled())
     kw = moe_ops.experts_mlp_kwargs(experts)
     plan = _make_plan(ws, indices)
     buf = _Dispatch.apply(x, ws, plan)
