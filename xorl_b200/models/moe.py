@@ -67,7 +67,8 @@ class TopKRouter(nn.Module):
 
     def forward(self, x: torch.Tensor):
         """x [T, H] -> (weights fp32 [T, k], indices int64 [T, k], probs fp32 [T, E])."""
-        if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 \
+                and self.weight.shape[0] % 8 == 0:
             # bf16 operands, fp32 accumulation and fp32 logits out of the tcgen05 GEMM: the same products
             # as an fp32 matmul of the bf16 values, without materialising fp32 copies of x and W
             logits = router_logits(x, self.weight)

@@ -227,16 +227,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
     """Linear layer through the tcgen05 GEMM (CUDA) or torch (CPU)."""
     if not x.is_cuda:
         return torch.nn.functional.linear(x, w, bias)
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[-1] % 8:
-        # the tcgen05 kernel takes bf16 operands with a reduction dim that is a multiple of 8; anything
-        # else runs in the library, and says so once per case instead of doing it silently
-        key = (x.dtype, w.dtype, x.shape[-1] % 8 != 0)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[-1] % 8 or w.shape[0] % 8:
+        # the tcgen05 kernel takes bf16 operands whose row pitches are multiples of 16 bytes (TMA): the
+        # reduction dim for the forward, the output dim for the gradient GEMMs; anything else runs in the
+        # library, and says so once per case instead of doing it silently
+        key = (x.dtype, w.dtype, x.shape[-1] % 8 != 0, w.shape[0] % 8 != 0)
         if key not in _LIBRARY_FALLBACKS:
             _LIBRARY_FALLBACKS.add(key)
             import logging
             logging.getLogger("xorl_b200").warning(
-                "ops.gemm.linear: %s x %s with K=%d runs in the library GEMM, not the tcgen05 kernel "
-                "(bf16 operands and K %% 8 == 0 are required)", x.dtype, w.dtype, x.shape[-1])
+                "ops.gemm.linear: %s x %s with K=%d, N=%d runs in the library GEMM, not the tcgen05 kernel "
+                "(bf16 operands, K %% 8 == 0 and N %% 8 == 0 are required)", x.dtype, w.dtype, x.shape[-1], w.shape[0])
         return torch.nn.functional.linear(x, w, bias)
     y = _Linear.apply(x, w)
     if bias is not None:
