@@ -171,6 +171,10 @@ def fused_linear_token_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: 
             gemm(h2[s:e], weight, out=logits)
             l, _ = ce_chunk_(logits, lab[s:e], 0.0, False, ignore_index)
             lp[s:e] = -l
+    if not torch.is_grad_enabled():
+        # evaluation (log-probabilities only): there is nothing to differentiate
+        loss, metrics = loss_fn(lp, mask)
+        return loss * grad_scale, lp, metrics
     lp_leaf = lp.clone().requires_grad_()
     loss, metrics = loss_fn(lp_leaf, mask)
     (coef,) = torch.autograd.grad(loss, lp_leaf)
