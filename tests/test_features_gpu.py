@@ -123,3 +123,47 @@ def test_distillation_step_on_the_gpu(tmp_path):
         assert torch.allclose(out.cpu(), ref, atol=2e-3, rtol=2e-2), (kind, (out.cpu() - ref).abs().max())
         assert (a[0].grad.float().cpu() - b[0].grad).abs().max() < 0.03 * b[0].grad.abs().max() + 1e-4
         assert (a[1].grad.float().cpu() - b[1].grad).abs().max() < 0.03 * b[1].grad.abs().max() + 1e-4
+
+
+def _optimizer_curve(device, dtype, optimizer, lr, steps=6):
+    from xorl_b200.models.config import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.state import get_parallel_state, init_parallel_state, reset_parallel_state
+    from xorl_b200.parallel.zero import Zero3Engine
+    reset_parallel_state()
+    init_parallel_state(device_type=device.type)
+    cfg = preset("tiny-qwen3", tie_word_embeddings=False)
+    eng = Zero3Engine(DecoderLM(cfg, dtype=dtype, device="meta"), get_parallel_state(), compute_dtype=dtype,
+                      device=device, seed=0)
+    opt = build_optimizer(eng, lr=lr, weight_decay=0.01, optimizer_type=optimizer,
+                          optimizer_kwargs={"muon_lr": 0.01} if optimizer == "muon" else None)
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, cfg.vocab_size, (1, 257), generator=g)
+    x, y = ids[:, :-1].clone().to(device), ids[:, 1:].clone().to(device)
+    cu = torch.tensor([0, 128, 256], dtype=torch.int32, device=device)
+    pos = torch.cat([torch.arange(128), torch.arange(128)]).unsqueeze(0).to(device)
+    out = []
+    for _ in range(steps):
+        opt.zero_grad()
+        out.append(float(eng.forward_backward(x, y, position_ids=pos, cu_seqlens=cu, grad_scale=1.0 / 256)))
+        eng.finish_grad_sync()
+        _, coef = eng.grad_norm_and_clip_coef(1.0)
+        opt.step(clip_coef=coef)
+    reset_parallel_state()
+    return out
+
+
+@pytest.mark.parametrize("optimizer,lr", [("adamw", 2e-3), ("anyprecision_adamw", 2e-3), ("sgd", 0.5), ("signsgd", 2e-4),
+                                          ("muon", 2e-3)])
+def test_optimizers_on_the_gpu_follow_the_host_curve(optimizer, lr):
+    """Every optimizer's device kernels (csrc/optim.cu, Newton-Schulz on the tcgen05 GEMM) with gradient
+    clipping, against the same optimizer's tensor-op form in fp32 on the host."""
+    from xorl_b200.ops import _lib
+    got = _optimizer_curve(torch.device("cuda", 0), torch.bfloat16, optimizer, lr)
+    torch.cuda.synchronize()
+    _lib.raise_on_status()
+    ref = _optimizer_curve(torch.device("cpu"), torch.float32, optimizer, lr)
+    assert all(math.isfinite(l) for l in got) and got[-1] < got[0], (optimizer, got)
+    for i, (a, b) in enumerate(zip(got, ref)):
+        assert abs(a - b) < 0.06 * abs(b) + 0.06, (optimizer, i, got, ref)
