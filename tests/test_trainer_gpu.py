@@ -1,0 +1,68 @@
+"""The trainer end to end on one GPU through the CLI entry point: feature combinations whose device paths
+differ from the host ones (activation offload through pinned memory, Hugging Face export and import with the
+multi-stream reader, fp8 linears, LoRA with PEFT export, z-loss + router loss on a MoE model, kept
+activations).  Each run must learn, write its artifacts and leave the kernels' status words clean."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+import yaml
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+pytestmark = pytest.mark.gpu
+
+
+def _run(tmp, name, model="small-qwen3", model_extra=None, lora=None, **train):
+    cfg = {
+        "model": {"config_path": model, **(model_extra or {})},
+        "data": {"datasets": [{"path": "random", "type": "tokenized", "max_seq_len": 500, "min_seq_len": 200,
+                               "num_samples": 16}],
+                 "sample_packing_sequence_len": 1024, "pad_to_multiple_of": 128, "shuffle_merged_datasets": False},
+        "train": {"output_dir": str(tmp / name), "lr": 1e-3, "max_steps": 8, "use_wandb": False,
+                  "save_hf_weights": False, "save_epochs": 0, "num_train_epochs": 100, "weight_decay": 0.0, **train},
+    }
+    if lora:
+        cfg["lora"] = lora
+    p = tmp / f"{name}.yaml"
+    p.write_text(yaml.safe_dump(cfg))
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run([sys.executable, "-m", "xorl_b200.cli.train", str(p)], env=env, capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    with open(tmp / name / "training_metrics.json") as f:
+        return json.load(f)
+
+
+def test_activation_offload_matches_the_plain_run(tmp_path):
+    plain = _run(tmp_path, "plain")["loss_history"]
+    off = _run(tmp_path, "offload", enable_activation_offload=True)["loss_history"]
+    assert plain[-1] < plain[0] - 0.5
+    assert plain == off, (plain, off)                    # moving saved inputs through host memory changes no bit
+
+
+def test_kept_activations_and_hf_round_trip(tmp_path):
+    m = _run(tmp_path, "keep", gradient_checkpointing_method="no_recompute", save_hf_weights=True, save_steps=8)
+    assert m["loss_history"][-1] < m["loss_history"][0] - 0.5
+    hf = tmp_path / "keep" / "global_step_8" / "hf_ckpt"
+    assert any(f.endswith(".safetensors") for f in os.listdir(hf))
+    # a second run that starts from the exported weights (multi-stream reader) begins trained, not at ln(V)
+    first = _run(tmp_path, "reload", model_extra={"model_path": str(hf)}, max_steps=1, lr=1e-9,
+                 load_weights_mode="all_ranks")["loss_history"][0]
+    assert first < m["loss_history"][0] - 0.5, (first, m["loss_history"])
+
+
+def test_fp8_linears_lora_and_moe_losses(tmp_path):
+    f8 = _run(tmp_path, "fp8", enable_fp8_training=True, fp8_training_allow_blackwell=True)["loss_history"]
+    bf = _run(tmp_path, "bf16")["loss_history"]
+    assert f8[-1] < f8[0] - 0.5 and abs(f8[-1] - bf[-1]) < 0.1 * abs(bf[-1]), (f8, bf)
+    lo = _run(tmp_path, "lora", lora={"enable_lora": True, "lora_rank": 8, "lora_alpha": 16}, lr=5e-3,
+              save_hf_weights=True, save_steps=8)
+    assert lo["loss_history"][-1] < lo["loss_history"][0]
+    peft = tmp_path / "lora" / "global_step_8" / "hf_ckpt"
+    assert os.path.exists(peft / "adapter_config.json") and any("adapter_model" in f for f in os.listdir(peft))
+    moe = _run(tmp_path, "moe", model="small-qwen3-moe", softmax_auxiliary_loss=True, auxiliary_loss_multiplier=1e-4)
+    assert moe["loss_history"][-1] < moe["loss_history"][0]
