@@ -83,6 +83,8 @@ def _check(ref, got):
 CASES = [
     ("fsdp2", 2, 2, dict()),
     ("fsdp2_no_recompute", 2, 2, dict(gradient_checkpointing_method="no_recompute")),
+    ("ddp2", 2, 2, dict(data_parallel_mode="ddp")),
+    ("hsdp2x2", 4, 4, dict(data_parallel_replicate_size=2, data_parallel_shard_size=2)),
     ("tp2", 2, 1, dict(tensor_parallel_size=2)),
     ("tp2_sp_fused", 2, 1, dict(tensor_parallel_size=2, tensor_parallel_sequence_parallel=True)),
     ("pp2_1f1b", 2, 1, dict(pipeline_parallel_size=2, pipeline_parallel_schedule="1F1B")),
