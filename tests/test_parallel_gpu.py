@@ -173,3 +173,22 @@ def test_checkpoint_resume_on_gpu(tmp_path):
     assert len(got) >= 2
     for a, b in zip(full[2:], got[-2:]):
         assert abs(a - b) <= 2e-3 * abs(a), (full, got)
+
+
+def test_checkpoint_written_on_two_gpus_resumes_on_one(tmp_path):
+    """ZeRO over two GPUs writes its pieces (plans gathered over NCCL); one GPU, which holds every
+    parameter whole, reads them back and continues the same loss curve (same global batch per step)."""
+    from dist_utils import run_distributed
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_distributed("-m", 2, "xorl_b200.cli.train", _cfg(tmp_path, "two", dp=2, max_steps=4, save_steps=2), env=ENV,
+                    timeout=600)
+    full = _losses(tmp_path, "two")
+    ckpt = tmp_path / "two" / "checkpoints" / "global_step_2"
+    assert (ckpt / ".metadata").exists()
+    run_distributed("-m", 1, "xorl_b200.cli.train",
+                    _cfg(tmp_path, "one", dp=1, max_steps=4, load_checkpoint_path=str(ckpt)), env=ENV, timeout=600)
+    got = _losses(tmp_path, "one")
+    assert len(got) >= 2
+    for a, b in zip(full[2:], got[-2:]):
+        assert abs(a - b) <= 0.01 * abs(a), (full, got)
