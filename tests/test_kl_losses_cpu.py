@@ -120,3 +120,39 @@ def _worker():
 
 if __name__ == "__main__":
     _worker()
+
+
+def test_policy_losses_with_reference_penalty_and_statistics():
+    from xorl_b200.ops import rl_losses as R
+    torch.manual_seed(0)
+    T = 40
+    lp = (torch.randn(T) * 0.3 - 2).requires_grad_()
+    old = lp.detach() + torch.randn(T) * 0.1
+    ref = lp.detach() + torch.randn(T) * 0.2
+    adv = torch.randn(T)
+    mask = (torch.rand(T) > 0.2).float()
+    base, m0 = R.policy_loss(lp, mask, old, adv)
+    pen, m1 = R.policy_loss(lp, mask, old, adv, ref_logprobs=ref, kl_coef=0.5, kl_estimator="k3", compute_kl_stats=True)
+    k3 = K.kl_penalty(lp, ref, "k3")
+    assert torch.allclose(pen, base + 0.5 * (k3 * mask).sum())
+    assert torch.allclose(m1["kl_ref"], (k3 * mask).sum() / mask.sum())
+    for key in ("kl_sample_train_k3", "logratio_max", "entropy_sample", "ratio_mean", "frac_ratio_outside_half_double"):
+        assert key in m1 and torch.isfinite(m1[key])
+    assert m1["kl_sample_train_k3"] >= 0
+    # the penalty pulls towards the reference: its gradient is that of the estimator
+    (g_pen,) = torch.autograd.grad(pen, lp, retain_graph=True)
+    (g_base,) = torch.autograd.grad(base, lp, retain_graph=True)
+    (g_k3,) = torch.autograd.grad((k3 * mask).sum(), lp)
+    assert torch.allclose(g_pen, g_base + 0.5 * g_k3, atol=1e-6)
+    g, _ = R.LOSS_REGISTRY["grpo"](lp, mask, old, adv, ref_logprobs=ref)
+    assert torch.allclose(g, base + 0.04 * (k3 * mask).sum())
+    # truncated importance sampling reports how often it truncated
+    _, m2 = R.policy_loss(lp, mask, old, adv, tis_cap=1.05, sampling_logprobs=old - 0.2)
+    assert float(m2["tis_clipfrac"]) == 1.0 and float(m2["tis_mean"]) > 1.05
+    # OPD: estimator modes
+    sf, ms = R.opd_loss(lp, mask, ref)
+    k2, _ = R.opd_loss(lp, mask, ref, loss_mode="k2")
+    assert torch.allclose(k2, (0.5 * (lp - ref) ** 2 * mask).sum()) and "reverse_kl" in ms
+    (gs,) = torch.autograd.grad(sf, lp, retain_graph=True)
+    (g2,) = torch.autograd.grad(k2, lp)
+    assert torch.allclose(gs, g2, atol=1e-6)          # score-function advantage and k2 share their gradient
