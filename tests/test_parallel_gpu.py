@@ -95,10 +95,13 @@ CASES = [
     ("tp2pp2", 4, 1, dict(tensor_parallel_size=2, pipeline_parallel_size=2,
                           pipeline_parallel_schedule="interleaved1f1b", pipeline_parallel_virtual_stages=2)),
     ("tp4_sp_fused", 4, 1, dict(tensor_parallel_size=4, tensor_parallel_sequence_parallel=True)),
+    # data-parallel body, lm-head split by vocabulary rows over the two ranks, tokens pooled for the loss
+    ("lm_head_tp2", 2, 2, dict(lm_head_tensor_parallel_size=2)),
 ]
 # model overrides of a case (and of the single-GPU run it is compared with): four-way tensor parallelism
 # needs at least four key/value heads
-FOUNDATION = {"tp4_sp_fused": {"num_attention_heads": 8, "num_key_value_heads": 4}}
+FOUNDATION = {"tp4_sp_fused": {"num_attention_heads": 8, "num_key_value_heads": 4},
+              "lm_head_tp2": {"tie_word_embeddings": False}}
 _REF = {}
 
 

@@ -58,3 +58,27 @@ def test_tp2_pp2_interleaved(tmp_path):
     got = _losses(tmp_path, "tppp")
     for a, b in zip(ref, got):
         assert abs(a - b) < 2e-4, (ref, got)
+
+
+@pytest.mark.distributed
+def test_lm_head_only_tp2_matches_plain_data_parallel(tmp_path):
+    """``lm_head_tensor_parallel_size=2`` with ``tensor_parallel_size=1``: the body is data parallel, the
+    two ranks hold half of the vocabulary rows each and pool their tokens for the loss.  Same loss
+    curve as plain data parallelism on the same two ranks, and the checkpoint it writes (the lm-head
+    under its full shape) resumes without lm-head parallelism."""
+    from dist_utils import run_distributed
+    run_distributed("-m", 2, "xorl_b200.cli.train", _cfg(tmp_path, "dp", max_grad_norm=0.5, max_steps=4))
+    ref = _losses(tmp_path, "dp")
+    cfg = _cfg(tmp_path, "lmtp", lm_head_tensor_parallel_size=2, max_grad_norm=0.5, max_steps=4, save_steps=2)
+    run_distributed("-m", 2, "xorl_b200.cli.train", cfg)
+    got = _losses(tmp_path, "lmtp")
+    assert len(got) == 4
+    with open(tmp_path / "lmtp" / "startup_metrics.json") as f:
+        assert json.load(f)["lm_head_rows_per_rank"] == 512          # half of the tiny model's 1024 rows
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 2e-4, (ref, got)
+    resumed = _cfg(tmp_path, "resumed", max_grad_norm=0.5, max_steps=4,
+                   load_checkpoint_path=str(tmp_path / "lmtp" / "checkpoints" / "global_step_2"))
+    run_distributed("-m", 2, "xorl_b200.cli.train", resumed)
+    for a, b in zip(ref[2:], _losses(tmp_path, "resumed")):
+        assert abs(a - b) < 2e-4, (ref, _losses(tmp_path, "resumed"))

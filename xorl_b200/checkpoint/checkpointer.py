@@ -69,6 +69,8 @@ class DistributedCheckpointer:
             return full, RowMap([(0, lshape[0], 0)], col_offset=ps.rank_in("tp") * lshape[1])
         if getattr(p, "_xb_ep", None) is not None and ps.ep_size > 1:
             return tuple(p._xb_full_shape), RowMap([(0, lshape[0], ps.rank_in("ep") * lshape[0])])
+        if getattr(p, "_xb_lmtp", None) is not None:
+            return tuple(p._xb_full_shape), RowMap([(0, lshape[0], p._xb_lmtp[0] * lshape[0])])
         return None, None
 
     def _state_sources(self):

@@ -125,8 +125,6 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "fp8_training_moe_grouped_backend": (_is("triton_grouped"), "the grouped fp8 GEMM has one backend: the tcgen05 block-scaled kernel"),
         "fsdp_sharded_lm_head_loss": (_falsy, "the FSDP-sharded lm-head loss is not built (use lm-head tensor parallelism or the chunked loss)"),
         "enable_compile": (_falsy, "there is no tracing compiler on any path"),
-        "lm_head_tensor_parallel_size": (_is(1), "lm-head-only tensor parallelism is not built: the process groups exist, "
-                                                 "the loss does not use them (vocabulary-parallel loss runs under tensor_parallel_size)"),
     },
     "lora": {
         "lora_target_manifest": (_falsy, "target manifests are not built (use lora_target_modules)"),

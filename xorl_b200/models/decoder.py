@@ -120,9 +120,24 @@ class DecoderLM(nn.Module):
             # the vocab-parallel loss; tied heads stay replicated with the embedding
             self.vocab_parallel = tp > 1 and not cfg.tie_word_embeddings and cfg.vocab_size % tp == 0
             self.head_tp = (tp, tp_rank, tp_group)
-            v_local = cfg.vocab_size // tp if self.vocab_parallel else cfg.vocab_size
+            # lm-head-only tensor parallelism (train.lm_head_tensor_parallel_size): the body is data parallel,
+            # only the head is split by vocabulary rows over groups of consecutive data-parallel ranks, which
+            # pool their tokens for the loss (src/xorl/distributed/parallel_state.py:64-116,781-830)
+            from ..parallel.state import get_parallel_state
+            ps = get_parallel_state()
+            lm_tp = getattr(ps, "lm_head_tp_size", 1)
+            self.head_gathers_tokens = False
+            if tp == 1 and lm_tp > 1:
+                if cfg.tie_word_embeddings or cfg.vocab_size % lm_tp:
+                    raise ValueError("lm_head_tensor_parallel_size needs an untied lm-head whose vocabulary divides by it")
+                self.vocab_parallel, self.head_gathers_tokens = True, True
+                self.head_tp = (lm_tp, ps.rank_in("lm_head_tp"), ps.group("lm_head_tp"))
+            v_local = cfg.vocab_size // self.head_tp[0] if self.vocab_parallel else cfg.vocab_size
             self.lm_head = Linear(cfg.hidden_size, v_local, bias=False, dtype=dtype, device=device)
-            if self.vocab_parallel:
+            if self.head_gathers_tokens:
+                from ..parallel.tp import mark_lm_head
+                mark_lm_head(self.lm_head.weight, (cfg.vocab_size, cfg.hidden_size), self.head_tp[0], self.head_tp[1])
+            elif self.vocab_parallel:
                 from ..parallel.tp import mark_col
                 mark_col(self.lm_head.weight, (cfg.vocab_size, cfg.hidden_size), (cfg.vocab_size,))
         if cfg.tie_word_embeddings and has_embed and has_head:
@@ -218,6 +233,8 @@ class DecoderLM(nn.Module):
             # token normalisation (``distill.distillation_loss_weight``)
             t_hidden, t_weight, kind, weight = distill
             from ..ops import kl_losses
+            if getattr(self, "head_gathers_tokens", False):
+                raise NotImplementedError("distillation is not supported with lm_head_tensor_parallel_size > 1")
             if getattr(self, "vocab_parallel", False):
                 # both lm-heads are row-sharded over the tensor-parallel group: the divergence is formed
                 # from local logit shards, only per-token statistics cross the group
@@ -244,9 +261,18 @@ class DecoderLM(nn.Module):
                 raise NotImplementedError("softmax_auxiliary_loss (z-loss) is not supported with a "
                                           "vocabulary-parallel lm-head")
             tp, tp_rank, tp_group = self.head_tp
+            flat_labels = labels.reshape(-1)
+            if getattr(self, "head_gathers_tokens", False):
+                # every rank of the lm-head group brings its own tokens: pool them, take the loss of all of
+                # them through this rank's vocabulary rows, report this rank's share of the total
+                from ..parallel.tp import _OwnShare, gather_tokens_for_head
+                hidden, flat_labels = gather_tokens_for_head(hidden.reshape(-1, hidden.shape[-1]), flat_labels,
+                                                             tp_group, tp, tp_rank)
             loss = loss_ops.vocab_parallel_linear_cross_entropy(
-                hidden, self.lm_head.weight, labels.reshape(-1), tp_group,
+                hidden, self.lm_head.weight, flat_labels, tp_group,
                 tp_rank * (self.config.vocab_size // tp), grad_scale, self.loss_chunk_tokens)
+            if getattr(self, "head_gathers_tokens", False):
+                loss = _OwnShare.apply(loss, tp)
             return (loss, None) if return_token_losses else loss
         return loss_ops.fused_linear_cross_entropy(hidden, self.lm_head.weight, labels.reshape(-1),
                                                    grad_scale, self.loss_chunk_tokens,

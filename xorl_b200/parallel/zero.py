@@ -37,7 +37,7 @@ ALIGN = 64  # elements; keeps every parameter and every shard 128-byte aligned i
 
 def _slice_fn(p):
     """This rank's part of the full tensor for a tensor-parallel or expert-parallel parameter."""
-    return getattr(p, "_xb_tp_slice", None) or getattr(p, "_xb_ep_slice", None)
+    return getattr(p, "_xb_tp_slice", None) or getattr(p, "_xb_ep_slice", None) or getattr(p, "_xb_lmtp_slice", None)
 
 
 def _round_up(x: int, m: int) -> int:
@@ -303,7 +303,7 @@ class Zero3Engine:
                     newp._xb_init = None if p.is_meta else p.detach()
                     for attr in ("_xb_expert", "_xb_tp", "_xb_no_decay", "_xb_full_shape",
                                  "_xb_tp_slice", "_xb_tp_reduce", "_xb_materialize", "_xb_lora", "_xb_ep",
-                                 "_xb_ep_slice"):
+                                 "_xb_ep_slice", "_xb_lmtp", "_xb_lmtp_slice"):
                         if hasattr(p, attr):
                             setattr(newp, attr, getattr(p, attr))
                     mapping[id(p)] = newp
@@ -324,19 +324,30 @@ class Zero3Engine:
             dense: List[Tuple[str, nn.Parameter]] = []
             expert: List[Tuple[str, nn.Parameter]] = []
             frozen: List[Tuple[str, nn.Parameter]] = []
+            head: List[Tuple[str, nn.Parameter]] = []       # lm-head rows under lm-head-only tensor parallelism
             for m in mods:
                 for p in m.parameters():
                     if id(p) in seen or not p.requires_grad and False:
                         continue
                     seen.add(id(p))
-                    if not p.requires_grad:
+                    if getattr(p, "_xb_lmtp", None) is not None:
+                        head.append((fqn_of[id(p)], p))
+                    elif not p.requires_grad:
                         frozen.append((fqn_of[id(p)], p))
                     else:
                         (expert if getattr(p, "_xb_expert", False) else dense).append((fqn_of[id(p)], p))
-            for kind, plist in (("dense", dense), ("expert", expert), ("frozen", frozen)):
+            for kind, plist in (("dense", dense), ("expert", expert), ("frozen", frozen), ("head", head)):
                 if not plist:
                     continue
-                if kind == "expert" and self.ps.ep_size > 1:
+                if kind == "head":
+                    # sharded over the ranks that hold the same vocabulary rows
+                    hp = self.ps.group("lm_head_replica") if self.shard_pg is not None else None
+                    g = FlatParamGroup(f"{uname}.{kind}", plist, hp, self.ps.size("lm_head_replica") if hp is not None else 1,
+                                       self.ps.rank_in("lm_head_replica") if hp is not None else 0, self.device,
+                                       self.compute_dtype,
+                                       None if hp is not None else self.ps.group("lm_head_replica"),
+                                       1 if hp is not None else self.ps.size("lm_head_replica"))
+                elif kind == "expert" and self.ps.ep_size > 1:
                     g = FlatParamGroup(f"{uname}.{kind}", plist, self.ep_shard_pg, self.ep_shard_world,
                                        self.ep_shard_rank, self.device, self.compute_dtype)
                 else:
@@ -344,7 +355,8 @@ class Zero3Engine:
                                        self.shard_rank, self.device, self.compute_dtype,
                                        self.rep_pg, self.rep_world)
                 g.is_expert = kind == "expert"
-                g.frozen = kind == "frozen"
+                g.is_head = kind == "head"
+                g.frozen = kind == "frozen" or (kind == "head" and not plist[0][1].requires_grad)
                 self._materialize_group(g, std, seed, index_of, zc, init_parameter_)
                 unit.groups.append(g)
             self.units.append(unit)
@@ -891,13 +903,21 @@ class Zero3Engine:
         def counts_as_expert(g) -> bool:
             return getattr(g, "is_expert", False) and self.ps.ep_size > 1
 
+        # lm-head rows under lm-head-only tensor parallelism: distinct rows on the ranks of an lm_head_tp group,
+        # each sharded over its lm_head_replica group
+        head_sq = torch.zeros(1, device=dev, dtype=torch.float32)
+        head_groups = [g for g in self.all_groups() if getattr(g, "is_head", False) and g.grad_ready]
+        for g in head_groups:
+            head_sq += g.grad_shard.float().pow(2).sum()
+            g.sq_valid = False
+
         if self.is_cuda:
             # per-unit partial sums taken early live on the side streams
             torch.cuda.current_stream().wait_stream(self.norm_stream)
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         early_d, early_e = [], []
         for g in self.all_groups():
-            if not g.grad_ready:
+            if not g.grad_ready or getattr(g, "is_head", False):
                 continue
             if g.sq_valid:
                 (early_e if counts_as_expert(g) else early_d).append(g.sq)
@@ -937,6 +957,12 @@ class Zero3Engine:
             if self.ps.group("ep") is not None:
                 dist.all_reduce(expert_sq, group=self.ps.group("ep"))
         total = dense_sq + expert_sq
+        if getattr(self.ps, "lm_head_tp_size", 1) > 1:
+            if head_groups and head_groups[0].pg is not None:
+                dist.all_reduce(head_sq, group=head_groups[0].pg)
+            if self.ps.group("lm_head_tp") is not None:
+                dist.all_reduce(head_sq, group=self.ps.group("lm_head_tp"))
+            total = total + head_sq
         if self.ps.pp_size > 1 and self.ps.group("pp") is not None:
             dist.all_reduce(total, group=self.ps.group("pp"))
         norm = torch.zeros(1, device=dev, dtype=torch.float32)
@@ -977,6 +1003,10 @@ class Zero3Engine:
                     parts = [torch.empty_like(view) for _ in range(self.ps.tp_size)]
                     dist.all_gather(parts, view.contiguous(), group=self.ps.group("tp"))
                     view = unshard_rows(parts, spec[1]) if spec[0] == "col" else torch.cat(parts, 1)
+                if getattr(p, "_xb_lmtp", None) is not None and self.ps.group("lm_head_tp") is not None:
+                    parts = [torch.empty_like(view) for _ in range(p._xb_lmtp[1])]
+                    dist.all_gather(parts, view.contiguous(), group=self.ps.group("lm_head_tp"))
+                    view = torch.cat(parts, 0)
                 if ep_full and getattr(p, "_xb_ep", None) is not None and self.ps.ep_size > 1:
                     parts = [torch.empty_like(view) for _ in range(self.ps.ep_size)]
                     dist.all_gather(parts, view.contiguous(), group=self.ps.group("ep"))

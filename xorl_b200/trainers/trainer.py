@@ -55,6 +55,8 @@ class Trainer:
         self._timed("build_optimizer", self._build_optimizer)
         self._timed("observability", self._setup_observability)
         self._timed("resume", self._resume_checkpoint)
+        head_rows = [p.shape[0] for n, p in self.model.named_parameters() if n.endswith("lm_head.weight")]
+        self.startup["lm_head_rows_per_rank"] = head_rows[0] if head_rows else 0
         if self.ps.rank == 0:
             os.makedirs(args.train.output_dir, exist_ok=True)
             with open(os.path.join(args.train.output_dir, "startup_metrics.json"), "w") as f:
@@ -270,6 +272,14 @@ class Trainer:
         self._canaries = os.environ.get("XORL_B200_CANARIES", "0") == "1"
         # equal micro-batch lengths over the data-parallel group; no collective needs it, it only balances work
         self._sync_padding = os.environ.get("XORL_B200_SYNC_PADDING", "0") == "1" and self.ps.ulysses_size * self.ps.ringattn_size == 1
+        if getattr(self.ps, "lm_head_tp_size", 1) > 1:
+            # the ranks of an lm-head group pool their tokens for the loss: they need the same number of
+            # micro-batches of the same lengths
+            if self.ps.ulysses_size * self.ps.ringattn_size > 1 or self.ps.pp_size > 1 or self.ps.ep_size > 1 \
+                    or (self.ps.size("dp_replicate") > 1 and self.ps.size("dp_shard") > 1):
+                raise NotImplementedError("lm_head_tensor_parallel_size > 1 is built for plain data parallelism "
+                                          "(no context, pipeline or expert parallelism, no HSDP)")
+            self._sync_padding = True
         if self.ps.world_size > 1 and dist.is_initialized() \
                 and os.environ.get("XORL_RANK_WATCHDOG", "1") not in ("0", "false"):
             store = dist.distributed_c10d._get_default_store()
