@@ -82,3 +82,20 @@ def test_lm_head_only_tp2_matches_plain_data_parallel(tmp_path):
     run_distributed("-m", 2, "xorl_b200.cli.train", resumed)
     for a, b in zip(ref[2:], _losses(tmp_path, "resumed")):
         assert abs(a - b) < 2e-4, (ref, _losses(tmp_path, "resumed"))
+
+
+@pytest.mark.distributed
+def test_fsdp_sharded_lm_head_loss_matches_plain_data_parallel(tmp_path):
+    """``fsdp_sharded_lm_head_loss``: the lm-head is never gathered, the loss streams the data-parallel
+    group's tokens through each rank's vocabulary rows in ``..._num_chunks`` chunks."""
+    from dist_utils import run_distributed
+    run_distributed("-m", 2, "xorl_b200.cli.train", _cfg(tmp_path, "dp", max_grad_norm=0.5))
+    ref = _losses(tmp_path, "dp")
+    cfg = _cfg(tmp_path, "sharded", fsdp_sharded_lm_head_loss=True, fsdp_sharded_lm_head_loss_num_chunks=3,
+               max_grad_norm=0.5)
+    run_distributed("-m", 2, "xorl_b200.cli.train", cfg)
+    got = _losses(tmp_path, "sharded")
+    with open(tmp_path / "sharded" / "startup_metrics.json") as f:
+        assert json.load(f)["lm_head_rows_per_rank"] == 512
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 2e-4, (ref, got)

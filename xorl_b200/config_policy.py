@@ -67,7 +67,6 @@ SATISFIED_BY_DESIGN: Dict[str, Dict[str, str]] = {
         "activation_offload_prefetch_count": "the offloader prefetches one layer ahead",
         "log_format": "step metrics are logged as one line per step and to metrics.jsonl / wandb",
         "ce_mode": "one fused lm-head + cross-entropy kernel path",
-        "fsdp_sharded_lm_head_loss_num_chunks": "only meaningful with fsdp_sharded_lm_head_loss",
     },
     "lora": {
         "aqn_alpha": "only meaningful with enable_aqn",
@@ -123,7 +122,6 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "fp8_training_correction_mode": (_is("none"), "residual correction is not built"),
         "fp8_training_module_overrides": (_falsy, "per-module fp8 overrides are not built (use target / exclude modules)"),
         "fp8_training_moe_grouped_backend": (_is("triton_grouped"), "the grouped fp8 GEMM has one backend: the tcgen05 block-scaled kernel"),
-        "fsdp_sharded_lm_head_loss": (_falsy, "the FSDP-sharded lm-head loss is not built (use lm-head tensor parallelism or the chunked loss)"),
         "enable_compile": (_falsy, "there is no tracing compiler on any path"),
     },
     "lora": {

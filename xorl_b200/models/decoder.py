@@ -261,18 +261,15 @@ class DecoderLM(nn.Module):
                 raise NotImplementedError("softmax_auxiliary_loss (z-loss) is not supported with a "
                                           "vocabulary-parallel lm-head")
             tp, tp_rank, tp_group = self.head_tp
-            flat_labels = labels.reshape(-1)
-            if getattr(self, "head_gathers_tokens", False):
-                # every rank of the lm-head group brings its own tokens: pool them, take the loss of all of
-                # them through this rank's vocabulary rows, report this rank's share of the total
-                from ..parallel.tp import _OwnShare, gather_tokens_for_head
-                hidden, flat_labels = gather_tokens_for_head(hidden.reshape(-1, hidden.shape[-1]), flat_labels,
-                                                             tp_group, tp, tp_rank)
+            pooled = getattr(self, "head_gathers_tokens", False)
+            # pooled: every rank of the lm-head group brings its own tokens; the loss streams the group's
+            # tokens chunk by chunk through this rank's vocabulary rows and returns the group total
             loss = loss_ops.vocab_parallel_linear_cross_entropy(
-                hidden, self.lm_head.weight, flat_labels, tp_group,
-                tp_rank * (self.config.vocab_size // tp), grad_scale, self.loss_chunk_tokens)
-            if getattr(self, "head_gathers_tokens", False):
-                loss = _OwnShare.apply(loss, tp)
+                hidden, self.lm_head.weight, labels.reshape(-1), tp_group,
+                tp_rank * (self.config.vocab_size // tp), grad_scale, self.loss_chunk_tokens, pooled=pooled)
+            if pooled:
+                from ..parallel.tp import _OwnShare
+                loss = _OwnShare.apply(loss, tp)        # this rank's share: the shares add up to the total
             return (loss, None) if return_token_losses else loss
         return loss_ops.fused_linear_cross_entropy(hidden, self.lm_head.weight, labels.reshape(-1),
                                                    grad_scale, self.loss_chunk_tokens,

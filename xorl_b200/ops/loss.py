@@ -240,23 +240,40 @@ class _VocabParallelLinearCE(torch.autograd.Function):
     The full [T, V] logits never exist on any rank (src/xorl/ops/loss/vocab_parallel_cross_entropy.py)."""
 
     @staticmethod
-    def forward(ctx, hidden, weight, labels, group, vocab_start, grad_scale, chunk_tokens, ignore_index):
+    def forward(ctx, hidden, weight, labels, group, vocab_start, grad_scale, chunk_tokens, ignore_index, pooled=False):
         import torch.distributed as dist
         global _launches
         T, H = hidden.shape
         Vl = weight.shape[0]
         cuda = hidden.is_cuda and hidden.dtype == torch.bfloat16
         need_dh, need_dw = hidden.requires_grad, weight.requires_grad
+        # pooled: every rank of the group brings T tokens of its own.  Chunk by chunk the group's tokens are
+        # gathered (rank order), taken through this rank's vocabulary rows, and the hidden gradient of the
+        # chunk is reduce-scattered back so that each rank keeps the summed gradient of its own tokens: the
+        # gathered hidden states and their gradient exist one chunk at a time
+        # (src/xorl/ops/loss/causallm_loss.py:46-192 streams the same way and all-reduces the gradient)
+        L = dist.get_world_size(group) if pooled else 1
+        nccl = pooled and dist.get_backend(group) == "nccl"
+        if pooled:
+            chunk_tokens = max(8, chunk_tokens // L // 8 * 8)
+
+        def pool(x):
+            out = x.new_empty((L * x.shape[0],) + tuple(x.shape[1:]))
+            dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+            return out
         dh = torch.zeros_like(hidden, dtype=torch.float32 if not cuda else hidden.dtype) if need_dh else None
         tgt, fresh = grad_target(weight) if (need_dw and cuda) else (None, False)
         dw_local = torch.zeros((Vl, H), device=hidden.device, dtype=torch.float32) if (need_dw and tgt is None) else None
         total = torch.zeros((), device=hidden.device, dtype=torch.float32)
         ldv = (Vl + 7) // 8 * 8
-        buf = torch.empty((min(chunk_tokens, T), ldv), device=hidden.device, dtype=torch.bfloat16) if cuda else None
+        buf = torch.empty((min(chunk_tokens, T) * L, ldv), device=hidden.device, dtype=torch.bfloat16) if cuda else None
         first = True
         for s in range(0, T, chunk_tokens):
             e = min(T, s + chunk_tokens)
             h, lab = hidden[s:e], labels[s:e]
+            if pooled:
+                h, lab = pool(h), pool(lab)
+                s0, s, e = s, 0, h.shape[0]             # the body below indexes the pooled chunk
             valid = lab != ignore_index
             if cuda:
                 logits = buf[: e - s, :Vl]
@@ -289,7 +306,11 @@ class _VocabParallelLinearCE(torch.autograd.Function):
                     int(vocab_start), ignore_index, float(grad_scale), _lib.stream_ptr()), "xb_cross_entropy_vp_grad")
                 _launches += 1
                 g = logits
-                if need_dh:
+                if need_dh and pooled:
+                    part = torch.empty((e, H), device=h.device, dtype=dh.dtype)
+                    gemm(g, weight, b_mn=True, out=part)
+                    dist.reduce_scatter_tensor(dh[s0:s0 + e // L], part, group=group)
+                elif need_dh:
                     gemm(g, weight, b_mn=True, out=dh[s:e])
                 if need_dw:
                     if tgt is not None:
@@ -303,12 +324,20 @@ class _VocabParallelLinearCE(torch.autograd.Function):
                 rows = torch.nonzero(mine)[:, 0]
                 g[rows, lt[rows]] -= 1.0
                 g = g * (valid[:, None] * grad_scale)
-                if need_dh:
+                if need_dh and pooled:
+                    part = g @ weight.float()
+                    if nccl:
+                        dist.reduce_scatter_tensor(dh[s0:s0 + e // L], part, group=group)
+                    else:
+                        dist.all_reduce(part, group=group)
+                        r = dist.get_rank(group)
+                        dh[s0:s0 + e // L] = part[r * (e // L):(r + 1) * (e // L)]
+                elif need_dh:
                     dh[s:e] = g @ weight.float()
                 if need_dw:
                     dw_local += g.t() @ h.float()
             first = False
-        if need_dh:
+        if need_dh and not pooled:
             dist.all_reduce(dh, group=group)
         if need_dw and tgt is not None:
             mark_written(weight)
@@ -323,18 +352,20 @@ class _VocabParallelLinearCE(torch.autograd.Function):
         if ctx.dw_local is not None:
             dw = deliver_param_grad(ctx.weight, ctx.dw_local * g)
         ctx.dh = ctx.dw_local = None
-        return dh, dw, None, None, None, None, None, None
+        return dh, dw, None, None, None, None, None, None, None
 
 
 def vocab_parallel_linear_cross_entropy(hidden, weight_shard, labels, group, vocab_start: int,
                                         grad_scale: float = 1.0, chunk_tokens: int = 1024,
-                                        ignore_index: int = IGNORE_INDEX):
-    """``grad_scale * sum_t CE`` with the lm-head sharded by vocabulary rows over ``group``; the
-    hidden states (and labels) are replicated over the group.  Back-propagate the result with an
+                                        ignore_index: int = IGNORE_INDEX, pooled: bool = False):
+    """``grad_scale * sum_t CE`` with the lm-head sharded by vocabulary rows over ``group``.  The hidden
+    states (and labels) are replicated over the group, or, with ``pooled``, every rank brings the same
+    number of tokens of its own and the result is the loss of the whole group's tokens (the same value on
+    every rank; the hidden gradient is that of this rank's tokens).  Back-propagate the result with an
     upstream gradient of 1, as for ``fused_linear_cross_entropy``."""
     return _VocabParallelLinearCE.apply(hidden.reshape(-1, hidden.shape[-1]), weight_shard, labels.reshape(-1),
                                         group, int(vocab_start), float(grad_scale), int(chunk_tokens),
-                                        int(ignore_index))
+                                        int(ignore_index), bool(pooled))
 
 
 def distillation_kl(hidden_s: torch.Tensor, w_s: torch.Tensor, hidden_t: torch.Tensor, w_t: torch.Tensor,

@@ -102,23 +102,6 @@ def mark_lm_head(p: torch.nn.Parameter, full_shape, size: int, rank: int) -> Non
     p._xb_lmtp_slice = lambda full, a=rank * per, b=(rank + 1) * per: full[a:b]
 
 
-class _GatherTokens(torch.autograd.Function):
-    """[T, H] on every rank of the group -> [size * T, H] (rank order).  The consumer's backward hands
-    back the gradient of all rows already summed over the group (the vocabulary-parallel loss all-reduces
-    its hidden-state gradient), so backward keeps this rank's rows."""
-
-    @staticmethod
-    def forward(ctx, x, group, size, rank):
-        ctx.rank, ctx.T = rank, x.shape[0]
-        parts = [torch.empty_like(x) for _ in range(size)]
-        dist.all_gather(parts, x.contiguous(), group=group)
-        return torch.cat(parts, 0)
-
-    @staticmethod
-    def backward(ctx, g):
-        return g[ctx.rank * ctx.T:(ctx.rank + 1) * ctx.T].contiguous(), None, None, None
-
-
 class _OwnShare(torch.autograd.Function):
     """Value ``x / size`` (every rank of the group computed the same group total: the shares add up to it
     over the group), gradient passed through unscaled (every rank back-propagates the whole total
@@ -131,15 +114,6 @@ class _OwnShare(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         return g, None
-
-
-def gather_tokens_for_head(hidden: torch.Tensor, labels: torch.Tensor, group, size: int, rank: int):
-    """Hidden states and labels of every rank of the lm-head group, in rank order.  All ranks must bring
-    the same number of tokens (micro-batches are padded to a common length under lm-head parallelism)."""
-    h = _GatherTokens.apply(hidden, group, size, rank)
-    labs = [torch.empty_like(labels) for _ in range(size)]
-    dist.all_gather(labs, labels.contiguous(), group=group)
-    return h, torch.cat(labs, 0)
 
 
 def mark_row(p: torch.nn.Parameter, full_shape) -> None:

@@ -77,11 +77,17 @@ class Trainer:
             kw = {"device_id": self.device} if backend == "nccl" else {}
             dist.init_process_group(backend, timeout=process_group_timeout(), **kw)
         set_seed(t.seed, t.enable_full_determinism)
+        lm_head_tp = t.lm_head_tensor_parallel_size
+        if t.fsdp_sharded_lm_head_loss and lm_head_tp == 1 and t.tensor_parallel_size == 1:
+            # the lm-head is never gathered: every rank of the data-parallel group keeps V / dp vocabulary
+            # rows and the loss streams the group's tokens through them (src/xorl/arguments.py:1464-1483)
+            lm_head_tp = max(1, world // max(1, t.pipeline_parallel_size * t.ulysses_parallel_size
+                                             * t.ringattn_parallel_size))
         self.ps = init_parallel_state(
             dp_replicate_size=t.data_parallel_replicate_size, dp_shard_size=t.data_parallel_shard_size,
             tp_size=t.tensor_parallel_size, ep_size=t.expert_parallel_size,
             pp_size=t.pipeline_parallel_size, ulysses_size=t.ulysses_parallel_size,
-            ringattn_size=t.ringattn_parallel_size, lm_head_tp_size=t.lm_head_tensor_parallel_size,
+            ringattn_size=t.ringattn_parallel_size, lm_head_tp_size=lm_head_tp,
             dp_mode=t.data_parallel_mode, cp_fsdp_mode=t.cp_fsdp_mode, device_type=self.device.type,
             ep_intranode=t.ep_intranode, tp_sequence_parallel=t.tensor_parallel_sequence_parallel)
         if self.ps.rank == 0:
@@ -110,6 +116,11 @@ class Trainer:
         if t.ce_num_chunks and t.ce_num_chunks > 0:
             self.model.loss_chunk_tokens = max(256, -(-int(a.data.sample_packing_sequence_len or 4096)
                                                       * t.micro_batch_size // t.ce_num_chunks))
+        if t.fsdp_sharded_lm_head_loss and getattr(self.ps, "lm_head_tp_size", 1) > 1:
+            # tokens of the whole group per chunk of the streamed loss
+            local = int(a.data.sample_packing_sequence_len or 4096) * t.micro_batch_size
+            self.model.loss_chunk_tokens = max(64, -(-local // max(1, t.fsdp_sharded_lm_head_loss_num_chunks))
+                                               * self.ps.lm_head_tp_size)
         if self.model_config.is_moe:
             # model.train_router: whether the gradient of the expert outputs flows into the routing
             # weights (off by default: the router then learns from the load-balancing loss only);
