@@ -438,6 +438,74 @@ def test_multi_tenant_adapters_are_isolated(tmp_path):
         reset_parallel_state()
 
 
+def test_adapter_sessions_have_their_own_rank_alpha_and_learning_rate(tmp_path):
+    """A session of rank 2 in a server of capacity 4: its rank components 2 and 3 start at zero and stay
+    zero through training (so it is a rank-2 adapter), its scale is its own alpha / rank, and the
+    learning rate it was last stepped with stays with it across switches."""
+    import torch
+    r = _lora_runner(tmp_path)
+    data = [{"tokens": list(range(3, 60))}]
+    out = r.create_model("small", lora_config={"rank": 2, "alpha": 6})
+    assert out["session"]["rank"] == 2 and out["session"]["alpha"] == 6
+    with pytest.raises(ValueError):
+        r.create_model("too_big", lora_config={"rank": 8})
+    assert "too_big" not in r.adapters.list()
+    for _ in range(3):
+        r.forward_backward("small", data, None)
+        r.optim_step("small", adam_params={"learning_rate": 7e-3})
+    from xorl_b200.adapters.lora import LoraLinear
+    mods = [m for m in r.engine.model.modules() if isinstance(m, LoraLinear)]
+    assert mods and all(m.scaling == 3.0 for m in mods)
+    full = dict(r.engine.iter_full_tensors("master"))
+    moved = 0
+    for n, t in full.items():
+        if "lora_A" in n:
+            assert float(t[2:].abs().max()) == 0.0 and float(t[:2].abs().max()) > 0, n
+        if "lora_B" in n:
+            assert float(t[:, 2:].abs().max()) == 0.0, n
+            moved += float(t[:, :2].abs().max()) > 0
+    assert moved > 0
+    # back on the default adapter: the server's alpha / rank and learning rate; the session keeps its own
+    r.forward_backward("default", data, None)
+    r.optim_step("default", adam_params={"learning_rate": 1e-3})
+    assert all(m.scaling == 2.0 for m in mods)
+    assert r.adapters.get_lr("small") == 7e-3 and r.adapters.get_lr("default") == 1e-3
+    r.adapters.set_lr("small", 2e-3)
+    r.forward_backward("small", data, None)
+    assert r.optim_step("small")["metrics"]["learning_rate"] == 2e-3
+    usage = r.adapters.memory_usage()
+    assert set(usage) == {"default", "small"} and all(v > 0 for v in usage.values())
+    from xorl_b200.parallel.state import reset_parallel_state
+    reset_parallel_state()
+
+
+def test_adapter_with_pending_gradients_is_not_dropped(tmp_path):
+    """Without a spill directory an adapter that holds accumulated gradients is never the eviction
+    victim; when every resident adapter holds some, creating another one raises."""
+    os.environ["XORL_MAX_ADAPTERS_PER_MODEL"] = "3"
+    try:
+        r = _lora_runner(tmp_path)
+        data = [{"tokens": list(range(3, 60))}]
+        r.create_model("a")
+        r.adapters.spill_dir = None
+        r.create_model("b")
+        r.forward_backward("a", data, None)                    # a: open epoch
+        r.forward_backward("b", data, None)                    # b: open epoch (a now rests on the host)
+        r.forward_backward("default", data, None)              # default active; a and b resident
+        with pytest.raises(RuntimeError, match="accumulated gradients"):
+            r.create_model("c")
+        assert "c" not in r.adapters.list()
+        r.optim_step("a", adam_params={"learning_rate": 1e-3})  # a is clean now (and active)
+        r.forward_backward("default", data, None)              # default active again: a rests clean, b pending
+        r.create_model("c")                                    # evicts a, the only clean resident one
+        assert sorted(r.adapters.list()) == ["b", "c", "default"]
+        assert r.optim_step("b", adam_params={"learning_rate": 1e-3})["metrics"]["tokens"] > 0
+    finally:
+        del os.environ["XORL_MAX_ADAPTERS_PER_MODEL"]
+        from xorl_b200.parallel.state import reset_parallel_state
+        reset_parallel_state()
+
+
 def test_rollout_routing_replay(tmp_path):
     from xorl_b200.parallel.state import reset_parallel_state
     from xorl_b200.server.runner import ModelRunner

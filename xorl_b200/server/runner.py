@@ -100,8 +100,9 @@ class ModelRunner:
         if self.adapters is None:
             from .adapters import AdapterManager
             self.adapters = AdapterManager(self, spill_dir=os.path.join(self.output_dir, "adapter_spill"))
-        self.adapters.create(model_id)
-        return {"model_id": model_id, "adapters": self.adapters.list()}
+        self.adapters.create(model_id, lora_config)
+        return {"model_id": model_id, "adapters": self.adapters.list(),
+                "session": self.adapters.session_spec(model_id)}
 
     def unload_model(self, model_id, **_):
         if self.adapters is not None:
@@ -354,6 +355,8 @@ class ModelRunner:
         opt.step(clip_coef=coef if clip > 0 else None, grad_scale=scale)
         self.epoch_open = False
         self.step += 1
+        if self.adapters is not None:
+            self.adapters.validate_replica_coherence()
         return {"metrics": {"grad_norm": float(norm_scaled), "step": float(self.step),
                             "learning_rate": opt.lr, "tokens": float(tokens)}}
 
