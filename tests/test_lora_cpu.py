@@ -241,3 +241,86 @@ def test_qlora_on_moe_experts_trains_and_loads_a_full_precision_checkpoint(tmp_p
         opt.step()
     assert losses[-1] < losses[0], losses
     reset_parallel_state()
+
+
+def test_qarl_config_grids_and_scope():
+    import pytest
+    from xorl_b200.adapters import qarl
+    assert qarl.normalize_quant_cfg(None)["format"] == "fp8_e4m3" and qarl.normalize_quant_cfg(None)["activation"]
+    nv = qarl.normalize_quant_cfg("nvfp4")
+    assert nv == {"format": "nvfp4", "weight": True, "activation": False, "dynamic": True, "group_size": 16}
+    assert qarl.normalize_quant_cfg({"quant_method": "FP8_DEFAULT_CFG", "weight_block_size": [64, 128]})["weight_block_size"] == [64, 128]
+    for bad in ({"format": "int3"}, {"format": "nvfp4", "group_size": 32}, {"dynamic": False}, {"blocks": 1},
+                {"weight_block_size": [0, 128]}, 7):
+        with pytest.raises(ValueError):
+            qarl.normalize_quant_cfg(bad)
+    assert qarl.unsupported_scope({"num_nextn_predict_layers": 1}) and qarl.unsupported_scope({"model_type": "Mamba2"})
+    assert qarl.unsupported_scope(None, ["model.mtp_head.proj"]) and qarl.unsupported_scope({"model_type": "qwen3"}) is None
+    # grids: values land on the grid, the gradient passes straight through
+    torch.manual_seed(0)
+    w = torch.randn(96, 160, requires_grad=True)
+    fq, scales = qarl.fake_quant_fp8_blocks(w, (64, 128))
+    assert scales.shape == (2, 2)
+    again, _ = qarl.fake_quant_fp8_blocks(fq.detach(), (64, 128))
+    assert torch.allclose(again, fq.detach(), rtol=0, atol=1e-6)           # already on the grid
+    assert 0 < float((fq - w).detach().abs().max()) < 0.2
+    fq.square().sum().backward()
+    assert torch.allclose(w.grad, 2 * fq.detach())
+    x = torch.randn(8, 160)
+    xq, s = qarl.fake_quant_fp8_tensor(x)
+    assert abs(float(s) - float(x.abs().max()) / 448.0) < 1e-9 and float((xq - x).abs().max()) < float(x.abs().max()) / 14
+    e = torch.randn(3, 32, 20)                                              # [E, K, N]: groups along K
+    eq = qarl.fake_quant_nvfp4(e, 16, dim=1)
+    per_group = eq.transpose(1, 2).reshape(3, 20, 2, 16)
+    assert all(len(torch.unique(per_group[i, j, g].abs())) <= 8 for i in range(3) for j in range(3) for g in range(2))
+
+
+def test_qarl_trains_dense_fp8_and_moe_nvfp4(tmp_path):
+    """Dense model on the fp8 grid (weights + activations) and a MoE model on the nvfp4 grid (linears and
+    stacked experts): both learn, the masters stay full precision, the statistics fill up, calibration
+    writes its summary and the sync configuration lists exactly the wrapped modules."""
+    import json
+    import pytest
+    from xorl_b200.adapters import qarl
+    from xorl_b200.arguments import TrainingArguments
+    from xorl_b200.models.moe import Experts
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.zero import Zero3Engine
+    reset_parallel_state()
+    ps = init_parallel_state(device_type="cpu")
+    calib = tmp_path / "calib.jsonl"
+    calib.write_text("\n".join(json.dumps({"input_ids": list(range(5 + i, 45 + i))}) for i in range(3)))
+    for name, cfgq, n_experts in (("tiny-qwen3", None, 0), ("tiny-qwen3-moe", "nvfp4", 2)):
+        ta = TrainingArguments(output_dir=str(tmp_path / name), enable_qarl=True, qarl_quant_cfg=cfgq,
+                               qarl_exclude_modules=["o_proj"], device="cpu")
+        model = DecoderLM(preset(name, tie_word_embeddings=False), device="meta")
+        wrapped = qarl.inject_fake_quant(model, ta)
+        assert wrapped and not any("o_proj" in w or "lm_head" in w or w.endswith(".gate") for w in wrapped)
+        assert sum(isinstance(m, Experts) for m in model.modules()) == len(model._xb_qarl_config["experts"]) == n_experts
+        eng = Zero3Engine(model, ps, compute_dtype=torch.float32, device=torch.device("cpu"))
+        opt = build_optimizer(eng, lr=3e-3, weight_decay=0.0)
+        summary = qarl.calibrate(lambda ids: eng.forward_only(ids), model, str(calib), size=2, sequence_length=32)
+        assert summary["calibration_batches"] == 2 and summary["enabled"]
+        assert all(v["forward_count"] == 2 and v["weight_amax"] > 0 for v in summary["modules"].values())
+        ids = torch.randint(0, 1024, (2, 65))
+        losses = []
+        for _ in range(5):
+            opt.zero_grad()
+            losses.append(float(eng.forward_backward(ids[:, :-1], ids[:, 1:], grad_scale=1.0 / 128)))
+            eng.finish_grad_sync()
+            opt.step()
+        assert losses[-1] < losses[0] - 0.05, (name, losses)
+        full = dict(eng.iter_full_tensors("master"))
+        some = next(v for k, v in full.items() if "q_proj" in k or "qkv_proj" in k)
+        regrid = qarl.fake_quant(some, "nvfp4" if cfgq else "fp8")
+        assert float((regrid - some).abs().max()) > 0                       # the masters are not on the grid
+        sync = qarl.sync_quantization_config(model)
+        assert sync["quant_method"] == ("nvfp4" if cfgq else "fp8")
+        assert set(sync["qarl"]["folded_modules"]) == set(wrapped)
+        assert any("o_proj" in m for m in sync["modules_to_not_convert"]) and "lm_head" in sync["modules_to_not_convert"]
+        assert not set(sync["modules_to_not_convert"]) & set(wrapped)
+    # fp8 on a MoE model is refused
+    with pytest.raises(ValueError, match="nvfp4"):
+        qarl.inject_fake_quant(DecoderLM(preset("tiny-qwen3-moe"), device="meta"),
+                               TrainingArguments(output_dir=str(tmp_path / "x"), enable_qarl=True, device="cpu"))
+    reset_parallel_state()

@@ -285,6 +285,44 @@ def test_weight_sync_transports(tmp_path, tiny_runner):
     assert [n for n, _ in q] == ["x.q_proj.weight", "x.q_proj.weight_scale_inv"] and q[0][1].dtype == torch.uint8
 
 
+def test_fake_quantised_policy_syncs_its_wrapped_weights_on_the_trained_grid(tmp_path):
+    """A server started with ``enable_qarl``: calibration ran at start-up, and a weight sync carries e4m3
+    bytes + block scales for exactly the wrapped projections (not for the excluded one, the lm-head or the
+    embedding), with the quantisation block the receiver needs."""
+    import json
+    from safetensors.torch import load_file
+    from xorl_b200.parallel.state import reset_parallel_state
+    from xorl_b200.server import weight_sync as ws
+    from xorl_b200.server.runner import ModelRunner
+    from xorl_b200.server.server_arguments import ServerArguments
+    from xorl_b200.trainers.trainer import Trainer
+    reset_parallel_state()
+    calib = tmp_path / "calib.json"
+    calib.write_text(json.dumps({"input_ids": [list(range(3, 40)), list(range(9, 46))]}))
+    with pytest.raises(ValueError):
+        ServerArguments(model_preset="tiny-qwen3", enable_qarl=True, enable_lora=True)
+    sa = ServerArguments(model_preset="tiny-qwen3", output_dir=str(tmp_path / "srv"), device="cpu",
+                         sample_packing_sequence_len=256, enable_mixed_precision=False, enable_qarl=True,
+                         qarl_exclude_modules=["down_proj"], qarl_calib_data=str(calib), qarl_calib_size=1)
+    r = ModelRunner(Trainer(sa.to_trainer_arguments()))
+    with open(tmp_path / "srv" / "qarl_calibration.json") as f:
+        cal = json.load(f)
+    assert cal["calibration_batches"] == 1 and cal["linear_count"] > 0
+    out = ws.WeightSyncHandler(r).sync(backend="file", directory=str(tmp_path / "w"))
+    assert out["quantization"] == "fp8" and out["quantization_config"]["weight_block_size"] == [128, 128]
+    got = {}
+    for f in sorted(os.listdir(tmp_path / "w")):
+        if f.endswith(".safetensors"):
+            got.update(load_file(str(tmp_path / "w" / f)))
+    assert got["model.layers.0.mlp.up_proj.weight"].dtype == torch.uint8
+    assert "model.layers.0.mlp.up_proj.weight_scale_inv" in got
+    assert got["model.layers.0.mlp.down_proj.weight"].dtype == torch.bfloat16
+    assert not any(k.startswith("lm_head") and k.endswith("scale_inv") for k in got)
+    with pytest.raises(ValueError, match="differs"):
+        ws.WeightSyncHandler(r).sync(backend="file", directory=str(tmp_path / "w2"), quantization="nvfp4")
+    reset_parallel_state()
+
+
 def test_endpoint_requests_revalidate_the_resolved_address(monkeypatch):
     """A hostname that resolved to a safe address at registration and to the metadata address
     later: the later request is refused, and requests go to the validated address literal, never

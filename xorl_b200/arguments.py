@@ -271,6 +271,16 @@ class TrainingArguments:
             raise ValueError("enable_step_memory_profiling requires enable_step_phase_timing=True")
         if self.enable_qarl and self.enable_fp8_training:
             raise ValueError("enable_qarl cannot be combined with enable_fp8_training")
+        if self.enable_qarl:
+            if self.qarl_calib_size < 0:
+                raise ValueError("qarl_calib_size must be non-negative")
+            if self.qarl_quant_sequence_length is not None and self.qarl_quant_sequence_length <= 0:
+                raise ValueError("qarl_quant_sequence_length must be positive when set")
+            if self.qarl_calib_data is None and (self.qarl_calib_size or self.qarl_quant_sequence_length is not None):
+                raise ValueError("qarl_calib_size and qarl_quant_sequence_length require qarl_calib_data")
+            from .adapters.qarl import normalize_quant_cfg
+            self.qarl_quant_cfg = normalize_quant_cfg(self.qarl_quant_cfg, default_format=self.qarl_sync_format
+                                                      if self.qarl_sync_format != "bf16" else "fp8")
         if self.fp8_cfg:
             self.enable_fp8_training = bool(self.fp8_cfg.get("enabled", True)) or self.enable_fp8_training
         sched = self.pipeline_parallel_schedule.lower()
@@ -390,6 +400,8 @@ class Arguments:
             raise ValueError("tensor parallelism cannot be combined with LoRA")
         if t.pipeline_parallel_size > 1 and self.data.sample_packing_sequence_len is None:
             raise ValueError("pipeline parallelism requires sample packing")
+        if t.enable_qarl and (self.lora.enable_lora or self.lora.enable_qlora):
+            raise ValueError("enable_qarl trains the full weights and cannot be combined with LoRA or QLoRA")
         # keys whose value asks for something that is not built raise here instead of being ignored
         from .config_policy import check_supported
         for section in ("model", "data", "train", "lora", "distill"):

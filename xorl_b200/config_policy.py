@@ -110,10 +110,6 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "muon_update_dtype": (_falsy, "Muon updates are bf16 Newton-Schulz iterates applied to fp32 masters"),
         "muon_force_momentum_path": (_falsy, "not built"),
         "muon_distributed_mode": (_is("shard_local"), "full-matrix Muon over gathered gradients is not built"),
-        "qarl_quant_cfg": (_falsy, "QARL uses the built-in fake-quant configuration"),
-        "qarl_calib_data": (_falsy, "QARL calibration is not built"),
-        "qarl_calib_size": (_falsy, "QARL calibration is not built"),
-        "qarl_quant_sequence_length": (_falsy, "QARL calibration is not built"),
         "fp8_training_block_size": (_is(128), "block fp8 uses 128-wide blocks (1 x 128 activations, 128 x 128 weights)"),
         "fp8_training_smoothquant_alpha": (_falsy, "SmoothQuant rescaling is not built"),
         "fp8_training_lm_head_smoothquant_alpha": (_falsy, "SmoothQuant rescaling is not built"),

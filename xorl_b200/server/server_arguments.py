@@ -45,6 +45,15 @@ class ServerArguments:
     enable_qlora: bool = False
     quant_format: str = "nvfp4"
     max_adapters_per_model: int = 8
+    # quantisation-aware RL: full-weight training on the grid the inference engine serves
+    enable_qarl: bool = False
+    qarl_quant_cfg: Optional[Any] = None
+    qarl_calib_data: Optional[str] = None
+    qarl_calib_size: int = 0
+    qarl_quant_sequence_length: Optional[int] = None
+    qarl_sync_format: str = "fp8"
+    qarl_target_modules: Optional[List[str]] = None
+    qarl_exclude_modules: Optional[List[str]] = None
     # service
     api_host: str = "127.0.0.1"
     api_port: int = 8000
@@ -79,6 +88,8 @@ class ServerArguments:
             raise ValueError(f"api_port {self.api_port} is not a TCP port")
         if self.enable_qlora and not self.enable_lora:
             raise ValueError("enable_qlora needs enable_lora (the quantised base is frozen; only adapters train)")
+        if self.enable_qarl and (self.enable_lora or self.enable_qlora):
+            raise ValueError("enable_qarl trains the full weights and cannot be combined with LoRA or QLoRA")
         if self.max_adapters_per_model < 1:
             raise ValueError("max_adapters_per_model must be at least 1")
         if self.future_ttl_seconds <= 0 or self.session_timeout_seconds <= 0:
@@ -118,6 +129,12 @@ class ServerArguments:
                       "enable_mixed_precision": self.enable_mixed_precision,
                       "enable_gradient_checkpointing": self.enable_gradient_checkpointing,
                       "device": self.device, "comm_backend": self.comm_backend,
+                      "enable_qarl": self.enable_qarl, "qarl_quant_cfg": self.qarl_quant_cfg,
+                      "qarl_calib_data": self.qarl_calib_data, "qarl_calib_size": self.qarl_calib_size,
+                      "qarl_quant_sequence_length": self.qarl_quant_sequence_length,
+                      "qarl_sync_format": self.qarl_sync_format,
+                      "qarl_target_modules": self.qarl_target_modules,
+                      "qarl_exclude_modules": self.qarl_exclude_modules,
                       "max_steps": 1, "lr_warmup_ratio": 0.0, "lr_decay_style": "constant"},
             "lora": {"enable_lora": self.enable_lora, "lora_rank": self.lora_rank,
                      "lora_alpha": self.lora_alpha, "lora_target_modules": self.lora_target_modules,

@@ -139,9 +139,14 @@ class EndpointManager:
 # ---------------------------------------------------------------------------------------------
 # tensor stream
 # ---------------------------------------------------------------------------------------------
-def _quantise(name: str, t: torch.Tensor, fmt: Optional[str]) -> List[Tuple[str, torch.Tensor]]:
-    if fmt in (None, "bf16") or t.dim() != 2 or not name.endswith(".weight") \
-            or "embed" in name or "lm_head" in name or "norm" in name or ".gate.weight" in name:
+def _quantise(name: str, t: torch.Tensor, fmt: Optional[str], selected: Optional[bool] = None
+              ) -> List[Tuple[str, torch.Tensor]]:
+    """``selected``: None = every 2-D projection weight is converted (by name); True / False = the caller
+    knows whether this weight's module is one of the modules to convert (a fake-quantised model exports
+    exactly the weights it trained on the grid)."""
+    if fmt in (None, "bf16") or t.dim() != 2 or not name.endswith(".weight") or selected is False:
+        return [(name, t)]
+    if selected is None and ("embed" in name or "lm_head" in name or "norm" in name or ".gate.weight" in name):
         return [(name, t)]
     if fmt == "fp8":
         if t.shape[0] % 128 or t.shape[1] % 128:
@@ -155,8 +160,8 @@ def _quantise(name: str, t: torch.Tensor, fmt: Optional[str]) -> List[Tuple[str,
 
 
 def iter_sync_tensors(engine, cfg, dtype=torch.bfloat16, quantization: Optional[str] = None,
-                      merged_lora: Optional[Callable[[str, torch.Tensor], torch.Tensor]] = None
-                      ) -> Iterator[Tuple[str, torch.Tensor]]:
+                      merged_lora: Optional[Callable[[str, torch.Tensor], torch.Tensor]] = None,
+                      only_modules: Optional[set] = None) -> Iterator[Tuple[str, torch.Tensor]]:
     """(engine-side name, tensor) for every weight, in model order.  All ranks of the shard groups
     must iterate together (the gathers are collectives); only the consumer on rank 0 uses them."""
     handler = get_checkpoint_handler(cfg)
@@ -169,8 +174,9 @@ def iter_sync_tensors(engine, cfg, dtype=torch.bfloat16, quantization: Optional[
             if merged_lora is not None:
                 t = merged_lora(fqn, t)
             t = t.to(dtype)
+            sel = None if only_modules is None else fqn.rsplit(".", 1)[0] in only_modules
             for name, part in handler.to_hf(fqn, t):
-                yield from _quantise(name, part, quantization)
+                yield from _quantise(name, part, quantization, sel)
 
     ps = engine.ps
     if getattr(ps, "pp_size", 1) <= 1 or not dist.is_initialized():
@@ -481,7 +487,18 @@ class WeightSyncHandler:
             self.endpoints.broadcast_post("/pause_generation", lambda e, off: {})
         names, nbytes, nb = 0, 0, 0
         merged = getattr(r.trainer, "lora_merged_view", None)
-        stream = iter_sync_tensors(r.engine, r.model.config, torch.bfloat16, quant, merged)
+        only, qcfg = None, None
+        if getattr(r.model, "_xb_qarl_config", None):
+            # a fake-quantised policy: the receiver gets exactly the wrapped weights, on the grid they trained on
+            from ..adapters.qarl import sync_quantization_config
+            qcfg = sync_quantization_config(r.model)
+            trained = qcfg["quant_method"]
+            fmt = getattr(r.trainer.args.train, "qarl_sync_format", trained)
+            if quant not in (None, "bf16", trained):
+                raise ValueError(f"sync quantization {quant!r} differs from the grid the policy trains on ({trained!r})")
+            if quant != "bf16" and fmt != "bf16":
+                quant, only = trained, set(qcfg["qarl"]["folded_modules"])
+        stream = iter_sync_tensors(r.engine, r.model.config, torch.bfloat16, quant, merged, only)
         for bucket in bucketize(stream, bucket_size_mb << 20):
             if not driver:
                 continue
@@ -506,4 +523,6 @@ class WeightSyncHandler:
             self.endpoints.broadcast_post("/continue_generation", lambda e, off: {})
         self.last = {"synced": True, "tensors": names, "bytes": nbytes, "buckets": nb,
                      "seconds": time.time() - t0, "backend": backend, "quantization": quant, **extra}
+        if only is not None:
+            self.last["quantization_config"] = qcfg
         return self.last

@@ -54,6 +54,8 @@ class Trainer:
         self._timed("build_data", lambda: self._build_data(dataset))
         self._timed("build_optimizer", self._build_optimizer)
         self._timed("observability", self._setup_observability)
+        if args.train.enable_qarl and args.train.qarl_calib_data:
+            self._timed("qarl_calibration", self._qarl_calibration)
         self._timed("resume", self._resume_checkpoint)
         head_rows = [p.shape[0] for n, p in self.model.named_parameters() if n.endswith("lm_head.weight")]
         self.startup["lm_head_rows_per_rank"] = head_rows[0] if head_rows else 0
@@ -259,6 +261,19 @@ class Trainer:
         self.lr_scheduler = build_lr_scheduler(self.optimizer, self.train_steps, t.lr, t.lr_min,
                                                t.lr_start, t.lr_warmup_ratio, t.lr_decay_style,
                                                t.lr_decay_ratio)
+
+    def _qarl_calibration(self) -> None:
+        """Calibration batches through the fake-quantised model before training: fills the wrapped modules'
+        statistics and writes them to ``qarl_calibration.json`` (src/xorl/qarl/calibration.py:110-138)."""
+        from ..adapters import qarl
+        t = self.args.train
+        out = qarl.calibrate(lambda ids: self.engine.forward_only(ids), self.model, t.qarl_calib_data,
+                             t.qarl_calib_size, t.qarl_quant_sequence_length, device=self.device)
+        self.qarl_calibration = out
+        if self.ps.rank == 0:
+            os.makedirs(t.output_dir, exist_ok=True)
+            with open(os.path.join(t.output_dir, "qarl_calibration.json"), "w") as f:
+                json.dump(out, f, indent=2)
 
     def _setup_observability(self) -> None:
         t = self.args.train
