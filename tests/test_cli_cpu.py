@@ -3,6 +3,7 @@ import json
 import os
 import sys
 
+import pytest
 import torch
 import yaml
 
@@ -55,12 +56,39 @@ def test_export_quantized_roundtrip(tmp_path):
     assert torch.equal(out["lm_head.weight"], w["lm_head.weight"])
     cfg = json.load(open(tmp_path / "fp8" / "config.json"))
     assert cfg["quantization_config"]["weight_block_size"] == [128, 128] and cfg["hidden_size"] == 128
-    export_nvfp4.main(["--src", str(src), "--dst", str(tmp_path / "fp4")])
+    # nvfp4: serving layout; q / k / v of one layer share the per-tensor scale, the lone projection has its own
+    w2 = dict(w)
+    w2["model.layers.0.self_attn.k_proj.weight"] = (torch.randn(64, 128) * 3).bfloat16()
+    w2["model.layers.0.self_attn.v_proj.weight"] = (torch.randn(64, 128) * 0.1).bfloat16()
+    src2 = tmp_path / "src2"
+    os.makedirs(src2)
+    save_file(w2, str(src2 / "model.safetensors"))
+    (src2 / "config.json").write_text(json.dumps({"model_type": "qwen3", "hidden_size": 128}))
+    amax = tmp_path / "amax.json"
+    amax.write_text(json.dumps({"modules": {"model.layers.0.mlp.down_proj": {"input_amax": 5.0}}}))
+    st4 = export_nvfp4.main(["--src", str(src2), "--dst", str(tmp_path / "fp4"), "--act-amax", str(amax)])
+    assert st4["quantized"] == 4 and st4["kept"] == 2 and st4["fused_groups"] == 1
     out4 = load_file(str(tmp_path / "fp4" / "model-00001.safetensors"))
-    k = "model.layers.0.mlp.down_proj.weight"
-    back4 = Q.nvfp4_dequantize(out4[k], out4[k + "_scale"], out4[k + "_scale_2"][0], (128, 384), dtype=torch.float32)
-    assert (back4 - w[k].float()).norm() / w[k].float().norm() < 0.15
+    k = "model.layers.0.mlp.down_proj"
+    assert out4[k + ".weight"].shape == (128, 192) and out4[k + ".weight_scale"].shape == (128, 24)
+    assert out4[k + ".weight_scale"].dtype == torch.float8_e4m3fn and out4[k + ".weight_scale_2"].dim() == 0
+    assert abs(float(out4[k + ".input_scale"]) - 5.0 / (6 * 448)) < 1e-9
+    back4 = Q.nvfp4_dequantize(out4[k + ".weight"].reshape(-1), out4[k + ".weight_scale"], out4[k + ".weight_scale_2"],
+                               (128, 384), dtype=torch.float32)
+    assert (back4 - w[k + ".weight"].float()).norm() / w[k + ".weight"].float().norm() < 0.15
+    a = "model.layers.0.self_attn."
+    shared = {float(out4[a + p + ".weight_scale_2"]) for p in ("q_proj", "k_proj", "v_proj")}
+    assert len(shared) == 1 and abs(shared.pop() - float(w2[a + "k_proj.weight"].float().abs().max()) / (6 * 448)) < 1e-7
+    assert a + "q_proj.input_scale" not in out4
+    vb = Q.nvfp4_dequantize(out4[a + "v_proj.weight"].reshape(-1), out4[a + "v_proj.weight_scale"],
+                            out4[a + "v_proj.weight_scale_2"], (64, 128), dtype=torch.float32)
+    ref_v = w2[a + "v_proj.weight"].float()
+    assert (vb - ref_v).norm() / ref_v.norm() < 0.2             # the small member survives the shared scale
+    hq = json.load(open(tmp_path / "fp4" / "hf_quant_config.json"))["quantization"]
+    assert hq["quant_algo"] == "NVFP4" and hq["exclude_modules"] == ["lm_head"]
     assert json.load(open(tmp_path / "fp4" / "config.json"))["quantization_config"]["format"] == "nvfp4"
+    with pytest.raises(FileExistsError):
+        export_nvfp4.main(["--src", str(src2), "--dst", str(tmp_path / "fp4")])
 
 
 def test_convert_hf_to_dcp_roundtrip(tmp_path):

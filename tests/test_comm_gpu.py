@@ -52,7 +52,6 @@ def _worker():
     from xorl_b200.ops import _lib
     from xorl_b200.optim import build_optimizer
     from xorl_b200.parallel.state import init_parallel_state
-    from xorl_b200.parallel.symm import try_attach_symmetric_transport
     from xorl_b200.parallel.zero import Zero3Engine
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -67,7 +66,7 @@ def _worker():
         model = DecoderLM(cfg, device="meta")
         eng = Zero3Engine(model, ps, compute_dtype=torch.bfloat16, device=dev, seed=0)
         if mode == "fused":
-            assert try_attach_symmetric_transport(eng, required=True)
+            assert eng.attach_peer_transport(required=True)
         opt = build_optimizer(eng, lr=1e-3, weight_decay=0.0)
         T = 1024
         losses = []

@@ -64,15 +64,33 @@ def test_block_fp8_gemm_matches_fp32_reference(M, N, K):
     assert (out.float() - dense).norm() / dense.norm() < 0.06  # fp8 quantisation noise
 
 
-def test_fp8_linear_training_step():
+@pytest.mark.parametrize("shape", [(512, 256, 384), (200, 320, 200)])
+def test_fp8_linear_training_step(shape):
+    """Forward and input-gradient GEMMs on e4m3 operands (cached weight codes, transposed for dgrad), weight
+    gradient in bf16; sizes that are not multiples of 128 are padded."""
     from xorl_b200.adapters.fp8 import _FP8LinearFn
-    x = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    w = (torch.randn(384, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
-    y = _FP8LinearFn.apply(x, w, True)
-    y.float().square().mean().backward()
-    ref = x.detach().float() @ w.detach().float().t()
-    assert (y.float() - ref).norm() / ref.norm() < 0.06
-    assert x.grad is not None and w.grad is not None and torch.isfinite(w.grad).all()
+    from xorl_b200.ops import fp8_grouped
+    M, K, N = shape
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16().requires_grad_()
+    g = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    for fp8_backward in (True, False):
+        x.grad = w.grad = None
+        y = _FP8LinearFn.apply(x, w, fp8_backward)
+        y.backward(g)
+        ref = x.detach().float() @ w.detach().float().t()
+        dx_ref = g.float() @ w.detach().float()
+        dw_ref = g.float().t() @ x.detach().float()
+        assert (y.float() - ref).norm() / ref.norm() < 0.06
+        assert (x.grad.float() - dx_ref).norm() / dx_ref.norm() < (0.06 if fp8_backward else 0.01)
+        assert (w.grad.float() - dw_ref).norm() / dw_ref.norm() < 0.01
+    cache = w._xb_fp8_cache
+    _FP8LinearFn.apply(x, w, True)
+    assert w._xb_fp8_cache is cache                           # weights unchanged: codes reused
+    fp8_grouped.invalidate_weight_cache()
+    _FP8LinearFn.apply(x, w, True)
+    assert w._xb_fp8_cache is not cache
 
 
 def test_token_loss_head_matches_autograd():

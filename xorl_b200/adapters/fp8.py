@@ -16,38 +16,84 @@ from ..models.layers import Linear
 from ..ops import quantize as Q
 
 
+def _pad_last(t: torch.Tensor, multiple: int = 128) -> torch.Tensor:
+    pad = (-t.shape[-1]) % multiple
+    return torch.nn.functional.pad(t, (0, pad)) if pad else t
+
+
+class _QuantizedWeight:
+    """e4m3 copies of one weight: ``[N, Kp]`` for the forward GEMM and ``[Kp, Np]`` (the transpose, the
+    same 128 x 128 blocks) for the input-gradient GEMM; ``Kp`` / ``Np`` are the sizes padded to 128."""
+    __slots__ = ("q_nk", "s_nk", "q_kn", "s_kn", "epoch", "ptr")
+
+
+def quantized_weight(w: torch.Tensor, need_transpose: bool) -> _QuantizedWeight:
+    """Quantised copies of ``w``, kept on the parameter object until the optimizers announce changed
+    weights (``ops.fp8_grouped.invalidate_weight_cache``): with gradient accumulation and recomputation a
+    weight is used many times per step and quantised once.  ``XORL_B200_FP8_WEIGHT_CACHE=0`` quantises
+    on every use instead (no fp8 copy of the model stays resident)."""
+    import os
+    from ..ops import fp8_gemm, fp8_grouped
+    use_cache = os.environ.get("XORL_B200_FP8_WEIGHT_CACHE", "1") == "1"
+    c = getattr(w, "_xb_fp8_cache", None) if use_cache else None
+    if c is None or c.epoch != fp8_grouped._weight_epoch or c.ptr != w.data_ptr():
+        c = _QuantizedWeight()
+        with torch.no_grad():
+            wp = _pad_last(w.detach())
+            if wp.shape[0] % 128:
+                wp = torch.nn.functional.pad(wp, (0, 0, 0, (-wp.shape[0]) % 128))
+            c.q_nk, c.s_nk = fp8_gemm.quantize_blocks(wp)
+        c.q_kn = c.s_kn = None
+        c.epoch, c.ptr = fp8_grouped._weight_epoch, w.data_ptr()
+        if use_cache:
+            try:
+                w._xb_fp8_cache = c
+            except AttributeError:
+                pass
+    if need_transpose and c.q_kn is None:
+        # square blocks: the transposed weight has the transposed codes and the transposed scale grid
+        c.q_kn, c.s_kn = c.q_nk.t().contiguous(), c.s_nk.t().contiguous()
+    return c
+
+
 class _FP8LinearFn(torch.autograd.Function):
+    """y = x W^T on e4m3 operands (1 x 128 activation scales, 128 x 128 weight scales).  With
+    ``fp8_backward`` the input gradient dx = dy W is an fp8 GEMM too (dy quantised along the output
+    features); the weight gradient stays in the compute dtype (src/xorl/fp8_training/linear.py:85-333)."""
+
     @staticmethod
     def forward(ctx, x, w, fp8_backward: bool):
-        x2 = x.reshape(-1, x.shape[-1])
-        K = x2.shape[1]
-        pad = (-K) % 128
-        if pad:
-            x2p = torch.nn.functional.pad(x2, (0, pad))
-            wp = torch.nn.functional.pad(w, (0, pad))
-        else:
-            x2p, wp = x2, w
         from ..ops import fp8_gemm
-        aq, as_ = fp8_gemm.quantize_rows(x2p)
-        bq, bs = fp8_gemm.quantize_blocks(wp)
-        y = fp8_gemm.block_fp8_gemm(aq, as_, bq, bs, out_dtype=x.dtype)
+        x2 = x.reshape(-1, x.shape[-1])
+        N, K = w.shape
+        qw = quantized_weight(w, need_transpose=False)
+        aq, as_ = fp8_gemm.quantize_rows(_pad_last(x2))
+        y = fp8_gemm.block_fp8_gemm(aq, as_, qw.q_nk, qw.s_nk, out_dtype=x.dtype)[:, :N]
         ctx.save_for_backward(x2, w)
         ctx.fp8_backward = fp8_backward
         ctx.x_shape = x.shape
-        return y.reshape(*x.shape[:-1], w.shape[0])
+        return y.reshape(*x.shape[:-1], N)
 
     @staticmethod
     def backward(ctx, dy):
         x2, w = ctx.saved_tensors
-        dy2 = dy.reshape(-1, dy.shape[-1])
+        N, K = w.shape
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        from ..ops import fp8_gemm
         from ..ops.gemm import gemm
-        if dy2.is_cuda and dy2.dtype == torch.bfloat16:
-            dx = gemm(dy2.contiguous(), w, b_mn=True)
-            dw = gemm(dy2.contiguous(), x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
-        else:
-            dx = dy2 @ w
-            dw = dy2.t() @ x2
-        return dx.reshape(ctx.x_shape), dw, None
+        on_kernel = dy2.is_cuda and dy2.dtype == torch.bfloat16
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            if ctx.fp8_backward:
+                qw = quantized_weight(w, need_transpose=True)
+                gq, gs = fp8_gemm.quantize_rows(_pad_last(dy2))
+                dx = fp8_gemm.block_fp8_gemm(gq, gs, qw.q_kn, qw.s_kn, out_dtype=dy2.dtype)[:, :K]
+            else:
+                dx = gemm(dy2, w, b_mn=True) if on_kernel else dy2 @ w
+            dx = dx.reshape(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype) if on_kernel else dy2.t() @ x2
+        return dx, dw, None
 
 
 class FP8Linear(nn.Module):

@@ -9,7 +9,7 @@ Reference: src/xorl/ops/quantize/{block_fp8,nvfp4,nf4,int4,mxfp4}_quantize.py, f
 """
 from __future__ import annotations
 
-from typing import Dict, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -121,11 +121,15 @@ def _e2m1_decode(codes: torch.Tensor) -> torch.Tensor:
     return torch.where((codes & 8) > 0, -mag, mag)
 
 
-def nvfp4_quantize(w: torch.Tensor, group: int = 16):
-    """e2m1 values, one e4m3 scale per 16 elements, one fp32 global scale per tensor."""
+def nvfp4_quantize(w: torch.Tensor, group: int = 16, global_scale: Optional[torch.Tensor] = None):
+    """e2m1 values, one e4m3 scale per 16 elements, one fp32 global scale per tensor (``global_scale``
+    forces a given one: matrices that a consumer fuses into one GEMM must share it)."""
     xg = _group(w, group)
-    gmax = xg.abs().max().clamp_min(1e-12)
-    global_scale = gmax / (6.0 * FP8_MAX)
+    if global_scale is None:
+        gmax = xg.abs().max().clamp_min(1e-12)
+        global_scale = gmax / (6.0 * FP8_MAX)
+    else:
+        global_scale = torch.as_tensor(global_scale, dtype=torch.float32, device=w.device).reshape(())
     bs = (xg.abs().amax(-1, keepdim=True) / 6.0 / global_scale).clamp(1e-12, FP8_MAX)
     bs8 = bs.to(torch.float8_e4m3fn)
     denom = (bs8.float() * global_scale).clamp_min(1e-30)

@@ -15,7 +15,7 @@ Replaces the reference's use of ``torch.distributed.fsdp.fully_shard``
   unit's backward.
 
 Transports: ``nccl`` / ``gloo`` collectives (baseline, and the CPU lane) or the fused peer-memory
-kernels of ``parallel/symm.py`` when available.
+kernels of ``parallel/symm_transport.py`` when available.
 """
 from __future__ import annotations
 
@@ -282,7 +282,7 @@ class Zero3Engine:
         self.norm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
         self._full_pool: Dict[Tuple[int, torch.dtype], List[torch.Tensor]] = {}
         self._build_units(seed)
-        self.symm = None  # fused peer-memory transport (attached by parallel.symm when usable)
+        self.symm = None  # fused peer-memory transport (attach_peer_transport)
 
     # ---------------------------------------------------------------------------------------
     # construction
@@ -368,6 +368,23 @@ class Zero3Engine:
             for k, b in list(m._buffers.items()):
                 if b is not None and b.device != self.device and not b.is_meta:
                     m._buffers[k] = b.to(self.device)
+
+    def attach_peer_transport(self, required: bool = False) -> bool:
+        """Moves the compute-dtype shards into a symmetric heap and switches parameter gathers and gradient
+        reduce-scatters to the framework's own kernels / copy-engine transfers over peer memory
+        (``parallel/symm_transport.py``).  Returns False (and keeps the collective library) when peer
+        mapping is not available, unless ``required``."""
+        try:
+            from .symm_transport import SymmetricTransport
+            self.symm = SymmetricTransport.create(self)
+            return self.symm is not None
+        except Exception as e:  # noqa: BLE001
+            if required:
+                raise
+            from ..utils.logging import warning_rank0
+            warning_rank0(f"fused peer-memory transport unavailable ({e!r}); using NCCL collectives")
+            self.symm = None
+            return False
 
     def _materialize_group(self, g: FlatParamGroup, std, seed, index_of, zc, init_fn) -> None:
         """Builds the unit's full fp32 image once (initialising meta parameters in place), keeps

@@ -167,8 +167,7 @@ class Trainer:
             backward_prefetch=True if t.enable_backward_prefetch is None else bool(t.enable_backward_prefetch),
             moe_grad_reduce_mode=t.moe_grad_reduce_mode)
         if t.comm_backend in ("auto", "fused") and self.device.type == "cuda" and self.ps.world_size > 1:
-            from ..parallel.symm import try_attach_symmetric_transport
-            try_attach_symmetric_transport(self.engine, required=(t.comm_backend == "fused"))
+            self.engine.attach_peer_transport(required=(t.comm_backend == "fused"))
         self.teacher_engine = None
         if a.distill.enable_distillation:
             self._build_teacher()

@@ -30,7 +30,6 @@ def main(argv=None) -> None:
     from ..models.decoder import DecoderLM
     from ..ops import _lib
     from ..parallel.state import init_parallel_state
-    from ..parallel.symm import try_attach_symmetric_transport
     from ..parallel.zero import Zero3Engine
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -45,7 +44,7 @@ def main(argv=None) -> None:
         model = DecoderLM(cfg, device="meta")
         eng = Zero3Engine(model, ps, compute_dtype=torch.bfloat16, device=dev, seed=0)
         symm_transport.MODE = mode
-        if mode != "nccl" and not try_attach_symmetric_transport(eng, required=False):
+        if mode != "nccl" and not eng.attach_peer_transport(required=False):
             if rank == 0:
                 print(json.dumps({"transport": mode, "unavailable": "symmetric memory could not be set up"}))
             continue
