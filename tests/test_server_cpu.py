@@ -285,6 +285,64 @@ def test_weight_sync_transports(tmp_path, tiny_runner):
     assert [n for n, _ in q] == ["x.q_proj.weight", "x.q_proj.weight_scale_inv"] and q[0][1].dtype == torch.uint8
 
 
+@pytest.mark.parametrize("preset_name", ["tiny-qwen3", "tiny-qwen3-moe"])
+def test_lora_policy_is_synced_with_its_adapter_folded_in(tmp_path, preset_name):
+    """The inference engine gets plain Hugging Face weights: base + scaling * B A (fused projections per
+    slice, stacked experts per expert).  A model loaded from the synced files without any adapter gives the
+    trained adapter model's log-probabilities; the engine's own base weights are untouched."""
+    from safetensors.torch import load_file
+    from xorl_b200.parallel.state import reset_parallel_state
+    from xorl_b200.server import weight_sync as ws
+    from xorl_b200.server.runner import ModelRunner
+    from xorl_b200.server.server_arguments import ServerArguments
+    from xorl_b200.trainers.trainer import Trainer
+    reset_parallel_state()
+    targets = ["q_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+    sa = ServerArguments(model_preset=preset_name, output_dir=str(tmp_path / "srv"), device="cpu",
+                         sample_packing_sequence_len=256, enable_mixed_precision=False, enable_lora=True,
+                         lora_rank=4, lora_alpha=8, lora_target_modules=targets)
+    r = ModelRunner(Trainer(sa.to_trainer_arguments()))
+    data = [{"tokens": list(range(3, 60))}]
+    base_lp = r.forward("default", data, None)["logprobs"][0]
+    for _ in range(3):
+        r.forward_backward("default", data, None)
+        r.optim_step("default", adam_params={"learning_rate": 2e-2})
+    tuned_lp = r.forward("default", data, None)["logprobs"][0]
+    assert max(abs(a - b) for a, b in zip(tuned_lp, base_lp)) > 0.1
+    before = {n: t.clone() for n, t in r.engine.iter_full_tensors("master") if "lora" not in n}
+    out = ws.WeightSyncHandler(r).sync(backend="file", directory=str(tmp_path / "w"))
+    assert out["synced"]
+    for n, t in r.engine.iter_full_tensors("master"):
+        if "lora" not in n:
+            assert torch.equal(t, before[n]), n                      # folding happened on copies
+    got = {}
+    for f in sorted(os.listdir(tmp_path / "w")):
+        if f.endswith(".safetensors"):
+            got.update(load_file(str(tmp_path / "w" / f)))
+    assert not any("lora" in k for k in got)
+    # a plain model (no adapters) loaded from the same stream in fp32 (the bf16 rounding of the wire format
+    # can flip a router's choice in a tiny random model, which says nothing about the folding)
+    from xorl_b200.adapters.lora import merged_weight_view
+    exact = dict(ws.iter_sync_tensors(r.engine, r.model.config, torch.float32, None, merged_weight_view(r.engine)))
+    assert set(exact) == set(got)
+    got = exact
+    reset_parallel_state()
+    sb = ServerArguments(model_preset=preset_name, output_dir=str(tmp_path / "srv2"), device="cpu",
+                         sample_packing_sequence_len=256, enable_mixed_precision=False)
+    r2 = ModelRunner(Trainer(sb.to_trainer_arguments()))
+    from xorl_b200.checkpoint.handlers import get_checkpoint_handler
+    from xorl_b200.checkpoint.hf_io import load_hf_weights
+    from safetensors.torch import save_file
+    os.makedirs(tmp_path / "hf")
+    save_file({k: v.contiguous() for k, v in got.items()}, str(tmp_path / "hf" / "model.safetensors"))
+    load_hf_weights(r2.engine, str(tmp_path / "hf"), r2.model.config)
+    plain_lp = r2.forward("default", data, None)["logprobs"][0]
+    moved = max(abs(a - b) for a, b in zip(tuned_lp, base_lp))
+    off = max(abs(a - b) for a, b in zip(plain_lp, tuned_lp))
+    assert off < 1e-4 and moved > 0.1, (off, moved)
+    reset_parallel_state()
+
+
 def test_fake_quantised_policy_syncs_its_wrapped_weights_on_the_trained_grid(tmp_path):
     """A server started with ``enable_qarl``: calibration ran at start-up, and a weight sync carries e4m3
     bytes + block scales for exactly the wrapped projections (not for the excluded one, the lm-head or the

@@ -261,6 +261,47 @@ def save_lora_checkpoint(engine, out_dir: str, base_model_name: str = "") -> Non
         json.dump(cfg, f, indent=2)
 
 
+def merged_weight_view(engine):
+    """``fn(name, full_weight) -> full_weight`` with the active adapter folded in
+    (``W + scaling * B A``, per output slice for fused projections, per expert for stacked experts), or
+    None for a model without adapters.  Building it gathers the adapter matrices (a collective: every
+    rank calls it); the frozen base weights in the engine are not touched, so training goes on with the
+    adapter separate.  This is what an inference engine is sent for a LoRA policy
+    (src/xorl/trainers/training_utils.py:346-372 merges in place and unmerges afterwards)."""
+    mods = {n: m for n, m in engine.model.named_modules()
+            if isinstance(m, LoraLinear) or isinstance(getattr(m, "lora", None), ExpertsLoRA)}
+    if not mods:
+        return None
+    factors = {n: t.float() for n, t in engine.iter_full_tensors("master") if ".lora_" in n or "_lora_" in n}
+
+    def fold(name: str, w: torch.Tensor) -> torch.Tensor:
+        mod, _, leaf = name.rpartition(".")
+        m = mods.get(mod)
+        if isinstance(m, LoraLinear) and leaf == "weight":
+            out = w.float().clone()
+            for part, s, e in m.slices:
+                out[s:e] += (factors[f"{mod}.lora_B.{part}"] @ factors[f"{mod}.lora_A.{part}"]).to(out.device) * m.scaling
+            return out.to(w.dtype)
+        lora = getattr(m, "lora", None) if m is not None else None
+        if isinstance(lora, ExpertsLoRA) and leaf in ("gate_up_proj", "down_proj"):
+            out = w.float().clone()
+            I = out.shape[1] if leaf == "down_proj" else out.shape[2] // 2
+            for p in lora.targets:
+                if (p == "down_proj") != (leaf == "down_proj"):
+                    continue
+                delta = torch.bmm(factors[f"{mod}.lora.{p}_lora_A"], factors[f"{mod}.lora.{p}_lora_B"]).to(out.device)
+                delta = delta * lora.scaling
+                if p == "gate_proj":
+                    out[:, :, :I] += delta
+                elif p == "up_proj":
+                    out[:, :, I:] += delta
+                else:
+                    out += delta
+            return out.to(w.dtype)
+        return w
+    return fold
+
+
 @contextmanager
 def adapters_disabled(model: nn.Module):
     """Inside the block every LoRA module computes its frozen base projection only: the forward pass

@@ -168,7 +168,7 @@ def iter_sync_tensors(engine, cfg, dtype=torch.bfloat16, quantization: Optional[
 
     def local():
         for fqn, full in engine.iter_full_tensors("master"):
-            if ".lora_" in fqn:
+            if ".lora_" in fqn or "_lora_" in fqn or ".lora." in fqn:
                 continue
             t = full
             if merged_lora is not None:
@@ -486,7 +486,11 @@ class WeightSyncHandler:
         if driver and self.endpoints.endpoints:
             self.endpoints.broadcast_post("/pause_generation", lambda e, off: {})
         names, nbytes, nb = 0, 0, 0
-        merged = getattr(r.trainer, "lora_merged_view", None)
+        merged = None
+        if getattr(r.model, "_xb_lora_config", None):
+            # a LoRA policy is sent with its active adapter folded into the base weights
+            from ..adapters.lora import merged_weight_view
+            merged = merged_weight_view(r.engine)
         only, qcfg = None, None
         if getattr(r.model, "_xb_qarl_config", None):
             # a fake-quantised policy: the receiver gets exactly the wrapped weights, on the grid they trained on
