@@ -575,6 +575,53 @@ def test_adapter_sessions_have_their_own_rank_alpha_and_learning_rate(tmp_path):
     reset_parallel_state()
 
 
+def test_sampler_weights_of_a_lora_session_are_its_adapter_at_its_own_rank(tmp_path):
+    """``save_sampler_weights`` on a LoRA server writes a PEFT directory for the session (rank 2 of the
+    server's 4: matrices cut to two components, ``r`` / ``lora_alpha`` the session's), refuses a name that
+    exists, and with ``merged`` writes full weights instead."""
+    import json
+    from safetensors.torch import load_file
+    r = _lora_runner(tmp_path)
+    data = [{"tokens": list(range(3, 60))}]
+    r.create_model("small", lora_config={"rank": 2, "alpha": 6})
+    r.forward_backward("small", data, None)
+    r.optim_step("small", adam_params={"learning_rate": 5e-3})
+    out = r.save_sampler_weights("small", "s1")
+    assert out["kind"] == "lora_adapter"
+    cfg = json.load(open(os.path.join(out["directory"], "adapter_config.json")))
+    assert cfg["r"] == 2 and cfg["lora_alpha"] == 6 and cfg["peft_type"] == "LORA"
+    t = load_file(os.path.join(out["directory"], "adapter_model.safetensors"))
+    a = [v for k, v in t.items() if "lora_A" in k]
+    b = [v for k, v in t.items() if "lora_B" in k]
+    assert a and all(v.shape[0] == 2 for v in a) and all(v.shape[1] == 2 for v in b)
+    assert any(float(v.abs().max()) > 0 for v in b)
+    with pytest.raises(ValueError, match="exist"):
+        r.save_sampler_weights("small", "s1")
+    full = r.save_sampler_weights("default", "s2")
+    assert json.load(open(os.path.join(full["directory"], "adapter_config.json")))["r"] == 4
+    merged = r.save_sampler_weights("small", "s3", merged=True)
+    assert merged["kind"] == "full_weights" and merged["synced"]
+    from xorl_b200.parallel.state import reset_parallel_state
+    reset_parallel_state()
+
+
+def test_saves_are_refused_beyond_the_storage_limit(tmp_path):
+    from fastapi.testclient import TestClient
+    from xorl_b200.server.api_server import ServerState, create_app
+    from xorl_b200.server.backend import DummyBackend
+    out = tmp_path / "o"
+    os.makedirs(out / "sampler_weights" / "taken")
+    (out / "blob.bin").write_bytes(b"x" * 4096)
+    st = ServerState(DummyBackend(), str(out), storage_limit_bytes=1024)
+    with TestClient(create_app(st)) as c:
+        assert c.post("/api/v1/save_weights", json={"path": "a"}).status_code == 507
+        assert c.post("/api/v1/save_weights_for_sampler", json={"path": "b"}).status_code == 507
+        st.storage_limit_bytes = 0
+        assert c.post("/api/v1/save_weights_for_sampler", json={"path": "taken"}).status_code == 409
+        rid = c.post("/api/v1/save_weights_for_sampler", json={"path": "fresh"}).json()["request_id"]
+        assert _poll(c, rid)["type"] == "save_weights_for_sampler"
+
+
 def test_adapter_with_pending_gradients_is_not_dropped(tmp_path):
     """Without a spill directory an adapter that holds accumulated gradients is never the eviction
     victim; when every resident adapter holds some, creating another one raises."""

@@ -244,17 +244,39 @@ def lora_state_dict_peft(named_full_tensors: Dict[str, torch.Tensor]) -> Dict[st
     return out
 
 
-def save_lora_checkpoint(engine, out_dir: str, base_model_name: str = "") -> None:
-    """PEFT directory: ``adapter_model.safetensors`` + ``adapter_config.json``."""
+def slice_to_rank(name: str, t: torch.Tensor, rank: int) -> torch.Tensor:
+    """The first ``rank`` rank components of an adapter matrix in its in-memory layout (dense A [R, in],
+    B [out, R]; stacked experts A [E, in, R], B [E, R, out])."""
+    if name.endswith("_lora_A"):
+        return t[..., :rank]
+    if name.endswith("_lora_B"):
+        return t[:, :rank]
+    if ".lora_A." in name:
+        return t[:rank]
+    if ".lora_B." in name:
+        return t[:, :rank]
+    return t
+
+
+def save_lora_checkpoint(engine, out_dir: str, base_model_name: str = "", rank: Optional[int] = None,
+                         alpha: Optional[float] = None) -> None:
+    """PEFT directory: ``adapter_model.safetensors`` + ``adapter_config.json``.  ``rank`` / ``alpha``: the
+    active session's own (an adapter of lower rank than the storage is written at its rank: its remaining
+    components are zero)."""
     from safetensors.torch import save_file
     tensors = {n: t.detach().to(torch.bfloat16).cpu().contiguous()
                for n, t in engine.iter_full_tensors("master") if ".lora_" in n or "_lora_" in n}
     if engine.ps.rank != 0:
         return
+    cfg = dict(getattr(engine.model, "_xb_lora_config", {}))
+    if rank is not None and rank < cfg.get("r", rank):
+        tensors = {n: slice_to_rank(n, t, rank).contiguous() for n, t in tensors.items()}
+        cfg["r"] = int(rank)
+    if alpha is not None:
+        cfg["lora_alpha"] = alpha
     os.makedirs(out_dir, exist_ok=True)
     save_file(lora_state_dict_peft(tensors), os.path.join(out_dir, "adapter_model.safetensors"),
               metadata={"format": "pt"})
-    cfg = dict(getattr(engine.model, "_xb_lora_config", {}))
     cfg.update({"peft_type": "LORA", "task_type": "CAUSAL_LM", "base_model_name_or_path": base_model_name,
                 "bias": "none", "lora_dropout": 0.0, "inference_mode": True, "fan_in_fan_out": False})
     with open(os.path.join(out_dir, "adapter_config.json"), "w") as f:

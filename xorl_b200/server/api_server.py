@@ -37,9 +37,10 @@ class ServerState:
     def __init__(self, backend, output_dir: str = "outputs", dp_size: int = 1, packing_len: int = 4096,
                  packing: str = "sequential", future_ttl: float = 3600.0, session_timeout: float = 600.0,
                  api_keys: Optional[List[str]] = None, idle_sleep_seconds: float = 0.0,
-                 on_oversized: str = "error"):
+                 on_oversized: str = "error", storage_limit_bytes: int = 0):
         self.backend = backend
         self.output_dir = output_dir
+        self.storage_limit_bytes = int(storage_limit_bytes)      # 0 = no limit on what is kept under output_dir
         self.futures = FutureStore(future_ttl)
         self.endpoints = EndpointManager()
         self.orch = Orchestrator(backend, SeqIdAwareFIFOPolicy(),
@@ -83,6 +84,22 @@ class ServerState:
 
     def touch(self) -> None:
         self.last_activity = time.time()
+
+    def check_storage(self) -> None:
+        """507 before a save when the files under the output directory already exceed the limit
+        (src/xorl/server/api_server/weights.py:692-697)."""
+        if self.storage_limit_bytes <= 0 or not os.path.isdir(self.output_dir):
+            return
+        used = 0
+        for root, _dirs, files in os.walk(self.output_dir):
+            for f in files:
+                try:
+                    used += os.path.getsize(os.path.join(root, f))
+                except OSError:
+                    pass
+        if used >= self.storage_limit_bytes:
+            raise HTTPException(507, f"storage limit reached: {used} of {self.storage_limit_bytes} bytes used under "
+                                     f"the output directory; delete checkpoints first")
 
     # ---- sessions --------------------------------------------------------------------------
     def expire_sessions(self, now: Optional[float] = None) -> List[str]:
@@ -266,6 +283,7 @@ def create_app(state: ServerState) -> FastAPI:
     # ---- weights -----------------------------------------------------------------------------
     @app.post("/api/v1/save_weights", dependencies=dep)
     def save_weights(req: T.SaveWeightsRequest):
+        state.check_storage()
         return state.enqueue("save_weights", req.model_id, {"path": req.path}, req.seq_id,
                              lambda r: {"type": "save_weights", "path": r.get("path")})
 
@@ -276,10 +294,12 @@ def create_app(state: ServerState) -> FastAPI:
             validate_identifier(name, "sampler weights name")
         except ValueError as e:
             raise HTTPException(422, str(e)) from None
-        d = os.path.join(state.output_dir, "sampler_weights", name)
-        return state.enqueue("sync_inference_weights", req.model_id,
-                             {"backend": "file", "directory": d, "quantization": state.sync_quantization},
-                             req.seq_id, lambda r: {"type": "save_weights_for_sampler",
+        if os.path.exists(os.path.join(state.output_dir, "sampler_weights", name)):
+            raise HTTPException(409, f"sampler weights {name!r} exist already; use another name or delete them first")
+        state.check_storage()
+        return state.enqueue("save_sampler_weights", req.model_id,
+                             {"name": name, "quantization": state.sync_quantization},
+                             req.seq_id, lambda r: {"type": "save_weights_for_sampler", "kind": r.get("kind"),
                                                     "path": f"xorl://{req.model_id}/sampler_weights/{name}"})
 
     @app.post("/api/v1/load_weights", dependencies=dep)

@@ -27,6 +27,9 @@ class Backend:
     def sync_inference_weights(self, model_id, **kw) -> Dict[str, Any]:
         raise NotImplementedError
 
+    def save_sampler_weights(self, model_id, **kw) -> Dict[str, Any]:
+        raise NotImplementedError
+
     def abort_gradient_epoch(self, model_id, **kw) -> Dict[str, Any]:
         raise NotImplementedError
 
@@ -90,6 +93,10 @@ class DummyBackend(Backend):
         self._maybe_fail("sync_inference_weights")
         return {"synced": True, "bytes": 0}
 
+    def save_sampler_weights(self, model_id, **kw):
+        self._maybe_fail("save_sampler_weights")
+        return {"kind": "full_weights", "directory": kw.get("name")}
+
     def abort_gradient_epoch(self, model_id, **kw):
         self.calls.append("abort_gradient_epoch")
         return {"aborted": True}
@@ -118,6 +125,9 @@ class LocalBackend(Backend):
 
     def sync_inference_weights(self, model_id, **kw):
         return self.runner.sync_inference_weights(model_id, **kw)
+
+    def save_sampler_weights(self, model_id, **kw):
+        return self.runner.save_sampler_weights(model_id, **kw)
 
     def abort_gradient_epoch(self, model_id, **kw):
         return self.runner.abort_gradient_epoch(model_id)

@@ -23,7 +23,7 @@ from .runner import ModelRunner, RunnerDispatcher
 from .server_arguments import ServerArguments
 
 _OPS = ("forward_backward", "forward", "optim_step", "save_weights", "load_weights",
-        "sync_inference_weights", "abort_gradient_epoch", "sleep", "wake_up", "create_model", "unload_model")
+        "sync_inference_weights", "save_sampler_weights", "abort_gradient_epoch", "sleep", "wake_up", "create_model", "unload_model")
 
 
 class DispatchBackend(Backend):
@@ -59,6 +59,9 @@ class DispatchBackend(Backend):
 
     def sync_inference_weights(self, model_id, **kw):
         return self._call("sync_inference_weights", model_id, kw)
+
+    def save_sampler_weights(self, model_id, **kw):
+        return self._call("save_sampler_weights", model_id, kw)
 
     def abort_gradient_epoch(self, model_id, **kw):
         return self._call("abort_gradient_epoch", model_id, {})
@@ -222,7 +225,8 @@ def main(argv=None) -> None:
     state = ServerState(backend, sargs.output_dir, dp, sargs.sample_packing_sequence_len,
                         sargs.sample_packing_strategy or sargs.sample_packing_method, sargs.future_ttl_seconds,
                         sargs.session_timeout_seconds, sargs.api_keys, sargs.idle_sleep_seconds,
-                        on_oversized=sargs.sample_packing_on_oversized)
+                        on_oversized=sargs.sample_packing_on_oversized,
+                        storage_limit_bytes=int(sargs.storage_limit_gb * (1 << 30)))
     try:
         uvicorn.run(create_app(state), host=sargs.api_host, port=sargs.api_port, log_level="info")
     finally:

@@ -413,6 +413,27 @@ class ModelRunner:
         self.abort_gradient_epoch(model_id)
         return {"path": path}
 
+    def save_sampler_weights(self, model_id, name, quantization=None, merged: bool = False, **_):
+        """Weights an inference engine can load, under ``sampler_weights/{name}``: for a LoRA session its
+        adapter alone as a PEFT directory at the session's own rank (the base model is unchanged, engines
+        hot-load adapters), otherwise -- or with ``merged`` -- full Hugging Face weights (adapter folded
+        in) (src/xorl/server/api_server/weights.py:700-760)."""
+        from .security import validate_identifier
+        d = os.path.join(self.output_dir, "sampler_weights", validate_identifier(name, "sampler weights name"))
+        if os.path.exists(d):
+            raise ValueError(f"sampler weights {name!r} exist already; use another name or delete them first")
+        self._activate(model_id)
+        if self.trainer.args.lora.enable_lora and not merged:
+            from ..adapters.lora import save_lora_checkpoint
+            spec = self.adapters.session_spec(model_id) if self.adapters is not None else {}
+            save_lora_checkpoint(self.engine, d, self.trainer.args.model.model_path or "",
+                                 rank=spec.get("rank"), alpha=spec.get("alpha"))
+            if dist.is_initialized():
+                dist.barrier(group=self.host_group) if getattr(self, "host_group", None) is not None else dist.barrier()
+            return {"directory": d, "kind": "lora_adapter", "lora_path": d}
+        out = self.sync_inference_weights(model_id, backend="file", directory=d, quantization=quantization)
+        return {**out, "directory": d, "kind": "full_weights"}
+
     def sync_inference_weights(self, model_id, **kw):
         from .weight_sync import WeightSyncHandler
         handler = getattr(self, "_sync", None) or WeightSyncHandler(self)

@@ -67,6 +67,7 @@ class ServerArguments:
     api_keys: List[str] = field(default_factory=list)
     worker_bind_address: str = "tcp://127.0.0.1:5555"
     sync_bucket_size_mb: int = 1024
+    storage_limit_gb: float = 0.0                        # saves are refused (507) beyond this much under output_dir; 0 = no limit
     enable_moe_metrics: bool = True                      # moe_metrics.jsonl for MoE models
 
     def __post_init__(self) -> None:
