@@ -29,6 +29,19 @@ def test_preprocess_cli(tmp_path):
     from xorl_b200.data.datasets import prepare_datasets
     ds = prepare_datasets([{"path": os.path.join(out, "data.arrow"), "type": "tokenized"}])
     assert len(ds) == 5 and len(ds[3]["input_ids"]) == 100
+    # numbered shard files + a validation split; the directory itself is a dataset (json files beside the data
+    # are not rows), with the held-out rows under ``split: eval``
+    cfg["data"].update(num_dataset_shards_to_save=2, val_set_size=2, dataset_prepared_path=str(tmp_path / "prep2"))
+    (tmp_path / "c2.yaml").write_text(yaml.safe_dump(cfg))
+    out2 = main([str(tmp_path / "c2.yaml")])
+    assert sorted(f for f in os.listdir(out2) if f.endswith(".arrow")) == \
+        ["data-00000-of-00002.arrow", "data-00001-of-00002.arrow", "eval.arrow"]
+    meta2 = json.load(open(os.path.join(out2, "meta.json")))
+    assert meta2["num_samples"] == 3 and meta2["num_eval_samples"] == 2
+    tr = prepare_datasets([{"path": out2, "type": "tokenized"}])
+    ev = prepare_datasets([{"path": out2, "type": "tokenized", "split": "eval"}])
+    assert len(tr) == 3 and len(ev) == 2
+    assert sorted([len(tr[i]["input_ids"]) for i in range(3)] + [len(ev[i]["input_ids"]) for i in range(2)]) == [10, 30, 60, 90, 100]
 
 
 def test_export_quantized_roundtrip(tmp_path):

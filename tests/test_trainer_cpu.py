@@ -95,9 +95,9 @@ def test_prepared_dataset_cache_is_built_once_and_keyed_by_content(tmp_path):
     calls = {"n": 0}
     real = D._load_rows
 
-    def counting(path):
+    def counting(path, *a):
         calls["n"] += 1
-        return real(path)
+        return real(path, *a)
     D._load_rows = counting
     try:
         a = D.prepare_datasets(spec, cache_dir=cache)
@@ -121,3 +121,70 @@ def test_prepared_dataset_cache_is_built_once_and_keyed_by_content(tmp_path):
                 raise AssertionError("a missing file must raise")
     finally:
         D._load_rows = real
+
+
+def test_dataset_shards_and_validation_split():
+    import numpy as np
+    from xorl_b200.data import datasets as D
+    base = D.RandomTokenDataset(23, 8, 40, 1000, 1)
+    shards = [D.shard_dataset(base, 4, i) for i in range(4)]
+    assert [len(s) for s in shards] == [6, 6, 6, 5]
+    assert np.concatenate([s.indices for s in shards]).tolist() == list(range(23))
+    assert np.array_equal(shards[1][0]["input_ids"], base[6]["input_ids"]) and shards[3].lengths.tolist() == np.asarray(base.lengths)[18:].tolist()
+    with pytest.raises(ValueError):
+        D.shard_dataset(base, 4, 4)
+    tr, va = D.train_validation_split(base, 0.25, seed=3)
+    tr2, va2 = D.train_validation_split(base, 0.25, seed=3)
+    assert len(va) == 6 and len(tr) == 17 and va.indices.tolist() == va2.indices.tolist()
+    assert sorted(tr.indices.tolist() + va.indices.tolist()) == list(range(23))
+    assert len(D.train_validation_split(base, 5, seed=0)[1]) == 5
+    with pytest.raises(ValueError):
+        D.train_validation_split(base, 23)
+
+
+def test_validation_split_is_evaluated_at_saves_and_at_the_end(tmp_path):
+    """``data.val_set_size``: the held-out rows never train, their loss is measured at every checkpoint and
+    at the end, and it falls while the model learns the (shared) structure of the dummy data."""
+    from xorl_b200.cli.train import main
+    from xorl_b200.parallel.state import reset_parallel_state
+    reset_parallel_state()
+    cfg = yaml.safe_load(open(_cfg(tmp_path, "tiny-qwen3", save_steps=3, max_steps=6)))
+    cfg["data"]["val_set_size"] = 0.125
+    cfg["data"]["eval_sample_packing"] = False
+    p = tmp_path / "eval.yaml"
+    p.write_text(yaml.safe_dump(cfg))
+    r = main([str(p)])
+    ev = r["eval_history"]
+    assert [e["step"] for e in ev] == [3, 6] and ev[0]["eval_tokens"] == ev[1]["eval_tokens"] > 0
+    assert ev[1]["eval_loss"] < ev[0]["eval_loss"] and abs(ev[1]["eval_perplexity"] - 2.718281828 ** ev[1]["eval_loss"]) < 1e-3 * ev[1]["eval_perplexity"]
+    with open(tmp_path / "out" / "training_metrics.json") as f:
+        assert len(json.load(f)["eval_history"]) == 2
+    reset_parallel_state()
+
+
+@pytest.mark.distributed
+def test_test_datasets_are_evaluated_on_two_ranks(tmp_path):
+    """``data.test_datasets`` on two data-parallel ranks gives the loss a single process measures on the same
+    rows (the ragged tail aside: the row count here divides by the ranks)."""
+    from dist_utils import run_distributed
+    from xorl_b200.cli.train import main
+    from xorl_b200.parallel.state import reset_parallel_state
+    cfg = yaml.safe_load(open(_cfg(tmp_path, "tiny-qwen3", max_steps=1, lr=1e-10)))
+    cfg["data"]["test_datasets"] = [{"path": "random", "type": "tokenized", "max_seq_len": 200, "min_seq_len": 150,
+                                     "num_samples": 8}]
+    cfg["data"]["eval_sample_packing"] = False
+    evals = {}
+    for name, n in (("one", 1), ("two", 2)):
+        cfg["train"]["output_dir"] = str(tmp_path / name)
+        p = tmp_path / f"{name}.yaml"
+        p.write_text(yaml.safe_dump(cfg))
+        if n == 1:
+            reset_parallel_state()
+            main([str(p)])
+            reset_parallel_state()
+        else:
+            run_distributed("-m", 2, "xorl_b200.cli.train", str(p))
+        with open(tmp_path / name / "training_metrics.json") as f:
+            evals[name] = json.load(f)["eval_history"][-1]
+    assert evals["one"]["eval_tokens"] == evals["two"]["eval_tokens"]
+    assert abs(evals["one"]["eval_loss"] - evals["two"]["eval_loss"]) < 1e-4, evals

@@ -93,13 +93,7 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "sparse_mla_backend": (_is("auto"), "no selectable sparse-MLA backend"),
     },
     "data": {
-        "test_datasets": (_falsy, "evaluation datasets are not wired into the trainer"),
-        "val_set_size": (_falsy, "no validation split"),
-        "eval_sample_packing": (_falsy, "no evaluation loop"),
         "push_dataset_to_hub": (_falsy, "no network access"),
-        "num_dataset_shards_to_save": (_falsy, "prepared datasets are not re-sharded on disk"),
-        "dataset_shard_num": (_falsy, "dataset sharding across jobs is not built"),
-        "dataset_shard_idx": (_falsy, "dataset sharding across jobs is not built"),
     },
     "train": {
         "anyprecision_adamw_denominator_chunk_size": (_falsy, "the AnyPrecision update is not chunked"),

@@ -86,9 +86,16 @@ def _read_jsonl(path: str) -> List[Dict[str, Any]]:
     return rows
 
 
-def _load_rows(path: str) -> List[Dict[str, Any]]:
+def _load_rows(path: str, split: str = "train") -> List[Dict[str, Any]]:
     files: List[str] = []
-    if os.path.isdir(path):
+    if os.path.isdir(path) and os.path.exists(os.path.join(path, "meta.json")) and \
+            glob.glob(os.path.join(path, "data*.arrow")):
+        # a directory written by ``cli.preprocess``: ``data*.arrow`` (one file or numbered shards) holds the
+        # training rows, ``eval*.arrow`` the evaluation rows; the json files beside them are not data
+        files = sorted(glob.glob(os.path.join(path, ("eval" if split in ("eval", "test", "validation") else "data") + "*.arrow")))
+        if not files:
+            raise FileNotFoundError(f"{path} holds no {split} split")
+    elif os.path.isdir(path):
         for ext in ("*.jsonl", "*.json", "*.parquet", "*.arrow"):
             files += sorted(glob.glob(os.path.join(path, ext)))
     else:
@@ -201,7 +208,7 @@ def prepare_datasets(specs: Sequence[Dict[str, Any]], tokenizer=None, vocab_size
             continue
         built.append(_prepared_or_build(cache_dir, _spec_digest(spec, tokenizer, select_columns),
                                         lambda spec=spec, kind=kind, max_len=max_len, path=path:
-                                        _tokenise_rows(_load_rows(path), spec, kind, max_len, tokenizer)))
+                                        _tokenise_rows(_load_rows(path, spec.get("split", "train")), spec, kind, max_len, tokenizer)))
     if not built:
         raise ValueError("data.datasets is empty")
     if len(built) == 1:
@@ -244,3 +251,60 @@ class ConcatTokenDataset(Dataset):
     @property
     def lengths(self):
         return np.concatenate([p.lengths for p in self.parts])
+
+
+class SubsetDataset(Dataset):
+    """Rows ``indices`` of another dataset (validation splits, job shards)."""
+
+    def __init__(self, base, indices: Sequence[int]):
+        self.base = base
+        self.indices = np.asarray(indices, dtype=np.int64)
+        self.lengths = np.asarray(base.lengths)[self.indices]
+
+    def __len__(self) -> int:
+        return len(self.indices)
+
+    def __getitem__(self, i: int):
+        return self.base[int(self.indices[i])]
+
+
+def shard_dataset(ds, num_shards: int, index: int) -> "SubsetDataset":
+    """Contiguous shard ``index`` of ``num_shards`` (sizes differ by at most one row, the first
+    ``len % num_shards`` shards are the longer ones), for jobs that each train on a part of the data
+    (``data.dataset_shard_num`` / ``dataset_shard_idx``; src/xorl/data/prepare/prepare_datasets.py:374-390)."""
+    if not 0 <= index < num_shards:
+        raise ValueError(f"dataset_shard_idx {index} outside 0..{num_shards - 1}")
+    n = len(ds)
+    base, extra = divmod(n, num_shards)
+    start = index * base + min(index, extra)
+    return SubsetDataset(ds, np.arange(start, start + base + (1 if index < extra else 0)))
+
+
+def train_validation_split(ds, val_set_size: float, seed: int = 42):
+    """(train, validation): ``val_set_size`` > 1 is a number of rows, otherwise a fraction; the rows are
+    drawn with a generator seeded by ``seed`` so every rank and every run makes the same split
+    (src/xorl/data/prepare/shared.py:391-415)."""
+    n = len(ds)
+    k = int(val_set_size) if val_set_size > 1 else int(round(n * float(val_set_size)))
+    if not 0 < k < n:
+        raise ValueError(f"val_set_size {val_set_size} leaves no rows for training or for validation ({n} rows)")
+    perm = np.random.default_rng(seed).permutation(n)
+    return SubsetDataset(ds, np.sort(perm[k:])), SubsetDataset(ds, np.sort(perm[:k]))
+
+
+def prepare_train_eval(data_args, tokenizer=None, vocab_size: int = 151936, seed: int = 42):
+    """(train dataset, evaluation dataset or None) as ``data`` configures them: ``datasets`` cut to this
+    job's shard, then either ``test_datasets`` or a ``val_set_size`` split of the training data."""
+    kw = dict(tokenizer=tokenizer, vocab_size=vocab_size, select_columns=data_args.select_columns, seed=seed,
+              cache_dir=data_args.dataset_prepared_path)
+    train = prepare_datasets(data_args.datasets, **kw)
+    if data_args.dataset_shard_num:
+        if data_args.dataset_shard_idx is None:
+            raise ValueError("dataset_shard_num needs dataset_shard_idx")
+        train = shard_dataset(train, int(data_args.dataset_shard_num), int(data_args.dataset_shard_idx))
+    evald = None
+    if data_args.test_datasets:
+        evald = prepare_datasets(data_args.test_datasets, **kw)
+    elif data_args.val_set_size:
+        train, evald = train_validation_split(train, float(data_args.val_set_size), seed)
+    return train, evald

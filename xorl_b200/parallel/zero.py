@@ -880,6 +880,25 @@ class Zero3Engine:
         return loss_value
 
     @torch.no_grad()
+    @torch.no_grad()
+    def eval_loss(self, input_ids, labels, *, position_ids=None, cu_seqlens=None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(sum of the next-token negative log-likelihoods over supervised labels, their count) of this
+        rank's batch, without gradients.  Built for data-parallel layouts (every rank holds whole
+        sequences and the whole vocabulary)."""
+        if self.ps.tp_size > 1 or self.ps.pp_size > 1 or self.ps.ulysses_size * self.ps.ringattn_size > 1 \
+                or getattr(self.ps, "lm_head_tp_size", 1) > 1:
+            raise NotImplementedError("evaluation runs on data-parallel layouts (no tensor, pipeline, context or "
+                                      "lm-head parallelism)")
+        from ..ops.loss import fused_linear_token_loss
+        hidden = self.forward_only(input_ids, position_ids=position_ids, cu_seqlens=cu_seqlens)
+        root, _ = self._units_by_role()
+        self.gather(root)
+        self.wait_gather(root)
+        head = self.model.lm_head.weight if hasattr(self.model, "lm_head") else self.model.embed_tokens.weight
+        _, lp, _ = fused_linear_token_loss(hidden, head, labels, lambda lp, mask: (lp.sum() * 0, {}), 1.0)
+        valid = labels.reshape(-1) != -100
+        return -(lp.float().reshape(-1) * valid).sum(), valid.sum()
+
     def forward_only(self, input_ids, *, position_ids=None, cu_seqlens=None) -> torch.Tensor:
         """Final normalised hidden states (no gradients, parameters gathered unit by unit)."""
         model = self.model

@@ -235,10 +235,13 @@ class Trainer:
 
     def _build_data(self, dataset=None) -> None:
         a = self.args
+        self.eval_dataloader, self.eval_history = None, []
         if dataset is None:
-            dataset = prepare_datasets(a.data.datasets, vocab_size=self.model_config.vocab_size,
-                                       select_columns=a.data.select_columns, seed=a.train.seed,
-                                       tokenizer=self._tokenizer(), cache_dir=a.data.dataset_prepared_path)
+            from ..data.datasets import prepare_train_eval
+            dataset, eval_dataset = prepare_train_eval(a.data, tokenizer=self._tokenizer(),
+                                                       vocab_size=self.model_config.vocab_size, seed=a.train.seed)
+            if eval_dataset is not None:
+                self.eval_dataloader = self._build_eval_dataloader(eval_dataset)
         shard = None
         if self.ps.sp_size > 1:
             from ..data import SequenceShardCollator
@@ -248,6 +251,53 @@ class Trainer:
         spe = max(1, len(self.dataloader))
         self.train_steps = a.train.max_steps or spe * a.train.num_train_epochs
         self.steps_per_epoch = spe
+
+    def _build_eval_dataloader(self, eval_dataset):
+        """Evaluation rows in a fixed order, one micro-batch per step and rank.  ``data.eval_sample_packing:
+        false`` gives every sample a row of its own; over several ranks the ragged tail (fewer rows than
+        ranks) is dropped so that every rank runs the same number of forward passes."""
+        from ..data.data_loader import PackedDataLoader
+        d, t = self.args.data, self.args.train
+        loader = PackedDataLoader(
+            eval_dataset, packing_len=int(d.sample_packing_sequence_len or 4096), micro_batch_size=t.micro_batch_size,
+            grad_accum=1, dp_rank=self.ps.dp_rank, dp_size=self.ps.dp_size,
+            packing_method=d.sample_packing_method or "sequential", group_size=int(d.sample_packing_group_size or 100000),
+            pad_to_multiple_of=int(d.pad_to_multiple_of or 1), shuffle=False, seed=t.seed,
+            drop_last=self.ps.dp_size > 1, pin_memory=bool(d.dataloader_pin_memory))
+        if d.eval_sample_packing is False:
+            loader.bins = [[i] for i in range(len(eval_dataset))]
+            per_step = loader.mbs * loader.dp_size
+            loader.steps_per_epoch = len(loader.bins) // per_step if loader.drop_last else -(-len(loader.bins) // per_step)
+        return loader
+
+    def evaluate(self) -> Optional[Dict[str, float]]:
+        """Mean next-token loss over the evaluation set (``data.test_datasets``, or the ``data.val_set_size``
+        split of the training data), summed over ranks by token."""
+        if self.eval_dataloader is None:
+            return None
+        import math
+        nll = torch.zeros((), device=self.device, dtype=torch.float64)
+        count = torch.zeros((), device=self.device, dtype=torch.float64)
+        self.eval_dataloader.epoch, self.eval_dataloader.cursor = 0, 0
+        for rows in self.eval_dataloader:
+            for mb in rows:
+                d = self._to_device(mb)
+                s, n = self.engine.eval_loss(d["input_ids"], d["labels"], position_ids=d.get("position_ids"),
+                                             cu_seqlens=d.get("cu_seqlens"))
+                nll += s.double()
+                count += n.double()
+        if self.ps.world_size > 1 and dist.is_initialized():
+            both = torch.stack([nll, count])
+            dist.all_reduce(both, group=self.ps.group("dp"))
+            nll, count = both[0], both[1]
+        loss = float(nll / count.clamp_min(1))
+        out = {"step": self.global_step, "eval_loss": loss, "eval_tokens": float(count),
+               "eval_perplexity": math.exp(min(loss, 50.0))}
+        self.eval_history.append(out)
+        logger.info("step %d: eval loss %.4f over %d tokens", self.global_step, loss, int(count))
+        if getattr(self, "sink", None) is not None and hasattr(self.sink, "log"):
+            self.sink.log({"eval/loss": loss, "eval/tokens": float(count)}, self.global_step)
+        return out
 
     def _build_optimizer(self) -> None:
         t = self.args.train
@@ -568,6 +618,8 @@ class Trainer:
                  "train_dataloader": self.dataloader.state_dict(),
                  "environ_meter": self.meter.state_dict(), "torch_rng_state": torch.get_rng_state()}
         self.checkpointer.save(self.global_step, extra)
+        if due:
+            self.evaluate()
 
     def _finalize(self) -> Dict[str, Any]:
         t = self.args.train
@@ -575,10 +627,14 @@ class Trainer:
             self.profiler.stop()
         if self.watchdog is not None:
             self.watchdog.stop()
+        if self.eval_dataloader is not None and not (self.eval_history and self.eval_history[-1]["step"] == self.global_step):
+            self.evaluate()
         self.sink.close()
         self.memhist.close()
         result = {"loss_history": self.loss_history, "global_step": self.global_step,
                   "metrics": self.metrics_history[-1] if self.metrics_history else {}}
+        if self.eval_history:
+            result["eval_history"] = self.eval_history
         if self.pp_runner is not None and self.pp_runner.bubble_stats:
             result["pp_bubble"] = dict(self.pp_runner.bubble_stats, pp_rank=self.ps.pp_rank)
         if self.ps.sp_size > 1:
