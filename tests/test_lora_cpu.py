@@ -324,3 +324,91 @@ def test_qarl_trains_dense_fp8_and_moe_nvfp4(tmp_path):
         qarl.inject_fake_quant(DecoderLM(preset("tiny-qwen3-moe"), device="meta"),
                                TrainingArguments(output_dir=str(tmp_path / "x"), enable_qarl=True, device="cpu"))
     reset_parallel_state()
+
+
+def test_lora_target_manifest_pins_the_adapter_coverage(tmp_path):
+    import json
+    import pytest
+    from xorl_b200.adapters import target_manifest as tm
+    from xorl_b200.adapters.lora import inject_lora
+    cfg = preset("tiny-qwen3", tie_word_embeddings=False)
+    L = cfg.num_hidden_layers
+    good = {"schema_version": 1, "target_modules": ["q_proj", "v_proj", "down_proj"],
+            "expected_modules": [{"pattern": "model.layers.*.self_attn.q_proj", "count": L, "rank": 4},
+                                 {"pattern": "model.layers.*.self_attn.v_proj", "count": L},
+                                 {"pattern": "model.layers.*.mlp.down_proj", "count": L, "rank": 4}]}
+    path = tmp_path / "manifest.json"
+    path.write_text(json.dumps(good))
+    la = LoRAArguments(enable_lora=True, lora_rank=4, lora_target_manifest=str(path))
+    model = DecoderLM(cfg, device="meta")
+    inject_lora(model, la)                                     # targets come from the manifest; coverage matches
+    units = tm.adapter_units(model)
+    assert len(units) == 3 * L and units["model.layers.0.self_attn.q_proj"] == 4
+    assert not any("k_proj" in u for u in units)               # the fused qkv projection adapts two of its three slices
+    # every kind of mismatch is reported
+    bad = json.loads(json.dumps(good))
+    bad["expected_modules"][0]["count"] = L + 1
+    bad["expected_modules"][1]["rank"] = 8
+    bad["expected_modules"].pop(2)
+    with pytest.raises(ValueError) as e:
+        tm.validate(model, bad)
+    msg = str(e.value)
+    assert "expects %d" % (L + 1) in msg and "rank 8 expected" in msg and "no pattern lists" in msg
+    bad["allow_unlisted"] = True
+    bad["expected_modules"] = [{"pattern": "model.layers.*", "count": 3 * L}, {"pattern": "*.q_proj", "count": L}]
+    with pytest.raises(ValueError, match="earlier pattern"):
+        tm.validate(model, bad)
+    # configured leaves that disagree with the manifest, and malformed manifests
+    with pytest.raises(ValueError, match="differ"):
+        inject_lora(DecoderLM(cfg, device="meta"), LoRAArguments(enable_lora=True, lora_rank=4, lora_target_modules=["q_proj"],
+                                                                 lora_target_manifest=good))
+    for broken in ({**good, "schema_version": 2}, {**good, "target_modules": []}, {**good, "allow_unlisted": "no"},
+                   {**good, "expected_modules": [{"pattern": "x", "count": -1}]}):
+        with pytest.raises(ValueError):
+            tm.load_manifest(broken)
+    # a MoE model: the stacked experts are one unit per layer
+    moe = DecoderLM(preset("tiny-qwen3-moe"), device="meta")
+    inject_lora(moe, LoRAArguments(enable_lora=True, lora_rank=4, lora_target_modules=["gate_proj", "up_proj", "down_proj"]))
+    assert sum(u.endswith(".mlp.experts") for u in tm.adapter_units(moe)) > 0
+
+
+def test_adaptive_quantisation_noise_has_the_size_of_the_grid_and_is_off_outside_training():
+    """``lora.enable_aqn``: training forwards see base weights jittered by ``aqn_alpha * N(0, 1) * step`` with the
+    step taken from the stored scales; evaluation and no-grad passes see the plain dequantised weights."""
+    from xorl_b200.adapters.qlora import QLoRALinear
+    from xorl_b200.models.layers import Linear
+    from xorl_b200.ops import quantize as Q
+    torch.manual_seed(0)
+    for fmt, group in (("nf4", 64), ("nvfp4", 16), ("block_fp8", 128), ("int4", 128), ("mxfp4", 32)):
+        base = Linear(256, 128, dtype=torch.float32)
+        q = QLoRALinear(base, 4, 8, [("x_proj", 0, 128)], fmt, group)
+        w = torch.randn(128, 256) * 0.05
+        for p in q.parameters():
+            if p.is_meta or p.numel() == 0:
+                continue
+        torch.nn.init.zeros_(q.lora_B["x_proj"])
+        torch.nn.init.normal_(q.lora_A["x_proj"], 0, 0.02)
+        q.load_base_weight(w)
+        step = q.quantisation_step()
+        deq = q.dequantized_weight().float()
+        assert step.shape == (128, 256) and float(step.min()) >= 0
+        err = (deq - w).abs()
+        if fmt == "block_fp8":
+            # the spacing of e4m3 around one, in the block's scale: a floor (larger codes are spaced wider)
+            assert abs(float(step.max()) - 0.125 * float(w.abs().max()) / 448.0) < 1e-9
+            assert float(err.mean()) > float(step.mean())
+        else:
+            # 4-bit grids: the step is of the order of the rounding error the format makes
+            assert float(err.mean()) < 2.5 * float(step.mean()) and float(step.mean()) < 40 * float(err.mean()), \
+                (fmt, float(err.mean()), float(step.mean()))
+        x = torch.eye(256)
+        q.enable_aqn, q.aqn_alpha = True, 0.5
+        q.train()
+        noisy = q(x).t()                                        # = jittered weight (B = 0)
+        ratio = ((noisy.detach() - deq) / step.clamp_min(1e-12))[step > 0]
+        assert abs(float(ratio.std()) - 0.5) < 0.03 and abs(float(ratio.mean())) < 0.02, (fmt, float(ratio.std()))
+        assert not torch.equal(q(x), q(x))                      # fresh noise every forward
+        with torch.no_grad():
+            assert torch.equal(q(x).t(), deq)
+        q.eval()
+        assert torch.equal(q(x).t(), deq)

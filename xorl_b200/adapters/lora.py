@@ -163,7 +163,9 @@ def _fused_slices(module_name: str, linear: Linear, parent, targets: Iterable[st
 def inject_lora(model: nn.Module, lora_args) -> List[str]:
     """Replaces targeted linears by ``LoraLinear`` and freezes everything else.  Returns the names
     of the wrapped modules."""
-    targets = tuple(lora_args.lora_target_modules or DEFAULT_TARGETS)
+    from .target_manifest import resolve_targets, validate
+    listed, manifest = resolve_targets(lora_args.lora_target_modules, getattr(lora_args, "lora_target_manifest", None))
+    targets = tuple(listed or DEFAULT_TARGETS)
     if "all-linear" in targets:
         targets = DEFAULT_TARGETS
     exclude = tuple(lora_args.exclude_modules or ())
@@ -190,6 +192,8 @@ def inject_lora(model: nn.Module, lora_args) -> List[str]:
         p.requires_grad_(("lora_A" in n) or ("lora_B" in n))
     model._xb_lora_config = {"r": lora_args.lora_rank, "lora_alpha": lora_args.lora_alpha,
                              "target_modules": list(targets)}
+    if manifest is not None:
+        validate(model, manifest)                   # exact adapter coverage, before any sharding or step
     return wrapped
 
 

@@ -73,8 +73,47 @@ class QLoRALinear(LoraLinear):
         dt = torch.bfloat16 if self.qparts["packed"].is_cuda else torch.float32
         return Q.dequantize_weight(parts, self.fmt, self.group, self.w_shape, dt)
 
+    def _parts(self) -> Dict[str, torch.Tensor]:
+        parts = {}
+        for key, (pdt, pshape) in self.part_meta.items():
+            raw = self.qparts[key].view(torch.uint8)
+            n = math.prod(pshape) * torch.empty(0, dtype=pdt).element_size()
+            parts[key] = raw[:n].view(pdt).reshape(pshape)
+        return parts
+
+    def quantisation_step(self) -> torch.Tensor:
+        """Smallest spacing of the grid around each weight, ``[out, in]`` fp32: half the smallest code
+        spacing times the element's scale (nf4: 0.5 * min code gap * absmax of its group; nvfp4 / mxfp4:
+        0.5 * block scale (* tensor scale); int4: 0.5 * group scale; block fp8: the e4m3 unit spacing
+        0.125 * block scale) (src/xorl/qlora/modules/{nf4,nvfp4,block_fp8}_linear.py ``_compute_aqn_step``)."""
+        N, K = self.w_shape
+        p = self._parts()
+        if self.fmt == "block_fp8":
+            s = p["scale"].float().reshape(-(-N // 128), -(-K // 128))
+            return 0.125 * s.repeat_interleave(128, 0).repeat_interleave(128, 1)[:N, :K]
+        if self.fmt == "nvfp4":
+            s = p["scale"].view(torch.float8_e4m3fn).float().reshape(N, K // self.group) * p["global_scale"].float().reshape(())
+            return 0.5 * s.repeat_interleave(self.group, 1)
+        if self.fmt == "mxfp4":                                    # scales are stored as biased power-of-two exponents
+            s = torch.exp2(p["scale"].float().reshape(N, K // self.group) - 127.0)
+            return 0.5 * s.repeat_interleave(self.group, 1)
+        s = p["scale"].float().reshape(N, K // self.group)
+        if self.fmt == "nf4":
+            gaps = (Q.NF4_VALUES[1:] - Q.NF4_VALUES[:-1]).min().item()
+            return (0.5 * gaps) * s.repeat_interleave(self.group, 1)
+        return 0.5 * s.repeat_interleave(self.group, 1)            # int4: unit code spacing
+
     def forward(self, x):
         w = self.dequantized_weight().to(x.dtype)
+        if getattr(self, "enable_aqn", False) and self.training and torch.is_grad_enabled():
+            # adaptive quantisation noise: Gaussian noise of the size of the grid spacing around each frozen
+            # weight, fresh on every training forward (not in evaluation / reference passes), so the adapters
+            # do not fit the rounding pattern of the base weights.  The step depends only on the stored
+            # scales and is kept until the base weight is re-quantised.
+            step = getattr(self, "_aqn_step", None)
+            if step is None or step.device != w.device:
+                step = self._aqn_step = self.quantisation_step().to(w.device, w.dtype)
+            w = torch.addcmul(w, torch.randn_like(w), step, value=float(self.aqn_alpha))
         y = gemm_ops.linear(x, w, self.bias)
         pieces, cur = [], 0
         for name, s, e in sorted(self.slices, key=lambda t: t[1]):
@@ -98,6 +137,7 @@ class QLoRALinear(LoraLinear):
         """Quantise a full-precision weight into this module's packed storage."""
         for key, t in self.quantize_parts(w.cpu()).items():
             self.qparts[key].copy_(t.to(self.qparts[key].device))
+        self._aqn_step = None
 
 
 class PackedWeight(nn.Module):
@@ -180,7 +220,9 @@ def quantize_experts_(experts: nn.Module, fmt: str, group: int) -> None:
 
 
 def inject_qlora(model: nn.Module, lora_args) -> List[str]:
-    targets = tuple(lora_args.lora_target_modules or DEFAULT_TARGETS)
+    from .target_manifest import resolve_targets, validate
+    listed, manifest = resolve_targets(lora_args.lora_target_modules, getattr(lora_args, "lora_target_manifest", None))
+    targets = tuple(listed or DEFAULT_TARGETS)
     exclude = tuple(lora_args.exclude_modules or ())
     wrapped = []
     for pname, parent in list(model.named_modules()):
@@ -191,9 +233,11 @@ def inject_qlora(model: nn.Module, lora_args) -> List[str]:
             slices = _fused_slices(full, child, parent, targets)
             if not slices:
                 continue
-            setattr(parent, cname, QLoRALinear(child, lora_args.lora_rank, lora_args.lora_alpha, slices,
-                                               lora_args.quant_format, lora_args.quant_group_size,
-                                               lora_args.lora_b_init_std, lora_args.lora_b_init_seed))
+            q = QLoRALinear(child, lora_args.lora_rank, lora_args.lora_alpha, slices,
+                            lora_args.quant_format, lora_args.quant_group_size,
+                            lora_args.lora_b_init_std, lora_args.lora_b_init_seed)
+            q.enable_aqn, q.aqn_alpha = bool(getattr(lora_args, "enable_aqn", False)), float(getattr(lora_args, "aqn_alpha", 1.0))
+            setattr(parent, cname, q)
             wrapped.append(full)
     if True:
         # MoE experts: per-expert adapters (when the expert projections are targeted) over a packed base
@@ -210,4 +254,6 @@ def inject_qlora(model: nn.Module, lora_args) -> List[str]:
         p.requires_grad_(("lora_A" in n) or ("lora_B" in n))
     model._xb_lora_config = {"r": lora_args.lora_rank, "lora_alpha": lora_args.lora_alpha,
                              "target_modules": list(targets), "quant_format": lora_args.quant_format}
+    if manifest is not None:
+        validate(model, manifest)
     return wrapped

@@ -69,7 +69,6 @@ SATISFIED_BY_DESIGN: Dict[str, Dict[str, str]] = {
         "ce_mode": "one fused lm-head + cross-entropy kernel path",
     },
     "lora": {
-        "aqn_alpha": "only meaningful with enable_aqn",
     },
     "distill": {
         "stream_num_workers": "teacher scores are produced in-process, one forward pass per micro-batch",
@@ -115,10 +114,8 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "enable_compile": (_falsy, "there is no tracing compiler on any path"),
     },
     "lora": {
-        "lora_target_manifest": (_falsy, "target manifests are not built (use lora_target_modules)"),
         "unfuse_for_lora": (_falsy, "adapters on fused projections are slice-exact; projections are not unfused"),
         "block_fp8_qlora_training": (_falsy, "fp8 training of QLoRA bases is not built"),
-        "enable_aqn": (_falsy, "adaptive quantisation noise is not built"),
         "moe_hybrid_shared_lora": (_falsy, "hybrid-shared expert LoRA is not built"),
     },
 }
