@@ -195,6 +195,47 @@ def test_moe_expert_lora_trains_adapters_and_merges(tmp_path):
     assert abs(before - after) < 1e-4 and float(ex.lora.gate_proj_lora_B.abs().max()) == 0.0
 
 
+def test_hybrid_shared_expert_lora(tmp_path):
+    """``moe_hybrid_shared_lora``: gate / up share one A over the experts, down shares one B; the shared factors
+    are dense parameters, the model learns, the adapter path equals the merged weights and the PEFT export
+    writes the shared factor under every expert."""
+    from xorl_b200.adapters.lora import merge_lora, save_lora_checkpoint
+    from xorl_b200.optim import build_optimizer
+    la = LoRAArguments(enable_lora=True, lora_rank=8, lora_alpha=16, moe_hybrid_shared_lora=True, lora_b_init_std=0.01,
+                       lora_target_modules=["gate_proj", "up_proj", "down_proj"])
+    model, eng, wrapped = _moe_engine(la)
+    ex = model.layers["0"].mlp.experts
+    assert ex.lora.gate_proj_lora_A.shape == (1, 128, 8) and ex.lora.gate_proj_lora_B.shape[0] == 8
+    assert ex.lora.down_proj_lora_A.shape[0] == 8 and ex.lora.down_proj_lora_B.shape == (1, 8, 128)
+    kinds = {n: g.name.rsplit(".", 1)[-1] for g in eng.all_groups() for n, _ in g.named_params if "lora" in n}
+    assert kinds["layers.0.mlp.experts.lora.gate_proj_lora_A"] == "dense"
+    assert kinds["layers.0.mlp.experts.lora.gate_proj_lora_B"] == "expert"
+    assert kinds["layers.0.mlp.experts.lora.down_proj_lora_B"] == "dense"
+    opt = build_optimizer(eng, lr=1e-2, weight_decay=0.0)
+    ids = torch.randint(0, 1024, (2, 65))
+    losses = []
+    for _ in range(6):
+        opt.zero_grad()
+        losses.append(float(eng.forward_backward(ids[:, :-1], ids[:, 1:], grad_scale=1.0 / 128)))
+        eng.finish_grad_sync()
+        opt.step()
+    assert losses[-1] < losses[0] - 0.02, losses
+    save_lora_checkpoint(eng, str(tmp_path / "peft"), "tiny-moe")
+    from safetensors.torch import load_file
+    sd = load_file(str(tmp_path / "peft" / "adapter_model.safetensors"))
+    a0 = sd["base_model.model.model.layers.0.mlp.experts.0.gate_proj.lora_A.weight"]
+    a5 = sd["base_model.model.model.layers.0.mlp.experts.5.gate_proj.lora_A.weight"]
+    b0 = sd["base_model.model.model.layers.0.mlp.experts.0.gate_proj.lora_B.weight"]
+    b5 = sd["base_model.model.model.layers.0.mlp.experts.5.gate_proj.lora_B.weight"]
+    assert torch.equal(a0, a5) and not torch.equal(b0, b5) and tuple(a0.shape) == (8, 128)
+    x, y = ids[:, :-1], ids[:, 1:]
+    with torch.no_grad():
+        before = float(model(x, labels=y, grad_scale=1.0 / 128)["loss"])
+        merge_lora(model)
+        after = float(model(x, labels=y, grad_scale=1.0 / 128)["loss"])
+    assert abs(before - after) < 1e-4
+
+
 def test_qlora_on_moe_experts_trains_and_loads_a_full_precision_checkpoint(tmp_path):
     """QLoRA over a MoE model: expert stacks are stored packed (4-bit) with per-expert adapters on top and
     the loss falls; a Hugging Face checkpoint of the full-precision model loads into the packed storage

@@ -188,3 +188,25 @@ def test_test_datasets_are_evaluated_on_two_ranks(tmp_path):
             evals[name] = json.load(f)["eval_history"][-1]
     assert evals["one"]["eval_tokens"] == evals["two"]["eval_tokens"]
     assert abs(evals["one"]["eval_loss"] - evals["two"]["eval_loss"]) < 1e-4, evals
+
+
+@pytest.mark.distributed
+def test_hybrid_shared_expert_lora_under_expert_parallelism(tmp_path):
+    """Two ranks with the experts split over them against the same two ranks with all experts everywhere: the
+    factors shared by all experts are reduced over both ranks, the per-expert ones over their owners, and
+    the loss curves agree."""
+    from dist_utils import run_distributed
+    curves = {}
+    for name, ep in (("ep1", 1), ("ep2", 2)):
+        cfg = yaml.safe_load(open(_cfg(tmp_path, "tiny-qwen3-moe", expert_parallel_size=ep, max_steps=4, lr=5e-3)))
+        cfg["train"]["output_dir"] = str(tmp_path / name)
+        cfg["lora"] = {"enable_lora": True, "lora_rank": 4, "lora_alpha": 8, "moe_hybrid_shared_lora": True,
+                       "lora_b_init_std": 0.02, "lora_target_modules": ["q_proj", "gate_proj", "up_proj", "down_proj"]}
+        p = tmp_path / f"{name}.yaml"
+        p.write_text(yaml.safe_dump(cfg))
+        run_distributed("-m", 2, "xorl_b200.cli.train", str(p))
+        with open(tmp_path / name / "training_metrics.json") as f:
+            curves[name] = json.load(f)["loss_history"]
+    assert curves["ep1"][-1] < curves["ep1"][0]
+    for a, b in zip(curves["ep1"], curves["ep2"]):
+        assert abs(a - b) < 3e-4, curves

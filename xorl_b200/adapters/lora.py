@@ -87,10 +87,17 @@ class ExpertsLoRA(nn.Module):
     and ``p_lora_B [E, r, out]`` (names and shapes of src/xorl/models/layers/moe/lora.py:13-15), the
     base expert weights frozen.  Lives as ``experts.lora``; the expert MLP adds
     ``(alpha / r) (x A_e) B_e`` with two extra grouped GEMMs per projection.  Under expert
-    parallelism the adapter tensors hold the local experts and are sharded like the expert weights."""
+    parallelism the adapter tensors hold the local experts and are sharded like the expert weights.
+
+    ``hybrid_shared`` (``lora.moe_hybrid_shared_lora``): the factor on the hidden-size side is one matrix for
+    all experts -- gate / up ``A [1, H, r]`` with per-expert ``B``, down ``B [1, r, H]`` with per-expert
+    ``A`` (src/xorl/models/layers/moe/lora.py:206-236).  A shared factor is an ordinary replicated
+    parameter (sharded and reduced with the dense ones, also across expert-parallel ranks) and its product
+    is one dense GEMM over all rows instead of a grouped one."""
     PROJ = ("gate_proj", "up_proj", "down_proj")
 
-    def __init__(self, experts, rank: int, alpha: float, targets: Iterable[str], b_init_std: float = 0.0):
+    def __init__(self, experts, rank: int, alpha: float, targets: Iterable[str], b_init_std: float = 0.0,
+                 hybrid_shared: bool = False):
         super().__init__()
         E, H, I2 = experts.gate_up_proj.shape
         I = experts.down_proj.shape[1]
@@ -101,12 +108,17 @@ class ExpertsLoRA(nn.Module):
         self.targets = tuple(p for p in self.PROJ if p in targets)
         dt, dev = experts.gate_up_proj.dtype, experts.gate_up_proj.device
         ep = getattr(experts.gate_up_proj, "_xb_ep", None)
+        self.hybrid_shared = bool(hybrid_shared)
         for p in self.targets:
             fin, fout = dims[p]
-            A = nn.Parameter(torch.empty(E, fin, rank, dtype=dt, device=dev))
-            B = nn.Parameter(torch.empty(E, rank, fout, dtype=dt, device=dev))
+            ea = 1 if hybrid_shared and p != "down_proj" else E
+            eb = 1 if hybrid_shared and p == "down_proj" else E
+            A = nn.Parameter(torch.empty(ea, fin, rank, dtype=dt, device=dev))
+            B = nn.Parameter(torch.empty(eb, rank, fout, dtype=dt, device=dev))
             A._xb_lora, B._xb_lora = "A", ("B" if b_init_std == 0.0 else "B_random")
-            for t in (A, B):
+            for t, n in ((A, ea), (B, eb)):
+                if n == 1 and hybrid_shared:
+                    continue                                   # shared over the experts: a replicated dense parameter
                 t._xb_expert = True
                 if ep is not None:
                     from ..parallel.ep import mark_ep
@@ -131,7 +143,8 @@ class ExpertsLoRA(nn.Module):
         I = experts.down_proj.shape[1]
         for p in self.targets:
             A, B = getattr(self, f"{p}_lora_A"), getattr(self, f"{p}_lora_B")
-            delta = torch.bmm(A.float(), B.float()) * self.scaling
+            E = max(A.shape[0], B.shape[0])
+            delta = torch.bmm(A.float().expand(E, -1, -1), B.float().expand(E, -1, -1)) * self.scaling
             if p == "gate_proj":
                 experts.gate_up_proj[:, :, :I] += delta.to(experts.gate_up_proj.dtype)
             elif p == "up_proj":
@@ -186,12 +199,17 @@ def inject_lora(model: nn.Module, lora_args) -> List[str]:
     for name, mod in list(model.named_modules()):
         if isinstance(mod, Experts) and not any(x in name for x in exclude) \
                 and any(p in targets for p in ExpertsLoRA.PROJ) and getattr(mod, "activation", None) is None:
-            mod.lora = ExpertsLoRA(mod, lora_args.lora_rank, lora_args.lora_alpha, targets, lora_args.lora_b_init_std)
+            mod.lora = ExpertsLoRA(mod, lora_args.lora_rank, lora_args.lora_alpha, targets, lora_args.lora_b_init_std,
+                                   hybrid_shared=bool(getattr(lora_args, "moe_hybrid_shared_lora", False)))
             wrapped.append(name)
     for n, p in model.named_parameters():
         p.requires_grad_(("lora_A" in n) or ("lora_B" in n))
     model._xb_lora_config = {"r": lora_args.lora_rank, "lora_alpha": lora_args.lora_alpha,
                              "target_modules": list(targets)}
+    if getattr(lora_args, "moe_hybrid_shared_lora", False):
+        model._xb_lora_config["moe_hybrid_shared_lora"] = True
+    if lora_args.lora_b_init_std:
+        model._xb_lora_config.update(b_init_std=float(lora_args.lora_b_init_std), b_init_seed=int(lora_args.lora_b_init_seed or 0))
     if manifest is not None:
         validate(model, manifest)                   # exact adapter coverage, before any sharding or step
     return wrapped
@@ -232,12 +250,15 @@ def lora_state_dict_peft(named_full_tensors: Dict[str, torch.Tensor]) -> Dict[st
     out = {}
     for name, t in named_full_tensors.items():
         if name.endswith("_lora_A") or name.endswith("_lora_B"):
-            # stacked expert adapters -> one PEFT pair per expert: A [r, in], B [out, r]
+            # stacked expert adapters -> one PEFT pair per expert: A [r, in], B [out, r]; a factor shared by
+            # all experts (hybrid-shared adapters) is written under every expert
             mod, leaf = name.rsplit(".", 1)                      # ...mlp.experts.lora , gate_proj_lora_A
             proj, kind = leaf.rsplit("_lora_", 1)
             experts = mod.rsplit(".", 1)[0]
-            for e in range(t.shape[0]):
-                out[f"base_model.model.model.{experts}.{e}.{proj}.lora_{kind}.weight"] = t[e].t().contiguous()
+            partner = named_full_tensors.get(f"{mod}.{proj}_lora_{'B' if kind == 'A' else 'A'}")
+            E = max(t.shape[0], partner.shape[0] if partner is not None else 1)
+            for e in range(E):
+                out[f"base_model.model.model.{experts}.{e}.{proj}.lora_{kind}.weight"] = t[e if t.shape[0] > 1 else 0].t().contiguous()
             continue
         if ".lora_A." not in name and ".lora_B." not in name:
             continue
@@ -315,7 +336,8 @@ def merged_weight_view(engine):
             for p in lora.targets:
                 if (p == "down_proj") != (leaf == "down_proj"):
                     continue
-                delta = torch.bmm(factors[f"{mod}.lora.{p}_lora_A"], factors[f"{mod}.lora.{p}_lora_B"]).to(out.device)
+                fa, fb = factors[f"{mod}.lora.{p}_lora_A"], factors[f"{mod}.lora.{p}_lora_B"]
+                delta = torch.bmm(fa.expand(out.shape[0], -1, -1), fb.expand(out.shape[0], -1, -1)).to(out.device)
                 delta = delta * lora.scaling
                 if p == "gate_proj":
                     out[:, :, :I] += delta

@@ -247,13 +247,16 @@ def inject_qlora(model: nn.Module, lora_args) -> List[str]:
             if isinstance(m, Experts) and not any(x in name for x in exclude) and "gate_up_proj" in m._parameters:
                 proj = [p for p in ExpertsLoRA.PROJ if p in targets]
                 if proj and getattr(m, "lora", None) is None and m.gate_up_proj.shape[2] == 2 * m.down_proj.shape[1]:
-                    m.lora = ExpertsLoRA(m, lora_args.lora_rank, lora_args.lora_alpha, proj, lora_args.lora_b_init_std)
+                    m.lora = ExpertsLoRA(m, lora_args.lora_rank, lora_args.lora_alpha, proj, lora_args.lora_b_init_std,
+                                         hybrid_shared=bool(getattr(lora_args, "moe_hybrid_shared_lora", False)))
                 quantize_experts_(m, lora_args.quant_format, lora_args.quant_group_size)
                 wrapped.append(name)
     for n, p in model.named_parameters():
         p.requires_grad_(("lora_A" in n) or ("lora_B" in n))
     model._xb_lora_config = {"r": lora_args.lora_rank, "lora_alpha": lora_args.lora_alpha,
                              "target_modules": list(targets), "quant_format": lora_args.quant_format}
+    if lora_args.lora_b_init_std:
+        model._xb_lora_config.update(b_init_std=float(lora_args.lora_b_init_std), b_init_seed=int(lora_args.lora_b_init_seed or 0))
     if manifest is not None:
         validate(model, manifest)
     return wrapped

@@ -116,7 +116,6 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
     "lora": {
         "unfuse_for_lora": (_falsy, "adapters on fused projections are slice-exact; projections are not unfused"),
         "block_fp8_qlora_training": (_falsy, "fp8 training of QLoRA bases is not built"),
-        "moe_hybrid_shared_lora": (_falsy, "hybrid-shared expert LoRA is not built"),
     },
 }
 

@@ -320,9 +320,19 @@ def expert_mlp_aligned(x_buf: torch.Tensor, seg: torch.Tensor, gate_up: torch.Te
     return y
 
 
+def _lora_factor(x, W, seg, n_experts: int):
+    """``x`` through one adapter factor ``W [E, in, out]``: grouped by expert, or -- a factor shared by all
+    experts, ``W [1, in, out]`` -- one dense GEMM over all rows."""
+    if W.shape[0] == 1 and n_experts > 1:
+        from .gemm import linear
+        return linear(x, W[0].t().contiguous())
+    return grouped_linear(x, W, seg)
+
+
 def _expert_mlp_lora(x_buf, seg, gate_up, down, lora: dict, fp8) -> torch.Tensor:
     s = float(lora["scaling"])
     I = down.shape[1]
+    E = gate_up.shape[0]
     h = grouped_linear(x_buf, gate_up, seg, fp8)
     parts = []
     for name in ("gate_proj", "up_proj"):
@@ -331,7 +341,7 @@ def _expert_mlp_lora(x_buf, seg, gate_up, down, lora: dict, fp8) -> torch.Tensor
             parts.append(None)
             continue
         A, B = ab
-        parts.append(grouped_linear(grouped_linear(x_buf, A, seg), B, seg) * s)
+        parts.append(_lora_factor(_lora_factor(x_buf, A, seg, E), B, seg, E) * s)
     if parts[0] is not None or parts[1] is not None:
         zero = None
         cols = []
@@ -345,7 +355,7 @@ def _expert_mlp_lora(x_buf, seg, gate_up, down, lora: dict, fp8) -> torch.Tensor
     y = grouped_linear(a, down, seg, fp8)
     ab = lora.get("down_proj")
     if ab is not None:
-        y = y + grouped_linear(grouped_linear(a, ab[0], seg), ab[1], seg) * s
+        y = y + _lora_factor(_lora_factor(a, ab[0], seg, E), ab[1], seg, E) * s
     return y
 
 

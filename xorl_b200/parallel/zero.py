@@ -318,12 +318,23 @@ class Zero3Engine:
         cfg = getattr(model, "config", None)
         std = getattr(cfg, "initializer_range", 0.02)
         zc = getattr(cfg, "zero_centered_norm", False)
-        from ..models.decoder import init_parameter_
+        from ..models.decoder import init_parameter_ as _init_plain
+        lora_cfg = getattr(model, "_xb_lora_config", None) or {}
+        b_std, b_seed = float(lora_cfg.get("b_init_std") or 0.0), int(lora_cfg.get("b_init_seed") or 0)
+
+        def init_parameter_(name, p, *a, **k):
+            # lora.lora_b_init_std: B starts as N(0, std) instead of zero (drawn from lora_b_init_seed)
+            if b_std > 0 and (".lora_B." in name or name.endswith("_lora_B")) and not p.is_meta:
+                from ..adapters.lora import init_lora_parameter_
+                return init_lora_parameter_(name, p, 0, b_seed, b_std)
+            return _init_plain(name, p, *a, **k)
+
         for uname, mods in model.unit_modules():
             unit = ZeroUnit(uname, mods)
             dense: List[Tuple[str, nn.Parameter]] = []
             expert: List[Tuple[str, nn.Parameter]] = []
             frozen: List[Tuple[str, nn.Parameter]] = []
+            frozen_expert: List[Tuple[str, nn.Parameter]] = []   # frozen expert weights (adapters over experts)
             head: List[Tuple[str, nn.Parameter]] = []       # lm-head rows under lm-head-only tensor parallelism
             for m in mods:
                 for p in m.parameters():
@@ -333,10 +344,14 @@ class Zero3Engine:
                     if getattr(p, "_xb_lmtp", None) is not None:
                         head.append((fqn_of[id(p)], p))
                     elif not p.requires_grad:
-                        frozen.append((fqn_of[id(p)], p))
+                        # expert-parallel slices differ from rank to rank of the data-parallel group: frozen or
+                        # not, they are sharded over the ranks that hold the same experts
+                        (frozen_expert if getattr(p, "_xb_expert", False) and self.ps.ep_size > 1
+                         else frozen).append((fqn_of[id(p)], p))
                     else:
                         (expert if getattr(p, "_xb_expert", False) else dense).append((fqn_of[id(p)], p))
-            for kind, plist in (("dense", dense), ("expert", expert), ("frozen", frozen), ("head", head)):
+            for kind, plist in (("dense", dense), ("expert", expert), ("frozen", frozen),
+                                ("frozen_expert", frozen_expert), ("head", head)):
                 if not plist:
                     continue
                 if kind == "head":
@@ -347,16 +362,16 @@ class Zero3Engine:
                                        self.compute_dtype,
                                        None if hp is not None else self.ps.group("lm_head_replica"),
                                        1 if hp is not None else self.ps.size("lm_head_replica"))
-                elif kind == "expert" and self.ps.ep_size > 1:
+                elif kind in ("expert", "frozen_expert") and self.ps.ep_size > 1:
                     g = FlatParamGroup(f"{uname}.{kind}", plist, self.ep_shard_pg, self.ep_shard_world,
                                        self.ep_shard_rank, self.device, self.compute_dtype)
                 else:
                     g = FlatParamGroup(f"{uname}.{kind}", plist, self.shard_pg, self.shard_world,
                                        self.shard_rank, self.device, self.compute_dtype,
                                        self.rep_pg, self.rep_world)
-                g.is_expert = kind == "expert"
+                g.is_expert = kind in ("expert", "frozen_expert")
                 g.is_head = kind == "head"
-                g.frozen = kind == "frozen" or (kind == "head" and not plist[0][1].requires_grad)
+                g.frozen = kind in ("frozen", "frozen_expert") or (kind == "head" and not plist[0][1].requires_grad)
                 self._materialize_group(g, std, seed, index_of, zc, init_parameter_)
                 unit.groups.append(g)
             self.units.append(unit)
