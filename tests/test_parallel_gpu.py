@@ -159,6 +159,26 @@ def test_moe_expert_parallel_block_fp8(tmp_path, tmp_path_factory):
     assert abs(ref[0][0] - bf16[0]) < 0.02 * bf16[0] and abs(ref[0][-1] - bf16[-1]) < 0.15 * bf16[-1] + 0.3
 
 
+def test_moe_expert_parallel_lora(tmp_path):
+    """Adapters over a MoE model whose frozen experts are split over two GPUs (hybrid-shared expert adapters:
+    per-expert factors live with their experts, shared factors are replicated): the loss curve and the
+    adapter gradients of the one-GPU run."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    lora = ("--lora.enable_lora", "true", "--lora.lora_rank", "8", "--lora.lora_alpha", "16",
+            "--lora.moe_hybrid_shared_lora", "true", "--lora.lora_b_init_std", "0.02")
+    (rl, rg) = _run(tmp_path, "ref_lora", 1, model="small-qwen3-moe", extra_cli=lora, lr=5e-3)
+    (gl, gg) = _run(tmp_path, "ep2_lora", 2, model="small-qwen3-moe", dp=2, expert_parallel_size=2, lr=5e-3,
+                    extra_cli=lora + ("--model.ep_dispatch", "fused"))
+    assert len(rl) == len(gl) == STEPS and rl[0] - min(rl) > 0.1, rl
+    for i, (a, b) in enumerate(zip(rl, gl)):
+        assert abs(a - b) < (0.01 if i < 8 else 0.05) * abs(a), (i, rl, gl)
+    assert set(rg) == set(gg) and rg and all("lora" in n for n in rg), sorted(set(rg) ^ set(gg))[:8]
+    worst = max(((n, float((gg[n].float() - g.float()).norm() / (g.float().norm() + 1e-12))) for n, g in rg.items()),
+                key=lambda t: t[1])
+    assert worst[1] < 0.06, worst
+
+
 def test_checkpoint_resume_on_gpu(tmp_path):
     """Pieces of the flat shards written from device memory, read back into them: a run resumed from
     step 2 repeats steps 3 and 4 of the uninterrupted run (the kernels are deterministic)."""
