@@ -69,6 +69,8 @@ SATISFIED_BY_DESIGN: Dict[str, Dict[str, str]] = {
         "ce_mode": "one fused lm-head + cross-entropy kernel path",
     },
     "lora": {
+        "unfuse_for_lora": "fused projections carry one adapter per output slice (q / k / v, gate / up) with the "
+                           "same mathematics as adapters on unfused projections, so nothing needs to be split",
     },
     "distill": {
         "stream_num_workers": "teacher scores are produced in-process, one forward pass per micro-batch",
@@ -114,7 +116,6 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "enable_compile": (_falsy, "there is no tracing compiler on any path"),
     },
     "lora": {
-        "unfuse_for_lora": (_falsy, "adapters on fused projections are slice-exact; projections are not unfused"),
         "block_fp8_qlora_training": (_falsy, "fp8 training of QLoRA bases is not built"),
     },
 }
