@@ -476,6 +476,45 @@ def test_dispatcher_two_ranks_agree_on_errors(tmp_path):
     assert "DISPATCH_OK" in out
 
 
+@pytest.mark.distributed
+def test_routing_replay_travels_beside_the_broadcast_command(tmp_path):
+    from dist_utils import run_distributed
+    out = run_distributed(os.path.join(os.path.dirname(__file__), "server_routing_payload_worker.py"), 2, str(tmp_path))
+    assert "ROUTING_PAYLOAD_OK" in out
+
+
+def test_routing_payload_chunks_and_checks(tmp_path):
+    import base64
+    import numpy as np
+    from xorl_b200.server.side_payloads import (FilesystemPayloadStore, PayloadError, RoutingPayloads,
+                                                canonical_routing, is_routing_ref)
+    rp = RoutingPayloads(FilesystemPayloadStore(str(tmp_path / "p")), chunk_bytes=1000, min_bytes=0)
+    g = torch.Generator().manual_seed(0)
+    rows = [torch.randint(-1, 64, (n, 3, 4), generator=g) for n in (20, 7, 33)]
+    enc = np.asarray(rows[1].numpy(), dtype="<i4")
+    datums = [{"tokens": [1] * 20, "routed_experts": rows[0].tolist()},
+              {"tokens": [1] * 7, "routed_experts": {"data": base64.b64encode(enc.tobytes()).decode(), "shape": [7, 3, 4],
+                                                     "dtype": "int32"}},
+              {"tokens": [1] * 5},
+              {"tokens": [1] * 33, "routed_experts": rows[2]}]
+    out, keys = rp.stash(datums)
+    assert len(keys) == 2 and "routed_experts" not in out[2] and datums[0]["routed_experts"] == rows[0].tolist()
+    for d, want in zip((out[0], out[1], out[3]), rows):
+        assert is_routing_ref(d["routed_experts"]) and torch.equal(rp.resolve(d)["routed_experts"], want)
+    # rows that do not match their checksum, rows that are gone
+    ref = dict(out[0]["routed_experts"], offset=2)
+    with pytest.raises(PayloadError, match="do not match"):
+        rp.load(ref)
+    assert rp.cleanup(keys)["chunks_deleted"] == 2 and rp.cleanup(keys)["chunks_deleted"] == 0
+    with pytest.raises(PayloadError, match="gone"):
+        rp.load(out[0]["routed_experts"])
+    with pytest.raises(PayloadError):
+        canonical_routing(torch.full((2, 1, 1), 40000))
+    small = RoutingPayloads(FilesystemPayloadStore(str(tmp_path / "q")))       # default threshold: tiny requests stay inline
+    same, none = small.stash(datums)
+    assert same is datums and none == []
+
+
 def _lora_runner(tmp_path, preset="tiny-qwen3"):
     from xorl_b200.parallel.state import reset_parallel_state
     from xorl_b200.server.runner import ModelRunner

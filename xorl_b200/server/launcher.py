@@ -32,6 +32,8 @@ class DispatchBackend(Backend):
     def __init__(self, dispatcher: RunnerDispatcher):
         self.d = dispatcher
         self._lock = threading.Lock()
+        # large routing-replay tensors travel beside the broadcast command, not inside it
+        self.payloads = getattr(dispatcher.runner, "payloads", None)
 
     def _call(self, op: str, model_id: str, args: Dict[str, Any]):
         with self._lock:
@@ -40,13 +42,22 @@ class DispatchBackend(Backend):
             raise RuntimeError(out["error"])
         return out["result"]
 
+    def _with_payloads(self, op, model_id, datums, plan, loss_fn, loss_fn_config):
+        keys = []
+        if self.payloads is not None:
+            datums, keys = self.payloads.stash(datums)
+        try:
+            return self._call(op, model_id, dict(datums=datums, plan=plan, loss_fn=loss_fn,
+                                                 loss_fn_config=loss_fn_config))
+        finally:
+            if keys:
+                self.payloads.cleanup(keys)          # every rank has answered (or failed together) by now
+
     def forward_backward(self, model_id, datums, plan, loss_fn, loss_fn_config):
-        return self._call("forward_backward", model_id, dict(datums=datums, plan=plan, loss_fn=loss_fn,
-                                                             loss_fn_config=loss_fn_config))
+        return self._with_payloads("forward_backward", model_id, datums, plan, loss_fn, loss_fn_config)
 
     def forward(self, model_id, datums, plan, loss_fn, loss_fn_config):
-        return self._call("forward", model_id, dict(datums=datums, plan=plan, loss_fn=loss_fn,
-                                                    loss_fn_config=loss_fn_config))
+        return self._with_payloads("forward", model_id, datums, plan, loss_fn, loss_fn_config)
 
     def optim_step(self, model_id, **kw):
         return self._call("optim_step", model_id, kw)

@@ -54,6 +54,8 @@ class ModelRunner:
         self.poisoned: Optional[str] = None
         self.output_dir = trainer.args.train.output_dir
         self.adapters = None                 # AdapterManager, created with the first extra adapter
+        from .side_payloads import FilesystemPayloadStore, RoutingPayloads
+        self.payloads = RoutingPayloads(FilesystemPayloadStore(os.path.join(self.output_dir, "side_payloads")))
         self.host_group = None               # gloo group of all ranks (set by the dispatcher); None: default group
         # expert-load metrics of MoE models: one JSON line per forward_backward in moe_metrics.jsonl
         self.moe_metrics = None
@@ -72,6 +74,8 @@ class ModelRunner:
             ds = []
             for i in b:
                 d = dict(datums[i])
+                if self.payloads is not None:
+                    d = self.payloads.resolve(d)         # this rank's rows of a routing payload parked beside the command
                 d["datum_index"] = i
                 ds.append(d)
             out.append(datums_to_micro_batch(ds, pad_to=128))
