@@ -19,6 +19,8 @@ from typing import Any, Callable, Dict, Tuple
 # section -> key -> reason
 SATISFIED_BY_DESIGN: Dict[str, Dict[str, str]] = {
     "model": {
+        "moe_routing_weights_before_down": "a rounding-point choice of the reference's Triton expert backend (same "
+                                           "mathematics); here the routing weights are applied in fp32 by the combine",
         "flash_attention_deterministic": "the attention backward has no atomics: it is deterministic with either value",
         "merge_qkv": "projections are always fused in memory; checkpoint handlers split and merge on disk",
         "rmsnorm_mode": "one RMSNorm kernel (csrc/norm.cu); the reference's implementation families do not exist here",
@@ -89,7 +91,6 @@ def _falsy(v) -> bool:
 # section -> key -> (predicate on the value: True = supported, what is missing)
 UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
     "model": {
-        "moe_routing_weights_before_down": (_is("auto", "false", False), "routing weights are applied after the down projection only"),
         "sparse_mla_enabled": (_falsy, "sparse MLA kernels are not built; attention over selected keys runs as masked softmax"),
         "sparse_mla_backend": (_is("auto"), "no selectable sparse-MLA backend"),
     },
