@@ -69,3 +69,33 @@ def test_fp8_linears_lora_and_moe_losses(tmp_path):
     assert os.path.exists(peft / "adapter_config.json") and any("adapter_model" in f for f in os.listdir(peft))
     moe = _run(tmp_path, "moe", model="small-qwen3-moe", softmax_auxiliary_loss=True, auxiliary_loss_multiplier=1e-4)
     assert moe["loss_history"][-1] < moe["loss_history"][0]
+
+
+def test_test_dataset_is_evaluated_at_checkpoints(tmp_path):
+    """``data.test_datasets`` = the training rows themselves: the evaluation pass (no gradients, parameters
+    gathered unit by unit, fused lm-head log-probabilities) sees the loss the run has memorised them to."""
+    p = tmp_path / "ev"
+    cfg_extra = {"test_datasets": [{"path": "random", "type": "tokenized", "max_seq_len": 700, "min_seq_len": 400,
+                                    "num_samples": 16}]}
+    cfg = {
+        "model": {"config_path": "small-qwen3"},
+        "data": {"datasets": [{"path": "random", "type": "tokenized", "max_seq_len": 700, "min_seq_len": 400,
+                               "num_samples": 16}],
+                 "sample_packing_sequence_len": 2048, "pad_to_multiple_of": 128, "shuffle_merged_datasets": False,
+                 **cfg_extra},
+        "train": {"output_dir": str(p), "lr": 1e-3, "max_steps": STEPS, "use_wandb": False, "save_hf_weights": False,
+                  "save_epochs": 0, "num_train_epochs": 1000, "weight_decay": 0.0, "gradient_accumulation_steps": 4,
+                  "save_steps": 7},
+    }
+    (tmp_path / "ev.yaml").write_text(yaml.safe_dump(cfg))
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    r = subprocess.run([sys.executable, "-m", "xorl_b200.cli.train", str(tmp_path / "ev.yaml")], env=env,
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    with open(p / "training_metrics.json") as f:
+        m = json.load(f)
+    ev = m["eval_history"]
+    assert [e["step"] for e in ev] == [7, 14] and ev[1]["eval_loss"] < ev[0]["eval_loss"]
+    # same rows, same weights: the evaluation loss after the last step is close to (a little below) the last
+    # training loss, which was measured before that step's update
+    assert ev[1]["eval_loss"] < m["loss_history"][-1] + 0.05 and ev[1]["eval_loss"] > 0.5 * m["loss_history"][-1] - 0.5
