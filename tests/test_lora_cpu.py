@@ -453,3 +453,20 @@ def test_adaptive_quantisation_noise_has_the_size_of_the_grid_and_is_off_outside
             assert torch.equal(q(x).t(), deq)
         q.eval()
         assert torch.equal(q(x).t(), deq)
+
+
+def test_fp8_module_overrides_choose_the_backward_precision_per_module():
+    import pytest
+    from xorl_b200.adapters.fp8 import FP8Linear, inject_fp8_training
+    from xorl_b200.arguments import TrainingArguments
+    ta = TrainingArguments(output_dir="o", device="cpu", enable_fp8_training=True, fp8_training_allow_blackwell=True,
+                           fp8_training_backward="fp8",
+                           fp8_training_module_overrides={"*.self_attn.o_proj": {"backward_mode": "bf16"},
+                                                          "down_proj": {"backward_mode": "bf16", "block_size": 128}})
+    model = DecoderLM(preset("tiny-qwen3", tie_word_embeddings=False), device="meta")
+    inject_fp8_training(model, ta)
+    modes = {n: m.fp8_backward for n, m in model.named_modules() if isinstance(m, FP8Linear)}
+    assert modes and all(v == (not (n.endswith("o_proj") or n.endswith("down_proj"))) for n, v in modes.items()), modes
+    ta.fp8_training_module_overrides = {"q*": {"smoothquant_alpha": 0.5}}
+    with pytest.raises(NotImplementedError, match="smoothquant_alpha"):
+        inject_fp8_training(DecoderLM(preset("tiny-qwen3"), device="meta"), ta)

@@ -115,8 +115,30 @@ def validate_blackwell_policy(train_args) -> None:
                          "(validated numerics artifact)")
 
 
+def _module_override(full: str, overrides) -> dict:
+    """First pattern of ``train.fp8_training_module_overrides`` (globs on the full or the last name) that
+    matches.  ``backward_mode`` (``fp8`` / ``bf16``) is the per-module choice that exists here; the block
+    size is 128 everywhere, and amax margins, SmoothQuant and residual correction are not built."""
+    import fnmatch
+    short = full.rsplit(".", 1)[-1]
+    for pattern, recipe in (overrides or {}).items():
+        if fnmatch.fnmatch(full, pattern) or fnmatch.fnmatch(short, pattern):
+            extra = {k: v for k, v in recipe.items()
+                     if k != "backward_mode" and not (k == "block_size" and v == 128)
+                     and not (k in ("activation_amax_scale", "weight_amax_scale") and v in (1, 1.0))
+                     and not (k == "correction_mode" and v == "none") and not (k == "smoothquant_alpha" and not v)}
+            if extra:
+                raise NotImplementedError(f"fp8_training_module_overrides[{pattern!r}]: {sorted(extra)} cannot be "
+                                          f"overridden per module (only backward_mode can)")
+            if recipe.get("backward_mode", "fp8") not in ("fp8", "bf16"):
+                raise ValueError(f"fp8_training_module_overrides[{pattern!r}].backward_mode must be fp8 or bf16")
+            return dict(recipe)
+    return {}
+
+
 def inject_fp8_training(model: nn.Module, train_args) -> List[str]:
     validate_blackwell_policy(train_args)
+    overrides = getattr(train_args, "fp8_training_module_overrides", None)
     targets = train_args.fp8_training_target_modules
     exclude = tuple(train_args.fp8_training_exclude_modules or ()) + ("lm_head",)
     n_layers = getattr(model.config, "num_hidden_layers", 0)
@@ -140,7 +162,8 @@ def inject_fp8_training(model: nn.Module, train_args) -> List[str]:
                 if any(x in full for x in exclude) or (targets and not any(t in full for t in targets)) \
                         or layer_skipped(full):
                     continue
-                child.fp8_mode = "fp8" if train_args.fp8_training_backward == "fp8" else "bf16"
+                mode = _module_override(full, overrides).get("backward_mode", train_args.fp8_training_backward)
+                child.fp8_mode = "fp8" if mode == "fp8" else "bf16"
                 wrapped.append(full)
                 continue
             if not isinstance(child, Linear) or any(x in full for x in exclude):
@@ -152,6 +175,7 @@ def inject_fp8_training(model: nn.Module, train_args) -> List[str]:
                 li = int(parts[parts.index("layers") + 1])
                 if li < skip_first or li >= n_layers - skip_last:
                     continue
-            setattr(parent, cname, FP8Linear(child, train_args.fp8_training_backward == "fp8"))
+            mode = _module_override(full, overrides).get("backward_mode", train_args.fp8_training_backward)
+            setattr(parent, cname, FP8Linear(child, mode == "fp8"))
             wrapped.append(full)
     return wrapped

@@ -114,7 +114,6 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "fp8_training_activation_amax_scale": (_is(1.0, 1), "amax margins are not built"),
         "fp8_training_weight_amax_scale": (_is(1.0, 1), "amax margins are not built"),
         "fp8_training_correction_mode": (_is("none"), "residual correction is not built"),
-        "fp8_training_module_overrides": (_falsy, "per-module fp8 overrides are not built (use target / exclude modules)"),
         "fp8_training_moe_grouped_backend": (_is("triton_grouped"), "the grouped fp8 GEMM has one backend: the tcgen05 block-scaled kernel"),
         "enable_compile": (_falsy, "there is no tracing compiler on any path"),
     },
