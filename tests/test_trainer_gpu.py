@@ -96,6 +96,7 @@ def test_test_dataset_is_evaluated_at_checkpoints(tmp_path):
         m = json.load(f)
     ev = m["eval_history"]
     assert [e["step"] for e in ev] == [7, 14] and ev[1]["eval_loss"] < ev[0]["eval_loss"]
-    # same rows, same weights: the evaluation loss after the last step is close to (a little below) the last
-    # training loss, which was measured before that step's update
-    assert ev[1]["eval_loss"] < m["loss_history"][-1] + 0.05 and ev[1]["eval_loss"] > 0.5 * m["loss_history"][-1] - 0.5
+    # the evaluation set also holds the rows that the training steps drop (a step takes four packed rows, the
+    # ragged rest of an epoch is dropped), so its loss stays above the training loss but well below the start
+    assert ev[0]["eval_tokens"] == ev[1]["eval_tokens"] > 4 * 1024
+    assert m["loss_history"][-1] - 0.1 < ev[1]["eval_loss"] < m["loss_history"][0] - 0.5, (ev, m["loss_history"])

@@ -198,3 +198,32 @@ if __name__ == "__main__":
     if dist.get_rank() == 0:
         print("LOSSES " + json.dumps(curve))
     dist.destroy_process_group()
+
+
+def test_eval_loss_equals_the_training_loss_at_the_same_weights():
+    """``eval_loss`` (no gradients, units gathered one by one, lm-head log-probabilities) on a packed batch with
+    ignored labels gives the loss that ``forward_backward`` reports for that batch before its update."""
+    from xorl_b200.models.config import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.state import init_parallel_state, reset_parallel_state
+    from xorl_b200.parallel.zero import Zero3Engine
+    reset_parallel_state()
+    ps = init_parallel_state(device_type="cpu")
+    eng = Zero3Engine(DecoderLM(preset("tiny-qwen3"), device="meta"), ps, compute_dtype=torch.float32,
+                      device=torch.device("cpu"))
+    opt = build_optimizer(eng, lr=1e-3, weight_decay=0.0)
+    ids = torch.randint(0, 1024, (1, 257))
+    x, y = ids[:, :-1], ids[:, 1:].clone()
+    y[0, 99] = -100
+    cu = torch.tensor([0, 100, 256], dtype=torch.int32)
+    pos = torch.cat([torch.arange(100), torch.arange(156)])[None]
+    for _ in range(3):
+        s, n = eng.eval_loss(x, y, position_ids=pos, cu_seqlens=cu)
+        assert int(n) == 255
+        opt.zero_grad()
+        loss = eng.forward_backward(x, y, position_ids=pos, cu_seqlens=cu, grad_scale=1.0 / float(n))
+        eng.finish_grad_sync()
+        opt.step()
+        assert abs(float(s / n) - float(loss)) < 1e-5
+    reset_parallel_state()
