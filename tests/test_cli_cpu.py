@@ -183,3 +183,11 @@ def test_every_config_key_is_read_or_accounted_for():
             assert raised, f"{sec}.{key} never raised NotImplementedError"
     # the defaults themselves are all accepted
     A.build_args({})
+
+
+def test_the_configuration_reference_is_current():
+    """``docs/config-reference.md`` is what ``python -m xorl_b200.cli.config_reference`` prints now."""
+    from xorl_b200.cli.config_reference import render
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "docs", "config-reference.md")) as f:
+        assert f.read() == render(), "regenerate: python -m xorl_b200.cli.config_reference > docs/config-reference.md"

@@ -127,7 +127,7 @@ class TrainingArguments:
     muon_grad_dtype: Optional[str] = None
     muon_update_dtype: Optional[str] = None
     muon_force_momentum_path: bool = False
-    muon_distributed_mode: Literal["shard_local", "full_matrix"] = "shard_local"
+    muon_distributed_mode: Literal["shard_local", "full_gradient"] = "shard_local"
     max_grad_norm: float = 1.0
     softmax_auxiliary_loss: bool = False
     auxiliary_loss_multiplier: float = 1e-5
