@@ -227,3 +227,34 @@ def test_eval_loss_equals_the_training_loss_at_the_same_weights():
         opt.step()
         assert abs(float(s / n) - float(loss)) < 1e-5
     reset_parallel_state()
+
+
+def test_anyprecision_adamw_memory_options_change_no_value():
+    """Moments in host memory, the update in chunks, and the first moment formed in place in the gradient
+    shard: the same weights after three steps as the plain bf16-moment optimizer."""
+    from xorl_b200.models.config import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.state import init_parallel_state, reset_parallel_state
+    from xorl_b200.parallel.zero import Zero3Engine
+    torch.manual_seed(0)
+    ids = torch.randint(0, 1024, (2, 65))
+    results = []
+    for okw in ({}, {"state_cpu_offload": True, "denominator_chunk_size": 1000, "reuse_grad_for_momentum": True}):
+        reset_parallel_state()
+        ps = init_parallel_state(device_type="cpu")
+        eng = Zero3Engine(DecoderLM(preset("tiny-qwen3"), device="meta"), ps, compute_dtype=torch.float32,
+                          device=torch.device("cpu"), seed=3)
+        opt = build_optimizer(eng, lr=1e-3, weight_decay=0.01, optimizer_type="anyprecision_adamw", optimizer_dtype="bf16",
+                              optimizer_kwargs=okw)
+        assert opt.offload == bool(okw) and opt.chunk == okw.get("denominator_chunk_size", 0)
+        for _ in range(3):
+            opt.zero_grad()
+            eng.forward_backward(ids[:, :-1], ids[:, 1:], grad_scale=1.0 / 128)
+            eng.finish_grad_sync()
+            _, coef = eng.grad_norm_and_clip_coef(1.0)
+            opt.step(clip_coef=coef)
+        results.append({n: t.clone() for n, t in eng.iter_full_tensors("master")})
+    for n, t in results[0].items():
+        assert float((t - results[1][n]).abs().max()) < 2e-5, (n, float((t - results[1][n]).abs().max()))  # fp32 summation order of the first moment only
+    reset_parallel_state()

@@ -101,9 +101,6 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "push_dataset_to_hub": (_falsy, "no network access"),
     },
     "train": {
-        "anyprecision_adamw_denominator_chunk_size": (_falsy, "the AnyPrecision update is not chunked"),
-        "anyprecision_adamw_reuse_grad_for_momentum": (_falsy, "not built"),
-        "anyprecision_adamw_state_cpu_offload": (_falsy, "optimizer state offload is not built"),
         "muon_fallback_optimizer": (_is("adamw"), "non-matrix parameters under Muon always use AdamW"),
         "muon_grad_dtype": (_falsy, "Muon works on the fp32 gradient shards"),
         "muon_update_dtype": (_falsy, "Muon updates are bf16 Newton-Schulz iterates applied to fp32 masters"),

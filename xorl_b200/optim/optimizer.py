@@ -142,12 +142,39 @@ class ShardedAnyPrecisionAdamW(ShardedOptimizer):
     kind = "anyprecision_adamw"
 
     def __init__(self, engine, lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0,
-                 state_dtype=torch.bfloat16, cautious_weight_decay=False, **kw):
+                 state_dtype=torch.bfloat16, cautious_weight_decay=False, state_cpu_offload: bool = False,
+                 denominator_chunk_size: int = 0, reuse_grad_for_momentum: bool = False, **kw):
+        """``state_cpu_offload``: the moments live in (pinned) host memory and visit the device one parameter
+        group at a time during the step, the next group's moments copied in while the current one updates.
+        ``denominator_chunk_size``: elements per pass of the update, which bounds its fp32 temporaries
+        (0 = a whole decay segment at once).  ``reuse_grad_for_momentum``: the scaled gradient and then the fp32
+        first moment are formed in place in the gradient shard instead of in new buffers (the gradient is
+        consumed by the step) (src/xorl/optim/anyprecision_adamw.py)."""
         super().__init__(engine, lr, weight_decay, kw.get("no_decay_modules", ()),
                          kw.get("no_decay_params", ()))
         self.betas, self.eps, self.cautious = betas, eps, cautious_weight_decay
+        self.offload = bool(state_cpu_offload)
+        self.chunk = int(denominator_chunk_size or 0)
+        self.reuse_grad = bool(reuse_grad_for_momentum)
         self.exp_avg = self._new_state("exp_avg", state_dtype)
         self.exp_avg_sq = self._new_state("exp_avg_sq", state_dtype)
+        if self.offload:
+            pin = self.engine.device.type == "cuda"
+            for d in (self.exp_avg, self.exp_avg_sq):
+                for k, t in d.items():
+                    d[k] = torch.zeros(t.shape, dtype=t.dtype, device="cpu", pin_memory=pin)
+            self._copy_stream = torch.cuda.Stream(self.engine.device) if pin else None
+
+    def _fetch(self, g):
+        """Device copies of a group's moments (the tensors themselves when nothing is offloaded)."""
+        m, v = self.exp_avg[id(g)], self.exp_avg_sq[id(g)]
+        if not self.offload or self.engine.device.type != "cuda":
+            return m, v, None
+        with torch.cuda.stream(self._copy_stream):
+            md, vd = m.to(self.engine.device, non_blocking=True), v.to(self.engine.device, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        return md, vd, ev
 
     @torch.no_grad()
     def step(self, clip_coef=None, grad_scale: float = 1.0) -> None:
@@ -155,27 +182,46 @@ class ShardedAnyPrecisionAdamW(ShardedOptimizer):
         b1, b2 = self.betas
         bc1 = 1 - b1 ** self.step_count
         bc2 = 1 - b2 ** self.step_count
-        for g in self.engine.all_groups():
-            if not g.grad_ready:
-                continue
-            for a, b, wd in self._segments(g):
-                p = g.master[a:b]
-                gr = g.grad_shard[a:b] * grad_scale
-                if clip_coef is not None:
-                    gr = gr * clip_coef
-                m = self.exp_avg[id(g)][a:b].float().mul_(b1).add_(gr, alpha=1 - b1)
-                v = self.exp_avg_sq[id(g)][a:b].float().mul_(b2).addcmul_(gr, gr, value=1 - b2)
-                self.exp_avg[id(g)][a:b].copy_(m)
-                self.exp_avg_sq[id(g)][a:b].copy_(v)
-                update = (m / bc1) / ((v / bc2).sqrt_().add_(self.eps))
-                if wd:
-                    if self.cautious:
-                        mask = (update * p >= 0).to(p.dtype)
-                        p.sub_(p * mask, alpha=self.lr * wd)
+        groups = [g for g in self.engine.all_groups() if g.grad_ready and not getattr(g, "frozen", False)]
+        nxt = self._fetch(groups[0]) if groups else None
+        for gi, g in enumerate(groups):
+            m_all, v_all, ready = nxt
+            nxt = self._fetch(groups[gi + 1]) if gi + 1 < len(groups) else None      # copied in under this group's update
+            if ready is not None:
+                torch.cuda.current_stream().wait_event(ready)
+            for a0, b0, wd in self._segments(g):
+                step_n = self.chunk if self.chunk > 0 else b0 - a0
+                for a in range(a0, b0, step_n):
+                    b = min(b0, a + step_n)
+                    p = g.master[a:b]
+                    if self.reuse_grad:
+                        gr = g.grad_shard[a:b].mul_(grad_scale)
+                        if clip_coef is not None:
+                            gr.mul_(clip_coef)
+                        v = v_all[a:b].float().mul_(b2).addcmul_(gr, gr, value=1 - b2)
+                        m = gr.mul_(1 - b1).add_(m_all[a:b].float(), alpha=b1)      # the gradient shard now holds m
                     else:
-                        p.mul_(1 - self.lr * wd)
-                p.sub_(update, alpha=self.lr)
+                        gr = g.grad_shard[a:b] * grad_scale
+                        if clip_coef is not None:
+                            gr = gr * clip_coef
+                        m = m_all[a:b].float().mul_(b1).add_(gr, alpha=1 - b1)
+                        v = v_all[a:b].float().mul_(b2).addcmul_(gr, gr, value=1 - b2)
+                    m_all[a:b].copy_(m)
+                    v_all[a:b].copy_(v)
+                    update = (m / bc1) / ((v / bc2).sqrt_().add_(self.eps))
+                    if wd:
+                        if self.cautious:
+                            mask = (update * p >= 0).to(p.dtype)
+                            p.sub_(p * mask, alpha=self.lr * wd)
+                        else:
+                            p.mul_(1 - self.lr * wd)
+                    p.sub_(update, alpha=self.lr)
+            if self.offload and m_all is not self.exp_avg[id(g)]:
+                self.exp_avg[id(g)].copy_(m_all, non_blocking=True)
+                self.exp_avg_sq[id(g)].copy_(v_all, non_blocking=True)
             self.engine.refresh_compute_copy(g)
+        if self.offload and self.engine.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()         # the host copies are complete before anyone reads them
 
 
 class ShardedSGD(ShardedOptimizer):
@@ -298,12 +344,13 @@ def build_optimizer(engine: Zero3Engine, lr: float = 1e-3, betas=(0.9, 0.95), ep
                     optimizer_kwargs: Optional[dict] = None, cautious_weight_decay: bool = False):
     kw = dict(no_decay_modules=no_decay_modules or (), no_decay_params=no_decay_params or ())
     okw = dict(optimizer_kwargs or {})
-    if optimizer_type == "adamw" and not cautious_weight_decay:
+    any_kw = {k: okw[k] for k in ("state_cpu_offload", "denominator_chunk_size", "reuse_grad_for_momentum") if okw.get(k)}
+    if optimizer_type == "adamw" and not cautious_weight_decay and not any_kw:
         return ShardedAdamW(engine, lr, betas, eps, weight_decay, **kw)
     if optimizer_type in ("adamw", "anyprecision_adamw"):
         dt = torch.float32 if (optimizer_dtype == "fp32" or optimizer_type == "adamw") else torch.bfloat16
         return ShardedAnyPrecisionAdamW(engine, lr, betas, eps, weight_decay, state_dtype=dt,
-                                        cautious_weight_decay=cautious_weight_decay, **kw)
+                                        cautious_weight_decay=cautious_weight_decay, **any_kw, **kw)
     if optimizer_type == "sgd":
         return ShardedSGD(engine, lr, okw.get("momentum", 0.0), okw.get("nesterov", False),
                           weight_decay, **kw)
