@@ -71,3 +71,41 @@ def test_gradient_accumulation_with_early_norms():
     l1, n1, _ = _run(True, True, True, steps=4, accum=2)
     for a, b in zip(n0, n1):
         assert abs(a - b) <= 1e-5 * max(1.0, abs(a)), (n0, n1)
+
+
+def test_anyprecision_adamw_with_moments_in_host_memory():
+    """bf16 moments kept in pinned host memory and streamed in group by group (next group's copy under the
+    current group's update), update in chunks, first moment formed in the gradient shard: the weights of the
+    plain bf16-moment optimizer."""
+    from xorl_b200.models import preset
+    from xorl_b200.models.decoder import DecoderLM
+    from xorl_b200.optim import build_optimizer
+    from xorl_b200.parallel.state import init_parallel_state, reset_parallel_state
+    from xorl_b200.parallel.zero import Zero3Engine
+    torch.cuda.set_device(0)
+    cfg = preset("qwen3-8b", num_hidden_layers=3, hidden_size=512, intermediate_size=1536,
+                 num_attention_heads=4, num_key_value_heads=2, vocab_size=4096)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (513,), generator=g).cuda()
+    cu = torch.tensor([0, 200, 512], device="cuda", dtype=torch.int32)
+    out = []
+    for okw in ({}, {"state_cpu_offload": True, "denominator_chunk_size": 100000, "reuse_grad_for_momentum": True}):
+        reset_parallel_state()
+        ps = init_parallel_state(device_type="cuda")
+        eng = Zero3Engine(DecoderLM(cfg, device="meta"), ps, compute_dtype=torch.bfloat16, device=torch.device("cuda", 0))
+        opt = build_optimizer(eng, lr=1e-3, weight_decay=0.01, optimizer_type="anyprecision_adamw",
+                              optimizer_dtype="bf16", optimizer_kwargs=okw)
+        if okw:
+            assert all(t.device.type == "cpu" and t.is_pinned() for t in opt.exp_avg.values())
+        for _ in range(4):
+            opt.zero_grad()
+            eng.forward_backward(ids[:-1], ids[1:], cu_seqlens=cu, grad_scale=1.0 / 512)
+            eng.finish_grad_sync()
+            _, coef = eng.grad_norm_and_clip_coef(1.0)
+            opt.step(clip_coef=coef)
+        eng.sync_optimizer()
+        out.append({n: t.float().clone() for n, t in eng.iter_full_tensors("master")})
+    for n, t in out[0].items():
+        d = float((t - out[1][n]).abs().max())
+        assert d < 5e-5, (n, d)                 # summation order of the first moment; an update is ~1e-3
+    reset_parallel_state()
