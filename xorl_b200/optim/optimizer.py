@@ -188,7 +188,10 @@ class ShardedAnyPrecisionAdamW(ShardedOptimizer):
             m_all, v_all, ready = nxt
             nxt = self._fetch(groups[gi + 1]) if gi + 1 < len(groups) else None      # copied in under this group's update
             if ready is not None:
-                torch.cuda.current_stream().wait_event(ready)
+                cur = torch.cuda.current_stream()
+                cur.wait_event(ready)
+                m_all.record_stream(cur)          # allocated on the copy stream, used (and freed) under this one
+                v_all.record_stream(cur)
             for a0, b0, wd in self._segments(g):
                 step_n = self.chunk if self.chunk > 0 else b0 - a0
                 for a in range(a0, b0, step_n):
