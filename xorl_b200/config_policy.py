@@ -51,6 +51,8 @@ SATISFIED_BY_DESIGN: Dict[str, Dict[str, str]] = {
     },
     "train": {
         "enable_reentrant": "recomputation is done by the engine, not by torch.utils.checkpoint",
+        "fp8_training_moe_grouped_backend": "the grouped fp8 expert GEMM has one backend here, the tcgen05 block-scaled "
+                                            "kernel (csrc/grouped_gemm_mx.cu), whichever of the reference's is named",
         "muon_distributed_mode": "Newton-Schulz always runs on the whole matrix (the update direction is gathered over "
                                  "the shard group and each rank keeps its slice of the result): the exact form, "
                                  "full_gradient; there is no approximate shard-local mode",
@@ -101,6 +103,8 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "push_dataset_to_hub": (_falsy, "no network access"),
     },
     "train": {
+        "anyprecision_adamw_reuse_grad_for_momentum": (_falsy, "the optimizer step never writes the gradient shard (other streams order "
+                                                                "themselves against reads of it only)"),
         "muon_fallback_optimizer": (_is("adamw"), "non-matrix parameters under Muon always use AdamW"),
         "muon_grad_dtype": (_falsy, "Muon works on the fp32 gradient shards"),
         "muon_update_dtype": (_falsy, "Muon updates are bf16 Newton-Schulz iterates applied to fp32 masters"),
@@ -111,7 +115,6 @@ UNSUPPORTED: Dict[str, Dict[str, Tuple[Callable[[Any], bool], str]]] = {
         "fp8_training_activation_amax_scale": (_is(1.0, 1), "amax margins are not built"),
         "fp8_training_weight_amax_scale": (_is(1.0, 1), "amax margins are not built"),
         "fp8_training_correction_mode": (_is("none"), "residual correction is not built"),
-        "fp8_training_moe_grouped_backend": (_is("triton_grouped"), "the grouped fp8 GEMM has one backend: the tcgen05 block-scaled kernel"),
         "enable_compile": (_falsy, "there is no tracing compiler on any path"),
     },
     "lora": {

@@ -143,19 +143,18 @@ class ShardedAnyPrecisionAdamW(ShardedOptimizer):
 
     def __init__(self, engine, lr, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0,
                  state_dtype=torch.bfloat16, cautious_weight_decay=False, state_cpu_offload: bool = False,
-                 denominator_chunk_size: int = 0, reuse_grad_for_momentum: bool = False, **kw):
+                 denominator_chunk_size: int = 0, **kw):
         """``state_cpu_offload``: the moments live in (pinned) host memory and visit the device one parameter
         group at a time during the step, the next group's moments copied in while the current one updates.
         ``denominator_chunk_size``: elements per pass of the update, which bounds its fp32 temporaries
-        (0 = a whole decay segment at once).  ``reuse_grad_for_momentum``: the scaled gradient and then the fp32
-        first moment are formed in place in the gradient shard instead of in new buffers (the gradient is
-        consumed by the step) (src/xorl/optim/anyprecision_adamw.py)."""
+        (0 = a whole decay segment at once) (src/xorl/optim/anyprecision_adamw.py).  Both leave every bit of
+        the result as it is.  The gradient shard is never written by the step: other streams (early norms,
+        the next step's gradient kernels) order themselves against reads of it only."""
         super().__init__(engine, lr, weight_decay, kw.get("no_decay_modules", ()),
                          kw.get("no_decay_params", ()))
         self.betas, self.eps, self.cautious = betas, eps, cautious_weight_decay
         self.offload = bool(state_cpu_offload)
         self.chunk = int(denominator_chunk_size or 0)
-        self.reuse_grad = bool(reuse_grad_for_momentum)
         self.exp_avg = self._new_state("exp_avg", state_dtype)
         self.exp_avg_sq = self._new_state("exp_avg_sq", state_dtype)
         if self.offload:
@@ -197,18 +196,11 @@ class ShardedAnyPrecisionAdamW(ShardedOptimizer):
                 for a in range(a0, b0, step_n):
                     b = min(b0, a + step_n)
                     p = g.master[a:b]
-                    if self.reuse_grad:
-                        gr = g.grad_shard[a:b].mul_(grad_scale)
-                        if clip_coef is not None:
-                            gr.mul_(clip_coef)
-                        v = v_all[a:b].float().mul_(b2).addcmul_(gr, gr, value=1 - b2)
-                        m = gr.mul_(1 - b1).add_(m_all[a:b].float(), alpha=b1)      # the gradient shard now holds m
-                    else:
-                        gr = g.grad_shard[a:b] * grad_scale
-                        if clip_coef is not None:
-                            gr = gr * clip_coef
-                        m = m_all[a:b].float().mul_(b1).add_(gr, alpha=1 - b1)
-                        v = v_all[a:b].float().mul_(b2).addcmul_(gr, gr, value=1 - b2)
+                    gr = g.grad_shard[a:b] * grad_scale
+                    if clip_coef is not None:
+                        gr = gr * clip_coef
+                    m = m_all[a:b].float().mul_(b1).add_(gr, alpha=1 - b1)
+                    v = v_all[a:b].float().mul_(b2).addcmul_(gr, gr, value=1 - b2)
                     m_all[a:b].copy_(m)
                     v_all[a:b].copy_(v)
                     update = (m / bc1) / ((v / bc2).sqrt_().add_(self.eps))
@@ -347,7 +339,7 @@ def build_optimizer(engine: Zero3Engine, lr: float = 1e-3, betas=(0.9, 0.95), ep
                     optimizer_kwargs: Optional[dict] = None, cautious_weight_decay: bool = False):
     kw = dict(no_decay_modules=no_decay_modules or (), no_decay_params=no_decay_params or ())
     okw = dict(optimizer_kwargs or {})
-    any_kw = {k: okw[k] for k in ("state_cpu_offload", "denominator_chunk_size", "reuse_grad_for_momentum") if okw.get(k)}
+    any_kw = {k: okw[k] for k in ("state_cpu_offload", "denominator_chunk_size") if okw.get(k)}
     if optimizer_type == "adamw" and not cautious_weight_decay and not any_kw:
         return ShardedAdamW(engine, lr, betas, eps, weight_decay, **kw)
     if optimizer_type in ("adamw", "anyprecision_adamw"):

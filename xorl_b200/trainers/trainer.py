@@ -308,8 +308,7 @@ class Trainer:
             optimizer_kwargs={k: getattr(t, k) for k in vars(t) if k.startswith("muon_")}
             if t.optimizer == "muon" else
             dict(state_cpu_offload=t.anyprecision_adamw_state_cpu_offload,
-                 denominator_chunk_size=t.anyprecision_adamw_denominator_chunk_size,
-                 reuse_grad_for_momentum=t.anyprecision_adamw_reuse_grad_for_momentum)
+                 denominator_chunk_size=t.anyprecision_adamw_denominator_chunk_size)
             if t.optimizer == "anyprecision_adamw" else None)
         self.lr_scheduler = build_lr_scheduler(self.optimizer, self.train_steps, t.lr, t.lr_min,
                                                t.lr_start, t.lr_warmup_ratio, t.lr_decay_style,
