@@ -661,6 +661,28 @@ def test_saves_are_refused_beyond_the_storage_limit(tmp_path):
         assert _poll(c, rid)["type"] == "save_weights_for_sampler"
 
 
+def test_server_arguments_reach_the_runner(tmp_path):
+    """``max_adapters_per_model``, ``enable_moe_metrics`` and ``sync_bucket_size_mb`` of the server configuration
+    are what the runner works with."""
+    from xorl_b200.parallel.state import reset_parallel_state
+    from xorl_b200.server.launcher import build_local_backend
+    from xorl_b200.server.server_arguments import ServerArguments
+    reset_parallel_state()
+    sa = ServerArguments(model_preset="tiny-qwen3-moe", output_dir=str(tmp_path / "srv"), device="cpu",
+                         sample_packing_sequence_len=256, enable_mixed_precision=False, enable_lora=True, lora_rank=4,
+                         max_adapters_per_model=2, enable_moe_metrics=False, sync_bucket_size_mb=1)
+    backend, _ = build_local_backend(sa)
+    r = backend.runner
+    assert r.moe_metrics is None
+    r.create_model("a")
+    assert r.adapters.max_adapters == 2
+    out = r.sync_inference_weights("default", backend="file", directory=str(tmp_path / "w"))
+    assert out["buckets"] > 1                                   # one-megabyte buckets, not the 1 GiB default
+    out = r.sync_inference_weights("default", backend="file", directory=str(tmp_path / "w2"), bucket_size_mb=1024)
+    assert out["buckets"] == 1
+    reset_parallel_state()
+
+
 def test_adapter_with_pending_gradients_is_not_dropped(tmp_path):
     """Without a spill directory an adapter that holds accumulated gradients is never the eviction
     victim; when every resident adapter holds some, creating another one raises."""

@@ -142,7 +142,7 @@ class SyncWeightsRequest(BaseModel):
     model_id: str = "default"
     backend: Literal["nccl_broadcast", "peer_copy", "sparse_delta", "file"] = "nccl_broadcast"
     quantization: Optional[str] = None
-    bucket_size_mb: int = 1024
+    bucket_size_mb: Optional[int] = None            # None: the server's sync_bucket_size_mb
 
 
 class SetSyncQuantizationRequest(BaseModel):

@@ -179,7 +179,8 @@ def build_local_backend(sargs: ServerArguments):
     """Trainer + runner in this process (every rank calls this)."""
     from ..trainers.trainer import Trainer
     trainer = Trainer(sargs.to_trainer_arguments())
-    runner = ModelRunner(trainer)
+    runner = ModelRunner(trainer, max_adapters=sargs.max_adapters_per_model, moe_metrics=sargs.enable_moe_metrics,
+                         sync_bucket_size_mb=sargs.sync_bucket_size_mb)
     world = dist.get_world_size() if dist.is_initialized() else 1
     if world == 1:
         return LocalBackend(runner), None

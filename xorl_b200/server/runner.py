@@ -40,8 +40,14 @@ def validate_token_ids(datums: List[Dict[str, Any]], vocab_size: int) -> None:
 
 
 class ModelRunner:
-    def __init__(self, trainer):
+    def __init__(self, trainer, max_adapters: Optional[int] = None, moe_metrics: bool = True,
+                 sync_bucket_size_mb: Optional[int] = None):
+        """``max_adapters``: adapters kept per base model (the active one included; default
+        ``XORL_MAX_ADAPTERS_PER_MODEL`` or 8); ``moe_metrics``: expert-load statistics per forward_backward;
+        ``sync_bucket_size_mb``: default bucket of a weight sync that names none."""
         self.trainer = trainer
+        self.max_adapters = max_adapters
+        self.sync_bucket_size_mb = sync_bucket_size_mb
         self.engine = trainer.engine
         self.optimizer = trainer.optimizer
         self.model = trainer.model
@@ -61,7 +67,7 @@ class ModelRunner:
         self.moe_metrics = None
         n_exp = int(getattr(self.model.config, "num_experts", 0) or 0)
         if n_exp > 0 and os.environ.get("XORL_ENABLE_MOE_METRICS", "1") != "0" \
-                and getattr(trainer, "enable_moe_metrics", True):
+                and moe_metrics and getattr(trainer, "enable_moe_metrics", True):
             from ..utils.moe_metrics import ExpertLoadTracker
             self.moe_metrics = ExpertLoadTracker(n_exp, self.output_dir, self.ps.rank, self.ps.group("dp"))
             self.engine.expert_load_tracker = self.moe_metrics
@@ -103,7 +109,8 @@ class ModelRunner:
             raise ValueError("create_model needs a server started with enable_lora")
         if self.adapters is None:
             from .adapters import AdapterManager
-            self.adapters = AdapterManager(self, spill_dir=os.path.join(self.output_dir, "adapter_spill"))
+            self.adapters = AdapterManager(self, max_adapters=self.max_adapters,
+                                           spill_dir=os.path.join(self.output_dir, "adapter_spill"))
         self.adapters.create(model_id, lora_config)
         return {"model_id": model_id, "adapters": self.adapters.list(),
                 "session": self.adapters.session_spec(model_id)}
@@ -442,6 +449,8 @@ class ModelRunner:
         from .weight_sync import WeightSyncHandler
         handler = getattr(self, "_sync", None) or WeightSyncHandler(self)
         self._sync = handler
+        if not kw.get("bucket_size_mb"):
+            kw["bucket_size_mb"] = int(self.sync_bucket_size_mb or 1024)
         return handler.sync(**kw)
 
     def sleep(self):
