@@ -194,3 +194,22 @@ def test_server_arguments_reject_inconsistent_settings():
                     (dict(worker_bind_address="127.0.0.1:5555"), "worker_bind_address")):
         with pytest.raises(ValueError, match=msg):
             ServerArguments(**kw)
+
+
+def test_every_server_argument_is_read_somewhere():
+    """No key of the service configuration is accepted and then ignored: each is read outside its own
+    declaration (by the launcher, the API state, the runner) or mapped into the trainer's arguments."""
+    import dataclasses
+    import glob
+    import re
+    from xorl_b200.server.server_arguments import ServerArguments
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "xorl_b200")
+    own = open(os.path.join(root, "server", "server_arguments.py")).read()
+    src = "".join(open(f).read() for f in glob.glob(os.path.join(root, "**", "*.py"), recursive=True))
+    mapped = own.split("def to_trainer_arguments")[1]
+    unused = []
+    for f in dataclasses.fields(ServerArguments):
+        elsewhere = len(re.findall(r"\.%s\b" % f.name, src)) - len(re.findall(r"self\.%s\b" % f.name, own))
+        if elsewhere <= 0 and not re.search(r"self\.%s\b" % f.name, mapped):
+            unused.append(f.name)
+    assert not unused, unused
