@@ -210,3 +210,26 @@ def test_hybrid_shared_expert_lora_under_expert_parallelism(tmp_path):
     assert curves["ep1"][-1] < curves["ep1"][0]
     for a, b in zip(curves["ep1"], curves["ep2"]):
         assert abs(a - b) < 3e-4, curves
+
+
+def test_evaluation_on_an_unsupported_layout_is_refused_at_start_up(tmp_path, monkeypatch):
+    from xorl_b200.arguments import build_args
+    from xorl_b200.models.config import preset
+    from xorl_b200.parallel import state as pstate
+    from xorl_b200.trainers.trainer import Trainer
+    pstate.reset_parallel_state()
+    args = build_args({"model": {"config_path": "tiny-qwen3"},
+                       "data": {"datasets": [{"path": "dummy", "type": "tokenized", "max_seq_len": 64, "num_samples": 16}],
+                                "sample_packing_sequence_len": 128, "val_set_size": 0.25},
+                       "train": {"output_dir": str(tmp_path / "o"), "device": "cpu", "use_wandb": False,
+                                 "save_hf_weights": False, "save_epochs": 0, "max_steps": 1}})
+    real = pstate.init_parallel_state
+
+    def fake(**kw):
+        st = real(**kw)
+        st.sizes["tp"] = 2                      # as if the body were tensor parallel
+        return st
+    monkeypatch.setattr("xorl_b200.trainers.trainer.init_parallel_state", fake)
+    with pytest.raises(NotImplementedError, match="evaluation pass"):
+        Trainer(args, model_config=preset("tiny-qwen3"))
+    pstate.reset_parallel_state()

@@ -241,6 +241,11 @@ class Trainer:
             dataset, eval_dataset = prepare_train_eval(a.data, tokenizer=self._tokenizer(),
                                                        vocab_size=self.model_config.vocab_size, seed=a.train.seed)
             if eval_dataset is not None:
+                if self.ps.tp_size > 1 or self.ps.pp_size > 1 or self.ps.sp_size > 1 \
+                        or getattr(self.ps, "lm_head_tp_size", 1) > 1:
+                    # said at start-up, not at the first checkpoint
+                    raise NotImplementedError("data.val_set_size / data.test_datasets: the evaluation pass runs on "
+                                              "data-parallel layouts (no tensor, pipeline, context or lm-head parallelism)")
                 self.eval_dataloader = self._build_eval_dataloader(eval_dataset)
         shard = None
         if self.ps.sp_size > 1:
