@@ -553,8 +553,11 @@ class Trainer:
                     self.watchdog.check()           # a dead peer is noticed before the next launch
                 t0 = time.time()
                 if self._sync_padding:
+                    # lm-head parallelism needs equal lengths inside each lm-head group only
+                    pad_group = self.ps.group("lm_head_tp") if getattr(self.ps, "lm_head_tp_size", 1) > 1 \
+                        and os.environ.get("XORL_B200_SYNC_PADDING", "0") != "1" else self.ps.group("dp")
                     micro_batches = synchronize_micro_batch_padding(
-                        micro_batches, self.ps.group("dp"), multiple_of=max(1, self.args.data.pad_to_multiple_of or 1))
+                        micro_batches, pad_group, multiple_of=max(1, self.args.data.pad_to_multiple_of or 1))
                 try:
                     with nvtx_range("train_step"):
                         out = self.train_step(micro_batches)
