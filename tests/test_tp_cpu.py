@@ -99,3 +99,19 @@ def test_fsdp_sharded_lm_head_loss_matches_plain_data_parallel(tmp_path):
         assert json.load(f)["lm_head_rows_per_rank"] == 512
     for a, b in zip(ref, got):
         assert abs(a - b) < 2e-4, (ref, got)
+
+
+@pytest.mark.distributed
+def test_lm_head_tp2_on_four_ranks_shards_the_head_rows_over_their_replicas(tmp_path):
+    """Four data-parallel ranks in two lm-head groups of two: each half of the vocabulary rows lives on two
+    ranks (one per group) and is ZeRO-sharded over that pair; gradients of a row reach it from both groups.
+    Same loss curve as plain data parallelism over the four ranks."""
+    from dist_utils import run_distributed
+    run_distributed("-m", 4, "xorl_b200.cli.train", _cfg(tmp_path, "dp4", max_grad_norm=0.5, gradient_accumulation_steps=2))
+    ref = _losses(tmp_path, "dp4")
+    cfg = _cfg(tmp_path, "lmtp4", lm_head_tensor_parallel_size=2, max_grad_norm=0.5, gradient_accumulation_steps=2)
+    run_distributed("-m", 4, "xorl_b200.cli.train", cfg)
+    got = _losses(tmp_path, "lmtp4")
+    assert len(got) == len(ref) == 3
+    for a, b in zip(ref, got):
+        assert abs(a - b) < 2e-4, (ref, got)
