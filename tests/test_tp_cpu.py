@@ -69,10 +69,20 @@ def test_lm_head_only_tp2_matches_plain_data_parallel(tmp_path):
     from dist_utils import run_distributed
     run_distributed("-m", 2, "xorl_b200.cli.train", _cfg(tmp_path, "dp", max_grad_norm=0.5, max_steps=4))
     ref = _losses(tmp_path, "dp")
-    cfg = _cfg(tmp_path, "lmtp", lm_head_tensor_parallel_size=2, max_grad_norm=0.5, max_steps=4, save_steps=2)
+    cfg = _cfg(tmp_path, "lmtp", lm_head_tensor_parallel_size=2, max_grad_norm=0.5, max_steps=4, save_steps=2,
+               save_hf_weights=True)
     run_distributed("-m", 2, "xorl_b200.cli.train", cfg)
     got = _losses(tmp_path, "lmtp")
     assert len(got) == 4
+    # the Hugging Face export holds the whole lm-head, gathered over the lm-head group
+    from safetensors import safe_open
+    hf = tmp_path / "lmtp" / "global_step_4" / "hf_ckpt"
+    shapes = {}
+    for f in os.listdir(hf):
+        if f.endswith(".safetensors"):
+            with safe_open(str(hf / f), "pt") as fh:
+                shapes.update({k: tuple(fh.get_slice(k).get_shape()) for k in fh.keys()})
+    assert shapes["lm_head.weight"] == (1024, shapes["model.embed_tokens.weight"][1]), shapes.get("lm_head.weight")
     with open(tmp_path / "lmtp" / "startup_metrics.json") as f:
         assert json.load(f)["lm_head_rows_per_rank"] == 512          # half of the tiny model's 1024 rows
     for a, b in zip(ref, got):
