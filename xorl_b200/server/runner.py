@@ -62,6 +62,8 @@ class ModelRunner:
         self.adapters = None                 # AdapterManager, created with the first extra adapter
         from .side_payloads import FilesystemPayloadStore, RoutingPayloads
         self.payloads = RoutingPayloads(FilesystemPayloadStore(os.path.join(self.output_dir, "side_payloads")))
+        if self.ps.rank == 0:
+            self.payloads.store.sweep()          # chunks a crashed predecessor left behind (older than the time-to-live)
         self.host_group = None               # gloo group of all ranks (set by the dispatcher); None: default group
         # expert-load metrics of MoE models: one JSON line per forward_backward in moe_metrics.jsonl
         self.moe_metrics = None
