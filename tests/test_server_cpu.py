@@ -477,6 +477,13 @@ def test_dispatcher_two_ranks_agree_on_errors(tmp_path):
 
 
 @pytest.mark.distributed
+def test_adapter_replicas_are_compared_after_optimizer_steps(tmp_path):
+    from dist_utils import run_distributed
+    out = run_distributed(os.path.join(os.path.dirname(__file__), "server_replica_check_worker.py"), 2, str(tmp_path))
+    assert "REPLICA_CHECK_OK" in out
+
+
+@pytest.mark.distributed
 def test_routing_replay_travels_beside_the_broadcast_command(tmp_path):
     from dist_utils import run_distributed
     out = run_distributed(os.path.join(os.path.dirname(__file__), "server_routing_payload_worker.py"), 2, str(tmp_path))
